@@ -1,0 +1,98 @@
+"""One step's batch as flat device arrays.
+
+A step is a list of (request, its next tokens, wanted positions).  All tokens
+of all entries form one flat list of ``N`` rows; per-token and per-sequence
+index arrays say where each row belongs.  Everything that varies from step to
+step lives in one int32 device buffer, filled by a single host→device copy:
+
+    token_ids[N] positions[N] seq_of_token[N] q_start[B+1] ctx_len[B]
+    slot_ids[B] logit_rows[M] block_table_g[B, W_g] for every cache group g
+
+``positions`` are absolute (crates/leone/src/cpu.rs:1759-1765: prefill position
+= start + t); ``ctx_len`` is a sequence's length after this step, so the query
+at position p reads keys ``..p`` (the reference masks by loop bound,
+crates/leone/src/cpu.rs:2372).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..parts.base import PagedCacheView, StateView
+
+
+@dataclass
+class StepEntry:
+    rid: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+class StepContext:
+    """Device views of one step's metadata plus what the parts need to find their caches."""
+
+    def __init__(self):
+        self.n_tokens = 0
+        self.n_seqs = 0
+        self.n_logit_rows = 0
+        self.token_ids = self.positions = self.seq_of_token = None
+        self.q_start = self.ctx_len = self.slot_ids = self.logit_rows = None
+        self.block_tables: List[torch.Tensor] = []
+        self.q_lens: np.ndarray = None
+        self.starts: np.ndarray = None
+        self.ctx_lens: np.ndarray = None
+        self.max_q_len = 0
+        self.max_ctx_len = 0
+        self.decode_only = False
+        self.status: torch.Tensor = None
+        self.logits_out: Optional[torch.Tensor] = None
+        self.layer_caches: Dict[int, object] = {}
+        self.fixed_shapes = False      # True while a CUDA graph is captured or replayed
+
+    def cache_view(self, layer_index: int):
+        return self.layer_caches.get(layer_index)
+
+
+def pack_metadata(token_lists: Sequence[Sequence[int]], starts: Sequence[int], slots: Sequence[int],
+                  wants: Sequence[Sequence[int]], block_tables: Sequence[np.ndarray]):
+    """Host side of the layout above.  Returns (packed int32 array, offsets dict, host stats)."""
+    b = len(token_lists)
+    q_lens = np.array([len(t) for t in token_lists], dtype=np.int64)
+    n = int(q_lens.sum())
+    q_start = np.zeros(b + 1, dtype=np.int64)
+    np.cumsum(q_lens, out=q_start[1:])
+    starts = np.asarray(starts, dtype=np.int64)
+    token_ids = np.concatenate([np.asarray(t, dtype=np.int64) for t in token_lists]) if n else np.zeros(0, np.int64)
+    seq_of_token = np.repeat(np.arange(b, dtype=np.int64), q_lens)
+    positions = np.arange(n, dtype=np.int64) - q_start[seq_of_token] + starts[seq_of_token]
+    ctx_len = starts + q_lens
+    rows: List[int] = []
+    for i, w in enumerate(wants):
+        for j in w:
+            if not 0 <= j < q_lens[i]:
+                raise ValueError(f"entry {i}: wanted place {j} is outside its {q_lens[i]} tokens")
+            rows.append(int(q_start[i]) + int(j))
+    pieces = [token_ids, positions, seq_of_token, q_start, ctx_len, np.asarray(slots, dtype=np.int64),
+              np.asarray(rows, dtype=np.int64)]
+    names = ["token_ids", "positions", "seq_of_token", "q_start", "ctx_len", "slot_ids", "logit_rows"]
+    offsets = {}
+    cursor = 0
+    for name, piece in zip(names, pieces):
+        offsets[name] = (cursor, piece.size)
+        cursor += piece.size
+    bt_offsets = []
+    for bt in block_tables:
+        bt_offsets.append((cursor, bt.shape))
+        cursor += bt.size
+    packed = np.empty(max(cursor, 1), dtype=np.int32)
+    for name, piece in zip(names, pieces):
+        o, s = offsets[name]
+        packed[o:o + s] = piece
+    for (o, shape), bt in zip(bt_offsets, block_tables):
+        packed[o:o + bt.size] = bt.reshape(-1)
+    stats = dict(n=n, b=b, m=len(rows), q_lens=q_lens, starts=starts, ctx_lens=ctx_len,
+                 max_q_len=int(q_lens.max()) if b else 0, max_ctx_len=int(ctx_len.max()) if b else 0)
+    return packed, offsets, bt_offsets, stats

@@ -1,0 +1,278 @@
+"""The engine: a model, its cache and the one step function.
+
+``Engine.step`` takes a batch of (request, its next tokens, wanted places) —
+portions of prompts beside single decoded tokens, cut anywhere — runs exactly
+those tokens as one flat batch against what earlier steps left in the cache,
+and returns the fp32 logits at the wanted places.  The reference runs prompt
+portions one request at a time and then one shared decode pass
+(crates/leone-cli/src/server.rs:3667-3938, crates/leone/src/runtime.rs:7461);
+here both kinds of rows go through the same kernels in the same launches.
+
+The step is a transaction on the cache (crates/leone/src/kv.rs:326-347):
+pages for every token of the step are taken before anything runs, lengths
+advance only after the step succeeded, and a failure gives the pages back.
+"""
+from __future__ import annotations
+
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.pages import CacheManager, GroupSpec, OutOfPages
+from ..parts.base import FixedState, PagedCacheView, PagedKV, Runtime, StateView
+from ..parts.spec import ModelSpec
+from ..registry import config_from_folder, spec_from_config
+from ..weights.loader import load_checkpoint
+from ..weights.random_init import random_tensors
+from .batch import StepContext, StepEntry, pack_metadata
+from .model import Model
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
+           "float32": torch.float32, "fp32": torch.float32, "f32": torch.float32}
+
+
+class StepError(RuntimeError):
+    """A kernel reported a fault through the status word (bad token id, bad page, ...)."""
+
+
+def parse_dtype(dtype) -> torch.dtype:
+    if isinstance(dtype, torch.dtype):
+        return dtype
+    if dtype not in _DTYPES:
+        raise ValueError(f"dtype must be one of {sorted(_DTYPES)}, got {dtype!r}")
+    return _DTYPES[dtype]
+
+
+def default_ops(device, dtype):
+    """The CUDA kernels.  There is no other product path: this raises without them."""
+    from ..ops.cuda import CudaOps
+    return CudaOps(device, dtype)
+
+
+class Engine:
+    def __init__(self, spec: ModelSpec, tensors: Optional[Dict[str, torch.Tensor]] = None, *,
+                 dtype="bfloat16", device="cuda:0", page_tokens: int = 16,
+                 max_tokens: Optional[int] = None, num_pages: Optional[int] = None,
+                 max_requests: int = 64, max_batch_tokens: int = 2048, ops=None,
+                 folder: Optional[str] = None, random_seed: Optional[int] = None):
+        self.dtype = parse_dtype(dtype)
+        self.device = torch.device(device)
+        self.spec = spec
+        if ops is None:
+            ops = default_ops(self.device, self.dtype)
+        self.ops = ops
+        self.rt = Runtime(self.device, self.dtype, ops, max_batch_tokens)
+        self.max_batch_tokens = max_batch_tokens
+        self.model = Model(spec, self.rt)
+        specs = self.model.weight_specs()
+        if tensors is None and folder is not None:
+            from ..weights.safetensors import Checkpoint
+            probe = Checkpoint(folder)
+            notes = self.model.load_notes(set(probe.names()))
+            probe.close()
+            tensors = load_checkpoint(folder, specs, self.dtype, self.device, notes)
+        elif tensors is None:
+            if random_seed is None:
+                raise ValueError("an engine needs a model folder, tensors or a random seed")
+            tensors = self._random_on_device(specs, random_seed)
+        else:
+            from ..weights.loader import check_names_and_shapes, target_dtype
+            check_names_and_shapes(specs, tensors, self.model.load_notes(set(tensors)))
+            by_name = {s.name: s for s in specs}
+            tensors = {n: t.to(target_dtype(by_name[n], t.dtype, self.dtype)).to(self.device).contiguous()
+                       for n, t in tensors.items()}
+        self.model.load(tensors)
+        del tensors
+
+        # -- cache ----------------------------------------------------------------------
+        self.page_tokens = page_tokens
+        if num_pages is None:
+            if max_tokens is None:
+                max_tokens = max_requests * 256
+            num_pages = -(-max_tokens // page_tokens)
+        self.num_pages = num_pages
+        self.max_requests = max_requests
+        requests = self.model.cache_requests()
+        group_specs: List[GroupSpec] = []
+        self._layer_group: Dict[int, tuple] = {}      # layer -> (gid, index within group)
+        self._layer_state: Dict[int, torch.Tensor] = {}
+        for li, req in enumerate(requests):
+            if isinstance(req, PagedKV):
+                gs = GroupSpec("window" if req.window else "full", req.num_kv_heads, req.head_dim,
+                               req.window)
+                for gid, existing in enumerate(group_specs):
+                    if existing.key() == gs.key():
+                        break
+                else:
+                    gid = len(group_specs)
+                    group_specs.append(gs)
+                self._layer_group[li] = (gid, len(group_specs[gid].layers))
+                group_specs[gid].layers.append(li)
+            elif isinstance(req, FixedState):
+                self._layer_state[li] = torch.zeros((max_requests,) + tuple(req.shape),
+                                                    dtype=torch.float32, device=self.device)
+            elif req is not None:
+                raise TypeError(f"layer {li}: unknown cache request {req!r}")
+        self.cache = CacheManager(group_specs, page_tokens, num_pages, max_requests)
+        self.pools = []
+        for gs in group_specs:
+            shape = (len(gs.layers), num_pages, gs.num_kv_heads, page_tokens, gs.head_dim)
+            self.pools.append((torch.zeros(shape, dtype=self.dtype, device=self.device),
+                               torch.zeros(shape, dtype=self.dtype, device=self.device)))
+        self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self._meta_dev = None
+        self._meta_host = None
+        self._meta_event = None
+        self.steps_run = 0
+
+    # -- construction helpers -----------------------------------------------------------
+    @classmethod
+    def from_folder(cls, folder: str, **kw) -> "Engine":
+        config = config_from_folder(folder)
+        return cls(spec_from_config(config), folder=folder, **kw)
+
+    @classmethod
+    def from_config(cls, config, seed: int = 0, **kw) -> "Engine":
+        """Random weights drawn on the device; nothing is written to disk."""
+        return cls(spec_from_config(config), random_seed=seed, **kw)
+
+    def _random_on_device(self, specs, seed):
+        from ..weights.loader import target_dtype
+        out = {}
+        for spec in specs:
+            from ..weights.random_init import draw
+            t = draw(spec, seed, self.device)
+            out[spec.name] = t.to(target_dtype(spec, torch.float32, self.dtype))
+        return out
+
+    # -- request lifetime ---------------------------------------------------------------
+    def open(self, rid: Hashable) -> int:
+        slot = self.cache.open(rid)
+        for state in self._layer_state.values():
+            state[slot].zero_()
+        return slot
+
+    def close(self, rid: Hashable) -> None:
+        self.cache.close(rid)
+
+    def length(self, rid: Hashable) -> int:
+        return self.cache.length(rid)
+
+    # -- the step -----------------------------------------------------------------------
+    def _stage(self, packed: np.ndarray) -> torch.Tensor:
+        n = packed.size
+        if self._meta_dev is None or self._meta_dev.numel() < n:
+            cap = max(4096, 2 * n)
+            self._meta_dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+            if self.device.type == "cuda":
+                self._meta_host = torch.empty(cap, dtype=torch.int32, pin_memory=True)
+                self._meta_event = torch.cuda.Event()
+            else:
+                self._meta_host = torch.empty(cap, dtype=torch.int32)
+        elif self._meta_event is not None:
+            self._meta_event.synchronize()     # the last copy out of the staging buffer is done
+        self._meta_host[:n].numpy()[:] = packed
+        self._meta_dev[:n].copy_(self._meta_host[:n], non_blocking=True)
+        if self._meta_event is not None:
+            self._meta_event.record()
+        return self._meta_dev
+
+    def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
+        rids = [e.rid for e in entries]
+        starts = [self.cache.length(r) for r in rids]
+        slots = [self.cache.slot(r) for r in rids]
+        tables = [self.cache.block_table(g.gid, rids) for g in self.cache.groups]
+        packed, offsets, bt_offsets, stats = pack_metadata(
+            [e.tokens for e in entries], starts, slots, [e.want for e in entries], tables)
+        dev = self._stage(packed)
+        ctx = StepContext()
+        for name, (o, s) in offsets.items():
+            setattr(ctx, name, dev[o:o + s])
+        ctx.block_tables = [dev[o:o + shape[0] * shape[1]].view(shape) for o, shape in bt_offsets]
+        ctx.n_tokens, ctx.n_seqs, ctx.n_logit_rows = stats["n"], stats["b"], stats["m"]
+        ctx.q_lens, ctx.starts, ctx.ctx_lens = stats["q_lens"], stats["starts"], stats["ctx_lens"]
+        ctx.max_q_len, ctx.max_ctx_len = stats["max_q_len"], stats["max_ctx_len"]
+        ctx.decode_only = stats["max_q_len"] == 1
+        ctx.status = self.status
+        self._attach_caches(ctx)
+        return ctx
+
+    def _attach_caches(self, ctx: StepContext) -> None:
+        for li, layer in enumerate(self.spec.layers):
+            src = li if layer.cache_of is None else layer.cache_of
+            writes = layer.cache_of is None
+            if src in self._layer_group:
+                gid, k = self._layer_group[src]
+                kp, vp = self.pools[gid]
+                ctx.layer_caches[li] = PagedCacheView(kp[k], vp[k], ctx.block_tables[gid],
+                                                      self.page_tokens, writes)
+            elif src in self._layer_state:
+                ctx.layer_caches[li] = StateView(self._layer_state[src], writes)
+
+    def step(self, entries: Sequence, check: bool = True) -> Optional[torch.Tensor]:
+        """Run one batch.  ``entries``: ``StepEntry`` or ``(rid, tokens, want)`` tuples.
+
+        Returns fp32 logits ``[wanted, vocab]`` in the order of the entries and of each
+        entry's ``want`` (``None`` if nothing is wanted).  Raises :class:`OutOfPages`
+        without changing anything if the pool cannot hold the step's tokens.
+        """
+        entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
+        if not entries:
+            return None
+        seen = set()
+        total = 0
+        for e in entries:
+            if e.rid in seen:
+                raise ValueError(f"request {e.rid!r} appears twice in one step")
+            seen.add(e.rid)
+            if len(e.tokens) == 0:
+                raise ValueError(f"request {e.rid!r}: a step entry needs at least one token")
+            bad = [t for t in e.tokens if not 0 <= int(t) < self.spec.vocab_size]
+            if bad:
+                raise ValueError(f"request {e.rid!r}: token ids {bad[:8]} are outside the "
+                                 f"vocabulary of {self.spec.vocab_size}")
+            total += len(e.tokens)
+        if total > self.rt.max_tokens:
+            raise ValueError(f"step has {total} tokens; this engine was built for at most "
+                             f"{self.rt.max_tokens} per step")
+        opened = []
+        try:
+            for e in entries:
+                if not self.cache.is_open(e.rid):
+                    self.open(e.rid)
+                    opened.append(e.rid)
+            wants = {}
+            for e in entries:
+                new_len = self.cache.length(e.rid) + len(e.tokens)
+                if new_len > self.spec.max_positions:
+                    raise ValueError(f"request {e.rid!r}: {new_len} tokens exceed the model's "
+                                     f"{self.spec.max_positions} positions")
+                wants[e.rid] = new_len
+            self.cache.reserve(wants)
+        except Exception:
+            for rid in opened:
+                self.cache.close(rid)
+            raise
+        try:
+            ctx = self.build_context(entries)
+            logits = self.model.forward(ctx)
+            if check:
+                self.check_status()
+        except Exception:
+            for e in entries:
+                self.cache.rollback(e.rid)
+            for rid in opened:
+                self.cache.close(rid)
+            raise
+        for e in entries:
+            self.cache.commit(e.rid, wants[e.rid])
+        self.steps_run += 1
+        return logits
+
+    def check_status(self) -> None:
+        word = self.status.tolist()
+        if word[0] != 0:
+            self.status.zero_()
+            raise StepError(f"kernel status {word[0]:#x} (detail {word[1]}, {word[2]}, {word[3]}): "
+                            + self.ops.describe_status(word[0]))

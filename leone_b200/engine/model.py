@@ -1,0 +1,137 @@
+"""A model built from a :class:`ModelSpec`: embedding, layers in run order, final norm, head.
+
+The forward pass runs only the tokens of the step: embedding gather
+(crates/leone/src/runtime.rs:6686-6692), the layers in ``run_order``, then the
+final norm and the output head on the wanted rows only
+(crates/leone/src/runtime.rs:7428-7452, 6542-6608).  A tied head reads the
+embedding table (crates/leone/src/model.rs:452-471).
+"""
+from __future__ import annotations
+
+import inspect
+from typing import Dict, List, Optional
+
+import torch
+
+from .. import parts as _parts  # noqa: F401  (registers built-in parts)
+from ..parts.base import FixedState, PagedKV, Runtime, WeightSpec
+from ..parts.spec import ModelSpec
+from ..registry import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, spec_from_config
+
+
+class _Prefixed:
+    """Gives a part its tensors under the names it declared, from the checkpoint's full names."""
+
+    def __init__(self, prefix: str, part):
+        self.prefix = prefix
+        self.part = part
+
+    def full_specs(self) -> List[WeightSpec]:
+        return [WeightSpec(f"{self.prefix}.{s.name}", s.shape, s.role, s.std)
+                for s in self.part.weight_specs()]
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.part.load({s.name: tensors[f"{self.prefix}.{s.name}"] for s in self.part.weight_specs()})
+
+
+def _build_mixer(spec, rt, position_encodings):
+    cls = MIXERS.get(spec.kind)
+    if "position_encodings" in inspect.signature(cls.__init__).parameters:
+        return cls(dict(spec.params), rt, position_encodings=position_encodings)
+    return cls(dict(spec.params), rt)
+
+
+class Model:
+    def __init__(self, spec: ModelSpec, rt: Runtime):
+        spec.validate()
+        self.spec = spec
+        self.rt = rt
+        self.hidden_size = spec.hidden_size
+        self.vocab_size = spec.vocab_size
+        self.position_encodings = {
+            name: POSITION_ENCODINGS.get(ps.kind)(dict(ps.params), rt)
+            for name, ps in spec.position_encodings.items()}
+        self.blocks = []
+        self._holders: List[_Prefixed] = []
+        for layer in spec.layers:
+            mixer = _build_mixer(layer.mixer, rt, self.position_encodings)
+            ffn = FEED_FORWARDS.get(layer.feed_forward.kind)(dict(layer.feed_forward.params), rt)
+            n1 = NORMS.get(layer.mixer_norm.kind)(dict(layer.mixer_norm.params), rt)
+            n2 = NORMS.get(layer.ffn_norm.kind)(dict(layer.ffn_norm.params), rt)
+            self.blocks.append(BLOCKS.get(layer.block)(mixer, ffn, n1, n2))
+            self._holders += [_Prefixed(layer.prefix, p) for p in (mixer, ffn, n1, n2)]
+        self.final_norm = NORMS.get(spec.final_norm.kind)(
+            {**spec.final_norm.params, "name": spec.final_norm_name}, rt)
+        self.embedding = None
+        self.lm_head = None
+
+    # -- weights ----------------------------------------------------------------------
+    def weight_specs(self) -> List[WeightSpec]:
+        s = self.spec
+        specs = [WeightSpec(s.embedding_name, (s.vocab_size, s.hidden_size), role="embedding")]
+        for holder in self._holders:
+            specs += holder.full_specs()
+        specs += self.final_norm.weight_specs()
+        if s.lm_head_name is not None:
+            specs.append(WeightSpec(s.lm_head_name, (s.vocab_size, s.hidden_size)))
+        return specs
+
+    def load_notes(self, names) -> List[str]:
+        """Extra findings for the weight error: a tied model whose file still has a head."""
+        if self.spec.lm_head_name is None and "lm_head.weight" in names:
+            return ["lm_head.weight is present although the configuration ties the head to "
+                    "the embedding table"]
+        return []
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        s = self.spec
+        self.embedding = tensors[s.embedding_name]
+        for holder in self._holders:
+            holder.load(tensors)
+        self.final_norm.load({s.final_norm_name: tensors[s.final_norm_name]})
+        head = self.embedding if s.lm_head_name is None else tensors[s.lm_head_name]
+        self.lm_head = self.rt.ops.prepare_matrix(head)
+
+    # -- cache needs ------------------------------------------------------------------
+    def cache_requests(self):
+        """Per layer: ``PagedKV``, ``FixedState`` or ``None`` (also ``None`` for borrowers)."""
+        out = []
+        for layer, block in zip(self.spec.layers, self.blocks):
+            out.append(None if layer.cache_of is not None else block.mixer.cache_request())
+        return out
+
+    def decode_weight_bytes(self) -> int:
+        """Bytes of weights one decode step reads: every layer once per run, the head once
+        (the reference's per-step accounting, crates/leone/src/model.rs:306-323)."""
+        total = 0
+        for idx in self.spec.run_order:
+            block = self.blocks[idx]
+            for part in (block.mixer, block.feed_forward):
+                if hasattr(part, "weight_bytes"):
+                    total += part.weight_bytes()
+        total += self.vocab_size * self.hidden_size * self.rt.dtype.itemsize
+        return total
+
+    # -- forward ----------------------------------------------------------------------
+    def forward(self, ctx) -> Optional[torch.Tensor]:
+        rt = self.rt
+        hidden = rt.buffer("hidden", ctx.n_tokens, self.hidden_size, torch.float32)
+        rt.ops.embedding(self.embedding, ctx.token_ids, hidden, ctx.status)
+        for idx in self.spec.run_order:
+            self.blocks[idx].forward(ctx, ctx.cache_view(idx), hidden)
+        return self.logits(ctx, hidden)
+
+    def logits(self, ctx, hidden) -> Optional[torch.Tensor]:
+        m = ctx.n_logit_rows
+        if m == 0:
+            return None
+        x = self.final_norm.forward(ctx, hidden, rows=ctx.logit_rows, out_name="final_normed")
+        out = ctx.logits_out if ctx.logits_out is not None else torch.empty(
+            (m, self.vocab_size), dtype=torch.float32, device=self.rt.device)
+        self.rt.ops.linear(x, self.lm_head, out)
+        return out
+
+
+def weight_specs_for_config(config) -> List[WeightSpec]:
+    spec = spec_from_config(config)
+    return Model(spec, Runtime("cpu", torch.float32, None, 0)).weight_specs()

@@ -1,0 +1,106 @@
+"""Causal grouped-query attention over a paged cache.
+
+One step of the reference's layer (crates/leone/src/runtime.rs:9111-9157):
+``q, k, v = W_qkv x``; per-head RMSNorm of q and k with one weight ``[head_dim]``
+shared by all heads and the layer's eps, v untouched
+(crates/leone/src/model.rs:601-631, crates/leone/src/cpu.rs:802-820); rotary
+on q and k; k and v written at their positions; for a query at absolute
+position ``p`` the keys ``max(0, p-window+1) .. p`` are read with
+``kv_head = q_head // (n_q / n_kv)``, ``score = (q.k) / sqrt(head_dim)``,
+softmax and weighted sum in fp32 (crates/leone/src/cpu.rs:2299-2421); then
+``hidden += W_o attn``.  The window is this part's own parameter (``None`` =
+all keys); the reference has no windowed layer.
+
+Every size is a parameter: number of heads, groups, head size (independent of
+the hidden size), presence of the q/k norm, the position encoding and the
+window.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..registry import MIXERS
+from .base import Mixer, PagedKV, WeightSpec
+
+
+@MIXERS.register("attention")
+class Attention(Mixer):
+    def __init__(self, params, rt, position_encodings=None):
+        super().__init__(params, rt)
+        self.hidden = int(params["hidden_size"])
+        self.n_q = int(params["num_heads"])
+        self.n_kv = int(params["num_kv_heads"])
+        self.d = int(params["head_dim"])
+        if self.n_q % self.n_kv:
+            raise ValueError(f"num_heads {self.n_q} is not a multiple of num_kv_heads {self.n_kv}")
+        self.qk_norm = bool(params.get("qk_norm", False))
+        self.eps = float(params.get("qk_norm_eps", 1e-6))
+        self.window = params.get("window")
+        self.scale = float(params.get("scale", 1.0 / math.sqrt(self.d)))
+        pe_name = params.get("position_encoding")
+        self.pos = (position_encodings or {}).get(pe_name) if pe_name else None
+        if pe_name and self.pos is None:
+            raise ValueError(f"attention names position encoding '{pe_name}' that the model lacks")
+        self.names = {k: params.get(f"{k}_name", f"{k}_proj.weight") for k in ("q", "k", "v", "o")}
+        self.q_norm_name = params.get("q_norm_name", "q_norm.weight")
+        self.k_norm_name = params.get("k_norm_name", "k_norm.weight")
+        self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = None
+        self.qkv_cols = (self.n_q + 2 * self.n_kv) * self.d
+
+    def weight_specs(self):
+        specs = [WeightSpec(self.names["q"], (self.n_q * self.d, self.hidden)),
+                 WeightSpec(self.names["k"], (self.n_kv * self.d, self.hidden)),
+                 WeightSpec(self.names["v"], (self.n_kv * self.d, self.hidden)),
+                 WeightSpec(self.names["o"], (self.hidden, self.n_q * self.d))]
+        if self.qk_norm:
+            specs += [WeightSpec(self.q_norm_name, (self.d,), role="norm", std=0.1),
+                      WeightSpec(self.k_norm_name, (self.d,), role="norm", std=0.1)]
+        return specs
+
+    def load(self, tensors):
+        stacked = torch.cat([tensors[self.names["q"]], tensors[self.names["k"]],
+                             tensors[self.names["v"]]], dim=0).contiguous()
+        self.w_qkv = self.rt.ops.prepare_matrix(stacked)
+        self.w_o = self.rt.ops.prepare_matrix(tensors[self.names["o"]])
+        if self.qk_norm:
+            self.q_norm_w = tensors[self.q_norm_name]
+            self.k_norm_w = tensors[self.k_norm_name]
+
+    def weight_bytes(self):
+        return (self.qkv_cols * self.hidden + self.hidden * self.n_q * self.d) * self.rt.dtype.itemsize
+
+    def cache_request(self):
+        return PagedKV(self.n_kv, self.d, self.window)
+
+    def forward(self, ctx, cache, x, hidden):
+        rt = self.rt
+        n = x.shape[0]
+        qkv = rt.buffer("qkv", n, self.qkv_cols, rt.dtype)
+        rt.ops.linear(x, self.w_qkv, qkv)
+        table, rotary_dim, pairing = None, 0, None
+        if self.pos is not None:
+            table = self.pos.rotary_table()
+            if table is not None:
+                rotary_dim, pairing = table.shape[1] * 2, self.pos.pairing
+                if pairing != "half_split":
+                    raise ValueError(f"attention kernels rotate half-split pairs, not '{pairing}'")
+        # q/k norm, rotation and the cache write are one kernel; an encoding without a
+        # rotary table is applied by the encoding itself between norm and cache write.
+        if self.pos is not None and table is None:
+            rt.ops.qk_norm_rope_write(ctx, qkv, self.n_q, self.n_kv, self.d, self.q_norm_w,
+                                      self.k_norm_w, self.eps, None, 0, None)
+            q = qkv[:, :self.n_q * self.d].unflatten(1, (self.n_q, self.d))
+            k = qkv[:, self.n_q * self.d:(self.n_q + self.n_kv) * self.d].unflatten(1, (self.n_kv, self.d))
+            self.pos.apply(ctx, q, k)
+            rt.ops.qk_norm_rope_write(ctx, qkv, self.n_q, self.n_kv, self.d, None, None,
+                                      self.eps, None, 0, cache if cache.writes else None)
+        else:
+            rt.ops.qk_norm_rope_write(ctx, qkv, self.n_q, self.n_kv, self.d, self.q_norm_w,
+                                      self.k_norm_w, self.eps, table, rotary_dim,
+                                      cache if cache.writes else None)
+        attn = rt.buffer("attn_out", n, self.n_q * self.d, rt.dtype)
+        rt.ops.attention(ctx, qkv, attn, self.n_q, self.n_kv, self.d, self.scale,
+                         self.window, cache)
+        rt.ops.linear(attn, self.w_o, hidden, residual=hidden)

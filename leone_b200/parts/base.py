@@ -1,0 +1,161 @@
+"""Interfaces of the parts a layer is built from.
+
+A part is constructed from ``(PartSpec.params, Runtime)`` and never learns
+which model it is in.  It names the tensors it needs (:class:`WeightSpec`,
+relative to the layer's prefix), receives them in ``load`` and runs in
+``forward``.  Kinds are looked up in the registries of
+:mod:`leone_b200.registry`.
+
+Interfaces, by kind:
+
+``Norm.forward(ctx, hidden, rows=None) -> Tensor``
+    ``hidden`` is the fp32 residual stream ``[N, size]``; returns the normed
+    rows in the run dtype (``rows``: optional int32 device indices to gather).
+
+``Mixer.forward(ctx, cache, x, hidden) -> None``
+    ``x`` are the normed tokens ``[N, hidden]``; the mixer adds its output to
+    the fp32 ``hidden`` in place.  ``cache`` is what ``cache_request()`` asked
+    for: a :class:`PagedCacheView`, a :class:`StateView` or ``None``.
+
+``FeedForward.forward(ctx, x, hidden) -> None``
+    Same contract without a cache.
+
+``PositionEncoding``
+    Either offers ``rotary_table()`` (a ``[max_positions, rotary_dim/2, 2]``
+    fp32 cos/sin table that an attention kernel applies itself, with
+    ``pairing`` saying which elements form a pair) or implements
+    ``apply(ctx, q, k)`` on ``[N, heads, head_dim]`` views in place.
+
+``Block.forward(ctx, cache, hidden) -> None``
+    The arrangement of norm, mixer and feed-forward around the residual stream.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+
+@dataclass(frozen=True)
+class WeightSpec:
+    """One tensor a part reads.  ``role`` decides dtype policy and random init:
+
+    ``matrix``/``embedding``: kept in the run dtype, drawn N(0, std);
+    ``norm``: a 32-bit tensor stays 32-bit, drawn 1 + N(0, std);
+    ``vector``: like ``norm`` but drawn N(0, std);
+    ``int_table``: int32.
+    """
+    name: str
+    shape: Tuple[int, ...]
+    role: str = "matrix"
+    std: float = 0.02
+
+
+@dataclass
+class PagedKV:
+    """A mixer's request for paged keys and values."""
+    num_kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+
+@dataclass
+class FixedState:
+    """A mixer's request for fixed-size per-request state, ``shape`` per request, fp32."""
+    shape: Tuple[int, ...]
+
+
+@dataclass
+class PagedCacheView:
+    """What a mixer sees of a paged group for one layer in one step."""
+    k_pool: torch.Tensor          # [pages, kv_heads, page_tokens, head_dim]
+    v_pool: torch.Tensor
+    block_table: torch.Tensor     # int32 [B, max_blocks]; -1 where no page
+    page_tokens: int
+    writes: bool = True           # False for a layer that borrows another layer's cache
+
+
+@dataclass
+class StateView:
+    """Fixed-size state for one layer: row ``slot`` belongs to the request in that slot."""
+    state: torch.Tensor           # [num_slots, *shape] fp32
+    writes: bool = True
+
+
+class Runtime:
+    """What every part gets at construction: device, run dtype, kernels and scratch buffers."""
+
+    def __init__(self, device, dtype: torch.dtype, ops, max_tokens: int):
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"run dtype must be float32 or bfloat16, got {dtype}")
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.ops = ops
+        self.max_tokens = max_tokens
+        self._buffers: Dict[str, torch.Tensor] = {}
+
+    def buffer(self, name: str, rows: int, cols: int, dtype: torch.dtype) -> torch.Tensor:
+        """A scratch ``[rows, cols]`` view; one allocation per name, sized for ``max_tokens`` rows.
+
+        The contents are whatever the last user left.  Two buffers of different
+        names never overlap; the same name is the same memory.
+        """
+        cap_rows = max(rows, self.max_tokens)
+        key = f"{name}/{cols}/{dtype}"
+        buf = self._buffers.get(key)
+        if buf is None or buf.shape[0] < cap_rows:
+            buf = torch.empty((cap_rows, cols), dtype=dtype, device=self.device)
+            self._buffers[key] = buf
+        return buf[:rows]
+
+
+class Part:
+    def __init__(self, params: dict, rt: Runtime):
+        self.params = params
+        self.rt = rt
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return []
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        pass
+
+
+class Norm(Part):
+    def forward(self, ctx, hidden, rows=None):
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    def cache_request(self):
+        return None
+
+    def forward(self, ctx, cache, x, hidden):
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, ctx, x, hidden):
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    pairing: Optional[str] = None
+
+    def rotary_table(self) -> Optional[torch.Tensor]:
+        return None
+
+    def apply(self, ctx, q, k):
+        raise NotImplementedError
+
+
+class Block:
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, ffn_norm: Norm):
+        self.mixer = mixer
+        self.feed_forward = feed_forward
+        self.mixer_norm = mixer_norm
+        self.ffn_norm = ffn_norm
+
+    def forward(self, ctx, cache, hidden):
+        raise NotImplementedError

@@ -1,0 +1,259 @@
+"""A plain, slow implementation of the Qwen3 dense decoder for the tests.
+
+Whole sequences, no cache, one function per part, float64 by default.  It
+shares no code with ``leone_b200``: it reads ``config.json`` keys and
+safetensors names itself.  It rests on the reference's formulas (each
+function cites the file and line it restates); the reference's model code is
+Rust and cannot be compiled or imported here, so nothing but the attention
+oracle under ``tests/golden`` is checked against running reference code.
+"""
+from __future__ import annotations
+
+import json
+import math
+import os
+import struct
+
+import numpy as np
+import torch
+
+DT = torch.float64
+
+
+# ---------------------------------------------------------------------------------------
+# reading a model folder (independent of the engine's loader)
+# ---------------------------------------------------------------------------------------
+def read_folder(folder):
+    with open(os.path.join(folder, "config.json")) as fh:
+        cfg = json.load(fh)
+    path = os.path.join(folder, "model.safetensors")
+    with open(path, "rb") as fh:
+        (hlen,) = struct.unpack("<Q", fh.read(8))
+        header = json.loads(fh.read(hlen))
+        data = fh.read()
+    np_types = {"F32": np.float32, "F16": np.float16, "I32": np.int32}
+    tensors = {}
+    for name, meta in header.items():
+        if name == "__metadata__":
+            continue
+        b, e = meta["data_offsets"]
+        raw = data[b:e]
+        if meta["dtype"] == "BF16":
+            u16 = np.frombuffer(raw, dtype=np.uint16).astype(np.uint32) << 16
+            arr = u16.view(np.float32)
+        else:
+            arr = np.frombuffer(raw, dtype=np_types[meta["dtype"]])
+        tensors[name] = torch.from_numpy(arr.astype(np.float64).reshape(meta["shape"]))
+    return cfg, tensors
+
+
+def round_bf16(t):
+    """Round to bfloat16 and back: what a bfloat16 run keeps of a matrix."""
+    return t.to(torch.float32).to(torch.bfloat16).to(t.dtype)
+
+
+# ---------------------------------------------------------------------------------------
+# parts
+# ---------------------------------------------------------------------------------------
+def embedding(table, ids):
+    """h[t,:] = E[id_t,:], no scale (crates/leone/src/cpu.rs:1243-1265)."""
+    return table[torch.as_tensor(ids, dtype=torch.long)]
+
+
+def rms_norm(x, weight, eps):
+    """y = x * w / sqrt(mean(x^2) + eps); weight multiplies directly
+    (crates/leone/src/cpu.rs:1642-1663)."""
+    ms = (x * x).sum(dim=-1, keepdim=True) / x.shape[-1]
+    return x * weight / torch.sqrt(ms + eps)
+
+
+def linear(x, w):
+    """y[r] = sum_c W[r,c] x[c], no bias (crates/leone/src/cpu.rs:1622-1640)."""
+    return x @ w.t()
+
+
+def rope_half_split(x, positions, theta, rotary_dim=None):
+    """Half-split rotary: pair i = (i, i+half); inv_i = theta^(-2i/d), angle = pos*inv_i in
+    float64 (crates/leone/src/cpu.rs:1735-1745, 1747-1779).  ``x``: [T, heads, d]."""
+    d = x.shape[-1]
+    rd = d if rotary_dim is None else rotary_dim
+    half = rd // 2
+    inv = torch.tensor([float(theta) ** (-2.0 * i / rd) for i in range(half)], dtype=torch.float64)
+    ang = torch.as_tensor(positions, dtype=torch.float64)[:, None] * inv[None, :]
+    cos, sin = torch.cos(ang)[:, None, :].to(x.dtype), torch.sin(ang)[:, None, :].to(x.dtype)
+    out = x.clone()
+    a, b = x[..., :half], x[..., half:rd]
+    out[..., :half] = a * cos - b * sin
+    out[..., half:rd] = a * sin + b * cos
+    return out
+
+
+def attention(q, k, v, positions, scale=None, window=None):
+    """Causal grouped-query attention, one query row at a time.
+
+    kv_head = q_head // (n_q/n_kv); score = (q.k) * 1/sqrt(d); the query at absolute
+    position p reads keys 0..p (crates/leone/src/cpu.rs:2299-2421; mask by loop bound,
+    :2372).  ``window`` (not in the reference) limits keys to p-window+1..p.
+    q: [T, n_q, d], k/v: [T, n_kv, d] for the whole sequence from position 0;
+    ``positions[t]`` is row t's absolute position and equals its row index in k/v.
+    """
+    t_len, n_q, d = q.shape
+    n_kv = k.shape[1]
+    g = n_q // n_kv
+    scale = 1.0 / math.sqrt(d) if scale is None else scale
+    out = torch.zeros_like(q)
+    for t in range(t_len):
+        p = int(positions[t])
+        lo = 0 if window is None else max(0, p - window + 1)
+        for h in range(n_q):
+            kh = h // g
+            s = (k[lo:p + 1, kh, :] @ q[t, h, :]) * scale
+            w = torch.exp(s - s.max())
+            out[t, h, :] = (w[:, None] * v[lo:p + 1, kh, :]).sum(0) / w.sum()
+    return out
+
+
+def swiglu(gate, up):
+    """a = g / (1 + exp(-g)) * u (crates/leone/src/cpu.rs:903-905)."""
+    return gate / (1.0 + torch.exp(-gate)) * up
+
+
+def attention_layer(x, w, prefix, cfg, positions, window=None):
+    """q/k/v projection, per-head q/k RMSNorm with the layer eps before rotary, attention,
+    output projection (crates/leone/src/runtime.rs:9111-9157; crates/leone/src/model.rs:601-631)."""
+    n_q, n_kv = cfg["num_attention_heads"], cfg.get("num_key_value_heads", cfg["num_attention_heads"])
+    d = cfg.get("head_dim", cfg["hidden_size"] // n_q)
+    t_len = x.shape[0]
+    q = linear(x, w[prefix + "self_attn.q_proj.weight"]).reshape(t_len, n_q, d)
+    k = linear(x, w[prefix + "self_attn.k_proj.weight"]).reshape(t_len, n_kv, d)
+    v = linear(x, w[prefix + "self_attn.v_proj.weight"]).reshape(t_len, n_kv, d)
+    q = rms_norm(q, w[prefix + "self_attn.q_norm.weight"], cfg["rms_norm_eps"])
+    k = rms_norm(k, w[prefix + "self_attn.k_norm.weight"], cfg["rms_norm_eps"])
+    q = rope_half_split(q, positions, cfg["rope_theta"])
+    k = rope_half_split(k, positions, cfg["rope_theta"])
+    a = attention(q, k, v, positions, window=window)
+    return linear(a.reshape(t_len, n_q * d), w[prefix + "self_attn.o_proj.weight"])
+
+
+def mlp_layer(x, w, prefix):
+    """SwiGLU feed-forward (crates/leone/src/runtime.rs:9298-9317)."""
+    g = linear(x, w[prefix + "mlp.gate_proj.weight"])
+    u = linear(x, w[prefix + "mlp.up_proj.weight"])
+    return linear(swiglu(g, u), w[prefix + "mlp.down_proj.weight"])
+
+
+def block(h, w, i, cfg, positions):
+    """Pre-norm residual block (crates/leone/src/runtime.rs:9103-9317)."""
+    p = f"model.layers.{i}."
+    h = h + attention_layer(rms_norm(h, w[p + "input_layernorm.weight"], cfg["rms_norm_eps"]),
+                            w, p, cfg, positions)
+    h = h + mlp_layer(rms_norm(h, w[p + "post_attention_layernorm.weight"], cfg["rms_norm_eps"]), w, p)
+    return h
+
+
+def forward_logits(cfg, w, tokens):
+    """Logits [T, V] for a whole sequence from position 0
+    (final norm + head: crates/leone/src/runtime.rs:7428-7452; tied head model.rs:452-471)."""
+    positions = list(range(len(tokens)))
+    h = embedding(w["model.embed_tokens.weight"], tokens)
+    for i in range(cfg["num_hidden_layers"]):
+        h = block(h, w, i, cfg, positions)
+    h = rms_norm(h, w["model.norm.weight"], cfg["rms_norm_eps"])
+    head = w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings", False) else w["lm_head.weight"]
+    return linear(h, head)
+
+
+class PlainModel:
+    """A model folder read once; ``logits(tokens)`` runs the whole sequence."""
+
+    def __init__(self, folder, matrices_as_bf16=False):
+        self.cfg, self.w = read_folder(folder)
+        if matrices_as_bf16:
+            for name, t in self.w.items():
+                if t.dim() == 2:
+                    self.w[name] = round_bf16(t)
+        self._memo = {}
+
+    def logits(self, tokens):
+        key = tuple(int(t) for t in tokens)
+        if key not in self._memo:
+            self._memo[key] = forward_logits(self.cfg, self.w, list(key))
+        return self._memo[key]
+
+
+# ---------------------------------------------------------------------------------------
+# sampling (host, float64)
+# ---------------------------------------------------------------------------------------
+MASK = (1 << 64) - 1
+
+
+def splitmix64(v):
+    """crates/leone/src/sampler.rs:166-171."""
+    z = (v + 0x9E3779B97F4A7C15) & MASK
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & MASK
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & MASK
+    return z ^ (z >> 31)
+
+
+def uniform(seed, position):
+    """Select-purpose draw in [0,1): crates/leone/src/sampler.rs:84-94."""
+    mixed = splitmix64((seed & MASK) ^ splitmix64((position ^ 0xBF58476D1CE4E5B9) & MASK))
+    return (mixed >> 11) * (1.0 / (1 << 53))
+
+
+def argmax(logits):
+    """Highest finite logit, lowest index on a tie (crates/leone/src/sampler.rs:787-799)."""
+    best, best_v = None, None
+    for i, v in enumerate(logits):
+        v = float(v)
+        if not math.isfinite(v):
+            continue
+        if best is None or v > best_v:
+            best, best_v = i, v
+    return best
+
+
+def temperature_probs(logits, temperature):
+    """w_i = exp(l_i/t - max_j l_j/t) over finite logits in float64, normalised
+    (crates/leone/src/sampler.rs:502-534)."""
+    l = np.asarray(logits, dtype=np.float64)
+    finite = np.isfinite(l)
+    scaled = np.where(finite, l / temperature, -np.inf)
+    w = np.where(finite, np.exp(scaled - scaled[finite].max()), 0.0)
+    return w / w.sum()
+
+
+def select(probs, u):
+    """First token in id order whose cumulative probability exceeds u; last eligible otherwise
+    (crates/leone/src/sampler.rs:839-858)."""
+    c, last = 0.0, None
+    for i, p in enumerate(probs):
+        if p <= 0.0:
+            continue
+        last = i
+        c += p
+        if u < c:
+            return i
+    return last
+
+
+def sample(logits, temperature, seed, position):
+    if temperature is None or temperature == 0.0:
+        return argmax(logits)
+    return select(temperature_probs(logits, temperature), uniform(seed, position))
+
+
+def generate(model: PlainModel, prompt, max_new_tokens, temperature=0.0, seed=0, eos=None):
+    """Greedy/temperature generation by re-running the whole sequence each token.  The draw
+    for a token uses the position of the token whose logits are sampled
+    (crates/leone/src/runtime.rs:4945, 6080)."""
+    tokens = list(prompt)
+    out = []
+    for _ in range(max_new_tokens):
+        logits = model.logits(tokens)[-1].tolist()
+        tok = sample(logits, temperature, seed, len(tokens) - 1)
+        out.append(tok)
+        tokens.append(tok)
+        if eos is not None and tok == eos:
+            break
+    return out
