@@ -1,0 +1,107 @@
+// Shared helpers for the engine's CUDA kernels (sm_100a).
+//
+// Conventions used by every entry point in this directory:
+//  * entry points are `extern "C"`, take raw device pointers, sizes and a
+//    cudaStream_t, launch asynchronously and return a cudaError_t-compatible int
+//    (0 = launched; negative = the sizes were refused, nothing was launched);
+//  * `dtype` arguments: 0 = float32, 1 = bfloat16;
+//  * kernels never trap: a bad index found on the device sets the status word
+//    (atomicCAS on word 0 so the first fault wins) and the access is skipped.
+//    The reference guards the same way
+//    (crates/leone-cuda/cuda/ie_cuda.cu:2960-2966, 5610-5640).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace leone {
+
+enum Status : int {
+  kOk = 0,
+  kBadTokenId = 1,      // detail: row, id
+  kBadPage = 2,         // detail: token row, page id
+  kBadPosition = 3,     // detail: token row, position
+  kWaitTimeout = 4,     // detail: block, which wait
+  kBadSequence = 5,     // detail: token row, sequence index
+};
+
+enum Refusal : int {
+  kRefusedSize = -1,        // a size the kernel does not take
+  kRefusedAlignment = -2,   // a pointer or stride that is not aligned as needed
+  kRefusedDtype = -3,
+};
+
+__device__ __forceinline__ void set_status(int* status, int code, int d0, int d1, int d2 = 0) {
+  if (status == nullptr) return;
+  if (atomicCAS(status, 0, code) == 0) {
+    status[1] = d0;
+    status[2] = d1;
+    status[3] = d2;
+  }
+}
+
+template <typename T> __device__ __forceinline__ float to_float(T v);
+template <> __device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) {
+  return __bfloat162float(v);
+}
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+// A value rounded to the storage type and back: what a later reader of T will see.
+template <typename T> __device__ __forceinline__ float round_to(float v) {
+  return to_float<T>(from_float<T>(v));
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.
+// `scratch` is 33 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int warps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < warps ? scratch[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int warps = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < warps ? scratch[lane] : -INFINITY;
+    t = warp_max(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+inline int launch_result() {
+  return (int)cudaGetLastError();
+}
+
+}  // namespace leone

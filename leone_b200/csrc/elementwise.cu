@@ -1,0 +1,341 @@
+// Row-wise kernels: embedding gather, RMSNorm, SwiGLU, the fused per-head
+// q/k RMSNorm + rotary + paged cache write, and sampling.  All take float32 or
+// bfloat16 storage; every reduction and every softmax/rotation is in fp32 (the
+// sampling sums in fp64, like the reference's host sampler).
+#include "common.cuh"
+
+namespace leone {
+
+// ---------------------------------------------------------------------------
+// Embedding gather: out[t,:] = table[id_t,:]  (crates/leone/src/cpu.rs:1243-1265;
+// CUDA counterpart crates/leone-cuda/cuda/ie_cuda.cu:3569).  Output is the fp32
+// residual stream.  An id outside [0, vocab) sets the status word and zeroes the row.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                                 float* __restrict__ out, int hidden, int vocab, int* status) {
+  const int row = blockIdx.x;
+  const int id = ids[row];
+  float* dst = out + (size_t)row * hidden;
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0) set_status(status, kBadTokenId, row, id);
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = 0.f;
+    return;
+  }
+  const T* src = table + (size_t)id * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = to_float<T>(src[c]);
+}
+
+// ---------------------------------------------------------------------------
+// RMSNorm: y = x * w * rsqrt(mean(x^2) + eps)  (crates/leone/src/cpu.rs:1642-1663;
+// crates/leone-cuda/cuda/ie_cuda.cu:2357-2380).  Input rows are fp32 (the residual
+// stream); `rows` optionally gathers input rows.  One block per output row.
+// ---------------------------------------------------------------------------
+template <typename TW, typename TO>
+__global__ void rms_norm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                                const TW* __restrict__ w, TO* __restrict__ out, int hidden,
+                                float eps) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const float* src = x + (size_t)(rows ? rows[r] : r) * hidden;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    const float v = src[c];
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)hidden + eps);
+  TO* dst = out + (size_t)r * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x)
+    dst[c] = from_float<TO>(src[c] * to_float<TW>(w[c]) * inv);
+}
+
+// ---------------------------------------------------------------------------
+// SwiGLU on stacked [gate | up] rows: out = gate / (1 + exp(-gate)) * up
+// (crates/leone/src/cpu.rs:903-905; ie_cuda.cu:2864-2874).
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int n, int inter) {
+  const size_t total = (size_t)n * inter;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x) {
+    const size_t row = i / inter, col = i - row * inter;
+    const float g = to_float<T>(gate_up[row * 2 * inter + col]);
+    const float u = to_float<T>(gate_up[row * 2 * inter + inter + col]);
+    out[i] = from_float<T>(g / (1.f + expf(-g)) * u);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Per-head q/k RMSNorm + half-split rotary + paged cache write, one warp per
+// (token, head) of the fused qkv row [q heads | k heads | v heads]
+// (crates/leone-cuda/cuda/ie_cuda.cu:2426-2484 does the same three things in one
+// launch; formulas crates/leone/src/cpu.rs:802-820 and 1747-1779).
+//  q heads: normed, rotated, written back in place.
+//  k heads: normed, rotated, written back in place and into the key page.
+//  v heads: copied into the value page.
+// Page of token t: block_table[seq_of_token[t]][pos / page_tokens]; a missing or
+// out-of-range page sets the status word and nothing is written.
+// Values are rounded to the storage type after the norm and again after the
+// rotation only once: the rotation works on fp32 normed values.
+// ---------------------------------------------------------------------------
+template <typename T, typename TW>
+__global__ void qk_norm_rope_write_kernel(
+    T* __restrict__ qkv, int n_tokens, int n_q, int n_kv, int d, const TW* __restrict__ q_w,
+    const TW* __restrict__ k_w, float eps, const float2* __restrict__ rope, int rotary_dim,
+    int max_positions, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+    const int* __restrict__ block_table, int table_width, int n_seqs, T* __restrict__ k_pool,
+    T* __restrict__ v_pool, int num_pages, int page_tokens, int* status) {
+  extern __shared__ float smem[];
+  const int warps_per_block = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = n_q + 2 * n_kv;
+  const long long item = (long long)blockIdx.x * warps_per_block + warp;
+  if (item >= (long long)n_tokens * heads) return;
+  const int t = (int)(item / heads), h = (int)(item - (long long)t * heads);
+  float* buf = smem + warp * d;
+  T* row = qkv + ((size_t)t * heads + h) * d;
+  const bool is_q = h < n_q, is_k = !is_q && h < n_q + n_kv;
+  const int pos = positions[t];
+
+  float ss = 0.f;
+  for (int c = lane; c < d; c += 32) {
+    const float v = to_float<T>(row[c]);
+    buf[c] = v;
+    ss = fmaf(v, v, ss);
+  }
+  const TW* w = is_q ? q_w : (is_k ? k_w : nullptr);
+  if (w != nullptr) {
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)d + eps);
+    for (int c = lane; c < d; c += 32) buf[c] = buf[c] * to_float<TW>(w[c]) * inv;
+  }
+  __syncwarp();
+  const bool rotate = (is_q || is_k) && rope != nullptr;
+  if (rotate && (pos < 0 || pos >= max_positions)) {
+    if (lane == 0) set_status(status, kBadPosition, t, pos);
+    return;
+  }
+  // destination in the cache
+  T* cache_row = nullptr;
+  if (!is_q && k_pool != nullptr) {
+    const int s = seq_of_token[t];
+    if (s < 0 || s >= n_seqs) {
+      if (lane == 0) set_status(status, kBadSequence, t, s);
+      return;
+    }
+    const int blk = pos / page_tokens;
+    const int page = (pos >= 0 && blk < table_width) ? block_table[(size_t)s * table_width + blk] : -1;
+    if (page < 0 || page >= num_pages) {
+      if (lane == 0) set_status(status, kBadPage, t, page, pos);
+      return;
+    }
+    const int kvh = is_k ? h - n_q : h - n_q - n_kv;
+    T* pool = is_k ? k_pool : v_pool;
+    cache_row = pool + (((size_t)page * n_kv + kvh) * page_tokens + (pos % page_tokens)) * d;
+  }
+  const int half = rotary_dim >> 1;
+  for (int c = lane; c < d; c += 32) {
+    float v = buf[c];
+    if (rotate && c < rotary_dim) {
+      const int pair = c < half ? c : c - half;
+      const float2 cs = rope[(size_t)pos * half + pair];
+      const float a = buf[pair], b = buf[pair + half];
+      v = c < half ? a * cs.x - b * cs.y : a * cs.y + b * cs.x;
+    }
+    const T o = from_float<T>(v);
+    if (is_q || is_k) row[c] = o;
+    if (cache_row != nullptr) cache_row[c] = o;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Sampling over fp32 logits [rows, vocab], one block per row.
+//  temperature == 0: greedy, highest finite logit, lowest index on a tie
+//    (crates/leone/src/sampler.rs:787-799; ie_cuda.cu:4814-4823).
+//  temperature > 0: w_i = exp(l_i/t - max_j l_j/t) over finite logits, summed in fp64;
+//    u = uniform(seed, position) from the reference's counter-based generator
+//    (crates/leone/src/sampler.rs:84-94, 166-171); the token is the first in id order
+//    whose cumulative weight exceeds u * total, else the last eligible one (:839-858).
+//    Each thread owns a contiguous run of ids so the scan keeps id order.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ unsigned long long splitmix64(unsigned long long v) {
+  unsigned long long z = v + 0x9e3779b97f4a7c15ull;
+  z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
+  z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
+  return z ^ (z >> 31);
+}
+
+__global__ void sample_kernel(const float* __restrict__ logits, int vocab,
+                              const float* __restrict__ temperature,
+                              const long long* __restrict__ seeds,
+                              const long long* __restrict__ positions, int* __restrict__ out) {
+  __shared__ float s_val[1024];
+  __shared__ int s_idx[1024];
+  __shared__ double s_sum[1024];
+  const int row = blockIdx.x, tid = threadIdx.x, nthr = blockDim.x;
+  const float* l = logits + (size_t)row * vocab;
+  const int per = (vocab + nthr - 1) / nthr;
+  const int lo = min(tid * per, vocab), hi = min(lo + per, vocab);
+  float best = -INFINITY;
+  int best_i = -1;
+  for (int i = lo; i < hi; ++i) {
+    const float v = l[i];
+    if (isfinite(v) && (best_i < 0 || v > best)) { best = v; best_i = i; }
+  }
+  s_val[tid] = best;
+  s_idx[tid] = best_i;
+  __syncthreads();
+  for (int o = 512; o > 0; o >>= 1) {
+    if (tid < o && tid + o < nthr) {
+      const int j = s_idx[tid + o];
+      // on equal values the lower id wins
+      if (j >= 0 && (s_idx[tid] < 0 || s_val[tid + o] > s_val[tid] ||
+                     (s_val[tid + o] == s_val[tid] && j < s_idx[tid]))) {
+        s_val[tid] = s_val[tid + o];
+        s_idx[tid] = j;
+      }
+    }
+    __syncthreads();
+  }
+  const float top = s_val[0];
+  const int top_i = s_idx[0];
+  const float temp = temperature ? temperature[row] : 0.f;
+  if (!(temp > 0.f) || top_i < 0) {
+    if (tid == 0) out[row] = top_i;
+    return;
+  }
+  const double t = (double)temp, hi_scaled = (double)top / t;
+  double sum = 0.0;
+  for (int i = lo; i < hi; ++i) {
+    const float v = l[i];
+    if (isfinite(v)) sum += exp((double)v / t - hi_scaled);
+  }
+  s_sum[tid] = sum;
+  __syncthreads();
+  if (tid == 0) {
+    double total = 0.0;
+    for (int i = 0; i < nthr; ++i) total += s_sum[i];
+    const unsigned long long purpose = 0xbf58476d1ce4e5b9ull;
+    const unsigned long long mixed = splitmix64(
+        (unsigned long long)seeds[row] ^ splitmix64((unsigned long long)positions[row] ^ purpose));
+    const double u = (double)(mixed >> 11) * (1.0 / 9007199254740992.0);
+    const double target = u * total;
+    double c = 0.0;
+    int owner = nthr - 1;
+    for (int i = 0; i < nthr; ++i) {
+      if (target < c + s_sum[i]) { owner = i; break; }
+      c += s_sum[i];
+    }
+    // scan the owner's run; fall back to the last eligible id at or before its end
+    int chosen = -1, last = -1;
+    const int olo = min(owner * per, vocab), ohi = min(olo + per, vocab);
+    for (int i = olo; i < ohi && chosen < 0; ++i) {
+      const float v = l[i];
+      if (!isfinite(v)) continue;
+      const double wgt = exp((double)v / t - hi_scaled);
+      if (wgt <= 0.0) continue;
+      last = i;
+      c += wgt;
+      if (target < c) chosen = i;
+    }
+    if (chosen < 0) {
+      if (last >= 0) {
+        chosen = last;
+      } else {
+        for (int i = vocab - 1; i >= 0; --i) {
+          const float v = l[i];
+          if (isfinite(v) && exp((double)v / t - hi_scaled) > 0.0) { chosen = i; break; }
+        }
+      }
+    }
+    out[row] = chosen;
+  }
+}
+
+}  // namespace leone
+
+using namespace leone;
+
+extern "C" int leone_embedding(int dtype, const void* table, const int* ids, float* out, int n,
+                               int hidden, int vocab, int* status, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (hidden <= 0 || vocab <= 0) return kRefusedSize;
+  const int threads = hidden >= 1024 ? 256 : 128;
+  if (dtype == 0)
+    embedding_kernel<float><<<n, threads, 0, stream>>>((const float*)table, ids, out, hidden, vocab, status);
+  else if (dtype == 1)
+    embedding_kernel<__nv_bfloat16><<<n, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, hidden, vocab, status);
+  else
+    return kRefusedDtype;
+  return launch_result();
+}
+
+extern "C" int leone_rms_norm(const float* x, const int* rows, const void* w, int w_dtype, void* out,
+                              int out_dtype, int n_out, int hidden, float eps, cudaStream_t stream) {
+  if (n_out <= 0) return 0;
+  if (hidden <= 0) return kRefusedSize;
+  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+#define LAUNCH(TW, TO)                                                                   \
+  rms_norm_kernel<TW, TO><<<n_out, threads, 0, stream>>>(x, rows, (const TW*)w, (TO*)out, \
+                                                        hidden, eps)
+  if (w_dtype == 0 && out_dtype == 0) LAUNCH(float, float);
+  else if (w_dtype == 0 && out_dtype == 1) LAUNCH(float, __nv_bfloat16);
+  else if (w_dtype == 1 && out_dtype == 0) LAUNCH(__nv_bfloat16, float);
+  else if (w_dtype == 1 && out_dtype == 1) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  else return kRefusedDtype;
+#undef LAUNCH
+  return launch_result();
+}
+
+extern "C" int leone_swiglu(int dtype, const void* gate_up, void* out, int n, int inter,
+                            cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (inter <= 0) return kRefusedSize;
+  const size_t total = (size_t)n * inter;
+  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  if (dtype == 0)
+    swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, n, inter);
+  else if (dtype == 1)
+    swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, n, inter);
+  else
+    return kRefusedDtype;
+  return launch_result();
+}
+
+extern "C" int leone_qk_norm_rope_write(
+    int dtype, void* qkv, int n_tokens, int n_q, int n_kv, int d, const void* q_w, const void* k_w,
+    int w_dtype, float eps, const float* rope, int rotary_dim, int max_positions,
+    const int* positions, const int* seq_of_token, const int* block_table, int table_width,
+    int n_seqs, void* k_pool, void* v_pool, int num_pages, int page_tokens, int* status,
+    cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (d <= 0 || d > 1024 || n_q <= 0 || n_kv <= 0) return kRefusedSize;
+  if (rope != nullptr && (rotary_dim <= 0 || rotary_dim > d || (rotary_dim & 1))) return kRefusedSize;
+  if (k_pool != nullptr && (page_tokens <= 0 || table_width <= 0)) return kRefusedSize;
+  const int warps = 4;
+  const long long items = (long long)n_tokens * (n_q + 2 * n_kv);
+  const int blocks = (int)((items + warps - 1) / warps);
+  const size_t smem = (size_t)warps * d * sizeof(float);
+#define LAUNCH(T, TW)                                                                            \
+  qk_norm_rope_write_kernel<T, TW><<<blocks, warps * 32, smem, stream>>>(                         \
+      (T*)qkv, n_tokens, n_q, n_kv, d, (const TW*)q_w, (const TW*)k_w, eps, (const float2*)rope,  \
+      rotary_dim, max_positions, positions, seq_of_token, block_table, table_width, n_seqs,       \
+      (T*)k_pool, (T*)v_pool, num_pages, page_tokens, status)
+  if (dtype == 0 && w_dtype == 0) LAUNCH(float, float);
+  else if (dtype == 1 && w_dtype == 0) LAUNCH(__nv_bfloat16, float);
+  else if (dtype == 0 && w_dtype == 1) LAUNCH(float, __nv_bfloat16);
+  else if (dtype == 1 && w_dtype == 1) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  else return kRefusedDtype;
+#undef LAUNCH
+  return launch_result();
+}
+
+extern "C" int leone_sample(const float* logits, int rows, int vocab, const float* temperature,
+                            const long long* seeds, const long long* positions, int* out,
+                            cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (vocab <= 0) return kRefusedSize;
+  sample_kernel<<<rows, 1024, 0, stream>>>(logits, vocab, temperature, seeds, positions, out);
+  return launch_result();
+}

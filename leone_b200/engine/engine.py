@@ -121,6 +121,8 @@ class Engine:
             self.pools.append((torch.zeros(shape, dtype=self.dtype, device=self.device),
                                torch.zeros(shape, dtype=self.dtype, device=self.device)))
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+        if hasattr(self.ops, "bind_status"):
+            self.ops.bind_status(self.status)
         self._meta_dev = None
         self._meta_host = None
         self._meta_event = None

@@ -1,0 +1,279 @@
+"""The kernel table: Python calls into the engine's own CUDA libraries.
+
+Every call checks shapes, dtypes and contiguity on the host, then launches on
+the current torch stream through a C entry point of ``csrc`` (loaded with
+ctypes; compiled on first use by :mod:`leone_b200.csrc.build`).  There is no
+other implementation behind these calls: without a CUDA device or without the
+compiled libraries, construction raises.  The reference has the same split
+between checked wrappers and raw entry points
+(crates/leone-cuda/src/cuda.rs, crates/leone-cuda/src/ffi.rs).
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+from typing import Optional
+
+import torch
+
+from ..csrc.build import ensure_built
+
+_STATUS_TEXT = {
+    1: "a token id outside the vocabulary reached the embedding kernel",
+    2: "a token's block has no valid page in its block table",
+    3: "a position outside the position table",
+    4: "a bounded wait inside a kernel ran out",
+    5: "a token names a sequence outside the batch",
+}
+_REFUSALS = {
+    -1: "a size this kernel does not take",
+    -2: "a pointer or stride that is not aligned as the kernel needs",
+    -3: "a dtype this kernel does not take",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _dt(t: torch.dtype) -> int:
+    if t == torch.float32:
+        return 0
+    if t == torch.bfloat16:
+        return 1
+    raise KernelError(f"kernels take float32 or bfloat16, not {t}")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code < 0:
+        raise KernelError(f"{what}: refused — {_REFUSALS.get(code, code)}")
+    raise KernelError(f"{what}: CUDA error {code} at launch")
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+class PreparedMatrix:
+    """A weight matrix ``[out, in]`` with what the kernels precompute for it."""
+
+    def __init__(self, weight: torch.Tensor):
+        self.weight = weight
+        self.out_features, self.in_features = weight.shape
+        self.tma = None           # tensor map for the tensor-core kernel, made on first use
+
+    @property
+    def shape(self):
+        return self.weight.shape
+
+    @property
+    def dtype(self):
+        return self.weight.dtype
+
+
+class CudaOps:
+    def __init__(self, device, dtype: torch.dtype):
+        self.device = torch.device(device)
+        if self.device.type != "cuda" or not torch.cuda.is_available():
+            raise KernelError(
+                "leone_b200 runs on a CUDA device only (there is no CPU path); "
+                f"asked for device '{device}', torch.cuda.is_available() = {torch.cuda.is_available()}")
+        major, minor = torch.cuda.get_device_capability(self.device)
+        if major != 10:
+            raise KernelError(f"the kernels are built for sm_100a; device reports sm_{major}{minor}")
+        self.dtype = dtype
+        self.core = ctypes.CDLL(ensure_built("core"))
+        self.fast = None
+        if dtype == torch.bfloat16:
+            from .fast import FastKernels
+            self.fast = FastKernels(self.device)
+        self.launches = 0
+        self.status = None
+
+    def bind_status(self, status: torch.Tensor) -> None:
+        """The engine's status word; kernels with bounded waits report into it."""
+        self.status = status
+        if self.fast is not None:
+            self.fast.status = status
+
+    # -- helpers ------------------------------------------------------------------------
+    def _stream(self):
+        return c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def describe_status(self, word: int) -> str:
+        return _STATUS_TEXT.get(word, "unknown status")
+
+    # -- weights ------------------------------------------------------------------------
+    def prepare_matrix(self, w: torch.Tensor) -> PreparedMatrix:
+        _need(w.dim() == 2 and w.is_contiguous(), "a weight matrix must be contiguous [out, in]")
+        return PreparedMatrix(w)
+
+    def prepare_gate_up(self, gate: torch.Tensor, up: torch.Tensor) -> PreparedMatrix:
+        _need(gate.shape == up.shape, "gate and up matrices differ in shape")
+        if self.fast is not None:
+            return self.fast.prepare_gate_up(gate, up)
+        m = PreparedMatrix(torch.cat([gate, up], dim=0).contiguous())
+        m.gate_up_layout = "stacked"
+        return m
+
+    # -- kernels ------------------------------------------------------------------------
+    def embedding(self, table, ids, out, status):
+        n, hidden = out.shape
+        _need(out.dtype == torch.float32 and out.is_contiguous(), "embedding output must be fp32")
+        _need(ids.dtype == torch.int32 and ids.numel() == n, "embedding ids must be int32 [N]")
+        _need(table.shape[1] == hidden and table.is_contiguous(), "embedding table shape")
+        self.launches += 1
+        _check(self.core.leone_embedding(_dt(table.dtype), _ptr(table), _ptr(ids), _ptr(out), n,
+                                         hidden, table.shape[0], _ptr(status), self._stream()),
+               "embedding")
+
+    def rms_norm(self, x, weight, out, eps, rows=None):
+        n_out, hidden = out.shape
+        _need(x.dtype == torch.float32 and x.is_contiguous() and x.shape[1] == hidden,
+              "rms_norm input must be contiguous fp32 [*, hidden]")
+        _need(weight.numel() == hidden and out.is_contiguous(), "rms_norm weight/output shape")
+        if rows is not None:
+            _need(rows.dtype == torch.int32 and rows.numel() == n_out, "rms_norm rows must be int32")
+        else:
+            _need(x.shape[0] >= n_out, "rms_norm input has fewer rows than the output")
+        self.launches += 1
+        _check(self.core.leone_rms_norm(_ptr(x), _ptr(rows), _ptr(weight), _dt(weight.dtype),
+                                        _ptr(out), _dt(out.dtype), n_out, hidden, c_float(eps),
+                                        self._stream()), "rms_norm")
+
+    def _gemm_simt(self, x, w, out, epilogue, residual):
+        m, k = x.shape
+        n = w.shape[0]
+        self.launches += 1
+        _check(self.core.leone_gemm_simt(_dt(x.dtype), epilogue, _ptr(x), _ptr(w), _ptr(out),
+                                         _ptr(residual), m, n, k, x.stride(0), w.stride(0),
+                                         out.stride(0), self._stream()), "gemm_simt")
+
+    def linear(self, x, w: PreparedMatrix, out, residual=None):
+        """``out = x @ w.T`` (+ ``residual``).  ``out`` in x's dtype, or fp32 (then a fp32
+        ``residual`` may be added; it may be ``out`` itself)."""
+        m, k = x.shape
+        _need(k == w.in_features and out.shape == (m, w.out_features), "linear: shapes do not chain")
+        _need(x.dtype == w.dtype and x.stride(1) == 1 and out.stride(1) == 1, "linear: dtype/stride")
+        if residual is not None:
+            _need(out.dtype == torch.float32 and residual.dtype == torch.float32
+                  and residual.shape == out.shape and residual.stride() == out.stride(),
+                  "linear: a residual needs fp32 output of the same layout")
+            epilogue = 2
+        elif out.dtype == torch.float32 and x.dtype != torch.float32:
+            epilogue = 1
+        else:
+            _need(out.dtype == x.dtype, "linear: output dtype")
+            epilogue = 0
+        if m == 0:
+            return
+        if self.fast is not None and self.fast.linear(x, w, out, epilogue, residual):
+            self.launches += 1
+            return
+        self._gemm_simt(x, w.weight, out, epilogue, residual)
+
+    def linear_swiglu(self, x, w_gate_up: PreparedMatrix, out):
+        """``out = silu(x @ gate.T) * (x @ up.T)`` for a matrix from ``prepare_gate_up``."""
+        m = x.shape[0]
+        inter = w_gate_up.out_features // 2
+        _need(out.shape == (m, inter) and out.dtype == x.dtype and out.is_contiguous(),
+              "linear_swiglu: output shape")
+        if m == 0:
+            return
+        if self.fast is not None and self.fast.linear_swiglu(x, w_gate_up, out):
+            self.launches += 1
+            return
+        _need(getattr(w_gate_up, "gate_up_layout", None) == "stacked", "gate/up layout")
+        scratch = self._scratch("gate_up", m, 2 * inter, x.dtype)
+        self._gemm_simt(x, w_gate_up.weight, scratch, 0, None)
+        self.launches += 1
+        _check(self.core.leone_swiglu(_dt(x.dtype), _ptr(scratch), _ptr(out), m, inter,
+                                      self._stream()), "swiglu")
+
+    def swiglu(self, gate_up, out):
+        m, two_i = gate_up.shape
+        _need(out.shape == (m, two_i // 2) and gate_up.is_contiguous() and out.is_contiguous(),
+              "swiglu shapes")
+        self.launches += 1
+        _check(self.core.leone_swiglu(_dt(gate_up.dtype), _ptr(gate_up), _ptr(out), m, two_i // 2,
+                                      self._stream()), "swiglu")
+
+    _scratch_bufs = None
+
+    def _scratch(self, name, rows, cols, dtype):
+        if self._scratch_bufs is None:
+            self._scratch_bufs = {}
+        key = (name, cols, dtype)
+        buf = self._scratch_bufs.get(key)
+        if buf is None or buf.shape[0] < rows:
+            buf = torch.empty((max(rows, 64), cols), dtype=dtype, device=self.device)
+            self._scratch_bufs[key] = buf
+        return buf[:rows]
+
+    def qk_norm_rope_write(self, ctx, qkv, n_q, n_kv, d, q_norm_w, k_norm_w, eps, table,
+                           rotary_dim, cache):
+        n = qkv.shape[0]
+        _need(qkv.is_contiguous() and qkv.shape[1] == (n_q + 2 * n_kv) * d, "qkv layout")
+        w_dtype = 0
+        if q_norm_w is not None:
+            _need(k_norm_w is not None and q_norm_w.dtype == k_norm_w.dtype
+                  and q_norm_w.numel() == d and k_norm_w.numel() == d, "q/k norm weights")
+            w_dtype = _dt(q_norm_w.dtype)
+        max_pos = 0
+        if table is not None:
+            _need(table.dtype == torch.float32 and table.is_contiguous() and table.dim() == 3
+                  and table.shape[1] * 2 == rotary_dim and table.shape[2] == 2, "rotary table layout")
+            max_pos = table.shape[0]
+        if cache is not None:
+            kp, vp, bt = cache.k_pool, cache.v_pool, cache.block_table
+            _need(kp.is_contiguous() and vp.is_contiguous() and kp.dtype == qkv.dtype
+                  and kp.shape[1] == n_kv and kp.shape[3] == d and kp.shape[2] == cache.page_tokens,
+                  "cache pool layout")
+            _need(bt.dtype == torch.int32 and bt.is_contiguous(), "block table")
+            pool_args = (_ptr(bt), bt.shape[1], bt.shape[0], _ptr(kp), _ptr(vp), kp.shape[0],
+                         cache.page_tokens)
+        else:
+            pool_args = (c_void_p(0), 0, 0, c_void_p(0), c_void_p(0), 0, 0)
+        self.launches += 1
+        _check(self.core.leone_qk_norm_rope_write(
+            _dt(qkv.dtype), _ptr(qkv), n, n_q, n_kv, d, _ptr(q_norm_w), _ptr(k_norm_w), w_dtype,
+            c_float(eps), _ptr(table), rotary_dim, max_pos, _ptr(ctx.positions),
+            _ptr(ctx.seq_of_token), pool_args[0], pool_args[1], pool_args[2], pool_args[3],
+            pool_args[4], pool_args[5], pool_args[6], _ptr(ctx.status), self._stream()),
+            "qk_norm_rope_write")
+
+    def attention(self, ctx, qkv, out, n_q, n_kv, d, scale, window, cache):
+        n = qkv.shape[0]
+        kp, vp, bt = cache.k_pool, cache.v_pool, cache.block_table
+        _need(out.shape == (n, n_q * d) and out.is_contiguous() and out.dtype == qkv.dtype,
+              "attention output layout")
+        _need(kp.is_contiguous() and vp.is_contiguous() and kp.dtype == qkv.dtype
+              and kp.shape[1] == n_kv and kp.shape[3] == d, "cache pool layout")
+        if self.fast is not None and self.fast.attention(ctx, qkv, out, n_q, n_kv, d, scale,
+                                                         window, cache):
+            self.launches += 1
+            return
+        self.launches += 1
+        _check(self.core.leone_attention_generic(
+            _dt(qkv.dtype), _ptr(qkv), qkv.stride(0), _ptr(out), out.stride(0), _ptr(kp), _ptr(vp),
+            _ptr(bt), bt.shape[1], _ptr(ctx.seq_of_token), _ptr(ctx.positions), n, n_q, n_kv, d,
+            c_float(scale), int(window or 0), cache.page_tokens, kp.shape[0], bt.shape[0],
+            _ptr(ctx.status), self._stream()), "attention_generic")
+
+    def sample(self, logits, temperature, seeds, positions, out):
+        rows, vocab = logits.shape
+        _need(logits.dtype == torch.float32 and logits.is_contiguous(), "logits must be fp32")
+        _need(temperature.dtype == torch.float32 and seeds.dtype == torch.int64
+              and positions.dtype == torch.int64 and out.dtype == torch.int32, "sample arguments")
+        _need(temperature.numel() >= rows and seeds.numel() >= rows and positions.numel() >= rows
+              and out.numel() >= rows, "sample argument lengths")
+        self.launches += 1
+        _check(self.core.leone_sample(_ptr(logits), rows, vocab, _ptr(temperature), _ptr(seeds),
+                                      _ptr(positions), _ptr(out), self._stream()), "sample")

@@ -1,0 +1,105 @@
+"""The bfloat16 serving kernels: tensor-core products (and tiled attention).
+
+Each call returns ``True`` if it ran and ``False`` if the kernel refuses the
+sizes (the caller then uses the any-size kernel).  Refusal is decided on the
+host from the kernel's stated limits, never by trying.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_int, c_longlong, c_void_p, byref
+
+import torch
+
+from ..csrc.build import ensure_built
+
+
+def _ptr(t):
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+class FastKernels:
+    def __init__(self, device):
+        self.device = torch.device(device)
+        self.lib = ctypes.CDLL(ensure_built("bf16"))
+        self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self._workspace = None
+        self._counters = None
+        # LEONE_NO_TENSOR_CORES=1 routes every product to the CUDA-core kernel (for fault finding)
+        self.use_tensor_cores = os.environ.get("LEONE_NO_TENSOR_CORES", "0") != "1"
+        self.status = None
+
+    def _stream(self):
+        return c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    # -- split-K scratch ----------------------------------------------------------------
+    def _scratch(self, floats: int, counters: int):
+        if self._workspace is None or self._workspace.numel() < floats:
+            self._workspace = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=self.device)
+        if self._counters is None or self._counters.numel() < counters:
+            self._counters = torch.zeros(max(counters, 4096), dtype=torch.int32, device=self.device)
+        return self._workspace, self._counters
+
+    def choose_splits(self, m: int, n: int, k: int) -> int:
+        """Split K only when few tokens leave most SMs without a weight tile."""
+        if m > 64:
+            return 1
+        tiles = -(-n // 128)
+        k_blocks = -(-k // 64)
+        if tiles * 2 > self.sm_count:
+            return 1
+        splits = min(self.sm_count // tiles, k_blocks // 8, 16)
+        return max(1, splits)
+
+    def _tc_ok(self, x, w, out) -> bool:
+        if not self.use_tensor_cores or x.dtype != torch.bfloat16:
+            return False
+        k = x.shape[1]
+        return (k % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+                and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+    def _gemm(self, x, w, out, epilogue, residual, n_rows, splits=None) -> bool:
+        m, k = x.shape
+        if splits is None:
+            splits = self.choose_splits(m, n_rows, k)
+        ws = ct = None
+        if splits > 1:
+            floats, counters = c_longlong(0), c_int(0)
+            self.lib.leone_gemm_tc_scratch(m, n_rows, splits, byref(floats), byref(counters))
+            ws, ct = self._scratch(floats.value, counters.value)
+        code = self.lib.leone_gemm_tc(_ptr(x), _ptr(w), _ptr(out), _ptr(residual), m, n_rows, k,
+                                      x.stride(0), w.stride(0), out.stride(0), epilogue, splits,
+                                      _ptr(ws), _ptr(ct), _ptr(self.status), self.sm_count, self._stream())
+        if code != 0:
+            raise RuntimeError(f"gemm_tc refused or failed with code {code} for m={m} n={n_rows} k={k}")
+        return True
+
+    def linear(self, x, w, out, epilogue, residual) -> bool:
+        if not self._tc_ok(x, w.weight, out):
+            return False
+        return self._gemm(x, w.weight, out, epilogue, residual, w.out_features)
+
+    # -- gate/up --------------------------------------------------------------------------
+    def prepare_gate_up(self, gate, up):
+        from .cuda import PreparedMatrix
+        inter, hidden = gate.shape
+        if gate.dtype == torch.bfloat16 and inter % 16 == 0 and hidden % 8 == 0 and self.use_tensor_cores:
+            # groups of 32 rows: 16 gate rows, then the 16 up rows of the same columns
+            stacked = torch.stack([gate.view(inter // 16, 16, hidden), up.view(inter // 16, 16, hidden)],
+                                  dim=1).reshape(2 * inter, hidden).contiguous()
+            m = PreparedMatrix(stacked)
+            m.gate_up_layout = "interleaved16"
+            return m
+        m = PreparedMatrix(torch.cat([gate, up], dim=0).contiguous())
+        m.gate_up_layout = "stacked"
+        return m
+
+    def linear_swiglu(self, x, w, out) -> bool:
+        if getattr(w, "gate_up_layout", None) != "interleaved16" or not self._tc_ok(x, w.weight, out):
+            return False
+        return self._gemm(x, w.weight, out, 3, None, w.out_features, splits=1)
+
+    # -- attention ------------------------------------------------------------------------
+    def attention(self, ctx, qkv, out, n_q, n_kv, d, scale, window, cache) -> bool:
+        return False

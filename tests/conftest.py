@@ -10,8 +10,3 @@ if ROOT not in sys.path:
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200)")
-
-
-def pytest_collection_modifyitems(config, items):
-    # The no-allocation entry point's test runs last, after every other test.
-    items.sort(key=lambda item: 1 if "test_zz_" in item.nodeid else 0)

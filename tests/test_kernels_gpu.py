@@ -1,0 +1,358 @@
+"""Each CUDA kernel alone against a plain torch reference, at sizes other than the engine's."""
+import math
+import types
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def ops32():
+    from leone_b200.ops.cuda import CudaOps
+    return CudaOps(DEV, torch.float32)
+
+
+@pytest.fixture(scope="module")
+def ops16():
+    from leone_b200.ops.cuda import CudaOps
+    return CudaOps(DEV, torch.bfloat16)
+
+
+def _gen(seed):
+    g = torch.Generator(device=DEV)
+    g.manual_seed(seed)
+    return g
+
+
+def _randn(shape, seed, dtype=torch.float32, scale=1.0):
+    return (torch.randn(shape, generator=_gen(seed), device=DEV) * scale).to(dtype)
+
+
+def _close(got, want, rtol, atol, what=""):
+    got, want = got.double(), want.double()
+    err = (got - want).abs()
+    bound = atol + rtol * want.abs()
+    bad = err > bound
+    assert not bad.any(), (f"{what}: {int(bad.sum())} of {bad.numel()} outside tolerance; worst "
+                           f"err {err.max().item():.3e} at {int(err.argmax())}, "
+                           f"|want| there {want.flatten()[err.argmax()].abs().item():.3e}")
+
+
+# -- embedding -----------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("vocab,hidden,n", [(331, 80, 7), (1000, 1536, 33)])
+def test_embedding(ops32, dtype, vocab, hidden, n):
+    table = _randn((vocab, hidden), 1, dtype)
+    ids = torch.randint(0, vocab, (n,), generator=_gen(2), device=DEV, dtype=torch.int32)
+    out = torch.empty((n, hidden), device=DEV)
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    ops32.embedding(table, ids, out, status)
+    assert torch.equal(out, table[ids.long()].float())
+    assert status[0].item() == 0
+
+
+def test_embedding_bad_id_sets_status(ops32):
+    table = _randn((50, 32), 1)
+    ids = torch.tensor([3, 50, 7], device=DEV, dtype=torch.int32)
+    out = torch.full((3, 32), 9.0, device=DEV)
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    ops32.embedding(table, ids, out, status)
+    assert status.tolist()[:3] == [1, 1, 50]
+    assert torch.equal(out[1], torch.zeros(32, device=DEV))
+    assert torch.equal(out[0], table[3])
+
+
+# -- rms norm ------------------------------------------------------------------------------
+@pytest.mark.parametrize("hidden,eps", [(80, 3e-6), (96, 1e-5), (4096, 1e-6), (5120, 1e-6), (1000, 1e-5)])
+@pytest.mark.parametrize("wdtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("odtype", [torch.float32, torch.bfloat16])
+def test_rms_norm(ops32, hidden, eps, wdtype, odtype):
+    x = _randn((13, hidden), 3, scale=2.5)
+    w = (1 + 0.1 * _randn((hidden,), 4)).to(wdtype)
+    out = torch.empty((13, hidden), device=DEV, dtype=odtype)
+    ops32.rms_norm(x, w, out, eps)
+    xd = x.double()
+    want = xd * w.double() / torch.sqrt((xd * xd).mean(-1, keepdim=True) + eps)
+    if odtype == torch.float32:
+        _close(out, want, 2e-5, 3e-6, "rms_norm")
+    else:
+        _close(out, want, 2 ** -8, 1e-6, "rms_norm bf16")
+
+
+def test_rms_norm_gathers_rows(ops32):
+    x = _randn((20, 96), 5)
+    w = _randn((96,), 6)
+    rows = torch.tensor([19, 0, 7, 7], device=DEV, dtype=torch.int32)
+    out = torch.empty((4, 96), device=DEV)
+    ops32.rms_norm(x, w, out, 1e-5, rows)
+    xd = x[rows.long()].double()
+    want = xd * w.double() / torch.sqrt((xd * xd).mean(-1, keepdim=True) + 1e-5)
+    _close(out, want, 2e-5, 3e-6, "rms_norm rows")
+
+
+# -- CUDA-core matrix product ----------------------------------------------------------------
+@pytest.mark.parametrize("m,n,k", [(1, 7, 5), (3, 100, 33), (65, 129, 64), (130, 64, 200), (17, 331, 80)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gemm_simt(ops32, m, n, k, dtype):
+    x = _randn((m, k), 7, dtype)
+    w = _randn((n, k), 8, dtype, scale=0.1)
+    want = x.double() @ w.double().t()
+    out = torch.empty((m, n), device=DEV, dtype=dtype)
+    ops32._gemm_simt(x, w, out, 0, None)
+    if dtype == torch.float32:
+        _close(out, want, 1e-5, 1e-5 * math.sqrt(k), "simt f32")
+    else:
+        _close(out, want, 2 ** -8, 1e-4, "simt bf16")
+    res = _randn((m, n), 9)
+    out32 = res.clone()
+    ops32._gemm_simt(x, w, out32, 2, out32)
+    _close(out32, want + res.double(), 1e-5, 1e-5 * math.sqrt(k), "simt residual in place")
+    if dtype == torch.bfloat16:
+        out32 = torch.empty((m, n), device=DEV)
+        ops32._gemm_simt(x, w, out32, 1, None)
+        _close(out32, want, 1e-5, 1e-5 * math.sqrt(k), "simt fp32 out")
+
+
+def test_gemm_simt_true_fp32(ops32):
+    """Values that a reduced-precision matrix mode would round away must survive."""
+    k = 64
+    x = torch.ones((4, k), device=DEV)
+    x[:, 0] = 1.0 + 2.0 ** -20
+    w = torch.ones((8, k), device=DEV)
+    out = torch.empty((4, 8), device=DEV)
+    ops32._gemm_simt(x, w, out, 0, None)
+    assert torch.equal(out, torch.full((4, 8), k + 2.0 ** -20, device=DEV))
+
+
+# -- tensor-core matrix product ----------------------------------------------------------------
+TC_SHAPES = [(1, 128, 64), (5, 100, 72), (16, 256, 128), (17, 384, 200), (64, 1000, 4096),
+             (100, 128, 640), (200, 520, 512), (300, 264, 1024), (2048, 512, 256), (8, 4096, 12288)]
+
+
+@pytest.mark.parametrize("m,n,k", TC_SHAPES)
+@pytest.mark.parametrize("splits", [1, 3])
+def test_gemm_tc(ops16, m, n, k, splits):
+    fast = ops16.fast
+    x = _randn((m, k), 11, torch.bfloat16)
+    w = _randn((n, k), 12, torch.bfloat16, scale=0.05)
+    want = x.double() @ w.double().t()
+    atol32 = 2e-6 * math.sqrt(k) * 4
+    out = torch.empty((m, n), device=DEV, dtype=torch.bfloat16)
+    fast._gemm(x, w, out, 0, None, n, splits=splits)
+    _close(out, want, 2 ** -8, atol32, f"tc bf16 out m{m} n{n} k{k} s{splits}")
+    out32 = torch.empty((m, n), device=DEV)
+    fast._gemm(x, w, out32, 1, None, n, splits=splits)
+    _close(out32, want, 1e-5, atol32, "tc fp32 out")
+    res = _randn((m, n), 13)
+    hidden = res.clone()
+    fast._gemm(x, w, hidden, 2, hidden, n, splits=splits)
+    _close(hidden, want + res.double(), 1e-5, atol32, "tc residual in place")
+    torch.cuda.synchronize()
+    if fast._counters is not None:
+        assert int(fast._counters.abs().sum()) == 0, "split-K counters were not reset"
+
+
+@pytest.mark.parametrize("m,inter,k", [(1, 64, 64), (7, 176, 80), (33, 224, 96), (260, 1024, 512)])
+def test_gemm_tc_swiglu(ops16, m, inter, k):
+    gate = _randn((inter, k), 14, torch.bfloat16, scale=0.2)
+    up = _randn((inter, k), 15, torch.bfloat16, scale=0.2)
+    x = _randn((m, k), 16, torch.bfloat16)
+    w = ops16.prepare_gate_up(gate, up)
+    assert w.gate_up_layout == "interleaved16"
+    out = torch.empty((m, inter), device=DEV, dtype=torch.bfloat16)
+    ops16.linear_swiglu(x, w, out)
+    g = x.double() @ gate.double().t()
+    u = x.double() @ up.double().t()
+    _close(out, g / (1 + torch.exp(-g)) * u, 2 ** -7, 1e-4, "tc swiglu")
+
+
+def test_gemm_tc_refuses_unaligned_k(ops16):
+    x = _randn((4, 60), 1, torch.bfloat16)
+    w = ops16.prepare_matrix(_randn((32, 60), 2, torch.bfloat16))
+    out = torch.empty((4, 32), device=DEV, dtype=torch.bfloat16)
+    ops16.linear(x, w, out)          # falls to the any-size kernel
+    _close(out, x.double() @ w.weight.double().t(), 2 ** -8, 1e-4, "k=60")
+
+
+# -- q/k norm + rotary + cache write, and attention ------------------------------------------
+def _paged_setup(seq_lens, page_tokens, n_kv, d, dtype, seed, extra_pages=3):
+    """Random block tables over a shuffled pool."""
+    blocks = [-(-l // page_tokens) for l in seq_lens]
+    num_pages = sum(blocks) + extra_pages
+    perm = torch.randperm(num_pages, generator=torch.Generator().manual_seed(seed)).tolist()
+    width = max(blocks) + 1
+    table = torch.full((len(seq_lens), width), -1, dtype=torch.int32)
+    for s, nb in enumerate(blocks):
+        for b in range(nb):
+            table[s, b] = perm.pop()
+    k_pool = torch.zeros((num_pages, n_kv, page_tokens, d), device=DEV, dtype=dtype)
+    v_pool = torch.zeros_like(k_pool)
+    return table.to(DEV), k_pool, v_pool
+
+
+def _ctx(positions, seq_of_token):
+    c = types.SimpleNamespace()
+    c.positions = torch.tensor(positions, device=DEV, dtype=torch.int32)
+    c.seq_of_token = torch.tensor(seq_of_token, device=DEV, dtype=torch.int32)
+    c.status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    return c
+
+
+def _rope_table(max_pos, rd, theta):
+    from leone_b200.parts.rotary import build_rotary_table
+    return build_rotary_table(max_pos, rd, theta).to(DEV)
+
+
+def _ref_norm_rope(x, w, eps, positions, theta, rd):
+    """x [n, heads, d] float64."""
+    if w is not None:
+        x = x * w.double() / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
+    half = rd // 2
+    inv = torch.tensor([theta ** (-2.0 * i / rd) for i in range(half)], dtype=torch.float64, device=x.device)
+    ang = torch.tensor(positions, dtype=torch.float64, device=x.device)[:, None] * inv[None]
+    cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    out = x.clone()
+    a, b = x[..., :half], x[..., half:rd]
+    out[..., :half] = a * cos - b * sin
+    out[..., half:rd] = a * sin + b * cos
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n_q,n_kv,d,pt,theta,eps", [(5, 1, 48, 16, 5e4, 3e-6), (6, 3, 32, 8, 1e6, 1e-5),
+                                                     (8, 2, 128, 16, 1e6, 1e-6), (3, 3, 80, 4, 1e4, 1e-6)])
+def test_qk_norm_rope_write(ops32, dtype, n_q, n_kv, d, pt, theta, eps):
+    seq_lens = [11, 3, 25]
+    starts = [4, 0, 20]                      # tokens of this step: positions start..len-1
+    positions, seqs = [], []
+    for s, (l, st) in enumerate(zip(seq_lens, starts)):
+        positions += list(range(st, l))
+        seqs += [s] * (l - st)
+    n = len(positions)
+    table, k_pool, v_pool = _paged_setup(seq_lens, pt, n_kv, d, dtype, 5)
+    qkv = _randn((n, (n_q + 2 * n_kv) * d), 21, dtype)
+    qw = (1 + 0.1 * _randn((d,), 22))
+    kw = (1 + 0.1 * _randn((d,), 23))
+    rope = _rope_table(64, d, theta)
+    orig = qkv.clone()
+    cache = types.SimpleNamespace(k_pool=k_pool, v_pool=v_pool, block_table=table, page_tokens=pt)
+    ctx = _ctx(positions, seqs)
+    ops32.qk_norm_rope_write(ctx, qkv, n_q, n_kv, d, qw, kw, eps, rope, d, cache)
+    assert ctx.status[0].item() == 0
+    x = orig.double().view(n, n_q + 2 * n_kv, d)
+    q_ref = _ref_norm_rope(x[:, :n_q], qw, eps, positions, theta, d)
+    k_ref = _ref_norm_rope(x[:, n_q:n_q + n_kv], kw, eps, positions, theta, d)
+    got = qkv.view(n, n_q + 2 * n_kv, d)
+    rt, at = (5e-6, 5e-6) if dtype == torch.float32 else (2 ** -7, 1e-5)
+    _close(got[:, :n_q], q_ref, rt * 4, at, "q")
+    _close(got[:, n_q:n_q + n_kv], k_ref, rt * 4, at, "k")
+    assert torch.equal(got[:, n_q + n_kv:], orig.view(n, -1, d)[:, n_q + n_kv:])
+    for i, (p, s) in enumerate(zip(positions, seqs)):
+        page = int(table[s, p // pt])
+        assert torch.equal(k_pool[page, :, p % pt, :], got[i, n_q:n_q + n_kv])
+        assert torch.equal(v_pool[page, :, p % pt, :], got[i, n_q + n_kv:])
+
+
+def test_qk_write_missing_page_sets_status(ops32):
+    table = torch.full((1, 2), -1, dtype=torch.int32, device=DEV)
+    k_pool = torch.zeros((2, 1, 4, 16), device=DEV)
+    cache = types.SimpleNamespace(k_pool=k_pool, v_pool=k_pool.clone(), block_table=table, page_tokens=4)
+    ctx = _ctx([0], [0])
+    qkv = _randn((1, 3 * 16), 1)
+    ops32.qk_norm_rope_write(ctx, qkv, 1, 1, 16, None, None, 1e-6, None, 0, cache)
+    assert ctx.status[0].item() == 2
+    assert float(k_pool.abs().sum()) == 0.0
+
+
+def _ref_attention(q, keys, vals, n_q, n_kv, scale, lo):
+    """q [n_q, d]; keys/vals [ctx, n_kv, d] float64 → [n_q, d]."""
+    g = n_q // n_kv
+    out = torch.zeros_like(q)
+    for h in range(n_q):
+        s = (keys[lo:, h // g] @ q[h]) * scale
+        w = torch.softmax(s, 0)
+        out[h] = (w[:, None] * vals[lo:, h // g]).sum(0)
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n_q,n_kv,d,pt,window", [(5, 1, 48, 16, None), (6, 3, 32, 8, None),
+                                                  (8, 2, 128, 16, None), (4, 4, 80, 4, 7), (2, 1, 256, 16, 130)])
+def test_attention_generic(ops32, dtype, n_q, n_kv, d, pt, window):
+    seq_lens = [300, 3, 131]
+    starts = [290, 0, 100]
+    positions, seqs = [], []
+    for s, (l, st) in enumerate(zip(seq_lens, starts)):
+        positions += list(range(st, l))
+        seqs += [s] * (l - st)
+    n = len(positions)
+    table, k_pool, v_pool = _paged_setup(seq_lens, pt, n_kv, d, dtype, 9)
+    keys = [_randn((l, n_kv, d), 30 + s, dtype) for s, l in enumerate(seq_lens)]
+    vals = [_randn((l, n_kv, d), 40 + s, dtype) for s, l in enumerate(seq_lens)]
+    for s, l in enumerate(seq_lens):
+        for p in range(l):
+            page = int(table[s, p // pt])
+            k_pool[page, :, p % pt] = keys[s][p]
+            v_pool[page, :, p % pt] = vals[s][p]
+    qkv = _randn((n, (n_q + 2 * n_kv) * d), 50, dtype)
+    # make one far key dominate for one row: a single wrong page would show
+    qkv.view(n, -1, d)[0, 0] = (keys[0][5, 0].float() * 4).to(dtype)
+    out = torch.empty((n, n_q * d), device=DEV, dtype=dtype)
+    cache = types.SimpleNamespace(k_pool=k_pool, v_pool=v_pool, block_table=table, page_tokens=pt)
+    ctx = _ctx(positions, seqs)
+    scale = 1 / math.sqrt(d)
+    ops32.attention(ctx, qkv, out, n_q, n_kv, d, scale, window, cache)
+    assert ctx.status[0].item() == 0
+    for i, (p, s) in enumerate(zip(positions, seqs)):
+        lo = 0 if not window else max(0, p - window + 1)
+        want = _ref_attention(qkv[i].double().view(-1, d)[:n_q], keys[s][:p + 1].double(),
+                              vals[s][:p + 1].double(), n_q, n_kv, scale, lo)
+        rt, at = (3e-4, 3e-5) if dtype == torch.float32 else (2 ** -7, 2e-3)
+        _close(out[i].view(n_q, d), want, rt, at, f"attention row {i}")
+
+
+# -- sampling ------------------------------------------------------------------------------------
+def test_sample_greedy_ties_and_nonfinite(ops32):
+    logits = torch.zeros((3, 1000), device=DEV)
+    logits[0, 17] = 5.0
+    logits[0, 900] = 5.0                 # tie → lowest id
+    logits[1, :] = float("-inf")
+    logits[1, 333] = -7.0
+    logits[2, 0] = float("nan")
+    logits[2, 999] = 1.0
+    out = torch.empty(3, dtype=torch.int32, device=DEV)
+    z = torch.zeros(3, device=DEV)
+    zi = torch.zeros(3, dtype=torch.int64, device=DEV)
+    ops32.sample(logits, z, zi, zi, out)
+    assert out.tolist() == [17, 333, 999]
+
+
+@pytest.mark.parametrize("vocab", [331, 151936])
+def test_sample_temperature_matches_host(ops32, vocab):
+    from tests.plain.model import temperature_probs, uniform
+    import numpy as np
+    rows = 6
+    logits = _randn((rows, vocab), 60, scale=3.0)
+    logits[0, 5] = float("-inf")
+    temps = torch.tensor([0.8, 1.0, 0.3, 2.0, 0.0, 0.7], device=DEV)
+    seeds = torch.tensor([0, 1, 2, 3, 4, 12345678901], dtype=torch.int64, device=DEV)
+    pos = torch.tensor([0, 5, 17, 100, 3, 2047], dtype=torch.int64, device=DEV)
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    ops32.sample(logits, temps, seeds, pos, out)
+    host = logits.cpu().numpy()
+    for r in range(rows):
+        t = float(temps[r])
+        if t == 0.0:
+            assert out[r].item() == int(np.argmax(host[r]))
+            continue
+        probs = temperature_probs(host[r], t)
+        cdf = np.cumsum(probs)
+        u = uniform(int(seeds[r]), int(pos[r]))
+        got = out[r].item()
+        lo = cdf[got - 1] if got > 0 else 0.0
+        # the drawn value lies in the chosen token's interval, up to summation rounding
+        assert lo - 1e-9 <= u < cdf[got] + 1e-9 and probs[got] > 0
