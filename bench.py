@@ -1,0 +1,38 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of a Qwen3-8B-shaped model on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl leone_b200|reference]
+
+Prints one JSON line.  ``--gpus N`` with N > 1 prints one line saying that this engine runs
+on one GPU and exits with 2.  ``--impl reference`` prints why the reference cannot run here.
+"""
+import argparse
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="leone_b200", choices=["leone_b200", "reference"])
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=2048)
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
+    args = ap.parse_args()
+    if args.impl != "reference" and args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    from leone_b200.benchmark import run
+    return run(args.gpus, args.steps, max(args.warmup, 3), args.impl, layers=args.layers,
+               batch=args.batch, context=args.context, points=not args.no_points)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,272 @@
+"""Throughput measurement: decode tokens per second and prefill tokens per second.
+
+The workload is the reference's headline one scaled to this engine: a Qwen3-8B-shaped
+model with seeded random bfloat16 weights, prompts of uniform random token ids, decode
+from 2,048-token contexts.  The reference's own ``leone bench`` measures batch 1 only,
+prompt ``[1; P]``, one warm-up run then repetitions (crates/leone-cli/src/main.rs:2098-2157),
+and relates the decode rate to memory bandwidth (crates/leone-cli/src/main.rs:4762).  Rates
+are defined as there: decode rate = decoded tokens / decode time including reading the
+sampled ids back (crates/leone/src/runtime.rs:419-427).
+
+Timing: CUDA events on the launching stream around exactly ``steps`` decode steps, after
+``warmup`` untimed steps.  Every decode step reads all weights (≈15 GB), far more than the
+126 MB L2, so consecutive timed steps cannot serve each other from cache.
+"""
+from __future__ import annotations
+
+import json
+import os
+import statistics
+import subprocess
+import threading
+import time
+from typing import Dict, List, Optional
+
+import torch
+
+QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=36, hidden_size=4096,
+                num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288,
+                vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6,
+                max_position_embeddings=4096, tie_word_embeddings=False)
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def measured_peaks() -> Dict[str, float]:
+    """Measured copy bandwidth and bf16 GEMM rate of this pool's GPUs, if the file is there."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        with open(path) as fh:
+            raw = json.load(fh)
+        return dict(hbm_gbs=float(raw["hbm_gbs"]), bf16_tflops=float(raw["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+        self.lines: List[str] = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        clocks, max_clock, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                clocks.append(float(parts[0]))
+                max_clock = float(parts[1])
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[2:6]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": max_clock,
+                "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def _random_prompts(vocab: int, batch: int, length: int, seed: int) -> List[List[int]]:
+    gen = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (batch, length), generator=gen).tolist()
+
+
+def prefill_all(engine, rids, prompts, chunk: int) -> List[int]:
+    """Run the prompts through the step function in portions; returns each request's first
+    sampled token (greedy)."""
+    from .sampling.sampler import SamplingParams
+    firsts = []
+    for rid, prompt in zip(rids, prompts):
+        pos = 0
+        logits = None
+        while pos < len(prompt):
+            n = min(chunk, len(prompt) - pos)
+            last = pos + n == len(prompt)
+            logits = engine.step([(rid, prompt[pos:pos + n], [n - 1] if last else [])])
+            pos += n
+        firsts.append(engine.sample(logits, [SamplingParams()], [len(prompt) - 1])[0])
+    return firsts
+
+
+def time_decode(engine, batch: int, context: int, steps: int, warmup: int, seed: int = 0):
+    """Device-timed decode: ``steps`` graph replays with tokens fed back on the device."""
+    from .sampling.sampler import SamplingParams
+    vocab = engine.spec.vocab_size
+    rids = [f"bench{batch}_{i}" for i in range(batch)]
+    prompts = _random_prompts(vocab, batch, context, seed + batch)
+    firsts = prefill_all(engine, rids, prompts, engine.max_batch_tokens)
+    params = [SamplingParams() for _ in rids]
+    last = firsts
+    for _ in range(max(warmup, 1)):
+        last = engine.decode_steps(rids, last, params, 1)[-1]
+    graph = engine._decode_graphs[batch]
+    lengths = [engine.cache.length(r) for r in rids]
+    engine.cache.reserve({r: l + steps for r, l in zip(rids, lengths)})
+    graph.fill(rids, last, lengths, params)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(steps):
+        graph.graph.replay()
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop)
+    engine.check_status()
+    for r, l in zip(rids, lengths):
+        engine.cache.commit(r, l + steps)
+    mid_ctx = lengths[0] + steps / 2.0
+    for r in rids:
+        engine.close(r)
+    return dict(ms_per_step=ms / steps, tokens_per_s=batch * steps / (ms / 1e3), mid_context=mid_ctx,
+                launches=graph.launches_per_step * steps)
+
+
+def time_prefill(engine, tokens: int, reps: int = 3, seed: int = 99):
+    vocab = engine.spec.vocab_size
+    times = []
+    for rep in range(reps + 1):
+        prompt = _random_prompts(vocab, 1, tokens, seed + rep)[0]
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        pos = 0
+        while pos < tokens:
+            n = min(engine.max_batch_tokens, tokens - pos)
+            engine.step([("prefill_bench", prompt[pos:pos + n], [n - 1] if pos + n == tokens else [])],
+                        check=False)
+            pos += n
+        stop.record()
+        torch.cuda.synchronize()
+        engine.check_status()
+        engine.close("prefill_bench")
+        if rep > 0:                      # the first run is the warm-up
+            times.append(start.elapsed_time(stop))
+    return statistics.median(times)
+
+
+def model_flops_prefill(cfg: dict, layers: int, tokens: int) -> float:
+    h, d = cfg["hidden_size"], cfg["head_dim"]
+    n_q, n_kv, inter = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["intermediate_size"]
+    linear = 2.0 * tokens * (h * (n_q + 2 * n_kv) * d + n_q * d * h + 3 * h * inter)
+    attention = 2.0 * n_q * d * tokens * tokens          # causal half of 4 n_q d T^2
+    return layers * (linear + attention) + 2.0 * cfg["vocab_size"] * h
+
+
+def kv_bytes_per_token(cfg: dict, layers: int, itemsize: int = 2) -> int:
+    return 2 * layers * cfg["num_key_value_heads"] * cfg["head_dim"] * itemsize
+
+
+def run(gpus: int, steps: int, warmup: int, impl: str, layers: Optional[int] = None, batch: int = 8,
+        context: int = 2048, prefill_tokens: int = 2048, points: bool = True) -> int:
+    if impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a Rust workspace (maturin bin wheel); no cargo/rustc in this "
+                          "image and its CUDA kernels target sm_89 GGUF Q4_K only"}))
+        return 0
+    if gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {gpus} is not supported")
+        return 2
+    from .config.qwen3 import Qwen3Config
+    from .engine.engine import Engine
+    from .engine.generate import generate
+
+    cfg = dict(QWEN3_8B)
+    full_layers = cfg["num_hidden_layers"]
+    if layers:
+        cfg["num_hidden_layers"] = layers
+    layers = cfg["num_hidden_layers"]
+    config = Qwen3Config.from_dict(cfg)
+    peaks = measured_peaks()
+    page_tokens = 16
+    big = 64 if points else batch
+    pool_tokens = big * (context + steps + warmup + 64)
+    t_build = time.time()
+    engine = Engine.from_config(config, seed=0, dtype="bfloat16", page_tokens=page_tokens,
+                                max_tokens=pool_tokens, max_requests=max(big, batch),
+                                max_batch_tokens=max(prefill_tokens, 2048))
+    build_s = time.time() - t_build
+
+    # prefill
+    prefill_ms = time_prefill(engine, prefill_tokens)
+    flops = model_flops_prefill(cfg, layers, prefill_tokens)
+    prefill = {"value": prefill_tokens / (prefill_ms / 1e3), "tokens": prefill_tokens, "ms": prefill_ms,
+               "frac": flops / (prefill_ms / 1e3) / (peaks["bf16_tflops"] * 1e12),
+               "tflops": flops / (prefill_ms / 1e3) / 1e12, "peak_tflops": peaks["bf16_tflops"]}
+
+    # the headline decode batch, with clocks sampled during the timed region
+    sampler = ClockSampler()
+    sampler.start()
+    main = time_decode(engine, batch, context, steps, warmup)
+    clocks = sampler.stop()
+    weight_bytes = engine.model.decode_weight_bytes()
+    step_bytes = weight_bytes + batch * main["mid_context"] * kv_bytes_per_token(cfg, layers)
+    achieved = step_bytes / (main["ms_per_step"] / 1e3) / 1e9
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": achieved / peaks["hbm_gbs"], "peaks": peaks["source"]}
+
+    extra = {}
+    if points:
+        for b in (1, 64):
+            r = time_decode(engine, b, context, steps, warmup)
+            extra[f"decode_b{b}"] = r["tokens_per_s"]
+
+    # end to end through the Python entry point: host token ids in, host token ids out
+    prompts = _random_prompts(config.vocab_size, batch, context, 4242)
+    torch.cuda.synchronize()
+    new_tokens = steps + 1
+    results, stats = generate(engine, prompts, new_tokens, temperature=0.0, return_stats=True,
+                              eos_token_id=-1, prefill_chunk=engine.max_batch_tokens,
+                              max_batch_tokens=engine.max_batch_tokens, max_running=batch)
+    graph = engine._decode_graphs[batch]
+    e2e = {"value": stats.decode_tokens_per_second, "unit": "tokens/s",
+           "h2d_bytes_per_step": int(graph.size * 4 + graph.sample_host.numel() * 8),
+           "d2h_bytes_per_step": int(batch * 4 + 16),
+           "prefill_tokens_per_s": stats.prefill_tokens_per_second}
+
+    line = {
+        "metric": "decode tok/s at batch 8 (Qwen3-8B bf16, 2,048-token contexts); prefill and batch 1/64 alongside",
+        "value": main["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": main["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: uniform random token ids, seeded random weights N(0,0.02)",
+        "config": {"model": "Qwen3-8B shape", "layers": layers, "layers_of_model": full_layers,
+                   "hidden_size": cfg["hidden_size"], "num_heads": cfg["num_attention_heads"],
+                   "num_kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate_size": cfg["intermediate_size"], "vocab_size": cfg["vocab_size"],
+                   "tied_head": False, "global_batch": batch, "seq_len": context,
+                   "max_context": cfg["max_position_embeddings"], "page_tokens": page_tokens,
+                   "prefill_tokens": prefill_tokens, "parallelism": "1 gpu",
+                   "cache_between_steps": "each step reads ~15 GB of weights, far beyond the 126 MB L2",
+                   "decode": "CUDA graph per step, sampled ids fed back on device"},
+        "clocks": clocks, "e2e": e2e, "gpu_launches": main["launches"], "prefill": prefill,
+        "roofline": roofline, "points": extra, "impl": "leone_b200", "build_seconds": round(build_s, 1),
+    }
+    print(json.dumps(line))
+    return 0

@@ -1,0 +1,647 @@
+// Causal grouped-query attention over the paged cache in bfloat16 with fp32 softmax:
+// a tiled kernel for prompt portions (and mixed batches), and a split-KV kernel
+// for decode steps with its merge.
+//
+// Formulas: kv_head = q_head / (n_q / n_kv); score = (q.k) * scale; online softmax
+// with running maximum and sum; output = numerator / sum (crates/leone/src/cpu.rs:2299-2421).
+// The reference's decode kernel runs one block per (query head, split), so the keys of
+// a KV head are fetched once per query head (crates/leone-cuda/cuda/ie_cuda.cu:4464-4556),
+// and its prompt path materialises the score matrix (ie_cuda.cu:5123-5220).  Here the
+// query heads of one KV head share each key/value tile, scores never leave registers,
+// and pages are gathered through the block table with asynchronous 16-byte copies.
+//
+// Both kernels keep the products on mma.sync tensor-core tiles (m16n8k16, bf16 in, fp32
+// out): the decode step is bound by reading the cache, not by arithmetic.
+//
+// Sizes: head_dim a multiple of 16 up to 128 (instantiated below); up to 64 query heads
+// per KV head; any page size; any window.  Other sizes are refused (the caller falls
+// back to the any-size kernel).
+#include "common.cuh"
+
+namespace leone {
+namespace tiled {
+
+constexpr int kThreads = 128;
+constexpr int kKeyTile = 64;
+constexpr int kRowsPerBlock = 64;      // query rows (token, head) per block in the prompt kernel
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;     // 0 source bytes: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t* r) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t* r) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+      "{%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+struct PagedArgs {
+  const __nv_bfloat16* k_pool;
+  const __nv_bfloat16* v_pool;
+  const int* block_table;
+  int table_width;
+  int page_tokens;
+  int num_pages;
+  int n_kv;
+};
+
+// Copies keys/values [tile_start, tile_start+64) of one sequence and KV head into shared
+// memory rows of D+8 elements; rows at or past `k_end` are zero-filled.
+template <int D>
+__device__ __forceinline__ void load_kv_tile(__nv_bfloat16* k_s, __nv_bfloat16* v_s,
+                                             long long* row_src, const PagedArgs& pa, int seq,
+                                             int kvh, int tile_start, int k_end, int* status,
+                                             int token_row) {
+  constexpr int kRow = D + 8;
+  constexpr int kChunks = D / 8;
+  const int tid = threadIdx.x;
+  if (tid < kKeyTile) {
+    const int kj = tile_start + tid;
+    long long src = -1;
+    if (kj < k_end && kj >= 0) {
+      const int blk = kj / pa.page_tokens;
+      const int page = blk < pa.table_width ? pa.block_table[(size_t)seq * pa.table_width + blk] : -1;
+      if (page < 0 || page >= pa.num_pages) {
+        set_status(status, kBadPage, token_row, page, kj);
+      } else {
+        src = (((long long)page * pa.n_kv + kvh) * pa.page_tokens + (kj % pa.page_tokens)) * D;
+      }
+    }
+    row_src[tid] = src;
+  }
+  __syncthreads();
+  for (int idx = tid; idx < kKeyTile * kChunks; idx += kThreads) {
+    const int row = idx / kChunks, ch = idx - row * kChunks;
+    const long long src = row_src[row];
+    const bool ok = src >= 0;
+    const long long off = ok ? src + ch * 8 : 0;
+    cp_async16(smem_u32(k_s + row * kRow + ch * 8), pa.k_pool + off, ok);
+    cp_async16(smem_u32(v_s + row * kRow + ch * 8), pa.v_pool + off, ok);
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// Prompt portions and mixed batches.  grid = (query tiles, n_kv, sequences).
+// A block owns up to 64 rows = (tokens of the tile) x (the g query heads of one KV head),
+// 16 rows per warp, and walks the keys in tiles of 64.
+// ------------------------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(kThreads)
+attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
+                         __nv_bfloat16* __restrict__ out, int out_stride, PagedArgs pa,
+                         const int* __restrict__ q_start, const int* __restrict__ ctx_len,
+                         int n_q, float scale, int window, int* status) {
+  constexpr int kRow = D + 8;
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [64][kRow]
+  __nv_bfloat16* kv_s = q_s + kRowsPerBlock * kRow;                           // [2 stages][K,V][64][kRow]
+  long long* row_src = reinterpret_cast<long long*>(kv_s + 4 * kKeyTile * kRow);   // [2][64]
+
+  const int seq = blockIdx.z, kvh = blockIdx.y, qt = blockIdx.x;
+  const int g = n_q / pa.n_kv;
+  const int tq = kRowsPerBlock / g;                 // tokens per tile
+  const int q0 = q_start[seq], q_len = q_start[seq + 1] - q0;
+  const int tok0 = qt * tq;
+  if (tok0 >= q_len) return;
+  const int ctx = ctx_len[seq], start = ctx - q_len;
+  const int tok1 = min(q_len, tok0 + tq);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  // gather the tile's query rows
+  for (int idx = tid; idx < kRowsPerBlock * (D / 8); idx += kThreads) {
+    const int r = idx / (D / 8), ch = idx - r * (D / 8);
+    const int tl = r / g, hh = r - tl * g;
+    const int token = tok0 + tl;
+    const bool ok = tl < tq && token < tok1;
+    const __nv_bfloat16* src =
+        qkv + (size_t)(q0 + (ok ? token : 0)) * row_stride + (size_t)(kvh * g + hh) * D + ch * 8;
+    cp_async16(smem_u32(q_s + r * kRow + ch * 8), src, ok);
+  }
+  cp_async_commit();
+
+  const int k_hi = start + tok1;                       // one past the last key any row reads
+  int k_lo = 0;
+  if (window > 0) k_lo = max(0, start + tok0 - window + 1);
+  const int tile0 = (k_lo / kKeyTile) * kKeyTile;
+  const int n_tiles = (k_hi - tile0 + kKeyTile - 1) / kKeyTile;
+
+  load_kv_tile<D>(kv_s, kv_s + kKeyTile * kRow, row_src, pa, seq, kvh, tile0, k_hi, status, q0 + tok0);
+  cp_async_commit();
+
+  // this thread's two rows
+  int row_pos[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = warp * 16 + (lane >> 2) + h * 8;
+    const int tl = r / g;
+    row_pos[h] = (tl < tq && tok0 + tl < tok1) ? start + tok0 + tl : -1;   // -1: row unused
+  }
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  float o_acc[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o_acc[i][j] = 0.f;
+  uint32_t q_frag[D / 16][4];
+  const float sl2 = scale * kLog2e;
+
+  for (int t = 0; t < n_tiles; ++t) {
+    const int stage = t & 1;
+    __nv_bfloat16* k_s = kv_s + stage * 2 * kKeyTile * kRow;
+    __nv_bfloat16* v_s = k_s + kKeyTile * kRow;
+    if (t + 1 < n_tiles) {
+      __nv_bfloat16* k_n = kv_s + (stage ^ 1) * 2 * kKeyTile * kRow;
+      load_kv_tile<D>(k_n, k_n + kKeyTile * kRow, row_src + (stage ^ 1) * kKeyTile, pa, seq, kvh,
+                      tile0 + (t + 1) * kKeyTile, k_hi, status, q0 + tok0);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    if (t == 0) {
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        const int mi = lane >> 3;
+        const int r = warp * 16 + (mi & 1) * 8 + (lane & 7), c = ks * 16 + (mi >> 1) * 8;
+        ldmatrix_x4(smem_u32(q_s + r * kRow + c), q_frag[ks]);
+      }
+    }
+    const int tile_start = tile0 + t * kKeyTile;
+    // S = Q K^T for 64 keys: 8 n-tiles of 8 keys
+    float s[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+#pragma unroll
+      for (int kp = 0; kp < 4; ++kp) {            // 16 keys per ldmatrix.x4
+        uint32_t b[4];
+        const int mi = lane >> 3;
+        const int r = kp * 16 + (mi >> 1) * 8 + (lane & 7), c = ks * 16 + (mi & 1) * 8;
+        ldmatrix_x4(smem_u32(k_s + r * kRow + c), b);
+        mma_16816(s[kp * 2], q_frag[ks], b[0], b[1]);
+        mma_16816(s[kp * 2 + 1], q_frag[ks], b[2], b[3]);
+      }
+    }
+    // mask and online softmax
+    float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int h = j >> 1;
+        const int kj = tile_start + nt * 8 + (lane & 3) * 2 + (j & 1);
+        const bool keep = row_pos[h] >= 0 && kj <= row_pos[h] &&
+                          (window <= 0 || kj > row_pos[h] - window);
+        const float v = keep ? s[nt][j] * sl2 : -INFINITY;
+        s[nt][j] = v;
+        tile_max[h] = fmaxf(tile_max[h], v);
+      }
+    }
+    float alpha[2], m_use[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 1));
+      tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 2));
+      const float m_new = fmaxf(m_run[h], tile_max[h]);
+      m_use[h] = m_new == -INFINITY ? 0.f : m_new;
+      alpha[h] = m_run[h] == -INFINITY ? 0.f : exp2f(m_run[h] - m_use[h]);
+      m_run[h] = m_new;
+      l_run[h] *= alpha[h];
+    }
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      o_acc[i][0] *= alpha[0];
+      o_acc[i][1] *= alpha[0];
+      o_acc[i][2] *= alpha[1];
+      o_acc[i][3] *= alpha[1];
+    }
+    uint32_t p_frag[4][4];
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      const float p0 = exp2f(s[nt][0] - m_use[0]), p1 = exp2f(s[nt][1] - m_use[0]);
+      const float p2 = exp2f(s[nt][2] - m_use[1]), p3 = exp2f(s[nt][3] - m_use[1]);
+      l_run[0] += p0 + p1;
+      l_run[1] += p2 + p3;
+      p_frag[nt >> 1][(nt & 1) * 2] = pack_bf16(p0, p1);
+      p_frag[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(p2, p3);
+    }
+    // O += P V
+#pragma unroll
+    for (int kp = 0; kp < 4; ++kp) {
+#pragma unroll
+      for (int np = 0; np < D / 16; ++np) {
+        uint32_t b[4];
+        const int mi = lane >> 3;
+        const int r = kp * 16 + (mi & 1) * 8 + (lane & 7), c = np * 16 + (mi >> 1) * 8;
+        ldmatrix_x4_trans(smem_u32(v_s + r * kRow + c), b);
+        mma_16816(o_acc[np * 2], p_frag[kp], b[0], b[1]);
+        mma_16816(o_acc[np * 2 + 1], p_frag[kp], b[2], b[3]);
+      }
+    }
+    __syncthreads();      // everyone is done with this stage before it is refilled
+  }
+
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    if (row_pos[h] < 0) continue;
+    const int r = warp * 16 + (lane >> 2) + h * 8;
+    const int tl = r / g, hh = r - tl * g;
+    const float inv = l_run[h] > 0.f ? 1.f / l_run[h] : 0.f;
+    __nv_bfloat16* dst = out + (size_t)(q0 + tok0 + tl) * out_stride + (size_t)(kvh * g + hh) * D;
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      const uint32_t v = pack_bf16(o_acc[i][h * 2] * inv, o_acc[i][h * 2 + 1] * inv);
+      *reinterpret_cast<uint32_t*>(dst + i * 8 + (lane & 3) * 2) = v;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// Decode: one query token per sequence.  grid = (n_kv * head groups, splits, sequences).
+// The (up to 16) query heads of the KV head are the 16 rows of every MMA; the four warps
+// take 16 keys each of every 64-key tile and are merged at the end.  With more than one
+// split the block writes (max, sum, unnormalised output) to scratch for the merge kernel.
+// ------------------------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(kThreads)
+attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
+                        __nv_bfloat16* __restrict__ out, int out_stride, PagedArgs pa,
+                        const int* __restrict__ q_start, const int* __restrict__ ctx_len, int n_q,
+                        float scale, int window, int splits, float* __restrict__ part_o,
+                        float* __restrict__ part_ml, int* status) {
+  constexpr int kRow = D + 8;
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [16][kRow]
+  __nv_bfloat16* kv_s = q_s + 16 * kRow;                                      // [2][K,V][64][kRow]
+  long long* row_src = reinterpret_cast<long long*>(kv_s + 4 * kKeyTile * kRow);   // [2][64]
+
+  const int g = n_q / pa.n_kv;
+  const int groups = (g + 15) / 16;
+  const int kvh = blockIdx.x / groups, hg = blockIdx.x - kvh * groups;
+  const int head0 = kvh * g + hg * 16, heads = min(16, g - hg * 16);
+  const int split = blockIdx.y, seq = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int row_token = q_start[seq];
+  const int ctx = ctx_len[seq];
+  const int pos = ctx - 1;
+  const int k_lo = window > 0 ? max(0, ctx - window) : 0;
+  const int total = ctx - k_lo;
+  const int chunk = ((total + splits - 1) / splits + kKeyTile - 1) / kKeyTile * kKeyTile;
+  const int k_begin = k_lo + split * chunk, k_end = min(ctx, k_begin + chunk);
+  const int n_tiles = k_end > k_begin ? (k_end - k_begin + kKeyTile - 1) / kKeyTile : 0;
+
+  if (n_tiles == 0) {
+    if (splits > 1) {
+      for (int h = tid; h < heads; h += kThreads) {
+        float* ml = part_ml + (((size_t)seq * n_q + head0 + h) * splits + split) * 2;
+        ml[0] = -INFINITY;
+        ml[1] = 0.f;
+      }
+    } else {
+      for (int idx = tid; idx < heads * D; idx += kThreads)
+        out[(size_t)row_token * out_stride + (size_t)head0 * D + idx] = __float2bfloat16_rn(0.f);
+    }
+    return;
+  }
+
+  for (int idx = tid; idx < 16 * (D / 8); idx += kThreads) {
+    const int r = idx / (D / 8), ch = idx - r * (D / 8);
+    const bool ok = r < heads;
+    const __nv_bfloat16* src =
+        qkv + (size_t)row_token * row_stride + (size_t)(head0 + (ok ? r : 0)) * D + ch * 8;
+    cp_async16(smem_u32(q_s + r * kRow + ch * 8), src, ok);
+  }
+  cp_async_commit();
+  load_kv_tile<D>(kv_s, kv_s + kKeyTile * kRow, row_src, pa, seq, kvh, k_begin, k_end, status, row_token);
+  cp_async_commit();
+
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  float o_acc[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o_acc[i][j] = 0.f;
+  uint32_t q_frag[D / 16][4];
+  const float sl2 = scale * kLog2e;
+
+  for (int t = 0; t < n_tiles; ++t) {
+    const int stage = t & 1;
+    __nv_bfloat16* k_s = kv_s + stage * 2 * kKeyTile * kRow;
+    __nv_bfloat16* v_s = k_s + kKeyTile * kRow;
+    if (t + 1 < n_tiles) {
+      __nv_bfloat16* k_n = kv_s + (stage ^ 1) * 2 * kKeyTile * kRow;
+      load_kv_tile<D>(k_n, k_n + kKeyTile * kRow, row_src + (stage ^ 1) * kKeyTile, pa, seq, kvh,
+                      k_begin + (t + 1) * kKeyTile, k_end, status, row_token);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    if (t == 0) {
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        const int mi = lane >> 3;
+        const int r = (mi & 1) * 8 + (lane & 7), c = ks * 16 + (mi >> 1) * 8;
+        ldmatrix_x4(smem_u32(q_s + r * kRow + c), q_frag[ks]);
+      }
+    }
+    const int key0 = k_begin + t * kKeyTile + warp * 16;     // this warp's 16 keys
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      uint32_t b[4];
+      const int mi = lane >> 3;
+      const int r = warp * 16 + (mi >> 1) * 8 + (lane & 7), c = ks * 16 + (mi & 1) * 8;
+      ldmatrix_x4(smem_u32(k_s + r * kRow + c), b);
+      mma_16816(s[0], q_frag[ks], b[0], b[1]);
+      mma_16816(s[1], q_frag[ks], b[2], b[3]);
+    }
+    float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int kj = key0 + nt * 8 + (lane & 3) * 2 + (j & 1);
+        const float v = (kj < k_end && kj <= pos) ? s[nt][j] * sl2 : -INFINITY;
+        s[nt][j] = v;
+        tile_max[j >> 1] = fmaxf(tile_max[j >> 1], v);
+      }
+    float alpha[2], m_use[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 1));
+      tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 2));
+      const float m_new = fmaxf(m_run[h], tile_max[h]);
+      m_use[h] = m_new == -INFINITY ? 0.f : m_new;
+      alpha[h] = m_run[h] == -INFINITY ? 0.f : exp2f(m_run[h] - m_use[h]);
+      m_run[h] = m_new;
+      l_run[h] *= alpha[h];
+    }
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      o_acc[i][0] *= alpha[0];
+      o_acc[i][1] *= alpha[0];
+      o_acc[i][2] *= alpha[1];
+      o_acc[i][3] *= alpha[1];
+    }
+    uint32_t p_frag[4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      const float p0 = exp2f(s[nt][0] - m_use[0]), p1 = exp2f(s[nt][1] - m_use[0]);
+      const float p2 = exp2f(s[nt][2] - m_use[1]), p3 = exp2f(s[nt][3] - m_use[1]);
+      l_run[0] += p0 + p1;
+      l_run[1] += p2 + p3;
+      p_frag[nt * 2] = pack_bf16(p0, p1);
+      p_frag[nt * 2 + 1] = pack_bf16(p2, p3);
+    }
+#pragma unroll
+    for (int np = 0; np < D / 16; ++np) {
+      uint32_t b[4];
+      const int mi = lane >> 3;
+      const int r = warp * 16 + (mi & 1) * 8 + (lane & 7), c = np * 16 + (mi >> 1) * 8;
+      ldmatrix_x4_trans(smem_u32(v_s + r * kRow + c), b);
+      mma_16816(o_acc[np * 2], p_frag, b[0], b[1]);
+      mma_16816(o_acc[np * 2 + 1], p_frag, b[2], b[3]);
+    }
+    __syncthreads();
+  }
+
+  // merge the four warps through shared memory (the K/V stages are free now)
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+  }
+  float* mo = reinterpret_cast<float*>(kv_s);          // [4 warps][16 rows][D]
+  float* mml = mo + 4 * 16 * D;                        // [4][16][2]
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = (lane >> 2) + h * 8;
+    if ((lane & 3) == 0) {
+      mml[(warp * 16 + r) * 2] = m_run[h];
+      mml[(warp * 16 + r) * 2 + 1] = l_run[h];
+    }
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      float* dst = mo + (size_t)(warp * 16 + r) * D + i * 8 + (lane & 3) * 2;
+      dst[0] = o_acc[i][h * 2];
+      dst[1] = o_acc[i][h * 2 + 1];
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < heads * D; idx += kThreads) {
+    const int r = idx / D, c = idx - r * D;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) m = fmaxf(m, mml[(w * 16 + r) * 2]);
+    float l = 0.f, o = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = mml[(w * 16 + r) * 2];
+      const float f = mw == -INFINITY ? 0.f : exp2f(mw - m);
+      l += f * mml[(w * 16 + r) * 2 + 1];
+      o += f * mo[(size_t)(w * 16 + r) * D + c];
+    }
+    if (splits > 1) {
+      const size_t p = ((size_t)seq * n_q + head0 + r) * splits + split;
+      part_o[p * D + c] = o;
+      if (c == 0) {
+        part_ml[p * 2] = m;
+        part_ml[p * 2 + 1] = l;
+      }
+    } else {
+      out[(size_t)row_token * out_stride + (size_t)(head0 + r) * D + c] =
+          __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+    }
+  }
+}
+
+// Merge of the split partials: global maximum, rescaled sums, weighted numerators / global
+// sum (crates/leone-cuda/cuda/ie_cuda.cu:4769-4812).  grid = (n_q, sequences), D threads... any.
+__global__ void attention_merge_kernel(const float* __restrict__ part_o,
+                                       const float* __restrict__ part_ml,
+                                       __nv_bfloat16* __restrict__ out, int out_stride,
+                                       const int* __restrict__ q_start, int n_q, int d, int splits) {
+  const int head = blockIdx.x, seq = blockIdx.y;
+  const size_t base = ((size_t)seq * n_q + head) * splits;
+  float m = -INFINITY;
+  for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[(base + s) * 2]);
+  float l = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float ms = part_ml[(base + s) * 2];
+    if (ms != -INFINITY) l += exp2f(ms - m) * part_ml[(base + s) * 2 + 1];
+  }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  __nv_bfloat16* dst = out + (size_t)q_start[seq] * out_stride + (size_t)head * d;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    float o = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float ms = part_ml[(base + s) * 2];
+      if (ms != -INFINITY) o += exp2f(ms - m) * part_o[(base + s) * d + c];
+    }
+    dst[c] = __float2bfloat16_rn(o * inv);
+  }
+}
+
+template <int D> constexpr int prefill_smem() {
+  return (kRowsPerBlock + 4 * kKeyTile) * (D + 8) * 2 + 2 * kKeyTile * 8;
+}
+template <int D> constexpr int decode_smem() {
+  const int tiles = (16 + 4 * kKeyTile) * (D + 8) * 2 + 2 * kKeyTile * 8;
+  const int merge = 16 * (D + 8) * 2 + 4 * 16 * D * 4 + 4 * 16 * 2 * 4;
+  return tiles > merge ? tiles : merge;
+}
+
+template <int D>
+int launch_prefill(const __nv_bfloat16* qkv, int row_stride, __nv_bfloat16* out, int out_stride,
+                   const PagedArgs& pa, const int* q_start, const int* ctx_len, int n_seqs, int n_q,
+                   int max_q_len, float scale, int window, int* status, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<D>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, prefill_smem<D>());
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int g = n_q / pa.n_kv;
+  const int tq = kRowsPerBlock / g;
+  dim3 grid((max_q_len + tq - 1) / tq, pa.n_kv, n_seqs);
+  attention_prefill_kernel<D><<<grid, kThreads, prefill_smem<D>(), stream>>>(
+      qkv, row_stride, out, out_stride, pa, q_start, ctx_len, n_q, scale, window, status);
+  return launch_result();
+}
+
+template <int D>
+int launch_decode(const __nv_bfloat16* qkv, int row_stride, __nv_bfloat16* out, int out_stride,
+                  const PagedArgs& pa, const int* q_start, const int* ctx_len, int n_seqs, int n_q,
+                  float scale, int window, int splits, float* part_o, float* part_ml, int* status,
+                  cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, decode_smem<D>());
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int g = n_q / pa.n_kv;
+  dim3 grid(pa.n_kv * ((g + 15) / 16), splits, n_seqs);
+  attention_decode_kernel<D><<<grid, kThreads, decode_smem<D>(), stream>>>(
+      qkv, row_stride, out, out_stride, pa, q_start, ctx_len, n_q, scale, window, splits, part_o,
+      part_ml, status);
+  int r = launch_result();
+  if (r != 0 || splits == 1) return r;
+  dim3 mgrid(n_q, n_seqs);
+  attention_merge_kernel<<<mgrid, D >= 64 ? 64 : 32, 0, stream>>>(part_o, part_ml, out, out_stride,
+                                                                q_start, n_q, D, splits);
+  return launch_result();
+}
+
+}  // namespace tiled
+}  // namespace leone
+
+using namespace leone;
+using namespace leone::tiled;
+
+#define LEONE_DISPATCH_D(d, CALL)              \
+  switch (d) {                                 \
+    case 16: { constexpr int DD = 16; CALL; }  \
+    case 32: { constexpr int DD = 32; CALL; }  \
+    case 48: { constexpr int DD = 48; CALL; }  \
+    case 64: { constexpr int DD = 64; CALL; }  \
+    case 80: { constexpr int DD = 80; CALL; }  \
+    case 96: { constexpr int DD = 96; CALL; }  \
+    case 112: { constexpr int DD = 112; CALL; } \
+    case 128: { constexpr int DD = 128; CALL; } \
+    default: return kRefusedSize;              \
+  }
+
+static int check_common(int d, int n_q, int n_kv, int row_stride, int out_stride, const void* qkv,
+                        const void* k_pool, const void* v_pool, int page_tokens, int table_width) {
+  if (d <= 0 || d % 16 != 0 || d > 128) return kRefusedSize;
+  if (n_q <= 0 || n_kv <= 0 || n_q % n_kv != 0) return kRefusedSize;
+  if (page_tokens <= 0 || table_width <= 0) return kRefusedSize;
+  if (row_stride % 8 != 0 || out_stride % 2 != 0) return kRefusedAlignment;
+  if (((uintptr_t)qkv | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) return kRefusedAlignment;
+  return 0;
+}
+
+// Prompt portions and mixed batches.  qkv: [tokens, row_stride] bf16 with the query heads first;
+// out: [tokens, out_stride] bf16; q_start: [n_seqs+1]; ctx_len: [n_seqs] lengths after this step.
+extern "C" int leone_attention_prefill(const void* qkv, int row_stride, void* out, int out_stride,
+                                       const void* k_pool, const void* v_pool,
+                                       const int* block_table, int table_width, const int* q_start,
+                                       const int* ctx_len, int n_seqs, int max_q_len, int n_q,
+                                       int n_kv, int d, float scale, int window, int page_tokens,
+                                       int num_pages, int* status, cudaStream_t stream) {
+  if (n_seqs <= 0 || max_q_len <= 0) return 0;
+  int r = check_common(d, n_q, n_kv, row_stride, out_stride, qkv, k_pool, v_pool, page_tokens, table_width);
+  if (r != 0) return r;
+  if (n_q / n_kv > kRowsPerBlock || n_kv > 65535 || n_seqs > 65535) return kRefusedSize;
+  PagedArgs pa{(const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, block_table, table_width,
+               page_tokens, num_pages, n_kv};
+  LEONE_DISPATCH_D(d, return launch_prefill<DD>((const __nv_bfloat16*)qkv, row_stride,
+                                                (__nv_bfloat16*)out, out_stride, pa, q_start, ctx_len,
+                                                n_seqs, n_q, max_q_len, scale, window, status, stream));
+}
+
+// Scratch floats a decode call with `splits` needs: part_o then part_ml, contiguous.
+extern "C" long long leone_attention_decode_scratch(int n_seqs, int n_q, int d, int splits) {
+  return splits > 1 ? (long long)n_seqs * n_q * splits * (d + 2) : 0;
+}
+
+// Decode steps: every sequence has exactly one query token (row q_start[seq]).
+extern "C" int leone_attention_decode(const void* qkv, int row_stride, void* out, int out_stride,
+                                      const void* k_pool, const void* v_pool, const int* block_table,
+                                      int table_width, const int* q_start, const int* ctx_len,
+                                      int n_seqs, int n_q, int n_kv, int d, float scale, int window,
+                                      int page_tokens, int num_pages, int splits, float* scratch,
+                                      int* status, cudaStream_t stream) {
+  if (n_seqs <= 0) return 0;
+  int r = check_common(d, n_q, n_kv, row_stride, out_stride, qkv, k_pool, v_pool, page_tokens, table_width);
+  if (r != 0) return r;
+  if (splits < 1 || splits > 65535 || n_seqs > 65535) return kRefusedSize;
+  if (splits > 1 && scratch == nullptr) return kRefusedSize;
+  PagedArgs pa{(const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, block_table, table_width,
+               page_tokens, num_pages, n_kv};
+  float* part_o = scratch;
+  float* part_ml = scratch ? scratch + (size_t)n_seqs * n_q * splits * d : nullptr;
+  LEONE_DISPATCH_D(d, return launch_decode<DD>((const __nv_bfloat16*)qkv, row_stride,
+                                               (__nv_bfloat16*)out, out_stride, pa, q_start, ctx_len,
+                                               n_seqs, n_q, scale, window, splits, part_o, part_ml,
+                                               status, stream));
+}

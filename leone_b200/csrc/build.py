@@ -30,7 +30,7 @@ MODULES: Dict[str, List[str]] = {
     # every run needs these: both dtypes, every size
     "core": ["elementwise.cu", "gemm_simt.cu", "attention_generic.cu"],
     # the bfloat16 serving path: tensor-core products and tiled attention
-    "bf16": ["gemm_tc.cu"],
+    "bf16": ["gemm_tc.cu", "attention_tiled.cu"],
 }
 HEADERS = ["common.cuh", "tc_common.cuh"]
 

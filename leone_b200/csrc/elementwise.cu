@@ -253,9 +253,41 @@ __global__ void sample_kernel(const float* __restrict__ logits, int vocab,
   }
 }
 
+// ---------------------------------------------------------------------------
+// Feeds a decode step's sampled tokens back as the next step's inputs without the host:
+// token_ids <- sampled, positions/ctx_len/sample positions += 1, and the sampled ids are
+// appended to a history the host reads once per quantum.  One block.  The reference keeps
+// its decode position in a device word that a kernel increments for graph replay
+// (crates/leone-cuda/cuda/ie_cuda.cu:2940); this is the same idea for a whole batch.
+// ---------------------------------------------------------------------------
+__global__ void decode_advance_kernel(int* token_ids, int* positions, int* ctx_len,
+                                      long long* sample_pos, const int* sampled, int* history,
+                                      int* step_counter, int n, int max_steps) {
+  const int step = *step_counter;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int tok = sampled[i];
+    token_ids[i] = tok;
+    positions[i] += 1;
+    ctx_len[i] += 1;
+    sample_pos[i] += 1;
+    if (step < max_steps) history[(size_t)step * n + i] = tok;
+  }
+  if (threadIdx.x == 0) *step_counter = step + 1;
+}
+
 }  // namespace leone
 
 using namespace leone;
+
+extern "C" int leone_decode_advance(int* token_ids, int* positions, int* ctx_len,
+                                    long long* sample_pos, const int* sampled, int* history,
+                                    int* step_counter, int n, int max_steps, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  decode_advance_kernel<<<1, n < 1024 ? ((n + 31) / 32) * 32 : 1024, 0, stream>>>(
+      token_ids, positions, ctx_len, sample_pos, sampled, history, step_counter, n, max_steps);
+  return launch_result();
+}
 
 extern "C" int leone_embedding(int dtype, const void* table, const int* ids, float* out, int n,
                                int hidden, int vocab, int* status, cudaStream_t stream) {

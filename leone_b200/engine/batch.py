@@ -52,8 +52,9 @@ class StepContext:
         self.layer_caches: Dict[int, object] = {}
         self.fixed_shapes = False      # True while a CUDA graph is captured or replayed
 
-    def cache_view(self, layer_index: int):
-        return self.layer_caches.get(layer_index)
+    def cache_view(self, run_position: int):
+        """The cache of the layer at this position of the run order (None if it has none)."""
+        return self.layer_caches.get(run_position)
 
 
 def pack_metadata(token_lists: Sequence[Sequence[int]], starts: Sequence[int], slots: Sequence[int],

@@ -1,0 +1,123 @@
+"""Decode steps replayed from a CUDA graph, with sampled tokens fed back on the device.
+
+For a fixed set of B decoding requests the whole step — embedding, every layer, final norm,
+output head, sampling, and the kernel that turns the sampled ids into the next step's inputs —
+is captured once and replayed.  Everything that changes between steps (token ids, positions,
+lengths, block tables, sampling positions) lives in device buffers that the captured kernels
+read, so one graph serves any context length.  The reference captures its single-request
+decode chain the same way and keeps the position in a device word
+(crates/leone/src/runtime.rs:7107-7291, crates/leone/src/backend.rs:1586-1595); it re-captures
+when the context bucket changes (crates/leone/src/runtime.rs:5005-5009), which is not needed here.
+
+A *quantum* of up to ``max_quantum`` steps runs without the host: pages for the whole quantum
+are reserved and written into the block tables first, and the sampled ids of all its steps are
+read back once (the reference's service quantum is 4 tokens, crates/leone-cli/src/server.rs:6190-6203).
+"""
+from __future__ import annotations
+
+from typing import Dict, Hashable, List, Sequence
+
+import numpy as np
+import torch
+
+from .batch import StepContext, pack_metadata
+
+
+class DecodeGraph:
+    def __init__(self, engine, batch: int, max_quantum: int = 64):
+        self.engine = engine
+        self.batch = batch
+        self.max_quantum = max_quantum
+        dev = engine.device
+        self.widths = [-(-engine.spec.max_positions // engine.page_tokens) for _ in engine.cache.groups]
+        tables = [np.full((batch, w), -1, dtype=np.int32) for w in self.widths]
+        packed, self.offsets, self.bt_offsets, _ = pack_metadata(
+            [[0]] * batch, [0] * batch, [0] * batch, [[0]] * batch, tables)
+        self.size = packed.size
+        self.meta = torch.zeros(self.size, dtype=torch.int32, device=dev)
+        self.meta_host = torch.zeros(self.size, dtype=torch.int32, pin_memory=True)
+        self.sample_host = torch.zeros(3 * batch, dtype=torch.int64, pin_memory=True)
+        self.sample_dev = torch.zeros(3 * batch, dtype=torch.int64, device=dev)
+        self.sampled = torch.zeros(batch, dtype=torch.int32, device=dev)
+        self.history = torch.zeros((max_quantum, batch), dtype=torch.int32, device=dev)
+        self.history_host = torch.zeros((max_quantum, batch), dtype=torch.int32, pin_memory=True)
+        self.counter = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.status_host = torch.zeros(4, dtype=torch.int32, pin_memory=True)
+        self.logits = torch.empty((batch, engine.spec.vocab_size), dtype=torch.float32, device=dev)
+        self.ctx = self._context()
+        self.graph = None
+        self.launches_per_step = 0
+        self.stream = torch.cuda.Stream(device=dev)
+
+    def _view(self, name):
+        o, s = self.offsets[name]
+        return self.meta[o:o + s]
+
+    def _context(self) -> StepContext:
+        e = self.engine
+        ctx = StepContext()
+        for name in self.offsets:
+            setattr(ctx, name, self._view(name))
+        ctx.block_tables = [self.meta[o:o + shape[0] * shape[1]].view(shape) for o, shape in self.bt_offsets]
+        ctx.n_tokens = ctx.n_seqs = ctx.n_logit_rows = self.batch
+        ctx.max_q_len = 1
+        ctx.max_ctx_len = e.spec.max_positions
+        ctx.decode_only = True
+        ctx.fixed_shapes = True
+        ctx.status = e.status
+        ctx.logits_out = self.logits
+        e._attach_caches(ctx)
+        return ctx
+
+    def _one_step(self):
+        e = self.engine
+        b = self.batch
+        logits = e.model.forward(self.ctx)
+        temps = self.sample_dev[:b].view(torch.float32)[:b]
+        e.ops.sample(logits, temps, self.sample_dev[b:2 * b], self.sample_dev[2 * b:3 * b], self.sampled)
+        e.ops.decode_advance(self.ctx.token_ids, self.ctx.positions, self.ctx.ctx_len,
+                             self.sample_dev[2 * b:3 * b], self.sampled, self.history, self.counter)
+
+    def fill(self, rids: Sequence[Hashable], last_tokens: Sequence[int], lengths: Sequence[int], params):
+        """Host → device: this quantum's starting state."""
+        e = self.engine
+        b = self.batch
+        tables = [e.cache.block_table(g.gid, rids, width=w) for g, w in zip(e.cache.groups, self.widths)]
+        packed, _, _, _ = pack_metadata([[int(t)] for t in last_tokens], list(lengths),
+                                        [e.cache.slot(r) for r in rids], [[0]] * b, tables)
+        self.meta_host.numpy()[:] = packed
+        sh = self.sample_host.numpy()
+        self.sample_host[:b].view(torch.float32).numpy()[:b] = np.array([p.temperature for p in params], dtype=np.float32)
+        sh[b:2 * b] = np.array([p.seed & 0xFFFF_FFFF_FFFF_FFFF for p in params], dtype=np.uint64).view(np.int64)
+        sh[2 * b:3 * b] = np.asarray(lengths, dtype=np.int64)      # position of the token being fed
+        self.meta.copy_(self.meta_host, non_blocking=True)
+        self.sample_dev.copy_(self.sample_host, non_blocking=True)
+        self.counter.zero_()
+
+    def capture(self):
+        """Run one step eagerly on the filled buffers (so every scratch buffer exists), then
+        capture one step.  The caller fills the buffers again afterwards: the eager step has
+        advanced them."""
+        cur = torch.cuda.current_stream(self.engine.device)
+        self.stream.wait_stream(cur)
+        with torch.cuda.stream(self.stream):
+            self._one_step()
+            self.stream.synchronize()
+            before = self.engine.ops.launches
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=self.stream):
+                self._one_step()
+            self.launches_per_step = self.engine.ops.launches - before
+        cur.wait_stream(self.stream)
+        self.counter.zero_()
+
+    def run(self, steps: int) -> np.ndarray:
+        """Replay ``steps`` steps and read the sampled ids back: int32 [steps, batch]."""
+        for _ in range(steps):
+            self.graph.replay()
+        self.history_host[:steps].copy_(self.history[:steps], non_blocking=True)
+        self.status_host.copy_(self.engine.status, non_blocking=True)
+        torch.cuda.current_stream(self.engine.device).synchronize()
+        if int(self.status_host[0]) != 0:
+            self.engine.check_status()
+        return self.history_host[:steps].numpy().copy()

@@ -93,12 +93,15 @@ class Engine:
             num_pages = -(-max_tokens // page_tokens)
         self.num_pages = num_pages
         self.max_requests = max_requests
-        requests = self.model.cache_requests()
+        plan = self.model.cache_plan()
         group_specs: List[GroupSpec] = []
-        self._layer_group: Dict[int, tuple] = {}      # layer -> (gid, index within group)
-        self._layer_state: Dict[int, torch.Tensor] = {}
-        for li, req in enumerate(requests):
-            if isinstance(req, PagedKV):
+        self._run_group: Dict[int, tuple] = {}      # run position -> (gid, index within group)
+        self._run_state: Dict[int, torch.Tensor] = {}
+        self._run_source: Dict[int, int] = {}       # run position -> position whose cache it reads
+        for pos, (req, source) in enumerate(plan):
+            if source is not None:
+                self._run_source[pos] = source
+            elif isinstance(req, PagedKV):
                 gs = GroupSpec("window" if req.window else "full", req.num_kv_heads, req.head_dim,
                                req.window)
                 for gid, existing in enumerate(group_specs):
@@ -107,13 +110,13 @@ class Engine:
                 else:
                     gid = len(group_specs)
                     group_specs.append(gs)
-                self._layer_group[li] = (gid, len(group_specs[gid].layers))
-                group_specs[gid].layers.append(li)
+                self._run_group[pos] = (gid, len(group_specs[gid].layers))
+                group_specs[gid].layers.append(pos)
             elif isinstance(req, FixedState):
-                self._layer_state[li] = torch.zeros((max_requests,) + tuple(req.shape),
-                                                    dtype=torch.float32, device=self.device)
+                self._run_state[pos] = torch.zeros((max_requests,) + tuple(req.shape),
+                                                   dtype=torch.float32, device=self.device)
             elif req is not None:
-                raise TypeError(f"layer {li}: unknown cache request {req!r}")
+                raise TypeError(f"run position {pos}: unknown cache request {req!r}")
         self.cache = CacheManager(group_specs, page_tokens, num_pages, max_requests)
         self.pools = []
         for gs in group_specs:
@@ -127,6 +130,8 @@ class Engine:
         self._meta_host = None
         self._meta_event = None
         self.steps_run = 0
+        self._sampler = None
+        self._decode_graphs = {}
 
     # -- construction helpers -----------------------------------------------------------
     @classmethod
@@ -151,7 +156,7 @@ class Engine:
     # -- request lifetime ---------------------------------------------------------------
     def open(self, rid: Hashable) -> int:
         slot = self.cache.open(rid)
-        for state in self._layer_state.values():
+        for state in self._run_state.values():
             state[slot].zero_()
         return slot
 
@@ -201,16 +206,16 @@ class Engine:
         return ctx
 
     def _attach_caches(self, ctx: StepContext) -> None:
-        for li, layer in enumerate(self.spec.layers):
-            src = li if layer.cache_of is None else layer.cache_of
-            writes = layer.cache_of is None
-            if src in self._layer_group:
-                gid, k = self._layer_group[src]
+        for pos in range(len(self.spec.run_order)):
+            src = self._run_source.get(pos, pos)
+            writes = pos not in self._run_source
+            if src in self._run_group:
+                gid, k = self._run_group[src]
                 kp, vp = self.pools[gid]
-                ctx.layer_caches[li] = PagedCacheView(kp[k], vp[k], ctx.block_tables[gid],
-                                                      self.page_tokens, writes)
-            elif src in self._layer_state:
-                ctx.layer_caches[li] = StateView(self._layer_state[src], writes)
+                ctx.layer_caches[pos] = PagedCacheView(kp[k], vp[k], ctx.block_tables[gid],
+                                                       self.page_tokens, writes)
+            elif src in self._run_state:
+                ctx.layer_caches[pos] = StateView(self._run_state[src], writes)
 
     def step(self, entries: Sequence, check: bool = True) -> Optional[torch.Tensor]:
         """Run one batch.  ``entries``: ``StepEntry`` or ``(rid, tokens, want)`` tuples.
@@ -271,6 +276,56 @@ class Engine:
             self.cache.commit(e.rid, wants[e.rid])
         self.steps_run += 1
         return logits
+
+    def sample(self, logits: torch.Tensor, params, positions) -> List[int]:
+        """One token per logits row (greedy or temperature); returns host ints."""
+        if self._sampler is None:
+            from ..sampling.sampler import Sampler
+            self._sampler = Sampler(self.ops, self.device)
+        return self._sampler.sample(logits, params, positions).tolist()
+
+    # -- decode quanta ------------------------------------------------------------------
+    def decode_steps(self, rids: Sequence[Hashable], last_tokens: Sequence[int], params,
+                     steps: int, use_graph: bool = True):
+        """Decode ``steps`` tokens for every request in ``rids``: feed ``last_tokens`` at each
+        request's current length, sample, feed the sample, and so on.  Returns the sampled ids
+        as ``[steps][len(rids)]`` host ints.  Pages for all ``steps`` positions are taken first
+        (:class:`OutOfPages` leaves everything as it was); lengths advance by ``steps``.
+        """
+        rids = list(rids)
+        lengths = [self.cache.length(r) for r in rids]
+        if steps <= 0 or not rids:
+            return []
+        if max(lengths) + steps > self.spec.max_positions:
+            raise ValueError("decode_steps would run past the model's positions")
+        if not (use_graph and self.device.type == "cuda") or steps > 64:
+            out = []
+            toks = list(last_tokens)
+            for _ in range(steps):
+                logits = self.step([(r, [t], [0]) for r, t in zip(rids, toks)])
+                toks = self.sample(logits, params, [self.cache.length(r) - 1 for r in rids])
+                out.append(toks)
+            return out
+        self.cache.reserve({r: l + steps for r, l in zip(rids, lengths)})
+        try:
+            graph = self._decode_graphs.get(len(rids))
+            if graph is None:
+                from .decode_graph import DecodeGraph
+                graph = DecodeGraph(self, len(rids))
+                # capture needs valid tables: fill first, then warm up and capture on them
+                graph.fill(rids, last_tokens, lengths, params)
+                graph.capture()
+                self._decode_graphs[len(rids)] = graph
+            graph.fill(rids, last_tokens, lengths, params)
+            tokens = graph.run(steps)       # also reads and checks the status word
+        except Exception:
+            for r in rids:
+                self.cache.rollback(r)
+            raise
+        for r, l in zip(rids, lengths):
+            self.cache.commit(r, l + steps)
+        self.steps_run += steps
+        return tokens.tolist()
 
     def check_status(self) -> None:
         word = self.status.tolist()

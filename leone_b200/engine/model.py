@@ -93,12 +93,24 @@ class Model:
         self.lm_head = self.rt.ops.prepare_matrix(head)
 
     # -- cache needs ------------------------------------------------------------------
-    def cache_requests(self):
-        """Per layer: ``PagedKV``, ``FixedState`` or ``None`` (also ``None`` for borrowers)."""
-        out = []
-        for layer, block in zip(self.spec.layers, self.blocks):
-            out.append(None if layer.cache_of is not None else block.mixer.cache_request())
-        return out
+    def cache_plan(self):
+        """Per position of ``run_order``: ``(request, source)``.
+
+        A layer that is run twice shares its weights, not its cache: every occurrence in the
+        run order owns a cache of its own (``request`` is a ``PagedKV``/``FixedState``,
+        ``source`` is ``None``).  A layer with ``cache_of`` owns none and reads the cache of
+        the latest earlier occurrence of that layer (``request`` is ``None``, ``source`` its
+        run position)."""
+        plan = []
+        latest = {}
+        for pos, idx in enumerate(self.spec.run_order):
+            layer = self.spec.layers[idx]
+            if layer.cache_of is None:
+                plan.append((self.blocks[idx].mixer.cache_request(), None))
+                latest[idx] = pos
+            else:
+                plan.append((None, latest[layer.cache_of]))
+        return plan
 
     def decode_weight_bytes(self) -> int:
         """Bytes of weights one decode step reads: every layer once per run, the head once
@@ -117,8 +129,8 @@ class Model:
         rt = self.rt
         hidden = rt.buffer("hidden", ctx.n_tokens, self.hidden_size, torch.float32)
         rt.ops.embedding(self.embedding, ctx.token_ids, hidden, ctx.status)
-        for idx in self.spec.run_order:
-            self.blocks[idx].forward(ctx, ctx.cache_view(idx), hidden)
+        for pos, idx in enumerate(self.spec.run_order):
+            self.blocks[idx].forward(ctx, ctx.cache_view(pos), hidden)
         return self.logits(ctx, hidden)
 
     def logits(self, ctx, hidden) -> Optional[torch.Tensor]:

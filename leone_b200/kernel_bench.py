@@ -1,0 +1,163 @@
+"""Times single kernels at given sizes and relates them to the measured rooflines.
+
+    python -m leone_b200.kernel_bench gemm --m 8 --n 4096 --k 12288 [--splits S] [--epilogue E]
+    python -m leone_b200.kernel_bench decode-attention --batch 8 --context 2048
+    python -m leone_b200.kernel_bench prefill-attention --tokens 2048
+    python -m leone_b200.kernel_bench layer-shapes --m 8          # every product of a Qwen3-8B layer
+
+The reference's ``--profile-decode`` prints per-operation microseconds and GEMV GB/s by shape
+(crates/leone-cli/src/main.rs:2918-2995); this is the same kind of table for this engine's
+kernels.  Inputs are larger than the 126 MB L2, or a buffer larger than L2 is written between
+timed launches (``--flush``), so DRAM figures mean something.  Timing is by CUDA events on the
+launching stream after warm-up launches.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import sys
+import types
+
+import torch
+
+from .benchmark import measured_peaks
+
+DEV = "cuda:0"
+
+
+def _time(fn, reps: int, warmup: int, flush=None) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(reps):
+        if flush is not None:
+            flush.add_(1.0)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        fn()
+        stop.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(stop))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def bench_gemm(ops, m, n, k, splits, epilogue, reps, warmup, flush):
+    fast = ops.fast
+    x = torch.randn((m, k), device=DEV).to(torch.bfloat16)
+    # several copies of the weight so successive launches do not hit L2
+    copies = max(1, min(8, int(300e6 // (n * k * 2)) + 1))
+    ws = [(torch.randn((n, k), device=DEV) * 0.02).to(torch.bfloat16) for _ in range(copies)]
+    out_cols = n // 2 if epilogue == 3 else n
+    out = torch.empty((m, out_cols), device=DEV, dtype=torch.bfloat16 if epilogue in (0, 3) else torch.float32)
+    res = out if epilogue == 2 else None
+    if epilogue == 2:
+        out.zero_()
+    state = {"i": 0}
+    if splits is None:
+        splits = fast.choose_splits(m, n, k) if epilogue != 3 else 1
+
+    def run():
+        w = ws[state["i"] % copies]
+        state["i"] += 1
+        fast._gemm(x, w, out, epilogue, res, n, splits=splits)
+
+    ms = _time(run, reps, warmup, flush)
+    bytes_ = n * k * 2 + m * k * 2 + out.numel() * out.element_size()
+    flops = 2.0 * m * n * k
+    return dict(kernel="gemm_tc", m=m, n=n, k=k, splits=splits, epilogue=epilogue, us=ms * 1e3,
+                gbs=bytes_ / ms / 1e6, tflops=flops / ms / 1e9)
+
+
+def bench_decode_attention(ops, batch, context, n_q, n_kv, d, page_tokens, reps, warmup, flush):
+    blocks = -(-context // page_tokens)
+    pages = batch * blocks
+    k_pool = torch.randn((pages, n_kv, page_tokens, d), device=DEV).to(torch.bfloat16)
+    v_pool = torch.randn((pages, n_kv, page_tokens, d), device=DEV).to(torch.bfloat16)
+    table = torch.randperm(pages, device=DEV).to(torch.int32).view(batch, blocks)
+    qkv = torch.randn((batch, (n_q + 2 * n_kv) * d), device=DEV).to(torch.bfloat16)
+    out = torch.empty((batch, n_q * d), device=DEV, dtype=torch.bfloat16)
+    ctx = types.SimpleNamespace(
+        q_start=torch.arange(batch + 1, device=DEV, dtype=torch.int32),
+        ctx_len=torch.full((batch,), context, device=DEV, dtype=torch.int32),
+        status=torch.zeros(4, device=DEV, dtype=torch.int32), n_seqs=batch, max_q_len=1,
+        max_ctx_len=context, decode_only=True)
+    cache = types.SimpleNamespace(k_pool=k_pool, v_pool=v_pool, block_table=table, page_tokens=page_tokens)
+    ms = _time(lambda: ops.fast.attention(ctx, qkv, out, n_q, n_kv, d, 1 / math.sqrt(d), None, cache),
+               reps, warmup, flush)
+    bytes_ = 2.0 * batch * context * n_kv * d * 2
+    return dict(kernel="attention_decode", batch=batch, context=context, us=ms * 1e3,
+                splits=ops.fast.decode_splits(batch, n_kv, n_q // n_kv, context), gbs=bytes_ / ms / 1e6)
+
+
+def bench_prefill_attention(ops, tokens, n_q, n_kv, d, page_tokens, reps, warmup):
+    blocks = -(-tokens // page_tokens)
+    k_pool = torch.randn((blocks, n_kv, page_tokens, d), device=DEV).to(torch.bfloat16)
+    v_pool = torch.randn((blocks, n_kv, page_tokens, d), device=DEV).to(torch.bfloat16)
+    table = torch.randperm(blocks, device=DEV).to(torch.int32).view(1, blocks)
+    qkv = torch.randn((tokens, (n_q + 2 * n_kv) * d), device=DEV).to(torch.bfloat16)
+    out = torch.empty((tokens, n_q * d), device=DEV, dtype=torch.bfloat16)
+    ctx = types.SimpleNamespace(
+        q_start=torch.tensor([0, tokens], device=DEV, dtype=torch.int32),
+        ctx_len=torch.tensor([tokens], device=DEV, dtype=torch.int32),
+        status=torch.zeros(4, device=DEV, dtype=torch.int32), n_seqs=1, max_q_len=tokens,
+        max_ctx_len=tokens, decode_only=False)
+    cache = types.SimpleNamespace(k_pool=k_pool, v_pool=v_pool, block_table=table, page_tokens=page_tokens)
+    ms = _time(lambda: ops.fast.attention(ctx, qkv, out, n_q, n_kv, d, 1 / math.sqrt(d), None, cache),
+               reps, warmup)
+    flops = 2.0 * n_q * d * tokens * tokens       # causal half of QK^T and PV
+    return dict(kernel="attention_prefill", tokens=tokens, us=ms * 1e3, tflops=flops / ms / 1e9)
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="python -m leone_b200.kernel_bench")
+    ap.add_argument("what", choices=["gemm", "decode-attention", "prefill-attention", "layer-shapes"])
+    ap.add_argument("--m", type=int, default=8)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--splits", type=int, default=None)
+    ap.add_argument("--epilogue", type=int, default=0)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=2048)
+    ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--page-tokens", type=int, default=16)
+    ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--flush", action="store_true", help="write a 256 MB buffer between timed launches")
+    args = ap.parse_args(argv)
+    from .ops.cuda import CudaOps
+    ops = CudaOps(DEV, torch.bfloat16)
+    peaks = measured_peaks()
+    flush = torch.zeros(64 << 20, device=DEV) if args.flush else None
+    rows = []
+    if args.what == "gemm":
+        rows.append(bench_gemm(ops, args.m, args.n, args.k, args.splits, args.epilogue, args.reps, args.warmup, flush))
+    elif args.what == "layer-shapes":
+        h, inter, qkv = 4096, 12288, (args.heads + 2 * args.kv_heads) * args.head_dim
+        for name, n, k, epi in (("qkv", qkv, h, 0), ("o_proj", h, args.heads * args.head_dim, 2),
+                                ("gate_up", 2 * inter, h, 3), ("down", h, inter, 2), ("lm_head", 151936, h, 1)):
+            r = bench_gemm(ops, args.m, n, k, None, epi, args.reps, args.warmup, flush)
+            r["name"] = name
+            rows.append(r)
+    elif args.what == "decode-attention":
+        rows.append(bench_decode_attention(ops, args.batch, args.context, args.heads, args.kv_heads,
+                                           args.head_dim, args.page_tokens, args.reps, args.warmup, flush))
+    else:
+        rows.append(bench_prefill_attention(ops, args.tokens, args.heads, args.kv_heads, args.head_dim,
+                                            args.page_tokens, args.reps, args.warmup))
+    for r in rows:
+        if "gbs" in r:
+            r["hbm_frac"] = r["gbs"] / peaks["hbm_gbs"]
+        if "tflops" in r:
+            r["tensor_frac"] = r["tflops"] / peaks["bf16_tflops"]
+        print(json.dumps({k: (round(v, 4) if isinstance(v, float) else v) for k, v in r.items()}))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -277,3 +277,13 @@ class CudaOps:
         self.launches += 1
         _check(self.core.leone_sample(_ptr(logits), rows, vocab, _ptr(temperature), _ptr(seeds),
                                       _ptr(positions), _ptr(out), self._stream()), "sample")
+
+    def decode_advance(self, token_ids, positions, ctx_len, sample_pos, sampled, history, counter):
+        n = token_ids.numel()
+        _need(history.dtype == torch.int32 and history.shape[1] == n and counter.dtype == torch.int32
+              and sample_pos.dtype == torch.int64, "decode_advance arguments")
+        self.launches += 1
+        _check(self.core.leone_decode_advance(_ptr(token_ids), _ptr(positions), _ptr(ctx_len),
+                                              _ptr(sample_pos), _ptr(sampled), _ptr(history),
+                                              _ptr(counter), n, history.shape[0], self._stream()),
+               "decode_advance")

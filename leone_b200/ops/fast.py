@@ -29,6 +29,9 @@ class FastKernels:
         # LEONE_NO_TENSOR_CORES=1 routes every product to the CUDA-core kernel (for fault finding)
         self.use_tensor_cores = os.environ.get("LEONE_NO_TENSOR_CORES", "0") != "1"
         self.status = None
+        self._attn_ws = None
+        self.use_tiled_attention = os.environ.get("LEONE_NO_TILED_ATTENTION", "0") != "1"
+        self.lib.leone_attention_decode_scratch.restype = ctypes.c_longlong
 
     def _stream(self):
         return c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
@@ -101,5 +104,40 @@ class FastKernels:
         return self._gemm(x, w.weight, out, 3, None, w.out_features, splits=1)
 
     # -- attention ------------------------------------------------------------------------
+    def decode_splits(self, n_seqs: int, n_kv: int, g: int, max_ctx: int) -> int:
+        """Splits of the key range so that about two blocks per SM are in flight."""
+        blocks = n_seqs * n_kv * (-(-g // 16))
+        want = max(1, (2 * self.sm_count) // max(blocks, 1))
+        return int(max(1, min(want, -(-max_ctx // 256), 64)))
+
     def attention(self, ctx, qkv, out, n_q, n_kv, d, scale, window, cache) -> bool:
-        return False
+        if not self.use_tiled_attention or qkv.dtype != torch.bfloat16:
+            return False
+        g = n_q // n_kv
+        if d % 16 != 0 or d > 128 or g > 64 or qkv.stride(0) % 8 != 0:
+            return False
+        from ctypes import c_float
+        kp, vp, bt = cache.k_pool, cache.v_pool, cache.block_table
+        common = (_ptr(qkv), qkv.stride(0), _ptr(out), out.stride(0), _ptr(kp), _ptr(vp), _ptr(bt),
+                  bt.shape[1], _ptr(ctx.q_start), _ptr(ctx.ctx_len), ctx.n_seqs)
+        if ctx.decode_only:
+            splits = self.decode_splits(ctx.n_seqs, n_kv, g, ctx.max_ctx_len)
+            scratch = None
+            if splits > 1:
+                need = self.lib.leone_attention_decode_scratch(ctx.n_seqs, n_q, d, splits)
+                scratch = self._attn_scratch(need)
+            code = self.lib.leone_attention_decode(
+                *common, n_q, n_kv, d, c_float(scale), int(window or 0), cache.page_tokens,
+                kp.shape[0], splits, _ptr(scratch), _ptr(ctx.status), self._stream())
+        else:
+            code = self.lib.leone_attention_prefill(
+                *common, ctx.max_q_len, n_q, n_kv, d, c_float(scale), int(window or 0),
+                cache.page_tokens, kp.shape[0], _ptr(ctx.status), self._stream())
+        if code != 0:
+            raise RuntimeError(f"tiled attention refused or failed with code {code}")
+        return True
+
+    def _attn_scratch(self, floats: int):
+        if self._attn_ws is None or self._attn_ws.numel() < floats:
+            self._attn_ws = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=self.device)
+        return self._attn_ws

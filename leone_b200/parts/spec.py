@@ -27,7 +27,8 @@ class LayerSpec:
 
     ``prefix`` is the layer's tensor-name prefix in the checkpoint.
     ``cache_of`` names another layer whose cache this layer's mixer reads
-    instead of owning one (it then writes nothing).
+    instead of owning one (it then writes nothing).  A layer named twice in the
+    run order shares its weights between the runs; each run owns its own cache.
     """
     prefix: str
     block: str

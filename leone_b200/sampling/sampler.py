@@ -61,8 +61,8 @@ class Sampler:
         temps = np.array([p.temperature for p in params], dtype=np.float32)
         host_f = self._host[:self._cap].view(torch.float32).numpy()      # first `cap` int64 = 2*cap floats
         host_f[:rows] = temps
-        host[self._cap:self._cap + rows] = np.array([p.seed & 0x7FFF_FFFF_FFFF_FFFF if p.seed >= 0 else p.seed
-                                                     for p in params], dtype=np.int64)
+        host[self._cap:self._cap + rows] = np.array([p.seed & 0xFFFF_FFFF_FFFF_FFFF for p in params],
+                                                    dtype=np.uint64).view(np.int64)
         host[2 * self._cap:2 * self._cap + rows] = np.asarray(positions, dtype=np.int64)
         self._dev.copy_(self._host, non_blocking=True)
         t = self._dev[:self._cap].view(torch.float32)[:rows]

@@ -1,0 +1,144 @@
+"""The cache manager: no page lost, held twice or freed twice, under random orders of requests."""
+import random
+
+import pytest
+
+from leone_b200.cache.pages import CacheError, CacheManager, GroupSpec, OutOfPages, PagePool, StateSlots
+
+
+def _manager(pages=16, page_tokens=4, slots=4, window=None):
+    groups = [GroupSpec("full", 2, 16)]
+    if window:
+        groups.append(GroupSpec("window", 1, 8, window))
+    return CacheManager(groups, page_tokens, pages, slots)
+
+
+def test_pool_take_and_give_back():
+    pool = PagePool(4)
+    pages = pool.take(3)
+    assert len(set(pages)) == 3 and pool.num_free == 1
+    with pytest.raises(OutOfPages):
+        pool.take(2)
+    assert pool.num_free == 1                     # a refused take takes nothing
+    pool.give_back(pages[:1])
+    with pytest.raises(CacheError):
+        pool.give_back(pages[:1])                 # freed twice
+    with pytest.raises(CacheError):
+        pool.give_back([99])
+    assert pool.take(1) == pages[:1]              # the page just freed is used again first
+
+
+def test_slots():
+    slots = StateSlots(2)
+    a, b = slots.take(), slots.take()
+    assert {a, b} == {0, 1}
+    with pytest.raises(OutOfPages):
+        slots.take()
+    slots.give_back(a)
+    with pytest.raises(CacheError):
+        slots.give_back(a)
+    assert slots.take() == a
+
+
+def test_reserve_commit_rollback_close():
+    m = _manager()
+    m.open("a")
+    m.reserve({"a": 9})                           # 3 pages of 4 tokens
+    assert m.free_pages() == [13] and m.length("a") == 0
+    m.commit("a", 9)
+    m.reserve({"a": 13})
+    m.rollback("a")                               # the failed step's page goes back
+    assert m.free_pages() == [13] and m.length("a") == 9
+    with pytest.raises(CacheError):
+        m.commit("a", 20)                         # more than was reserved
+    table = m.block_table(0, ["a"])
+    assert table.shape == (1, 3) and (table >= 0).all()
+    m.close("a")
+    assert m.free_pages() == [16]
+    with pytest.raises(CacheError):
+        m.close("a")
+    m.check_invariants()
+
+
+def test_reserve_is_all_or_nothing_across_requests():
+    m = _manager(pages=5)
+    m.open("a"), m.open("b")
+    with pytest.raises(OutOfPages):
+        m.reserve({"a": 12, "b": 12})             # 3 + 3 pages > 5
+    assert m.free_pages() == [5]
+    assert m.can_reserve({"a": 12, "b": 8})
+    m.reserve({"a": 12, "b": 8})
+    assert m.free_pages() == [0]
+    m.check_invariants()
+
+
+def test_truncate():
+    m = _manager()
+    m.open("a")
+    m.reserve({"a": 14}), m.commit("a", 14)
+    m.truncate("a", 5)
+    assert m.length("a") == 5 and m.free_pages() == [14]
+    with pytest.raises(CacheError):
+        m.truncate("a", 6)
+
+
+def test_window_group_gives_pages_back_as_the_window_passes():
+    m = _manager(pages=8, page_tokens=4, window=6)
+    m.open("a")
+    m.reserve({"a": 20}), m.commit("a", 20)
+    full, win = m.groups
+    assert full.pool.num_held == 5
+    # the next query is at position 20 and reads keys 15..20: blocks 0..2 (keys 0..11) are passed
+    assert win.tables["a"][:3] == [-1, -1, -1] and win.pool.num_held == 2
+    row = m.block_table(1, ["a"])[0]
+    assert list(row[:3]) == [-1, -1, -1] and (row[3:5] >= 0).all()
+    m.reserve({"a": 24}), m.commit("a", 24)
+    assert win.pool.num_held == 2                 # one taken, one passed
+    m.close("a")
+    assert m.free_pages() == [8, 8]
+    m.check_invariants()
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_orders_never_lose_or_share_a_page(seed):
+    rng = random.Random(seed)
+    m = _manager(pages=24, page_tokens=4, slots=5, window=7 if seed % 2 else None)
+    live, counter = {}, 0
+    for _ in range(400):
+        action = rng.random()
+        if action < 0.25 and len(live) < 5:
+            rid = f"r{counter}"
+            counter += 1
+            m.open(rid)
+            live[rid] = 0
+        elif action < 0.75 and live:
+            picked = rng.sample(sorted(live), rng.randint(1, len(live)))
+            wants = {r: live[r] + rng.randint(1, 9) for r in picked}
+            try:
+                m.reserve(wants)
+            except OutOfPages:
+                before = m.free_pages()
+                assert before == m.free_pages()
+            else:
+                if rng.random() < 0.15:            # the step failed
+                    for r in picked:
+                        m.rollback(r)
+                else:
+                    for r, n in wants.items():
+                        m.commit(r, n)
+                        live[r] = n
+        elif live:
+            rid = rng.choice(sorted(live))
+            m.close(rid)
+            del live[rid]
+        m.check_invariants()
+        for rid, n in live.items():
+            assert m.length(rid) == n
+            for g in m.groups:
+                table = g.tables[rid]
+                for b in range(g.first_live_block(n), g.blocks_for(n)):
+                    assert table[b] >= 0          # every block a query can still read has a page
+    for rid in list(live):
+        m.close(rid)
+    assert all(f == 24 for f in m.free_pages())
+    m.check_invariants()

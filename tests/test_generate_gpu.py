@@ -1,0 +1,89 @@
+"""Generation through the Python entry point on the GPU against the plain implementation."""
+import pytest
+import torch
+
+from tests import replay
+from tests.plain.model import PlainModel, generate as plain_generate
+from tests.tiny import PAGE_TOKENS, make_folder
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    base = tmp_path_factory.mktemp("gen_models")
+    return {w: make_folder(base, w) for w in "ABC"}
+
+
+def _engine(folder, which, dtype, pages, **kw):
+    from leone_b200.engine.engine import Engine
+    return Engine.from_folder(folder, dtype=dtype, page_tokens=PAGE_TOKENS[which], num_pages=pages,
+                              max_requests=4, max_batch_tokens=64, **kw)
+
+
+def test_greedy_three_requests_fp32(folders):
+    """Tiny A: prompts of 5/9/13 tokens, 8 new tokens each, greedy."""
+    from leone_b200 import generate
+    plain = PlainModel(folders["A"])
+    prompts = [replay.random_tokens(256, n, 50 + n) for n in (5, 9, 13)]
+    want = [plain_generate(plain, p, 8) for p in prompts]
+    got = generate(folders["A"], prompts, 8, dtype="float32", page_tokens=4, eos_token_id=-1)
+    assert got == want
+
+
+@pytest.mark.parametrize("policy,pages", [("reserve", 14), ("optimistic", 9)])
+@pytest.mark.parametrize("quantum", [1, 4])
+def test_temperature_chunked_mixed_fp32(folders, policy, pages, quantum):
+    """Tiny B: prompts of 1/7/17/30, prefill portions of 6 mixed with decode, 6 new tokens,
+    temperature 0.8 with per-request seeds; few pages, both page policies."""
+    from leone_b200 import generate
+    plain = PlainModel(folders["B"])
+    prompts = [replay.random_tokens(384, n, 60 + n) for n in (1, 7, 17, 30)]
+    want = [plain_generate(plain, p, 6, 0.8, 7 + i) for i, p in enumerate(prompts)]
+    eng = _engine(folders["B"], "B", "float32", pages)
+    got, stats = generate(eng, prompts, 6, temperature=0.8, seed=7, prefill_chunk=6, max_batch_tokens=16,
+                          policy=policy, return_stats=True, eos_token_id=-1, decode_quantum=quantum)
+    assert got == want
+    if policy == "optimistic":
+        assert stats.preemptions > 0
+    eng.cache.check_invariants()
+    assert eng.cache.free_pages()[0] == pages
+
+
+@pytest.mark.parametrize("which", ["A", "B", "C"])
+def test_greedy_bf16_stays_within_rounding(folders, which):
+    from leone_b200 import generate
+    plain = PlainModel(folders[which], matrices_as_bf16=True)
+    vocab = plain.cfg["vocab_size"]
+    prompts = [replay.random_tokens(vocab, n, 70 + n) for n in (3, 11, 24)]
+    got = generate(folders[which], prompts, 8, dtype="bfloat16", page_tokens=PAGE_TOKENS[which],
+                   eos_token_id=-1)
+    for p, toks in zip(prompts, got):
+        assert len(toks) == 8
+        seq = list(p)
+        for t in toks:
+            logits = plain.logits(seq)[-1]
+            assert float(logits.max() - logits[t]) <= 0.05 * float(logits.abs().max())
+            seq.append(t)
+
+
+def test_graph_decode_equals_eager_decode(folders):
+    from leone_b200 import generate
+    prompts = [replay.random_tokens(331, n, 80 + n) for n in (4, 19, 33, 8)]
+    for dtype in ("float32", "bfloat16"):
+        outs = []
+        for kw in (dict(use_graphs=False), dict(use_graphs=True, decode_quantum=1),
+                   dict(use_graphs=True, decode_quantum=5)):
+            eng = _engine(folders["C"], "C", dtype, 40)
+            outs.append(generate(eng, prompts, 12, temperature=0.7, seed=3, eos_token_id=-1, **kw))
+        assert outs[0] == outs[1] == outs[2], dtype
+
+
+def test_eos_stops_a_request(folders):
+    from leone_b200 import generate
+    plain = PlainModel(folders["A"])
+    prompt = replay.random_tokens(256, 6, 5)
+    free_run = plain_generate(plain, prompt, 8)
+    eos = free_run[3]
+    got = generate(folders["A"], [prompt], 8, dtype="float32", page_tokens=4, eos_token_id=eos)
+    assert got[0] == free_run[:free_run.index(eos) + 1]

@@ -356,3 +356,63 @@ def test_sample_temperature_matches_host(ops32, vocab):
         lo = cdf[got - 1] if got > 0 else 0.0
         # the drawn value lies in the chosen token's interval, up to summation rounding
         assert lo - 1e-9 <= u < cdf[got] + 1e-9 and probs[got] > 0
+
+
+# -- tiled bf16 attention: prompt portions / mixed batches, and split-KV decode ------------------
+def _tiled_case(ops16, n_q, n_kv, d, pt, window, seq_lens, starts, seed):
+    positions, seqs, q_start = [], [], [0]
+    for s, (l, st) in enumerate(zip(seq_lens, starts)):
+        positions += list(range(st, l))
+        seqs += [s] * (l - st)
+        q_start.append(len(positions))
+    n = len(positions)
+    dtype = torch.bfloat16
+    table, k_pool, v_pool = _paged_setup(seq_lens, pt, n_kv, d, dtype, seed)
+    keys = [_randn((l, n_kv, d), seed * 100 + s, dtype) for s, l in enumerate(seq_lens)]
+    vals = [_randn((l, n_kv, d), seed * 100 + 50 + s, dtype) for s, l in enumerate(seq_lens)]
+    for s, l in enumerate(seq_lens):
+        pos = torch.arange(l)
+        pages = table[s, (pos // pt).to(DEV)].long()
+        k_pool[pages, :, (pos % pt).to(DEV)] = keys[s]
+        v_pool[pages, :, (pos % pt).to(DEV)] = vals[s]
+    qkv = _randn((n, (n_q + 2 * n_kv) * d), seed + 7, dtype)
+    # one far key dominates for the first row of every sequence: a wrong page or a lost
+    # tile changes the output by far more than the tolerance
+    for s in range(len(seq_lens)):
+        row = q_start[s]
+        far = min(3, positions[row])
+        qkv.view(n, -1, d)[row, 0] = (keys[s][far, 0].float() * 3).to(dtype)
+    out = torch.full((n, n_q * d), 7.0, device=DEV, dtype=dtype)
+    cache = types.SimpleNamespace(k_pool=k_pool, v_pool=v_pool, block_table=table, page_tokens=pt)
+    ctx = _ctx(positions, seqs)
+    ctx.q_start = torch.tensor(q_start, device=DEV, dtype=torch.int32)
+    ctx.ctx_len = torch.tensor(seq_lens, device=DEV, dtype=torch.int32)
+    ctx.n_seqs = len(seq_lens)
+    ctx.max_q_len = max(l - st for l, st in zip(seq_lens, starts))
+    ctx.max_ctx_len = max(seq_lens)
+    ctx.decode_only = ctx.max_q_len == 1
+    scale = 1 / math.sqrt(d)
+    assert ops16.fast.attention(ctx, qkv, out, n_q, n_kv, d, scale, window, cache)
+    assert ctx.status[0].item() == 0
+    for i, (p, s) in enumerate(zip(positions, seqs)):
+        lo = 0 if not window else max(0, p - window + 1)
+        want = _ref_attention(qkv[i].double().view(-1, d)[:n_q], keys[s][:p + 1].double(),
+                              vals[s][:p + 1].double(), n_q, n_kv, scale, lo)
+        _close(out[i].view(n_q, d), want, 2 ** -6, 4e-3, f"tiled attention row {i} (seq {s}, pos {p})")
+
+
+@pytest.mark.parametrize("n_q,n_kv,d,pt,window", [(5, 1, 48, 16, None), (6, 3, 32, 8, None),
+                                                  (8, 2, 128, 16, None), (4, 4, 80, 4, 37),
+                                                  (32, 8, 128, 16, None), (16, 1, 64, 64, 100), (40, 2, 16, 16, None)])
+def test_attention_prefill_tiled(ops16, n_q, n_kv, d, pt, window):
+    # whole prompts, a continued portion, a 1-token row and a 2-token portion in one batch
+    _tiled_case(ops16, n_q, n_kv, d, pt, window, seq_lens=[150, 3, 131, 70, 64], starts=[0, 0, 100, 69, 62],
+                seed=3)
+
+
+@pytest.mark.parametrize("n_q,n_kv,d,pt,window", [(5, 1, 48, 16, None), (6, 3, 32, 8, None),
+                                                  (8, 2, 128, 16, None), (4, 4, 80, 4, 37),
+                                                  (32, 8, 128, 16, None), (40, 2, 16, 16, None)])
+@pytest.mark.parametrize("seq_lens", [[1], [300, 2, 64, 65, 1000], [2100]])
+def test_attention_decode_tiled(ops16, n_q, n_kv, d, pt, window, seq_lens):
+    _tiled_case(ops16, n_q, n_kv, d, pt, window, seq_lens=seq_lens, starts=[l - 1 for l in seq_lens], seed=4)

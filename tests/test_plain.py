@@ -1,0 +1,76 @@
+"""The plain implementation itself: each part against hand-checked values or identities."""
+import math
+
+import numpy as np
+import torch
+
+from tests.plain import model as pm
+
+
+def test_rms_norm_weight_multiplies_directly():
+    x = torch.tensor([[3.0, 4.0]], dtype=torch.float64)
+    y = pm.rms_norm(x, torch.tensor([2.0, 0.5], dtype=torch.float64), 0.0)
+    assert torch.allclose(y, torch.tensor([[6.0, 2.0]], dtype=torch.float64) / math.sqrt(12.5))
+
+
+def test_rope_is_a_rotation_and_identity_at_position_zero():
+    x = torch.randn(3, 2, 8, dtype=torch.float64)
+    y = pm.rope_half_split(x, [0, 5, 9], 10000.0)
+    assert torch.allclose(y[0], x[0])
+    assert torch.allclose(y.norm(dim=-1), x.norm(dim=-1))
+    # pair (i, i+half): element 0 pairs with element 4 at frequency 1
+    one = torch.zeros(1, 1, 8, dtype=torch.float64)
+    one[0, 0, 0] = 1.0
+    r = pm.rope_half_split(one, [1], 10000.0)[0, 0]
+    assert abs(r[0] - math.cos(1.0)) < 1e-12 and abs(r[4] - math.sin(1.0)) < 1e-12
+
+
+def test_rope_scores_depend_on_distance_only():
+    q, k = torch.randn(1, 1, 16, dtype=torch.float64), torch.randn(1, 1, 16, dtype=torch.float64)
+    a = (pm.rope_half_split(q, [7], 1e6) * pm.rope_half_split(k, [3], 1e6)).sum()
+    b = (pm.rope_half_split(q, [104], 1e6) * pm.rope_half_split(k, [100], 1e6)).sum()
+    assert abs(a - b) < 1e-9
+
+
+def test_attention_is_causal_grouped_and_windowed():
+    t, n_q, n_kv, d = 6, 4, 2, 8
+    q, k, v = (torch.randn(t, h, d, dtype=torch.float64) for h in (n_q, n_kv, n_kv))
+    out = pm.attention(q, k, v, list(range(t)))
+    assert torch.allclose(out[0, 1], v[0, 0])                 # first token sees only itself; head 1 -> kv 0
+    assert torch.allclose(out[0, 2], v[0, 1])                 # head 2 -> kv head 1
+    k2, v2 = k.clone(), v.clone()
+    k2[4:], v2[4:] = 0, 0
+    assert torch.allclose(pm.attention(q, k2, v2, list(range(t)))[:4], out[:4])   # the future does not matter
+    w1 = pm.attention(q, k, v, list(range(t)), window=1)
+    assert torch.allclose(w1, v[:, [0, 0, 1, 1]])             # a window of one key is that key's value
+    s = (k[:3, 0] @ q[2, 0]) / math.sqrt(d)
+    want = (torch.softmax(s, 0)[:, None] * v[:3, 0]).sum(0)
+    assert torch.allclose(out[2, 0], want)
+
+
+def test_swiglu():
+    g, u = torch.tensor([0.0, 2.0]).double(), torch.tensor([3.0, 5.0]).double()
+    assert torch.allclose(pm.swiglu(g, u), torch.tensor([0.0, 2.0 / (1 + math.exp(-2.0)) * 5.0]).double())
+
+
+def test_sampling_rules():
+    assert pm.argmax([1.0, 3.0, 3.0, float("nan"), float("inf")]) == 1       # lowest id on a tie; non-finite skipped
+    assert pm.argmax([float("nan")]) is None
+    p = pm.temperature_probs([0.0, math.log(3.0), float("-inf")], 1.0)
+    assert np.allclose(p, [0.25, 0.75, 0.0])
+    assert pm.select(p, 0.2499) == 0 and pm.select(p, 0.25) == 1 and pm.select(p, 0.9999999) == 1
+    assert pm.select([0.5, 0.5 - 1e-17, 0.0], 1.0 - 1e-18) == 1             # falls back to the last eligible
+    u = [pm.uniform(0, i) for i in range(2000)]
+    assert 0.0 <= min(u) and max(u) < 1.0 and abs(np.mean(u) - 0.5) < 0.03
+    assert pm.uniform(1, 5) != pm.uniform(2, 5) and pm.uniform(1, 5) == pm.uniform(1, 5)
+    assert pm.splitmix64(0) == 0xE220A8397B1DCDAF                           # the published first output of splitmix64
+
+
+def test_whole_model_prefix_property(tmp_path):
+    """Logits at a position do not depend on later tokens."""
+    from tests.tiny import make_folder
+    m = pm.PlainModel(make_folder(tmp_path, "B"))
+    a = m.logits([5, 9, 200, 31, 7])
+    b = m.logits([5, 9, 200, 1, 1])
+    assert torch.allclose(a[:3], b[:3]) and not torch.allclose(a[3], b[3])
+    assert a.shape == (5, 384)

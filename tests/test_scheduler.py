@@ -1,0 +1,209 @@
+"""The scheduler's decisions, with a fake step function (no model) and with the tiny model on
+emulated kernels."""
+import random
+
+import pytest
+import torch
+
+from leone_b200.cache.pages import CacheManager, GroupSpec, OutOfPages
+from leone_b200.engine.scheduler import AdmissionError, Scheduler, SchedulerConfig
+from leone_b200.sampling.sampler import SamplingParams
+
+
+class FakeSpec:
+    vocab_size = 100
+    max_positions = 64
+
+
+class FakeEngine:
+    """The engine's interface without a model: the 'next token' is a function of the request's
+    tokens so far, so any scheduling must produce the same stream as running alone."""
+
+    def __init__(self, pages=8, page_tokens=4, slots=4):
+        self.spec = FakeSpec()
+        self.cache = CacheManager([GroupSpec("full", 1, 8)], page_tokens, pages, slots)
+        self.seen = {}
+        self.batches = []
+
+    def open(self, rid):
+        self.cache.open(rid)
+        self.seen[rid] = []
+
+    def close(self, rid):
+        self.cache.close(rid)
+
+    def step(self, entries):
+        wants = {rid: self.cache.length(rid) + len(toks) for rid, toks, _ in entries}
+        self.cache.reserve(wants)
+        rows = []
+        for rid, toks, want in entries:
+            assert len(self.seen[rid]) == self.cache.length(rid)
+            self.seen[rid] = self.seen[rid] + list(toks)
+            for w in want:
+                prefix = self.seen[rid][:len(self.seen[rid]) - len(toks) + w + 1]
+                rows.append(prefix)
+            self.cache.commit(rid, wants[rid])
+        self.batches.append([(rid, len(toks)) for rid, toks, _ in entries])
+        self.cache.check_invariants()
+        return rows
+
+    def sample(self, rows, params, positions):
+        assert [len(r) - 1 for r in rows] == list(positions)
+        return [next_token(r) for r in rows]
+
+
+def next_token(prefix):
+    return (sum(prefix) * 31 + len(prefix) * 7) % 100
+
+
+def alone(prompt, n):
+    toks, out = list(prompt), []
+    for _ in range(n):
+        out.append(next_token(toks))
+        toks.append(out[-1])
+    return out
+
+
+def _run(sched):
+    guard = 0
+    while sched.has_work():
+        sched.step()
+        guard += 1
+        assert guard < 10000
+    return {rid: r.generated for rid, r in sched.requests.items()}
+
+
+def test_typed_rejections():
+    s = Scheduler(FakeEngine(), SchedulerConfig(max_waiting=1))
+    for reason, args in [("empty_prompt", ([], 3)), ("output_limit", ([1], 0)), ("token_id", ([100], 2)),
+                         ("prompt_limit", ([1] * 60, 10)), ("kv_capacity", ([1] * 30, 10))]:
+        with pytest.raises(AdmissionError) as err:
+            s.add_request("x", *args)
+        assert err.value.reason == reason
+    s.add_request("a", [1, 2], 2)
+    with pytest.raises(AdmissionError) as err:
+        s.add_request("a", [1], 1)
+    assert err.value.reason == "duplicate"
+    with pytest.raises(AdmissionError) as err:
+        s.add_request("b", [1], 1)
+    assert err.value.reason == "queue_limit"
+
+
+def test_token_budget_and_portions():
+    eng = FakeEngine(pages=16)
+    s = Scheduler(eng, SchedulerConfig(max_batch_tokens=8, prefill_chunk_tokens=5))
+    s.add_request("a", list(range(1, 14)), 3)       # 13 prompt tokens
+    s.add_request("b", [5, 6, 7], 3)
+    got = _run(s)
+    assert got == {"a": alone(list(range(1, 14)), 3), "b": alone([5, 6, 7], 3)}
+    assert all(sum(n for _, n in batch) <= 8 for batch in eng.batches)
+    assert all(n <= 5 for batch in eng.batches for _, n in batch)
+    # the first batch: a's first portion of 5 and b's whole prompt of 3
+    assert eng.batches[0] == [("a", 5), ("b", 3)]
+    # later, a decodes beside nothing or beside b: decode rows come first in a batch
+    mixed = [b for b in eng.batches if len(b) == 2 and b[0][1] == 1 and b[1][1] > 1]
+    assert mixed, "a decode row and a prompt portion never shared a batch"
+
+
+def test_reserve_policy_never_runs_out_and_queues_in_order():
+    eng = FakeEngine(pages=6, page_tokens=4)
+    s = Scheduler(eng, SchedulerConfig(policy="reserve"))
+    prompts = {i: [i + 1] * 7 for i in range(4)}     # 7 + 6 - 1 = 12 tokens = 3 pages each
+    for i, p in prompts.items():
+        s.add_request(i, p, 6)
+    s.step()
+    assert [r.rid for r in s.running] == [0, 1] and [r.rid for r in s.waiting] == [2, 3]
+    got = _run(s)
+    assert got == {i: alone(p, 6) for i, p in prompts.items()}
+    assert s.stats["preemptions"] == 0
+    assert eng.cache.free_pages() == [6]
+
+
+def test_optimistic_policy_preempts_the_youngest_and_recomputes():
+    eng = FakeEngine(pages=5, page_tokens=4)
+    s = Scheduler(eng, SchedulerConfig(policy="optimistic"))
+    prompts = {i: [i + 3] * 6 for i in range(3)}     # each grows to 6 + 8 - 1 = 13 tokens = 4 pages
+    for i, p in prompts.items():
+        s.add_request(i, p, 8)
+    got = _run(s)
+    assert got == {i: alone(p, 8) for i, p in prompts.items()}
+    assert s.stats["preemptions"] > 0
+    assert s.requests[0].preemptions == 0            # the oldest is never the victim
+    assert eng.cache.free_pages() == [5]
+
+
+def test_cancel_waiting_and_running():
+    eng = FakeEngine(pages=16)
+    s = Scheduler(eng, SchedulerConfig(max_running=1))
+    s.add_request("a", [1, 2, 3], 20)
+    s.add_request("b", [4, 5], 5)
+    s.step()
+    s.cancel("b")                                    # still queued: gone at once
+    assert s.requests["b"].state == "cancelled" and not s.waiting
+    s.step()
+    s.cancel("a")                                    # running: stops at the next step boundary
+    before = len(s.requests["a"].generated)
+    s.step()
+    assert s.requests["a"].state == "cancelled" and len(s.requests["a"].generated) == before
+    assert not s.has_work() and eng.cache.free_pages() == [16]
+
+
+def test_eos_and_length():
+    eng = FakeEngine(pages=16)
+    s = Scheduler(eng)
+    free = alone([9, 9], 6)
+    s.add_request("a", [9, 9], 6, eos_token_id=free[2])
+    s.add_request("b", [9, 9], 4)
+    got = _run(s)
+    assert got["a"] == free[:free.index(free[2]) + 1] and s.requests["a"].finish_reason == "eos"
+    assert got["b"] == free[:4] and s.requests["b"].finish_reason == "length"
+
+
+@pytest.mark.parametrize("seed", range(5))
+def test_interleaved_transcripts_equal_isolated_ones(seed):
+    """A scripted arrival trace: whatever the interleaving, each request's tokens are the ones
+    it produces alone (the reference checks the same, crates/leone/src/scheduler.rs:1227-1252)."""
+    rng = random.Random(seed)
+    eng = FakeEngine(pages=12, page_tokens=4, slots=3)
+    s = Scheduler(eng, SchedulerConfig(max_running=3, max_batch_tokens=rng.choice([4, 6, 16]),
+                                       prefill_chunk_tokens=rng.choice([2, 3, 7]),
+                                       policy=rng.choice(["reserve", "optimistic"])))
+    arrivals = sorted((rng.randint(0, 25), i) for i in range(7))
+    specs = {i: ([rng.randrange(100) for _ in range(rng.randint(1, 12))], rng.randint(1, 9)) for _, i in arrivals}
+    tick = 0
+    while arrivals or s.has_work():
+        while arrivals and arrivals[0][0] <= tick:
+            _, i = arrivals.pop(0)
+            s.add_request(i, *specs[i])
+        if s.has_work():
+            s.step()
+        tick += 1
+        assert tick < 5000
+    for i, (prompt, n) in specs.items():
+        assert s.requests[i].generated == alone(prompt, n), i
+    assert eng.cache.free_pages() == [12]
+
+
+def test_generation_with_the_tiny_model_on_emulated_kernels(tmp_path):
+    """The scheduler over the real step function (CPU stand-in kernels): tiny A greedy and
+    tiny B with temperature, both page policies, against the plain implementation."""
+    from leone_b200.engine.engine import Engine
+    from leone_b200.engine.generate import generate
+    from tests import replay
+    from tests.emulated_ops import EmulatedOps
+    from tests.plain.model import PlainModel, generate as plain_generate
+    from tests.tiny import PAGE_TOKENS, make_folder
+    for which, temp, lens, n_new in (("A", 0.0, (5, 9, 13), 8), ("B", 0.8, (1, 7, 17, 30), 6)):
+        folder = make_folder(tmp_path, which)
+        plain = PlainModel(folder)
+        prompts = [replay.random_tokens(plain.cfg["vocab_size"], n, 50 + n) for n in lens]
+        want = [plain_generate(plain, p, n_new, temp, 7 + i) for i, p in enumerate(prompts)]
+        for policy, pages in (("reserve", 14), ("optimistic", 9)):
+            eng = Engine.from_folder(folder, dtype="float32", device="cpu", ops=EmulatedOps(),
+                                     page_tokens=PAGE_TOKENS[which], num_pages=pages, max_requests=4,
+                                     max_batch_tokens=16)
+            got = generate(eng, prompts, n_new, temperature=temp, seed=7, prefill_chunk=6,
+                           max_batch_tokens=16, policy=policy, eos_token_id=-1)
+            assert got == want, (which, policy)
+            eng.cache.check_invariants()
+            assert eng.cache.free_pages()[0] == pages
