@@ -71,19 +71,20 @@ struct PagedArgs {
 };
 
 // Copies keys/values [tile_start, tile_start+64) of one sequence and KV head into shared
-// memory rows of D+8 elements; rows at or past `k_end` are zero-filled.
+// memory rows of D+8 elements; rows before `k_first` (keys a window has passed, whose pages
+// may already be given back) and rows at or past `k_end` are zero-filled.
 template <int D>
 __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* k_s, __nv_bfloat16* v_s,
                                              long long* row_src, const PagedArgs& pa, int seq,
-                                             int kvh, int tile_start, int k_end, int* status,
-                                             int token_row) {
+                                             int kvh, int tile_start, int k_first, int k_end,
+                                             int* status, int token_row) {
   constexpr int kRow = D + 8;
   constexpr int kChunks = D / 8;
   const int tid = threadIdx.x;
   if (tid < kKeyTile) {
     const int kj = tile_start + tid;
     long long src = -1;
-    if (kj < k_end && kj >= 0) {
+    if (kj < k_end && kj >= k_first) {
       const int blk = kj / pa.page_tokens;
       const int page = blk < pa.table_width ? pa.block_table[(size_t)seq * pa.table_width + blk] : -1;
       if (page < 0 || page >= pa.num_pages) {
@@ -150,7 +151,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
   const int tile0 = (k_lo / kKeyTile) * kKeyTile;
   const int n_tiles = (k_hi - tile0 + kKeyTile - 1) / kKeyTile;
 
-  load_kv_tile<D>(kv_s, kv_s + kKeyTile * kRow, row_src, pa, seq, kvh, tile0, k_hi, status, q0 + tok0);
+  load_kv_tile<D>(kv_s, kv_s + kKeyTile * kRow, row_src, pa, seq, kvh, tile0, k_lo, k_hi, status,
+                  q0 + tok0);
   cp_async_commit();
 
   // this thread's two rows
@@ -177,7 +179,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
     if (t + 1 < n_tiles) {
       __nv_bfloat16* k_n = kv_s + (stage ^ 1) * 2 * kKeyTile * kRow;
       load_kv_tile<D>(k_n, k_n + kKeyTile * kRow, row_src + (stage ^ 1) * kKeyTile, pa, seq, kvh,
-                      tile0 + (t + 1) * kKeyTile, k_hi, status, q0 + tok0);
+                      tile0 + (t + 1) * kKeyTile, k_lo, k_hi, status, q0 + tok0);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -346,7 +348,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
     cp_async16(smem_u32(q_s + r * kRow + ch * 8), src, ok);
   }
   cp_async_commit();
-  load_kv_tile<D>(kv_s, kv_s + kKeyTile * kRow, row_src, pa, seq, kvh, k_begin, k_end, status, row_token);
+  load_kv_tile<D>(kv_s, kv_s + kKeyTile * kRow, row_src, pa, seq, kvh, k_begin, k_lo, k_end, status,
+                  row_token);
   cp_async_commit();
 
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
@@ -365,7 +368,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
     if (t + 1 < n_tiles) {
       __nv_bfloat16* k_n = kv_s + (stage ^ 1) * 2 * kKeyTile * kRow;
       load_kv_tile<D>(k_n, k_n + kKeyTile * kRow, row_src + (stage ^ 1) * kKeyTile, pa, seq, kvh,
-                      k_begin + (t + 1) * kKeyTile, k_end, status, row_token);
+                      k_begin + (t + 1) * kKeyTile, k_lo, k_end, status, row_token);
       cp_async_commit();
       cp_async_wait<1>();
     } else {

@@ -9,7 +9,7 @@ The reference's ``--profile-decode`` prints per-operation microseconds and GEMV 
 (crates/leone-cli/src/main.rs:2918-2995); this is the same kind of table for this engine's
 kernels.  Inputs are larger than the 126 MB L2, or a buffer larger than L2 is written between
 timed launches (``--flush``), so DRAM figures mean something.  Timing is by CUDA events on the
-launching stream after warm-up launches.
+launching stream around a CUDA graph of the launches, after warm-up launches.
 """
 from __future__ import annotations
 
@@ -26,20 +26,31 @@ from .benchmark import measured_peaks
 DEV = "cuda:0"
 
 
-def _time(fn, reps: int, warmup: int, flush=None) -> float:
-    for _ in range(warmup):
+def _time(fn, reps: int, warmup: int, flush=None, per_graph: int = 1) -> float:
+    """Median device time of one launch, in ms.  ``per_graph`` launches (each on its own copy
+    of the operands, together larger than L2) are captured into a CUDA graph and the graph's
+    time is divided by their number, so the time is the kernels', not the Python calls'."""
+    for _ in range(max(warmup, 1) * per_graph):
         fn()
     torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(per_graph):
+                fn()
+    torch.cuda.current_stream().wait_stream(side)
     times = []
     for _ in range(reps):
         if flush is not None:
             flush.add_(1.0)
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
-        fn()
+        graph.replay()
         stop.record()
         torch.cuda.synchronize()
-        times.append(start.elapsed_time(stop))
+        times.append(start.elapsed_time(stop) / per_graph)
     times.sort()
     return times[len(times) // 2]
 
@@ -48,7 +59,7 @@ def bench_gemm(ops, m, n, k, splits, epilogue, reps, warmup, flush):
     fast = ops.fast
     x = torch.randn((m, k), device=DEV).to(torch.bfloat16)
     # several copies of the weight so successive launches do not hit L2
-    copies = max(1, min(8, int(300e6 // (n * k * 2)) + 1))
+    copies = max(1, min(16, int(400e6 // (n * k * 2)) + 1))
     ws = [(torch.randn((n, k), device=DEV) * 0.02).to(torch.bfloat16) for _ in range(copies)]
     out_cols = n // 2 if epilogue == 3 else n
     out = torch.empty((m, out_cols), device=DEV, dtype=torch.bfloat16 if epilogue in (0, 3) else torch.float32)
@@ -64,7 +75,7 @@ def bench_gemm(ops, m, n, k, splits, epilogue, reps, warmup, flush):
         state["i"] += 1
         fast._gemm(x, w, out, epilogue, res, n, splits=splits)
 
-    ms = _time(run, reps, warmup, flush)
+    ms = _time(run, reps, warmup, flush, per_graph=copies)
     bytes_ = n * k * 2 + m * k * 2 + out.numel() * out.element_size()
     flops = 2.0 * m * n * k
     return dict(kernel="gemm_tc", m=m, n=n, k=k, splits=splits, epilogue=epilogue, us=ms * 1e3,
@@ -73,10 +84,13 @@ def bench_gemm(ops, m, n, k, splits, epilogue, reps, warmup, flush):
 
 def bench_decode_attention(ops, batch, context, n_q, n_kv, d, page_tokens, reps, warmup, flush):
     blocks = -(-context // page_tokens)
-    pages = batch * blocks
+    per_copy = batch * blocks
+    bytes_ = 2.0 * batch * context * n_kv * d * 2
+    copies = max(1, min(64, int(400e6 // bytes_) + 1))       # successive launches read different pages
+    pages = per_copy * copies
     k_pool = torch.randn((pages, n_kv, page_tokens, d), device=DEV).to(torch.bfloat16)
     v_pool = torch.randn((pages, n_kv, page_tokens, d), device=DEV).to(torch.bfloat16)
-    table = torch.randperm(pages, device=DEV).to(torch.int32).view(batch, blocks)
+    tables = torch.randperm(pages, device=DEV).to(torch.int32).view(copies, batch, blocks)
     qkv = torch.randn((batch, (n_q + 2 * n_kv) * d), device=DEV).to(torch.bfloat16)
     out = torch.empty((batch, n_q * d), device=DEV, dtype=torch.bfloat16)
     ctx = types.SimpleNamespace(
@@ -84,10 +98,15 @@ def bench_decode_attention(ops, batch, context, n_q, n_kv, d, page_tokens, reps,
         ctx_len=torch.full((batch,), context, device=DEV, dtype=torch.int32),
         status=torch.zeros(4, device=DEV, dtype=torch.int32), n_seqs=batch, max_q_len=1,
         max_ctx_len=context, decode_only=True)
-    cache = types.SimpleNamespace(k_pool=k_pool, v_pool=v_pool, block_table=table, page_tokens=page_tokens)
-    ms = _time(lambda: ops.fast.attention(ctx, qkv, out, n_q, n_kv, d, 1 / math.sqrt(d), None, cache),
-               reps, warmup, flush)
-    bytes_ = 2.0 * batch * context * n_kv * d * 2
+    state = {"i": 0}
+
+    def run():
+        cache = types.SimpleNamespace(k_pool=k_pool, v_pool=v_pool,
+                                      block_table=tables[state["i"] % copies], page_tokens=page_tokens)
+        state["i"] += 1
+        ops.fast.attention(ctx, qkv, out, n_q, n_kv, d, 1 / math.sqrt(d), None, cache)
+
+    ms = _time(run, reps, warmup, flush, per_graph=copies)
     return dict(kernel="attention_decode", batch=batch, context=context, us=ms * 1e3,
                 splits=ops.fast.decode_splits(batch, n_kv, n_q // n_kv, context), gbs=bytes_ / ms / 1e6)
 

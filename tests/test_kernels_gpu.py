@@ -298,6 +298,9 @@ def test_attention_generic(ops32, dtype, n_q, n_kv, d, pt, window):
             page = int(table[s, p // pt])
             k_pool[page, :, p % pt] = keys[s][p]
             v_pool[page, :, p % pt] = vals[s][p]
+    if window:
+        for s, st in enumerate(starts):
+            table[s, :max(0, st - window + 1) // pt] = -1      # pages the window has passed are gone
     qkv = _randn((n, (n_q + 2 * n_kv) * d), 50, dtype)
     # make one far key dominate for one row: a single wrong page would show
     qkv.view(n, -1, d)[0, 0] = (keys[0][5, 0].float() * 4).to(dtype)
@@ -375,6 +378,11 @@ def _tiled_case(ops16, n_q, n_kv, d, pt, window, seq_lens, starts, seed):
         pages = table[s, (pos // pt).to(DEV)].long()
         k_pool[pages, :, (pos % pt).to(DEV)] = keys[s]
         v_pool[pages, :, (pos % pt).to(DEV)] = vals[s]
+    if window:
+        # pages that the window has passed are given back before the step: the kernel must not read them
+        for s, st in enumerate(starts):
+            passed = max(0, st - window + 1) // pt
+            table[s, :passed] = -1
     qkv = _randn((n, (n_q + 2 * n_kv) * d), seed + 7, dtype)
     # one far key dominates for the first row of every sequence: a wrong page or a lost
     # tile changes the output by far more than the tolerance
