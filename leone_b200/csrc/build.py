@@ -31,8 +31,10 @@ MODULES: Dict[str, List[str]] = {
     "core": ["elementwise.cu", "gemm_simt.cu", "attention_generic.cu"],
     # the bfloat16 serving path: tensor-core products and tiled attention
     "bf16": ["gemm_tc.cu", "attention_tiled.cu"],
+    # the entry point that allocates nothing (leone_static.h); it compiles attention_tiled.cu in
+    "static": ["attention_decode_static.cu"],
 }
-HEADERS = ["common.cuh", "tc_common.cuh"]
+HEADERS = ["common.cuh", "tc_common.cuh", "leone_static.h", "attention_tiled.cu"]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
