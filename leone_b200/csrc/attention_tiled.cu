@@ -123,6 +123,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
   __nv_bfloat16* kv_s = q_s + kRowsPerBlock * kRow;                           // [2 stages][K,V][64][kRow]
   long long* row_src = reinterpret_cast<long long*>(kv_s + 4 * kKeyTile * kRow);   // [2][64]
 
+  pdl_trigger();
+  pdl_wait();
   const int seq = blockIdx.z, kvh = blockIdx.y, qt = blockIdx.x;
   const int g = n_q / pa.n_kv;
   const int tq = kRowsPerBlock / g;                 // tokens per tile
@@ -311,6 +313,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
   __nv_bfloat16* kv_s = q_s + 16 * kRow;                                      // [2][K,V][64][kRow]
   long long* row_src = reinterpret_cast<long long*>(kv_s + 4 * kKeyTile * kRow);   // [2][64]
 
+  pdl_trigger();
+  pdl_wait();
   const int g = n_q / pa.n_kv;
   const int groups = (g + 15) / 16;
   const int kvh = blockIdx.x / groups, hg = blockIdx.x - kvh * groups;
@@ -500,6 +504,8 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o,
                                        const float* __restrict__ part_ml,
                                        __nv_bfloat16* __restrict__ out, int out_stride,
                                        const int* __restrict__ q_start, int n_q, int d, int splits) {
+  pdl_trigger();
+  pdl_wait();
   const int head = blockIdx.x, seq = blockIdx.y;
   const size_t base = ((size_t)seq * n_q + head) * splits;
   float m = -INFINITY;
@@ -544,9 +550,8 @@ int launch_prefill(const __nv_bfloat16* qkv, int row_stride, __nv_bfloat16* out,
   const int g = n_q / pa.n_kv;
   const int tq = kRowsPerBlock / g;
   dim3 grid((max_q_len + tq - 1) / tq, pa.n_kv, n_seqs);
-  attention_prefill_kernel<D><<<grid, kThreads, prefill_smem<D>(), stream>>>(
-      qkv, row_stride, out, out_stride, pa, q_start, ctx_len, n_q, scale, window, status);
-  return launch_result();
+  return launch_kernel(attention_prefill_kernel<D>, grid, dim3(kThreads), prefill_smem<D>(), stream, qkv,
+                       row_stride, out, out_stride, pa, q_start, ctx_len, n_q, scale, window, status);
 }
 
 template <int D>
@@ -563,15 +568,14 @@ int launch_decode(const __nv_bfloat16* qkv, int row_stride, __nv_bfloat16* out, 
   }
   const int g = n_q / pa.n_kv;
   dim3 grid(pa.n_kv * ((g + 15) / 16), splits, n_seqs);
-  attention_decode_kernel<D><<<grid, kThreads, decode_smem<D>(), stream>>>(
-      qkv, row_stride, out, out_stride, pa, q_start, ctx_len, n_q, scale, window, splits, part_o,
-      part_ml, status);
-  int r = launch_result();
+  int r = launch_kernel(attention_decode_kernel<D>, grid, dim3(kThreads), decode_smem<D>(), stream, qkv,
+                        row_stride, out, out_stride, pa, q_start, ctx_len, n_q, scale, window, splits,
+                        part_o, part_ml, status);
   if (r != 0 || splits == 1) return r;
   dim3 mgrid(n_q, n_seqs);
-  attention_merge_kernel<<<mgrid, D >= 64 ? 64 : 32, 0, stream>>>(part_o, part_ml, out, out_stride,
-                                                                q_start, n_q, D, splits);
-  return launch_result();
+  return launch_kernel(attention_merge_kernel, mgrid, dim3(D >= 64 ? 64 : 32), 0, stream,
+                       (const float*)part_o, (const float*)part_ml, out, out_stride, q_start, n_q, D,
+                       splits);
 }
 
 }  // namespace tiled

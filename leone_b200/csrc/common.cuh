@@ -104,4 +104,40 @@ inline int launch_result() {
   return (int)cudaGetLastError();
 }
 
+// ---- programmatic dependent launch -------------------------------------------------
+// Kernels of a step are launched so that a kernel may start while its predecessor in the
+// stream is still running.  A kernel calls pdl_trigger() early (its successor may then be
+// scheduled once every block of this kernel has started) and pdl_wait() before it reads or
+// writes anything a predecessor may still touch; pdl_wait() returns when the predecessor grid
+// has completed and its writes are visible.  Work that depends on nothing written during the
+// step (fetching weights) is done before pdl_wait().  Launched without the attribute, both
+// calls do nothing.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// One switch per library image; off until the host turns it on.
+inline int& pdl_flag() {
+  static int enabled = 0;
+  return enabled;
+}
+
+template <typename... KArgs, typename... Args>
+inline int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                         cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = pdl_flag() ? 1 : 0;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+  return e == cudaSuccess ? launch_result() : (int)e;
+}
+
 }  // namespace leone

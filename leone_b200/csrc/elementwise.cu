@@ -14,6 +14,8 @@ namespace leone {
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                  float* __restrict__ out, int hidden, int vocab, int* status) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   const int id = ids[row];
   float* dst = out + (size_t)row * hidden;
@@ -36,6 +38,8 @@ __global__ void rms_norm_kernel(const float* __restrict__ x, const int* __restri
                                 const TW* __restrict__ w, TO* __restrict__ out, int hidden,
                                 float eps) {
   __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   const float* src = x + (size_t)(rows ? rows[r] : r) * hidden;
   float ss = 0.f;
@@ -87,6 +91,8 @@ __global__ void qk_norm_rope_write_kernel(
     const int* __restrict__ block_table, int table_width, int n_seqs, T* __restrict__ k_pool,
     T* __restrict__ v_pool, int num_pages, int page_tokens, int* status) {
   extern __shared__ float smem[];
+  pdl_trigger();
+  pdl_wait();
   const int warps_per_block = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = n_q + 2 * n_kv;
@@ -157,7 +163,6 @@ __global__ void qk_norm_rope_write_kernel(
 //    u = uniform(seed, position) from the reference's counter-based generator
 //    (crates/leone/src/sampler.rs:84-94, 166-171); the token is the first in id order
 //    whose cumulative weight exceeds u * total, else the last eligible one (:839-858).
-//    Each thread owns a contiguous run of ids so the scan keeps id order.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ unsigned long long splitmix64(unsigned long long v) {
   unsigned long long z = v + 0x9e3779b97f4a7c15ull;
@@ -166,38 +171,57 @@ __device__ __forceinline__ unsigned long long splitmix64(unsigned long long v) {
   return z ^ (z >> 31);
 }
 
-__global__ void sample_kernel(const float* __restrict__ logits, int vocab,
+__device__ __forceinline__ double warp_sum_f64(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// One block of 1024 threads per row.  Pass 1 (coalesced): highest finite logit and its lowest
+// id.  Temperature rows: each of the 32 warps owns one contiguous run of ids and sums its
+// weights with coalesced loads; the run that holds u * total is found by a scan over the 32
+// warp sums in id order, and that warp walks its run 32 ids at a time with a warp prefix sum,
+// so the chosen token is the first in id order whose cumulative weight exceeds the target.
+__global__ void __launch_bounds__(1024)
+sample_kernel(const float* __restrict__ logits, int vocab,
                               const float* __restrict__ temperature,
                               const long long* __restrict__ seeds,
                               const long long* __restrict__ positions, int* __restrict__ out) {
-  __shared__ float s_val[1024];
-  __shared__ int s_idx[1024];
-  __shared__ double s_sum[1024];
-  const int row = blockIdx.x, tid = threadIdx.x, nthr = blockDim.x;
+  __shared__ float s_val[32];
+  __shared__ int s_idx[32];
+  __shared__ double s_sum[32];
+  __shared__ double s_before;
+  __shared__ int s_owner;
+  pdl_trigger();
+  pdl_wait();
+  const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const float* l = logits + (size_t)row * vocab;
-  const int per = (vocab + nthr - 1) / nthr;
-  const int lo = min(tid * per, vocab), hi = min(lo + per, vocab);
   float best = -INFINITY;
   int best_i = -1;
-  for (int i = lo; i < hi; ++i) {
+  for (int i = tid; i < vocab; i += 1024) {      // ids rise within a thread: '>' keeps the lowest
     const float v = l[i];
     if (isfinite(v) && (best_i < 0 || v > best)) { best = v; best_i = i; }
   }
-  s_val[tid] = best;
-  s_idx[tid] = best_i;
-  __syncthreads();
-  for (int o = 512; o > 0; o >>= 1) {
-    if (tid < o && tid + o < nthr) {
-      const int j = s_idx[tid + o];
-      // on equal values the lower id wins
-      if (j >= 0 && (s_idx[tid] < 0 || s_val[tid + o] > s_val[tid] ||
-                     (s_val[tid + o] == s_val[tid] && j < s_idx[tid]))) {
-        s_val[tid] = s_val[tid + o];
-        s_idx[tid] = j;
-      }
-    }
-    __syncthreads();
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+    if (oi >= 0 && (best_i < 0 || ov > best || (ov == best && oi < best_i))) { best = ov; best_i = oi; }
   }
+  if (lane == 0) { s_val[warp] = best; s_idx[warp] = best_i; }
+  __syncthreads();
+  if (warp == 0) {
+    best = s_val[lane];
+    best_i = s_idx[lane];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+      if (oi >= 0 && (best_i < 0 || ov > best || (ov == best && oi < best_i))) { best = ov; best_i = oi; }
+    }
+    if (lane == 0) { s_val[0] = best; s_idx[0] = best_i; }
+  }
+  __syncthreads();
   const float top = s_val[0];
   const int top_i = s_idx[0];
   const float temp = temperature ? temperature[row] : 0.f;
@@ -206,51 +230,66 @@ __global__ void sample_kernel(const float* __restrict__ logits, int vocab,
     return;
   }
   const double t = (double)temp, hi_scaled = (double)top / t;
+  const int run = ((vocab + 31) / 32 + 31) / 32 * 32;          // ids per warp, a multiple of 32
+  const int lo = min(warp * run, vocab), hi = min(lo + run, vocab);
   double sum = 0.0;
-  for (int i = lo; i < hi; ++i) {
+  for (int i = lo + lane; i < hi; i += 32) {
     const float v = l[i];
     if (isfinite(v)) sum += exp((double)v / t - hi_scaled);
   }
-  s_sum[tid] = sum;
+  sum = warp_sum_f64(sum);
+  if (lane == 0) s_sum[warp] = sum;
   __syncthreads();
   if (tid == 0) {
     double total = 0.0;
-    for (int i = 0; i < nthr; ++i) total += s_sum[i];
+    for (int i = 0; i < 32; ++i) total += s_sum[i];
     const unsigned long long purpose = 0xbf58476d1ce4e5b9ull;
     const unsigned long long mixed = splitmix64(
         (unsigned long long)seeds[row] ^ splitmix64((unsigned long long)positions[row] ^ purpose));
     const double u = (double)(mixed >> 11) * (1.0 / 9007199254740992.0);
     const double target = u * total;
     double c = 0.0;
-    int owner = nthr - 1;
-    for (int i = 0; i < nthr; ++i) {
+    int owner = -1;
+    for (int i = 0; i < 32; ++i) {
       if (target < c + s_sum[i]) { owner = i; break; }
       c += s_sum[i];
     }
-    // scan the owner's run; fall back to the last eligible id at or before its end
-    int chosen = -1, last = -1;
-    const int olo = min(owner * per, vocab), ohi = min(olo + per, vocab);
-    for (int i = olo; i < ohi && chosen < 0; ++i) {
-      const float v = l[i];
-      if (!isfinite(v)) continue;
-      const double wgt = exp((double)v / t - hi_scaled);
-      if (wgt <= 0.0) continue;
-      last = i;
-      c += wgt;
-      if (target < c) chosen = i;
+    if (owner < 0) {                     // rounding left the sum just below the target:
+      owner = 31;                        // the last run with any weight takes it
+      while (owner > 0 && !(s_sum[owner] > 0.0)) --owner;
+      c = total - s_sum[owner];
     }
-    if (chosen < 0) {
-      if (last >= 0) {
-        chosen = last;
-      } else {
-        for (int i = vocab - 1; i >= 0; --i) {
-          const float v = l[i];
-          if (isfinite(v) && exp((double)v / t - hi_scaled) > 0.0) { chosen = i; break; }
-        }
-      }
-    }
-    out[row] = chosen;
+    s_owner = owner;
+    s_before = c;
+    // the target is recomputed by the owner from the same values
+    s_sum[0] = target;
   }
+  __syncthreads();
+  if (warp != s_owner) return;
+  const double target = s_sum[0];
+  double c = s_before;
+  int chosen = -1, last = -1;
+  for (int base = lo; base < hi && chosen < 0; base += 32) {
+    const int i = base + lane;
+    double wgt = 0.0;
+    if (i < hi) {
+      const float v = l[i];
+      if (isfinite(v)) wgt = exp((double)v / t - hi_scaled);
+    }
+    double incl = wgt;                   // inclusive prefix over the 32 lanes, in id order
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const double up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    const bool hit = wgt > 0.0 && target < c + incl;
+    const unsigned hits = __ballot_sync(0xffffffffu, hit);
+    const unsigned live = __ballot_sync(0xffffffffu, wgt > 0.0);
+    if (live) last = base + 31 - __clz(live);
+    if (hits) chosen = base + __ffs(hits) - 1;
+    c += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  if (lane == 0) out[row] = chosen >= 0 ? chosen : (last >= 0 ? last : top_i);
 }
 
 // ---------------------------------------------------------------------------
@@ -263,6 +302,8 @@ __global__ void sample_kernel(const float* __restrict__ logits, int vocab,
 __global__ void decode_advance_kernel(int* token_ids, int* positions, int* ctx_len,
                                       long long* sample_pos, const int* sampled, int* history,
                                       int* step_counter, int n, int max_steps) {
+  pdl_trigger();
+  pdl_wait();
   const int step = *step_counter;
   __syncthreads();
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
@@ -284,10 +325,13 @@ extern "C" int leone_decode_advance(int* token_ids, int* positions, int* ctx_len
                                     long long* sample_pos, const int* sampled, int* history,
                                     int* step_counter, int n, int max_steps, cudaStream_t stream) {
   if (n <= 0) return 0;
-  decode_advance_kernel<<<1, n < 1024 ? ((n + 31) / 32) * 32 : 1024, 0, stream>>>(
-      token_ids, positions, ctx_len, sample_pos, sampled, history, step_counter, n, max_steps);
-  return launch_result();
+  return launch_kernel(decode_advance_kernel, dim3(1), dim3(n < 1024 ? ((n + 31) / 32) * 32 : 1024), 0,
+                       stream, token_ids, positions, ctx_len, sample_pos, sampled, history,
+                       step_counter, n, max_steps);
 }
+
+// Turns programmatic dependent launch on or off for the kernels of this library.
+extern "C" void leone_core_set_pdl(int enabled) { pdl_flag() = enabled ? 1 : 0; }
 
 extern "C" int leone_embedding(int dtype, const void* table, const int* ids, float* out, int n,
                                int hidden, int vocab, int* status, cudaStream_t stream) {
@@ -295,12 +339,12 @@ extern "C" int leone_embedding(int dtype, const void* table, const int* ids, flo
   if (hidden <= 0 || vocab <= 0) return kRefusedSize;
   const int threads = hidden >= 1024 ? 256 : 128;
   if (dtype == 0)
-    embedding_kernel<float><<<n, threads, 0, stream>>>((const float*)table, ids, out, hidden, vocab, status);
-  else if (dtype == 1)
-    embedding_kernel<__nv_bfloat16><<<n, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, hidden, vocab, status);
-  else
-    return kRefusedDtype;
-  return launch_result();
+    return launch_kernel(embedding_kernel<float>, dim3(n), dim3(threads), 0, stream, (const float*)table,
+                         ids, out, hidden, vocab, status);
+  if (dtype == 1)
+    return launch_kernel(embedding_kernel<__nv_bfloat16>, dim3(n), dim3(threads), 0, stream,
+                         (const __nv_bfloat16*)table, ids, out, hidden, vocab, status);
+  return kRefusedDtype;
 }
 
 extern "C" int leone_rms_norm(const float* x, const int* rows, const void* w, int w_dtype, void* out,
@@ -308,16 +352,15 @@ extern "C" int leone_rms_norm(const float* x, const int* rows, const void* w, in
   if (n_out <= 0) return 0;
   if (hidden <= 0) return kRefusedSize;
   const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
-#define LAUNCH(TW, TO)                                                                   \
-  rms_norm_kernel<TW, TO><<<n_out, threads, 0, stream>>>(x, rows, (const TW*)w, (TO*)out, \
-                                                        hidden, eps)
+#define LAUNCH(TW, TO)                                                                       \
+  return launch_kernel(rms_norm_kernel<TW, TO>, dim3(n_out), dim3(threads), 0, stream, x, rows, \
+                       (const TW*)w, (TO*)out, hidden, eps)
   if (w_dtype == 0 && out_dtype == 0) LAUNCH(float, float);
-  else if (w_dtype == 0 && out_dtype == 1) LAUNCH(float, __nv_bfloat16);
-  else if (w_dtype == 1 && out_dtype == 0) LAUNCH(__nv_bfloat16, float);
-  else if (w_dtype == 1 && out_dtype == 1) LAUNCH(__nv_bfloat16, __nv_bfloat16);
-  else return kRefusedDtype;
+  if (w_dtype == 0 && out_dtype == 1) LAUNCH(float, __nv_bfloat16);
+  if (w_dtype == 1 && out_dtype == 0) LAUNCH(__nv_bfloat16, float);
+  if (w_dtype == 1 && out_dtype == 1) LAUNCH(__nv_bfloat16, __nv_bfloat16);
 #undef LAUNCH
-  return launch_result();
+  return kRefusedDtype;
 }
 
 extern "C" int leone_swiglu(int dtype, const void* gate_up, void* out, int n, int inter,
@@ -349,18 +392,18 @@ extern "C" int leone_qk_norm_rope_write(
   const long long items = (long long)n_tokens * (n_q + 2 * n_kv);
   const int blocks = (int)((items + warps - 1) / warps);
   const size_t smem = (size_t)warps * d * sizeof(float);
-#define LAUNCH(T, TW)                                                                            \
-  qk_norm_rope_write_kernel<T, TW><<<blocks, warps * 32, smem, stream>>>(                         \
-      (T*)qkv, n_tokens, n_q, n_kv, d, (const TW*)q_w, (const TW*)k_w, eps, (const float2*)rope,  \
-      rotary_dim, max_positions, positions, seq_of_token, block_table, table_width, n_seqs,       \
-      (T*)k_pool, (T*)v_pool, num_pages, page_tokens, status)
+#define LAUNCH(T, TW)                                                                              \
+  return launch_kernel(qk_norm_rope_write_kernel<T, TW>, dim3(blocks), dim3(warps * 32), smem, stream, \
+                       (T*)qkv, n_tokens, n_q, n_kv, d, (const TW*)q_w, (const TW*)k_w, eps,          \
+                       (const float2*)rope, rotary_dim, max_positions, positions, seq_of_token,      \
+                       block_table, table_width, n_seqs, (T*)k_pool, (T*)v_pool, num_pages,          \
+                       page_tokens, status)
   if (dtype == 0 && w_dtype == 0) LAUNCH(float, float);
-  else if (dtype == 1 && w_dtype == 0) LAUNCH(__nv_bfloat16, float);
-  else if (dtype == 0 && w_dtype == 1) LAUNCH(float, __nv_bfloat16);
-  else if (dtype == 1 && w_dtype == 1) LAUNCH(__nv_bfloat16, __nv_bfloat16);
-  else return kRefusedDtype;
+  if (dtype == 1 && w_dtype == 0) LAUNCH(__nv_bfloat16, float);
+  if (dtype == 0 && w_dtype == 1) LAUNCH(float, __nv_bfloat16);
+  if (dtype == 1 && w_dtype == 1) LAUNCH(__nv_bfloat16, __nv_bfloat16);
 #undef LAUNCH
-  return launch_result();
+  return kRefusedDtype;
 }
 
 extern "C" int leone_sample(const float* logits, int rows, int vocab, const float* temperature,
@@ -368,6 +411,6 @@ extern "C" int leone_sample(const float* logits, int rows, int vocab, const floa
                             cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (vocab <= 0) return kRefusedSize;
-  sample_kernel<<<rows, 1024, 0, stream>>>(logits, vocab, temperature, seeds, positions, out);
-  return launch_result();
+  return launch_kernel(sample_kernel, dim3(rows), dim3(1024), 0, stream, logits, vocab, temperature,
+                       seeds, positions, out);
 }

@@ -1,14 +1,15 @@
 // out[M,N] = x[M,K] * w[N,K]^T in bfloat16 on the 5th-generation tensor cores.
 //
-// Orientation.  The weight matrix always rides the MMA's M dimension (128 weight
-// rows per tile, one TMEM lane each) and the tokens ride the MMA's N dimension
-// (BN = 16..256 tokens per tile).  A decode step with a handful of tokens is
-// then a pure weight stream through 128x16 MMAs, and a prompt portion uses
-// 128x256 tiles; one kernel serves both.  The reference has a GEMV family for
-// decode and a library GEMM for prompts
+// Orientation.  Both operands are K-major, so either may ride the MMA's M dimension.
+// Up to 256 tokens ("swapped"): the weight matrix rides M (128 weight rows per tile, one
+// TMEM lane each) and the tokens ride N (BN = 16..256 tokens per tile), so a decode step
+// with a handful of tokens is a pure weight stream through 128x16 MMAs.  More tokens
+// (prompt portions): 128 tokens ride M and 256 weight rows ride N, so each epilogue
+// thread owns one token row and writes 16 consecutive outputs at a time with vector
+// stores.  The reference has a GEMV family for decode and a library GEMM for prompts
 // (crates/leone-cuda/cuda/ie_cuda.cu:1718, 5069); this kernel replaces both.
 //
-// Structure (persistent, one block per SM, 6 warps):
+// Structure (persistent; two blocks per SM for up to 64 tokens, else one; 6 warps):
 //   warp 0       TMA producer: weight tile [128 x 64] and token tile [BN x 64] per
 //                k-block into a ring of shared-memory stages (128-byte swizzle);
 //   warp 1       allocates tensor memory, issues tcgen05.mma (one thread), commits each
@@ -30,9 +31,13 @@ constexpr int kTileW = 128;     // weight rows per tile = MMA M
 constexpr int kTileK = 64;      // one 128-byte swizzle row of bf16
 constexpr int kGemmThreads = 192;
 
+// Up to 64 tokens per tile a block keeps about 100 KB of stages, so two blocks (of this kernel
+// or of this one and the next) share an SM: while one drains its epilogue the other already
+// streams weights.  Larger token tiles take the whole SM.
 template <int BN> struct GemmCfg {
   static constexpr int kStageBytes = kTileW * kTileK * 2 + BN * kTileK * 2;
-  static constexpr int kStages = BN <= 16 ? 10 : BN <= 32 ? 9 : BN <= 64 ? 8 : BN <= 128 ? 6 : 4;
+  static constexpr int kStages = BN <= 16 ? 5 : BN <= 32 ? 5 : BN <= 64 ? 4 : BN <= 128 ? 6 : 4;
+  static constexpr int kBlocksPerSm = BN <= 64 ? 2 : 1;
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment*/ + 256 /*barriers*/;
 };
@@ -42,14 +47,29 @@ struct GemmParams {
   const float* residual;
   int M, N, K, ldc;
   int epilogue;
-  int splits;
+  int splits;        // K is split this many ways ...
+  int full_tiles;    // ... for tiles at or past this index; earlier tiles are not split
   float* workspace;
   int* counters;
   int* status;
 };
 
-template <int BN>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+// Work units in launch order: the unsplit tiles first, then `splits` units per remaining tile.
+// Splitting only the tiles of the last, partly filled round keeps every SM busy without
+// paying the partial-sum round trip on the others.
+struct Unit {
+  int tile, split, nsplit;
+};
+__device__ __forceinline__ Unit unit_of(int u, const GemmParams& p) {
+  if (u < p.full_tiles) return Unit{u, 0, 1};
+  const int r = u - p.full_tiles;
+  return Unit{p.full_tiles + r / p.splits, r % p.splits, p.splits};
+}
+
+// kSwap: weights on the MMA's M side (tile 128), tokens on its N side (tile BN).
+// !kSwap: tokens on the M side (tile 128), weights on the N side (tile BN); no split-K.
+template <int BN, bool kSwap>
+__global__ void __launch_bounds__(kGemmThreads, GemmCfg<BN>::kBlocksPerSm)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                const GemmParams p) {
   using Cfg = GemmCfg<BN>;
@@ -67,11 +87,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __shared__ int last_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_tiles = (p.N + kTileW - 1) / kTileW;
-  const int m_tiles = (p.M + BN - 1) / BN;
+  // tiles along the tokens (m) and along the weight rows (n); the token tile index runs
+  // fastest so that blocks working at the same time share weight tiles through L2
+  constexpr int kTokRows = kSwap ? BN : kTileW, kWRows = kSwap ? kTileW : BN;
+  const int n_tiles = (p.N + kWRows - 1) / kWRows;
+  const int m_tiles = (p.M + kTokRows - 1) / kTokRows;
   const int k_blocks = (p.K + kTileK - 1) / kTileK;
-  const int kb_per_split = (k_blocks + p.splits - 1) / p.splits;
-  const int total = n_tiles * m_tiles * p.splits;
+  const int total = p.full_tiles + (n_tiles * m_tiles - p.full_tiles) * p.splits;
 
   if (threadIdx.x == 0) {
     gave_up = 0;
@@ -93,23 +115,45 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = tmem_holder;
   volatile int* giveup = &gave_up;
+  pdl_trigger();
 
   if (warp == 0) {
     // ---------------- producer ----------------
+    // The weights do not depend on the kernels before this one: the weight halves of the
+    // first stages are requested at once, and only then does the producer wait for the
+    // predecessor (whose output is the token operand).  Pass 0 issues those early weight
+    // loads, pass 1 is the steady loop, which for the first stages adds the token half only.
     if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      for (int t = blockIdx.x; t < total && !*giveup; t += gridDim.x) {
-        const int split = t % p.splits, tile = t / p.splits;
-        const int m_tile = tile % m_tiles, n_tile = tile / m_tiles;
-        const int kb0 = split * kb_per_split, kb1 = min(k_blocks, kb0 + kb_per_split);
-        for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, giveup)) break;
-          const uint32_t dst = tiles_base + stage * Cfg::kStageBytes;
-          mbar_expect_tx(full0 + 8 * stage, Cfg::kStageBytes);
-          tma_load_2d(dst, &map_w, full0 + 8 * stage, kb * kTileK, n_tile * kTileW);
-          tma_load_2d(dst + kTileW * kTileK * 2, &map_x, full0 + 8 * stage, kb * kTileK, m_tile * BN);
-          if (++stage == kStages) { stage = 0; phase ^= 1; }
+      int early = 0;                       // stages whose weight half was requested in pass 0
+      for (int pass = 0; pass < 2; ++pass) {
+        int stage = 0, filled = 0;
+        uint32_t phase = 0;
+        bool stop = false;
+        for (int t = blockIdx.x; t < total && !*giveup && !stop; t += gridDim.x) {
+          const Unit un = unit_of(t, p);
+          const int m_tile = un.tile % m_tiles, n_tile = un.tile / m_tiles;
+          const int per = (k_blocks + un.nsplit - 1) / un.nsplit;
+          const int kb0 = un.split * per, kb1 = min(k_blocks, kb0 + per);
+          for (int kb = kb0; kb < kb1; ++kb, ++filled) {
+            if (pass == 0 && filled == kStages) { stop = true; break; }
+            const bool had_weights = pass == 1 && filled < early;
+            if (pass == 1 && !had_weights && !mbar_wait(empty0 + 8 * stage, phase ^ 1, giveup)) {
+              stop = true;
+              break;
+            }
+            const uint32_t dst = tiles_base + stage * Cfg::kStageBytes;
+            const uint32_t bar = full0 + 8 * stage;
+            if (!had_weights) mbar_expect_tx(bar, Cfg::kStageBytes);
+            const uint32_t w_dst = kSwap ? dst : dst + kTileW * kTileK * 2;
+            const uint32_t x_dst = kSwap ? dst + kTileW * kTileK * 2 : dst;
+            if (!had_weights) tma_load_2d(w_dst, &map_w, bar, kb * kTileK, n_tile * (kSwap ? kTileW : BN));
+            if (pass == 1) tma_load_2d(x_dst, &map_x, bar, kb * kTileK, m_tile * (kSwap ? BN : kTileW));
+            if (++stage == kStages) { stage = 0; phase ^= 1; }
+          }
+        }
+        if (pass == 0) {
+          early = filled;
+          pdl_wait();
         }
       }
     }
@@ -121,8 +165,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       uint32_t phase = 0;
       int it = 0;
       for (int t = blockIdx.x; t < total && !*giveup; t += gridDim.x, ++it) {
-        const int split = t % p.splits;
-        const int kb0 = split * kb_per_split, kb1 = min(k_blocks, kb0 + kb_per_split);
+        const Unit un = unit_of(t, p);
+        const int per = (k_blocks + un.nsplit - 1) / un.nsplit;
+        const int kb0 = un.split * per, kb1 = min(k_blocks, kb0 + per);
         const int buf = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         if (!mbar_wait(acc_empty0 + 8 * buf, acc_phase ^ 1, giveup)) break;
@@ -152,20 +197,102 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const int quarter = warp & 3;                     // TMEM lanes 32*quarter .. +31
     const int ep_tid = (warp - 2) * 32 + lane;        // 0..127
     int it = 0;
+    pdl_wait();      // outputs, residual and the split-K workspace may be in use until here
     for (int t = blockIdx.x; t < total && !*giveup; t += gridDim.x, ++it) {
-      const int split = t % p.splits, tile = t / p.splits;
+      const Unit un = unit_of(t, p);
+      const int tile = un.tile, split = un.split, nsplit = un.nsplit;
       const int m_tile = tile % m_tiles, n_tile = tile / m_tiles;
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       if (!mbar_wait(acc_full0 + 8 * buf, acc_phase, giveup)) break;
       tc_fence_after();
       const int row_local = quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
+      if (!kSwap) {
+        // this thread owns token row m and walks the tile's weight rows 16 at a time
+        const int m = m_tile * kTileW + row_local;
+        const int n0 = n_tile * BN;
+        const bool vec_ok = (p.ldc & 7) == 0;
+        if (p.epilogue == 3) {
+          __nv_bfloat16* orow = (__nv_bfloat16*)p.out + (size_t)m * p.ldc;
+          for (int c = 0; c < BN; c += 32) {             // 16 gate columns, then their 16 up columns
+            float g[16], u[16];
+            tmem_ld16(taddr + c, g);
+            tmem_ld16(taddr + c + 16, u);
+            const int col = (n0 + c) >> 1;
+            if (m < p.M && n0 + c < p.N) {
+              uint32_t packed[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float a = g[2 * j] / (1.f + expf(-g[2 * j])) * u[2 * j];
+                const float b = g[2 * j + 1] / (1.f + expf(-g[2 * j + 1])) * u[2 * j + 1];
+                __nv_bfloat162 v2 = __floats2bfloat162_rn(a, b);
+                packed[j] = *reinterpret_cast<uint32_t*>(&v2);
+              }
+              if (vec_ok) {
+                uint4* dst = reinterpret_cast<uint4*>(orow + col);
+                dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) *reinterpret_cast<uint32_t*>(orow + col + 2 * j) = packed[j];
+              }
+            }
+          }
+        } else {
+          for (int c = 0; c < BN; c += 16) {
+            float v[16];
+            tmem_ld16(taddr + c, v);
+            const int n = n0 + c;
+            if (m >= p.M || n >= p.N) continue;
+            const size_t o = (size_t)m * p.ldc + n;
+            const bool full = n + 16 <= p.N && vec_ok;
+            if (p.epilogue == 0) {
+              __nv_bfloat16* dst = (__nv_bfloat16*)p.out + o;
+              if (full) {
+                uint32_t packed[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  __nv_bfloat162 v2 = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                  packed[j] = *reinterpret_cast<uint32_t*>(&v2);
+                }
+                reinterpret_cast<uint4*>(dst)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                reinterpret_cast<uint4*>(dst)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+              } else {
+                for (int j = 0; j < 16 && n + j < p.N; ++j) dst[j] = __float2bfloat16_rn(v[j]);
+              }
+            } else {
+              float* dst = (float*)p.out + o;
+              if (full) {
+                if (p.epilogue == 2) {
+                  const float4* res = reinterpret_cast<const float4*>(p.residual + o);
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    const float4 r = res[j];
+                    v[4 * j] += r.x; v[4 * j + 1] += r.y; v[4 * j + 2] += r.z; v[4 * j + 3] += r.w;
+                  }
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                  reinterpret_cast<float4*>(dst)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+              } else {
+                for (int j = 0; j < 16 && n + j < p.N; ++j)
+                  dst[j] = p.epilogue == 2 ? v[j] + p.residual[o + j] : v[j];
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
+        continue;
+      }
       const int n = n_tile * kTileW + row_local;
       const int m0 = m_tile * BN;
-      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
       bool do_epilogue = true;
-      if (p.splits > 1) {
-        float* ws = p.workspace + ((size_t)tile * p.splits + split) * (BN * kTileW);
+      const int split_tile = tile - p.full_tiles;        // index among the split tiles
+      if (nsplit > 1) {
+        float* ws = p.workspace + ((size_t)split_tile * nsplit + split) * (BN * kTileW);
         for (int c = 0; c < BN; c += 16) {
           float v[16];
           tmem_ld16(taddr + c, v);
@@ -175,9 +302,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         __threadfence();
         named_barrier_sync(1, 128);
         if (ep_tid == 0) {
-          const int old = atomicAdd(&p.counters[tile], 1);
-          const int last = old == p.splits - 1;
-          if (last) p.counters[tile] = 0;      // ready for the next launch
+          const int old = atomicAdd(&p.counters[split_tile], 1);
+          const int last = old == nsplit - 1;
+          if (last) p.counters[split_tile] = 0;      // ready for the next launch
           last_flag = last;
         }
         named_barrier_sync(1, 128);
@@ -185,19 +312,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (do_epilogue) __threadfence();
       }
       // the accumulator buffer is free once its values are in registers or in the workspace
-      if (p.splits > 1) {
+      if (nsplit > 1) {
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
       }
       if (do_epilogue) {
-        const float* ws_tile = p.splits > 1 ? p.workspace + (size_t)tile * p.splits * (BN * kTileW) : nullptr;
+        const float* ws_tile = nsplit > 1 ? p.workspace + (size_t)split_tile * nsplit * (BN * kTileW) : nullptr;
         for (int c = 0; c < BN; c += 16) {
           float v[16];
-          if (p.splits > 1) {
+          if (nsplit > 1) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] = 0.f;
-            for (int s = 0; s < p.splits; ++s) {
+            for (int s = 0; s < nsplit; ++s) {
               const float* src = ws_tile + (size_t)s * (BN * kTileW);
 #pragma unroll
               for (int j = 0; j < 16; ++j) v[j] += __ldcg(src + (c + j) * kTileW + row_local);
@@ -232,7 +359,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           }
         }
       }
-      if (p.splits == 1) {
+      if (nsplit == 1) {
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
@@ -256,22 +383,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   }
 }
 
-template <int BN>
+template <int BN, bool kSwap>
 int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, int sm_count,
                 cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Cfg::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, kSwap>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  const int n_tiles = (p.N + kTileW - 1) / kTileW, m_tiles = (p.M + BN - 1) / BN;
-  const long long total = (long long)n_tiles * m_tiles * p.splits;
-  const int grid = (int)(total < sm_count ? total : sm_count);
-  gemm_tc_kernel<BN><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(mw, mx, p);
-  return launch_result();
+  const int w_rows = kSwap ? kTileW : BN, tok_rows = kSwap ? BN : kTileW;
+  const int n_tiles = (p.N + w_rows - 1) / w_rows, m_tiles = (p.M + tok_rows - 1) / tok_rows;
+  const long long total = p.full_tiles + ((long long)n_tiles * m_tiles - p.full_tiles) * p.splits;
+  const long long slots = (long long)sm_count * Cfg::kBlocksPerSm;
+  const int grid = (int)(total < slots ? total : slots);
+  return launch_kernel(gemm_tc_kernel<BN, kSwap>, dim3(grid), dim3(kGemmThreads), Cfg::kSmemBytes, stream,
+                       mw, mx, p);
 }
 
 }  // namespace tc
@@ -280,50 +409,68 @@ int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& 
 using namespace leone;
 using namespace leone::tc;
 
+// Turns programmatic dependent launch on or off for the kernels of this library.
+extern "C" void leone_bf16_set_pdl(int enabled) { pdl_flag() = enabled ? 1 : 0; }
+
 // Token-tile width the kernel will use for M tokens.
 extern "C" int leone_gemm_tc_tile(int m) {
   return m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : m <= 128 ? 128 : 256;
 }
 
-// Workspace floats and counters needed for (m, n, splits); both 0 when splits == 1.
-extern "C" void leone_gemm_tc_scratch(int m, int n, int splits, long long* workspace_floats,
+// Number of (weight tile, token tile) pairs the kernel makes of an [m, n] product.
+extern "C" int leone_gemm_tc_tiles(int m, int n) {
+  if (m > 256) return ((n + 255) / 256) * ((m + kTileW - 1) / kTileW);
+  const int bn = leone_gemm_tc_tile(m);
+  return ((n + kTileW - 1) / kTileW) * ((m + bn - 1) / bn);
+}
+
+// Workspace floats and counters needed when `split_tiles` tiles are split `splits` ways;
+// both 0 when splits == 1.
+extern "C" void leone_gemm_tc_scratch(int m, int split_tiles, int splits, long long* workspace_floats,
                                       int* counters) {
   const int bn = leone_gemm_tc_tile(m);
-  const long long tiles = (long long)((n + kTileW - 1) / kTileW) * ((m + bn - 1) / bn);
-  *workspace_floats = splits > 1 ? tiles * splits * bn * kTileW : 0;
-  *counters = splits > 1 ? (int)tiles : 0;
+  *workspace_floats = splits > 1 ? (long long)split_tiles * splits * bn * kTileW : 0;
+  *counters = splits > 1 ? split_tiles : 0;
 }
 
 // x: [m, k] bf16 (row stride ldx), w: [n, k] bf16 (row stride ldw), out: [m, n] (row stride ldc).
 // epilogue 0: bf16 out; 1: fp32 out; 2: fp32 out = acc + residual (same layout as out);
 // 3: w holds interleaved gate/up rows, out is bf16 [m, n/2] = silu(gate) * up.
-// splits > 1 needs `workspace` (fp32) and zeroed `counters` of the sizes leone_gemm_tc_scratch gives.
+// The first `full_tiles` tiles (in the kernel's tile order) are computed whole; the others have K
+// split `splits` ways.  splits > 1 needs `workspace` (fp32) and zeroed `counters` of the sizes
+// leone_gemm_tc_scratch gives for (tiles - full_tiles).  More than 256 tokens are never split.
 extern "C" int leone_gemm_tc(const void* x, const void* w, void* out, const float* residual, int m,
                              int n, int k, int ldx, int ldw, int ldc, int epilogue, int splits,
-                             float* workspace, int* counters, int* status, int sm_count,
-                             cudaStream_t stream) {
+                             int full_tiles, float* workspace, int* counters, int* status,
+                             int sm_count, cudaStream_t stream) {
   if (m <= 0 || n <= 0) return 0;
   if (k <= 0 || (k % 8) != 0 || (ldx % 8) != 0 || (ldw % 8) != 0) return kRefusedAlignment;
   if (epilogue < 0 || epilogue > 3 || splits < 1 || sm_count < 1) return kRefusedSize;
   if (epilogue == 2 && residual == nullptr) return kRefusedSize;
   if (epilogue == 3 && (n % 32) != 0) return kRefusedSize;
   const int k_blocks = (k + kTileK - 1) / kTileK;
+  if (m > 256) splits = 1;
   if (splits > k_blocks) splits = k_blocks;
   // every split must own at least one k-block
   while (splits > 1 && (splits - 1) * ((k_blocks + splits - 1) / splits) >= k_blocks) --splits;
   if (splits > 1 && (workspace == nullptr || counters == nullptr)) return kRefusedSize;
+  const int tiles = leone_gemm_tc_tiles(m, n);
+  if (splits == 1) full_tiles = tiles;
+  if (full_tiles < 0 || full_tiles > tiles) return kRefusedSize;
   const int bn = leone_gemm_tc_tile(m);
+  const bool swap = m <= 256;
   CUtensorMap mw, mx;
-  int r = make_tensor_map_2d(&mw, w, (uint64_t)n, (uint64_t)k, (uint64_t)ldw, kTileW);
+  int r = make_tensor_map_2d(&mw, w, (uint64_t)n, (uint64_t)k, (uint64_t)ldw, swap ? kTileW : 256);
   if (r != 0) return r;
-  r = make_tensor_map_2d(&mx, x, (uint64_t)m, (uint64_t)k, (uint64_t)ldx, (uint32_t)bn);
+  r = make_tensor_map_2d(&mx, x, (uint64_t)m, (uint64_t)k, (uint64_t)ldx, swap ? (uint32_t)bn : kTileW);
   if (r != 0) return r;
-  GemmParams p{out, residual, m, n, k, ldc, epilogue, splits, workspace, counters, status};
+  GemmParams p{out, residual, m, n, k, ldc, epilogue, splits, full_tiles, workspace, counters, status};
+  if (!swap) return launch_gemm<256, false>(mw, mx, p, sm_count, stream);
   switch (bn) {
-    case 16: return launch_gemm<16>(mw, mx, p, sm_count, stream);
-    case 32: return launch_gemm<32>(mw, mx, p, sm_count, stream);
-    case 64: return launch_gemm<64>(mw, mx, p, sm_count, stream);
-    case 128: return launch_gemm<128>(mw, mx, p, sm_count, stream);
-    default: return launch_gemm<256>(mw, mx, p, sm_count, stream);
+    case 16: return launch_gemm<16, true>(mw, mx, p, sm_count, stream);
+    case 32: return launch_gemm<32, true>(mw, mx, p, sm_count, stream);
+    case 64: return launch_gemm<64, true>(mw, mx, p, sm_count, stream);
+    case 128: return launch_gemm<128, true>(mw, mx, p, sm_count, stream);
+    default: return launch_gemm<256, true>(mw, mx, p, sm_count, stream);
   }
 }

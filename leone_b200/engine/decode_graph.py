@@ -15,6 +15,8 @@ read back once (the reference's service quantum is 4 tokens, crates/leone-cli/sr
 """
 from __future__ import annotations
 
+import gc
+import weakref
 from typing import Dict, Hashable, List, Sequence
 
 import numpy as np
@@ -25,7 +27,7 @@ from .batch import StepContext, pack_metadata
 
 class DecodeGraph:
     def __init__(self, engine, batch: int, max_quantum: int = 64):
-        self.engine = engine
+        self.engine = weakref.proxy(engine)     # the engine owns this object: no reference cycle
         self.batch = batch
         self.max_quantum = max_quantum
         dev = engine.device
@@ -105,8 +107,16 @@ class DecodeGraph:
             self.stream.synchronize()
             before = self.engine.ops.launches
             self.graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(self.graph, stream=self.stream):
-                self._one_step()
+            # an object that the collector finalises in the middle of a capture (an older
+            # graph, a freed pool) would invalidate the capture: keep the collector out
+            was_enabled = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(self.graph, stream=self.stream, capture_error_mode="thread_local"):
+                    self._one_step()
+            finally:
+                if was_enabled:
+                    gc.enable()
             self.launches_per_step = self.engine.ops.launches - before
         cur.wait_stream(self.stream)
         self.counter.zero_()

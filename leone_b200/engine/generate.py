@@ -45,13 +45,15 @@ def generate(model: Union[str, Engine], prompts: Sequence[Sequence[int]], max_ne
              num_pages: Optional[int] = None, prefill_chunk: int = 2048,
              max_batch_tokens: int = 2048, max_running: int = 64, policy: str = "reserve",
              device: str = "cuda:0", return_stats: bool = False, decode_quantum: int = 1,
-             use_graphs: bool = True):
+             use_graphs: bool = True, prefill_first: bool = True):
     """Generate ``max_new_tokens`` tokens for each prompt (a list of token ids).
 
     ``model`` is a model folder (config.json + model.safetensors) or an :class:`Engine`.
     ``temperature`` 0 is greedy; otherwise each request ``i`` draws with seed ``seed + i`` so
-    its stream does not depend on what it is batched with.  Returns the generated ids per
-    prompt (and a :class:`GenerationStats` if ``return_stats``).
+    its stream does not depend on what it is batched with.  ``prefill_first`` (default) runs
+    all prompts before decoding starts, so the requests decode as one batch; ``False`` mixes
+    prompt portions with decode tokens of earlier requests, as a server would.  Returns the
+    generated ids per prompt (and a :class:`GenerationStats` if ``return_stats``).
     """
     prompts = [list(map(int, p)) for p in prompts]
     if isinstance(model, Engine):
@@ -69,7 +71,8 @@ def generate(model: Union[str, Engine], prompts: Sequence[Sequence[int]], max_ne
     sched = Scheduler(engine, SchedulerConfig(max_running=min(max_running, engine.max_requests),
                                               max_batch_tokens=min(max_batch_tokens, engine.max_batch_tokens),
                                               prefill_chunk_tokens=prefill_chunk, policy=policy,
-                                              decode_quantum=decode_quantum, use_graphs=use_graphs))
+                                              decode_quantum=decode_quantum, use_graphs=use_graphs,
+                                              prefill_first=prefill_first))
     for i, p in enumerate(prompts):
         sched.add_request(i, p, max_new_tokens, SamplingParams(temperature, seed + i), eos_token_id)
     stats = GenerationStats(prompt_tokens=sum(len(p) for p in prompts))

@@ -4,7 +4,9 @@ Each call of :meth:`Scheduler.step` builds one batch for the engine's step
 function: one token for every request that is decoding, then portions of
 waiting prompts in arrival order until the token budget is used
 (``max_batch_tokens`` for the whole step, ``prefill_chunk_tokens`` per
-request).  The reference dispatches per request with a token budget of
+request).  With ``prefill_first`` decode rows are held back while any running
+request still has prompt left, so requests that start together also decode
+together (larger decode batches; the choice for offline generation).  The reference dispatches per request with a token budget of
 ``min(remaining_prefill, prefill_chunk_tokens)`` or a decode quantum
 (crates/leone/src/scheduler.rs:341-378) and runs prompt portions and decode
 rows in separate passes; here they share one batch.
@@ -52,6 +54,7 @@ class SchedulerConfig:
     prefill_chunk_tokens: int = 2048
     policy: str = "reserve"            # or "optimistic"
     decode_quantum: int = 1            # decode steps run without the host when only decoding
+    prefill_first: bool = False        # True: no decode rows while a running request has prompt left
     use_graphs: bool = True            # replay decode-only steps from a CUDA graph
 
     def __post_init__(self):
@@ -194,7 +197,11 @@ class Scheduler:
             self._try_admit()
         budget = self.config.max_batch_tokens
         plan = []
+        decoding = lambda r: bool(r.generated) and r.computed == len(r.tokens) - 1   # noqa: E731
+        hold_decodes = self.config.prefill_first and any(not decoding(r) for r in self.running)
         for req in self.running:                       # decode rows first
+            if hold_decodes:
+                break
             if req.computed == len(req.tokens) - 1 and req.generated and budget > 0:
                 plan.append((req, req.computed, 1))
                 budget -= 1

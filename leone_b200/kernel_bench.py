@@ -67,18 +67,19 @@ def bench_gemm(ops, m, n, k, splits, epilogue, reps, warmup, flush):
     if epilogue == 2:
         out.zero_()
     state = {"i": 0}
+    full_tiles = 0
     if splits is None:
-        splits = fast.choose_splits(m, n, k) if epilogue != 3 else 1
+        splits, full_tiles = fast.choose_splits(m, n, k)
 
     def run():
         w = ws[state["i"] % copies]
         state["i"] += 1
-        fast._gemm(x, w, out, epilogue, res, n, splits=splits)
+        fast._gemm(x, w, out, epilogue, res, n, splits=splits, full_tiles=full_tiles)
 
     ms = _time(run, reps, warmup, flush, per_graph=copies)
     bytes_ = n * k * 2 + m * k * 2 + out.numel() * out.element_size()
     flops = 2.0 * m * n * k
-    return dict(kernel="gemm_tc", m=m, n=n, k=k, splits=splits, epilogue=epilogue, us=ms * 1e3,
+    return dict(kernel="gemm_tc", m=m, n=n, k=k, splits=splits, full_tiles=full_tiles, epilogue=epilogue, us=ms * 1e3,
                 gbs=bytes_ / ms / 1e6, tflops=flops / ms / 1e9)
 
 

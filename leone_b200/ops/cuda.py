@@ -11,6 +11,7 @@ between checked wrappers and raw entry points
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_void_p
 from typing import Optional
 
@@ -96,6 +97,15 @@ class CudaOps:
             self.fast = FastKernels(self.device)
         self.launches = 0
         self.status = None
+        # LEONE_NO_PDL=1 launches every kernel fully serialised after its predecessor
+        self.set_pdl(os.environ.get("LEONE_NO_PDL", "0") != "1")
+
+    def set_pdl(self, enabled: bool) -> None:
+        """Programmatic dependent launch: a kernel may start (and fetch weights) while its
+        predecessor in the stream still runs; it waits before touching the step's data."""
+        self.core.leone_core_set_pdl(1 if enabled else 0)
+        if self.fast is not None:
+            self.fast.lib.leone_bf16_set_pdl(1 if enabled else 0)
 
     def bind_status(self, status: torch.Tensor) -> None:
         """The engine's status word; kernels with bounded waits report into it."""

@@ -44,16 +44,26 @@ class FastKernels:
             self._counters = torch.zeros(max(counters, 4096), dtype=torch.int32, device=self.device)
         return self._workspace, self._counters
 
-    def choose_splits(self, m: int, n: int, k: int) -> int:
-        """Split K only when few tokens leave most SMs without a weight tile."""
-        if m > 64:
-            return 1
-        tiles = -(-n // 128)
+    def choose_splits(self, m: int, n: int, k: int):
+        """How to split K: ``(splits, full_tiles)``; tiles before ``full_tiles`` are not split.
+
+        Fewer tiles than SMs: every tile is split so that one round of units fills the SMs.
+        More tiles than SMs: only the tiles of the last, partly filled round are split, so
+        that round costs a fraction of a full one.  A split costs a partial-sum round trip, so
+        a unit keeps at least 12 k-blocks.  Prompt-sized M is never split."""
+        tiles = int(self.lib.leone_gemm_tc_tiles(m, n))
+        if m > 256:
+            return 1, tiles
         k_blocks = -(-k // 64)
-        if tiles * 2 > self.sm_count:
-            return 1
-        splits = min(self.sm_count // tiles, k_blocks // 8, 16)
-        return max(1, splits)
+        sms = self.sm_count
+        if tiles < sms:
+            s = max(1, min(sms // tiles, k_blocks // 12, 8))
+            return (s, 0) if s > 1 else (1, tiles)
+        rem = tiles % sms
+        if rem == 0 or rem * 4 > sms * 3:
+            return 1, tiles
+        s = min(sms // rem, k_blocks // 12, 8)
+        return (s, tiles - rem) if s > 1 else (1, tiles)
 
     def _tc_ok(self, x, w, out) -> bool:
         if not self.use_tensor_cores or x.dtype != torch.bfloat16:
@@ -62,18 +72,22 @@ class FastKernels:
         return (k % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
                 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
-    def _gemm(self, x, w, out, epilogue, residual, n_rows, splits=None) -> bool:
+    def _gemm(self, x, w, out, epilogue, residual, n_rows, splits=None, full_tiles=0) -> bool:
+        """``splits=None`` lets :meth:`choose_splits` decide; otherwise tiles from
+        ``full_tiles`` on are split ``splits`` ways."""
         m, k = x.shape
         if splits is None:
-            splits = self.choose_splits(m, n_rows, k)
+            splits, full_tiles = self.choose_splits(m, n_rows, k)
         ws = ct = None
         if splits > 1:
+            tiles = int(self.lib.leone_gemm_tc_tiles(m, n_rows))
             floats, counters = c_longlong(0), c_int(0)
-            self.lib.leone_gemm_tc_scratch(m, n_rows, splits, byref(floats), byref(counters))
+            self.lib.leone_gemm_tc_scratch(m, max(tiles - full_tiles, 0), splits, byref(floats), byref(counters))
             ws, ct = self._scratch(floats.value, counters.value)
         code = self.lib.leone_gemm_tc(_ptr(x), _ptr(w), _ptr(out), _ptr(residual), m, n_rows, k,
                                       x.stride(0), w.stride(0), out.stride(0), epilogue, splits,
-                                      _ptr(ws), _ptr(ct), _ptr(self.status), self.sm_count, self._stream())
+                                      full_tiles, _ptr(ws), _ptr(ct), _ptr(self.status), self.sm_count,
+                                      self._stream())
         if code != 0:
             raise RuntimeError(f"gemm_tc refused or failed with code {code} for m={m} n={n_rows} k={k}")
         return True
@@ -101,14 +115,14 @@ class FastKernels:
     def linear_swiglu(self, x, w, out) -> bool:
         if getattr(w, "gate_up_layout", None) != "interleaved16" or not self._tc_ok(x, w.weight, out):
             return False
-        return self._gemm(x, w.weight, out, 3, None, w.out_features, splits=1)
+        return self._gemm(x, w.weight, out, 3, None, w.out_features)
 
     # -- attention ------------------------------------------------------------------------
     def decode_splits(self, n_seqs: int, n_kv: int, g: int, max_ctx: int) -> int:
         """Splits of the key range so that about two blocks per SM are in flight."""
         blocks = n_seqs * n_kv * (-(-g // 16))
-        want = max(1, (2 * self.sm_count) // max(blocks, 1))
-        return int(max(1, min(want, -(-max_ctx // 256), 64)))
+        want = max(1, (3 * self.sm_count) // max(blocks, 1))
+        return int(max(1, min(want, -(-max_ctx // 128), 64)))
 
     def attention(self, ctx, qkv, out, n_q, n_kv, d, scale, window, cache) -> bool:
         if not self.use_tiled_attention or qkv.dtype != torch.bfloat16:

@@ -42,7 +42,8 @@ def test_temperature_chunked_mixed_fp32(folders, policy, pages, quantum):
     want = [plain_generate(plain, p, 6, 0.8, 7 + i) for i, p in enumerate(prompts)]
     eng = _engine(folders["B"], "B", "float32", pages)
     got, stats = generate(eng, prompts, 6, temperature=0.8, seed=7, prefill_chunk=6, max_batch_tokens=16,
-                          policy=policy, return_stats=True, eos_token_id=-1, decode_quantum=quantum)
+                          policy=policy, return_stats=True, eos_token_id=-1, decode_quantum=quantum,
+                          prefill_first=False)
     assert got == want
     if policy == "optimistic":
         assert stats.preemptions > 0

@@ -170,6 +170,24 @@ def test_gemm_tc_swiglu(ops16, m, inter, k):
     _close(out, g / (1 + torch.exp(-g)) * u, 2 ** -7, 1e-4, "tc swiglu")
 
 
+@pytest.mark.parametrize("m,n,k,splits,full", [(8, 128 * 7, 1024, 3, 4), (40, 128 * 5 + 17, 2048, 4, 2),
+                                               (1, 128 * 3, 4096, 8, 1), (64, 1000, 512, 2, 7)])
+def test_gemm_tc_splits_only_the_last_tiles(ops16, m, n, k, splits, full):
+    fast = ops16.fast
+    x = _randn((m, k), 21, torch.bfloat16)
+    w = _randn((n, k), 22, torch.bfloat16, scale=0.05)
+    want = x.double() @ w.double().t()
+    res = _randn((m, n), 23)
+    hidden = res.clone()
+    fast._gemm(x, w, hidden, 2, hidden, n, splits=splits, full_tiles=full)
+    _close(hidden, want + res.double(), 1e-5, 2e-6 * math.sqrt(k) * 4, "tail split")
+    out = torch.empty((m, n), device=DEV, dtype=torch.bfloat16)
+    fast._gemm(x, w, out, 0, None, n)                    # the heuristic's own choice
+    _close(out, want, 2 ** -8, 2e-6 * math.sqrt(k) * 4, "heuristic split")
+    torch.cuda.synchronize()
+    assert int(fast._counters.abs().sum()) == 0
+
+
 def test_gemm_tc_refuses_unaligned_k(ops16):
     x = _randn((4, 60), 1, torch.bfloat16)
     w = ops16.prepare_matrix(_randn((32, 60), 2, torch.bfloat16))

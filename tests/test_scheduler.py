@@ -105,6 +105,19 @@ def test_token_budget_and_portions():
     assert mixed, "a decode row and a prompt portion never shared a batch"
 
 
+def test_prefill_first_holds_decodes_until_prompts_are_done():
+    eng = FakeEngine(pages=16)
+    s = Scheduler(eng, SchedulerConfig(max_batch_tokens=8, prefill_chunk_tokens=5, prefill_first=True))
+    s.add_request("a", list(range(1, 14)), 3)
+    s.add_request("b", [5, 6, 7], 3)
+    got = _run(s)
+    assert got == {"a": alone(list(range(1, 14)), 3), "b": alone([5, 6, 7], 3)}
+    prompt_steps = [i for i, b in enumerate(eng.batches) if any(n > 1 for _, n in b)]
+    decode_steps = [i for i, b in enumerate(eng.batches) if all(n == 1 for _, n in b)]
+    assert max(prompt_steps) < min(decode_steps)
+    assert all(len(b) == 2 for b in eng.batches[min(decode_steps):min(decode_steps) + 2])
+
+
 def test_reserve_policy_never_runs_out_and_queues_in_order():
     eng = FakeEngine(pages=6, page_tokens=4)
     s = Scheduler(eng, SchedulerConfig(policy="reserve"))
@@ -202,8 +215,9 @@ def test_generation_with_the_tiny_model_on_emulated_kernels(tmp_path):
             eng = Engine.from_folder(folder, dtype="float32", device="cpu", ops=EmulatedOps(),
                                      page_tokens=PAGE_TOKENS[which], num_pages=pages, max_requests=4,
                                      max_batch_tokens=16)
-            got = generate(eng, prompts, n_new, temperature=temp, seed=7, prefill_chunk=6,
-                           max_batch_tokens=16, policy=policy, eos_token_id=-1)
-            assert got == want, (which, policy)
+            for first in (False, True):
+                got = generate(eng, prompts, n_new, temperature=temp, seed=7, prefill_chunk=6,
+                               max_batch_tokens=16, policy=policy, eos_token_id=-1, prefill_first=first)
+                assert got == want, (which, policy, first)
             eng.cache.check_invariants()
             assert eng.cache.free_pages()[0] == pages
