@@ -76,5 +76,11 @@ extern "C" int leone_attention_decode_static(const void* qkv, int row_stride, vo
                                           n_kv, d, scale, window, page_tokens, num_pages, splits,
                                           scratch, status, stream);
   if (code < 0) set_error(error, error_len, "leone_attention_decode_static: the kernel refuses these sizes");
+  if (code > 0) {
+    char text[160];
+    snprintf(text, sizeof(text), "leone_attention_decode_static: launch failed: %s",
+             cudaGetErrorString((cudaError_t)code));
+    set_error(error, error_len, text);
+  }
   return code;
 }

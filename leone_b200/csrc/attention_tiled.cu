@@ -296,10 +296,14 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
 
 // ------------------------------------------------------------------------------------
 // Decode: one query token per sequence.  grid = (n_kv * head groups, splits, sequences).
-// The (up to 16) query heads of the KV head are the 16 rows of every MMA; the four warps
-// take 16 keys each of every 64-key tile and are merged at the end.  With more than one
-// split the block writes (max, sum, unnormalised output) to scratch for the merge kernel.
+// The (up to 16) query heads of the KV head are the 16 rows of every MMA.  The block's key
+// range is cut into groups of 16 keys dealt round-robin to the four warps; every warp runs a
+// private cp.async pipeline (kDecodeStages groups of keys and values in flight) and never
+// waits for the others inside the loop; the warps are merged once at the end.  With more than
+// one split the block writes (max, sum, unnormalised output) to scratch for the merge kernel.
 // ------------------------------------------------------------------------------------
+constexpr int kDecodeStages = 3;
+
 template <int D>
 __global__ void __launch_bounds__(kThreads)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
@@ -308,10 +312,11 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
                         float scale, int window, int splits, float* __restrict__ part_o,
                         float* __restrict__ part_ml, int* status) {
   constexpr int kRow = D + 8;
+  constexpr int kChunks = D / 8;                        // 16-byte chunks per key row
+  constexpr int kGroupElems = 16 * kRow;                // one group of 16 rows
   extern __shared__ __align__(16) uint8_t smem_raw[];
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [16][kRow]
-  __nv_bfloat16* kv_s = q_s + 16 * kRow;                                      // [2][K,V][64][kRow]
-  long long* row_src = reinterpret_cast<long long*>(kv_s + 4 * kKeyTile * kRow);   // [2][64]
+  __nv_bfloat16* kv_s = q_s + kGroupElems;              // [4 warps][stages][K,V][16][kRow]
 
   pdl_trigger();
   pdl_wait();
@@ -323,14 +328,13 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int row_token = q_start[seq];
   const int ctx = ctx_len[seq];
-  const int pos = ctx - 1;
   const int k_lo = window > 0 ? max(0, ctx - window) : 0;
   const int total = ctx - k_lo;
   const int chunk = ((total + splits - 1) / splits + kKeyTile - 1) / kKeyTile * kKeyTile;
   const int k_begin = k_lo + split * chunk, k_end = min(ctx, k_begin + chunk);
-  const int n_tiles = k_end > k_begin ? (k_end - k_begin + kKeyTile - 1) / kKeyTile : 0;
+  const int n_groups = k_end > k_begin ? (k_end - k_begin + 15) / 16 : 0;
 
-  if (n_tiles == 0) {
+  if (n_groups == 0) {
     if (splits > 1) {
       for (int h = tid; h < heads; h += kThreads) {
         float* ml = part_ml + (((size_t)seq * n_q + head0 + h) * splits + split) * 2;
@@ -344,17 +348,51 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
     return;
   }
 
-  for (int idx = tid; idx < 16 * (D / 8); idx += kThreads) {
-    const int r = idx / (D / 8), ch = idx - r * (D / 8);
+  for (int idx = tid; idx < 16 * kChunks; idx += kThreads) {
+    const int r = idx / kChunks, ch = idx - r * kChunks;
     const bool ok = r < heads;
     const __nv_bfloat16* src =
         qkv + (size_t)row_token * row_stride + (size_t)(head0 + (ok ? r : 0)) * D + ch * 8;
     cp_async16(smem_u32(q_s + r * kRow + ch * 8), src, ok);
   }
   cp_async_commit();
-  load_kv_tile<D>(kv_s, kv_s + kKeyTile * kRow, row_src, pa, seq, kvh, k_begin, k_lo, k_end, status,
-                  row_token);
-  cp_async_commit();
+  cp_async_wait<0>();
+  __syncthreads();
+  uint32_t q_frag[D / 16][4];
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks) {
+    const int mi = lane >> 3;
+    const int r = (mi & 1) * 8 + (lane & 7), c = ks * 16 + (mi >> 1) * 8;
+    ldmatrix_x4(smem_u32(q_s + r * kRow + c), q_frag[ks]);
+  }
+
+  __nv_bfloat16* my_s = kv_s + (size_t)warp * kDecodeStages * 2 * kGroupElems;
+  // Requests keys/values of group `grp` (16 keys from k_begin + 16*grp) into stage `st`.
+  auto issue = [&](int grp, int st) {
+    if (grp < n_groups) {
+      long long src = -1;
+      if (lane < 16) {
+        const int kj = k_begin + grp * 16 + lane;
+        if (kj < k_end) {
+          const int blk = kj / pa.page_tokens;
+          const int page = blk < pa.table_width ? pa.block_table[(size_t)seq * pa.table_width + blk] : -1;
+          if (page < 0 || page >= pa.num_pages) set_status(status, kBadPage, row_token, page, kj);
+          else src = (((long long)page * pa.n_kv + kvh) * pa.page_tokens + (kj % pa.page_tokens)) * D;
+        }
+      }
+      __nv_bfloat16* k_dst = my_s + (size_t)st * 2 * kGroupElems;
+      __nv_bfloat16* v_dst = k_dst + kGroupElems;
+      for (int idx = lane; idx < 16 * kChunks; idx += 32) {
+        const int r = idx / kChunks, ch = idx - r * kChunks;
+        const long long rs = __shfl_sync(0xffffffffu, src, r);
+        const bool ok = rs >= 0;
+        const long long off = ok ? rs + ch * 8 : 0;
+        cp_async16(smem_u32(k_dst + r * kRow + ch * 8), pa.k_pool + off, ok);
+        cp_async16(smem_u32(v_dst + r * kRow + ch * 8), pa.v_pool + off, ok);
+      }
+    }
+    cp_async_commit();          // always: keeps the group count the same in every iteration
+  };
 
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   float o_acc[D / 8][4];
@@ -362,38 +400,24 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
   for (int i = 0; i < D / 8; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j) o_acc[i][j] = 0.f;
-  uint32_t q_frag[D / 16][4];
   const float sl2 = scale * kLog2e;
 
-  for (int t = 0; t < n_tiles; ++t) {
-    const int stage = t & 1;
-    __nv_bfloat16* k_s = kv_s + stage * 2 * kKeyTile * kRow;
-    __nv_bfloat16* v_s = k_s + kKeyTile * kRow;
-    if (t + 1 < n_tiles) {
-      __nv_bfloat16* k_n = kv_s + (stage ^ 1) * 2 * kKeyTile * kRow;
-      load_kv_tile<D>(k_n, k_n + kKeyTile * kRow, row_src + (stage ^ 1) * kKeyTile, pa, seq, kvh,
-                      k_begin + (t + 1) * kKeyTile, k_lo, k_end, status, row_token);
-      cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
-    __syncthreads();
-    if (t == 0) {
 #pragma unroll
-      for (int ks = 0; ks < D / 16; ++ks) {
-        const int mi = lane >> 3;
-        const int r = (mi & 1) * 8 + (lane & 7), c = ks * 16 + (mi >> 1) * 8;
-        ldmatrix_x4(smem_u32(q_s + r * kRow + c), q_frag[ks]);
-      }
-    }
-    const int key0 = k_begin + t * kKeyTile + warp * 16;     // this warp's 16 keys
+  for (int s0 = 0; s0 < kDecodeStages - 1; ++s0) issue(warp + 4 * s0, s0);
+  int it = 0;
+  for (int grp = warp; grp < n_groups; grp += 4, ++it) {
+    issue(grp + 4 * (kDecodeStages - 1), (it + kDecodeStages - 1) % kDecodeStages);
+    cp_async_wait<kDecodeStages - 1>();
+    __syncwarp();
+    const __nv_bfloat16* k_s = my_s + (size_t)(it % kDecodeStages) * 2 * kGroupElems;
+    const __nv_bfloat16* v_s = k_s + kGroupElems;
+    const int key0 = k_begin + grp * 16;
     float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
     for (int ks = 0; ks < D / 16; ++ks) {
       uint32_t b[4];
       const int mi = lane >> 3;
-      const int r = warp * 16 + (mi >> 1) * 8 + (lane & 7), c = ks * 16 + (mi & 1) * 8;
+      const int r = (mi >> 1) * 8 + (lane & 7), c = ks * 16 + (mi & 1) * 8;
       ldmatrix_x4(smem_u32(k_s + r * kRow + c), b);
       mma_16816(s[0], q_frag[ks], b[0], b[1]);
       mma_16816(s[1], q_frag[ks], b[2], b[3]);
@@ -404,7 +428,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int kj = key0 + nt * 8 + (lane & 3) * 2 + (j & 1);
-        const float v = (kj < k_end && kj <= pos) ? s[nt][j] * sl2 : -INFINITY;
+        const float v = kj < k_end ? s[nt][j] * sl2 : -INFINITY;
         s[nt][j] = v;
         tile_max[j >> 1] = fmaxf(tile_max[j >> 1], v);
       }
@@ -440,15 +464,16 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
     for (int np = 0; np < D / 16; ++np) {
       uint32_t b[4];
       const int mi = lane >> 3;
-      const int r = warp * 16 + (mi & 1) * 8 + (lane & 7), c = np * 16 + (mi >> 1) * 8;
+      const int r = (mi & 1) * 8 + (lane & 7), c = np * 16 + (mi >> 1) * 8;
       ldmatrix_x4_trans(smem_u32(v_s + r * kRow + c), b);
       mma_16816(o_acc[np * 2], p_frag, b[0], b[1]);
       mma_16816(o_acc[np * 2 + 1], p_frag, b[2], b[3]);
     }
-    __syncthreads();
+    __syncwarp();      // the stage is refilled by the next iteration's request
   }
+  cp_async_wait<0>();
+  __syncthreads();     // every warp is done with its stages: the space becomes the merge buffer
 
-  // merge the four warps through shared memory (the K/V stages are free now)
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
@@ -531,7 +556,7 @@ template <int D> constexpr int prefill_smem() {
   return (kRowsPerBlock + 4 * kKeyTile) * (D + 8) * 2 + 2 * kKeyTile * 8;
 }
 template <int D> constexpr int decode_smem() {
-  const int tiles = (16 + 4 * kKeyTile) * (D + 8) * 2 + 2 * kKeyTile * 8;
+  const int tiles = (16 + 4 * kDecodeStages * 2 * 16) * (D + 8) * 2;
   const int merge = 16 * (D + 8) * 2 + 4 * 16 * D * 4 + 4 * 16 * 2 * 4;
   return tiles > merge ? tiles : merge;
 }

@@ -36,8 +36,12 @@ MODULES: Dict[str, List[str]] = {
 }
 HEADERS = ["common.cuh", "tc_common.cuh", "leone_static.h", "attention_tiled.cu"]
 
+# -fno-gnu-unique: statics inside inline functions and templates (the once-per-kernel set-up
+# flags, the launch mode switch) must belong to one library image each; with GNU unique
+# binding the loader would share them between this package's libraries even though each is
+# loaded with local scope.
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
-              "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
+              "-Xcompiler", "-fPIC", "-Xcompiler", "-fno-gnu-unique", "--expt-relaxed-constexpr"]
 
 
 class BuildError(RuntimeError):

@@ -223,6 +223,8 @@ class CudaOps:
         key = (name, cols, dtype)
         buf = self._scratch_bufs.get(key)
         if buf is None or buf.shape[0] < rows:
+            if buf is not None:
+                self._scratch_bufs[("retired", id(buf))] = buf     # a captured graph may still use it
             buf = torch.empty((max(rows, 64), cols), dtype=dtype, device=self.device)
             self._scratch_bufs[key] = buf
         return buf[:rows]

@@ -25,6 +25,8 @@ class FastKernels:
         self.lib = ctypes.CDLL(ensure_built("bf16"))
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self._workspace = None
+        self._retired = []
+        self.min_scratch_floats = 1 << 20
         self._counters = None
         # LEONE_NO_TENSOR_CORES=1 routes every product to the CUDA-core kernel (for fault finding)
         self.use_tensor_cores = os.environ.get("LEONE_NO_TENSOR_CORES", "0") != "1"
@@ -37,10 +39,19 @@ class FastKernels:
         return c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
 
     # -- split-K scratch ----------------------------------------------------------------
+    def _retire(self, tensor) -> None:
+        """A scratch buffer that is outgrown is kept, not freed: a captured CUDA graph may have
+        its address baked in and will go on using it."""
+        if tensor is not None:
+            self._retired.append(tensor)
+
     def _scratch(self, floats: int, counters: int):
         if self._workspace is None or self._workspace.numel() < floats:
-            self._workspace = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=self.device)
+            self._retire(self._workspace)
+            self._workspace = torch.empty(max(floats, self.min_scratch_floats), dtype=torch.float32,
+                                          device=self.device)
         if self._counters is None or self._counters.numel() < counters:
+            self._retire(self._counters)
             self._counters = torch.zeros(max(counters, 4096), dtype=torch.int32, device=self.device)
         return self._workspace, self._counters
 
@@ -119,10 +130,17 @@ class FastKernels:
 
     # -- attention ------------------------------------------------------------------------
     def decode_splits(self, n_seqs: int, n_kv: int, g: int, max_ctx: int) -> int:
-        """Splits of the key range so that about two blocks per SM are in flight."""
+        """Splits of the key range.  Two blocks fit an SM; the cost of a choice is its number of
+        rounds over those slots times the share of the keys a block walks, plus a little per
+        split for the merge.  A split keeps at least 128 keys."""
         blocks = n_seqs * n_kv * (-(-g // 16))
-        want = max(1, (3 * self.sm_count) // max(blocks, 1))
-        return int(max(1, min(want, -(-max_ctx // 128), 64)))
+        slots = 2 * self.sm_count
+        best, best_cost = 1, None
+        for s in range(1, min(32, max(1, max_ctx // 128)) + 1):
+            cost = -(-(blocks * s) // slots) / s + 0.02 * s
+            if best_cost is None or cost < best_cost - 1e-9:
+                best, best_cost = s, cost
+        return best
 
     def attention(self, ctx, qkv, out, n_q, n_kv, d, scale, window, cache) -> bool:
         if not self.use_tiled_attention or qkv.dtype != torch.bfloat16:
@@ -153,5 +171,7 @@ class FastKernels:
 
     def _attn_scratch(self, floats: int):
         if self._attn_ws is None or self._attn_ws.numel() < floats:
-            self._attn_ws = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=self.device)
+            self._retire(self._attn_ws)
+            self._attn_ws = torch.empty(max(floats, self.min_scratch_floats), dtype=torch.float32,
+                                        device=self.device)
         return self._attn_ws

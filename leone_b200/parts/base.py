@@ -105,6 +105,8 @@ class Runtime:
         key = f"{name}/{cols}/{dtype}"
         buf = self._buffers.get(key)
         if buf is None or buf.shape[0] < cap_rows:
+            if buf is not None:
+                self._buffers[f"retired/{id(buf)}"] = buf    # a captured graph may still use it
             buf = torch.empty((cap_rows, cols), dtype=dtype, device=self.device)
             self._buffers[key] = buf
         return buf[:rows]

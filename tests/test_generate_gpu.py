@@ -88,3 +88,20 @@ def test_eos_stops_a_request(folders):
     eos = free_run[3]
     got = generate(folders["A"], [prompt], 8, dtype="float32", page_tokens=4, eos_token_id=eos)
     assert got[0] == free_run[:free_run.index(eos) + 1]
+
+
+def test_a_captured_graph_survives_growth_of_the_scratch_buffers(folders):
+    """A decode graph keeps the addresses of the split scratch it was captured with.  A later,
+    larger batch outgrows that scratch; the small batch's graph must still be usable."""
+    from leone_b200 import generate
+    eng = _engine(folders["C"], "C", "bfloat16", 200)
+    eng.ops.fast.min_scratch_floats = 1            # every growth reallocates
+    small = [replay.random_tokens(331, n, 90 + n) for n in (150, 140)]
+    large = [replay.random_tokens(331, 150, 200 + i) for i in range(4)]
+    first = generate(eng, small, 6, eos_token_id=-1)
+    generate(eng, large, 6, eos_token_id=-1)       # larger batch: more scratch
+    torch.cuda.empty_cache()
+    again = generate(eng, small, 6, eos_token_id=-1)
+    torch.cuda.synchronize()
+    assert first == again
+    assert len(eng.ops.fast._retired) > 0
