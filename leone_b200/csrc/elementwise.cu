@@ -54,6 +54,69 @@ __global__ void rms_norm_kernel(const float* __restrict__ x, const int* __restri
     dst[c] = from_float<TO>(src[c] * to_float<TW>(w[c]) * inv);
 }
 
+// The same, for rows of 4*k elements up to 8192: each thread keeps its part of the row in
+// registers (float4 loads), so the row is read once.
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+  static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+  static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Vec4<__nv_bfloat16> {
+  static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<uint32_t*>(&a);
+    raw.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = raw;
+  }
+};
+
+constexpr int kNormThreads = 256;
+constexpr int kNormItems = 8;          // float4 per thread: rows up to 256 * 8 * 4 = 8192 elements
+
+template <typename TW, typename TO>
+__global__ void __launch_bounds__(kNormThreads)
+rms_norm_vec_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                    const TW* __restrict__ w, TO* __restrict__ out, int hidden, float eps) {
+  __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const float* src = x + (size_t)(rows ? rows[r] : r) * hidden;
+  const int vecs = hidden >> 2;
+  float4 v[kNormItems];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < kNormItems; ++i) {
+    const int c = threadIdx.x + i * kNormThreads;
+    if (c < vecs) {
+      v[i] = Vec4<float>::load(src + 4 * c);
+      ss = fmaf(v[i].x, v[i].x, ss);
+      ss = fmaf(v[i].y, v[i].y, ss);
+      ss = fmaf(v[i].z, v[i].z, ss);
+      ss = fmaf(v[i].w, v[i].w, ss);
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)hidden + eps);
+  TO* dst = out + (size_t)r * hidden;
+#pragma unroll
+  for (int i = 0; i < kNormItems; ++i) {
+    const int c = threadIdx.x + i * kNormThreads;
+    if (c < vecs) {
+      const float4 g = Vec4<TW>::load(w + 4 * c);
+      Vec4<TO>::store(dst + 4 * c, make_float4(v[i].x * g.x * inv, v[i].y * g.y * inv,
+                                               v[i].z * g.z * inv, v[i].w * g.w * inv));
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------
 // SwiGLU on stacked [gate | up] rows: out = gate / (1 + exp(-gate)) * up
 // (crates/leone/src/cpu.rs:903-905; ie_cuda.cu:2864-2874).
@@ -152,6 +215,95 @@ __global__ void qk_norm_rope_write_kernel(
     const T o = from_float<T>(v);
     if (is_q || is_k) row[c] = o;
     if (cache_row != nullptr) cache_row[c] = o;
+  }
+}
+
+// The same for head sizes 64, 128 and 256 in bfloat16 with a full-width rotary table: a lane
+// holds E = head_dim/32 consecutive elements, so the element's rotation partner (half a head
+// away) sits in lane ^ 16 at the same place and comes by one shuffle; loads and stores are
+// 4- to 16-byte vectors.
+template <int E, typename TW>
+__global__ void __launch_bounds__(128)
+qk_norm_rope_write_vec_kernel(
+    __nv_bfloat16* __restrict__ qkv, int n_tokens, int n_q, int n_kv, const TW* __restrict__ q_w,
+    const TW* __restrict__ k_w, float eps, const float2* __restrict__ rope, int max_positions,
+    const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+    const int* __restrict__ block_table, int table_width, int n_seqs,
+    __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool, int num_pages,
+    int page_tokens, int* status) {
+  constexpr int d = 32 * E;
+  pdl_trigger();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = n_q + 2 * n_kv;
+  const long long item = (long long)blockIdx.x * 4 + warp;
+  if (item >= (long long)n_tokens * heads) return;
+  const int t = (int)(item / heads), h = (int)(item - (long long)t * heads);
+  const bool is_q = h < n_q, is_k = !is_q && h < n_q + n_kv;
+  __nv_bfloat16* row = qkv + ((size_t)t * heads + h) * d + lane * E;
+  const int pos = positions[t];
+  float v[E];
+  {
+    const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(row);
+#pragma unroll
+    for (int i = 0; i < E / 2; ++i) {
+      const __nv_bfloat162 two = p2[i];
+      v[2 * i] = __low2float(two);
+      v[2 * i + 1] = __high2float(two);
+    }
+  }
+  const TW* w = is_q ? q_w : (is_k ? k_w : nullptr);
+  if (w != nullptr) {
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < E; ++i) ss = fmaf(v[i], v[i], ss);
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)d + eps);
+#pragma unroll
+    for (int i = 0; i < E; ++i) v[i] = v[i] * to_float<TW>(w[lane * E + i]) * inv;
+  }
+  const bool rotate = (is_q || is_k) && rope != nullptr;
+  if (rotate && (pos < 0 || pos >= max_positions)) {
+    if (lane == 0) set_status(status, kBadPosition, t, pos);
+    return;
+  }
+  __nv_bfloat16* cache_row = nullptr;
+  if (!is_q && k_pool != nullptr) {
+    const int s = seq_of_token[t];
+    if (s < 0 || s >= n_seqs) {
+      if (lane == 0) set_status(status, kBadSequence, t, s);
+      return;
+    }
+    const int blk = pos / page_tokens;
+    const int page = (pos >= 0 && blk < table_width) ? block_table[(size_t)s * table_width + blk] : -1;
+    if (page < 0 || page >= num_pages) {
+      if (lane == 0) set_status(status, kBadPage, t, page, pos);
+      return;
+    }
+    const int kvh = is_k ? h - n_q : h - n_q - n_kv;
+    __nv_bfloat16* pool = is_k ? k_pool : v_pool;
+    cache_row = pool + (((size_t)page * n_kv + kvh) * page_tokens + (pos % page_tokens)) * d + lane * E;
+  }
+  if (rotate) {
+    const bool upper = lane >= 16;                   // elements of the second half
+    const int pair0 = (lane & 15) * E;               // pair index of this lane's first element
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+      const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
+      const float2 cs = rope[(size_t)pos * (d / 2) + pair0 + i];
+      v[i] = upper ? other * cs.y + v[i] * cs.x : v[i] * cs.x - other * cs.y;
+    }
+  }
+  __nv_bfloat162 o2[E / 2];
+#pragma unroll
+  for (int i = 0; i < E / 2; ++i) o2[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  if (is_q || is_k) {
+#pragma unroll
+    for (int i = 0; i < E / 2; ++i) reinterpret_cast<__nv_bfloat162*>(row)[i] = o2[i];
+  }
+  if (cache_row != nullptr) {
+#pragma unroll
+    for (int i = 0; i < E / 2; ++i) reinterpret_cast<__nv_bfloat162*>(cache_row)[i] = o2[i];
   }
 }
 
@@ -352,9 +504,16 @@ extern "C" int leone_rms_norm(const float* x, const int* rows, const void* w, in
   if (n_out <= 0) return 0;
   if (hidden <= 0) return kRefusedSize;
   const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
-#define LAUNCH(TW, TO)                                                                       \
-  return launch_kernel(rms_norm_kernel<TW, TO>, dim3(n_out), dim3(threads), 0, stream, x, rows, \
-                       (const TW*)w, (TO*)out, hidden, eps)
+  const bool vec = (hidden % 4) == 0 && hidden >= 512 && hidden <= kNormThreads * kNormItems * 4 &&
+                   (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) == 0;
+#define LAUNCH(TW, TO)                                                                           \
+  {                                                                                              \
+    if (vec)                                                                                     \
+      return launch_kernel(rms_norm_vec_kernel<TW, TO>, dim3(n_out), dim3(kNormThreads), 0, stream, x, \
+                           rows, (const TW*)w, (TO*)out, hidden, eps);                            \
+    return launch_kernel(rms_norm_kernel<TW, TO>, dim3(n_out), dim3(threads), 0, stream, x, rows, \
+                         (const TW*)w, (TO*)out, hidden, eps);                                    \
+  }
   if (w_dtype == 0 && out_dtype == 0) LAUNCH(float, float);
   if (w_dtype == 0 && out_dtype == 1) LAUNCH(float, __nv_bfloat16);
   if (w_dtype == 1 && out_dtype == 0) LAUNCH(__nv_bfloat16, float);
@@ -392,6 +551,25 @@ extern "C" int leone_qk_norm_rope_write(
   const long long items = (long long)n_tokens * (n_q + 2 * n_kv);
   const int blocks = (int)((items + warps - 1) / warps);
   const size_t smem = (size_t)warps * d * sizeof(float);
+  if (dtype == 1 && (d == 64 || d == 128 || d == 256) && (rope == nullptr || rotary_dim == d) &&
+      (q_w == nullptr) == (k_w == nullptr)) {
+#define LAUNCH_VEC(E, TW)                                                                          \
+  return launch_kernel(qk_norm_rope_write_vec_kernel<E, TW>, dim3(blocks), dim3(128), 0, stream,   \
+                       (__nv_bfloat16*)qkv, n_tokens, n_q, n_kv, (const TW*)q_w, (const TW*)k_w, eps, \
+                       (const float2*)rope, max_positions, positions, seq_of_token, block_table,  \
+                       table_width, n_seqs, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool,        \
+                       num_pages, page_tokens, status)
+    if (w_dtype == 0) {
+      if (d == 64) LAUNCH_VEC(2, float);
+      if (d == 128) LAUNCH_VEC(4, float);
+      LAUNCH_VEC(8, float);
+    } else if (w_dtype == 1) {
+      if (d == 64) LAUNCH_VEC(2, __nv_bfloat16);
+      if (d == 128) LAUNCH_VEC(4, __nv_bfloat16);
+      LAUNCH_VEC(8, __nv_bfloat16);
+    }
+#undef LAUNCH_VEC
+  }
 #define LAUNCH(T, TW)                                                                              \
   return launch_kernel(qk_norm_rope_write_kernel<T, TW>, dim3(blocks), dim3(warps * 32), smem, stream, \
                        (T*)qkv, n_tokens, n_q, n_kv, d, (const TW*)q_w, (const TW*)k_w, eps,          \

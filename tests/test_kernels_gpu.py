@@ -242,7 +242,8 @@ def _ref_norm_rope(x, w, eps, positions, theta, rd):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("n_q,n_kv,d,pt,theta,eps", [(5, 1, 48, 16, 5e4, 3e-6), (6, 3, 32, 8, 1e6, 1e-5),
-                                                     (8, 2, 128, 16, 1e6, 1e-6), (3, 3, 80, 4, 1e4, 1e-6)])
+                                                     (8, 2, 128, 16, 1e6, 1e-6), (3, 3, 80, 4, 1e4, 1e-6),
+                                                     (4, 2, 64, 16, 1e4, 1e-6), (2, 1, 256, 8, 1e6, 1e-5)])
 def test_qk_norm_rope_write(ops32, dtype, n_q, n_kv, d, pt, theta, eps):
     seq_lens = [11, 3, 25]
     starts = [4, 0, 20]                      # tokens of this step: positions start..len-1
