@@ -57,7 +57,7 @@ def round_bf16(t):
 # ---------------------------------------------------------------------------------------
 def embedding(table, ids):
     """h[t,:] = E[id_t,:], no scale (crates/leone/src/cpu.rs:1243-1265)."""
-    return table[torch.as_tensor(ids, dtype=torch.long)]
+    return table[torch.as_tensor(ids, dtype=torch.long, device=table.device)]
 
 
 def rms_norm(x, weight, eps):
@@ -78,8 +78,9 @@ def rope_half_split(x, positions, theta, rotary_dim=None):
     d = x.shape[-1]
     rd = d if rotary_dim is None else rotary_dim
     half = rd // 2
-    inv = torch.tensor([float(theta) ** (-2.0 * i / rd) for i in range(half)], dtype=torch.float64)
-    ang = torch.as_tensor(positions, dtype=torch.float64)[:, None] * inv[None, :]
+    inv = torch.tensor([float(theta) ** (-2.0 * i / rd) for i in range(half)], dtype=torch.float64,
+                       device=x.device)
+    ang = torch.as_tensor(positions, dtype=torch.float64, device=x.device)[:, None] * inv[None, :]
     cos, sin = torch.cos(ang)[:, None, :].to(x.dtype), torch.sin(ang)[:, None, :].to(x.dtype)
     out = x.clone()
     a, b = x[..., :half], x[..., half:rd]
