@@ -52,7 +52,17 @@ struct GemmParams {
   float* workspace;
   int* counters;
   int* status;
+  long long* trace;  // optional: 8 nanosecond time stamps per block (see leone_gemm_tc_set_trace)
 };
+
+__device__ __forceinline__ long long global_ns() {
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)::"memory");
+  return t;
+}
+__device__ __forceinline__ void stamp(const GemmParams& p, int slot) {
+  if (p.trace != nullptr) p.trace[(size_t)blockIdx.x * 8 + slot] = global_ns();
+}
 
 // Work units in launch order: the unsplit tiles first, then `splits` units per remaining tile.
 // Splitting only the tiles of the last, partly filled round keeps every SM busy without
@@ -87,6 +97,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __shared__ int last_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) stamp(p, 7);                       // first instruction of the block
   // tiles along the tokens (m) and along the weight rows (n); the token tile index runs
   // fastest so that blocks working at the same time share weight tiles through L2
   constexpr int kTokRows = kSwap ? BN : kTileW, kWRows = kSwap ? kTileW : BN;
@@ -116,6 +127,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const uint32_t tmem_base = tmem_holder;
   volatile int* giveup = &gave_up;
   pdl_trigger();
+  if (threadIdx.x == 0) stamp(p, 0);                       // set-up done
 
   if (warp == 0) {
     // ---------------- producer ----------------
@@ -153,7 +165,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
         if (pass == 0) {
           early = filled;
+          stamp(p, 1);                                     // early weight requests issued
           pdl_wait();
+          stamp(p, 2);                                     // predecessor complete
         }
       }
     }
@@ -177,6 +191,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(full0 + 8 * stage, phase, giveup)) { ok = false; break; }
           tc_fence_after();
+          if (it == 0 && kb == kb0) stamp(p, 3);           // first stage complete in shared memory
           const uint32_t a_addr = tiles_base + stage * Cfg::kStageBytes;
           const uint32_t b_addr = a_addr + kTileW * kTileK * 2;
           const uint64_t a_desc = smem_desc_sw128(a_addr), b_desc = smem_desc_sw128(b_addr);
@@ -190,6 +205,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
         if (!ok) break;
         umma_commit(acc_full0 + 8 * buf);
+        stamp(p, 4);                                       // last MMA of the (latest) unit issued
       }
     }
   } else {
@@ -206,6 +222,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       const uint32_t acc_phase = (it >> 1) & 1;
       if (!mbar_wait(acc_full0 + 8 * buf, acc_phase, giveup)) break;
       tc_fence_after();
+      if (ep_tid == 0) stamp(p, 5);                        // accumulator of the (latest) unit complete
       const int row_local = quarter * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
       if (!kSwap) {
@@ -346,14 +363,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
               }
             }
           } else if (n < p.N) {
+            if (p.epilogue == 2) {
+              // The residual may be the output itself, so the compiler must keep every load
+              // behind the store before it: fetch all sixteen first, then store.
+              float r[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const int m = m0 + c + j;
+                r[j] = m < p.M ? p.residual[(size_t)m * p.ldc + n] : 0.f;
+              }
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] += r[j];
+            }
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int m = m0 + c + j;
               if (m < p.M) {
                 const size_t o = (size_t)m * p.ldc + n;
                 if (p.epilogue == 0) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(v[j]);
-                else if (p.epilogue == 1) ((float*)p.out)[o] = v[j];
-                else ((float*)p.out)[o] = v[j] + p.residual[o];
+                else ((float*)p.out)[o] = v[j];
               }
             }
           }
@@ -370,6 +398,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   // ---------------- teardown ----------------
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) stamp(p, 6);                       // block done
   if (gave_up) {
     if (threadIdx.x == 0) set_status(p.status, kWaitTimeout, blockIdx.x, 0);
     // let tile copies that are still in flight land before the block's memory goes away
@@ -411,6 +440,18 @@ using namespace leone::tc;
 
 // Turns programmatic dependent launch on or off for the kernels of this library.
 extern "C" void leone_bf16_set_pdl(int enabled) { pdl_flag() = enabled ? 1 : 0; }
+
+// Phase trace for tuning: while `buffer` is not null every block of a product writes eight
+// %globaltimer stamps (ns) at [block * 8 + i]: 0 set-up done, 1 early weight requests issued,
+// 2 predecessor complete, 3 first stage landed, 4 last MMA issued, 5 accumulator complete,
+// 6 block done, 7 first instruction.  Every launch writes at `buffer` and then moves it on by
+// `stride` int64 (0: all launches share one area), so consecutive launches can be told apart.
+static long long* g_gemm_trace = nullptr;
+static long long g_gemm_trace_stride = 0;
+extern "C" void leone_gemm_tc_set_trace(long long* buffer, long long stride) {
+  g_gemm_trace = buffer;
+  g_gemm_trace_stride = stride;
+}
 
 // Token-tile width the kernel will use for M tokens.
 extern "C" int leone_gemm_tc_tile(int m) {
@@ -464,7 +505,9 @@ extern "C" int leone_gemm_tc(const void* x, const void* w, void* out, const floa
   if (r != 0) return r;
   r = make_tensor_map_2d(&mx, x, (uint64_t)m, (uint64_t)k, (uint64_t)ldx, swap ? (uint32_t)bn : kTileW);
   if (r != 0) return r;
-  GemmParams p{out, residual, m, n, k, ldc, epilogue, splits, full_tiles, workspace, counters, status};
+  GemmParams p{out, residual, m, n, k, ldc, epilogue, splits, full_tiles, workspace, counters, status,
+               g_gemm_trace};
+  if (g_gemm_trace != nullptr) g_gemm_trace += g_gemm_trace_stride;
   if (!swap) return launch_gemm<256, false>(mw, mx, p, sm_count, stream);
   switch (bn) {
     case 16: return launch_gemm<16, true>(mw, mx, p, sm_count, stream);

@@ -55,7 +55,7 @@ def _time(fn, reps: int, warmup: int, flush=None, per_graph: int = 1) -> float:
     return times[len(times) // 2]
 
 
-def bench_gemm(ops, m, n, k, splits, epilogue, reps, warmup, flush):
+def bench_gemm(ops, m, n, k, splits, epilogue, reps, warmup, flush, trace=False):
     fast = ops.fast
     x = torch.randn((m, k), device=DEV).to(torch.bfloat16)
     # several copies of the weight so successive launches do not hit L2
@@ -77,10 +77,51 @@ def bench_gemm(ops, m, n, k, splits, epilogue, reps, warmup, flush):
         fast._gemm(x, w, out, epilogue, res, n, splits=splits, full_tiles=full_tiles)
 
     ms = _time(run, reps, warmup, flush, per_graph=copies)
+    if trace:
+        _print_trace(ops, run, copies)
     bytes_ = n * k * 2 + m * k * 2 + out.numel() * out.element_size()
     flops = 2.0 * m * n * k
     return dict(kernel="gemm_tc", m=m, n=n, k=k, splits=splits, full_tiles=full_tiles, epilogue=epilogue, us=ms * 1e3,
                 gbs=bytes_ / ms / 1e6, tflops=flops / ms / 1e9)
+
+
+def _print_trace(ops, run, copies):
+    """Phase stamps of launches replayed back to back from a CUDA graph, the way the engine
+    runs them (see leone_gemm_tc_set_trace).  Times are relative to the first instruction of
+    the first block of the launch before the last; both launches are shown."""
+    import ctypes
+    n = max(copies, 4)
+    stride = 600 * 8
+    buf = torch.zeros((n, 600, 8), dtype=torch.int64, device=DEV)
+    ops.fast.lib.leone_gemm_tc_set_trace(ctypes.c_void_p(buf.data_ptr()), ctypes.c_longlong(stride))
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(n):
+                run()
+    torch.cuda.current_stream().wait_stream(side)
+    ops.fast.lib.leone_gemm_tc_set_trace(ctypes.c_void_p(0), ctypes.c_longlong(0))
+    graph.replay()
+    torch.cuda.synchronize()
+    buf.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    names = ["setup done", "early weights issued", "predecessor done", "first stage landed",
+             "last mma issued", "accumulator done", "block done", "first instruction"]
+    t0 = None
+    for launch in (n - 2, n - 1):
+        t = buf[launch]
+        t = t[t[:, 6] > 0].cpu().double()
+        if t.numel() == 0:
+            continue
+        if t0 is None:
+            t0 = t[:, 7].min()
+        print(f"  launch {launch} ({t.shape[0]} blocks)")
+        for i in (7, 0, 1, 2, 3, 4, 5, 6):
+            col = (t[:, i] - t0) / 1e3
+            print(f"    {names[i]:22s} min {col.min():7.2f}  median {col.median():7.2f}  max {col.max():7.2f} us")
 
 
 def bench_decode_attention(ops, batch, context, n_q, n_kv, d, page_tokens, reps, warmup, flush):
@@ -149,6 +190,7 @@ def main(argv=None) -> int:
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--flush", action="store_true", help="write a 256 MB buffer between timed launches")
+    ap.add_argument("--trace", action="store_true", help="gemm: print the kernel's phase time stamps")
     args = ap.parse_args(argv)
     from .ops.cuda import CudaOps
     ops = CudaOps(DEV, torch.bfloat16)
@@ -156,7 +198,8 @@ def main(argv=None) -> int:
     flush = torch.zeros(64 << 20, device=DEV) if args.flush else None
     rows = []
     if args.what == "gemm":
-        rows.append(bench_gemm(ops, args.m, args.n, args.k, args.splits, args.epilogue, args.reps, args.warmup, flush))
+        rows.append(bench_gemm(ops, args.m, args.n, args.k, args.splits, args.epilogue, args.reps, args.warmup, flush,
+                               args.trace))
     elif args.what == "layer-shapes":
         h, inter, qkv = 4096, 12288, (args.heads + 2 * args.kv_heads) * args.head_dim
         for name, n, k, epi in (("qkv", qkv, h, 0), ("o_proj", h, args.heads * args.head_dim, 2),
