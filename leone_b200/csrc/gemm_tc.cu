@@ -76,9 +76,59 @@ __device__ __forceinline__ Unit unit_of(int u, const GemmParams& p) {
   return Unit{p.full_tiles + r / p.splits, r % p.splits, p.splits};
 }
 
+// Swapped orientation: the thread that owns weight row n finishes NC token columns
+// m0 + c .. m0 + c + NC - 1 whose sums are in v (r: the residual values, fetched by the caller
+// before anything is stored, because the residual may be the output itself).
+template <int NC>
+__device__ __forceinline__ void finish_swapped(const GemmParams& p, float (&v)[NC], const float (&r)[NC],
+                                               int n, int m0, int c, int lane) {
+  if (p.epilogue == 3) {
+    // rows come in groups of 32: 16 gate rows then their 16 up rows
+    const int col = (n >> 5) * 16 + (lane & 15);
+#pragma unroll
+    for (int j = 0; j < NC; ++j) {
+      const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
+      const int m = m0 + c + j;
+      if (lane < 16 && n < p.N && m < p.M) {
+        const float g = v[j], u = other;
+        ((__nv_bfloat16*)p.out)[(size_t)m * p.ldc + col] = __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
+      }
+    }
+  } else if (n < p.N) {
+    if (p.epilogue == 2) {
+#pragma unroll
+      for (int j = 0; j < NC; ++j) v[j] += r[j];
+    }
+#pragma unroll
+    for (int j = 0; j < NC; ++j) {
+      const int m = m0 + c + j;
+      if (m < p.M) {
+        const size_t o = (size_t)m * p.ldc + n;
+        if (p.epilogue == 0) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(v[j]);
+        else ((float*)p.out)[o] = v[j];
+      }
+    }
+  }
+}
+template <int NC>
+__device__ __forceinline__ void fetch_residual(const GemmParams& p, float (&r)[NC], int n, int m0, int c) {
+  if (p.epilogue == 2 && n < p.N) {
+#pragma unroll
+    for (int j = 0; j < NC; ++j) {
+      const int m = m0 + c + j;
+      r[j] = m < p.M ? p.residual[(size_t)m * p.ldc + n] : 0.f;
+    }
+  }
+}
+
 // kSwap: weights on the MMA's M side (tile 128), tokens on its N side (tile BN).
 // !kSwap: tokens on the M side (tile 128), weights on the N side (tile BN); no split-K.
-template <int BN, bool kSwap>
+// kCluster (swapped only): the `splits` blocks of a tile form a thread-block cluster, one unit
+// per block; every block leaves its fp32 partial tile in its own shared memory, then the tile's
+// rows are dealt to the blocks, each of which adds its rows' partials in rank order through
+// distributed shared memory and runs the epilogue on them.  No workspace, no counters, no
+// round trip through global memory.
+template <int BN, bool kSwap, bool kCluster>
 __global__ void __launch_bounds__(kGemmThreads, GemmCfg<BN>::kBlocksPerSm)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                const GemmParams p) {
@@ -306,6 +356,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
       const int n = n_tile * kTileW + row_local;
       const int m0 = m_tile * BN;
+      if constexpr (kCluster) {
+        // this block's partial tile goes to its own shared memory, [token column][weight row];
+        // the stages are free: the accumulator is complete, so every MMA has read its operands
+        static_assert(kStages * Cfg::kStageBytes >= BN * kTileW * 4, "partial tile must fit in the stages");
+        float* part = reinterpret_cast<float*>(aligned);
+        for (int c = 0; c < BN; c += 16) {
+          float v[16];
+          tmem_ld16(taddr + c, v);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) part[(c + j) * kTileW + row_local] = v[j];
+        }
+        break;                                           // one unit per block in this mode
+      }
       bool do_epilogue = true;
       const int split_tile = tile - p.full_tiles;        // index among the split tiles
       if (nsplit > 1) {
@@ -338,53 +401,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const float* ws_tile = nsplit > 1 ? p.workspace + (size_t)split_tile * nsplit * (BN * kTileW) : nullptr;
         for (int c = 0; c < BN; c += 16) {
           float v[16];
+          float r[16];
+          fetch_residual<16>(p, r, n, m0, c);
           if (nsplit > 1) {
+            // Partial sums are added in split order, four splits' loads in flight at a time:
+            // one wait per four splits instead of one per split.
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] = 0.f;
-            for (int s = 0; s < nsplit; ++s) {
-              const float* src = ws_tile + (size_t)s * (BN * kTileW);
+            for (int s0 = 0; s0 < nsplit; s0 += 4) {
+              float t[4][16];
 #pragma unroll
-              for (int j = 0; j < 16; ++j) v[j] += __ldcg(src + (c + j) * kTileW + row_local);
+              for (int u = 0; u < 4; ++u) {
+                if (s0 + u < nsplit) {
+                  const float* src = ws_tile + (size_t)(s0 + u) * (BN * kTileW) + c * kTileW + row_local;
+#pragma unroll
+                  for (int j = 0; j < 16; ++j) t[u][j] = __ldcg(src + j * kTileW);
+                }
+              }
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                if (s0 + u < nsplit) {
+#pragma unroll
+                  for (int j = 0; j < 16; ++j) v[j] += t[u][j];
+                }
+              }
             }
           } else {
             tmem_ld16(taddr + c, v);
           }
-          if (p.epilogue == 3) {
-            // rows come in groups of 32: 16 gate rows then their 16 up rows
-            const int col = (n >> 5) * 16 + (lane & 15);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
-              const int m = m0 + c + j;
-              if (lane < 16 && n < p.N && m < p.M) {
-                const float g = v[j], u = other;
-                ((__nv_bfloat16*)p.out)[(size_t)m * p.ldc + col] =
-                    __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
-              }
-            }
-          } else if (n < p.N) {
-            if (p.epilogue == 2) {
-              // The residual may be the output itself, so the compiler must keep every load
-              // behind the store before it: fetch all sixteen first, then store.
-              float r[16];
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const int m = m0 + c + j;
-                r[j] = m < p.M ? p.residual[(size_t)m * p.ldc + n] : 0.f;
-              }
-#pragma unroll
-              for (int j = 0; j < 16; ++j) v[j] += r[j];
-            }
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int m = m0 + c + j;
-              if (m < p.M) {
-                const size_t o = (size_t)m * p.ldc + n;
-                if (p.epilogue == 0) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(v[j]);
-                else ((float*)p.out)[o] = v[j];
-              }
-            }
-          }
+          finish_swapped<16>(p, v, r, n, m0, c, lane);
         }
       }
       if (nsplit == 1) {
@@ -393,6 +438,57 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
       }
     }
+  }
+
+  if constexpr (kCluster) {
+    // Every thread of every block of the cluster comes here (all loops above are bounded).
+    // The tile's 128 weight rows are four chunks of 32; chunk ch is summed and finished by the
+    // block of rank ch % splits, so the sums and the epilogue are spread over the cluster.
+    // In a chunk, lane = row and each epilogue warp owns a quarter of the token columns.
+    __syncwarp();
+    cluster_sync_all();                                  // all partial tiles are in place
+    if (warp >= 2 && blockIdx.x < total) {
+      const Unit un = unit_of(blockIdx.x, p);
+      const int m_tile = un.tile % m_tiles, n_tile = un.tile / m_tiles;
+      const int m0 = m_tile * BN;
+      constexpr int kColsPerWarp = BN / 4;
+      constexpr int NC = kColsPerWarp < 16 ? kColsPerWarp : 16;
+      const int rank = (int)cluster_ctarank();
+      for (int ch = rank; ch < kTileW / 32; ch += un.nsplit) {
+        const int row_local = ch * 32 + lane;
+        const int n = n_tile * kTileW + row_local;
+        const uint32_t mine = tiles_base + row_local * 4;
+        for (int c = (warp & 3) * kColsPerWarp; c < (warp & 3) * kColsPerWarp + kColsPerWarp; c += NC) {
+          float v[NC];
+          float r[NC];
+          fetch_residual<NC>(p, r, n, m0, c);
+#pragma unroll
+          for (int j = 0; j < NC; ++j) v[j] = 0.f;
+          constexpr int kBatch = NC <= 8 ? 8 : 4;        // ranks whose loads are in flight together
+          for (int s0 = 0; s0 < un.nsplit; s0 += kBatch) {
+            float t[kBatch][NC];
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+              if (s0 + u < un.nsplit) {
+                const uint32_t src = cluster_map(mine, s0 + u) + c * kTileW * 4;
+#pragma unroll
+                for (int j = 0; j < NC; ++j) t[u][j] = cluster_ld_f32(src + j * kTileW * 4);
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {           // rank order
+              if (s0 + u < un.nsplit) {
+#pragma unroll
+                for (int j = 0; j < NC; ++j) v[j] += t[u][j];
+              }
+            }
+          }
+          finish_swapped<NC>(p, v, r, n, m0, c, lane);
+        }
+      }
+    }
+    __syncwarp();
+    cluster_sync_all();                                  // the partial tiles may go away
   }
 
   // ---------------- teardown ----------------
@@ -412,13 +508,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   }
 }
 
-template <int BN, bool kSwap>
+template <int BN, bool kSwap, bool kCluster = false>
 int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, int sm_count,
                 cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, kSwap>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, kSwap, kCluster>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
     if (e != cudaSuccess) return (int)e;
     configured = true;
@@ -428,8 +524,38 @@ int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& 
   const long long total = p.full_tiles + ((long long)n_tiles * m_tiles - p.full_tiles) * p.splits;
   const long long slots = (long long)sm_count * Cfg::kBlocksPerSm;
   const int grid = (int)(total < slots ? total : slots);
-  return launch_kernel(gemm_tc_kernel<BN, kSwap>, dim3(grid), dim3(kGemmThreads), Cfg::kSmemBytes, stream,
-                       mw, mx, p);
+  if constexpr (kCluster) {
+    if (total > slots) return kRefusedSize;              // one unit per block, one round
+    return launch_kernel_cluster(gemm_tc_kernel<BN, kSwap, true>, dim3((unsigned)total), dim3(kGemmThreads),
+                                 Cfg::kSmemBytes, stream, p.splits, mw, mx, p);
+  }
+  return launch_kernel(gemm_tc_kernel<BN, kSwap, kCluster>, dim3(grid), dim3(kGemmThreads), Cfg::kSmemBytes,
+                       stream, mw, mx, p);
+}
+
+// How many clusters of `splits` blocks of the swapped kernel for token tile BN can be resident
+// at once (0: this cluster size cannot be launched).
+template <int BN>
+int cluster_capacity(int splits) {
+  using Cfg = GemmCfg<BN>;
+  cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, true, true>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+  if (e != cudaSuccess) { cudaGetLastError(); return 0; }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(splits * 64);
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = splits;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int clusters = 0;
+  e = cudaOccupancyMaxActiveClusters(&clusters, gemm_tc_kernel<BN, true, true>, &cfg);
+  if (e != cudaSuccess) { cudaGetLastError(); return 0; }
+  return clusters;
 }
 
 }  // namespace tc
@@ -474,16 +600,32 @@ extern "C" void leone_gemm_tc_scratch(int m, int split_tiles, int splits, long l
   *counters = splits > 1 ? split_tiles : 0;
 }
 
+// Clusters of `splits` blocks that can be resident at once for M tokens (0: not launchable).
+extern "C" int leone_gemm_tc_cluster_capacity(int m, int splits) {
+  if (m > 256 || splits < 2 || splits > 8) return 0;
+  switch (leone_gemm_tc_tile(m)) {
+    case 16: return cluster_capacity<16>(splits);
+    case 32: return cluster_capacity<32>(splits);
+    case 64: return cluster_capacity<64>(splits);
+    case 128: return cluster_capacity<128>(splits);
+    default: return cluster_capacity<256>(splits);
+  }
+}
+
 // x: [m, k] bf16 (row stride ldx), w: [n, k] bf16 (row stride ldw), out: [m, n] (row stride ldc).
 // epilogue 0: bf16 out; 1: fp32 out; 2: fp32 out = acc + residual (same layout as out);
 // 3: w holds interleaved gate/up rows, out is bf16 [m, n/2] = silu(gate) * up.
 // The first `full_tiles` tiles (in the kernel's tile order) are computed whole; the others have K
 // split `splits` ways.  splits > 1 needs `workspace` (fp32) and zeroed `counters` of the sizes
 // leone_gemm_tc_scratch gives for (tiles - full_tiles).  More than 256 tokens are never split.
+// cluster != 0: the splits of a tile form a thread-block cluster and are summed through
+// distributed shared memory (needs full_tiles == 0, 2 <= splits <= 8, at most 256 tokens, and
+// tiles * splits blocks resident at once: see leone_gemm_tc_cluster_capacity); workspace and
+// counters are not used.
 extern "C" int leone_gemm_tc(const void* x, const void* w, void* out, const float* residual, int m,
                              int n, int k, int ldx, int ldw, int ldc, int epilogue, int splits,
                              int full_tiles, float* workspace, int* counters, int* status,
-                             int sm_count, cudaStream_t stream) {
+                             int sm_count, int cluster, cudaStream_t stream) {
   if (m <= 0 || n <= 0) return 0;
   if (k <= 0 || (k % 8) != 0 || (ldx % 8) != 0 || (ldw % 8) != 0) return kRefusedAlignment;
   if (epilogue < 0 || epilogue > 3 || splits < 1 || sm_count < 1) return kRefusedSize;
@@ -494,7 +636,9 @@ extern "C" int leone_gemm_tc(const void* x, const void* w, void* out, const floa
   if (splits > k_blocks) splits = k_blocks;
   // every split must own at least one k-block
   while (splits > 1 && (splits - 1) * ((k_blocks + splits - 1) / splits) >= k_blocks) --splits;
-  if (splits > 1 && (workspace == nullptr || counters == nullptr)) return kRefusedSize;
+  if (splits == 1) cluster = 0;
+  if (cluster && (full_tiles != 0 || splits > 8 || m > 256)) return kRefusedSize;
+  if (splits > 1 && !cluster && (workspace == nullptr || counters == nullptr)) return kRefusedSize;
   const int tiles = leone_gemm_tc_tiles(m, n);
   if (splits == 1) full_tiles = tiles;
   if (full_tiles < 0 || full_tiles > tiles) return kRefusedSize;
@@ -509,6 +653,15 @@ extern "C" int leone_gemm_tc(const void* x, const void* w, void* out, const floa
                g_gemm_trace};
   if (g_gemm_trace != nullptr) g_gemm_trace += g_gemm_trace_stride;
   if (!swap) return launch_gemm<256, false>(mw, mx, p, sm_count, stream);
+  if (cluster) {
+    switch (bn) {
+      case 16: return launch_gemm<16, true, true>(mw, mx, p, sm_count, stream);
+      case 32: return launch_gemm<32, true, true>(mw, mx, p, sm_count, stream);
+      case 64: return launch_gemm<64, true, true>(mw, mx, p, sm_count, stream);
+      case 128: return launch_gemm<128, true, true>(mw, mx, p, sm_count, stream);
+      default: return launch_gemm<256, true, true>(mw, mx, p, sm_count, stream);
+    }
+  }
   switch (bn) {
     case 16: return launch_gemm<16, true>(mw, mx, p, sm_count, stream);
     case 32: return launch_gemm<32, true>(mw, mx, p, sm_count, stream);

@@ -55,7 +55,7 @@ def _time(fn, reps: int, warmup: int, flush=None, per_graph: int = 1) -> float:
     return times[len(times) // 2]
 
 
-def bench_gemm(ops, m, n, k, splits, epilogue, reps, warmup, flush, trace=False):
+def bench_gemm(ops, m, n, k, splits, epilogue, reps, warmup, flush, trace=False, cluster=False):
     fast = ops.fast
     x = torch.randn((m, k), device=DEV).to(torch.bfloat16)
     # several copies of the weight so successive launches do not hit L2
@@ -69,19 +69,19 @@ def bench_gemm(ops, m, n, k, splits, epilogue, reps, warmup, flush, trace=False)
     state = {"i": 0}
     full_tiles = 0
     if splits is None:
-        splits, full_tiles = fast.choose_splits(m, n, k)
+        splits, full_tiles, cluster = fast.choose_splits(m, n, k)
 
     def run():
         w = ws[state["i"] % copies]
         state["i"] += 1
-        fast._gemm(x, w, out, epilogue, res, n, splits=splits, full_tiles=full_tiles)
+        fast._gemm(x, w, out, epilogue, res, n, splits=splits, full_tiles=full_tiles, cluster=cluster)
 
     ms = _time(run, reps, warmup, flush, per_graph=copies)
     if trace:
         _print_trace(ops, run, copies)
     bytes_ = n * k * 2 + m * k * 2 + out.numel() * out.element_size()
     flops = 2.0 * m * n * k
-    return dict(kernel="gemm_tc", m=m, n=n, k=k, splits=splits, full_tiles=full_tiles, epilogue=epilogue, us=ms * 1e3,
+    return dict(kernel="gemm_tc", m=m, n=n, k=k, splits=splits, full_tiles=full_tiles, cluster=bool(cluster), epilogue=epilogue, us=ms * 1e3,
                 gbs=bytes_ / ms / 1e6, tflops=flops / ms / 1e9)
 
 
@@ -191,6 +191,8 @@ def main(argv=None) -> int:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--flush", action="store_true", help="write a 256 MB buffer between timed launches")
     ap.add_argument("--trace", action="store_true", help="gemm: print the kernel's phase time stamps")
+    ap.add_argument("--cluster", action="store_true",
+                    help="gemm with --splits: sum the splits inside thread-block clusters")
     args = ap.parse_args(argv)
     from .ops.cuda import CudaOps
     ops = CudaOps(DEV, torch.bfloat16)
@@ -199,7 +201,7 @@ def main(argv=None) -> int:
     rows = []
     if args.what == "gemm":
         rows.append(bench_gemm(ops, args.m, args.n, args.k, args.splits, args.epilogue, args.reps, args.warmup, flush,
-                               args.trace))
+                               args.trace, args.cluster))
     elif args.what == "layer-shapes":
         h, inter, qkv = 4096, 12288, (args.heads + 2 * args.kv_heads) * args.head_dim
         for name, n, k, epi in (("qkv", qkv, h, 0), ("o_proj", h, args.heads * args.head_dim, 2),

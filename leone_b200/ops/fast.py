@@ -30,6 +30,17 @@ class FastKernels:
         self._counters = None
         # LEONE_NO_TENSOR_CORES=1 routes every product to the CUDA-core kernel (for fault finding)
         self.use_tensor_cores = os.environ.get("LEONE_NO_TENSOR_CORES", "0") != "1"
+        # LEONE_NO_CLUSTERS=1 sums split-K partial tiles through a workspace instead of inside clusters
+        self.use_clusters = os.environ.get("LEONE_NO_CLUSTERS", "0") != "1"
+        self._cluster_capacity = {}
+        self.max_cluster = int(os.environ.get("LEONE_MAX_CLUSTER", "8"))
+        # tuning aid: LEONE_GEMM_SPLITS="6144x4096:4,4096x12288:c8" forces the split of [n x k]
+        # products at decode sizes ("c": summed inside a cluster)
+        self.split_override = {}
+        for item in filter(None, os.environ.get("LEONE_GEMM_SPLITS", "").split(",")):
+            shape, _, how = item.partition(":")
+            n_, _, k_ = shape.partition("x")
+            self.split_override[(int(n_), int(k_))] = (int(how.lstrip("c")), how.startswith("c"))
         self.status = None
         self._attn_ws = None
         self.use_tiled_attention = os.environ.get("LEONE_NO_TILED_ATTENTION", "0") != "1"
@@ -55,26 +66,46 @@ class FastKernels:
             self._counters = torch.zeros(max(counters, 4096), dtype=torch.int32, device=self.device)
         return self._workspace, self._counters
 
-    def choose_splits(self, m: int, n: int, k: int):
-        """How to split K: ``(splits, full_tiles)``; tiles before ``full_tiles`` are not split.
+    def cluster_capacity(self, m: int, splits: int) -> int:
+        """Clusters of ``splits`` blocks of the GEMM for ``m`` tokens that fit on the device at once."""
+        key = (int(self.lib.leone_gemm_tc_tile(m)) if m <= 256 else 0, splits)
+        if key not in self._cluster_capacity:
+            self._cluster_capacity[key] = int(self.lib.leone_gemm_tc_cluster_capacity(m, splits))
+        return self._cluster_capacity[key]
 
-        Fewer tiles than SMs: every tile is split so that one round of units fills the SMs.
-        More tiles than SMs: only the tiles of the last, partly filled round are split, so
-        that round costs a fraction of a full one.  A split costs a partial-sum round trip, so
-        a unit keeps at least 12 k-blocks.  Prompt-sized M is never split."""
+    def choose_splits(self, m: int, n: int, k: int):
+        """How to split K: ``(splits, full_tiles, cluster)``; tiles before ``full_tiles`` are not split.
+
+        Fewer tiles than SMs: every tile is split, and its splits form a thread-block cluster that
+        sums the partial tiles through distributed shared memory.  The most splits (up to 8) win
+        that keep the blocks within two thirds of the block slots: more blocks keep more bytes in
+        flight, but the last third is what lets the next kernels' blocks start early and fetch
+        their first weights while this product is still running (measured on the decode step:
+        filling every slot was slower than leaving the product unsplit).  More tiles than SMs:
+        only a small remainder of tiles (under a quarter of the SMs) is split, through a
+        workspace, so that those few tiles do not cost a round of their own; such a unit keeps
+        at least 12 k-blocks.  Prompt-sized M is never split."""
         tiles = int(self.lib.leone_gemm_tc_tiles(m, n))
         if m > 256:
-            return 1, tiles
+            return 1, tiles, False
         k_blocks = -(-k // 64)
         sms = self.sm_count
+        if (n, k) in self.split_override:
+            s, cluster = self.split_override[(n, k)]
+            return (s, 0, cluster) if s > 1 else (1, tiles, False)
         if tiles < sms:
+            slots = sms * (2 if m <= 64 else 1)
+            if self.use_clusters:
+                for s in (8, 7, 6, 5, 4, 3, 2):
+                    if tiles * s <= slots * 2 // 3 and k_blocks // s >= 4 and s <= self.max_cluster and self.cluster_capacity(m, s) > 0:
+                        return s, 0, True
             s = max(1, min(sms // tiles, k_blocks // 12, 8))
-            return (s, 0) if s > 1 else (1, tiles)
+            return (s, 0, False) if s > 1 else (1, tiles, False)
         rem = tiles % sms
-        if rem == 0 or rem * 4 > sms * 3:
-            return 1, tiles
+        if rem == 0 or rem * 4 > sms:
+            return 1, tiles, False
         s = min(sms // rem, k_blocks // 12, 8)
-        return (s, tiles - rem) if s > 1 else (1, tiles)
+        return (s, tiles - rem, False) if s > 1 else (1, tiles, False)
 
     def _tc_ok(self, x, w, out) -> bool:
         if not self.use_tensor_cores or x.dtype != torch.bfloat16:
@@ -83,14 +114,15 @@ class FastKernels:
         return (k % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
                 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
-    def _gemm(self, x, w, out, epilogue, residual, n_rows, splits=None, full_tiles=0) -> bool:
+    def _gemm(self, x, w, out, epilogue, residual, n_rows, splits=None, full_tiles=0, cluster=False) -> bool:
         """``splits=None`` lets :meth:`choose_splits` decide; otherwise tiles from
-        ``full_tiles`` on are split ``splits`` ways."""
+        ``full_tiles`` on are split ``splits`` ways, summed through a workspace or, with
+        ``cluster``, inside a thread-block cluster."""
         m, k = x.shape
         if splits is None:
-            splits, full_tiles = self.choose_splits(m, n_rows, k)
+            splits, full_tiles, cluster = self.choose_splits(m, n_rows, k)
         ws = ct = None
-        if splits > 1:
+        if splits > 1 and not cluster:
             tiles = int(self.lib.leone_gemm_tc_tiles(m, n_rows))
             floats, counters = c_longlong(0), c_int(0)
             self.lib.leone_gemm_tc_scratch(m, max(tiles - full_tiles, 0), splits, byref(floats), byref(counters))
@@ -98,9 +130,10 @@ class FastKernels:
         code = self.lib.leone_gemm_tc(_ptr(x), _ptr(w), _ptr(out), _ptr(residual), m, n_rows, k,
                                       x.stride(0), w.stride(0), out.stride(0), epilogue, splits,
                                       full_tiles, _ptr(ws), _ptr(ct), _ptr(self.status), self.sm_count,
-                                      self._stream())
+                                      1 if cluster else 0, self._stream())
         if code != 0:
-            raise RuntimeError(f"gemm_tc refused or failed with code {code} for m={m} n={n_rows} k={k}")
+            raise RuntimeError(f"gemm_tc refused or failed with code {code} for m={m} n={n_rows} k={k} "
+                               f"splits={splits} cluster={cluster}")
         return True
 
     def linear(self, x, w, out, epilogue, residual) -> bool:

@@ -188,6 +188,56 @@ def test_gemm_tc_splits_only_the_last_tiles(ops16, m, n, k, splits, full):
     assert int(fast._counters.abs().sum()) == 0
 
 
+@pytest.mark.parametrize("m,n,k,splits", [(1, 384, 4096, 8), (5, 1000, 1024, 3), (16, 128 * 9, 520, 2),
+                                          (40, 520, 2048, 5), (64, 4096, 1024, 4), (100, 300, 640, 7),
+                                          (200, 1000, 2048, 6), (8, 4096, 4096, 8)])
+def test_gemm_tc_cluster_split(ops16, m, n, k, splits):
+    """The splits of a tile as a thread-block cluster: same sums, in the same order, as through
+    the workspace, for every epilogue."""
+    fast = ops16.fast
+    assert fast.cluster_capacity(m, splits) > 0
+    x = _randn((m, k), 31, torch.bfloat16)
+    w = _randn((n, k), 32, torch.bfloat16, scale=0.05)
+    want = x.double() @ w.double().t()
+    atol32 = 2e-6 * math.sqrt(k) * 4
+    out = torch.empty((m, n), device=DEV, dtype=torch.bfloat16)
+    fast._gemm(x, w, out, 0, None, n, splits=splits, cluster=True)
+    _close(out, want, 2 ** -8, atol32, f"cluster bf16 out m{m} n{n} k{k} s{splits}")
+    via_workspace = torch.empty_like(out)
+    fast._gemm(x, w, via_workspace, 0, None, n, splits=splits)
+    assert torch.equal(out, via_workspace)
+    res = _randn((m, n), 33)
+    hidden = res.clone()
+    fast._gemm(x, w, hidden, 2, hidden, n, splits=splits, cluster=True)
+    _close(hidden, want + res.double(), 1e-5, atol32, "cluster residual in place")
+    again = res.clone()
+    fast._gemm(x, w, again, 2, again, n, splits=splits, cluster=True)
+    assert torch.equal(hidden, again)
+    # SwiGLU epilogue on interleaved gate/up rows
+    inter = (n // 32) * 16
+    if inter:
+        gate, up = w[:inter].contiguous(), w[inter:2 * inter].contiguous()
+        gu = ops16.prepare_gate_up(gate, up)
+        act = torch.empty((m, inter), device=DEV, dtype=torch.bfloat16)
+        fast._gemm(x, gu.weight, act, 3, None, 2 * inter, splits=splits, cluster=True)
+        g = x.double() @ gate.double().t()
+        u = x.double() @ up.double().t()
+        _close(act, g / (1 + torch.exp(-g)) * u, 2 ** -7, 1e-4, "cluster swiglu")
+
+
+def test_gemm_tc_cluster_refusals(ops16):
+    fast = ops16.fast
+    x = _randn((8, 512), 1, torch.bfloat16)
+    w = _randn((256, 512), 2, torch.bfloat16)
+    out = torch.empty((8, 256), device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="refused"):
+        fast._gemm(x, w, out, 0, None, 256, splits=2, full_tiles=1, cluster=True)   # tail-only split
+    big = _randn((4096 * 4, 512), 3, torch.bfloat16)
+    out_big = torch.empty((8, 4096 * 4), device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="refused"):
+        fast._gemm(x, big, out_big, 0, None, 4096 * 4, splits=8, cluster=True)      # more than one round
+
+
 def test_gemm_tc_refuses_unaligned_k(ops16):
     x = _randn((4, 60), 1, torch.bfloat16)
     w = ops16.prepare_matrix(_randn((32, 60), 2, torch.bfloat16))
