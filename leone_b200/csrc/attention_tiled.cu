@@ -304,6 +304,75 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
 // ------------------------------------------------------------------------------------
 constexpr int kDecodeStages = 3;
 
+// One group of 16 keys of a decode step for one warp: scores of the block's 16 query rows
+// against the group (rows of k_s), online softmax update, and the weighted values added to
+// o_acc.  Keys at or past k_end are masked.
+template <int D>
+__device__ __forceinline__ void decode_group(const __nv_bfloat16* k_s, const __nv_bfloat16* v_s,
+                                             const uint32_t (&q_frag)[D / 16][4], int key0, int k_end,
+                                             float sl2, float (&m_run)[2], float (&l_run)[2],
+                                             float (&o_acc)[D / 8][4], int lane) {
+  constexpr int kRow = D + 8;
+  float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks) {
+    uint32_t b[4];
+    const int mi = lane >> 3;
+    const int r = (mi >> 1) * 8 + (lane & 7), c = ks * 16 + (mi & 1) * 8;
+    ldmatrix_x4(smem_u32(k_s + r * kRow + c), b);
+    mma_16816(s[0], q_frag[ks], b[0], b[1]);
+    mma_16816(s[1], q_frag[ks], b[2], b[3]);
+  }
+  float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int kj = key0 + nt * 8 + (lane & 3) * 2 + (j & 1);
+      const float v = kj < k_end ? s[nt][j] * sl2 : -INFINITY;
+      s[nt][j] = v;
+      tile_max[j >> 1] = fmaxf(tile_max[j >> 1], v);
+    }
+  float alpha[2], m_use[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 1));
+    tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 2));
+    const float m_new = fmaxf(m_run[h], tile_max[h]);
+    m_use[h] = m_new == -INFINITY ? 0.f : m_new;
+    alpha[h] = m_run[h] == -INFINITY ? 0.f : exp2f(m_run[h] - m_use[h]);
+    m_run[h] = m_new;
+    l_run[h] *= alpha[h];
+  }
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) {
+    o_acc[i][0] *= alpha[0];
+    o_acc[i][1] *= alpha[0];
+    o_acc[i][2] *= alpha[1];
+    o_acc[i][3] *= alpha[1];
+  }
+  uint32_t p_frag[4];
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt) {
+    const float p0 = exp2f(s[nt][0] - m_use[0]), p1 = exp2f(s[nt][1] - m_use[0]);
+    const float p2 = exp2f(s[nt][2] - m_use[1]), p3 = exp2f(s[nt][3] - m_use[1]);
+    l_run[0] += p0 + p1;
+    l_run[1] += p2 + p3;
+    p_frag[nt * 2] = pack_bf16(p0, p1);
+    p_frag[nt * 2 + 1] = pack_bf16(p2, p3);
+  }
+#pragma unroll
+  for (int np = 0; np < D / 16; ++np) {
+    uint32_t b[4];
+    const int mi = lane >> 3;
+    const int r = (mi & 1) * 8 + (lane & 7), c = np * 16 + (mi >> 1) * 8;
+    ldmatrix_x4_trans(smem_u32(v_s + r * kRow + c), b);
+    mma_16816(o_acc[np * 2], p_frag, b[0], b[1]);
+    mma_16816(o_acc[np * 2 + 1], p_frag, b[2], b[3]);
+  }
+}
+
+
 template <int D>
 __global__ void __launch_bounds__(kThreads)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
@@ -412,63 +481,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
     const __nv_bfloat16* k_s = my_s + (size_t)(it % kDecodeStages) * 2 * kGroupElems;
     const __nv_bfloat16* v_s = k_s + kGroupElems;
     const int key0 = k_begin + grp * 16;
-    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-#pragma unroll
-    for (int ks = 0; ks < D / 16; ++ks) {
-      uint32_t b[4];
-      const int mi = lane >> 3;
-      const int r = (mi >> 1) * 8 + (lane & 7), c = ks * 16 + (mi & 1) * 8;
-      ldmatrix_x4(smem_u32(k_s + r * kRow + c), b);
-      mma_16816(s[0], q_frag[ks], b[0], b[1]);
-      mma_16816(s[1], q_frag[ks], b[2], b[3]);
-    }
-    float tile_max[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-    for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int kj = key0 + nt * 8 + (lane & 3) * 2 + (j & 1);
-        const float v = kj < k_end ? s[nt][j] * sl2 : -INFINITY;
-        s[nt][j] = v;
-        tile_max[j >> 1] = fmaxf(tile_max[j >> 1], v);
-      }
-    float alpha[2], m_use[2];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 1));
-      tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 2));
-      const float m_new = fmaxf(m_run[h], tile_max[h]);
-      m_use[h] = m_new == -INFINITY ? 0.f : m_new;
-      alpha[h] = m_run[h] == -INFINITY ? 0.f : exp2f(m_run[h] - m_use[h]);
-      m_run[h] = m_new;
-      l_run[h] *= alpha[h];
-    }
-#pragma unroll
-    for (int i = 0; i < D / 8; ++i) {
-      o_acc[i][0] *= alpha[0];
-      o_acc[i][1] *= alpha[0];
-      o_acc[i][2] *= alpha[1];
-      o_acc[i][3] *= alpha[1];
-    }
-    uint32_t p_frag[4];
-#pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
-      const float p0 = exp2f(s[nt][0] - m_use[0]), p1 = exp2f(s[nt][1] - m_use[0]);
-      const float p2 = exp2f(s[nt][2] - m_use[1]), p3 = exp2f(s[nt][3] - m_use[1]);
-      l_run[0] += p0 + p1;
-      l_run[1] += p2 + p3;
-      p_frag[nt * 2] = pack_bf16(p0, p1);
-      p_frag[nt * 2 + 1] = pack_bf16(p2, p3);
-    }
-#pragma unroll
-    for (int np = 0; np < D / 16; ++np) {
-      uint32_t b[4];
-      const int mi = lane >> 3;
-      const int r = (mi & 1) * 8 + (lane & 7), c = np * 16 + (mi >> 1) * 8;
-      ldmatrix_x4_trans(smem_u32(v_s + r * kRow + c), b);
-      mma_16816(o_acc[np * 2], p_frag, b[0], b[1]);
-      mma_16816(o_acc[np * 2 + 1], p_frag, b[2], b[3]);
-    }
+    decode_group<D>(k_s, v_s, q_frag, key0, k_end, sl2, m_run, l_run, o_acc, lane);
     __syncwarp();      // the stage is refilled by the next iteration's request
   }
   cp_async_wait<0>();
@@ -552,6 +565,317 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o,
   }
 }
 
+// ------------------------------------------------------------------------------------
+// Decode with the splits of one (sequence, KV head group) as a thread-block cluster.
+// grid = (n_kv * head groups, splits, sequences), cluster = (1, splits, 1), splits <= 8.
+// The loop over the keys is the one above.  Each block then leaves its (max, sum,
+// unnormalised output) in its own shared memory; after a cluster barrier the outputs are dealt
+// to the blocks, each of which merges its share of all splits in split order through
+// distributed shared memory (global maximum, rescaled sums, weighted numerators / global sum,
+// crates/leone-cuda/cuda/ie_cuda.cu:4769-4812) and writes it.  No scratch in global memory, no
+// merge kernel.
+//
+// Optionally (DecodeFuse) the step's q/k RMSNorm, rotary and cache write are done here instead
+// of in a kernel of their own: the query rows are normed and rotated as they are loaded; the
+// block whose key range holds the new position norms and rotates the new key, uses it and the
+// new value in place of what the cache holds there, and (one block per KV head) writes both to
+// the cache.  The arithmetic is that of qk_norm_rope_write_vec_kernel, operation for operation,
+// so a key is the same bits whichever kernel wrote it.
+// ------------------------------------------------------------------------------------
+struct DecodeFuse {
+  int enabled;              // 0: rows of qkv are final and the cache already holds the new token
+  const float* q_w;         // [D] norm weights or null
+  const float* k_w;
+  float eps;
+  const float2* rope;       // [max_positions][D / 2] (cos, sin) or null
+  int max_positions;
+  int write_cache;          // 0 for a layer that only reads another layer's cache
+};
+
+// One warp: RMSNorm (if w) and half-split rotary over the whole row (if rope_row) of D bf16
+// values at src; the result goes to dst and, if not null, to dst2.  Lane l owns elements
+// l*E .. l*E+E-1, E = D / 32.
+template <int D>
+__device__ __forceinline__ void norm_rope_row(const __nv_bfloat16* src, __nv_bfloat16* dst,
+                                              __nv_bfloat16* dst2, const float* w, float eps,
+                                              const float2* rope_row, int lane) {
+  constexpr int E = D / 32;
+  static_assert(D % 64 == 0, "two elements per lane at least");
+  float v[E], wv[E];
+  float2 cs[E];
+  const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(src + lane * E);
+#pragma unroll
+  for (int i = 0; i < E / 2; ++i) {
+    const __nv_bfloat162 two = p2[i];
+    v[2 * i] = __low2float(two);
+    v[2 * i + 1] = __high2float(two);
+  }
+#pragma unroll
+  for (int i = 0; i < E; ++i) {
+    wv[i] = w != nullptr ? w[lane * E + i] : 1.f;
+    cs[i] = rope_row != nullptr ? rope_row[(lane & 15) * E + i] : make_float2(1.f, 0.f);
+  }
+  if (w != nullptr) {
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < E; ++i) ss = fmaf(v[i], v[i], ss);
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)D + eps);
+#pragma unroll
+    for (int i = 0; i < E; ++i) v[i] = v[i] * wv[i] * inv;
+  }
+  if (rope_row != nullptr) {
+    const bool upper = lane >= 16;
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+      const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
+      v[i] = upper ? other * cs[i].y + v[i] * cs[i].x : v[i] * cs[i].x - other * cs[i].y;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < E / 2; ++i) {
+    const __nv_bfloat162 o2 = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    reinterpret_cast<__nv_bfloat162*>(dst + lane * E)[i] = o2;
+    if (dst2 != nullptr) reinterpret_cast<__nv_bfloat162*>(dst2 + lane * E)[i] = o2;
+  }
+}
+
+template <int D, bool kFuse>
+__global__ void __launch_bounds__(kThreads)
+attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
+                                __nv_bfloat16* __restrict__ out, int out_stride, PagedArgs pa,
+                                const int* __restrict__ q_start, const int* __restrict__ ctx_len,
+                                int n_q, float scale, int window, int splits, DecodeFuse fz,
+                                int* status) {
+  constexpr int kRow = D + 8;
+  constexpr int kChunks = D / 8;
+  constexpr int kGroupElems = 16 * kRow;
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [16][kRow]
+  __nv_bfloat16* new_s = q_s + kGroupElems;             // the new token's key and value: [2][kRow]
+  __nv_bfloat16* kv_s = new_s + 2 * kRow;               // [4 warps][stages][K,V][16][kRow]
+
+  pdl_trigger();
+  pdl_wait();
+  const int g = n_q / pa.n_kv;
+  const int groups = (g + 15) / 16;
+  const int kvh = blockIdx.x / groups, hg = blockIdx.x - kvh * groups;
+  const int head0 = kvh * g + hg * 16, heads = min(16, g - hg * 16);
+  const int split = blockIdx.y, seq = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int row_token = q_start[seq];
+  const int ctx = ctx_len[seq];
+  const int pos = ctx - 1;                              // the query's (and the new key's) position
+  const int k_lo = window > 0 ? max(0, ctx - window) : 0;
+  const int total = ctx - k_lo;
+  const int chunk = ((total + splits - 1) / splits + kKeyTile - 1) / kKeyTile * kKeyTile;
+  const int k_begin = k_lo + split * chunk, k_end = min(ctx, k_begin + chunk);
+  const int n_groups = k_end > k_begin ? (k_end - k_begin + 15) / 16 : 0;
+  // the group of the new token, if this block's range holds it and the cache does not yet
+  const bool own_new = kFuse && pos >= k_begin && pos < k_end;
+  const int new_grp = own_new ? (pos - k_begin) / 16 : -1;
+
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  float o_acc[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o_acc[i][j] = 0.f;
+
+  if (n_groups > 0) {
+    __nv_bfloat16* my_s = kv_s + (size_t)warp * kDecodeStages * 2 * kGroupElems;
+    // Requests keys/values of group `grp` (16 keys from k_begin + 16*grp) into stage `st`.
+    auto issue = [&](int grp, int st) {
+      if (grp < n_groups) {
+        long long src = -1;
+        if (lane < 16) {
+          const int kj = k_begin + grp * 16 + lane;
+          if (kj < k_end && !(kFuse && kj == pos)) {      // the new token's row is filled in below
+            const int blk = kj / pa.page_tokens;
+            const int page = blk < pa.table_width ? pa.block_table[(size_t)seq * pa.table_width + blk] : -1;
+            if (page < 0 || page >= pa.num_pages) set_status(status, kBadPage, row_token, page, kj);
+            else src = (((long long)page * pa.n_kv + kvh) * pa.page_tokens + (kj % pa.page_tokens)) * D;
+          }
+        }
+        __nv_bfloat16* k_dst = my_s + (size_t)st * 2 * kGroupElems;
+        __nv_bfloat16* v_dst = k_dst + kGroupElems;
+        for (int idx = lane; idx < 16 * kChunks; idx += 32) {
+          const int r = idx / kChunks, ch = idx - r * kChunks;
+          const long long rs = __shfl_sync(0xffffffffu, src, r);
+          const bool ok = rs >= 0;
+          const long long off = ok ? rs + ch * 8 : 0;
+          cp_async16(smem_u32(k_dst + r * kRow + ch * 8), pa.k_pool + off, ok);
+          cp_async16(smem_u32(v_dst + r * kRow + ch * 8), pa.v_pool + off, ok);
+        }
+      }
+      cp_async_commit();          // always: keeps the group count the same in every iteration
+    };
+    // the keys first: nothing of them depends on the query
+#pragma unroll
+    for (int s0 = 0; s0 < kDecodeStages - 1; ++s0) issue(warp + 4 * s0, s0);
+
+    // the query rows (and the new key and value) while those copies are in flight
+    const __nv_bfloat16* tok = qkv + (size_t)row_token * row_stride;
+    if constexpr (kFuse) {
+      const float2* rope_row = nullptr;
+      if (fz.rope != nullptr) {
+        if (pos < 0 || pos >= fz.max_positions) {
+          if (tid == 0) set_status(status, kBadPosition, row_token, pos);
+        } else {
+          rope_row = fz.rope + (size_t)pos * (D / 2);
+        }
+      }
+      for (int r = warp; r < 16 + (own_new ? 2 : 0); r += 4) {
+        if (r < heads) {
+          norm_rope_row<D>(tok + (size_t)(head0 + r) * D, q_s + r * kRow, nullptr, fz.q_w, fz.eps, rope_row, lane);
+        } else if (r < 16) {
+          for (int c = lane; c < kRow; c += 32) q_s[r * kRow + c] = __float2bfloat16_rn(0.f);
+        } else {
+          // r == 16: the new key, normed and rotated; r == 17: the new value as it is
+          const bool is_k = r == 16;
+          __nv_bfloat16* cache_row = nullptr;
+          if (hg == 0 && fz.write_cache) {
+            const int blk = pos / pa.page_tokens;
+            const int page = blk < pa.table_width ? pa.block_table[(size_t)seq * pa.table_width + blk] : -1;
+            if (page < 0 || page >= pa.num_pages) {
+              if (lane == 0) set_status(status, kBadPage, row_token, page, pos);
+            } else {
+              const size_t off = (((size_t)page * pa.n_kv + kvh) * pa.page_tokens + (pos % pa.page_tokens)) * D;
+              cache_row = const_cast<__nv_bfloat16*>(is_k ? pa.k_pool : pa.v_pool) + off;
+            }
+          }
+          const __nv_bfloat16* src = tok + (size_t)(n_q + (is_k ? 0 : pa.n_kv) + kvh) * D;
+          norm_rope_row<D>(src, new_s + (r - 16) * kRow, cache_row, is_k ? fz.k_w : nullptr, fz.eps,
+                           is_k ? rope_row : nullptr, lane);
+        }
+      }
+    } else {
+      for (int idx = tid; idx < 16 * kChunks; idx += kThreads) {
+        const int r = idx / kChunks, ch = idx - r * kChunks;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r < heads) v = *reinterpret_cast<const uint4*>(tok + (size_t)(head0 + r) * D + ch * 8);
+        *reinterpret_cast<uint4*>(q_s + r * kRow + ch * 8) = v;
+      }
+    }
+    __syncthreads();
+    uint32_t q_frag[D / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      const int mi = lane >> 3;
+      const int r = (mi & 1) * 8 + (lane & 7), c = ks * 16 + (mi >> 1) * 8;
+      ldmatrix_x4(smem_u32(q_s + r * kRow + c), q_frag[ks]);
+    }
+    const float sl2 = scale * kLog2e;
+    int it = 0;
+    for (int grp = warp; grp < n_groups; grp += 4, ++it) {
+      issue(grp + 4 * (kDecodeStages - 1), (it + kDecodeStages - 1) % kDecodeStages);
+      cp_async_wait<kDecodeStages - 1>();
+      __syncwarp();
+      __nv_bfloat16* k_s = my_s + (size_t)(it % kDecodeStages) * 2 * kGroupElems;
+      __nv_bfloat16* v_s = k_s + kGroupElems;
+      const int key0 = k_begin + grp * 16;
+      if (kFuse && grp == new_grp) {
+        // the new token: its key and value come from this step's projections, not from the cache
+        const int rp = pos - key0;
+        for (int c = lane; c < D / 2; c += 32) {
+          reinterpret_cast<uint32_t*>(k_s + rp * kRow)[c] = reinterpret_cast<const uint32_t*>(new_s)[c];
+          reinterpret_cast<uint32_t*>(v_s + rp * kRow)[c] = reinterpret_cast<const uint32_t*>(new_s + kRow)[c];
+        }
+        __syncwarp();
+      }
+      decode_group<D>(k_s, v_s, q_frag, key0, k_end, sl2, m_run, l_run, o_acc, lane);
+      __syncwarp();      // the stage is refilled by the next iteration's request
+    }
+    cp_async_wait<0>();
+  }
+  __syncthreads();     // every warp is done with its stages: the space becomes the merge buffer
+
+  // the four warps -> one (max, sum, output) per query row of the block
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+  }
+  float* mo = reinterpret_cast<float*>(kv_s);          // [4 warps][16 rows][D]
+  float* mml = mo + 4 * 16 * D;                        // [4][16][2]
+  float* cl_o = mml + 4 * 16 * 2;                      // [16][D]: this block's partial for the cluster
+  float* cl_ml = cl_o + 16 * D;                        // [16][2]
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = (lane >> 2) + h * 8;
+    if ((lane & 3) == 0) {
+      mml[(warp * 16 + r) * 2] = m_run[h];
+      mml[(warp * 16 + r) * 2 + 1] = l_run[h];
+    }
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      float* dst = mo + (size_t)(warp * 16 + r) * D + i * 8 + (lane & 3) * 2;
+      dst[0] = o_acc[i][h * 2];
+      dst[1] = o_acc[i][h * 2 + 1];
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < heads * D; idx += kThreads) {
+    const int r = idx / D, c = idx - r * D;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) m = fmaxf(m, mml[(w * 16 + r) * 2]);
+    float l = 0.f, o = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = mml[(w * 16 + r) * 2];
+      const float f = mw == -INFINITY ? 0.f : exp2f(mw - m);
+      l += f * mml[(w * 16 + r) * 2 + 1];
+      o += f * mo[(size_t)(w * 16 + r) * D + c];
+    }
+    if (splits > 1) {
+      cl_o[r * D + c] = o;
+      if (c == 0) {
+        cl_ml[r * 2] = m;
+        cl_ml[r * 2 + 1] = l;
+      }
+    } else {
+      out[(size_t)row_token * out_stride + (size_t)(head0 + r) * D + c] =
+          __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+    }
+  }
+  if (splits == 1) return;            // grid-uniform: a launch has clusters or it has none
+
+  // Every thread of every block of the cluster comes here.  Block `split` merges outputs
+  // [split * per, split * per + per) of the heads * D of this (sequence, head group).
+  cluster_sync_all();
+  const int n_out = heads * D;
+  const int per = (n_out + splits - 1) / splits;
+  const uint32_t o_base = smem_u32(cl_o), ml_base = smem_u32(cl_ml);
+  for (int idx = split * per + tid; idx < min(n_out, split * per + per); idx += kThreads) {
+    const int r = idx / D;
+    float ms[8], ls[8], os[8];
+    float m = -INFINITY;
+#pragma unroll
+    for (int s2 = 0; s2 < 8; ++s2) {
+      if (s2 < splits) {
+        ms[s2] = cluster_ld_f32(cluster_map(ml_base + r * 8, s2));
+        ls[s2] = cluster_ld_f32(cluster_map(ml_base + r * 8 + 4, s2));
+        os[s2] = cluster_ld_f32(cluster_map(o_base + idx * 4, s2));
+      }
+    }
+#pragma unroll
+    for (int s2 = 0; s2 < 8; ++s2)
+      if (s2 < splits) m = fmaxf(m, ms[s2]);
+    float l = 0.f, o = 0.f;
+#pragma unroll
+    for (int s2 = 0; s2 < 8; ++s2) {
+      if (s2 < splits && ms[s2] != -INFINITY) {
+        const float f = exp2f(ms[s2] - m);
+        l += f * ls[s2];
+        o += f * os[s2];
+      }
+    }
+    out[(size_t)row_token * out_stride + (size_t)head0 * D + idx] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+  }
+  cluster_sync_all();                 // the partials may go away
+}
+
 template <int D> constexpr int prefill_smem() {
   return (kRowsPerBlock + 4 * kKeyTile) * (D + 8) * 2 + 2 * kKeyTile * 8;
 }
@@ -577,6 +901,35 @@ int launch_prefill(const __nv_bfloat16* qkv, int row_stride, __nv_bfloat16* out,
   dim3 grid((max_q_len + tq - 1) / tq, pa.n_kv, n_seqs);
   return launch_kernel(attention_prefill_kernel<D>, grid, dim3(kThreads), prefill_smem<D>(), stream, qkv,
                        row_stride, out, out_stride, pa, q_start, ctx_len, n_q, scale, window, status);
+}
+
+template <int D> constexpr int decode_cluster_smem() {
+  const int tiles = (16 + 4 * kDecodeStages * 2 * 16) * (D + 8) * 2 + 2 * (D + 8) * 2;
+  const int merge = 18 * (D + 8) * 2 + (4 * 16 * D + 4 * 16 * 2 + 16 * D + 16 * 2) * 4;
+  return tiles > merge ? tiles : merge;
+}
+
+template <int D, bool kFuse>
+int launch_decode_cluster(const __nv_bfloat16* qkv, int row_stride, __nv_bfloat16* out, int out_stride,
+                          const PagedArgs& pa, const int* q_start, const int* ctx_len, int n_seqs, int n_q,
+                          float scale, int window, int splits, const DecodeFuse& fz, int* status,
+                          cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_cluster_kernel<D, kFuse>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, decode_cluster_smem<D>());
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int g = n_q / pa.n_kv;
+  dim3 grid(pa.n_kv * ((g + 15) / 16), splits, n_seqs);
+  if (splits == 1)
+    return launch_kernel(attention_decode_cluster_kernel<D, kFuse>, grid, dim3(kThreads), decode_cluster_smem<D>(),
+                         stream, qkv, row_stride, out, out_stride, pa, q_start, ctx_len, n_q, scale, window,
+                         splits, fz, status);
+  return launch_kernel_cluster(attention_decode_cluster_kernel<D, kFuse>, grid, dim3(kThreads),
+                               decode_cluster_smem<D>(), stream, dim3(1, splits, 1), qkv, row_stride, out,
+                               out_stride, pa, q_start, ctx_len, n_q, scale, window, splits, fz, status);
 }
 
 template <int D>
@@ -676,4 +1029,43 @@ extern "C" int leone_attention_decode(const void* qkv, int row_stride, void* out
                                                (__nv_bfloat16*)out, out_stride, pa, q_start, ctx_len,
                                                n_seqs, n_q, scale, window, splits, part_o, part_ml,
                                                status, stream));
+}
+
+// The same product with the splits of a (sequence, head group) as a thread-block cluster that
+// merges through distributed shared memory: 1 <= splits <= 8, no scratch.  With `fuse` != 0 the
+// rows of qkv are raw projections: the kernel applies the per-head RMSNorm (weights q_norm_w /
+// k_norm_w, fp32 [d], or null for none) and the rotary table (`rope`: [max_positions][d/2]
+// (cos, sin) fp32 over the whole head, or null) to the queries and to the new key at position
+// ctx_len-1, uses the new key and value in place of what the cache holds there and, if
+// `write_cache`, stores them into the pools.  fuse needs d of 64 or 128.
+extern "C" int leone_attention_decode_cluster(const void* qkv, int row_stride, void* out, int out_stride,
+                                              void* k_pool, void* v_pool, const int* block_table,
+                                              int table_width, const int* q_start, const int* ctx_len,
+                                              int n_seqs, int n_q, int n_kv, int d, float scale, int window,
+                                              int page_tokens, int num_pages, int splits, int fuse,
+                                              const float* q_norm_w, const float* k_norm_w, float eps,
+                                              const float* rope, int max_positions, int write_cache,
+                                              int* status, cudaStream_t stream) {
+  if (n_seqs <= 0) return 0;
+  int r = check_common(d, n_q, n_kv, row_stride, out_stride, qkv, k_pool, v_pool, page_tokens, table_width);
+  if (r != 0) return r;
+  if (splits < 1 || splits > 8 || n_seqs > 65535) return kRefusedSize;
+  if (fuse && d != 64 && d != 128) return kRefusedSize;
+  PagedArgs pa{(const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, block_table, table_width,
+               page_tokens, num_pages, n_kv};
+  DecodeFuse fz{fuse ? 1 : 0, q_norm_w, k_norm_w, eps, reinterpret_cast<const float2*>(rope), max_positions,
+                write_cache};
+  if (fuse) {
+    if (d == 64)
+      return launch_decode_cluster<64, true>((const __nv_bfloat16*)qkv, row_stride, (__nv_bfloat16*)out,
+                                             out_stride, pa, q_start, ctx_len, n_seqs, n_q, scale, window,
+                                             splits, fz, status, stream);
+    return launch_decode_cluster<128, true>((const __nv_bfloat16*)qkv, row_stride, (__nv_bfloat16*)out,
+                                            out_stride, pa, q_start, ctx_len, n_seqs, n_q, scale, window,
+                                            splits, fz, status, stream);
+  }
+  LEONE_DISPATCH_D(d, return (launch_decode_cluster<DD, false>((const __nv_bfloat16*)qkv, row_stride,
+                                                               (__nv_bfloat16*)out, out_stride, pa, q_start,
+                                                               ctx_len, n_seqs, n_q, scale, window, splits,
+                                                               fz, status, stream)));
 }

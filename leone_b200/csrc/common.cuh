@@ -104,6 +104,31 @@ inline int launch_result() {
   return (int)cudaGetLastError();
 }
 
+// ---- thread-block clusters ---------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Every thread of every block of the cluster arrives and waits; shared-memory writes before the
+// barrier are visible to the cluster's other blocks after it.  The hardware wait has no time
+// limit, so it stands only where every thread is certain to arrive (after bounded loops).
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+}
+// Address of this block's shared-memory location `addr` in the block of rank `rank`.
+__device__ __forceinline__ uint32_t cluster_map(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ float cluster_ld_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+
 // ---- programmatic dependent launch -------------------------------------------------
 // Kernels of a step are launched so that a kernel may start while its predecessor in the
 // stream is still running.  A kernel calls pdl_trigger() early (its successor may then be
@@ -140,10 +165,10 @@ inline int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t
   return e == cudaSuccess ? launch_result() : (int)e;
 }
 
-// The same for a grid of thread-block clusters of `cluster_x` blocks along x.
+// The same for a grid of thread-block clusters of shape `cluster`.
 template <typename... KArgs, typename... Args>
 inline int launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                                 cudaStream_t stream, int cluster_x, Args... args) {
+                                 cudaStream_t stream, dim3 cluster, Args... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -151,9 +176,9 @@ inline int launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block
   cfg.stream = stream;
   cudaLaunchAttribute attrs[2];
   attrs[0].id = cudaLaunchAttributeClusterDimension;
-  attrs[0].val.clusterDim.x = cluster_x;
-  attrs[0].val.clusterDim.y = 1;
-  attrs[0].val.clusterDim.z = 1;
+  attrs[0].val.clusterDim.x = cluster.x;
+  attrs[0].val.clusterDim.y = cluster.y;
+  attrs[0].val.clusterDim.z = cluster.z;
   attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attrs[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attrs;

@@ -527,7 +527,7 @@ int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& 
   if constexpr (kCluster) {
     if (total > slots) return kRefusedSize;              // one unit per block, one round
     return launch_kernel_cluster(gemm_tc_kernel<BN, kSwap, true>, dim3((unsigned)total), dim3(kGemmThreads),
-                                 Cfg::kSmemBytes, stream, p.splits, mw, mx, p);
+                                 Cfg::kSmemBytes, stream, dim3(p.splits), mw, mx, p);
   }
   return launch_kernel(gemm_tc_kernel<BN, kSwap, kCluster>, dim3(grid), dim3(kGemmThreads), Cfg::kSmemBytes,
                        stream, mw, mx, p);

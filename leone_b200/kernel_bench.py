@@ -124,7 +124,9 @@ def _print_trace(ops, run, copies):
             print(f"    {names[i]:22s} min {col.min():7.2f}  median {col.median():7.2f}  max {col.max():7.2f} us")
 
 
-def bench_decode_attention(ops, batch, context, n_q, n_kv, d, page_tokens, reps, warmup, flush):
+def bench_decode_attention(ops, batch, context, n_q, n_kv, d, page_tokens, reps, warmup, flush, prep="none"):
+    """``prep``: "none" times attention over final q rows; "kernel" adds the q/k norm + rotary +
+    cache-write kernel before it; "fused" lets the attention kernel do that work itself."""
     blocks = -(-context // page_tokens)
     per_copy = batch * blocks
     bytes_ = 2.0 * batch * context * n_kv * d * 2
@@ -141,15 +143,28 @@ def bench_decode_attention(ops, batch, context, n_q, n_kv, d, page_tokens, reps,
         status=torch.zeros(4, device=DEV, dtype=torch.int32), n_seqs=batch, max_q_len=1,
         max_ctx_len=context, decode_only=True)
     state = {"i": 0}
+    ctx.positions = ctx.ctx_len - 1
+    ctx.seq_of_token = torch.arange(batch, device=DEV, dtype=torch.int32)
+    ctx.n_tokens = batch
+    from .parts.rotary import build_rotary_table
+    rope = build_rotary_table(context + 1, d, 1e6).to(DEV)
+    qw = torch.ones(d, device=DEV)
+    kw = torch.ones(d, device=DEV)
 
     def run():
         cache = types.SimpleNamespace(k_pool=k_pool, v_pool=v_pool,
                                       block_table=tables[state["i"] % copies], page_tokens=page_tokens)
         state["i"] += 1
-        ops.fast.attention(ctx, qkv, out, n_q, n_kv, d, 1 / math.sqrt(d), None, cache)
+        fuse = None
+        if prep == "kernel":
+            ops.qk_norm_rope_write(ctx, qkv, n_q, n_kv, d, qw, kw, 1e-6, rope, d, cache)
+        elif prep == "fused":
+            fuse = dict(q_w=qw, k_w=kw, eps=1e-6, rope=rope, write_cache=True)
+        ops.fast.attention(ctx, qkv, out, n_q, n_kv, d, 1 / math.sqrt(d), None, cache, fuse)
 
     ms = _time(run, reps, warmup, flush, per_graph=copies)
-    return dict(kernel="attention_decode", batch=batch, context=context, us=ms * 1e3,
+    return dict(kernel="attention_decode", batch=batch, context=context, prep=prep,
+                clusters=ops.fast.use_clusters, us=ms * 1e3,
                 splits=ops.fast.decode_splits(batch, n_kv, n_q // n_kv, context), gbs=bytes_ / ms / 1e6)
 
 
@@ -191,6 +206,8 @@ def main(argv=None) -> int:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--flush", action="store_true", help="write a 256 MB buffer between timed launches")
     ap.add_argument("--trace", action="store_true", help="gemm: print the kernel's phase time stamps")
+    ap.add_argument("--prep", choices=["none", "kernel", "fused"], default="none",
+                    help="decode-attention: where q/k norm, rotary and cache write are done")
     ap.add_argument("--cluster", action="store_true",
                     help="gemm with --splits: sum the splits inside thread-block clusters")
     args = ap.parse_args(argv)
@@ -211,7 +228,7 @@ def main(argv=None) -> int:
             rows.append(r)
     elif args.what == "decode-attention":
         rows.append(bench_decode_attention(ops, args.batch, args.context, args.heads, args.kv_heads,
-                                           args.head_dim, args.page_tokens, args.reps, args.warmup, flush))
+                                           args.head_dim, args.page_tokens, args.reps, args.warmup, flush, args.prep))
     else:
         rows.append(bench_prefill_attention(ops, args.tokens, args.heads, args.kv_heads, args.head_dim,
                                             args.page_tokens, args.reps, args.warmup))

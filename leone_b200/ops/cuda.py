@@ -261,7 +261,14 @@ class CudaOps:
             pool_args[4], pool_args[5], pool_args[6], _ptr(ctx.status), self._stream()),
             "qk_norm_rope_write")
 
-    def attention(self, ctx, qkv, out, n_q, n_kv, d, scale, window, cache):
+    def can_fuse_decode(self, ctx, qkv, n_q, n_kv, d) -> bool:
+        """True if the attention kernel can do the q/k norm, rotation and cache write itself
+        for this step (then ``qk_norm_rope_write`` is not called and ``attention`` gets
+        ``fuse``: q_w, k_w (fp32 [d] or None), eps, rope ([positions, d/2, 2] fp32 or None),
+        write_cache)."""
+        return self.fast is not None and self.fast.decode_fusable(ctx, qkv.dtype, n_q, n_kv, d, qkv.stride(0))
+
+    def attention(self, ctx, qkv, out, n_q, n_kv, d, scale, window, cache, fuse=None):
         n = qkv.shape[0]
         kp, vp, bt = cache.k_pool, cache.v_pool, cache.block_table
         _need(out.shape == (n, n_q * d) and out.is_contiguous() and out.dtype == qkv.dtype,
@@ -269,9 +276,10 @@ class CudaOps:
         _need(kp.is_contiguous() and vp.is_contiguous() and kp.dtype == qkv.dtype
               and kp.shape[1] == n_kv and kp.shape[3] == d, "cache pool layout")
         if self.fast is not None and self.fast.attention(ctx, qkv, out, n_q, n_kv, d, scale,
-                                                         window, cache):
+                                                         window, cache, fuse):
             self.launches += 1
             return
+        _need(fuse is None, "the any-size attention kernel needs q/k norm and cache write done before")
         self.launches += 1
         _check(self.core.leone_attention_generic(
             _dt(qkv.dtype), _ptr(qkv), qkv.stride(0), _ptr(out), out.stride(0), _ptr(kp), _ptr(vp),

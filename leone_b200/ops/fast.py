@@ -33,6 +33,8 @@ class FastKernels:
         # LEONE_NO_CLUSTERS=1 sums split-K partial tiles through a workspace instead of inside clusters
         self.use_clusters = os.environ.get("LEONE_NO_CLUSTERS", "0") != "1"
         self._cluster_capacity = {}
+        # LEONE_NO_FUSED_DECODE=1 keeps q/k norm, rotation and cache write in their own kernel
+        self.fuse_decode = os.environ.get("LEONE_NO_FUSED_DECODE", "0") != "1"
         self.max_cluster = int(os.environ.get("LEONE_MAX_CLUSTER", "8"))
         # tuning aid: LEONE_GEMM_SPLITS="6144x4096:4,4096x12288:c8" forces the split of [n x k]
         # products at decode sizes ("c": summed inside a cluster)
@@ -175,26 +177,60 @@ class FastKernels:
                 best, best_cost = s, cost
         return best
 
-    def attention(self, ctx, qkv, out, n_q, n_kv, d, scale, window, cache) -> bool:
-        if not self.use_tiled_attention or qkv.dtype != torch.bfloat16:
+    def attention_supported(self, dtype, n_q, n_kv, d, row_stride) -> bool:
+        return (self.use_tiled_attention and dtype == torch.bfloat16 and d % 16 == 0 and d <= 128
+                and n_q // n_kv <= 64 and row_stride % 8 == 0)
+
+    def decode_fusable(self, ctx, dtype, n_q, n_kv, d, row_stride) -> bool:
+        """True if a decode step's attention runs as clusters that can also do the q/k norm,
+        the rotation and the cache write."""
+        return (self.attention_supported(dtype, n_q, n_kv, d, row_stride) and self.fuse_decode
+                and ctx.decode_only and d in (64, 128)
+                and self.decode_in_clusters(ctx.n_seqs, n_kv, n_q // n_kv, ctx.max_ctx_len))
+
+    def decode_in_clusters(self, n_seqs: int, n_kv: int, g: int, max_ctx: int) -> bool:
+        """Whether a decode step's splits merge inside thread-block clusters: when all blocks
+        are resident at once.  With several rounds of blocks, clusters (which need all their
+        blocks' slots free in one GPC at the same moment) were measured slower than scratch
+        and a merge kernel."""
+        splits = self.decode_splits(n_seqs, n_kv, g, max_ctx)
+        blocks = n_seqs * n_kv * (-(-g // 16)) * splits
+        return self.use_clusters and splits <= 8 and blocks <= 2 * self.sm_count
+
+    def attention(self, ctx, qkv, out, n_q, n_kv, d, scale, window, cache, fuse=None) -> bool:
+        if not self.attention_supported(qkv.dtype, n_q, n_kv, d, qkv.stride(0)):
             return False
         g = n_q // n_kv
-        if d % 16 != 0 or d > 128 or g > 64 or qkv.stride(0) % 8 != 0:
-            return False
         from ctypes import c_float
         kp, vp, bt = cache.k_pool, cache.v_pool, cache.block_table
         common = (_ptr(qkv), qkv.stride(0), _ptr(out), out.stride(0), _ptr(kp), _ptr(vp), _ptr(bt),
                   bt.shape[1], _ptr(ctx.q_start), _ptr(ctx.ctx_len), ctx.n_seqs)
         if ctx.decode_only:
             splits = self.decode_splits(ctx.n_seqs, n_kv, g, ctx.max_ctx_len)
-            scratch = None
-            if splits > 1:
-                need = self.lib.leone_attention_decode_scratch(ctx.n_seqs, n_q, d, splits)
-                scratch = self._attn_scratch(need)
-            code = self.lib.leone_attention_decode(
-                *common, n_q, n_kv, d, c_float(scale), int(window or 0), cache.page_tokens,
-                kp.shape[0], splits, _ptr(scratch), _ptr(ctx.status), self._stream())
+            if self.decode_in_clusters(ctx.n_seqs, n_kv, g, ctx.max_ctx_len):
+                # the splits of a (sequence, KV head) merge inside a cluster; optionally the
+                # kernel norms and rotates q and the new k and writes the cache itself
+                fz = (0, None, None, c_float(0.0), None, 0, 0)
+                if fuse is not None:
+                    rope = fuse["rope"]
+                    fz = (1, _ptr(fuse["q_w"]), _ptr(fuse["k_w"]), c_float(fuse["eps"]), _ptr(rope),
+                          rope.shape[0] if rope is not None else 0, 1 if fuse["write_cache"] else 0)
+                code = self.lib.leone_attention_decode_cluster(
+                    *common, n_q, n_kv, d, c_float(scale), int(window or 0), cache.page_tokens,
+                    kp.shape[0], splits, *fz, _ptr(ctx.status), self._stream())
+            else:
+                if fuse is not None:
+                    raise RuntimeError("fused decode attention asked for where decode_fusable() is false")
+                scratch = None
+                if splits > 1:
+                    need = self.lib.leone_attention_decode_scratch(ctx.n_seqs, n_q, d, splits)
+                    scratch = self._attn_scratch(need)
+                code = self.lib.leone_attention_decode(
+                    *common, n_q, n_kv, d, c_float(scale), int(window or 0), cache.page_tokens,
+                    kp.shape[0], splits, _ptr(scratch), _ptr(ctx.status), self._stream())
         else:
+            if fuse is not None:
+                raise RuntimeError("fused q/k preparation is a decode-step feature")
             code = self.lib.leone_attention_prefill(
                 *common, ctx.max_q_len, n_q, n_kv, d, c_float(scale), int(window or 0),
                 cache.page_tokens, kp.shape[0], _ptr(ctx.status), self._stream())

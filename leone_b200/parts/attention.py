@@ -64,9 +64,13 @@ class Attention(Mixer):
                              tensors[self.names["v"]]], dim=0).contiguous()
         self.w_qkv = self.rt.ops.prepare_matrix(stacked)
         self.w_o = self.rt.ops.prepare_matrix(tensors[self.names["o"]])
+        self.q_norm_f32 = self.k_norm_f32 = None
         if self.qk_norm:
             self.q_norm_w = tensors[self.q_norm_name]
             self.k_norm_w = tensors[self.k_norm_name]
+            # fp32 copies for the decode kernel that does the norm itself
+            self.q_norm_f32 = self.q_norm_w.float().contiguous()
+            self.k_norm_f32 = self.k_norm_w.float().contiguous()
 
     def weight_bytes(self):
         return (self.qkv_cols * self.hidden + self.hidden * self.n_q * self.d) * self.rt.dtype.itemsize
@@ -86,6 +90,18 @@ class Attention(Mixer):
                 rotary_dim, pairing = table.shape[1] * 2, self.pos.pairing
                 if pairing != "half_split":
                     raise ValueError(f"attention kernels rotate half-split pairs, not '{pairing}'")
+        attn = rt.buffer("attn_out", n, self.n_q * self.d, rt.dtype)
+        # A decode step whose new key goes to this layer's own cache: the attention kernel may norm
+        # and rotate q and the new k and write the cache itself.  (A layer that reads another
+        # layer's cache takes every key from there, the newest too, so it is not fused.)
+        fusable = cache.writes and (self.pos is None or (table is not None and rotary_dim == self.d))
+        if fusable and hasattr(rt.ops, "can_fuse_decode") and \
+                rt.ops.can_fuse_decode(ctx, qkv, self.n_q, self.n_kv, self.d):
+            rt.ops.attention(ctx, qkv, attn, self.n_q, self.n_kv, self.d, self.scale, self.window, cache,
+                             fuse=dict(q_w=self.q_norm_f32, k_w=self.k_norm_f32, eps=self.eps, rope=table,
+                                       write_cache=True))
+            rt.ops.linear(attn, self.w_o, hidden, residual=hidden)
+            return
         # q/k norm, rotation and the cache write are one kernel; an encoding without a
         # rotary table is applied by the encoding itself between norm and cache write.
         if self.pos is not None and table is None:
@@ -100,7 +116,6 @@ class Attention(Mixer):
             rt.ops.qk_norm_rope_write(ctx, qkv, self.n_q, self.n_kv, self.d, self.q_norm_w,
                                       self.k_norm_w, self.eps, table, rotary_dim,
                                       cache if cache.writes else None)
-        attn = rt.buffer("attn_out", n, self.n_q * self.d, rt.dtype)
         rt.ops.attention(ctx, qkv, attn, self.n_q, self.n_kv, self.d, self.scale,
                          self.window, cache)
         rt.ops.linear(attn, self.w_o, hidden, residual=hidden)

@@ -96,6 +96,7 @@ def test_a_captured_graph_survives_growth_of_the_scratch_buffers(folders):
     from leone_b200 import generate
     eng = _engine(folders["C"], "C", "bfloat16", 200)
     eng.ops.fast.min_scratch_floats = 1            # every growth reallocates
+    eng.ops.fast.use_clusters = False              # the paths that keep partial results in scratch
     small = [replay.random_tokens(331, n, 90 + n) for n in (150, 140)]
     large = [replay.random_tokens(331, 150, 200 + i) for i in range(4)]
     first = generate(eng, small, 6, eos_token_id=-1)

@@ -491,5 +491,68 @@ def test_attention_prefill_tiled(ops16, n_q, n_kv, d, pt, window):
                                                   (8, 2, 128, 16, None), (4, 4, 80, 4, 37),
                                                   (32, 8, 128, 16, None), (40, 2, 16, 16, None)])
 @pytest.mark.parametrize("seq_lens", [[1], [300, 2, 64, 65, 1000], [2100]])
-def test_attention_decode_tiled(ops16, n_q, n_kv, d, pt, window, seq_lens):
+@pytest.mark.parametrize("clusters", [True, False])
+def test_attention_decode_tiled(ops16, n_q, n_kv, d, pt, window, seq_lens, clusters, monkeypatch):
+    """Split-KV decode, the splits merged inside a thread-block cluster or through scratch and a
+    merge kernel."""
+    monkeypatch.setattr(ops16.fast, "use_clusters", clusters)
     _tiled_case(ops16, n_q, n_kv, d, pt, window, seq_lens=seq_lens, starts=[l - 1 for l in seq_lens], seed=4)
+
+
+@pytest.mark.parametrize("n_q,n_kv,d,pt,window,qk_norm,rotary", [
+    (8, 2, 128, 16, None, True, True), (6, 3, 64, 8, None, True, True), (5, 1, 64, 16, 40, False, True),
+    (40, 2, 128, 16, None, True, False), (4, 4, 128, 4, 300, True, True)])
+@pytest.mark.parametrize("seq_lens", [[300, 1, 64, 65, 17], [2100], [1, 2]])
+def test_attention_decode_fused_norm_rope_write(ops16, n_q, n_kv, d, pt, window, qk_norm, rotary, seq_lens):
+    """The decode kernel doing q/k norm, rotation and cache write itself against the two-kernel
+    path on the same raw projections: the same cache bit for bit, the same outputs."""
+    dtype = torch.bfloat16
+    n = len(seq_lens)
+    table, k_pool, v_pool = _paged_setup(seq_lens, pt, n_kv, d, dtype, 6)
+    k_pool.copy_(_randn(tuple(k_pool.shape), 300, dtype))      # what older tokens (and freed pages) left
+    v_pool.copy_(_randn(tuple(v_pool.shape), 400, dtype))
+    raw = _randn((n, (n_q + 2 * n_kv) * d), 77, dtype)
+    qw = (1 + 0.1 * _randn((d,), 78)) if qk_norm else None
+    kw = (1 + 0.1 * _randn((d,), 79)) if qk_norm else None
+    rope = _rope_table(4096, d, 1e4) if rotary else None
+    ctx = _ctx([l - 1 for l in seq_lens], list(range(n)))
+    ctx.q_start = torch.arange(n + 1, device=DEV, dtype=torch.int32)
+    ctx.ctx_len = torch.tensor(seq_lens, device=DEV, dtype=torch.int32)
+    ctx.n_seqs, ctx.max_q_len, ctx.max_ctx_len, ctx.decode_only = n, 1, max(seq_lens), True
+    scale = 1 / math.sqrt(d)
+    # two kernels
+    qkv_a, k_a, v_a = raw.clone(), k_pool.clone(), v_pool.clone()
+    cache_a = types.SimpleNamespace(k_pool=k_a, v_pool=v_a, block_table=table, page_tokens=pt)
+    ops16.qk_norm_rope_write(ctx, qkv_a, n_q, n_kv, d, qw, kw, 1e-6, rope, d if rotary else 0, cache_a)
+    out_a = torch.empty((n, n_q * d), device=DEV, dtype=dtype)
+    ops16.attention(ctx, qkv_a, out_a, n_q, n_kv, d, scale, window, cache_a)
+    # one kernel
+    qkv_b, k_b, v_b = raw.clone(), k_pool.clone(), v_pool.clone()
+    cache_b = types.SimpleNamespace(k_pool=k_b, v_pool=v_b, block_table=table, page_tokens=pt)
+    out_b = torch.full_like(out_a, 7.0)
+    assert ops16.can_fuse_decode(ctx, qkv_b, n_q, n_kv, d)
+    ops16.attention(ctx, qkv_b, out_b, n_q, n_kv, d, scale, window, cache_b,
+                    fuse=dict(q_w=qw, k_w=kw, eps=1e-6, rope=rope, write_cache=True))
+    torch.cuda.synchronize()
+    assert ctx.status[0].item() == 0
+    assert torch.equal(k_a, k_b) and torch.equal(v_a, v_b), "the cache differs"
+    assert torch.equal(out_a, out_b), "the outputs differ"
+    # without the cache write the pools stay as they were and the outputs are the same
+    k_c, v_c = k_pool.clone(), v_pool.clone()
+    cache_c = types.SimpleNamespace(k_pool=k_c, v_pool=v_c, block_table=table, page_tokens=pt)
+    out_c = torch.empty_like(out_a)
+    ops16.attention(ctx, raw.clone(), out_c, n_q, n_kv, d, scale, window, cache_c,
+                    fuse=dict(q_w=qw, k_w=kw, eps=1e-6, rope=rope, write_cache=False))
+    torch.cuda.synchronize()
+    assert torch.equal(k_c, k_pool) and torch.equal(v_c, v_pool)
+    assert torch.equal(out_c, out_a)
+
+
+def test_attention_decode_cluster_refuses_what_it_cannot_do(ops16):
+    from ctypes import c_float, c_void_p
+    lib = ops16.fast.lib
+    z = c_void_p(0)
+    args = lambda d, splits, fuse: (z, 1024, z, 1024, z, z, z, 4, z, z, 2, 8, 2, d, c_float(1.0), 0, 16, 8,
+                                    splits, fuse, z, z, c_float(1e-6), z, 0, 0, z, z)
+    assert lib.leone_attention_decode_cluster(*args(128, 9, 0)) != 0        # more splits than a cluster holds
+    assert lib.leone_attention_decode_cluster(*args(96, 2, 1)) != 0         # fused preparation needs d 64 or 128
