@@ -53,6 +53,19 @@ struct GemmParams {
   int* counters;
   int* status;
   long long* trace;  // optional: 8 nanosecond time stamps per block (see leone_gemm_tc_set_trace)
+  // RMSNorm around the product (swapped orientation), so that a norm between two products
+  // needs no kernel of its own.  The product before the norm (fp32 output, epilogue 1 or 2)
+  // also writes norm_out_x[m][n] = bf16(out[m][n] * norm_out_w[n]) and, per 32 weight rows, the
+  // sum of out[m][n]^2 into norm_out_ss[(n / 32)][m]; the product after the norm reads
+  // norm_out_x as its token operand and scales every output of token m by
+  // rsqrt(sum_p norm_in_ss[p][m] / K + norm_eps), which is W . rmsnorm(out).
+  __nv_bfloat16* norm_out_x;
+  const float* norm_out_w;
+  float* norm_out_ss;
+  int ld_norm_out;
+  const float* norm_in_ss;
+  int norm_in_parts;
+  float norm_eps;
 };
 
 __device__ __forceinline__ long long global_ns() {
@@ -81,7 +94,11 @@ __device__ __forceinline__ Unit unit_of(int u, const GemmParams& p) {
 // before anything is stored, because the residual may be the output itself).
 template <int NC>
 __device__ __forceinline__ void finish_swapped(const GemmParams& p, float (&v)[NC], const float (&r)[NC],
-                                               int n, int m0, int c, int lane) {
+                                               int n, int m0, int c, int lane, const float* rs_s) {
+  if (p.norm_in_ss != nullptr) {
+#pragma unroll
+    for (int j = 0; j < NC; ++j) v[j] *= rs_s[c + j];
+  }
   if (p.epilogue == 3) {
     // rows come in groups of 32: 16 gate rows then their 16 up rows
     const int col = (n >> 5) * 16 + (lane & 15);
@@ -94,7 +111,9 @@ __device__ __forceinline__ void finish_swapped(const GemmParams& p, float (&v)[N
         ((__nv_bfloat16*)p.out)[(size_t)m * p.ldc + col] = __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
       }
     }
-  } else if (n < p.N) {
+    return;
+  }
+  if (n < p.N) {
     if (p.epilogue == 2) {
 #pragma unroll
       for (int j = 0; j < NC; ++j) v[j] += r[j];
@@ -107,6 +126,21 @@ __device__ __forceinline__ void finish_swapped(const GemmParams& p, float (&v)[N
         if (p.epilogue == 0) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(v[j]);
         else ((float*)p.out)[o] = v[j];
       }
+    }
+  }
+  if (p.norm_out_x != nullptr) {
+    // the operand of the product after the following norm, and this warp's 32 rows' share of
+    // the sums of squares (the lanes of a warp are 32 consecutive weight rows)
+    const float gw = n < p.N ? p.norm_out_w[n] : 0.f;
+#pragma unroll
+    for (int j = 0; j < NC; ++j) {
+      const int m = m0 + c + j;
+      const float val = n < p.N ? v[j] : 0.f;
+      if (n < p.N && m < p.M) p.norm_out_x[(size_t)m * p.ld_norm_out + n] = __float2bfloat16_rn(val * gw);
+      float sq = val * val;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+      if (lane == 0 && m < p.M && n < p.N) p.norm_out_ss[(size_t)(n >> 5) * p.M + m] = sq;
     }
   }
 }
@@ -145,6 +179,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __shared__ uint32_t tmem_holder;
   __shared__ int gave_up;
   __shared__ int last_flag;
+  __shared__ float rs_s[kSwap ? BN : 1];          // per token: the scale of the norm before this product
+  __shared__ float red_s[kSwap ? 4 * BN : 1];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) stamp(p, 7);                       // first instruction of the block
@@ -264,6 +300,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const int ep_tid = (warp - 2) * 32 + lane;        // 0..127
     int it = 0;
     pdl_wait();      // outputs, residual and the split-K workspace may be in use until here
+    if constexpr (kSwap) {
+      if (p.norm_in_ss != nullptr) {
+        // the scale of every token from the partial sums the product before the norm left:
+        // thread t adds parts t, t + 128, ..; then a fixed tree over the warp and the four warps
+        // (the loads of a batch of tokens are issued together: one round trip per batch)
+        constexpr int kBatch = BN < 32 ? BN : 32;
+        for (int mb = 0; mb < p.M && mb < BN; mb += kBatch) {
+          float part[kBatch];
+#pragma unroll
+          for (int j = 0; j < kBatch; ++j) part[j] = 0.f;
+          for (int q = ep_tid; q < p.norm_in_parts; q += 128) {
+            const float* row = p.norm_in_ss + (size_t)q * p.M + mb;
+#pragma unroll
+            for (int j = 0; j < kBatch; ++j)
+              if (mb + j < p.M) part[j] += row[j];
+          }
+#pragma unroll
+          for (int j = 0; j < kBatch; ++j) {
+            float v = part[j];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0) red_s[(warp - 2) * BN + mb + j] = v;
+          }
+        }
+        named_barrier_sync(1, 128);
+        for (int m = ep_tid; m < BN; m += 128) {
+          const float ss = red_s[m] + red_s[BN + m] + red_s[2 * BN + m] + red_s[3 * BN + m];
+          rs_s[m] = m < p.M ? rsqrtf(ss / (float)p.K + p.norm_eps) : 0.f;
+        }
+        named_barrier_sync(1, 128);
+      }
+    }
     for (int t = blockIdx.x; t < total && !*giveup; t += gridDim.x, ++it) {
       const Unit un = unit_of(t, p);
       const int tile = un.tile, split = un.split, nsplit = un.nsplit;
@@ -429,7 +497,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           } else {
             tmem_ld16(taddr + c, v);
           }
-          finish_swapped<16>(p, v, r, n, m0, c, lane);
+          finish_swapped<16>(p, v, r, n, m0, c, lane, rs_s);
         }
       }
       if (nsplit == 1) {
@@ -483,7 +551,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
               }
             }
           }
-          finish_swapped<NC>(p, v, r, n, m0, c, lane);
+          finish_swapped<NC>(p, v, r, n, m0, c, lane, rs_s);
         }
       }
     }
@@ -591,6 +659,9 @@ extern "C" int leone_gemm_tc_tiles(int m, int n) {
   return ((n + kTileW - 1) / kTileW) * ((m + bn - 1) / bn);
 }
 
+// Parts of the sums of squares a product with n outputs leaves for the norm after it.
+extern "C" int leone_gemm_tc_norm_parts(int n) { return (n + 31) / 32; }
+
 // Workspace floats and counters needed when `split_tiles` tiles are split `splits` ways;
 // both 0 when splits == 1.
 extern "C" void leone_gemm_tc_scratch(int m, int split_tiles, int splits, long long* workspace_floats,
@@ -618,6 +689,12 @@ extern "C" int leone_gemm_tc_cluster_capacity(int m, int splits) {
 // The first `full_tiles` tiles (in the kernel's tile order) are computed whole; the others have K
 // split `splits` ways.  splits > 1 needs `workspace` (fp32) and zeroed `counters` of the sizes
 // leone_gemm_tc_scratch gives for (tiles - full_tiles).  More than 256 tokens are never split.
+// A norm between two products without a kernel of its own (at most 256 tokens):
+//  norm_out_x != null (epilogue 1 or 2): also write norm_out_x[m][n] = bf16(out[m][n] * norm_out_w[n])
+//    (row stride ld_norm_out) and norm_out_ss[(n / 32)][m] = sum of out[m][n]^2 over those 32 rows;
+//    leone_gemm_tc_norm_parts(n) gives the number of parts;
+//  norm_in_ss != null: every output of token m is scaled by rsqrt(sum_p norm_in_ss[p][m] / k + norm_eps)
+//    (x is then the norm_out_x another product wrote).
 // cluster != 0: the splits of a tile form a thread-block cluster and are summed through
 // distributed shared memory (needs full_tiles == 0, 2 <= splits <= 8, at most 256 tokens, and
 // tiles * splits blocks resident at once: see leone_gemm_tc_cluster_capacity); workspace and
@@ -625,7 +702,9 @@ extern "C" int leone_gemm_tc_cluster_capacity(int m, int splits) {
 extern "C" int leone_gemm_tc(const void* x, const void* w, void* out, const float* residual, int m,
                              int n, int k, int ldx, int ldw, int ldc, int epilogue, int splits,
                              int full_tiles, float* workspace, int* counters, int* status,
-                             int sm_count, int cluster, cudaStream_t stream) {
+                             int sm_count, int cluster, void* norm_out_x, const float* norm_out_w,
+                             float* norm_out_ss, int ld_norm_out, const float* norm_in_ss,
+                             int norm_in_parts, float norm_eps, cudaStream_t stream) {
   if (m <= 0 || n <= 0) return 0;
   if (k <= 0 || (k % 8) != 0 || (ldx % 8) != 0 || (ldw % 8) != 0) return kRefusedAlignment;
   if (epilogue < 0 || epilogue > 3 || splits < 1 || sm_count < 1) return kRefusedSize;
@@ -637,6 +716,10 @@ extern "C" int leone_gemm_tc(const void* x, const void* w, void* out, const floa
   // every split must own at least one k-block
   while (splits > 1 && (splits - 1) * ((k_blocks + splits - 1) / splits) >= k_blocks) --splits;
   if (splits == 1) cluster = 0;
+  if (norm_out_x != nullptr &&
+      (m > 256 || (epilogue != 1 && epilogue != 2) || norm_out_w == nullptr || norm_out_ss == nullptr))
+    return kRefusedSize;
+  if (norm_in_ss != nullptr && (m > 256 || norm_in_parts < 1)) return kRefusedSize;
   if (cluster && (full_tiles != 0 || splits > 8 || m > 256)) return kRefusedSize;
   if (splits > 1 && !cluster && (workspace == nullptr || counters == nullptr)) return kRefusedSize;
   const int tiles = leone_gemm_tc_tiles(m, n);
@@ -650,7 +733,8 @@ extern "C" int leone_gemm_tc(const void* x, const void* w, void* out, const floa
   r = make_tensor_map_2d(&mx, x, (uint64_t)m, (uint64_t)k, (uint64_t)ldx, swap ? (uint32_t)bn : kTileW);
   if (r != 0) return r;
   GemmParams p{out, residual, m, n, k, ldc, epilogue, splits, full_tiles, workspace, counters, status,
-               g_gemm_trace};
+               g_gemm_trace, (__nv_bfloat16*)norm_out_x, norm_out_w, norm_out_ss, ld_norm_out, norm_in_ss,
+               norm_in_parts, norm_eps};
   if (g_gemm_trace != nullptr) g_gemm_trace += g_gemm_trace_stride;
   if (!swap) return launch_gemm<256, false>(mw, mx, p, sm_count, stream);
   if (cluster) {

@@ -129,8 +129,18 @@ class Model:
         rt = self.rt
         hidden = rt.buffer("hidden", ctx.n_tokens, self.hidden_size, torch.float32)
         rt.ops.embedding(self.embedding, ctx.token_ids, hidden, ctx.status)
-        for pos, idx in enumerate(self.spec.run_order):
-            self.blocks[idx].forward(ctx, ctx.cache_view(pos), hidden)
+        order = self.spec.run_order
+        pre = None           # the entry norm of the next block, if the last product before it folded it in
+        for pos, idx in enumerate(order):
+            block = self.blocks[idx]
+            if not getattr(block, "chains_norms", False):
+                block.forward(ctx, ctx.cache_view(pos), hidden)
+                pre = None
+                continue
+            after = None
+            if pos + 1 < len(order) and getattr(self.blocks[order[pos + 1]], "chains_norms", False):
+                after = self.blocks[order[pos + 1]].entry_norm(ctx, hidden)
+            pre = block.forward(ctx, ctx.cache_view(pos), hidden, pre=pre, after=after)
         return self.logits(ctx, hidden)
 
     def logits(self, ctx, hidden) -> Optional[torch.Tensor]:

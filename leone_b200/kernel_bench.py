@@ -55,7 +55,7 @@ def _time(fn, reps: int, warmup: int, flush=None, per_graph: int = 1) -> float:
     return times[len(times) // 2]
 
 
-def bench_gemm(ops, m, n, k, splits, epilogue, reps, warmup, flush, trace=False, cluster=False):
+def bench_gemm(ops, m, n, k, splits, epilogue, reps, warmup, flush, trace=False, cluster=False, norm="none"):
     fast = ops.fast
     x = torch.randn((m, k), device=DEV).to(torch.bfloat16)
     # several copies of the weight so successive launches do not hit L2
@@ -71,17 +71,27 @@ def bench_gemm(ops, m, n, k, splits, epilogue, reps, warmup, flush, trace=False,
     if splits is None:
         splits, full_tiles, cluster = fast.choose_splits(m, n, k)
 
+    # an RMSNorm folded into this product: "out" = it is the product before the norm, "in" = after
+    norm_out = norm_in = None
+    if norm == "out":
+        norm_out = (torch.empty((m, n), device=DEV, dtype=torch.bfloat16), torch.ones(n, device=DEV),
+                    torch.empty((fast.norm_parts(n), m), device=DEV))
+    elif norm == "in":
+        parts = fast.norm_parts(k)
+        norm_in = (torch.rand((parts, m), device=DEV), parts, 1e-6)
+
     def run():
         w = ws[state["i"] % copies]
         state["i"] += 1
-        fast._gemm(x, w, out, epilogue, res, n, splits=splits, full_tiles=full_tiles, cluster=cluster)
+        fast._gemm(x, w, out, epilogue, res, n, splits=splits, full_tiles=full_tiles, cluster=cluster,
+                   norm_in=norm_in, norm_out=norm_out)
 
     ms = _time(run, reps, warmup, flush, per_graph=copies)
     if trace:
         _print_trace(ops, run, copies)
     bytes_ = n * k * 2 + m * k * 2 + out.numel() * out.element_size()
     flops = 2.0 * m * n * k
-    return dict(kernel="gemm_tc", m=m, n=n, k=k, splits=splits, full_tiles=full_tiles, cluster=bool(cluster), epilogue=epilogue, us=ms * 1e3,
+    return dict(kernel="gemm_tc", m=m, n=n, k=k, norm=norm, splits=splits, full_tiles=full_tiles, cluster=bool(cluster), epilogue=epilogue, us=ms * 1e3,
                 gbs=bytes_ / ms / 1e6, tflops=flops / ms / 1e9)
 
 
@@ -208,6 +218,8 @@ def main(argv=None) -> int:
     ap.add_argument("--trace", action="store_true", help="gemm: print the kernel's phase time stamps")
     ap.add_argument("--prep", choices=["none", "kernel", "fused"], default="none",
                     help="decode-attention: where q/k norm, rotary and cache write are done")
+    ap.add_argument("--norm", choices=["none", "in", "out"], default="none",
+                    help="gemm: fold an RMSNorm after (out) or before (in) the product into it")
     ap.add_argument("--cluster", action="store_true",
                     help="gemm with --splits: sum the splits inside thread-block clusters")
     args = ap.parse_args(argv)
@@ -218,7 +230,7 @@ def main(argv=None) -> int:
     rows = []
     if args.what == "gemm":
         rows.append(bench_gemm(ops, args.m, args.n, args.k, args.splits, args.epilogue, args.reps, args.warmup, flush,
-                               args.trace, args.cluster))
+                               args.trace, args.cluster, args.norm))
     elif args.what == "layer-shapes":
         h, inter, qkv = 4096, 12288, (args.heads + 2 * args.kv_heads) * args.head_dim
         for name, n, k, epi in (("qkv", qkv, h, 0), ("o_proj", h, args.heads * args.head_dim, 2),

@@ -166,9 +166,41 @@ class CudaOps:
                                          _ptr(residual), m, n, k, x.stride(0), w.stride(0),
                                          out.stride(0), self._stream()), "gemm_simt")
 
-    def linear(self, x, w: PreparedMatrix, out, residual=None):
+    def linear_fuses_norm(self, n_tokens: int, w: PreparedMatrix) -> bool:
+        """True if a product of ``n_tokens`` tokens with ``w`` can take part in a fused RMSNorm:
+        as the product before the norm (``linear(..., norm_out=d)`` also leaves
+        ``d.xn = bf16(out * d.weight)`` and the sums of ``out^2`` in ``d.ss``) or as the one
+        after it (``linear(d.xn, ..., norm_in=d)`` scales its rows by the norm's factor)."""
+        wt = w.weight
+        return (self.fast is not None and self.fast.fuses_norm(n_tokens) and wt.dtype == torch.bfloat16
+                and wt.shape[0] % 8 == 0 and wt.shape[1] % 8 == 0 and wt.stride(0) % 8 == 0
+                and wt.data_ptr() % 16 == 0)
+
+    def norm_parts(self, n: int) -> int:
+        """Rows of the ``ss`` buffer a product with ``n`` outputs fills for the norm after it."""
+        return self.fast.norm_parts(n)
+
+    def _norm_args(self, m, w, norm_in, norm_out):
+        ni = no = None
+        if norm_in is not None:
+            d = norm_in
+            _need(self.linear_fuses_norm(m, w) and d.ss.dtype == torch.float32 and d.ss.is_contiguous()
+                  and d.ss.shape == (d.parts, m), "linear: norm_in layout")
+            ni = (d.ss, d.parts, d.eps)
+        if norm_out is not None:
+            d = norm_out
+            _need(self.linear_fuses_norm(m, w) and d.weight.dtype == torch.float32 and d.weight.is_contiguous()
+                  and d.weight.numel() == w.out_features and d.xn.dtype == torch.bfloat16
+                  and d.xn.shape == (m, w.out_features) and d.xn.stride(1) == 1
+                  and d.ss.dtype == torch.float32 and d.ss.is_contiguous()
+                  and d.ss.shape == (self.norm_parts(w.out_features), m), "linear: norm_out layout")
+            no = (d.xn, d.weight, d.ss)
+        return ni, no
+
+    def linear(self, x, w: PreparedMatrix, out, residual=None, norm_in=None, norm_out=None):
         """``out = x @ w.T`` (+ ``residual``).  ``out`` in x's dtype, or fp32 (then a fp32
-        ``residual`` may be added; it may be ``out`` itself)."""
+        ``residual`` may be added; it may be ``out`` itself).  ``norm_in`` / ``norm_out``: see
+        :meth:`linear_fuses_norm`."""
         m, k = x.shape
         _need(k == w.in_features and out.shape == (m, w.out_features), "linear: shapes do not chain")
         _need(x.dtype == w.dtype and x.stride(1) == 1 and out.stride(1) == 1, "linear: dtype/stride")
@@ -184,18 +216,29 @@ class CudaOps:
             epilogue = 0
         if m == 0:
             return
+        if norm_in is not None or norm_out is not None:
+            _need(norm_out is None or epilogue in (1, 2), "linear: norm_out needs fp32 output")
+            ni, no = self._norm_args(m, w, norm_in, norm_out)
+            _need(self.fast.linear(x, w, out, epilogue, residual, ni, no), "linear: fused norm off the tensor-core path")
+            self.launches += 1
+            return
         if self.fast is not None and self.fast.linear(x, w, out, epilogue, residual):
             self.launches += 1
             return
         self._gemm_simt(x, w.weight, out, epilogue, residual)
 
-    def linear_swiglu(self, x, w_gate_up: PreparedMatrix, out):
+    def linear_swiglu(self, x, w_gate_up: PreparedMatrix, out, norm_in=None):
         """``out = silu(x @ gate.T) * (x @ up.T)`` for a matrix from ``prepare_gate_up``."""
         m = x.shape[0]
         inter = w_gate_up.out_features // 2
         _need(out.shape == (m, inter) and out.dtype == x.dtype and out.is_contiguous(),
               "linear_swiglu: output shape")
         if m == 0:
+            return
+        if norm_in is not None:
+            ni, _ = self._norm_args(m, w_gate_up, norm_in, None)
+            _need(self.fast.linear_swiglu(x, w_gate_up, out, ni), "linear_swiglu: fused norm off the tensor-core path")
+            self.launches += 1
             return
         if self.fast is not None and self.fast.linear_swiglu(x, w_gate_up, out):
             self.launches += 1

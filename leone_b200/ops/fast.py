@@ -33,6 +33,9 @@ class FastKernels:
         # LEONE_NO_CLUSTERS=1 sums split-K partial tiles through a workspace instead of inside clusters
         self.use_clusters = os.environ.get("LEONE_NO_CLUSTERS", "0") != "1"
         self._cluster_capacity = {}
+        # LEONE_NO_FUSED_NORM=1 keeps every RMSNorm a kernel of its own
+        self.fuse_norm = os.environ.get("LEONE_NO_FUSED_NORM", "0") != "1"
+        self.fuse_norm_tokens = 32
         # LEONE_NO_FUSED_DECODE=1 keeps q/k norm, rotation and cache write in their own kernel
         self.fuse_decode = os.environ.get("LEONE_NO_FUSED_DECODE", "0") != "1"
         self.max_cluster = int(os.environ.get("LEONE_MAX_CLUSTER", "8"))
@@ -116,10 +119,16 @@ class FastKernels:
         return (k % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
                 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
-    def _gemm(self, x, w, out, epilogue, residual, n_rows, splits=None, full_tiles=0, cluster=False) -> bool:
+    def _gemm(self, x, w, out, epilogue, residual, n_rows, splits=None, full_tiles=0, cluster=False,
+              norm_in=None, norm_out=None) -> bool:
         """``splits=None`` lets :meth:`choose_splits` decide; otherwise tiles from
         ``full_tiles`` on are split ``splits`` ways, summed through a workspace or, with
-        ``cluster``, inside a thread-block cluster."""
+        ``cluster``, inside a thread-block cluster.
+
+        ``norm_out=(xn, weight, ss)``: the product (fp32 output) also leaves
+        ``xn = bf16(out * weight)`` and the partial sums of ``out^2`` in ``ss`` ``[parts, m]``
+        for the RMSNorm that follows it; ``norm_in=(ss, parts, eps)``: ``x`` is such an ``xn``
+        and every output row is scaled by the norm's ``rsqrt(mean + eps)``."""
         m, k = x.shape
         if splits is None:
             splits, full_tiles, cluster = self.choose_splits(m, n_rows, k)
@@ -129,19 +138,32 @@ class FastKernels:
             floats, counters = c_longlong(0), c_int(0)
             self.lib.leone_gemm_tc_scratch(m, max(tiles - full_tiles, 0), splits, byref(floats), byref(counters))
             ws, ct = self._scratch(floats.value, counters.value)
+        from ctypes import c_float
+        no = (None, None, None, 0) if norm_out is None else \
+            (_ptr(norm_out[0]), _ptr(norm_out[1]), _ptr(norm_out[2]), norm_out[0].stride(0))
+        ni = (None, 0, c_float(0.0)) if norm_in is None else (_ptr(norm_in[0]), int(norm_in[1]), c_float(norm_in[2]))
         code = self.lib.leone_gemm_tc(_ptr(x), _ptr(w), _ptr(out), _ptr(residual), m, n_rows, k,
                                       x.stride(0), w.stride(0), out.stride(0), epilogue, splits,
                                       full_tiles, _ptr(ws), _ptr(ct), _ptr(self.status), self.sm_count,
-                                      1 if cluster else 0, self._stream())
+                                      1 if cluster else 0, *no, *ni, self._stream())
         if code != 0:
             raise RuntimeError(f"gemm_tc refused or failed with code {code} for m={m} n={n_rows} k={k} "
                                f"splits={splits} cluster={cluster}")
         return True
 
-    def linear(self, x, w, out, epilogue, residual) -> bool:
+    def fuses_norm(self, m: int) -> bool:
+        """Whether the products of ``m`` tokens carry an RMSNorm between them.  The kernels take
+        up to 256 tokens; beyond 32 the extra work in the two epilogues was measured to cost
+        more than the norm kernel it replaces."""
+        return self.use_tensor_cores and self.fuse_norm and 0 < m <= self.fuse_norm_tokens
+
+    def norm_parts(self, n: int) -> int:
+        return int(self.lib.leone_gemm_tc_norm_parts(n))
+
+    def linear(self, x, w, out, epilogue, residual, norm_in=None, norm_out=None) -> bool:
         if not self._tc_ok(x, w.weight, out):
             return False
-        return self._gemm(x, w.weight, out, epilogue, residual, w.out_features)
+        return self._gemm(x, w.weight, out, epilogue, residual, w.out_features, norm_in=norm_in, norm_out=norm_out)
 
     # -- gate/up --------------------------------------------------------------------------
     def prepare_gate_up(self, gate, up):
@@ -158,10 +180,10 @@ class FastKernels:
         m.gate_up_layout = "stacked"
         return m
 
-    def linear_swiglu(self, x, w, out) -> bool:
+    def linear_swiglu(self, x, w, out, norm_in=None) -> bool:
         if getattr(w, "gate_up_layout", None) != "interleaved16" or not self._tc_ok(x, w.weight, out):
             return False
-        return self._gemm(x, w.weight, out, 3, None, w.out_features)
+        return self._gemm(x, w.weight, out, 3, None, w.out_features, norm_in=norm_in)
 
     # -- attention ------------------------------------------------------------------------
     def decode_splits(self, n_seqs: int, n_kv: int, g: int, max_ctx: int) -> int:

@@ -22,11 +22,14 @@ import math
 import torch
 
 from ..registry import MIXERS
-from .base import Mixer, PagedKV, WeightSpec
+from .base import DeferredNorm, Mixer, PagedKV, WeightSpec
 
 
 @MIXERS.register("attention")
 class Attention(Mixer):
+    accepts_deferred_norm = True
+    fuses_following_norm = True
+
     def __init__(self, params, rt, position_encodings=None):
         super().__init__(params, rt)
         self.hidden = int(params["hidden_size"])
@@ -78,11 +81,28 @@ class Attention(Mixer):
     def cache_request(self):
         return PagedKV(self.n_kv, self.d, self.window)
 
-    def forward(self, ctx, cache, x, hidden):
+    def _out_proj(self, attn, hidden, then):
+        """``hidden += W_o attn``; folds the norm that follows (``then``) into the product if it can."""
+        ops = self.rt.ops
+        n = hidden.shape[0]
+        if then is not None and hasattr(ops, "linear_fuses_norm") and ops.linear_fuses_norm(n, self.w_o):
+            then.prepare(self.rt, ops.norm_parts(self.hidden))
+            ops.linear(attn, self.w_o, hidden, residual=hidden, norm_out=then)
+            then.ready = True
+        else:
+            ops.linear(attn, self.w_o, hidden, residual=hidden)
+
+    def forward(self, ctx, cache, x, hidden, then=None):
         rt = self.rt
-        n = x.shape[0]
+        n = hidden.shape[0]
         qkv = rt.buffer("qkv", n, self.qkv_cols, rt.dtype)
-        rt.ops.linear(x, self.w_qkv, qkv)
+        if isinstance(x, DeferredNorm):
+            if x.ready and rt.ops.linear_fuses_norm(n, self.w_qkv):
+                rt.ops.linear(x.xn, self.w_qkv, qkv, norm_in=x)          # the norm's factor in the epilogue
+            else:
+                rt.ops.linear(x.materialize(), self.w_qkv, qkv)
+        else:
+            rt.ops.linear(x, self.w_qkv, qkv)
         table, rotary_dim, pairing = None, 0, None
         if self.pos is not None:
             table = self.pos.rotary_table()
@@ -100,7 +120,7 @@ class Attention(Mixer):
             rt.ops.attention(ctx, qkv, attn, self.n_q, self.n_kv, self.d, self.scale, self.window, cache,
                              fuse=dict(q_w=self.q_norm_f32, k_w=self.k_norm_f32, eps=self.eps, rope=table,
                                        write_cache=True))
-            rt.ops.linear(attn, self.w_o, hidden, residual=hidden)
+            self._out_proj(attn, hidden, then)
             return
         # q/k norm, rotation and the cache write are one kernel; an encoding without a
         # rotary table is applied by the encoding itself between norm and cache write.
@@ -118,4 +138,4 @@ class Attention(Mixer):
                                       cache if cache.writes else None)
         rt.ops.attention(ctx, qkv, attn, self.n_q, self.n_kv, self.d, self.scale,
                          self.window, cache)
-        rt.ops.linear(attn, self.w_o, hidden, residual=hidden)
+        self._out_proj(attn, hidden, then)

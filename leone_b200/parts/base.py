@@ -13,8 +13,11 @@ Interfaces, by kind:
     rows in the run dtype (``rows``: optional int32 device indices to gather).
 
 ``Mixer.forward(ctx, cache, x, hidden) -> None``
-    ``x`` are the normed tokens ``[N, hidden]``; the mixer adds its output to
-    the fp32 ``hidden`` in place.  ``cache`` is what ``cache_request()`` asked
+    ``x`` are the normed tokens ``[N, hidden]``; the mixer adds its output to the
+    fp32 ``hidden`` in place.  Optional fusion of the norms around it: a mixer
+    that sets ``accepts_deferred_norm`` may be given a :class:`DeferredNorm`
+    as ``x``; one that sets ``fuses_following_norm`` takes ``then=`` (the
+    :class:`DeferredNorm` of the norm after its residual add, or ``None``).  ``cache`` is what ``cache_request()`` asked
     for: a :class:`PagedCacheView`, a :class:`StateView` or ``None``.
 
 ``FeedForward.forward(ctx, x, hidden) -> None``
@@ -83,6 +86,38 @@ class StateView:
     writes: bool = True
 
 
+@dataclass
+class DeferredNorm:
+    """An RMSNorm folded into the products around it instead of run as a kernel.
+
+    The part whose last product writes the residual stream (``fuses_following_norm``) is handed
+    this object as ``then``; if its product can, it calls :meth:`prepare`, passes the object as
+    ``norm_out`` (the product then also leaves ``xn = bf16(hidden * weight)`` and the sums of
+    ``hidden^2`` in ``ss``) and sets ``ready``.  The part that consumes the normed tokens
+    (``accepts_deferred_norm``) is given the object instead of a tensor: if ``ready`` it feeds
+    ``xn`` to its first product with ``norm_in=self``; otherwise it calls :meth:`materialize`,
+    which runs the norm as a kernel of its own."""
+    norm: "Norm"
+    ctx: object
+    hidden: torch.Tensor
+    weight: torch.Tensor          # fp32
+    eps: float
+    tag: str = "a"                # names the buffers: two deferred norms alive together differ in it
+    xn: Optional[torch.Tensor] = None
+    ss: Optional[torch.Tensor] = None
+    parts: int = 0
+    ready: bool = False
+
+    def prepare(self, rt, parts: int) -> None:
+        n, size = self.hidden.shape
+        self.parts = parts
+        self.xn = rt.buffer(f"deferred_norm_x_{self.tag}", n, size, rt.dtype)
+        self.ss = rt.buffer(f"deferred_norm_ss_{self.tag}_{n}", parts, n, torch.float32)
+
+    def materialize(self) -> torch.Tensor:
+        return self.norm.forward(self.ctx, self.hidden)
+
+
 class Runtime:
     """What every part gets at construction: device, run dtype, kernels and scratch buffers."""
 
@@ -128,8 +163,18 @@ class Norm(Part):
     def forward(self, ctx, hidden, rows=None):
         raise NotImplementedError
 
+    def defer(self, ctx, hidden, tag="a") -> Optional[DeferredNorm]:
+        """A :class:`DeferredNorm` if this norm is ``x * w / sqrt(mean(x^2) + eps)`` and may be
+        folded into the products around it; ``None`` (the default) if it must run itself."""
+        return None
+
 
 class Mixer(Part):
+    # True if ``forward`` copes with ``x`` being a DeferredNorm instead of the normed tokens
+    accepts_deferred_norm = False
+    # True if ``forward`` takes ``then=DeferredNorm`` (the norm that follows its residual add)
+    fuses_following_norm = False
+
     def cache_request(self):
         return None
 
@@ -138,6 +183,9 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    accepts_deferred_norm = False     # as for Mixer
+    fuses_following_norm = False
+
     def forward(self, ctx, x, hidden):
         raise NotImplementedError
 

@@ -8,7 +8,7 @@ crates/leone-cuda/cuda/ie_cuda.cu:2357-2380).
 from __future__ import annotations
 
 from ..registry import NORMS
-from .base import Norm, WeightSpec
+from .base import DeferredNorm, Norm, WeightSpec
 
 
 @NORMS.register("rms_norm")
@@ -18,13 +18,17 @@ class RMSNorm(Norm):
         self.size = int(params["size"])
         self.eps = float(params["eps"])
         self.name = params.get("name", "weight")
-        self.weight = None
+        self.weight = self.weight_f32 = None
 
     def weight_specs(self):
         return [WeightSpec(self.name, (self.size,), role="norm", std=0.1)]
 
     def load(self, tensors):
         self.weight = tensors[self.name]
+        self.weight_f32 = self.weight.float().contiguous()    # for a product that applies the norm itself
+
+    def defer(self, ctx, hidden, tag="a"):
+        return DeferredNorm(self, ctx, hidden, self.weight_f32, self.eps, tag)
 
     def forward(self, ctx, hidden, rows=None, out_name="normed"):
         n = hidden.shape[0] if rows is None else rows.shape[0]

@@ -10,11 +10,14 @@ from __future__ import annotations
 import torch
 
 from ..registry import FEED_FORWARDS
-from .base import FeedForward, WeightSpec
+from .base import DeferredNorm, FeedForward, WeightSpec
 
 
 @FEED_FORWARDS.register("swiglu")
 class SwiGLU(FeedForward):
+    accepts_deferred_norm = True
+    fuses_following_norm = True
+
     def __init__(self, params, rt):
         super().__init__(params, rt)
         self.hidden = int(params["hidden_size"])
@@ -37,8 +40,20 @@ class SwiGLU(FeedForward):
     def weight_bytes(self):
         return (2 * self.inter * self.hidden + self.hidden * self.inter) * self.rt.dtype.itemsize
 
-    def forward(self, ctx, x, hidden):
-        n = x.shape[0]
+    def forward(self, ctx, x, hidden, then=None):
+        n = hidden.shape[0]
+        ops = self.rt.ops
         act = self.rt.buffer("ffn_act", n, self.inter, self.rt.dtype)
-        self.rt.ops.linear_swiglu(x, self.w_gate_up, act)
-        self.rt.ops.linear(act, self.w_down, hidden, residual=hidden)
+        if isinstance(x, DeferredNorm):
+            if x.ready and ops.linear_fuses_norm(n, self.w_gate_up):
+                ops.linear_swiglu(x.xn, self.w_gate_up, act, norm_in=x)      # the norm's factor in the epilogue
+            else:
+                ops.linear_swiglu(x.materialize(), self.w_gate_up, act)
+        else:
+            ops.linear_swiglu(x, self.w_gate_up, act)
+        if then is not None and hasattr(ops, "linear_fuses_norm") and ops.linear_fuses_norm(n, self.w_down):
+            then.prepare(self.rt, ops.norm_parts(self.hidden))
+            ops.linear(act, self.w_down, hidden, residual=hidden, norm_out=then)
+            then.ready = True
+        else:
+            ops.linear(act, self.w_down, hidden, residual=hidden)

@@ -19,7 +19,12 @@ def ops32():
 @pytest.fixture(scope="module")
 def ops16():
     from leone_b200.ops.cuda import CudaOps
-    return CudaOps(DEV, torch.bfloat16)
+    ops = CudaOps(DEV, torch.bfloat16)
+    status = torch.zeros(4, device=DEV, dtype=torch.int32)
+    ops.bind_status(status)                 # a wait that runs out inside a kernel shows here
+    yield ops
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 0, 0, 0], f"a kernel reported {ops.describe_status(int(status[0]))}: {status.tolist()}"
 
 
 def _gen(seed):
@@ -223,6 +228,76 @@ def test_gemm_tc_cluster_split(ops16, m, n, k, splits):
         g = x.double() @ gate.double().t()
         u = x.double() @ up.double().t()
         _close(act, g / (1 + torch.exp(-g)) * u, 2 ** -7, 1e-4, "cluster swiglu")
+
+
+@pytest.mark.parametrize("m,n,k,splits,cluster", [(1, 384, 4096, 1, False), (8, 1000, 1032, 1, False),
+                                                  (5, 640, 520, 3, True), (16, 4096, 4096, 4, True),
+                                                  (17, 256, 2048, 2, True), (33, 1024, 1024, 5, True),
+                                                  (64, 520, 4096, 3, False), (200, 384, 768, 6, True)])
+def test_gemm_tc_norm_between_products(ops16, m, n, k, splits, cluster):
+    """An RMSNorm folded into the product before it (which leaves bf16(out * weight) and the sums
+    of out^2) and the product after it (which scales its rows): against float64."""
+    fast = ops16.fast
+    x = _randn((m, k), 41, torch.bfloat16)
+    w1 = _randn((n, k), 42, torch.bfloat16, scale=0.05)
+    res = _randn((m, n), 43) * 2.0
+    res[0, 5] = 40.0                                       # one large element dominates a row's scale
+    g = 1 + 0.2 * _randn((n,), 44)
+    eps = 1e-5
+    hidden = res.clone()
+    parts = fast.norm_parts(n)
+    xn = torch.full((m, n), 7.0, device=DEV, dtype=torch.bfloat16)
+    ss = torch.full((parts, m), -1.0, device=DEV)
+    fast._gemm(x, w1, hidden, 2, hidden, n, splits=splits, cluster=cluster, norm_out=(xn, g, ss))
+    want_hidden = x.double() @ w1.double().t() + res.double()
+    _close(hidden, want_hidden, 1e-5, 2e-6 * math.sqrt(k) * 4, "the product before the norm")
+    h64 = hidden.double()
+    _close(xn, h64 * g.double(), 2 ** -8, 1e-6, "bf16(out * weight)")
+    _close(ss.sum(0), (h64 * h64).sum(1), 1e-5, 1e-6, "sums of squares")
+    # the product after the norm
+    n2 = 328
+    w2 = _randn((n2, n), 45, torch.bfloat16, scale=0.05)
+    rs = torch.rsqrt((h64 * h64).mean(dim=1, keepdim=True) + eps)
+    want = (xn.double() @ w2.double().t()) * rs
+    exact = (h64 * g.double() * rs) @ w2.double().t()
+    out = torch.empty((m, n2), device=DEV, dtype=torch.bfloat16)
+    for s2, cl in ((1, False), (2, True), (3, False)):
+        fast._gemm(xn, w2, out, 0, None, n2, splits=s2, cluster=cl, norm_in=(ss, parts, eps))
+        _close(out, want, 2 ** -8, 1e-3, f"the product after the norm, splits {s2}")
+        _close(out, exact, 2 ** -5, 5e-2, "against the exact norm")
+    inter = 160
+    gate, up = w2[:inter].contiguous(), w2[inter:2 * inter].contiguous()
+    gu = ops16.prepare_gate_up(gate, up)
+    act = torch.empty((m, inter), device=DEV, dtype=torch.bfloat16)
+    fast._gemm(xn, gu.weight, act, 3, None, 2 * inter, norm_in=(ss, parts, eps))
+    gg = (xn.double() @ gate.double().t()) * rs
+    uu = (xn.double() @ up.double().t()) * rs
+    _close(act, gg / (1 + torch.exp(-gg)) * uu, 2 ** -7, 1e-3, "swiglu after the norm")
+    torch.cuda.synchronize()
+    assert int(fast.status.abs().sum()) == 0
+
+
+def test_linear_with_norm_through_the_ops_table(ops16):
+    from leone_b200.parts.base import DeferredNorm, Runtime
+    m, k, n = 8, 512, 640
+    rt = Runtime(DEV, torch.bfloat16, ops16, 16)
+    x = _randn((m, k), 50, torch.bfloat16)
+    hidden = _randn((m, n), 51)
+    g = 1 + 0.1 * _randn((n,), 52)
+    w1 = ops16.prepare_matrix(_randn((n, k), 53, torch.bfloat16, scale=0.05))
+    w2 = ops16.prepare_matrix(_randn((384, n), 54, torch.bfloat16, scale=0.05))
+    assert ops16.linear_fuses_norm(m, w1) and ops16.linear_fuses_norm(m, w2)
+    assert not ops16.linear_fuses_norm(300, w1)           # prompt-sized portions keep the norm kernel
+    d = DeferredNorm(None, None, hidden, g, 1e-6, "t")
+    d.prepare(rt, ops16.norm_parts(n))
+    ops16.linear(x, w1, hidden, residual=hidden, norm_out=d)
+    out = torch.empty((m, 384), device=DEV, dtype=torch.bfloat16)
+    ops16.linear(d.xn, w2, out, norm_in=d)
+    normed = torch.empty((m, n), device=DEV, dtype=torch.bfloat16)
+    ops16.rms_norm(hidden, g, normed, 1e-6)
+    two = torch.empty_like(out)
+    ops16.linear(normed, w2, two)
+    _close(out, two.double(), 2 ** -6, 2e-2, "folded norm against the norm kernel")
 
 
 def test_gemm_tc_cluster_refusals(ops16):
