@@ -43,6 +43,16 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t* r) {
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                : "r"(addr));
 }
+__device__ __forceinline__ void ldmatrix_x2(uint32_t addr, uint32_t* r) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+}
+// Transposes an 8x8 matrix of 16-bit values held across the warp (thread t: row t/4, columns
+// 2*(t%4) and 2*(t%4)+1 in one register): turns an accumulator's layout into a B operand's.
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+  return d;
+}
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t* r) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
@@ -296,7 +306,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
 
 // ------------------------------------------------------------------------------------
 // Decode: one query token per sequence.  grid = (n_kv * head groups, splits, sequences).
-// The (up to 16) query heads of the KV head are the 16 rows of every MMA.  The block's key
+// The (up to 16) query heads of the KV head share every key and value tile.  The block's key
 // range is cut into groups of 16 keys dealt round-robin to the four warps; every warp runs a
 // private cp.async pipeline (kDecodeStages groups of keys and values in flight) and never
 // waits for the others inside the loop; the warps are merged once at the end.  With more than
@@ -304,76 +314,135 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
 // ------------------------------------------------------------------------------------
 constexpr int kDecodeStages = 3;
 
-// One group of 16 keys of a decode step for one warp: scores of the block's 16 query rows
-// against the group (rows of k_s), online softmax update, and the weighted values added to
-// o_acc.  Keys at or past k_end are masked.
-template <int D>
-__device__ __forceinline__ void decode_group(const __nv_bfloat16* k_s, const __nv_bfloat16* v_s,
-                                             const uint32_t (&q_frag)[D / 16][4], int key0, int k_end,
-                                             float sl2, float (&m_run)[2], float (&l_run)[2],
-                                             float (&o_acc)[D / 8][4], int lane) {
-  constexpr int kRow = D + 8;
-  float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+// One warp's share of a decode block.  The keys ride the MMA's M side and the block's query
+// heads its N side (NT tiles of 8 heads), so a head group of up to 8 costs one MMA per 16 keys
+// x 16 dims instead of two, and the scores, the exponentials and the output accumulator are
+// held for 8 columns, not 16 padded rows:
+//   S^T[16 keys x 8 heads]   = K[16 x D] . Q^T            (A = keys, row-major; B = Q rows)
+//   O^T[D x 8 heads]        += V^T[D x 16 keys] . P^T     (A = V through ldmatrix.trans;
+//                                                          B = P^T, the transposed S^T tile)
+// Thread t holds, of every 16 x 8 accumulator tile, rows t/4 and t/4+8 and columns 2*(t%4),
+// 2*(t%4)+1: its two head columns are fixed, so the running maximum and sum are per thread.
+template <int D, int NT>
+struct DecodeWarp {
+  static constexpr int kRow = D + 8;
+  uint32_t qb[D / 16][NT][2];
+  float m_run[NT][2], l_run[NT][2];
+  float o[D / 16][NT][4];
+
+  __device__ __forceinline__ void init() {
 #pragma unroll
-  for (int ks = 0; ks < D / 16; ++ks) {
-    uint32_t b[4];
-    const int mi = lane >> 3;
-    const int r = (mi >> 1) * 8 + (lane & 7), c = ks * 16 + (mi & 1) * 8;
-    ldmatrix_x4(smem_u32(k_s + r * kRow + c), b);
-    mma_16816(s[0], q_frag[ks], b[0], b[1]);
-    mma_16816(s[1], q_frag[ks], b[2], b[3]);
-  }
-  float tile_max[2] = {-INFINITY, -INFINITY};
+    for (int nt = 0; nt < NT; ++nt) {
+      m_run[nt][0] = m_run[nt][1] = -INFINITY;
+      l_run[nt][0] = l_run[nt][1] = 0.f;
 #pragma unroll
-  for (int nt = 0; nt < 2; ++nt)
+      for (int i = 0; i < D / 16; ++i)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int kj = key0 + nt * 8 + (lane & 3) * 2 + (j & 1);
-      const float v = kj < k_end ? s[nt][j] * sl2 : -INFINITY;
-      s[nt][j] = v;
-      tile_max[j >> 1] = fmaxf(tile_max[j >> 1], v);
+        for (int j = 0; j < 4; ++j) o[i][nt][j] = 0.f;
     }
-  float alpha[2], m_use[2];
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 1));
-    tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 2));
-    const float m_new = fmaxf(m_run[h], tile_max[h]);
-    m_use[h] = m_new == -INFINITY ? 0.f : m_new;
-    alpha[h] = m_run[h] == -INFINITY ? 0.f : exp2f(m_run[h] - m_use[h]);
-    m_run[h] = m_new;
-    l_run[h] *= alpha[h];
   }
+
+  // q_s: [16 heads][kRow], rows past the block's heads zero.
+  __device__ __forceinline__ void load_q(const __nv_bfloat16* q_s, int lane) {
 #pragma unroll
-  for (int i = 0; i < D / 8; ++i) {
-    o_acc[i][0] *= alpha[0];
-    o_acc[i][1] *= alpha[0];
-    o_acc[i][2] *= alpha[1];
-    o_acc[i][3] *= alpha[1];
+    for (int ks = 0; ks < D / 16; ++ks)
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const int mi = (lane >> 3) & 1;
+        ldmatrix_x2(smem_u32(q_s + (nt * 8 + (lane & 7)) * kRow + ks * 16 + mi * 8), qb[ks][nt]);
+      }
   }
-  uint32_t p_frag[4];
-#pragma unroll
-  for (int nt = 0; nt < 2; ++nt) {
-    const float p0 = exp2f(s[nt][0] - m_use[0]), p1 = exp2f(s[nt][1] - m_use[0]);
-    const float p2 = exp2f(s[nt][2] - m_use[1]), p3 = exp2f(s[nt][3] - m_use[1]);
-    l_run[0] += p0 + p1;
-    l_run[1] += p2 + p3;
-    p_frag[nt * 2] = pack_bf16(p0, p1);
-    p_frag[nt * 2 + 1] = pack_bf16(p2, p3);
-  }
-#pragma unroll
-  for (int np = 0; np < D / 16; ++np) {
-    uint32_t b[4];
+
+  // One group of 16 keys (rows of k_s / v_s) from absolute position key0; keys at or past
+  // k_end are masked.
+  __device__ __forceinline__ void group(const __nv_bfloat16* k_s, const __nv_bfloat16* v_s, int key0, int k_end,
+                                        float sl2, int lane) {
     const int mi = lane >> 3;
-    const int r = (mi & 1) * 8 + (lane & 7), c = np * 16 + (mi >> 1) * 8;
-    ldmatrix_x4_trans(smem_u32(v_s + r * kRow + c), b);
-    mma_16816(o_acc[np * 2], p_frag, b[0], b[1]);
-    mma_16816(o_acc[np * 2 + 1], p_frag, b[2], b[3]);
+    float st[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) st[nt][j] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      uint32_t a[4];
+      ldmatrix_x4(smem_u32(k_s + ((mi & 1) * 8 + (lane & 7)) * kRow + ks * 16 + (mi >> 1) * 8), a);
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) mma_16816(st[nt], a, qb[ks][nt][0], qb[ks][nt][1]);
+    }
+    uint32_t pb[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int kj = key0 + (lane >> 2) + (j >> 1) * 8;
+        const float v = kj < k_end ? st[nt][j] * sl2 : -INFINITY;
+        st[nt][j] = v;
+        tile_max[j & 1] = fmaxf(tile_max[j & 1], v);
+      }
+      float alpha[2], m_use[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 4));
+        tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 8));
+        tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 16));
+        const float m_new = fmaxf(m_run[nt][h], tile_max[h]);
+        m_use[h] = m_new == -INFINITY ? 0.f : m_new;
+        alpha[h] = m_run[nt][h] == -INFINITY ? 0.f : exp2f(m_run[nt][h] - m_use[h]);
+        m_run[nt][h] = m_new;
+        l_run[nt][h] *= alpha[h];
+      }
+#pragma unroll
+      for (int i = 0; i < D / 16; ++i) {
+        o[i][nt][0] *= alpha[0];
+        o[i][nt][1] *= alpha[1];
+        o[i][nt][2] *= alpha[0];
+        o[i][nt][3] *= alpha[1];
+      }
+      const float p0 = exp2f(st[nt][0] - m_use[0]), p1 = exp2f(st[nt][1] - m_use[1]);
+      const float p2 = exp2f(st[nt][2] - m_use[0]), p3 = exp2f(st[nt][3] - m_use[1]);
+      l_run[nt][0] += p0 + p2;
+      l_run[nt][1] += p1 + p3;
+      pb[nt][0] = movmatrix_trans(pack_bf16(p0, p1));     // keys 0..7 of the group
+      pb[nt][1] = movmatrix_trans(pack_bf16(p2, p3));     // keys 8..15
+    }
+#pragma unroll
+    for (int dt = 0; dt < D / 16; ++dt) {
+      uint32_t a[4];
+      ldmatrix_x4_trans(smem_u32(v_s + ((mi >> 1) * 8 + (lane & 7)) * kRow + dt * 16 + (mi & 1) * 8), a);
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) mma_16816(o[dt][nt], a, pb[nt][0], pb[nt][1]);
+    }
   }
-}
 
+  // This warp's (max, sum, unnormalised output) per head into mo [4 warps][16 heads][D] and
+  // mml [4][16][2]; rows of heads past 8 * NT are not written (and never read).
+  __device__ __forceinline__ void stash(float* mo, float* mml, int warp, int lane) {
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float l = l_run[nt][h];
+        l += __shfl_xor_sync(0xffffffffu, l, 4);
+        l += __shfl_xor_sync(0xffffffffu, l, 8);
+        l += __shfl_xor_sync(0xffffffffu, l, 16);
+        const int r = nt * 8 + (lane & 3) * 2 + h;
+        if (lane < 4) {
+          mml[(warp * 16 + r) * 2] = m_run[nt][h];
+          mml[(warp * 16 + r) * 2 + 1] = l;
+        }
+#pragma unroll
+        for (int i = 0; i < D / 16; ++i) {
+          float* dst = mo + (size_t)(warp * 16 + r) * D + i * 16 + (lane >> 2);
+          dst[0] = o[i][nt][h];
+          dst[8] = o[i][nt][2 + h];
+        }
+      }
+  }
+};
 
-template <int D>
+template <int D, int NT>
 __global__ void __launch_bounds__(kThreads)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
                         __nv_bfloat16* __restrict__ out, int out_stride, PagedArgs pa,
@@ -427,13 +496,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
   cp_async_commit();
   cp_async_wait<0>();
   __syncthreads();
-  uint32_t q_frag[D / 16][4];
-#pragma unroll
-  for (int ks = 0; ks < D / 16; ++ks) {
-    const int mi = lane >> 3;
-    const int r = (mi & 1) * 8 + (lane & 7), c = ks * 16 + (mi >> 1) * 8;
-    ldmatrix_x4(smem_u32(q_s + r * kRow + c), q_frag[ks]);
-  }
+  DecodeWarp<D, NT> dw;
+  dw.init();
+  dw.load_q(q_s, lane);
 
   __nv_bfloat16* my_s = kv_s + (size_t)warp * kDecodeStages * 2 * kGroupElems;
   // Requests keys/values of group `grp` (16 keys from k_begin + 16*grp) into stage `st`.
@@ -463,12 +528,6 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
     cp_async_commit();          // always: keeps the group count the same in every iteration
   };
 
-  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-  float o_acc[D / 8][4];
-#pragma unroll
-  for (int i = 0; i < D / 8; ++i)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) o_acc[i][j] = 0.f;
   const float sl2 = scale * kLog2e;
 
 #pragma unroll
@@ -481,33 +540,15 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
     const __nv_bfloat16* k_s = my_s + (size_t)(it % kDecodeStages) * 2 * kGroupElems;
     const __nv_bfloat16* v_s = k_s + kGroupElems;
     const int key0 = k_begin + grp * 16;
-    decode_group<D>(k_s, v_s, q_frag, key0, k_end, sl2, m_run, l_run, o_acc, lane);
+    dw.group(k_s, v_s, key0, k_end, sl2, lane);
     __syncwarp();      // the stage is refilled by the next iteration's request
   }
   cp_async_wait<0>();
   __syncthreads();     // every warp is done with its stages: the space becomes the merge buffer
 
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
-    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
-  }
   float* mo = reinterpret_cast<float*>(kv_s);          // [4 warps][16 rows][D]
   float* mml = mo + 4 * 16 * D;                        // [4][16][2]
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const int r = (lane >> 2) + h * 8;
-    if ((lane & 3) == 0) {
-      mml[(warp * 16 + r) * 2] = m_run[h];
-      mml[(warp * 16 + r) * 2 + 1] = l_run[h];
-    }
-#pragma unroll
-    for (int i = 0; i < D / 8; ++i) {
-      float* dst = mo + (size_t)(warp * 16 + r) * D + i * 8 + (lane & 3) * 2;
-      dst[0] = o_acc[i][h * 2];
-      dst[1] = o_acc[i][h * 2 + 1];
-    }
-  }
+  dw.stash(mo, mml, warp, lane);
   __syncthreads();
   for (int idx = tid; idx < heads * D; idx += kThreads) {
     const int r = idx / D, c = idx - r * D;
@@ -640,7 +681,7 @@ __device__ __forceinline__ void norm_rope_row(const __nv_bfloat16* src, __nv_bfl
   }
 }
 
-template <int D, bool kFuse>
+template <int D, int NT, bool kFuse>
 __global__ void __launch_bounds__(kThreads)
 attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
                                 __nv_bfloat16* __restrict__ out, int out_stride, PagedArgs pa,
@@ -675,12 +716,8 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int row_s
   const bool own_new = kFuse && pos >= k_begin && pos < k_end;
   const int new_grp = own_new ? (pos - k_begin) / 16 : -1;
 
-  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-  float o_acc[D / 8][4];
-#pragma unroll
-  for (int i = 0; i < D / 8; ++i)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) o_acc[i][j] = 0.f;
+  DecodeWarp<D, NT> dw;
+  dw.init();
 
   if (n_groups > 0) {
     __nv_bfloat16* my_s = kv_s + (size_t)warp * kDecodeStages * 2 * kGroupElems;
@@ -758,13 +795,7 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int row_s
       }
     }
     __syncthreads();
-    uint32_t q_frag[D / 16][4];
-#pragma unroll
-    for (int ks = 0; ks < D / 16; ++ks) {
-      const int mi = lane >> 3;
-      const int r = (mi & 1) * 8 + (lane & 7), c = ks * 16 + (mi >> 1) * 8;
-      ldmatrix_x4(smem_u32(q_s + r * kRow + c), q_frag[ks]);
-    }
+    dw.load_q(q_s, lane);
     const float sl2 = scale * kLog2e;
     int it = 0;
     for (int grp = warp; grp < n_groups; grp += 4, ++it) {
@@ -783,7 +814,7 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int row_s
         }
         __syncwarp();
       }
-      decode_group<D>(k_s, v_s, q_frag, key0, k_end, sl2, m_run, l_run, o_acc, lane);
+      dw.group(k_s, v_s, key0, k_end, sl2, lane);
       __syncwarp();      // the stage is refilled by the next iteration's request
     }
     cp_async_wait<0>();
@@ -791,29 +822,11 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int row_s
   __syncthreads();     // every warp is done with its stages: the space becomes the merge buffer
 
   // the four warps -> one (max, sum, output) per query row of the block
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
-    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
-  }
   float* mo = reinterpret_cast<float*>(kv_s);          // [4 warps][16 rows][D]
   float* mml = mo + 4 * 16 * D;                        // [4][16][2]
   float* cl_o = mml + 4 * 16 * 2;                      // [16][D]: this block's partial for the cluster
   float* cl_ml = cl_o + 16 * D;                        // [16][2]
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const int r = (lane >> 2) + h * 8;
-    if ((lane & 3) == 0) {
-      mml[(warp * 16 + r) * 2] = m_run[h];
-      mml[(warp * 16 + r) * 2 + 1] = l_run[h];
-    }
-#pragma unroll
-    for (int i = 0; i < D / 8; ++i) {
-      float* dst = mo + (size_t)(warp * 16 + r) * D + i * 8 + (lane & 3) * 2;
-      dst[0] = o_acc[i][h * 2];
-      dst[1] = o_acc[i][h * 2 + 1];
-    }
-  }
+  dw.stash(mo, mml, warp, lane);
   __syncthreads();
   for (int idx = tid; idx < heads * D; idx += kThreads) {
     const int r = idx / D, c = idx - r * D;
@@ -909,14 +922,14 @@ template <int D> constexpr int decode_cluster_smem() {
   return tiles > merge ? tiles : merge;
 }
 
-template <int D, bool kFuse>
-int launch_decode_cluster(const __nv_bfloat16* qkv, int row_stride, __nv_bfloat16* out, int out_stride,
+template <int D, int NT, bool kFuse>
+int launch_decode_cluster_nt(const __nv_bfloat16* qkv, int row_stride, __nv_bfloat16* out, int out_stride,
                           const PagedArgs& pa, const int* q_start, const int* ctx_len, int n_seqs, int n_q,
                           float scale, int window, int splits, const DecodeFuse& fz, int* status,
                           cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_cluster_kernel<D, kFuse>,
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_cluster_kernel<D, NT, kFuse>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, decode_cluster_smem<D>());
     if (e != cudaSuccess) return (int)e;
     configured = true;
@@ -924,29 +937,42 @@ int launch_decode_cluster(const __nv_bfloat16* qkv, int row_stride, __nv_bfloat1
   const int g = n_q / pa.n_kv;
   dim3 grid(pa.n_kv * ((g + 15) / 16), splits, n_seqs);
   if (splits == 1)
-    return launch_kernel(attention_decode_cluster_kernel<D, kFuse>, grid, dim3(kThreads), decode_cluster_smem<D>(),
+    return launch_kernel(attention_decode_cluster_kernel<D, NT, kFuse>, grid, dim3(kThreads), decode_cluster_smem<D>(),
                          stream, qkv, row_stride, out, out_stride, pa, q_start, ctx_len, n_q, scale, window,
                          splits, fz, status);
-  return launch_kernel_cluster(attention_decode_cluster_kernel<D, kFuse>, grid, dim3(kThreads),
+  return launch_kernel_cluster(attention_decode_cluster_kernel<D, NT, kFuse>, grid, dim3(kThreads),
                                decode_cluster_smem<D>(), stream, dim3(1, splits, 1), qkv, row_stride, out,
                                out_stride, pa, q_start, ctx_len, n_q, scale, window, splits, fz, status);
 }
 
-template <int D>
-int launch_decode(const __nv_bfloat16* qkv, int row_stride, __nv_bfloat16* out, int out_stride,
+// Up to 8 query heads per block take one tile of 8 heads (NT = 1), up to 16 take two.
+template <int D, bool kFuse>
+int launch_decode_cluster(const __nv_bfloat16* qkv, int row_stride, __nv_bfloat16* out, int out_stride,
+                          const PagedArgs& pa, const int* q_start, const int* ctx_len, int n_seqs, int n_q,
+                          float scale, int window, int splits, const DecodeFuse& fz, int* status,
+                          cudaStream_t stream) {
+  if (n_q / pa.n_kv <= 8)
+    return launch_decode_cluster_nt<D, 1, kFuse>(qkv, row_stride, out, out_stride, pa, q_start, ctx_len, n_seqs,
+                                                 n_q, scale, window, splits, fz, status, stream);
+  return launch_decode_cluster_nt<D, 2, kFuse>(qkv, row_stride, out, out_stride, pa, q_start, ctx_len, n_seqs,
+                                               n_q, scale, window, splits, fz, status, stream);
+}
+
+template <int D, int NT>
+int launch_decode_nt(const __nv_bfloat16* qkv, int row_stride, __nv_bfloat16* out, int out_stride,
                   const PagedArgs& pa, const int* q_start, const int* ctx_len, int n_seqs, int n_q,
                   float scale, int window, int splits, float* part_o, float* part_ml, int* status,
                   cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D>,
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D, NT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, decode_smem<D>());
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   const int g = n_q / pa.n_kv;
   dim3 grid(pa.n_kv * ((g + 15) / 16), splits, n_seqs);
-  int r = launch_kernel(attention_decode_kernel<D>, grid, dim3(kThreads), decode_smem<D>(), stream, qkv,
+  int r = launch_kernel(attention_decode_kernel<D, NT>, grid, dim3(kThreads), decode_smem<D>(), stream, qkv,
                         row_stride, out, out_stride, pa, q_start, ctx_len, n_q, scale, window, splits,
                         part_o, part_ml, status);
   if (r != 0 || splits == 1) return r;
@@ -954,6 +980,18 @@ int launch_decode(const __nv_bfloat16* qkv, int row_stride, __nv_bfloat16* out, 
   return launch_kernel(attention_merge_kernel, mgrid, dim3(D >= 64 ? 64 : 32), 0, stream,
                        (const float*)part_o, (const float*)part_ml, out, out_stride, q_start, n_q, D,
                        splits);
+}
+
+template <int D>
+int launch_decode(const __nv_bfloat16* qkv, int row_stride, __nv_bfloat16* out, int out_stride,
+                  const PagedArgs& pa, const int* q_start, const int* ctx_len, int n_seqs, int n_q,
+                  float scale, int window, int splits, float* part_o, float* part_ml, int* status,
+                  cudaStream_t stream) {
+  if (n_q / pa.n_kv <= 8)
+    return launch_decode_nt<D, 1>(qkv, row_stride, out, out_stride, pa, q_start, ctx_len, n_seqs, n_q, scale,
+                                  window, splits, part_o, part_ml, status, stream);
+  return launch_decode_nt<D, 2>(qkv, row_stride, out, out_stride, pa, q_start, ctx_len, n_seqs, n_q, scale,
+                                window, splits, part_o, part_ml, status, stream);
 }
 
 }  // namespace tiled
