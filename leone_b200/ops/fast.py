@@ -49,6 +49,8 @@ class FastKernels:
         self.status = None
         self._attn_ws = None
         self.use_tiled_attention = os.environ.get("LEONE_NO_TILED_ATTENTION", "0") != "1"
+        # LEONE_NO_TC_ATTENTION=1 keeps prompt attention on the mma.sync kernel
+        self.use_tc_attention = os.environ.get("LEONE_NO_TC_ATTENTION", "0") != "1"
         self.lib.leone_attention_decode_scratch.restype = ctypes.c_longlong
 
     def _stream(self):
@@ -253,9 +255,11 @@ class FastKernels:
         else:
             if fuse is not None:
                 raise RuntimeError("fused q/k preparation is a decode-step feature")
-            code = self.lib.leone_attention_prefill(
-                *common, ctx.max_q_len, n_q, n_kv, d, c_float(scale), int(window or 0),
-                cache.page_tokens, kp.shape[0], _ptr(ctx.status), self._stream())
+            # head sizes 64 and 128 run on tcgen05; the others on the mma.sync kernel
+            tc = self.use_tc_attention and d in (64, 128) and g <= 128 and out.stride(0) % 8 == 0
+            entry = self.lib.leone_attention_prefill_tc if tc else self.lib.leone_attention_prefill
+            code = entry(*common, ctx.max_q_len, n_q, n_kv, d, c_float(scale), int(window or 0),
+                         cache.page_tokens, kp.shape[0], _ptr(ctx.status), self._stream())
         if code != 0:
             raise RuntimeError(f"tiled attention refused or failed with code {code}")
         return True
