@@ -20,7 +20,13 @@
 // Operand tiles are rows of 128 bytes with the 128-byte swizzle (16-byte chunk c of row r at
 // chunk c ^ (r & 7)); a tile with 128 elements per row is two such halves, 16 KB apart.  Keys
 // and values are gathered from the pages with 16-byte asynchronous copies that write this
-// layout directly; the next tile's copies run while the current tile is computed.
+// layout directly.
+//
+// The tile loop is software-pipelined so that the tensor core works under the softmax:
+// S of tile t+1 is issued (into the second S buffer of tensor memory) before the softmax of
+// tile t starts, and P.V of tile t runs while the next iteration loads and reduces S of tile
+// t+1; its result is added to the registers in the middle of that iteration, just before P of
+// tile t+1 is written.  Keys are copied two tiles ahead, values one tile ahead.
 // Every wait is bounded; a wait that runs out sets the status word and the block leaves.
 #include "tc_common.cuh"
 
@@ -78,43 +84,66 @@ __host__ __device__ constexpr uint32_t instr_desc_bf16_b_mn(int m, int n) {
   return instr_desc_bf16(m, n) | (1u << 16);
 }
 
-// Keys/values [tile_start, tile_start + 128) of one sequence and KV head into the swizzled
-// tiles at k_dst / v_dst; rows before k_first (keys a window has passed, whose pages may
-// already be given back) and rows at or past k_end are zero-filled.
+// Where the keys [tile_start, tile_start + 128) of one sequence and KV head lie in the pools,
+// in two steps so that the block table's latency can pass under other work: tile_page() reads
+// this thread's key's page number (-1: no key here, -2: outside the table), tile_rows() turns
+// it into an element offset in row_src[0..127] (-1 for none).  Rows before k_first (keys a
+// window has passed, whose pages may already be given back) and rows at or past k_end have
+// none.  The caller puts a block barrier between tile_rows and copy_tile.
+__device__ __forceinline__ int tile_page(const PagedArgs& pa, int seq, int tile_start, int k_first, int k_end) {
+  const int tid = threadIdx.x;
+  int page = -1;
+  if (tid < kKeys) {
+    const int kj = tile_start + tid;
+    if (kj < k_end && kj >= k_first) {
+      const int blk = kj / pa.page_tokens;
+      page = blk < pa.table_width ? pa.block_table[(size_t)seq * pa.table_width + blk] : -2;
+      if (page < 0) page = -2;
+    }
+  }
+  return page;
+}
 template <int D>
-__device__ __forceinline__ void load_kv_tile(uint32_t k_dst, uint32_t v_dst, long long* row_src,
-                                             const PagedArgs& pa, int seq, int kvh, int tile_start,
-                                             int k_first, int k_end, int* status, int token_row) {
-  constexpr int kChunks = D / 8;
+__device__ __forceinline__ void tile_rows(long long* row_src, int page, const PagedArgs& pa, int kvh,
+                                          int tile_start, int* status, int token_row) {
   const int tid = threadIdx.x;
   if (tid < kKeys) {
     const int kj = tile_start + tid;
     long long src = -1;
-    if (kj < k_end && kj >= k_first) {
-      const int blk = kj / pa.page_tokens;
-      const int page = blk < pa.table_width ? pa.block_table[(size_t)seq * pa.table_width + blk] : -1;
-      if (page < 0 || page >= pa.num_pages) {
-        set_status(status, kBadPage, token_row, page, kj);
-      } else {
-        src = (((long long)page * pa.n_kv + kvh) * pa.page_tokens + (kj % pa.page_tokens)) * D;
-      }
+    if (page >= pa.num_pages || page == -2) {
+      set_status(status, kBadPage, token_row, page, kj);
+    } else if (page >= 0) {
+      src = (((long long)page * pa.n_kv + kvh) * pa.page_tokens + (kj % pa.page_tokens)) * D;
     }
     row_src[tid] = src;
   }
-  __syncthreads();
-  for (int idx = tid; idx < kKeys * kChunks; idx += kThreads) {
-    const int row = idx / kChunks, ch = idx - row * kChunks;
-    const long long src = row_src[row];
-    const bool ok = src >= 0;
-    const long long off = ok ? src + ch * 8 : 0;
-    const uint32_t o = swizzled(row, ch);
-    cp_async16(k_dst + o, pa.k_pool + off, ok);
-    cp_async16(v_dst + o, pa.v_pool + off, ok);
+}
+
+// Copies the 128 rows whose offsets tile_rows gave from `pool` into the swizzled tile at dst
+// (rows without a source are zero-filled) and commits the copies as one group.
+template <int D>
+__device__ __forceinline__ void copy_tile(uint32_t dst, const long long* row_src, const __nv_bfloat16* pool,
+                                          bool any) {
+  constexpr int kChunks = D / 8;
+  constexpr int kStep = kThreads / kChunks;             // rows between a thread's copies
+  static_assert(kStep % 8 == 0 && kKeys % kStep == 0, "a thread's rows share their swizzle phase");
+  if (any) {
+    // a thread copies the same 16-byte chunk of rows r0, r0 + kStep, ..: one address to start from
+    const int ch = threadIdx.x % kChunks, r0 = threadIdx.x / kChunks;
+    const uint32_t d0 = dst + swizzled(r0, ch);
+    const __nv_bfloat16* p0 = pool + ch * 8;
+#pragma unroll
+    for (int i = 0; i < kKeys / kStep; ++i) {
+      const long long src = row_src[r0 + i * kStep];
+      const bool ok = src >= 0;
+      cp_async16(d0 + i * kStep * 128, ok ? p0 + src : pool, ok);
+    }
   }
+  cp_async_commit();      // always: the number of groups in flight is the same in every iteration
 }
 
 template <int D> constexpr int smem_bytes() {
-  // Q, two stages of (K, V), P, row sources [2][128], barriers; 1024 for alignment
+  // Q, two K and two V tiles, P, row sources [2][128], barriers; 1024 for alignment
   return kRows * D * 2 + 2 * 2 * kKeys * D * 2 + kRows * kKeys * 2 + 2 * kKeys * 8 + 64 + 1024;
 }
 
@@ -125,16 +154,17 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ qkv, int row_strid
                             const int* __restrict__ q_start, const int* __restrict__ ctx_len, int n_q,
                             float scale, int window, int* status) {
   constexpr int kTileBytes = kKeys * D * 2;             // one K or V tile; the Q tile has the same size
-  constexpr int kTmemCols = 256;                        // S: columns 0..127, PV: 128..128+D-1
+  constexpr int kTmemCols = 512;                        // S: two buffers at columns 0 and 128; PV at 256
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* aligned = smem_raw + (base - raw);
   const uint32_t q_t = base;
-  const uint32_t kv_t = q_t + kTileBytes;               // [2 stages][K, V]
-  const uint32_t p_t = kv_t + 4 * kTileBytes;
+  const uint32_t k_t = q_t + kTileBytes;                // [2] key tiles
+  const uint32_t v_t = k_t + 2 * kTileBytes;            // [2] value tiles
+  const uint32_t p_t = v_t + 2 * kTileBytes;
   long long* row_src = reinterpret_cast<long long*>(aligned + 5 * kTileBytes + kRows * kKeys * 2);   // [2][128]
-  const uint32_t bar_s = smem_u32(row_src + 2 * kKeys), bar_o = bar_s + 8;
+  const uint32_t bar_s = smem_u32(row_src + 2 * kKeys), bar_o = bar_s + 16;     // bar_s: one per S buffer
   __shared__ uint32_t tmem_holder;
   __shared__ int gave_up;
 
@@ -144,6 +174,7 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ qkv, int row_strid
   if (tid == 0) {
     gave_up = 0;
     mbar_init(bar_s, 1);
+    mbar_init(bar_s + 8, 1);
     mbar_init(bar_o, 1);
     mbar_fence_init();
   }
@@ -182,8 +213,22 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ qkv, int row_strid
     if (window > 0) k_lo = max(0, start + tok0 - window + 1);
     const int tile0 = (k_lo / kKeys) * kKeys;
     const int n_tiles = (k_hi - tile0 + kKeys - 1) / kKeys;
-    load_kv_tile<D>(kv_t, kv_t + kTileBytes, row_src, pa, seq, kvh, tile0, k_lo, k_hi, status, q0 + tok0);
-    cp_async_commit();
+    auto page_of = [&](int t) {          // this thread's key's page in tile t (read ahead of its use)
+      return t < n_tiles ? tile_page(pa, seq, tile0 + t * kKeys, k_lo, k_hi) : -1;
+    };
+    auto rows_of = [&](int t, int page) {          // row sources of tile t into buffer t & 1
+      if (t < n_tiles)
+        tile_rows<D>(row_src + (t & 1) * kKeys, page, pa, kvh, tile0 + t * kKeys, status, q0 + tok0);
+    };
+    auto copy_k = [&](int t) { copy_tile<D>(k_t + (t & 1) * kTileBytes, row_src + (t & 1) * kKeys, pa.k_pool, t < n_tiles); };
+    auto copy_v = [&](int t) { copy_tile<D>(v_t + (t & 1) * kTileBytes, row_src + (t & 1) * kKeys, pa.v_pool, t < n_tiles); };
+    rows_of(0, page_of(0));
+    rows_of(1, page_of(1));
+    int page_ahead = page_of(2);          // consumed in the first iteration
+    __syncthreads();
+    copy_k(0);                           // group: Q and K(0)
+    copy_k(1);                           // group: K(1)
+    copy_v(0);                           // group: V(0)
 
     // this thread's row and its share of the columns
     constexpr int kSC = kKeys / kSplit;                 // score columns per thread
@@ -201,44 +246,45 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ qkv, int row_strid
     const uint32_t t_row = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);   // this warp's lanes
     constexpr uint32_t idesc_s = instr_desc_bf16(kRows, kKeys);
     constexpr uint32_t idesc_o = instr_desc_bf16_b_mn(kRows, D);
-    uint32_t phase = 0;
     bool ok_all = true;
-
-    for (int t = 0; t < n_tiles && ok_all; ++t) {
-      const int stage = t & 1;
-      const uint32_t k_s = kv_t + stage * 2 * kTileBytes, v_s = k_s + kTileBytes;
-      if (t + 1 < n_tiles) {
-        const uint32_t nk = kv_t + (stage ^ 1) * 2 * kTileBytes;
-        load_kv_tile<D>(nk, nk + kTileBytes, row_src + (stage ^ 1) * kKeys, pa, seq, kvh,
-                        tile0 + (t + 1) * kKeys, k_lo, k_hi, status, q0 + tok0);
-        cp_async_commit();
-        cp_async_wait<1>();
-      } else {
-        cp_async_wait<0>();
-      }
-      // the copies wrote shared memory through the generic proxy; the tensor core reads it
-      // through the async proxy
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      __syncthreads();
-      if (tid == 0) {
-        tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          // 16 elements further along a 128-byte row: +32 bytes; past 64 elements: the next half
-          const uint32_t off = (ks >> 2) * (128 * 128) + (ks & 3) * 32;
-          umma_bf16(tmem_base, smem_desc_sw128(q_t + off), smem_desc_sw128(k_s + off), idesc_s, ks > 0 ? 1u : 0u);
-        }
-        umma_commit(bar_s);
-      }
-      if (!mbar_wait(bar_s, phase, giveup)) { ok_all = false; break; }
+    // S(t) = Q . K(t)^T into S buffer t & 1; its barrier's phase is (t >> 1) & 1
+    auto issue_s = [&](int t) {
       tc_fence_after();
+      const uint32_t k_s = k_t + (t & 1) * kTileBytes;
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        // 16 elements further along a 128-byte row: +32 bytes; past 64 elements: the next half
+        const uint32_t off = (ks >> 2) * (128 * 128) + (ks & 3) * 32;
+        umma_bf16(tmem_base + (t & 1) * kKeys, smem_desc_sw128(q_t + off), smem_desc_sw128(k_s + off), idesc_s,
+                  ks > 0 ? 1u : 0u);
+      }
+      umma_commit(bar_s + 8 * (t & 1));
+    };
+    // Q and K(0) have to be there for S(0)
+    cp_async_wait<2>();
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();
+    if (tid == 0) issue_s(0);
 
-      // softmax of this thread's quarter of its row
-      const int tile_start = tile0 + t * kKeys;
+    for (int t = 0; t < n_tiles; ++t) {
       const int col0 = part * kSC;
+      const int tile_start = tile0 + t * kKeys;
+      // (1) S(t) is complete, so K(t)'s tile is free for K(t+2); K(t+1) has to have landed
+      if (!mbar_wait(bar_s + 8 * (t & 1), (t >> 1) & 1, giveup)) { ok_all = false; break; }
+      tc_fence_after();
+      rows_of(t + 2, page_ahead);
+      page_ahead = page_of(t + 3);
+      cp_async_wait<1>();                 // groups so far: .. K(t+1), V(t): all but the newest is K(t+1) and older
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      tc_fence_before();
+      __syncthreads();
+      if (tid == 0 && t + 1 < n_tiles) issue_s(t + 1);     // runs under this tile's softmax
+      copy_k(t + 2);
+
+      // (2) this thread's quarter of its row of S(t)
       float sc[kSC];
 #pragma unroll
-      for (int c = 0; c < kSC; c += 16) tmem_ld16(t_row + col0 + c, sc + c);
+      for (int c = 0; c < kSC; c += 16) tmem_ld16(t_row + (t & 1) * kKeys + col0 + c, sc + c);
       const bool all_visible = tile_start + kKeys - 1 <= first_pos &&
                                (window <= 0 || tile_start > last_pos - window) && my_pos >= 0;
       float tile_max = -INFINITY;
@@ -258,6 +304,7 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ qkv, int row_strid
         }
       }
       max_s[part][row] = tile_max;
+      tc_fence_before();
       __syncthreads();
 #pragma unroll
       for (int q = 0; q < kSplit; ++q) tile_max = fmaxf(tile_max, max_s[q][row]);
@@ -266,6 +313,21 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ qkv, int row_strid
       const float alpha = m_run == -INFINITY ? 0.f : exp2f(m_run - m_use);
       m_run = m_new;
       l_run *= alpha;
+
+      // (3) P(t-1) . V(t-1) is complete: add it (still at the old maximum's scale), then its
+      // value tile is free for V(t+1) and P's tile for P(t)
+      if (t > 0) {
+        if (!mbar_wait(bar_o, (t - 1) & 1, giveup)) { ok_all = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < kOC; c += 16) {
+          float pv[16];
+          tmem_ld16(t_row + 2 * kKeys + part * kOC + c, pv);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) o_acc[c + j] += pv[j];
+        }
+      }
+      copy_v(t + 1);
       if (alpha != 1.f) {
 #pragma unroll
         for (int i = 0; i < kOC; ++i) o_acc[i] *= alpha;
@@ -284,32 +346,37 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ qkv, int row_strid
                      "r"(packed[0]), "r"(packed[1]), "r"(packed[2]), "r"(packed[3])
                      : "memory");
       }
+      // (4) V(t) has to have landed (groups so far: .. V(t), K(t+2), V(t+1)); then P(t) . V(t)
+      cp_async_wait<2>();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tc_fence_before();
       __syncthreads();
       if (tid == 0) {
         tc_fence_after();
+        const uint32_t v_s = v_t + (t & 1) * kTileBytes;
 #pragma unroll
         for (int ks = 0; ks < kKeys / 16; ++ks) {
           // A = P: 16 keys further along a row; B = V: 16 keys = 16 rows = 2048 bytes further
           const uint32_t a_off = (ks >> 2) * (128 * 128) + (ks & 3) * 32;
-          umma_bf16(tmem_base + kKeys, smem_desc_sw128(p_t + a_off),
+          umma_bf16(tmem_base + 2 * kKeys, smem_desc_sw128(p_t + a_off),
                     smem_desc_mn_sw128(v_s + ks * 2048, 128 * 128), idesc_o, ks > 0 ? 1u : 0u);
         }
         umma_commit(bar_o);
       }
-      if (!mbar_wait(bar_o, phase, giveup)) { ok_all = false; break; }
-      tc_fence_after();
+    }
+    // the last tile's P . V
+    if (ok_all && n_tiles > 0) {
+      if (!mbar_wait(bar_o, (n_tiles - 1) & 1, giveup)) ok_all = false;
+      if (ok_all) {
+        tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < kOC; c += 16) {
-        float pv[16];
-        tmem_ld16(t_row + kKeys + part * kOC + c, pv);
+        for (int c = 0; c < kOC; c += 16) {
+          float pv[16];
+          tmem_ld16(t_row + 2 * kKeys + part * kOC + c, pv);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) o_acc[c + j] += pv[j];
+          for (int j = 0; j < 16; ++j) o_acc[c + j] += pv[j];
+        }
       }
-      tc_fence_before();
-      phase ^= 1;
-      // (the next iteration's __syncthreads orders these loads before the next MMAs)
     }
 
     // the row's sum from its four parts, then every thread writes its columns

@@ -562,6 +562,22 @@ def test_attention_prefill_tiled(ops16, n_q, n_kv, d, pt, window):
                 seed=3)
 
 
+@pytest.mark.parametrize("n_q,n_kv,d,pt,window", [(10, 2, 64, 16, None), (28, 4, 128, 8, 200), (3, 1, 128, 32, None),
+                                                  (8, 2, 128, 16, 129), (64, 1, 64, 16, None)])
+def test_attention_prefill_tensor_memory_kernel_long(ops16, n_q, n_kv, d, pt, window):
+    """The tcgen05 prompt kernel over many key tiles: a long first portion, a continued portion
+    that starts in the middle of a tile, head groups that do not divide the 128 rows of a block,
+    windows that end inside a tile; and the mma.sync kernel on the same batch."""
+    assert ops16.fast.use_tc_attention
+    kw = dict(seq_lens=[700, 517, 130], starts=[0, 300, 127], seed=8)
+    _tiled_case(ops16, n_q, n_kv, d, pt, window, **kw)
+    ops16.fast.use_tc_attention = False
+    try:
+        _tiled_case(ops16, n_q, n_kv, d, pt, window, **kw)
+    finally:
+        ops16.fast.use_tc_attention = True
+
+
 @pytest.mark.parametrize("n_q,n_kv,d,pt,window", [(5, 1, 48, 16, None), (6, 3, 32, 8, None),
                                                   (8, 2, 128, 16, None), (4, 4, 80, 4, 37),
                                                   (32, 8, 128, 16, None), (40, 2, 16, 16, None)])
