@@ -26,7 +26,9 @@
 // S of tile t+1 is issued (into the second S buffer of tensor memory) before the softmax of
 // tile t starts, and P.V of tile t runs while the next iteration loads and reduces S of tile
 // t+1; its result is added to the registers in the middle of that iteration, just before P of
-// tile t+1 is written.  Keys are copied two tiles ahead, values one tile ahead.
+// tile t+1 is written.  Keys are copied two tiles ahead, values one tile ahead.  A warp of its
+// own issues the MMAs: the softmax warps tell it through mbarriers when an operand tile has
+// landed and a tensor-memory buffer is free, so they never wait for one thread's issue loop.
 // Every wait is bounded; a wait that runs out sets the status word and the block leaves.
 #include "tc_common.cuh"
 
@@ -37,7 +39,8 @@ using namespace leone::tc;
 
 constexpr int kSplit = 4;         // threads per query row
 constexpr int kRows = 128;        // query rows per block
-constexpr int kThreads = kRows * kSplit;
+constexpr int kThreads = kRows * kSplit;      // the softmax threads (16 warps); they also copy the tiles
+constexpr int kBlockThreads = kThreads + 32;  // + one warp that issues the tensor-core work
 constexpr int kKeys = 128;        // keys per tile
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -148,7 +151,7 @@ template <int D> constexpr int smem_bytes() {
 }
 
 template <int D>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kBlockThreads)
 attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
                             __nv_bfloat16* __restrict__ out, int out_stride, PagedArgs pa,
                             const int* __restrict__ q_start, const int* __restrict__ ctx_len, int n_q,
@@ -164,11 +167,13 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ qkv, int row_strid
   const uint32_t v_t = k_t + 2 * kTileBytes;            // [2] value tiles
   const uint32_t p_t = v_t + 2 * kTileBytes;
   long long* row_src = reinterpret_cast<long long*>(aligned + 5 * kTileBytes + kRows * kKeys * 2);   // [2][128]
-  const uint32_t bar_s = smem_u32(row_src + 2 * kKeys), bar_o = bar_s + 16;     // bar_s: one per S buffer
+  // bar_s (one per S buffer) and bar_o: the tensor core's results; bar_k and bar_p: the softmax
+  // warps' go-ahead for S of a tile and for P.V of a tile (one arrival per warp)
+  const uint32_t bar_s = smem_u32(row_src + 2 * kKeys), bar_o = bar_s + 16, bar_k = bar_s + 24, bar_p = bar_s + 32;
   __shared__ uint32_t tmem_holder;
   __shared__ int gave_up;
 
-  __shared__ float max_s[kSplit][kRows];                // the row maximum's parts, then the row sum's
+  __shared__ float max_s[2][kSplit][kRows];             // the row maximum's parts (two tiles' worth), then the row sum's
   const int tid = threadIdx.x, warp = tid >> 5;
   const int row = tid & (kRows - 1), part = tid >> 7;   // this thread: row, and which quarter of the columns
   if (tid == 0) {
@@ -176,9 +181,12 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ qkv, int row_strid
     mbar_init(bar_s, 1);
     mbar_init(bar_s + 8, 1);
     mbar_init(bar_o, 1);
+    mbar_init(bar_k, kThreads / 32);
+    mbar_init(bar_p, kThreads / 32);
     mbar_fence_init();
   }
-  if (warp == 0) tmem_alloc(smem_u32(&tmem_holder), kTmemCols);
+  constexpr int kMmaWarp = kThreads / 32;
+  if (warp == kMmaWarp) tmem_alloc(smem_u32(&tmem_holder), kTmemCols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -187,8 +195,10 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ qkv, int row_strid
   pdl_trigger();
   pdl_wait();
 
-  const int seq = blockIdx.z, kvh = blockIdx.y;
-  const int qt = gridDim.x - 1 - blockIdx.x;            // late tiles (most keys) first
+  // blocks in launch order: the latest query tile (most keys) of every KV head first, so that
+  // the long blocks start early and the short ones fill the end
+  const int seq = blockIdx.z, kvh = blockIdx.x % pa.n_kv;
+  const int qt = gridDim.x / pa.n_kv - 1 - blockIdx.x / pa.n_kv;
   const int g = n_q / pa.n_kv;
   const int tq = kRows / g;                             // tokens per tile
   const int q0 = q_start[seq], q_len = q_start[seq + 1] - q0;
@@ -197,127 +207,198 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ qkv, int row_strid
   if (live) {
     const int ctx = ctx_len[seq], start = ctx - q_len;
     const int tok1 = min(q_len, tok0 + tq);
-
-    // the tile's query rows: row r = (token r / g, head r % g)
-    for (int idx = tid; idx < kRows * (D / 8); idx += kThreads) {
-      const int r = idx / (D / 8), ch = idx - r * (D / 8);
-      const int tl = r / g, hh = r - tl * g;
-      const int token = tok0 + tl;
-      const bool ok = tl < tq && token < tok1;
-      const __nv_bfloat16* src =
-          qkv + (size_t)(q0 + (ok ? token : 0)) * row_stride + (size_t)(kvh * g + hh) * D + ch * 8;
-      cp_async16(q_t + swizzled(r, ch), src, ok);
-    }
     const int k_hi = start + tok1;                      // one past the last key any row reads
     int k_lo = 0;
     if (window > 0) k_lo = max(0, start + tok0 - window + 1);
     const int tile0 = (k_lo / kKeys) * kKeys;
     const int n_tiles = (k_hi - tile0 + kKeys - 1) / kKeys;
-    auto page_of = [&](int t) {          // this thread's key's page in tile t (read ahead of its use)
-      return t < n_tiles ? tile_page(pa, seq, tile0 + t * kKeys, k_lo, k_hi) : -1;
-    };
-    auto rows_of = [&](int t, int page) {          // row sources of tile t into buffer t & 1
-      if (t < n_tiles)
-        tile_rows<D>(row_src + (t & 1) * kKeys, page, pa, kvh, tile0 + t * kKeys, status, q0 + tok0);
-    };
-    auto copy_k = [&](int t) { copy_tile<D>(k_t + (t & 1) * kTileBytes, row_src + (t & 1) * kKeys, pa.k_pool, t < n_tiles); };
-    auto copy_v = [&](int t) { copy_tile<D>(v_t + (t & 1) * kTileBytes, row_src + (t & 1) * kKeys, pa.v_pool, t < n_tiles); };
-    rows_of(0, page_of(0));
-    rows_of(1, page_of(1));
-    int page_ahead = page_of(2);          // consumed in the first iteration
-    __syncthreads();
-    copy_k(0);                           // group: Q and K(0)
-    copy_k(1);                           // group: K(1)
-    copy_v(0);                           // group: V(0)
-
-    // this thread's row and its share of the columns
-    constexpr int kSC = kKeys / kSplit;                 // score columns per thread
-    constexpr int kOC = D / kSplit;                     // output columns per thread
-    const int my_tl = row / g;
-    const int my_pos = (my_tl < tq && tok0 + my_tl < tok1) ? start + tok0 + my_tl : -1;   // -1: row unused
-    // the block's rows read keys up to their own position: a tile that ends at or before the
-    // first row's position (and lies inside every row's window) needs no masking
-    const int first_pos = start + tok0, last_pos = start + tok1 - 1;
-    float m_run = -INFINITY, l_run = 0.f;
-    float o_acc[kOC];
-#pragma unroll
-    for (int i = 0; i < kOC; ++i) o_acc[i] = 0.f;
-    const float sl2 = scale * kLog2e;
-    const uint32_t t_row = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);   // this warp's lanes
     constexpr uint32_t idesc_s = instr_desc_bf16(kRows, kKeys);
     constexpr uint32_t idesc_o = instr_desc_bf16_b_mn(kRows, D);
-    bool ok_all = true;
-    // S(t) = Q . K(t)^T into S buffer t & 1; its barrier's phase is (t >> 1) & 1
-    auto issue_s = [&](int t) {
-      tc_fence_after();
-      const uint32_t k_s = k_t + (t & 1) * kTileBytes;
-#pragma unroll
-      for (int ks = 0; ks < D / 16; ++ks) {
-        // 16 elements further along a 128-byte row: +32 bytes; past 64 elements: the next half
-        const uint32_t off = (ks >> 2) * (128 * 128) + (ks & 3) * 32;
-        umma_bf16(tmem_base + (t & 1) * kKeys, smem_desc_sw128(q_t + off), smem_desc_sw128(k_s + off), idesc_s,
-                  ks > 0 ? 1u : 0u);
-      }
-      umma_commit(bar_s + 8 * (t & 1));
-    };
-    // Q and K(0) have to be there for S(0)
-    cp_async_wait<2>();
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    __syncthreads();
-    if (tid == 0) issue_s(0);
 
-    for (int t = 0; t < n_tiles; ++t) {
+    if (warp == kMmaWarp) {
+      // ---------------- the warp that issues the tensor-core work ----------------
+      // Order of the go-aheads: K(0); then per tile t: K(t+1), P(t).  One thread issues.
+      if ((tid & 31) == 0) {
+        auto issue_s = [&](int t) {     // S(t) = Q . K(t)^T into S buffer t & 1
+          tc_fence_after();
+          const uint32_t k_s = k_t + (t & 1) * kTileBytes;
+#pragma unroll
+          for (int ks = 0; ks < D / 16; ++ks) {
+            // 16 elements further along a 128-byte row: +32 bytes; past 64 elements: the next half
+            const uint32_t off = (ks >> 2) * (128 * 128) + (ks & 3) * 32;
+            umma_bf16(tmem_base + (t & 1) * kKeys, smem_desc_sw128(q_t + off), smem_desc_sw128(k_s + off),
+                      idesc_s, ks > 0 ? 1u : 0u);
+          }
+          umma_commit(bar_s + 8 * (t & 1));
+        };
+        bool ok = mbar_wait(bar_k, 0, giveup);
+        if (ok) issue_s(0);
+        for (int t = 0; t < n_tiles && ok; ++t) {
+          if (t + 1 < n_tiles) {
+            ok = mbar_wait(bar_k, (t + 1) & 1, giveup);
+            if (!ok) break;
+            issue_s(t + 1);
+          }
+          ok = mbar_wait(bar_p, t & 1, giveup);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t v_s = v_t + (t & 1) * kTileBytes;
+#pragma unroll
+          for (int ks = 0; ks < kKeys / 16; ++ks) {
+            // A = P: 16 keys further along a row; B = V: 16 keys = 16 rows = 2048 bytes further
+            const uint32_t a_off = (ks >> 2) * (128 * 128) + (ks & 3) * 32;
+            umma_bf16(tmem_base + 2 * kKeys, smem_desc_sw128(p_t + a_off),
+                      smem_desc_mn_sw128(v_s + ks * 2048, 128 * 128), idesc_o, ks > 0 ? 1u : 0u);
+          }
+          umma_commit(bar_o);
+        }
+      }
+    } else {
+      // ---------------- the softmax warps ----------------
+      const int lane = tid & 31;
+      // the tile's query rows: row r = (token r / g, head r % g)
+      for (int idx = tid; idx < kRows * (D / 8); idx += kThreads) {
+        const int r = idx / (D / 8), ch = idx - r * (D / 8);
+        const int tl = r / g, hh = r - tl * g;
+        const int token = tok0 + tl;
+        const bool ok = tl < tq && token < tok1;
+        const __nv_bfloat16* src =
+            qkv + (size_t)(q0 + (ok ? token : 0)) * row_stride + (size_t)(kvh * g + hh) * D + ch * 8;
+        cp_async16(q_t + swizzled(r, ch), src, ok);
+      }
+      auto page_of = [&](int t) {          // this thread's key's page in tile t (read ahead of its use)
+        return t < n_tiles ? tile_page(pa, seq, tile0 + t * kKeys, k_lo, k_hi) : -1;
+      };
+      auto rows_of = [&](int t, int page) {          // row sources of tile t into buffer t & 1
+        if (t < n_tiles)
+          tile_rows<D>(row_src + (t & 1) * kKeys, page, pa, kvh, tile0 + t * kKeys, status, q0 + tok0);
+      };
+      auto copy_k = [&](int t) {
+        copy_tile<D>(k_t + (t & 1) * kTileBytes, row_src + (t & 1) * kKeys, pa.k_pool, t < n_tiles);
+      };
+      auto copy_v = [&](int t) {
+        copy_tile<D>(v_t + (t & 1) * kTileBytes, row_src + (t & 1) * kKeys, pa.v_pool, t < n_tiles);
+      };
+      // one arrival per warp at a go-ahead barrier, after the warp's copies and tensor-memory
+      // reads are ordered before it
+      auto go_ahead = [&](uint32_t bar) {
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar);
+      };
+      rows_of(0, page_of(0));
+      rows_of(1, page_of(1));
+      int page_ahead = page_of(2);          // consumed in the first iteration
+      named_barrier_sync(1, kThreads);
+      copy_k(0);                           // group: Q and K(0)
+      copy_k(1);                           // group: K(1)
+      copy_v(0);                           // group: V(0)
+
+      // this thread's row and its share of the columns
+      constexpr int kSC = kKeys / kSplit;                 // score columns per thread
+      constexpr int kOC = D / kSplit;                     // output columns per thread
+      const int my_tl = row / g;
+      const int my_pos = (my_tl < tq && tok0 + my_tl < tok1) ? start + tok0 + my_tl : -1;   // -1: row unused
+      // the block's rows read keys up to their own position: a tile that ends at or before the
+      // first row's position (and lies inside every row's window) needs no masking
+      const int first_pos = start + tok0, last_pos = start + tok1 - 1;
+      float m_run = -INFINITY, l_run = 0.f;
+      float o_acc[kOC];
+#pragma unroll
+      for (int i = 0; i < kOC; ++i) o_acc[i] = 0.f;
+      const float sl2 = scale * kLog2e;
+      const uint32_t t_row = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);   // this warp's lanes
       const int col0 = part * kSC;
-      const int tile_start = tile0 + t * kKeys;
-      // (1) S(t) is complete, so K(t)'s tile is free for K(t+2); K(t+1) has to have landed
-      if (!mbar_wait(bar_s + 8 * (t & 1), (t >> 1) & 1, giveup)) { ok_all = false; break; }
-      tc_fence_after();
-      rows_of(t + 2, page_ahead);
-      page_ahead = page_of(t + 3);
-      cp_async_wait<1>();                 // groups so far: .. K(t+1), V(t): all but the newest is K(t+1) and older
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      tc_fence_before();
-      __syncthreads();
-      if (tid == 0 && t + 1 < n_tiles) issue_s(t + 1);     // runs under this tile's softmax
-      copy_k(t + 2);
+      // A wait that runs out leaves ok_all false; the thread still walks the loop (every later
+      // wait returns at once), so that the named barriers below keep their counts.
+      bool ok_all = true;
 
-      // (2) this thread's quarter of its row of S(t)
-      float sc[kSC];
+      cp_async_wait<2>();                  // Q and K(0) have landed
+      go_ahead(bar_k);                     // S(0) may be issued
+
+      for (int t = 0; t < n_tiles; ++t) {
+        const int tile_start = tile0 + t * kKeys;
+        // (1) S(t) is complete, so K(t)'s tile is free for K(t+2); K(t+1) has landed: S(t+1) may go
+        if (ok_all && !mbar_wait(bar_s + 8 * (t & 1), (t >> 1) & 1, giveup)) ok_all = false;
+        tc_fence_after();
+        rows_of(t + 2, page_ahead);
+        page_ahead = page_of(t + 3);
+        cp_async_wait<1>();                // groups so far: .. K(t+1), V(t): all but the newest have landed
+        if (t + 1 < n_tiles) go_ahead(bar_k);
+
+        // (2) this thread's quarter of its row of S(t)
+        float sc[kSC];
 #pragma unroll
-      for (int c = 0; c < kSC; c += 16) tmem_ld16(t_row + (t & 1) * kKeys + col0 + c, sc + c);
-      const bool all_visible = tile_start + kKeys - 1 <= first_pos &&
-                               (window <= 0 || tile_start > last_pos - window) && my_pos >= 0;
-      float tile_max = -INFINITY;
-      if (all_visible) {
+        for (int c = 0; c < kSC; c += 16) tmem_ld16(t_row + (t & 1) * kKeys + col0 + c, sc + c);
+        const bool all_visible = tile_start + kKeys - 1 <= first_pos &&
+                                 (window <= 0 || tile_start > last_pos - window) && my_pos >= 0;
+        float tile_max = -INFINITY;
+        if (all_visible) {
 #pragma unroll
-        for (int j = 0; j < kSC; ++j) {
-          sc[j] *= sl2;
-          tile_max = fmaxf(tile_max, sc[j]);
+          for (int j = 0; j < kSC; ++j) {
+            sc[j] *= sl2;
+            tile_max = fmaxf(tile_max, sc[j]);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < kSC; ++j) {
+            const int kj = tile_start + col0 + j;
+            const bool keep = my_pos >= 0 && kj <= my_pos && (window <= 0 || kj > my_pos - window);
+            sc[j] = keep ? sc[j] * sl2 : -INFINITY;
+            tile_max = fmaxf(tile_max, sc[j]);
+          }
         }
-      } else {
+        max_s[t & 1][part][row] = tile_max;
+        named_barrier_sync(1, kThreads);   // the row maximum's parts, and the row sources of tile t+2
+        copy_k(t + 2);
 #pragma unroll
-        for (int j = 0; j < kSC; ++j) {
-          const int kj = tile_start + col0 + j;
-          const bool keep = my_pos >= 0 && kj <= my_pos && (window <= 0 || kj > my_pos - window);
-          sc[j] = keep ? sc[j] * sl2 : -INFINITY;
-          tile_max = fmaxf(tile_max, sc[j]);
+        for (int q = 0; q < kSplit; ++q) tile_max = fmaxf(tile_max, max_s[t & 1][q][row]);
+        const float m_new = fmaxf(m_run, tile_max);
+        const float m_use = m_new == -INFINITY ? 0.f : m_new;
+        const float alpha = m_run == -INFINITY ? 0.f : exp2f(m_run - m_use);
+        m_run = m_new;
+        l_run *= alpha;
+
+        // (3) P(t-1) . V(t-1) is complete: add it (still at the old maximum's scale), then its
+        // value tile is free for V(t+1) and P's tile for P(t)
+        if (t > 0) {
+          if (ok_all && !mbar_wait(bar_o, (t - 1) & 1, giveup)) ok_all = false;
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < kOC; c += 16) {
+            float pv[16];
+            tmem_ld16(t_row + 2 * kKeys + part * kOC + c, pv);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) o_acc[c + j] += pv[j];
+          }
         }
+        copy_v(t + 1);
+        if (alpha != 1.f) {
+#pragma unroll
+          for (int i = 0; i < kOC; ++i) o_acc[i] *= alpha;
+        }
+#pragma unroll
+        for (int c = 0; c < kSC / 8; ++c) {
+          uint32_t packed[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float p0 = exp2f(sc[c * 8 + 2 * j] - m_use), p1 = exp2f(sc[c * 8 + 2 * j + 1] - m_use);
+            l_run += p0 + p1;
+            __nv_bfloat162 v2 = __floats2bfloat162_rn(p0, p1);
+            packed[j] = *reinterpret_cast<uint32_t*>(&v2);
+          }
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_t + swizzled(row, col0 / 8 + c)),
+                       "r"(packed[0]), "r"(packed[1]), "r"(packed[2]), "r"(packed[3])
+                       : "memory");
+        }
+        // (4) V(t) has landed (groups so far: .. V(t), K(t+2), V(t+1)): P(t) . V(t) may go
+        cp_async_wait<2>();
+        go_ahead(bar_p);
       }
-      max_s[part][row] = tile_max;
-      tc_fence_before();
-      __syncthreads();
-#pragma unroll
-      for (int q = 0; q < kSplit; ++q) tile_max = fmaxf(tile_max, max_s[q][row]);
-      const float m_new = fmaxf(m_run, tile_max);
-      const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      const float alpha = m_run == -INFINITY ? 0.f : exp2f(m_run - m_use);
-      m_run = m_new;
-      l_run *= alpha;
-
-      // (3) P(t-1) . V(t-1) is complete: add it (still at the old maximum's scale), then its
-      // value tile is free for V(t+1) and P's tile for P(t)
-      if (t > 0) {
-        if (!mbar_wait(bar_o, (t - 1) & 1, giveup)) { ok_all = false; break; }
+      // the last tile's P . V
+      if (n_tiles > 0) {
+        if (ok_all && !mbar_wait(bar_o, (n_tiles - 1) & 1, giveup)) ok_all = false;
         tc_fence_after();
 #pragma unroll
         for (int c = 0; c < kOC; c += 16) {
@@ -327,88 +408,38 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ qkv, int row_strid
           for (int j = 0; j < 16; ++j) o_acc[c + j] += pv[j];
         }
       }
-      copy_v(t + 1);
-      if (alpha != 1.f) {
-#pragma unroll
-        for (int i = 0; i < kOC; ++i) o_acc[i] *= alpha;
-      }
-#pragma unroll
-      for (int c = 0; c < kSC / 8; ++c) {
-        uint32_t packed[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float p0 = exp2f(sc[c * 8 + 2 * j] - m_use), p1 = exp2f(sc[c * 8 + 2 * j + 1] - m_use);
-          l_run += p0 + p1;
-          __nv_bfloat162 v2 = __floats2bfloat162_rn(p0, p1);
-          packed[j] = *reinterpret_cast<uint32_t*>(&v2);
-        }
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_t + swizzled(row, col0 / 8 + c)),
-                     "r"(packed[0]), "r"(packed[1]), "r"(packed[2]), "r"(packed[3])
-                     : "memory");
-      }
-      // (4) V(t) has to have landed (groups so far: .. V(t), K(t+2), V(t+1)); then P(t) . V(t)
-      cp_async_wait<2>();
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      tc_fence_before();
-      __syncthreads();
-      if (tid == 0) {
-        tc_fence_after();
-        const uint32_t v_s = v_t + (t & 1) * kTileBytes;
-#pragma unroll
-        for (int ks = 0; ks < kKeys / 16; ++ks) {
-          // A = P: 16 keys further along a row; B = V: 16 keys = 16 rows = 2048 bytes further
-          const uint32_t a_off = (ks >> 2) * (128 * 128) + (ks & 3) * 32;
-          umma_bf16(tmem_base + 2 * kKeys, smem_desc_sw128(p_t + a_off),
-                    smem_desc_mn_sw128(v_s + ks * 2048, 128 * 128), idesc_o, ks > 0 ? 1u : 0u);
-        }
-        umma_commit(bar_o);
-      }
-    }
-    // the last tile's P . V
-    if (ok_all && n_tiles > 0) {
-      if (!mbar_wait(bar_o, (n_tiles - 1) & 1, giveup)) ok_all = false;
-      if (ok_all) {
-        tc_fence_after();
-#pragma unroll
-        for (int c = 0; c < kOC; c += 16) {
-          float pv[16];
-          tmem_ld16(t_row + 2 * kKeys + part * kOC + c, pv);
-#pragma unroll
-          for (int j = 0; j < 16; ++j) o_acc[c + j] += pv[j];
-        }
-      }
-    }
 
-    // the row's sum from its four parts, then every thread writes its columns
-    __syncthreads();
-    max_s[part][row] = l_run;
-    __syncthreads();
-    float l_row = 0.f;
+      // the row's sum from its four parts, then every thread writes its columns
+      named_barrier_sync(1, kThreads);
+      max_s[0][part][row] = l_run;
+      named_barrier_sync(1, kThreads);
+      float l_row = 0.f;
 #pragma unroll
-    for (int q = 0; q < kSplit; ++q) l_row += max_s[q][row];
-    if (ok_all && my_pos >= 0) {
-      const int hh = row - my_tl * g;
-      const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
-      __nv_bfloat16* dst = out + (size_t)(q0 + tok0 + my_tl) * out_stride + (size_t)(kvh * g + hh) * D + part * kOC;
+      for (int q = 0; q < kSplit; ++q) l_row += max_s[0][q][row];
+      if (ok_all && my_pos >= 0) {
+        const int hh = row - my_tl * g;
+        const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
+        __nv_bfloat16* dst = out + (size_t)(q0 + tok0 + my_tl) * out_stride + (size_t)(kvh * g + hh) * D + part * kOC;
 #pragma unroll
-      for (int c = 0; c < kOC; c += 8) {
-        uint32_t packed[4];
+        for (int c = 0; c < kOC; c += 8) {
+          uint32_t packed[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          __nv_bfloat162 v2 = __floats2bfloat162_rn(o_acc[c + 2 * j] * inv, o_acc[c + 2 * j + 1] * inv);
-          packed[j] = *reinterpret_cast<uint32_t*>(&v2);
+          for (int j = 0; j < 4; ++j) {
+            __nv_bfloat162 v2 = __floats2bfloat162_rn(o_acc[c + 2 * j] * inv, o_acc[c + 2 * j + 1] * inv);
+            packed[j] = *reinterpret_cast<uint32_t*>(&v2);
+          }
+          *reinterpret_cast<uint4*>(dst + c) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
         }
-        *reinterpret_cast<uint4*>(dst + c) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
       }
+      cp_async_wait<0>();
     }
-    cp_async_wait<0>();
   }
 
   // ---------------- teardown ----------------
   tc_fence_before();
   __syncthreads();
   if (gave_up && tid == 0) set_status(status, kWaitTimeout, blockIdx.x, 1);
-  if (warp == 0) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
@@ -427,8 +458,8 @@ int launch(const __nv_bfloat16* qkv, int row_stride, __nv_bfloat16* out, int out
   }
   const int g = n_q / pa.n_kv;
   const int tq = kRows / g;
-  dim3 grid((max_q_len + tq - 1) / tq, pa.n_kv, n_seqs);
-  return launch_kernel(attention_prefill_tc_kernel<D>, grid, dim3(kThreads), smem_bytes<D>(), stream, qkv,
+  dim3 grid(((max_q_len + tq - 1) / tq) * pa.n_kv, 1, n_seqs);
+  return launch_kernel(attention_prefill_tc_kernel<D>, grid, dim3(kBlockThreads), smem_bytes<D>(), stream, qkv,
                        row_stride, out, out_stride, pa, q_start, ctx_len, n_q, scale, window, status);
 }
 
@@ -447,7 +478,7 @@ extern "C" int leone_attention_prefill_tc(const void* qkv, int row_stride, void*
   if (n_seqs <= 0 || max_q_len <= 0) return 0;
   if (d != 64 && d != 128) return kRefusedSize;
   if (n_q <= 0 || n_kv <= 0 || n_q % n_kv != 0 || n_q / n_kv > tcattn::kRows) return kRefusedSize;
-  if (page_tokens <= 0 || table_width <= 0 || n_kv > 65535 || n_seqs > 65535) return kRefusedSize;
+  if (page_tokens <= 0 || table_width <= 0 || n_seqs > 65535) return kRefusedSize;
   if (row_stride % 8 != 0 || out_stride % 8 != 0) return kRefusedAlignment;
   if (((uintptr_t)qkv | (uintptr_t)out | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) return kRefusedAlignment;
   tcattn::PagedArgs pa{(const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, block_table, table_width,
