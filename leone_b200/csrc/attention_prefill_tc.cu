@@ -64,6 +64,13 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
+// 2^x by the special-function unit (x <= 0 here; -inf gives 0).
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // Byte offset of 16-byte chunk `chunk` (8 elements) of row `row` in a tile of rows of
 // D elements stored as D/64 swizzled halves of [128 rows x 128 bytes].
 __device__ __forceinline__ uint32_t swizzled(int row, int chunk) {
@@ -333,22 +340,21 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ qkv, int row_strid
         for (int c = 0; c < kSC; c += 16) tmem_ld16(t_row + (t & 1) * kKeys + col0 + c, sc + c);
         const bool all_visible = tile_start + kKeys - 1 <= first_pos &&
                                  (window <= 0 || tile_start > last_pos - window) && my_pos >= 0;
+        // the maximum of the raw scores; the scale (positive) goes into the exponent's multiply-add
         float tile_max = -INFINITY;
         if (all_visible) {
 #pragma unroll
-          for (int j = 0; j < kSC; ++j) {
-            sc[j] *= sl2;
-            tile_max = fmaxf(tile_max, sc[j]);
-          }
+          for (int j = 0; j < kSC; ++j) tile_max = fmaxf(tile_max, sc[j]);
         } else {
 #pragma unroll
           for (int j = 0; j < kSC; ++j) {
             const int kj = tile_start + col0 + j;
             const bool keep = my_pos >= 0 && kj <= my_pos && (window <= 0 || kj > my_pos - window);
-            sc[j] = keep ? sc[j] * sl2 : -INFINITY;
+            sc[j] = keep ? sc[j] : -INFINITY;
             tile_max = fmaxf(tile_max, sc[j]);
           }
         }
+        tile_max *= sl2;                   // (-inf stays -inf)
         max_s[t & 1][part][row] = tile_max;
         named_barrier_sync(1, kThreads);   // the row maximum's parts, and the row sources of tile t+2
         copy_k(t + 2);
@@ -356,7 +362,7 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ qkv, int row_strid
         for (int q = 0; q < kSplit; ++q) tile_max = fmaxf(tile_max, max_s[t & 1][q][row]);
         const float m_new = fmaxf(m_run, tile_max);
         const float m_use = m_new == -INFINITY ? 0.f : m_new;
-        const float alpha = m_run == -INFINITY ? 0.f : exp2f(m_run - m_use);
+        const float alpha = m_run == -INFINITY ? 0.f : ex2(m_run - m_use);
         m_run = m_new;
         l_run *= alpha;
 
@@ -383,7 +389,7 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ qkv, int row_strid
           uint32_t packed[4];
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const float p0 = exp2f(sc[c * 8 + 2 * j] - m_use), p1 = exp2f(sc[c * 8 + 2 * j + 1] - m_use);
+            const float p0 = ex2(fmaf(sc[c * 8 + 2 * j], sl2, -m_use)), p1 = ex2(fmaf(sc[c * 8 + 2 * j + 1], sl2, -m_use));
             l_run += p0 + p1;
             __nv_bfloat162 v2 = __floats2bfloat162_rn(p0, p1);
             packed[j] = *reinterpret_cast<uint32_t*>(&v2);
