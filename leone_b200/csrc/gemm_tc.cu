@@ -374,6 +374,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
               }
             }
           }
+        } else if (p.epilogue == 2 && vec_ok && n0 + BN <= p.N) {
+          // fp32 out = acc + residual for a whole row of the tile: the residual is fetched three
+          // chunks ahead of its use, so its latency is paid once per row, not once per chunk
+          // (the residual may be the output itself: a chunk is read before it is written, and
+          // chunks do not overlap).  The branch is the same for every thread of the block, as
+          // the warp-wide tensor-memory loads need; rows past M read row 0 and store nothing.
+          constexpr int kAhead = 3;
+          const bool row_ok = m < p.M;
+          const size_t row_at = (size_t)(row_ok ? m : 0) * p.ldc + n0;
+          const float4* res = reinterpret_cast<const float4*>(p.residual + row_at);
+          float4* dst = reinterpret_cast<float4*>((float*)p.out + row_at);
+          float4 rb[kAhead][4];
+#pragma unroll
+          for (int a = 0; a < kAhead; ++a)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) rb[a][j] = res[a * 4 + j];
+#pragma unroll
+          for (int i = 0; i < BN / 16; ++i) {
+            float v[16];
+            tmem_ld16(taddr + i * 16, v);
+            float4 r[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) r[j] = rb[i % kAhead][j];
+            if (i + kAhead < BN / 16) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) rb[i % kAhead][j] = res[(i + kAhead) * 4 + j];
+            }
+            if (row_ok) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                dst[i * 4 + j] = make_float4(v[4 * j] + r[j].x, v[4 * j + 1] + r[j].y, v[4 * j + 2] + r[j].z,
+                                             v[4 * j + 3] + r[j].w);
+            }
+          }
         } else {
           for (int c = 0; c < BN; c += 16) {
             float v[16];

@@ -36,6 +36,7 @@ class FastKernels:
         # LEONE_NO_FUSED_NORM=1 keeps every RMSNorm a kernel of its own
         self.fuse_norm = os.environ.get("LEONE_NO_FUSED_NORM", "0") != "1"
         self.fuse_norm_tokens = 32
+        self.force_decode_splits = int(os.environ.get("LEONE_DECODE_SPLITS", "0"))    # tuning aid
         # LEONE_NO_FUSED_DECODE=1 keeps q/k norm, rotation and cache write in their own kernel
         self.fuse_decode = os.environ.get("LEONE_NO_FUSED_DECODE", "0") != "1"
         self.max_cluster = int(os.environ.get("LEONE_MAX_CLUSTER", "8"))
@@ -191,12 +192,17 @@ class FastKernels:
     def decode_splits(self, n_seqs: int, n_kv: int, g: int, max_ctx: int) -> int:
         """Splits of the key range.  Two blocks fit an SM; the cost of a choice is its number of
         rounds over those slots times the share of the keys a block walks, plus a little per
-        split for the merge.  A split keeps at least 128 keys."""
+        split for the merge, plus a fixed charge when the splits cannot merge inside clusters
+        (scratch and a merge kernel; measured at batch 64: one split 101 us, two to four 109-112).
+        A split keeps at least 128 keys."""
+        if self.force_decode_splits:
+            return self.force_decode_splits
         blocks = n_seqs * n_kv * (-(-g // 16))
         slots = 2 * self.sm_count
         best, best_cost = 1, None
         for s in range(1, min(32, max(1, max_ctx // 128)) + 1):
-            cost = -(-(blocks * s) // slots) / s + 0.02 * s
+            clustered = self.use_clusters and s <= 8 and blocks * s <= slots
+            cost = -(-(blocks * s) // slots) / s + 0.03 * s + (0.0 if s == 1 or clustered else 0.2)
             if best_cost is None or cost < best_cost - 1e-9:
                 best, best_cost = s, cost
         return best
@@ -213,13 +219,14 @@ class FastKernels:
                 and self.decode_in_clusters(ctx.n_seqs, n_kv, n_q // n_kv, ctx.max_ctx_len))
 
     def decode_in_clusters(self, n_seqs: int, n_kv: int, g: int, max_ctx: int) -> bool:
-        """Whether a decode step's splits merge inside thread-block clusters: when all blocks
-        are resident at once.  With several rounds of blocks, clusters (which need all their
+        """Whether a decode step runs the kernel whose splits merge inside thread-block clusters
+        (and which can do the q/k preparation itself): with one split, or when all blocks are
+        resident at once.  With several rounds of blocks, clusters (which need all their
         blocks' slots free in one GPC at the same moment) were measured slower than scratch
         and a merge kernel."""
         splits = self.decode_splits(n_seqs, n_kv, g, max_ctx)
         blocks = n_seqs * n_kv * (-(-g // 16)) * splits
-        return self.use_clusters and splits <= 8 and blocks <= 2 * self.sm_count
+        return self.use_clusters and (splits == 1 or (splits <= 8 and blocks <= 2 * self.sm_count))
 
     def attention(self, ctx, qkv, out, n_q, n_kv, d, scale, window, cache, fuse=None) -> bool:
         if not self.attention_supported(qkv.dtype, n_q, n_kv, d, qkv.stride(0)):
