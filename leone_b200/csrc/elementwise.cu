@@ -223,7 +223,7 @@ __global__ void qk_norm_rope_write_kernel(
 // away) sits in lane ^ 16 at the same place and comes by one shuffle; loads and stores are
 // 4- to 16-byte vectors.
 template <int E, typename TW>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 qk_norm_rope_write_vec_kernel(
     __nv_bfloat16* __restrict__ qkv, int n_tokens, int n_q, int n_kv, const TW* __restrict__ q_w,
     const TW* __restrict__ k_w, float eps, const float2* __restrict__ rope, int max_positions,
@@ -231,79 +231,97 @@ qk_norm_rope_write_vec_kernel(
     const int* __restrict__ block_table, int table_width, int n_seqs,
     __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool, int num_pages,
     int page_tokens, int* status) {
+  // One block per token, a warp per head at a time: the token's position, page, rotation row
+  // and the norm weights are fetched once per warp and serve all its heads, and the next
+  // head's row is requested before the current one is worked on.
   constexpr int d = 32 * E;
   pdl_trigger();
   pdl_wait();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
   const int heads = n_q + 2 * n_kv;
-  const long long item = (long long)blockIdx.x * 4 + warp;
-  if (item >= (long long)n_tokens * heads) return;
-  const int t = (int)(item / heads), h = (int)(item - (long long)t * heads);
-  const bool is_q = h < n_q, is_k = !is_q && h < n_q + n_kv;
-  __nv_bfloat16* row = qkv + ((size_t)t * heads + h) * d + lane * E;
+  const int t = blockIdx.x;
   const int pos = positions[t];
-  float v[E];
-  {
-    const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(row);
-#pragma unroll
-    for (int i = 0; i < E / 2; ++i) {
-      const __nv_bfloat162 two = p2[i];
-      v[2 * i] = __low2float(two);
-      v[2 * i + 1] = __high2float(two);
-    }
-  }
-  const TW* w = is_q ? q_w : (is_k ? k_w : nullptr);
-  if (w != nullptr) {
-    float ss = 0.f;
-#pragma unroll
-    for (int i = 0; i < E; ++i) ss = fmaf(v[i], v[i], ss);
-    ss = warp_sum(ss);
-    const float inv = rsqrtf(ss / (float)d + eps);
-#pragma unroll
-    for (int i = 0; i < E; ++i) v[i] = v[i] * to_float<TW>(w[lane * E + i]) * inv;
-  }
-  const bool rotate = (is_q || is_k) && rope != nullptr;
+  const bool rotate = rope != nullptr;
   if (rotate && (pos < 0 || pos >= max_positions)) {
-    if (lane == 0) set_status(status, kBadPosition, t, pos);
+    if (threadIdx.x == 0) set_status(status, kBadPosition, t, pos);
     return;
   }
-  __nv_bfloat16* cache_row = nullptr;
-  if (!is_q && k_pool != nullptr) {
+  long long cache_at = -1;                       // element offset of (page, kv head 0, slot) in the pools
+  if (k_pool != nullptr) {
     const int s = seq_of_token[t];
     if (s < 0 || s >= n_seqs) {
-      if (lane == 0) set_status(status, kBadSequence, t, s);
+      if (threadIdx.x == 0) set_status(status, kBadSequence, t, s);
       return;
     }
     const int blk = pos / page_tokens;
     const int page = (pos >= 0 && blk < table_width) ? block_table[(size_t)s * table_width + blk] : -1;
     if (page < 0 || page >= num_pages) {
-      if (lane == 0) set_status(status, kBadPage, t, page, pos);
+      if (threadIdx.x == 0) set_status(status, kBadPage, t, page, pos);
       return;
     }
-    const int kvh = is_k ? h - n_q : h - n_q - n_kv;
-    __nv_bfloat16* pool = is_k ? k_pool : v_pool;
-    cache_row = pool + (((size_t)page * n_kv + kvh) * page_tokens + (pos % page_tokens)) * d + lane * E;
+    cache_at = ((long long)page * n_kv * page_tokens + (pos % page_tokens)) * d;
   }
-  if (rotate) {
-    const bool upper = lane >= 16;                   // elements of the second half
-    const int pair0 = (lane & 15) * E;               // pair index of this lane's first element
+  const bool upper = lane >= 16;                   // elements of the second half
+  const int pair0 = (lane & 15) * E;               // pair index of this lane's first element
+  float2 cs[E];
+  float wq[E], wk[E];
 #pragma unroll
-    for (int i = 0; i < E; ++i) {
-      const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
-      const float2 cs = rope[(size_t)pos * (d / 2) + pair0 + i];
-      v[i] = upper ? other * cs.y + v[i] * cs.x : v[i] * cs.x - other * cs.y;
+  for (int i = 0; i < E; ++i) {
+    cs[i] = rotate ? rope[(size_t)pos * (d / 2) + pair0 + i] : make_float2(1.f, 0.f);
+    wq[i] = q_w != nullptr ? to_float<TW>(q_w[lane * E + i]) : 1.f;
+    wk[i] = k_w != nullptr ? to_float<TW>(k_w[lane * E + i]) : 1.f;
+  }
+  __nv_bfloat16* tok = qkv + (size_t)t * heads * d + lane * E;
+  auto fetch = [&](int h, __nv_bfloat162 (&raw)[E / 2]) {
+    if (h < heads) {
+      const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(tok + (size_t)h * d);
+#pragma unroll
+      for (int i = 0; i < E / 2; ++i) raw[i] = p2[i];
     }
-  }
-  __nv_bfloat162 o2[E / 2];
+  };
+  __nv_bfloat162 nxt[E / 2];
+  fetch(warp, nxt);
+  for (int h = warp; h < heads; h += n_warps) {
+    float v[E];
 #pragma unroll
-  for (int i = 0; i < E / 2; ++i) o2[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-  if (is_q || is_k) {
+    for (int i = 0; i < E / 2; ++i) {
+      v[2 * i] = __low2float(nxt[i]);
+      v[2 * i + 1] = __high2float(nxt[i]);
+    }
+    fetch(h + n_warps, nxt);
+    const bool is_q = h < n_q, is_k = !is_q && h < n_q + n_kv;
+    if ((is_q && q_w != nullptr) || (is_k && k_w != nullptr)) {
+      float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < E / 2; ++i) reinterpret_cast<__nv_bfloat162*>(row)[i] = o2[i];
-  }
-  if (cache_row != nullptr) {
+      for (int i = 0; i < E; ++i) ss = fmaf(v[i], v[i], ss);
+      ss = warp_sum(ss);
+      const float inv = rsqrtf(ss / (float)d + eps);
 #pragma unroll
-    for (int i = 0; i < E / 2; ++i) reinterpret_cast<__nv_bfloat162*>(cache_row)[i] = o2[i];
+      for (int i = 0; i < E; ++i) v[i] = v[i] * (is_q ? wq[i] : wk[i]) * inv;
+    }
+    if (rotate && (is_q || is_k)) {
+#pragma unroll
+      for (int i = 0; i < E; ++i) {
+        const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
+        v[i] = upper ? other * cs[i].y + v[i] * cs[i].x : v[i] * cs[i].x - other * cs[i].y;
+      }
+    }
+    __nv_bfloat162 o2[E / 2];
+#pragma unroll
+    for (int i = 0; i < E / 2; ++i) o2[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    if (is_q || is_k) {
+      __nv_bfloat162* row = reinterpret_cast<__nv_bfloat162*>(tok + (size_t)h * d);
+#pragma unroll
+      for (int i = 0; i < E / 2; ++i) row[i] = o2[i];
+    }
+    if (!is_q && cache_at >= 0) {
+      const int kvh = is_k ? h - n_q : h - n_q - n_kv;
+      __nv_bfloat16* pool = is_k ? k_pool : v_pool;
+      __nv_bfloat162* cache_row =
+          reinterpret_cast<__nv_bfloat162*>(pool + cache_at + (long long)kvh * page_tokens * d + lane * E);
+#pragma unroll
+      for (int i = 0; i < E / 2; ++i) cache_row[i] = o2[i];
+    }
   }
 }
 
@@ -551,10 +569,12 @@ extern "C" int leone_qk_norm_rope_write(
   const long long items = (long long)n_tokens * (n_q + 2 * n_kv);
   const int blocks = (int)((items + warps - 1) / warps);
   const size_t smem = (size_t)warps * d * sizeof(float);
+  // the vector kernel: a block per token, a warp for up to every eighth head
+  const int vec_threads = 32 * (n_q + 2 * n_kv < 8 ? n_q + 2 * n_kv : 8);
   if (dtype == 1 && (d == 64 || d == 128 || d == 256) && (rope == nullptr || rotary_dim == d) &&
       (q_w == nullptr) == (k_w == nullptr)) {
 #define LAUNCH_VEC(E, TW)                                                                          \
-  return launch_kernel(qk_norm_rope_write_vec_kernel<E, TW>, dim3(blocks), dim3(128), 0, stream,   \
+  return launch_kernel(qk_norm_rope_write_vec_kernel<E, TW>, dim3(n_tokens), dim3(vec_threads), 0, stream, \
                        (__nv_bfloat16*)qkv, n_tokens, n_q, n_kv, (const TW*)q_w, (const TW*)k_w, eps, \
                        (const float2*)rope, max_positions, positions, seq_of_token, block_table,  \
                        table_width, n_seqs, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool,        \

@@ -348,12 +348,48 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int m = m_tile * kTileW + row_local;
         const int n0 = n_tile * BN;
         const bool vec_ok = (p.ldc & 7) == 0;
+        // the norm before this product: this row's factor from the parts the product before left
+        float rs = 1.f;
+        if (p.norm_in_ss != nullptr) {
+          float ss = 0.f;
+          if (m < p.M)
+            for (int q = 0; q < p.norm_in_parts; ++q) ss += p.norm_in_ss[(size_t)q * p.M + m];
+          rs = rsqrtf(ss / (float)p.K + p.norm_eps);
+        }
+        // the norm after this product: this row's sum of squares over the tile's columns, and
+        // bf16(out * weight) beside the output (token-major: one part per tile of BN columns)
+        float ssq = 0.f;
+        auto norm_out16 = [&](const float (&val)[16], int n) {      // 16 finished outputs from column n
+          if (p.norm_out_x != nullptr && m < p.M && n < p.N) {
+            uint32_t packed[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float a = n + 2 * j < p.N ? val[2 * j] : 0.f, b = n + 2 * j + 1 < p.N ? val[2 * j + 1] : 0.f;
+              ssq = fmaf(a, a, fmaf(b, b, ssq));
+              __nv_bfloat162 v2 = __floats2bfloat162_rn(a * (n + 2 * j < p.N ? p.norm_out_w[n + 2 * j] : 0.f),
+                                                        b * (n + 2 * j + 1 < p.N ? p.norm_out_w[n + 2 * j + 1] : 0.f));
+              packed[j] = *reinterpret_cast<uint32_t*>(&v2);
+            }
+            __nv_bfloat16* xrow = p.norm_out_x + (size_t)m * p.ld_norm_out + n;
+            if (n + 16 <= p.N && (p.ld_norm_out & 7) == 0) {
+              reinterpret_cast<uint4*>(xrow)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+              reinterpret_cast<uint4*>(xrow)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+            } else {
+              for (int j = 0; j < 16 && n + j < p.N; ++j)
+                xrow[j] = __float2bfloat16_rn(val[j] * p.norm_out_w[n + j]);
+            }
+          }
+        };
         if (p.epilogue == 3) {
           __nv_bfloat16* orow = (__nv_bfloat16*)p.out + (size_t)m * p.ldc;
           for (int c = 0; c < BN; c += 32) {             // 16 gate columns, then their 16 up columns
             float g[16], u[16];
             tmem_ld16(taddr + c, g);
             tmem_ld16(taddr + c + 16, u);
+            if (p.norm_in_ss != nullptr) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) { g[j] *= rs; u[j] *= rs; }
+            }
             const int col = (n0 + c) >> 1;
             if (m < p.M && n0 + c < p.N) {
               uint32_t packed[8];
@@ -401,12 +437,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
               for (int j = 0; j < 4; ++j) rb[i % kAhead][j] = res[(i + kAhead) * 4 + j];
             }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              v[4 * j] += r[j].x; v[4 * j + 1] += r[j].y; v[4 * j + 2] += r[j].z; v[4 * j + 3] += r[j].w;
+            }
             if (row_ok) {
 #pragma unroll
               for (int j = 0; j < 4; ++j)
-                dst[i * 4 + j] = make_float4(v[4 * j] + r[j].x, v[4 * j + 1] + r[j].y, v[4 * j + 2] + r[j].z,
-                                             v[4 * j + 3] + r[j].w);
+                dst[i * 4 + j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
             }
+            norm_out16(v, n0 + i * 16);
           }
         } else {
           for (int c = 0; c < BN; c += 16) {
@@ -414,6 +454,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             tmem_ld16(taddr + c, v);
             const int n = n0 + c;
             if (m >= p.M || n >= p.N) continue;
+            if (p.norm_in_ss != nullptr) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] *= rs;
+            }
             const size_t o = (size_t)m * p.ldc + n;
             const bool full = n + 16 <= p.N && vec_ok;
             if (p.epilogue == 0) {
@@ -445,12 +489,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 for (int j = 0; j < 4; ++j)
                   reinterpret_cast<float4*>(dst)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
               } else {
-                for (int j = 0; j < 16 && n + j < p.N; ++j)
-                  dst[j] = p.epilogue == 2 ? v[j] + p.residual[o + j] : v[j];
+                for (int j = 0; j < 16 && n + j < p.N; ++j) {
+                  if (p.epilogue == 2) v[j] += p.residual[o + j];
+                  dst[j] = v[j];
+                }
               }
+              norm_out16(v, n);
             }
           }
         }
+        if (p.norm_out_x != nullptr && m < p.M) p.norm_out_ss[(size_t)n_tile * p.M + m] = ssq;
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
@@ -693,8 +741,9 @@ extern "C" int leone_gemm_tc_tiles(int m, int n) {
   return ((n + kTileW - 1) / kTileW) * ((m + bn - 1) / bn);
 }
 
-// Parts of the sums of squares a product with n outputs leaves for the norm after it.
-extern "C" int leone_gemm_tc_norm_parts(int n) { return (n + 31) / 32; }
+// Parts of the sums of squares a product of m tokens with n outputs leaves for the norm after
+// it: one per 32 weight rows up to 256 tokens, one per tile of 256 weight rows above.
+extern "C" int leone_gemm_tc_norm_parts(int m, int n) { return m <= 256 ? (n + 31) / 32 : (n + 255) / 256; }
 
 // Workspace floats and counters needed when `split_tiles` tiles are split `splits` ways;
 // both 0 when splits == 1.
@@ -723,10 +772,10 @@ extern "C" int leone_gemm_tc_cluster_capacity(int m, int splits) {
 // The first `full_tiles` tiles (in the kernel's tile order) are computed whole; the others have K
 // split `splits` ways.  splits > 1 needs `workspace` (fp32) and zeroed `counters` of the sizes
 // leone_gemm_tc_scratch gives for (tiles - full_tiles).  More than 256 tokens are never split.
-// A norm between two products without a kernel of its own (at most 256 tokens):
+// A norm between two products without a kernel of its own:
 //  norm_out_x != null (epilogue 1 or 2): also write norm_out_x[m][n] = bf16(out[m][n] * norm_out_w[n])
-//    (row stride ld_norm_out) and norm_out_ss[(n / 32)][m] = sum of out[m][n]^2 over those 32 rows;
-//    leone_gemm_tc_norm_parts(n) gives the number of parts;
+//    (row stride ld_norm_out) and norm_out_ss[part][m] = sum of out[m][n]^2 over the part's weight
+//    rows; leone_gemm_tc_norm_parts(m, n) gives the number of parts;
 //  norm_in_ss != null: every output of token m is scaled by rsqrt(sum_p norm_in_ss[p][m] / k + norm_eps)
 //    (x is then the norm_out_x another product wrote).
 // cluster != 0: the splits of a tile form a thread-block cluster and are summed through
@@ -750,10 +799,9 @@ extern "C" int leone_gemm_tc(const void* x, const void* w, void* out, const floa
   // every split must own at least one k-block
   while (splits > 1 && (splits - 1) * ((k_blocks + splits - 1) / splits) >= k_blocks) --splits;
   if (splits == 1) cluster = 0;
-  if (norm_out_x != nullptr &&
-      (m > 256 || (epilogue != 1 && epilogue != 2) || norm_out_w == nullptr || norm_out_ss == nullptr))
+  if (norm_out_x != nullptr && ((epilogue != 1 && epilogue != 2) || norm_out_w == nullptr || norm_out_ss == nullptr))
     return kRefusedSize;
-  if (norm_in_ss != nullptr && (m > 256 || norm_in_parts < 1)) return kRefusedSize;
+  if (norm_in_ss != nullptr && norm_in_parts < 1) return kRefusedSize;
   if (cluster && (full_tiles != 0 || splits > 8 || m > 256)) return kRefusedSize;
   if (splits > 1 && !cluster && (workspace == nullptr || counters == nullptr)) return kRefusedSize;
   const int tiles = leone_gemm_tc_tiles(m, n);

@@ -75,9 +75,9 @@ def bench_gemm(ops, m, n, k, splits, epilogue, reps, warmup, flush, trace=False,
     norm_out = norm_in = None
     if norm == "out":
         norm_out = (torch.empty((m, n), device=DEV, dtype=torch.bfloat16), torch.ones(n, device=DEV),
-                    torch.empty((fast.norm_parts(n), m), device=DEV))
+                    torch.empty((fast.norm_parts(m, n), m), device=DEV))
     elif norm == "in":
-        parts = fast.norm_parts(k)
+        parts = fast.norm_parts(m, k)
         norm_in = (torch.rand((parts, m), device=DEV), parts, 1e-6)
 
     def run():

@@ -176,9 +176,10 @@ class CudaOps:
                 and wt.shape[0] % 8 == 0 and wt.shape[1] % 8 == 0 and wt.stride(0) % 8 == 0
                 and wt.data_ptr() % 16 == 0)
 
-    def norm_parts(self, n: int) -> int:
-        """Rows of the ``ss`` buffer a product with ``n`` outputs fills for the norm after it."""
-        return self.fast.norm_parts(n)
+    def norm_parts(self, n_tokens: int, n: int) -> int:
+        """Rows of the ``ss`` buffer a product of ``n_tokens`` tokens with ``n`` outputs fills for
+        the norm after it."""
+        return self.fast.norm_parts(n_tokens, n)
 
     def _norm_args(self, m, w, norm_in, norm_out):
         ni = no = None
@@ -193,7 +194,7 @@ class CudaOps:
                   and d.weight.numel() == w.out_features and d.xn.dtype == torch.bfloat16
                   and d.xn.shape == (m, w.out_features) and d.xn.stride(1) == 1
                   and d.ss.dtype == torch.float32 and d.ss.is_contiguous()
-                  and d.ss.shape == (self.norm_parts(w.out_features), m), "linear: norm_out layout")
+                  and d.ss.shape == (self.norm_parts(m, w.out_features), m), "linear: norm_out layout")
             no = (d.xn, d.weight, d.ss)
         return ni, no
 

@@ -155,13 +155,14 @@ class FastKernels:
         return True
 
     def fuses_norm(self, m: int) -> bool:
-        """Whether the products of ``m`` tokens carry an RMSNorm between them.  The kernels take
-        up to 256 tokens; beyond 32 the extra work in the two epilogues was measured to cost
-        more than the norm kernel it replaces."""
-        return self.use_tensor_cores and self.fuse_norm and 0 < m <= self.fuse_norm_tokens
+        """Whether the products of ``m`` tokens carry an RMSNorm between them: decode-sized steps
+        (up to 32 tokens; from there to 256 the extra work in the two epilogues was measured to
+        cost more than the norm kernel it replaces) and prompt-sized ones (over 256 tokens,
+        where a thread owns a token row and the sums are its own)."""
+        return self.use_tensor_cores and self.fuse_norm and (0 < m <= self.fuse_norm_tokens or m > 256)
 
-    def norm_parts(self, n: int) -> int:
-        return int(self.lib.leone_gemm_tc_norm_parts(n))
+    def norm_parts(self, m: int, n: int) -> int:
+        return int(self.lib.leone_gemm_tc_norm_parts(m, n))
 
     def linear(self, x, w, out, epilogue, residual, norm_in=None, norm_out=None) -> bool:
         if not self._tc_ok(x, w.weight, out):

@@ -86,7 +86,7 @@ class Attention(Mixer):
         ops = self.rt.ops
         n = hidden.shape[0]
         if then is not None and hasattr(ops, "linear_fuses_norm") and ops.linear_fuses_norm(n, self.w_o):
-            then.prepare(self.rt, ops.norm_parts(self.hidden))
+            then.prepare(self.rt, ops.norm_parts(n, self.hidden))
             ops.linear(attn, self.w_o, hidden, residual=hidden, norm_out=then)
             then.ready = True
         else:

@@ -52,7 +52,7 @@ class SwiGLU(FeedForward):
         else:
             ops.linear_swiglu(x, self.w_gate_up, act)
         if then is not None and hasattr(ops, "linear_fuses_norm") and ops.linear_fuses_norm(n, self.w_down):
-            then.prepare(self.rt, ops.norm_parts(self.hidden))
+            then.prepare(self.rt, ops.norm_parts(n, self.hidden))
             ops.linear(act, self.w_down, hidden, residual=hidden, norm_out=then)
             then.ready = True
         else:

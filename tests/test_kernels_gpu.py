@@ -233,7 +233,8 @@ def test_gemm_tc_cluster_split(ops16, m, n, k, splits):
 @pytest.mark.parametrize("m,n,k,splits,cluster", [(1, 384, 4096, 1, False), (8, 1000, 1032, 1, False),
                                                   (5, 640, 520, 3, True), (16, 4096, 4096, 4, True),
                                                   (17, 256, 2048, 2, True), (33, 1024, 1024, 5, True),
-                                                  (64, 520, 4096, 3, False), (200, 384, 768, 6, True)])
+                                                  (64, 520, 4096, 3, False), (200, 384, 768, 6, True),
+                                                  (300, 520, 512, 1, False), (1000, 1024, 264, 1, False)])
 def test_gemm_tc_norm_between_products(ops16, m, n, k, splits, cluster):
     """An RMSNorm folded into the product before it (which leaves bf16(out * weight) and the sums
     of out^2) and the product after it (which scales its rows): against float64."""
@@ -245,7 +246,7 @@ def test_gemm_tc_norm_between_products(ops16, m, n, k, splits, cluster):
     g = 1 + 0.2 * _randn((n,), 44)
     eps = 1e-5
     hidden = res.clone()
-    parts = fast.norm_parts(n)
+    parts = fast.norm_parts(m, n)
     xn = torch.full((m, n), 7.0, device=DEV, dtype=torch.bfloat16)
     ss = torch.full((parts, m), -1.0, device=DEV)
     fast._gemm(x, w1, hidden, 2, hidden, n, splits=splits, cluster=cluster, norm_out=(xn, g, ss))
@@ -287,9 +288,10 @@ def test_linear_with_norm_through_the_ops_table(ops16):
     w1 = ops16.prepare_matrix(_randn((n, k), 53, torch.bfloat16, scale=0.05))
     w2 = ops16.prepare_matrix(_randn((384, n), 54, torch.bfloat16, scale=0.05))
     assert ops16.linear_fuses_norm(m, w1) and ops16.linear_fuses_norm(m, w2)
-    assert not ops16.linear_fuses_norm(300, w1)           # prompt-sized portions keep the norm kernel
+    assert not ops16.linear_fuses_norm(100, w1)           # between 33 and 256 tokens the norm kernel stays
+    assert ops16.linear_fuses_norm(300, w1)
     d = DeferredNorm(None, None, hidden, g, 1e-6, "t")
-    d.prepare(rt, ops16.norm_parts(n))
+    d.prepare(rt, ops16.norm_parts(m, n))
     ops16.linear(x, w1, hidden, residual=hidden, norm_out=d)
     out = torch.empty((m, 384), device=DEV, dtype=torch.bfloat16)
     ops16.linear(d.xn, w2, out, norm_in=d)
