@@ -154,6 +154,7 @@ class RequestCache:
     committed_len: int = 0
     reserved_len: int = 0
     fresh: bool = True          # no step has been committed yet: state slot must be cleared
+    version: int = 0            # changes whenever a block table changes other than by growing at its end
 
 
 class CacheManager:
@@ -165,13 +166,15 @@ class CacheManager:
         self.groups = [CacheGroup(i, s, page_tokens, num_pages) for i, s in enumerate(group_specs)]
         self.slots = StateSlots(num_slots)
         self.requests: Dict[Hashable, RequestCache] = {}
+        self._versions = 0
 
     # -- lifetime -------------------------------------------------------------------
     def open(self, rid: Hashable) -> int:
         if rid in self.requests:
             raise CacheError(f"request {rid!r} is already open")
         slot = self.slots.take()
-        self.requests[rid] = RequestCache(slot=slot)
+        self._versions += 1
+        self.requests[rid] = RequestCache(slot=slot, version=self._versions)
         for g in self.groups:
             g.tables[rid] = []
         return slot
@@ -197,6 +200,11 @@ class CacheManager:
 
     def slot(self, rid: Hashable) -> int:
         return self._get(rid).slot
+
+    def table_version(self, rid: Hashable) -> int:
+        """A number that changes whenever one of the request's block tables changes other than
+        by growing at its end (a mirror of the tables may then append instead of rewriting)."""
+        return self._get(rid).version
 
     # -- the step transaction -------------------------------------------------------
     def can_reserve(self, wants: Dict[Hashable, int]) -> bool:
@@ -239,6 +247,8 @@ class CacheManager:
                 g.pool.give_back(passed)
                 for b in range(live_from):
                     table[b] = -1
+                self._versions += 1
+                rc.version = self._versions
 
     def rollback(self, rid: Hashable) -> None:
         """The step failed: return pages beyond the committed length."""
@@ -254,6 +264,9 @@ class CacheManager:
             keep = g.blocks_for(length)
             extra = [p for p in table[keep:] if p >= 0]
             g.pool.give_back(extra)
+            if len(table) > keep:
+                self._versions += 1
+                rc.version = self._versions
             del table[keep:]
         rc.committed_len = length
         rc.reserved_len = length

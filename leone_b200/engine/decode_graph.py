@@ -48,6 +48,8 @@ class DecodeGraph:
         self.logits = torch.empty((batch, engine.spec.vocab_size), dtype=torch.float32, device=dev)
         self.ctx = self._context()
         self.graph = None
+        self._filled_rids = None           # what fill() last wrote into the host copy
+        self._filled_pages = [[0] * batch for _ in engine.cache.groups]
         self.launches_per_step = 0
         self.stream = torch.cuda.Stream(device=dev)
 
@@ -81,17 +83,46 @@ class DecodeGraph:
                              self.sample_dev[2 * b:3 * b], self.sampled, self.history, self.counter)
 
     def fill(self, rids: Sequence[Hashable], last_tokens: Sequence[int], lengths: Sequence[int], params):
-        """Host → device: this quantum's starting state."""
+        """Host → device: this quantum's starting state.  The pinned host copy keeps what the
+        last call wrote, so for the same requests in the same rows only what changed is
+        rewritten: tokens, lengths, and the block-table entries of pages taken since."""
         e = self.engine
         b = self.batch
-        tables = [e.cache.block_table(g.gid, rids, width=w) for g, w in zip(e.cache.groups, self.widths)]
-        packed, _, _, _ = pack_metadata([[int(t)] for t in last_tokens], list(lengths),
-                                        [e.cache.slot(r) for r in rids], [[0]] * b, tables)
-        self.meta_host.numpy()[:] = packed
+        host = self.meta_host.numpy()
+
+        def put(name, values):
+            o, s_ = self.offsets[name]
+            host[o:o + s_] = values
+
+        lengths = np.asarray(lengths, dtype=np.int32)
+        put("token_ids", np.asarray(last_tokens, dtype=np.int32))
+        put("positions", lengths)
+        put("ctx_len", lengths + 1)
+        key = tuple((r, e.cache.table_version(r)) for r in rids)
+        same = key == self._filled_rids
+        if not same:
+            put("seq_of_token", np.arange(b, dtype=np.int32))
+            put("q_start", np.arange(b + 1, dtype=np.int32))
+            put("slot_ids", np.asarray([e.cache.slot(r) for r in rids], dtype=np.int32))
+            put("logit_rows", np.arange(b, dtype=np.int32))
+        for gi, (g, w, (o, shape)) in enumerate(zip(e.cache.groups, self.widths, self.bt_offsets)):
+            view = host[o:o + shape[0] * shape[1]].reshape(shape)
+            windowed = g.spec.kind == "window"
+            for i, r in enumerate(rids):
+                table = g.tables[r]
+                if len(table) > w:
+                    raise ValueError(f"block table needs {len(table)} columns, only {w} given")
+                done = 0 if (not same or windowed) else self._filled_pages[gi][i]
+                if done == 0:
+                    view[i, :] = -1
+                if len(table) > done:
+                    view[i, done:len(table)] = table[done:]
+                self._filled_pages[gi][i] = len(table)
+        self._filled_rids = key
         sh = self.sample_host.numpy()
         self.sample_host[:b].view(torch.float32).numpy()[:b] = np.array([p.temperature for p in params], dtype=np.float32)
         sh[b:2 * b] = np.array([p.seed & 0xFFFF_FFFF_FFFF_FFFF for p in params], dtype=np.uint64).view(np.int64)
-        sh[2 * b:3 * b] = np.asarray(lengths, dtype=np.int64)      # position of the token being fed
+        sh[2 * b:3 * b] = lengths      # position of the token being fed
         self.meta.copy_(self.meta_host, non_blocking=True)
         self.sample_dev.copy_(self.sample_host, non_blocking=True)
         self.counter.zero_()

@@ -82,6 +82,34 @@ def test_truncate():
         m.truncate("a", 6)
 
 
+def test_table_version_changes_only_when_a_table_does_not_just_grow():
+    m = _manager(pages=16, page_tokens=4)
+    m.open("a")
+    v0 = m.table_version("a")
+    m.reserve({"a": 9})
+    m.commit("a", 9)
+    m.reserve({"a": 17})
+    m.commit("a", 17)
+    assert m.table_version("a") == v0                      # growing at the end
+    m.reserve({"a": 30})
+    m.rollback("a")                                         # pages past the committed length go back
+    v1 = m.table_version("a")
+    assert v1 != v0
+    m.truncate("a", 17)                                     # nothing dropped
+    assert m.table_version("a") == v1
+    m.truncate("a", 3)
+    assert m.table_version("a") != v1
+    m.close("a")
+    m.open("a")
+    assert m.table_version("a") not in (v0, v1)             # a new life of the same name
+    w = _manager(pages=16, page_tokens=4, window=6)
+    w.open("b")
+    vb = w.table_version("b")
+    w.reserve({"b": 20})
+    w.commit("b", 20)                                       # the window has passed whole pages
+    assert w.table_version("b") != vb
+
+
 def test_window_group_gives_pages_back_as_the_window_passes():
     m = _manager(pages=8, page_tokens=4, window=6)
     m.open("a")

@@ -36,8 +36,12 @@ def _plain_logits(tensors, tokens, as_bf16):
     return pm.forward_logits(CFG, w, tokens)
 
 
-@pytest.mark.parametrize("dtype,rtol,atol_scale", [("float32", 3e-5, 3e-5), ("bfloat16", 3e-2, 3e-2)])
-def test_real_layer_sizes_under_cuts(setup, dtype, rtol, atol_scale):
+@pytest.mark.parametrize("dtype,rtol,atol_scale,fusions", [("float32", 3e-5, 3e-5, True), ("bfloat16", 3e-2, 3e-2, True),
+                                                            ("bfloat16", 3e-2, 3e-2, False)])
+def test_real_layer_sizes_under_cuts(setup, dtype, rtol, atol_scale, fusions):
+    """``fusions=False``: the same with the cluster reductions, the folded norms, the fused decode
+    preparation and the tcgen05 prompt attention switched off, i.e. the kernels that other sizes
+    fall back to."""
     from leone_b200.engine.engine import Engine
     config, spec, tensors = setup
     reqs = {"a": replay.random_tokens(151936, 300, 1), "b": replay.random_tokens(151936, 45, 2)}
@@ -56,7 +60,10 @@ def test_real_layer_sizes_under_cuts(setup, dtype, rtol, atol_scale):
                 e["want"] = [w for w in e["want"] if w % 7 == 0 or w == len(e["tokens"]) - 1]
         engine = Engine(spec, dict(tensors), dtype=dtype, page_tokens=16, max_tokens=replay.max_live_tokens(steps),
                         max_requests=4, max_batch_tokens=320)
+        if not fusions:
+            fast = engine.ops.fast
+            fast.use_clusters = fast.fuse_norm = fast.fuse_decode = fast.use_tc_attention = False
         out = replay.run_trace_engine(engine, steps)
-        replay.compare(steps, out, Plain(), reqs, rtol, atol_scale, f"8B layer sizes {dtype} {name}")
+        replay.compare(steps, out, Plain(), reqs, rtol, atol_scale, f"8B layer sizes {dtype} {name} fusions={fusions}")
         del engine
         torch.cuda.empty_cache()
