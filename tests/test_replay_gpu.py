@@ -22,12 +22,12 @@ LENGTHS = [40, 7, 75, 33, 1, 64, 50]
 @pytest.fixture(scope="module")
 def folders(tmp_path_factory):
     base = tmp_path_factory.mktemp("models")
-    return {w: make_folder(base, w) for w in "ABC"}
+    return {w: make_folder(base, w) for w in "ABCD"}
 
 
 @pytest.fixture(scope="module")
 def plains(folders):
-    return {(w, bf): PlainModel(folders[w], matrices_as_bf16=bf) for w in "ABC" for bf in (False, True)}
+    return {(w, bf): PlainModel(folders[w], matrices_as_bf16=bf) for w in "ABCD" for bf in (False, True)}
 
 
 def _requests(vocab, lengths=LENGTHS):
@@ -39,7 +39,7 @@ def _traces(reqs):
             "portions": replay.trace_portions(reqs), "mixed": replay.trace_mixed(reqs, seed=3)}
 
 
-@pytest.mark.parametrize("which", ["A", "B", "C"])
+@pytest.mark.parametrize("which", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
 def test_replay_in_process(folders, plains, which, dtype, mode):

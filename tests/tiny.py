@@ -20,8 +20,14 @@ TINY_C = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_si
               num_attention_heads=5, num_key_value_heads=1, head_dim=48, intermediate_size=176,
               vocab_size=331, rope_theta=50000.0, rms_norm_eps=3e-6, max_position_embeddings=512,
               tie_word_embeddings=False)
-PAGE_TOKENS = {"A": 4, "B": 8, "C": 16}
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# Head size 64 (the smallest that the tensor-memory prompt attention and the fused decode
+# preparation take), three query heads per KV head (does not divide a block's 128 rows).
+TINY_D = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_size=192,
+              num_attention_heads=6, num_key_value_heads=2, head_dim=64, intermediate_size=320,
+              vocab_size=500, rope_theta=200000.0, rms_norm_eps=2e-6, max_position_embeddings=256,
+              tie_word_embeddings=True)
+PAGE_TOKENS = {"A": 4, "B": 8, "C": 16, "D": 16}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
 
 
 def tiny_config(which):
