@@ -1,7 +1,11 @@
 """Paged cache bookkeeping: pools of pages, block tables, fixed-size state slots.
 
 This module decides *which page holds which tokens of which request*; it owns
-no device memory (the engine allocates the pools this module describes).
+no device memory (the engine allocates the pools this module describes).  The
+bookkeeping itself is C++ (``csrc/host_runtime.cpp``, built into
+``libleone_host.so`` on first use); the classes here are its Python front:
+they map request names to the 64-bit ids the library uses, turn its return
+codes into exceptions and give read-only views of its state.
 
 The reference keeps keys and values in growing segments per session and uses
 pages only as the unit of admission (crates/leone/src/kv.rs:14-31, 637-674;
@@ -22,6 +26,9 @@ lives in numbered slots, one per live request.
 """
 from __future__ import annotations
 
+import ctypes
+from collections.abc import Mapping
+from ctypes import byref, c_int, c_longlong, c_void_p
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
 
@@ -36,42 +43,99 @@ class CacheError(RuntimeError):
     """A call that breaks the manager's rules (unknown request, double free...)."""
 
 
-class PagePool:
+_LIB = None
+
+
+def host_library():
+    """The C++ host runtime, compiled on first use."""
+    global _LIB
+    if _LIB is None:
+        from ..csrc.build import ensure_built
+        lib = ctypes.CDLL(ensure_built("host"))
+        lib.leone_host_last_error.restype = ctypes.c_char_p
+        lib.leone_freelist_create.restype = c_void_p
+        lib.leone_cache_create.restype = c_void_p
+        lib.leone_cache_first_live_block.restype = c_longlong
+        lib.leone_pack_step_size.restype = c_longlong
+        _LIB = lib
+    return _LIB
+
+
+def _check(code: int) -> None:
+    if code == 0:
+        return
+    message = host_library().leone_host_last_error().decode()
+    if code == 1:
+        raise OutOfPages(message)
+    raise CacheError(message)
+
+
+def _ll(values) -> ctypes.Array:
+    values = list(values)
+    return (c_longlong * max(len(values), 1))(*values)
+
+
+class _FreeList:
+    def __init__(self, count: int):
+        self._lib = host_library()
+        self._h = c_void_p(self._lib.leone_freelist_create(int(count)))
+        self._n = int(count)
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._lib.leone_freelist_destroy(self._h)
+            self._h = None
+
+    @property
+    def num_free(self) -> int:
+        return int(self._lib.leone_freelist_num_free(self._h))
+
+    def _take(self, count: int) -> List[int]:
+        out = (c_int * max(count, 1))()
+        _check(self._lib.leone_freelist_take(self._h, int(count), out))
+        return list(out[:count])
+
+    def _give_back(self, ids: Sequence[int]) -> None:
+        ids = [int(i) for i in ids]
+        _check(self._lib.leone_freelist_give_back(self._h, (c_int * max(len(ids), 1))(*ids), len(ids)))
+
+
+class PagePool(_FreeList):
     """Free list over page ids ``0..num_pages-1``; LIFO so freed pages are reused at once."""
 
     def __init__(self, num_pages: int):
         if num_pages <= 0:
             raise ValueError("a pool needs at least one page")
+        super().__init__(num_pages)
         self.num_pages = num_pages
-        self._free: List[int] = list(range(num_pages - 1, -1, -1))
-        self._held = [False] * num_pages
-        self.high_water = 0
-
-    @property
-    def num_free(self) -> int:
-        return len(self._free)
 
     @property
     def num_held(self) -> int:
-        return self.num_pages - len(self._free)
+        return self.num_pages - self.num_free
+
+    @property
+    def high_water(self) -> int:
+        return int(self._lib.leone_freelist_high_water(self._h))
 
     def take(self, count: int) -> List[int]:
-        if count > len(self._free):
-            raise OutOfPages(f"asked for {count} pages, {len(self._free)} free of {self.num_pages}")
-        pages = [self._free.pop() for _ in range(count)]
-        for p in pages:
-            if self._held[p]:
-                raise CacheError(f"page {p} handed out twice")
-            self._held[p] = True
-        self.high_water = max(self.high_water, self.num_held)
-        return pages
+        return self._take(count)
 
     def give_back(self, pages: Sequence[int]) -> None:
-        for p in pages:
-            if not 0 <= p < self.num_pages or not self._held[p]:
-                raise CacheError(f"page {p} freed but not held")
-            self._held[p] = False
-            self._free.append(p)
+        self._give_back(pages)
+
+
+class StateSlots(_FreeList):
+    """Numbered fixed-size slots, one per live request."""
+
+    def __init__(self, num_slots: int):
+        super().__init__(num_slots)
+        self.num_slots = num_slots
+
+    def take(self) -> int:
+        return self._take(1)[0]
+
+    def give_back(self, slot: int) -> None:
+        self._give_back([slot])
 
 
 @dataclass
@@ -87,74 +151,112 @@ class GroupSpec:
         return (self.kind, self.num_kv_heads, self.head_dim, self.window)
 
 
+@dataclass(frozen=True)
+class RequestCache:
+    """A request's bookkeeping, as it was when it was asked for."""
+    slot: int
+    committed_len: int
+    reserved_len: int
+    fresh: bool                 # no step has been committed yet: state slot must be cleared
+    version: int                # changes whenever a block table changes other than by growing at its end
+
+
+class _PoolView:
+    """The pool of one group, read-only."""
+
+    def __init__(self, manager, gid):
+        self._m, self._gid = manager, gid
+
+    def _get(self, what):
+        return int(self._m._lib.leone_cache_pool(self._m._h, self._gid, what))
+
+    num_pages = property(lambda self: self._get(0))
+    num_free = property(lambda self: self._get(1))
+    num_held = property(lambda self: self._get(2))
+    high_water = property(lambda self: self._get(3))
+
+
+class _TablesView:
+    """``tables[rid]``: the request's page per logical block (a copy); -1 where a window has passed."""
+
+    def __init__(self, manager, gid):
+        self._m, self._gid = manager, gid
+
+    def __contains__(self, rid) -> bool:
+        return rid in self._m._ids
+
+    def __getitem__(self, rid) -> List[int]:
+        m = self._m
+        n = int(m._lib.leone_cache_table_len(m._h, self._gid, c_longlong(m._id(rid))))
+        out = (c_int * max(n, 1))()
+        _check(m._lib.leone_cache_table_copy(m._h, self._gid, c_longlong(m._id(rid)), 0, n, out))
+        return list(out[:n])
+
+    def tail(self, rid, start: int) -> List[int]:
+        """Entries from ``start`` on (what a mirror of the table appends)."""
+        m = self._m
+        n = int(m._lib.leone_cache_table_len(m._h, self._gid, c_longlong(m._id(rid))))
+        if start >= n:
+            return []
+        out = (c_int * (n - start))()
+        _check(m._lib.leone_cache_table_copy(m._h, self._gid, c_longlong(m._id(rid)), start, n - start, out))
+        return list(out)
+
+    def length(self, rid) -> int:
+        m = self._m
+        return int(m._lib.leone_cache_table_len(m._h, self._gid, c_longlong(m._id(rid))))
+
+
 class CacheGroup:
-    def __init__(self, gid: int, spec: GroupSpec, page_tokens: int, num_pages: int):
-        if spec.kind not in ("full", "window"):
-            raise ValueError(f"unknown cache group kind '{spec.kind}'")
-        if spec.kind == "window" and (spec.window is None or spec.window <= 0):
-            raise ValueError("a window group needs a positive window")
+    def __init__(self, manager, gid: int, spec: GroupSpec, page_tokens: int):
         self.gid = gid
         self.spec = spec
         self.page_tokens = page_tokens
-        self.pool = PagePool(num_pages)
-        # request -> list of page ids by logical block; -1 where a window has passed.
-        self.tables: Dict[Hashable, List[int]] = {}
+        self.pool = _PoolView(manager, gid)
+        self.tables = _TablesView(manager, gid)
+        self._m = manager
 
     def blocks_for(self, length: int) -> int:
         return -(-length // self.page_tokens)
 
     def first_live_block(self, committed_len: int) -> int:
         """First logical block that a query at position >= committed_len can still read."""
-        if self.spec.kind != "window":
-            return 0
-        oldest_key = committed_len - self.spec.window + 1
-        return max(0, oldest_key // self.page_tokens)
+        return int(self._m._lib.leone_cache_first_live_block(self._m._h, self.gid, c_longlong(committed_len)))
 
     def pages_needed(self, table: List[int], new_len: int) -> int:
         return max(0, self.blocks_for(new_len) - len(table))
 
     def pages_for_request(self, total_len: int) -> int:
-        """Upper bound of pages a request of ``total_len`` tokens holds at one time."""
-        if self.spec.kind == "full":
-            return self.blocks_for(total_len)
-        # A window request holds the window's blocks plus the blocks of one step's portion;
-        # the caller adds the portion.  Without that knowledge the bound is the full length.
+        """Upper bound of pages a request of ``total_len`` tokens holds at one time (for a window
+        group the window's blocks plus one step's portion would do; without knowing the portion
+        the bound is the full length)."""
         return self.blocks_for(total_len)
 
 
-class StateSlots:
-    """Numbered fixed-size slots, one per live request."""
+class _SlotsView:
+    def __init__(self, manager):
+        self._m = manager
 
-    def __init__(self, num_slots: int):
-        self.num_slots = num_slots
-        self._free = list(range(num_slots - 1, -1, -1))
-        self._held = [False] * num_slots
-
-    @property
-    def num_free(self) -> int:
-        return len(self._free)
-
-    def take(self) -> int:
-        if not self._free:
-            raise OutOfPages(f"all {self.num_slots} state slots are in use")
-        s = self._free.pop()
-        self._held[s] = True
-        return s
-
-    def give_back(self, slot: int) -> None:
-        if not 0 <= slot < self.num_slots or not self._held[slot]:
-            raise CacheError(f"state slot {slot} freed but not held")
-        self._held[slot] = False
-        self._free.append(slot)
+    num_slots = property(lambda self: int(self._m._lib.leone_cache_slots(self._m._h, 0)))
+    num_free = property(lambda self: int(self._m._lib.leone_cache_slots(self._m._h, 1)))
 
 
-@dataclass
-class RequestCache:
-    slot: int
-    committed_len: int = 0
-    reserved_len: int = 0
-    fresh: bool = True          # no step has been committed yet: state slot must be cleared
-    version: int = 0            # changes whenever a block table changes other than by growing at its end
+class _RequestsView(Mapping):
+    def __init__(self, manager):
+        self._m = manager
+
+    def __getitem__(self, rid) -> RequestCache:
+        if rid not in self._m._ids:
+            raise KeyError(rid)
+        get = self._m._get_field
+        return RequestCache(slot=get(rid, 2), committed_len=get(rid, 0), reserved_len=get(rid, 1),
+                            fresh=bool(get(rid, 3)), version=get(rid, 4))
+
+    def __iter__(self):
+        return iter(list(self._m._ids))
+
+    def __len__(self) -> int:
+        return len(self._m._ids)
 
 
 class CacheManager:
@@ -162,127 +264,106 @@ class CacheManager:
 
     def __init__(self, group_specs: Sequence[GroupSpec], page_tokens: int, num_pages: int,
                  num_slots: int):
+        for spec in group_specs:
+            if spec.kind not in ("full", "window"):
+                raise ValueError(f"unknown cache group kind '{spec.kind}'")
+            if spec.kind == "window" and (spec.window is None or spec.window <= 0):
+                raise ValueError("a window group needs a positive window")
+        if num_pages <= 0:
+            raise ValueError("a pool needs at least one page")
+        self._lib = host_library()
+        n = len(group_specs)
+        kinds = (c_int * max(n, 1))(*[1 if s.kind == "window" else 0 for s in group_specs])
+        windows = _ll([int(s.window or 0) for s in group_specs])
+        handle = self._lib.leone_cache_create(n, kinds, windows, int(page_tokens), int(num_pages), int(num_slots))
+        if not handle:
+            raise ValueError("the cache manager's sizes must be positive")
+        self._h = c_void_p(handle)
         self.page_tokens = page_tokens
-        self.groups = [CacheGroup(i, s, page_tokens, num_pages) for i, s in enumerate(group_specs)]
-        self.slots = StateSlots(num_slots)
-        self.requests: Dict[Hashable, RequestCache] = {}
-        self._versions = 0
+        self._ids: Dict[Hashable, int] = {}
+        self._next_id = 1
+        self.groups = [CacheGroup(self, i, s, page_tokens) for i, s in enumerate(group_specs)]
+        self.slots = _SlotsView(self)
+        self.requests = _RequestsView(self)
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._lib.leone_cache_destroy(self._h)
+            self._h = None
+
+    def _id(self, rid: Hashable) -> int:
+        if rid not in self._ids:
+            raise CacheError(f"request {rid!r} is not open")
+        return self._ids[rid]
+
+    def _get_field(self, rid: Hashable, what: int) -> int:
+        value = c_longlong(0)
+        _check(self._lib.leone_cache_get(self._h, c_longlong(self._id(rid)), what, byref(value)))
+        return int(value.value)
 
     # -- lifetime -------------------------------------------------------------------
     def open(self, rid: Hashable) -> int:
-        if rid in self.requests:
+        if rid in self._ids:
             raise CacheError(f"request {rid!r} is already open")
-        slot = self.slots.take()
-        self._versions += 1
-        self.requests[rid] = RequestCache(slot=slot, version=self._versions)
-        for g in self.groups:
-            g.tables[rid] = []
-        return slot
+        slot = c_int(-1)
+        _check(self._lib.leone_cache_open(self._h, c_longlong(self._next_id), byref(slot)))
+        self._ids[rid] = self._next_id
+        self._next_id += 1
+        return int(slot.value)
 
     def close(self, rid: Hashable) -> None:
-        rc = self._get(rid)
-        for g in self.groups:
-            table = g.tables.pop(rid)
-            g.pool.give_back([p for p in table if p >= 0])
-        self.slots.give_back(rc.slot)
-        del self.requests[rid]
+        _check(self._lib.leone_cache_close(self._h, c_longlong(self._id(rid))))
+        del self._ids[rid]
 
     def is_open(self, rid: Hashable) -> bool:
-        return rid in self.requests
-
-    def _get(self, rid: Hashable) -> RequestCache:
-        if rid not in self.requests:
-            raise CacheError(f"request {rid!r} is not open")
-        return self.requests[rid]
+        return rid in self._ids
 
     def length(self, rid: Hashable) -> int:
-        return self._get(rid).committed_len
+        return self._get_field(rid, 0)
 
     def slot(self, rid: Hashable) -> int:
-        return self._get(rid).slot
+        return self._get_field(rid, 2)
 
     def table_version(self, rid: Hashable) -> int:
         """A number that changes whenever one of the request's block tables changes other than
         by growing at its end (a mirror of the tables may then append instead of rewriting)."""
-        return self._get(rid).version
+        return self._get_field(rid, 4)
 
     # -- the step transaction -------------------------------------------------------
+    def _pairs(self, wants: Dict[Hashable, int]):
+        rids = [self._id(r) for r in wants]
+        return len(rids), _ll(rids), _ll(int(v) for v in wants.values())
+
     def can_reserve(self, wants: Dict[Hashable, int]) -> bool:
         """Would ``reserve`` succeed for these (request → new length) pairs together?"""
-        for g in self.groups:
-            need = sum(g.pages_needed(g.tables[rid], new_len) for rid, new_len in wants.items())
-            if need > g.pool.num_free:
-                return False
-        return True
+        return bool(self._lib.leone_cache_can_reserve(self._h, *self._pairs(wants)))
 
     def reserve(self, wants: Dict[Hashable, int]) -> None:
         """Take pages so each request can hold ``new_len`` tokens.  All or nothing."""
-        for rid, new_len in wants.items():
-            rc = self._get(rid)
-            if new_len < rc.committed_len:
-                raise CacheError(f"request {rid!r}: cannot reserve {new_len} below its length")
-        if not self.can_reserve(wants):
-            raise OutOfPages("not enough free pages for this step")
-        for rid, new_len in wants.items():
-            rc = self.requests[rid]
-            for g in self.groups:
-                table = g.tables[rid]
-                table.extend(g.pool.take(g.pages_needed(table, new_len)))
-            rc.reserved_len = max(rc.reserved_len, new_len)
+        _check(self._lib.leone_cache_reserve(self._h, *self._pairs(wants)))
 
     def commit(self, rid: Hashable, new_len: int) -> None:
         """The step that wrote tokens up to ``new_len`` succeeded."""
-        rc = self._get(rid)
-        if new_len > rc.reserved_len or new_len < rc.committed_len:
-            raise CacheError(f"request {rid!r}: commit to {new_len} outside what was reserved")
-        rc.committed_len = new_len
-        rc.fresh = False
-        for g in self.groups:
-            if g.spec.kind != "window":
-                continue
-            table = g.tables[rid]
-            live_from = min(g.first_live_block(new_len), len(table))
-            passed = [p for p in table[:live_from] if p >= 0]
-            if passed:
-                g.pool.give_back(passed)
-                for b in range(live_from):
-                    table[b] = -1
-                self._versions += 1
-                rc.version = self._versions
+        _check(self._lib.leone_cache_commit(self._h, c_longlong(self._id(rid)), c_longlong(new_len)))
 
     def rollback(self, rid: Hashable) -> None:
         """The step failed: return pages beyond the committed length."""
-        self.truncate(rid, self._get(rid).committed_len)
+        _check(self._lib.leone_cache_truncate(self._h, c_longlong(self._id(rid)), c_longlong(-1)))
 
     def truncate(self, rid: Hashable, length: int) -> None:
         """Drop everything past ``length`` tokens (crates/leone/src/kv.rs:929-950)."""
-        rc = self._get(rid)
-        if length > rc.committed_len:
-            raise CacheError(f"request {rid!r}: cannot truncate to {length} past its length")
-        for g in self.groups:
-            table = g.tables[rid]
-            keep = g.blocks_for(length)
-            extra = [p for p in table[keep:] if p >= 0]
-            g.pool.give_back(extra)
-            if len(table) > keep:
-                self._versions += 1
-                rc.version = self._versions
-            del table[keep:]
-        rc.committed_len = length
-        rc.reserved_len = length
+        if length < 0:
+            raise CacheError(f"request {rid!r}: cannot truncate to a negative length")
+        _check(self._lib.leone_cache_truncate(self._h, c_longlong(self._id(rid)), c_longlong(length)))
 
     # -- views for the step function --------------------------------------------------
     def block_table(self, gid: int, rids: Sequence[Hashable], width: Optional[int] = None) -> np.ndarray:
-        g = self.groups[gid]
-        tables = [g.tables[r] for r in rids]
-        w = max([len(t) for t in tables] + [1])
-        if width is not None:
-            if width < w:
-                raise CacheError(f"block table needs {w} columns, only {width} given")
-            w = width
-        out = np.full((len(rids), w), -1, dtype=np.int32)
-        for i, t in enumerate(tables):
-            out[i, :len(t)] = t
+        ids = [self._id(r) for r in rids]
+        if width is None:
+            width = max([int(self._lib.leone_cache_table_len(self._h, gid, c_longlong(i))) for i in ids] + [1])
+        out = np.empty((len(ids), width), dtype=np.int32)
+        _check(self._lib.leone_cache_block_table(self._h, gid, len(ids), _ll(ids), int(width),
+                                                 out.ctypes.data_as(ctypes.POINTER(c_int))))
         return out
 
     # -- accounting -------------------------------------------------------------------
@@ -294,25 +375,4 @@ class CacheManager:
 
     def check_invariants(self) -> None:
         """Every page is either free or in exactly one table; counts add up."""
-        for g in self.groups:
-            seen = {}
-            for rid, table in g.tables.items():
-                for p in table:
-                    if p < 0:
-                        continue
-                    if p in seen:
-                        raise CacheError(f"group {g.gid}: page {p} held by {seen[p]!r} and {rid!r}")
-                    seen[p] = rid
-            free = set(g.pool._free)
-            if len(free) != len(g.pool._free):
-                raise CacheError(f"group {g.gid}: a page is on the free list twice")
-            if free & set(seen):
-                raise CacheError(f"group {g.gid}: a held page is on the free list")
-            if len(free) + len(seen) != g.pool.num_pages:
-                raise CacheError(
-                    f"group {g.gid}: {g.pool.num_pages - len(free) - len(seen)} pages lost")
-        held_slots = sorted(rc.slot for rc in self.requests.values())
-        if len(set(held_slots)) != len(held_slots):
-            raise CacheError("a state slot is held twice")
-        if len(held_slots) + self.slots.num_free != self.slots.num_slots:
-            raise CacheError("a state slot was lost")
+        _check(self._lib.leone_cache_check_invariants(self._h))

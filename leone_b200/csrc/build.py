@@ -33,7 +33,10 @@ MODULES: Dict[str, List[str]] = {
     "bf16": ["gemm_tc.cu", "attention_tiled.cu", "attention_prefill_tc.cu"],
     # the entry point that allocates nothing (leone_static.h); it compiles attention_tiled.cu in
     "static": ["attention_decode_static.cu"],
+    # the host side of the runtime (pages, block tables, step metadata): plain C++, no device code
+    "host": ["host_runtime.cpp"],
 }
+HOST_ONLY = {"host"}
 HEADERS = ["common.cuh", "tc_common.cuh", "leone_static.h", "attention_tiled.cu"]
 
 # -fno-gnu-unique: statics inside inline functions and templates (the once-per-kernel set-up
@@ -105,7 +108,7 @@ def _run_with_heartbeat(cmd: List[str], what: str) -> None:
     finally:
         done.set()
     if proc.returncode != 0:
-        raise BuildError(f"nvcc failed on {what}:\n{' '.join(cmd)}\n{proc.stdout}")
+        raise BuildError(f"the compiler failed on {what}:\n{' '.join(cmd)}\n{proc.stdout}")
 
 
 def ensure_built(module: str, verbose: bool = True) -> str:
@@ -128,6 +131,8 @@ def ensure_built(module: str, verbose: bool = True) -> str:
     missing = [s for s in MODULES[module] if not os.path.isfile(os.path.join(HERE, s))]
     if missing:
         raise BuildError(f"kernel module '{module}' lacks sources: {missing}")
+    if module in HOST_ONLY:
+        return _build_host(module, lib, stamp, digest, fresh, out_dir, verbose)
     nvcc = find_nvcc()
     lock_path = os.path.join(out_dir, f".{module}.lock")
     with open(lock_path, "w") as lock:
@@ -159,6 +164,41 @@ def ensure_built(module: str, verbose: bool = True) -> str:
                     os.remove(obj)
                 except OSError:
                     pass
+            if verbose:
+                print(f"[leone_b200] module '{module}' built in {time.time() - t0:.0f} s",
+                      file=sys.stderr, flush=True)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+    return lib
+
+
+def find_cxx() -> str:
+    for cand in (os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++"), shutil.which("clang++")):
+        if cand and os.path.isfile(cand) and os.access(cand, os.X_OK):
+            return cand
+    return find_nvcc()        # nvcc compiles plain C++ too
+
+
+def _build_host(module, lib, stamp, digest, fresh, out_dir, verbose) -> str:
+    """A module without device code: one call of the C++ compiler."""
+    cxx = find_cxx()
+    lock_path = os.path.join(out_dir, f".{module}.lock")
+    with open(lock_path, "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if fresh():
+                return lib
+            if verbose:
+                print(f"[leone_b200] compiling C++ module '{module}' into {out_dir}", file=sys.stderr, flush=True)
+            t0 = time.time()
+            tmp_lib = lib + f".tmp{os.getpid()}"
+            srcs = [os.path.join(HERE, s) for s in MODULES[module]]
+            flags = ["-O2", "-std=c++17", "-shared", "-Xcompiler", "-fPIC"] if os.path.basename(cxx).startswith("nvcc") \
+                else ["-O2", "-std=c++17", "-shared", "-fPIC", "-fno-gnu-unique"]
+            _run_with_heartbeat([cxx, *flags, "-I", HERE, *srcs, "-o", tmp_lib], MODULES[module][0])
+            os.replace(tmp_lib, lib)
+            with open(stamp, "w") as fh:
+                fh.write(digest)
             if verbose:
                 print(f"[leone_b200] module '{module}' built in {time.time() - t0:.0f} s",
                       file=sys.stderr, flush=True)

@@ -1,0 +1,431 @@
+// Host side of the engine's runtime in C++: pools of pages, block tables, fixed-size state
+// slots and the step transaction (reserve -> commit / roll back), and the packing of a step's
+// metadata.  No device code; the Python classes in leone_b200/cache/pages.py and
+// leone_b200/engine/batch.py are thin fronts over these functions.
+//
+// The reference keeps keys and values in growing segments per session and uses pages only as
+// the unit of admission (crates/leone/src/kv.rs:14-31, 637-674; crates/leone/src/scheduler.rs:
+// 652-667 rounds a reservation up to kv_page_tokens).  Here the pages are real: a request's
+// tokens live in fixed-size pages scattered over a pool and found through its block table.
+// What is kept from the reference is the transaction: space for a step is reserved before the
+// step runs and a request's length advances only when the step is committed (prepare_append ->
+// write_span -> commit_append, crates/leone/src/kv.rs:326-347, 791-927); a failed step rolls
+// back.
+//
+// Layers with different needs form different groups.  A group has its own pool and its own
+// block table per request.  Two kinds exist: "full" keeps every page until the request ends;
+// "window" gives a page back as soon as every later query lies more than `window` tokens past
+// its last token.  Requests are named by 64-bit ids (the Python front maps its hashable names).
+//
+// Every function returns a code (0 ok, 1 out of pages or slots, 2 a broken rule, -1 a bad
+// handle or argument) and leaves a message for leone_host_last_error().
+#include <algorithm>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <unordered_map>
+#include <unordered_set>
+#include <vector>
+
+namespace {
+
+enum Code { kOk = 0, kOutOfPages = 1, kRuleBroken = 2, kBadArgument = -1 };
+
+thread_local std::string g_error;
+
+int fail(Code code, const std::string& message) {
+  g_error = message;
+  return code;
+}
+
+// Free list over ids 0..n-1; LIFO, so what is given back is handed out again at once.
+struct FreeList {
+  int n = 0;
+  std::vector<int> free_;
+  std::vector<char> held;
+  int high_water = 0;
+
+  explicit FreeList(int count) : n(count), held(count, 0) {
+    free_.reserve(count);
+    for (int i = count - 1; i >= 0; --i) free_.push_back(i);
+  }
+  int num_free() const { return (int)free_.size(); }
+  int num_held() const { return n - (int)free_.size(); }
+  // All or nothing.
+  int take(int count, std::vector<int>* out, const char* what) {
+    if (count > (int)free_.size())
+      return fail(kOutOfPages, std::string("asked for ") + std::to_string(count) + " " + what + ", " +
+                                   std::to_string(free_.size()) + " free of " + std::to_string(n));
+    for (int i = 0; i < count; ++i) {
+      const int id = free_.back();
+      free_.pop_back();
+      if (held[id]) return fail(kRuleBroken, std::string(what) + " " + std::to_string(id) + " handed out twice");
+      held[id] = 1;
+      out->push_back(id);
+    }
+    high_water = std::max(high_water, num_held());
+    return kOk;
+  }
+  int give_back(int id, const char* what) {
+    if (id < 0 || id >= n || !held[id])
+      return fail(kRuleBroken, std::string(what) + " " + std::to_string(id) + " freed but not held");
+    held[id] = 0;
+    free_.push_back(id);
+    return kOk;
+  }
+};
+
+struct Request {
+  int slot = -1;
+  long long committed = 0, reserved = 0;
+  bool fresh = true;        // no step has been committed yet: a state slot must be cleared
+  long long version = 0;    // changes whenever a block table changes other than by growing at its end
+};
+
+struct Group {
+  int kind = 0;             // 0 full, 1 window
+  long long window = 0;
+  int page_tokens = 1;
+  FreeList pool;
+  std::unordered_map<long long, std::vector<int>> tables;   // request -> page per logical block; -1 where a window has passed
+
+  Group(int kind_, long long window_, int page_tokens_, int pages)
+      : kind(kind_), window(window_), page_tokens(page_tokens_), pool(pages) {}
+  long long blocks_for(long long length) const { return (length + page_tokens - 1) / page_tokens; }
+  // First logical block that a query at position >= committed can still read.
+  long long first_live_block(long long committed) const {
+    if (kind != 1) return 0;
+    const long long oldest_key = committed - window + 1;
+    return oldest_key <= 0 ? 0 : oldest_key / page_tokens;
+  }
+  long long pages_needed(const std::vector<int>& table, long long new_len) const {
+    return std::max(0ll, blocks_for(new_len) - (long long)table.size());
+  }
+};
+
+struct Manager {
+  int page_tokens;
+  std::vector<Group> groups;
+  FreeList slots;
+  std::unordered_map<long long, Request> requests;
+  long long versions = 0;
+
+  Manager(int page_tokens_, int num_slots) : page_tokens(page_tokens_), slots(num_slots) {}
+  Request* find(long long rid) {
+    auto it = requests.find(rid);
+    return it == requests.end() ? nullptr : &it->second;
+  }
+};
+
+int unknown(long long rid) { return fail(kRuleBroken, "request " + std::to_string(rid) + " is not open"); }
+
+}  // namespace
+
+extern "C" {
+
+const char* leone_host_last_error() { return g_error.c_str(); }
+
+// ---- a free list on its own (pages of one pool, or state slots) ---------------------------
+void* leone_freelist_create(int count) { return count > 0 ? new FreeList(count) : nullptr; }
+void leone_freelist_destroy(void* h) { delete static_cast<FreeList*>(h); }
+int leone_freelist_num_free(void* h) { return static_cast<FreeList*>(h)->num_free(); }
+int leone_freelist_high_water(void* h) { return static_cast<FreeList*>(h)->high_water; }
+int leone_freelist_take(void* h, int count, int* out) {
+  std::vector<int> got;
+  const int r = static_cast<FreeList*>(h)->take(count, &got, "pages");
+  if (r == kOk) std::copy(got.begin(), got.end(), out);
+  return r;
+}
+int leone_freelist_give_back(void* h, const int* ids, int count) {
+  for (int i = 0; i < count; ++i) {
+    const int r = static_cast<FreeList*>(h)->give_back(ids[i], "page");
+    if (r != kOk) return r;
+  }
+  return kOk;
+}
+
+// ---- the cache manager --------------------------------------------------------------------
+void* leone_cache_create(int n_groups, const int* kinds, const long long* windows, int page_tokens,
+                         int num_pages, int num_slots) {
+  if (n_groups < 0 || page_tokens <= 0 || num_pages <= 0 || num_slots <= 0) return nullptr;
+  for (int i = 0; i < n_groups; ++i)
+    if ((kinds[i] != 0 && kinds[i] != 1) || (kinds[i] == 1 && windows[i] <= 0)) return nullptr;
+  Manager* m = new Manager(page_tokens, num_slots);
+  for (int i = 0; i < n_groups; ++i) m->groups.emplace_back(kinds[i], windows[i], page_tokens, num_pages);
+  return m;
+}
+void leone_cache_destroy(void* h) { delete static_cast<Manager*>(h); }
+
+int leone_cache_open(void* h, long long rid, int* slot) {
+  Manager* m = static_cast<Manager*>(h);
+  if (m->find(rid)) return fail(kRuleBroken, "request " + std::to_string(rid) + " is already open");
+  std::vector<int> got;
+  const int r = m->slots.take(1, &got, "state slots");
+  if (r != kOk) return r;
+  Request rc;
+  rc.slot = got[0];
+  rc.version = ++m->versions;
+  m->requests[rid] = rc;
+  for (Group& g : m->groups) g.tables[rid] = {};
+  *slot = rc.slot;
+  return kOk;
+}
+
+int leone_cache_close(void* h, long long rid) {
+  Manager* m = static_cast<Manager*>(h);
+  Request* rc = m->find(rid);
+  if (!rc) return unknown(rid);
+  for (Group& g : m->groups) {
+    auto it = g.tables.find(rid);
+    for (int p : it->second)
+      if (p >= 0) {
+        const int r = g.pool.give_back(p, "page");
+        if (r != kOk) return r;
+      }
+    g.tables.erase(it);
+  }
+  const int r = m->slots.give_back(rc->slot, "state slot");
+  m->requests.erase(rid);
+  return r;
+}
+
+int leone_cache_is_open(void* h, long long rid) { return static_cast<Manager*>(h)->find(rid) ? 1 : 0; }
+int leone_cache_num_open(void* h) { return (int)static_cast<Manager*>(h)->requests.size(); }
+
+// what: 0 committed length, 1 reserved length, 2 slot, 3 fresh, 4 table version
+int leone_cache_get(void* h, long long rid, int what, long long* value) {
+  Request* rc = static_cast<Manager*>(h)->find(rid);
+  if (!rc) return unknown(rid);
+  switch (what) {
+    case 0: *value = rc->committed; break;
+    case 1: *value = rc->reserved; break;
+    case 2: *value = rc->slot; break;
+    case 3: *value = rc->fresh ? 1 : 0; break;
+    case 4: *value = rc->version; break;
+    default: return fail(kBadArgument, "unknown field");
+  }
+  return kOk;
+}
+
+// Would reserve succeed for these (request, new length) pairs together?  (1 yes, 0 no)
+int leone_cache_can_reserve(void* h, int n, const long long* rids, const long long* new_lens) {
+  Manager* m = static_cast<Manager*>(h);
+  for (Group& g : m->groups) {
+    long long need = 0;
+    for (int i = 0; i < n; ++i) {
+      auto it = g.tables.find(rids[i]);
+      if (it == g.tables.end()) return 0;
+      need += g.pages_needed(it->second, new_lens[i]);
+    }
+    if (need > g.pool.num_free()) return 0;
+  }
+  return 1;
+}
+
+// Take pages so each request can hold new_len tokens.  All or nothing.
+int leone_cache_reserve(void* h, int n, const long long* rids, const long long* new_lens) {
+  Manager* m = static_cast<Manager*>(h);
+  for (int i = 0; i < n; ++i) {
+    Request* rc = m->find(rids[i]);
+    if (!rc) return unknown(rids[i]);
+    if (new_lens[i] < rc->committed)
+      return fail(kRuleBroken, "request " + std::to_string(rids[i]) + ": cannot reserve " +
+                                   std::to_string(new_lens[i]) + " below its length");
+  }
+  if (!leone_cache_can_reserve(h, n, rids, new_lens)) return fail(kOutOfPages, "not enough free pages for this step");
+  for (int i = 0; i < n; ++i) {
+    Request* rc = m->find(rids[i]);
+    for (Group& g : m->groups) {
+      std::vector<int>& table = g.tables[rids[i]];
+      const int r = g.pool.take((int)g.pages_needed(table, new_lens[i]), &table, "pages");
+      if (r != kOk) return r;
+    }
+    rc->reserved = std::max(rc->reserved, new_lens[i]);
+  }
+  return kOk;
+}
+
+// The step that wrote tokens up to new_len succeeded.
+int leone_cache_commit(void* h, long long rid, long long new_len) {
+  Manager* m = static_cast<Manager*>(h);
+  Request* rc = m->find(rid);
+  if (!rc) return unknown(rid);
+  if (new_len > rc->reserved || new_len < rc->committed)
+    return fail(kRuleBroken, "request " + std::to_string(rid) + ": commit to " + std::to_string(new_len) +
+                                 " outside what was reserved");
+  rc->committed = new_len;
+  rc->fresh = false;
+  for (Group& g : m->groups) {
+    if (g.kind != 1) continue;
+    std::vector<int>& table = g.tables[rid];
+    const long long live_from = std::min(g.first_live_block(new_len), (long long)table.size());
+    bool any = false;
+    for (long long b = 0; b < live_from; ++b)
+      if (table[b] >= 0) {
+        const int r = g.pool.give_back(table[b], "page");
+        if (r != kOk) return r;
+        table[b] = -1;
+        any = true;
+      }
+    if (any) rc->version = ++m->versions;
+  }
+  return kOk;
+}
+
+// Drop everything past `length` tokens (crates/leone/src/kv.rs:929-950); length < 0: roll
+// back to the committed length (the step failed).
+int leone_cache_truncate(void* h, long long rid, long long length) {
+  Manager* m = static_cast<Manager*>(h);
+  Request* rc = m->find(rid);
+  if (!rc) return unknown(rid);
+  if (length < 0) length = rc->committed;
+  if (length > rc->committed)
+    return fail(kRuleBroken, "request " + std::to_string(rid) + ": cannot truncate to " + std::to_string(length) +
+                                 " past its length");
+  for (Group& g : m->groups) {
+    std::vector<int>& table = g.tables[rid];
+    const size_t keep = (size_t)g.blocks_for(length);
+    if (table.size() > keep) {
+      for (size_t b = keep; b < table.size(); ++b)
+        if (table[b] >= 0) {
+          const int r = g.pool.give_back(table[b], "page");
+          if (r != kOk) return r;
+        }
+      table.resize(keep);
+      rc->version = ++m->versions;
+    }
+  }
+  rc->committed = length;
+  rc->reserved = length;
+  return kOk;
+}
+
+// ---- views for the step function -------------------------------------------------------------
+int leone_cache_table_len(void* h, int gid, long long rid) {
+  Manager* m = static_cast<Manager*>(h);
+  if (gid < 0 || gid >= (int)m->groups.size()) return fail(kBadArgument, "no such group");
+  auto it = m->groups[gid].tables.find(rid);
+  return it == m->groups[gid].tables.end() ? -1 : (int)it->second.size();
+}
+// Entries [from, from + count) of a request's block table.
+int leone_cache_table_copy(void* h, int gid, long long rid, int from, int count, int* out) {
+  Manager* m = static_cast<Manager*>(h);
+  if (gid < 0 || gid >= (int)m->groups.size()) return fail(kBadArgument, "no such group");
+  auto it = m->groups[gid].tables.find(rid);
+  if (it == m->groups[gid].tables.end()) return unknown(rid);
+  if (from < 0 || count < 0 || (size_t)(from + count) > it->second.size()) return fail(kBadArgument, "table range");
+  std::copy(it->second.begin() + from, it->second.begin() + from + count, out);
+  return kOk;
+}
+// The block tables of n requests as rows of `width` entries, -1 where there is no page.
+int leone_cache_block_table(void* h, int gid, int n, const long long* rids, int width, int* out) {
+  Manager* m = static_cast<Manager*>(h);
+  if (gid < 0 || gid >= (int)m->groups.size()) return fail(kBadArgument, "no such group");
+  Group& g = m->groups[gid];
+  for (int i = 0; i < n; ++i) {
+    auto it = g.tables.find(rids[i]);
+    if (it == g.tables.end()) return unknown(rids[i]);
+    if ((int)it->second.size() > width)
+      return fail(kRuleBroken, "block table needs " + std::to_string(it->second.size()) + " columns, only " +
+                                   std::to_string(width) + " given");
+    int* row = out + (size_t)i * width;
+    std::copy(it->second.begin(), it->second.end(), row);
+    std::fill(row + it->second.size(), row + width, -1);
+  }
+  return kOk;
+}
+
+// ---- accounting ------------------------------------------------------------------------------
+// what: 0 pages in the pool, 1 free, 2 held, 3 most ever held
+int leone_cache_pool(void* h, int gid, int what) {
+  Manager* m = static_cast<Manager*>(h);
+  if (gid < 0 || gid >= (int)m->groups.size()) return fail(kBadArgument, "no such group");
+  const FreeList& p = m->groups[gid].pool;
+  return what == 0 ? p.n : what == 1 ? p.num_free() : what == 2 ? p.num_held() : p.high_water;
+}
+int leone_cache_slots(void* h, int what) {
+  const FreeList& s = static_cast<Manager*>(h)->slots;
+  return what == 0 ? s.n : s.num_free();
+}
+long long leone_cache_first_live_block(void* h, int gid, long long committed) {
+  return static_cast<Manager*>(h)->groups[gid].first_live_block(committed);
+}
+
+// Every page is either free or in exactly one table; counts add up.
+int leone_cache_check_invariants(void* h) {
+  Manager* m = static_cast<Manager*>(h);
+  for (size_t gi = 0; gi < m->groups.size(); ++gi) {
+    Group& g = m->groups[gi];
+    std::unordered_map<int, long long> seen;
+    for (auto& kv : g.tables)
+      for (int p : kv.second) {
+        if (p < 0) continue;
+        auto ins = seen.emplace(p, kv.first);
+        if (!ins.second)
+          return fail(kRuleBroken, "group " + std::to_string(gi) + ": page " + std::to_string(p) + " held by " +
+                                       std::to_string(ins.first->second) + " and " + std::to_string(kv.first));
+      }
+    std::unordered_set<int> free_set(g.pool.free_.begin(), g.pool.free_.end());
+    if (free_set.size() != g.pool.free_.size())
+      return fail(kRuleBroken, "group " + std::to_string(gi) + ": a page is on the free list twice");
+    for (auto& kv : seen)
+      if (free_set.count(kv.first))
+        return fail(kRuleBroken, "group " + std::to_string(gi) + ": a held page is on the free list");
+    if ((int)(free_set.size() + seen.size()) != g.pool.n)
+      return fail(kRuleBroken, "group " + std::to_string(gi) + ": " +
+                                   std::to_string(g.pool.n - (int)free_set.size() - (int)seen.size()) + " pages lost");
+  }
+  std::unordered_set<int> held;
+  for (auto& kv : m->requests)
+    if (!held.insert(kv.second.slot).second) return fail(kRuleBroken, "a state slot is held twice");
+  if ((int)held.size() + m->slots.num_free() != m->slots.n) return fail(kRuleBroken, "a state slot was lost");
+  return kOk;
+}
+
+// ---- a step's metadata -------------------------------------------------------------------------
+// Lays a step out as one int32 array: token_ids[N] positions[N] seq_of_token[N] q_start[B+1]
+// ctx_len[B] slot_ids[B] logit_rows[M], then the groups' block tables.  Sequence i brings
+// counts[i] tokens (taken in order from `tokens`) starting at position starts[i] and wants the
+// logits at the places wants[want_start[i] .. want_start[i+1]) among them.  `out` must hold
+// leone_pack_step_size words.  Returns 0, or 2 with a message if a wanted place is outside
+// its sequence's tokens.  (positions: crates/leone/src/cpu.rs:1759-1765, prefill position =
+// start + t.)
+long long leone_pack_step_size(int b, long long n_tokens, long long n_wanted, long long table_words) {
+  return 3 * n_tokens + (b + 1) + 2 * (long long)b + n_wanted + table_words;
+}
+int leone_pack_step(int b, const long long* counts, const long long* tokens, const long long* starts,
+                    const long long* slots, const long long* want_start, const long long* wants, int* out) {
+  long long n = 0;
+  for (int i = 0; i < b; ++i) n += counts[i];
+  const long long m = want_start[b];
+  int* token_ids = out;
+  int* positions = out + n;
+  int* seq_of_token = out + 2 * n;
+  int* q_start = out + 3 * n;
+  int* ctx_len = q_start + (b + 1);
+  int* slot_ids = ctx_len + b;
+  int* logit_rows = slot_ids + b;
+  long long at = 0;
+  for (int i = 0; i < b; ++i) {
+    q_start[i] = (int)at;
+    for (long long t = 0; t < counts[i]; ++t, ++at) {
+      token_ids[at] = (int)tokens[at];
+      positions[at] = (int)(starts[i] + t);
+      seq_of_token[at] = i;
+    }
+    ctx_len[i] = (int)(starts[i] + counts[i]);
+    slot_ids[i] = (int)slots[i];
+    for (long long w = want_start[i]; w < want_start[i + 1]; ++w) {
+      if (wants[w] < 0 || wants[w] >= counts[i])
+        return fail(kRuleBroken, "entry " + std::to_string(i) + ": wanted place " + std::to_string(wants[w]) +
+                                     " is outside its " + std::to_string(counts[i]) + " tokens");
+      logit_rows[w] = q_start[i] + (int)wants[w];
+    }
+  }
+  q_start[b] = (int)at;
+  (void)m;
+  return kOk;
+}
+
+}  // extern "C"

@@ -15,6 +15,7 @@ crates/leone/src/cpu.rs:2372).
 """
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional, Sequence
 
@@ -59,41 +60,46 @@ class StepContext:
 
 def pack_metadata(token_lists: Sequence[Sequence[int]], starts: Sequence[int], slots: Sequence[int],
                   wants: Sequence[Sequence[int]], block_tables: Sequence[np.ndarray]):
-    """Host side of the layout above.  Returns (packed int32 array, offsets dict, host stats)."""
+    """Host side of the layout above, laid out by the C++ host runtime (``leone_pack_step``).
+    Returns (packed int32 array, offsets dict, block-table offsets, host stats)."""
+    from ..cache.pages import host_library
+    lib = host_library()
     b = len(token_lists)
     q_lens = np.array([len(t) for t in token_lists], dtype=np.int64)
     n = int(q_lens.sum())
-    q_start = np.zeros(b + 1, dtype=np.int64)
-    np.cumsum(q_lens, out=q_start[1:])
-    starts = np.asarray(starts, dtype=np.int64)
-    token_ids = np.concatenate([np.asarray(t, dtype=np.int64) for t in token_lists]) if n else np.zeros(0, np.int64)
-    seq_of_token = np.repeat(np.arange(b, dtype=np.int64), q_lens)
-    positions = np.arange(n, dtype=np.int64) - q_start[seq_of_token] + starts[seq_of_token]
-    ctx_len = starts + q_lens
-    rows: List[int] = []
-    for i, w in enumerate(wants):
-        for j in w:
-            if not 0 <= j < q_lens[i]:
-                raise ValueError(f"entry {i}: wanted place {j} is outside its {q_lens[i]} tokens")
-            rows.append(int(q_start[i]) + int(j))
-    pieces = [token_ids, positions, seq_of_token, q_start, ctx_len, np.asarray(slots, dtype=np.int64),
-              np.asarray(rows, dtype=np.int64)]
-    names = ["token_ids", "positions", "seq_of_token", "q_start", "ctx_len", "slot_ids", "logit_rows"]
+    starts = np.ascontiguousarray(starts, dtype=np.int64)
+    token_ids = np.concatenate([np.asarray(t, dtype=np.int64) for t in token_lists]) if n else np.zeros(1, np.int64)
+    want_start = np.zeros(b + 1, dtype=np.int64)
+    np.cumsum([len(w) for w in wants], out=want_start[1:])
+    m = int(want_start[b])
+    flat_wants = np.array([j for w in wants for j in w] or [0], dtype=np.int64)
+    slot_ids = np.ascontiguousarray(slots if b else [0], dtype=np.int64)
+    sizes = [("token_ids", n), ("positions", n), ("seq_of_token", n), ("q_start", b + 1), ("ctx_len", b),
+             ("slot_ids", b), ("logit_rows", m)]
     offsets = {}
     cursor = 0
-    for name, piece in zip(names, pieces):
-        offsets[name] = (cursor, piece.size)
-        cursor += piece.size
+    for name, size in sizes:
+        offsets[name] = (cursor, size)
+        cursor += size
     bt_offsets = []
     for bt in block_tables:
         bt_offsets.append((cursor, bt.shape))
         cursor += bt.size
+    assert cursor == lib.leone_pack_step_size(b, ctypes.c_longlong(n), ctypes.c_longlong(m),
+                                              ctypes.c_longlong(sum(bt.size for bt in block_tables)))
     packed = np.empty(max(cursor, 1), dtype=np.int32)
-    for name, piece in zip(names, pieces):
-        o, s = offsets[name]
-        packed[o:o + s] = piece
+
+    def ptr(a):
+        return a.ctypes.data_as(ctypes.POINTER(ctypes.c_longlong))
+
+    code = lib.leone_pack_step(b, ptr(np.ascontiguousarray(q_lens if b else [0], dtype=np.int64)), ptr(token_ids),
+                               ptr(starts if b else np.zeros(1, np.int64)), ptr(slot_ids), ptr(want_start),
+                               ptr(flat_wants), packed.ctypes.data_as(ctypes.POINTER(ctypes.c_int)))
+    if code != 0:
+        raise ValueError(lib.leone_host_last_error().decode())
     for (o, shape), bt in zip(bt_offsets, block_tables):
         packed[o:o + bt.size] = bt.reshape(-1)
-    stats = dict(n=n, b=b, m=len(rows), q_lens=q_lens, starts=starts, ctx_lens=ctx_len,
+    ctx_len = starts + q_lens
+    stats = dict(n=n, b=b, m=m, q_lens=q_lens, starts=starts, ctx_lens=ctx_len,
                  max_q_len=int(q_lens.max()) if b else 0, max_ctx_len=int(ctx_len.max()) if b else 0)
     return packed, offsets, bt_offsets, stats

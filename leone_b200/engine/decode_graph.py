@@ -109,15 +109,15 @@ class DecodeGraph:
             view = host[o:o + shape[0] * shape[1]].reshape(shape)
             windowed = g.spec.kind == "window"
             for i, r in enumerate(rids):
-                table = g.tables[r]
-                if len(table) > w:
-                    raise ValueError(f"block table needs {len(table)} columns, only {w} given")
+                n = g.tables.length(r)
+                if n > w:
+                    raise ValueError(f"block table needs {n} columns, only {w} given")
                 done = 0 if (not same or windowed) else self._filled_pages[gi][i]
                 if done == 0:
                     view[i, :] = -1
-                if len(table) > done:
-                    view[i, done:len(table)] = table[done:]
-                self._filled_pages[gi][i] = len(table)
+                if n > done:
+                    view[i, done:n] = g.tables.tail(r, done)
+                self._filled_pages[gi][i] = n
         self._filled_rids = key
         sh = self.sample_host.numpy()
         self.sample_host[:b].view(torch.float32).numpy()[:b] = np.array([p.temperature for p in params], dtype=np.float32)

@@ -170,3 +170,87 @@ def test_random_orders_never_lose_or_share_a_page(seed):
         m.close(rid)
     assert all(f == 24 for f in m.free_pages())
     m.check_invariants()
+
+
+def _same_error(native_call, plain_call):
+    """Both raise the same kind of error, or neither raises."""
+    from tests.plain import cache_model as plain
+    kinds = []
+    for call, errors in ((native_call, (OutOfPages, CacheError)), (plain_call, (plain.OutOfPages, plain.CacheError))):
+        try:
+            call()
+            kinds.append(None)
+        except errors as exc:
+            kinds.append(type(exc).__name__)
+    assert kinds[0] == kinds[1], kinds
+    return kinds[0]
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_the_native_manager_and_the_plain_model_agree_call_by_call(seed):
+    """The same random calls, rule-breaking ones among them, go to the C++ manager and to the
+    Python model under tests/plain: same errors, same tables, lengths, slots, versions, counts."""
+    from tests.plain import cache_model as plain
+    rng = random.Random(1000 + seed)
+    window = [None, 7, 5, 12][seed % 4]
+    page_tokens = [4, 3, 8, 5][seed % 4]
+    pages, slots = 20 + seed, 4
+
+    def specs(mod):
+        out = [mod.GroupSpec("full", 2, 16, None, [0])]
+        if window:
+            out.append(mod.GroupSpec("window", 2, 16, window, [1]))
+        return out
+
+    a = CacheManager(specs(__import__("leone_b200.cache.pages", fromlist=["x"])), page_tokens, pages, slots)
+    b = plain.CacheManager(specs(plain), page_tokens, pages, slots)
+    live, counter = {}, 0
+    for _ in range(500):
+        action = rng.random()
+        if action < 0.2:
+            rid = f"r{counter}" if rng.random() < 0.9 or not live else rng.choice(sorted(live))
+            counter += 1
+            if _same_error(lambda: a.open(rid), lambda: b.open(rid)) is None:
+                live[rid] = 0
+                assert a.slot(rid) == b.slot(rid)
+        elif action < 0.7 and live:
+            picked = rng.sample(sorted(live), rng.randint(1, len(live)))
+            wants = {r: live[r] + rng.randint(-1 if rng.random() < 0.05 else 1, 11) for r in picked}
+            assert a.can_reserve(wants) == b.can_reserve(wants)
+            if _same_error(lambda: a.reserve(wants), lambda: b.reserve(wants)) is None:
+                if rng.random() < 0.15:
+                    for r in picked:
+                        a.rollback(r)
+                        b.rollback(r)
+                else:
+                    for r, n in wants.items():
+                        n = n - (1 if rng.random() < 0.1 and n > live[r] + 1 else 0)    # fewer than reserved
+                        if _same_error(lambda: a.commit(r, n), lambda: b.commit(r, n)) is None:
+                            live[r] = n
+        elif action < 0.8 and live:
+            rid = rng.choice(sorted(live))
+            to = rng.randint(0, live[rid] + 2)
+            if _same_error(lambda: a.truncate(rid, to), lambda: b.truncate(rid, to)) is None:
+                live[rid] = min(live[rid], to)
+        elif action < 0.95 and live:
+            rid = rng.choice(sorted(live))
+            a.close(rid)
+            b.close(rid)
+            del live[rid]
+        else:
+            _same_error(lambda: a.close("nobody"), lambda: b.close("nobody"))
+        a.check_invariants()
+        b.check_invariants()
+        assert a.free_pages() == b.free_pages()
+        assert a.slots.num_free == b.slots.num_free
+        for rid, n in live.items():
+            assert a.length(rid) == b.length(rid) == n
+            assert a.table_version(rid) == b.table_version(rid)
+            for ga, gb in zip(a.groups, b.groups):
+                assert ga.tables[rid] == gb.tables[rid]
+                assert ga.first_live_block(n) == gb.first_live_block(n)
+        if live:
+            rids = sorted(live)
+            for ga in a.groups:
+                assert (a.block_table(ga.gid, rids) == b.block_table(ga.gid, rids)).all()
+    assert [g.pool.high_water for g in a.groups] == [g.pool.high_water for g in b.groups]

@@ -85,3 +85,38 @@ def test_run_order_may_repeat_a_layer_and_borrow_a_cache(setup, tmp_path):
     plain_order = Engine(replace(spec, run_order=(0, 1, 2)), dict(tensors), dtype="float32", device="cpu",
                          ops=EmulatedOps(), page_tokens=8, num_pages=8, max_requests=2, max_batch_tokens=32)
     assert not torch.allclose(whole, plain_order.step([("x", toks, list(range(21)))]), atol=1e-4)
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_step_metadata_layout_against_a_plain_restatement(seed):
+    """The packed int32 array of a step, field by field, against numpy written out here."""
+    import numpy as np
+    from leone_b200.engine.batch import pack_metadata
+    rng = np.random.default_rng(seed)
+    b = int(rng.integers(1, 5))
+    token_lists = [list(rng.integers(0, 1000, int(rng.integers(1, 9)))) for _ in range(b)]
+    starts = [int(rng.integers(0, 50)) for _ in range(b)]
+    slots = list(rng.permutation(8)[:b])
+    wants = [sorted(set(int(j) for j in rng.integers(0, len(t), int(rng.integers(0, 3))))) for t in token_lists]
+    tables = [rng.integers(-1, 30, (b, 3 + g)).astype(np.int32) for g in range(2)]
+    packed, offsets, bt_offsets, stats = pack_metadata(token_lists, starts, slots, wants, tables)
+
+    def field(name):
+        o, s = offsets[name]
+        return packed[o:o + s].tolist()
+
+    q_start = [0]
+    for t in token_lists:
+        q_start.append(q_start[-1] + len(t))
+    assert field("token_ids") == [x for t in token_lists for x in t]
+    assert field("positions") == [starts[i] + j for i, t in enumerate(token_lists) for j in range(len(t))]
+    assert field("seq_of_token") == [i for i, t in enumerate(token_lists) for _ in t]
+    assert field("q_start") == q_start
+    assert field("ctx_len") == [starts[i] + len(t) for i, t in enumerate(token_lists)]
+    assert field("slot_ids") == [int(s) for s in slots]
+    assert field("logit_rows") == [q_start[i] + j for i, w in enumerate(wants) for j in w]
+    for (o, shape), bt in zip(bt_offsets, tables):
+        assert (packed[o:o + bt.size].reshape(shape) == bt).all()
+    assert stats["n"] == q_start[-1] and stats["m"] == sum(len(w) for w in wants)
+    with pytest.raises(ValueError, match="outside"):
+        pack_metadata(token_lists, starts, slots, [[len(token_lists[0])]] + [[]] * (b - 1), tables)
