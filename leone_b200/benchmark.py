@@ -29,6 +29,14 @@ QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=36, hidden
                 vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6,
                 max_position_embeddings=4096, tie_word_embeddings=False)
 
+QWEN3_1_7B = dict(QWEN3_8B, num_hidden_layers=28, hidden_size=2048, num_attention_heads=16,
+                  intermediate_size=6144, tie_word_embeddings=True)
+QWEN3_32B = dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64,
+                 intermediate_size=25600, max_position_embeddings=16384)
+# name -> (config, decode context, batch sizes measured beside the headline batch)
+SHAPES = {"qwen3-8b": (QWEN3_8B, 2048, (1, 64)), "qwen3-1.7b": (QWEN3_1_7B, 2048, (1, 64)),
+          "qwen3-32b": (QWEN3_32B, 8192, (1, 32))}
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
@@ -183,8 +191,71 @@ def kv_bytes_per_token(cfg: dict, layers: int, itemsize: int = 2) -> int:
     return 2 * layers * cfg["num_key_value_heads"] * cfg["head_dim"] * itemsize
 
 
+def serving(shape: str = "qwen3-1.7b", requests: int = 64, min_prompt: int = 64, max_prompt: int = 2048,
+            new_tokens: int = 128, max_batch_tokens: int = 2048, prefill_chunk: int = 1024,
+            layers: Optional[int] = None, seed: int = 0) -> int:
+    """Continuous batching through the scheduler: ``requests`` requests arrive at once with prompt
+    lengths uniform in [min_prompt, max_prompt]; prompt portions run beside the decode tokens of
+    the requests already past their prompt; each generates ``new_tokens``.  The workload runs
+    twice (the first run builds the decode graphs) and the second is reported: generated tokens
+    per second of wall clock, time to first token per request, and where the steps' time went."""
+    from .config.qwen3 import Qwen3Config
+    from .engine.engine import Engine
+    from .engine.scheduler import Scheduler, SchedulerConfig
+    from .sampling.sampler import SamplingParams
+    cfg = dict(SHAPES[shape][0])
+    full_layers = cfg["num_hidden_layers"]
+    if layers:
+        cfg["num_hidden_layers"] = layers
+    config = Qwen3Config.from_dict(cfg)
+    gen = torch.Generator().manual_seed(seed)
+    lengths = torch.randint(min_prompt, max_prompt + 1, (requests,), generator=gen).tolist()
+    prompts = [torch.randint(0, config.vocab_size, (n,), generator=gen).tolist() for n in lengths]
+    pool_tokens = sum(-(-(n + new_tokens) // 64) * 64 for n in lengths)
+    engine = Engine.from_config(config, seed=0, dtype="bfloat16", page_tokens=16, max_tokens=pool_tokens,
+                                max_requests=requests, max_batch_tokens=max_batch_tokens)
+    report = None
+    for rep in range(2):
+        sched = Scheduler(engine, SchedulerConfig(max_running=requests, max_batch_tokens=max_batch_tokens,
+                                                  prefill_chunk_tokens=prefill_chunk, prefill_first=False))
+        for i, p in enumerate(prompts):
+            sched.add_request(i, p, new_tokens, SamplingParams(0.0, seed + i), -1)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        first: Dict[int, float] = {}
+        kinds = {"mixed": [], "decode": []}
+        while sched.has_work():
+            before_prefill = sched.stats["prefill_tokens"]
+            t = time.perf_counter()
+            outs = sched.step()
+            now = time.perf_counter()
+            kinds["mixed" if sched.stats["prefill_tokens"] > before_prefill else "decode"].append(now - t)
+            for o in outs:
+                first.setdefault(o.rid, now - t0)
+        wall = time.perf_counter() - t0
+        generated = sum(len(sched.requests[i].generated) for i in range(requests))
+        ttft = sorted(first.values())
+        report = {
+            "metric": "generated tokens/s, continuous batching of chunked prefill with decode",
+            "value": generated / wall, "unit": "tokens/s", "wall_s": wall,
+            "prompt_tokens": sum(lengths), "generated_tokens": generated,
+            "all_tokens_per_s": (sum(lengths) + generated) / wall,
+            "ttft_s": {"p50": ttft[len(ttft) // 2], "p90": ttft[int(len(ttft) * 0.9)], "max": ttft[-1]},
+            "steps": {k: {"count": len(v), "total_s": sum(v), "mean_ms": 1e3 * sum(v) / max(len(v), 1)}
+                      for k, v in kinds.items()},
+            "config": {"model": shape, "layers": cfg["num_hidden_layers"], "layers_of_model": full_layers,
+                       "requests": requests, "prompt_lengths": f"uniform {min_prompt}-{max_prompt}",
+                       "new_tokens": new_tokens, "max_batch_tokens": max_batch_tokens,
+                       "prefill_chunk": prefill_chunk, "page_tokens": 16},
+            "dtype": "bf16", "data": "synthetic: uniform random token ids, seeded random weights N(0,0.02)",
+        }
+    print(json.dumps(report))
+    return 0
+
+
 def run(gpus: int, steps: int, warmup: int, impl: str, layers: Optional[int] = None, batch: int = 8,
-        context: int = 2048, prefill_tokens: int = 2048, points: bool = True) -> int:
+        context: Optional[int] = None, prefill_tokens: int = 2048, points: bool = True,
+        shape: str = "qwen3-8b") -> int:
     if impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
                           "the reference is a Rust workspace (maturin bin wheel); no cargo/rustc in this "
@@ -197,7 +268,9 @@ def run(gpus: int, steps: int, warmup: int, impl: str, layers: Optional[int] = N
     from .engine.engine import Engine
     from .engine.generate import generate
 
-    cfg = dict(QWEN3_8B)
+    cfg, shape_context, other_batches = SHAPES[shape]
+    cfg = dict(cfg)
+    context = context or shape_context
     full_layers = cfg["num_hidden_layers"]
     if layers:
         cfg["num_hidden_layers"] = layers
@@ -205,7 +278,7 @@ def run(gpus: int, steps: int, warmup: int, impl: str, layers: Optional[int] = N
     config = Qwen3Config.from_dict(cfg)
     peaks = measured_peaks()
     page_tokens = 16
-    big = 64 if points else batch
+    big = max(other_batches + (batch,)) if points else batch
     pool_tokens = big * (context + steps + warmup + 64)
     t_build = time.time()
     engine = Engine.from_config(config, seed=0, dtype="bfloat16", page_tokens=page_tokens,
@@ -233,7 +306,7 @@ def run(gpus: int, steps: int, warmup: int, impl: str, layers: Optional[int] = N
 
     extra = {}
     if points:
-        for b in (1, 64):
+        for b in other_batches:
             r = time_decode(engine, b, context, steps, warmup)
             extra[f"decode_b{b}"] = r["tokens_per_s"]
 
@@ -253,19 +326,20 @@ def run(gpus: int, steps: int, warmup: int, impl: str, layers: Optional[int] = N
            "prefill_tokens_per_s": stats.prefill_tokens_per_second}
 
     line = {
-        "metric": "decode tok/s at batch 8 (Qwen3-8B bf16, 2,048-token contexts); prefill and batch 1/64 alongside",
+        "metric": f"decode tok/s at batch {batch} ({shape} bf16, {context}-token contexts); prefill and batch "
+                  f"{'/'.join(map(str, other_batches))} alongside",
         "value": main["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": main["ms_per_step"], "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: uniform random token ids, seeded random weights N(0,0.02)",
-        "config": {"model": "Qwen3-8B shape", "layers": layers, "layers_of_model": full_layers,
+        "config": {"model": {"qwen3-8b": "Qwen3-8B shape"}.get(shape, shape + " shape"), "layers": layers, "layers_of_model": full_layers,
                    "hidden_size": cfg["hidden_size"], "num_heads": cfg["num_attention_heads"],
                    "num_kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate_size": cfg["intermediate_size"], "vocab_size": cfg["vocab_size"],
-                   "tied_head": False, "global_batch": batch, "seq_len": context,
+                   "tied_head": bool(cfg["tie_word_embeddings"]), "global_batch": batch, "seq_len": context,
                    "max_context": cfg["max_position_embeddings"], "page_tokens": page_tokens,
                    "prefill_tokens": prefill_tokens, "parallelism": "1 gpu",
-                   "cache_between_steps": "each step reads ~15 GB of weights, far beyond the 126 MB L2",
+                   "cache_between_steps": "each step reads all weights (GBs), far beyond the 126 MB L2",
                    "decode": "CUDA graph per step, sampled ids fed back on device"},
         "clocks": clocks, "e2e": e2e, "gpu_launches": main["launches"], "prefill": prefill,
         "roofline": roofline, "points": extra, "impl": "leone_b200", "build_seconds": round(build_s, 1),

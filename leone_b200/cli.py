@@ -188,9 +188,12 @@ def cmd_replay(args, rest) -> int:
 
 
 def cmd_bench(args) -> int:
-    from .benchmark import run
+    from .benchmark import run, serving
+    if args.workload == "serving":
+        return serving(args.shape or "qwen3-1.7b", requests=args.requests, new_tokens=args.new_tokens,
+                       prefill_chunk=args.prefill_chunk, layers=args.layers)
     return run(1, args.steps, max(3, args.warmup), "leone_b200", layers=args.layers, batch=args.batch,
-               context=args.context, points=not args.no_points)
+               context=args.context, points=not args.no_points, shape=args.shape or "qwen3-8b")
 
 
 def build_parser() -> argparse.ArgumentParser:
@@ -231,8 +234,14 @@ def build_parser() -> argparse.ArgumentParser:
     b.add_argument("--warmup", type=int, default=3)
     b.add_argument("--layers", type=int, default=None)
     b.add_argument("--batch", type=int, default=8)
-    b.add_argument("--context", type=int, default=2048)
+    b.add_argument("--context", type=int, default=None, help="decode context (default: the shape's)")
     b.add_argument("--no-points", action="store_true")
+    b.add_argument("--shape", choices=["qwen3-8b", "qwen3-1.7b", "qwen3-32b"], default=None)
+    b.add_argument("--workload", choices=["decode", "serving"], default="decode",
+                   help="decode: device-timed decode and prefill; serving: many requests through the scheduler")
+    b.add_argument("--requests", type=int, default=64)
+    b.add_argument("--new-tokens", type=int, default=128)
+    b.add_argument("--prefill-chunk", type=int, default=1024)
     return ap
 
 
