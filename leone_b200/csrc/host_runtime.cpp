@@ -1,7 +1,8 @@
 // Host side of the engine's runtime in C++: pools of pages, block tables, fixed-size state
-// slots and the step transaction (reserve -> commit / roll back), and the packing of a step's
-// metadata.  No device code; the Python classes in leone_b200/cache/pages.py and
-// leone_b200/engine/batch.py are thin fronts over these functions.
+// slots and the step transaction (reserve -> commit / roll back), the packing of a step's
+// metadata, and the scheduler's decisions (admission, the next step's entries, finishing,
+// preemption).  No device code; the Python classes in leone_b200/cache/pages.py,
+// leone_b200/engine/batch.py and leone_b200/engine/scheduler.py are fronts over these functions.
 //
 // The reference keeps keys and values in growing segments per session and uses pages only as
 // the unit of admission (crates/leone/src/kv.rs:14-31, 637-674; crates/leone/src/scheduler.rs:
@@ -23,6 +24,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
+#include <deque>
 #include <string>
 #include <unordered_map>
 #include <unordered_set>
@@ -426,6 +428,351 @@ int leone_pack_step(int b, const long long* counts, const long long* tokens, con
   q_start[b] = (int)at;
   (void)m;
   return kOk;
+}
+
+
+// ---- the scheduler's decisions -----------------------------------------------------------------
+// Which requests run, what the next step holds, when a request ends, whom to preempt.  The
+// planner keeps counts only (how many tokens a request has, how many are in the cache, how many
+// it has generated); the Python front keeps the token ids and does what the planner decides
+// (opens and closes requests in the engine, runs the step, samples).  It reads the cache
+// manager it was made over for free pages and slots and never changes it.
+//
+// One step's batch: one token for every decoding request, then portions of prompts in arrival
+// order until the token budget is used (max_batch_tokens for the step, prefill_chunk for a
+// request); with prefill_first decode rows are held back while any running request has prompt
+// left.  The reference dispatches per request with a budget of min(remaining_prefill,
+// prefill_chunk_tokens) or a decode quantum (crates/leone/src/scheduler.rs:341-378).
+// Page policies: 0 "reserve": admitted only if ceil((prompt + max_new - 1) / page_tokens) pages
+// can be set aside for its whole life (crates/leone/src/scheduler.rs:652-667); 1 "optimistic":
+// admitted when its first portion fits, the youngest running request is preempted when a step
+// cannot get its pages.  max_new counts the token sampled from the prompt, so N new tokens need
+// the cache for P + N - 1 positions (crates/leone/src/runtime.rs:3602-3607).
+namespace {
+
+enum SchedState { kWaiting = 0, kRunning = 1, kFinished = 2, kCancelled = 3 };
+enum Reject { kDuplicate = 1, kEmptyPrompt, kOutputLimit, kTokenId, kPromptLimit, kKvCapacity, kQueueLimit };
+enum Finish { kNotFinished = 0, kEos = 1, kLength = 2, kMaxPositions = 3 };
+
+struct SchedRequest {
+  long long n_tokens = 0;       // prompt + generated: what the cache must come to hold
+  long long computed = 0;       // tokens already in the cache
+  long long generated = 0;
+  long long max_new = 0;
+  long long arrival = 0;
+  long long reserved_pages = 0;
+  long long preemptions = 0;
+  int state = kWaiting;
+  bool cancel = false;
+  bool decoding() const { return generated > 0 && computed == n_tokens - 1; }
+};
+
+struct Planner {
+  Manager* cache;
+  long long max_running, max_waiting, max_batch_tokens, prefill_chunk;
+  int policy, prefill_first;
+  long long vocab, max_positions;
+  std::deque<long long> waiting;
+  std::vector<long long> running;
+  std::unordered_map<long long, SchedRequest> requests;
+  long long arrivals = 0, reserved_total = 0;
+  long long admitted = 0, finished = 0, cancelled = 0, preemptions = 0;
+
+  bool has_groups() const { return cache != nullptr && !cache->groups.empty(); }
+  long long pages_for(long long tokens) const {
+    long long most = 0;
+    for (const Group& g : cache->groups) most = std::max(most, g.blocks_for(tokens));
+    return most;
+  }
+  long long pool_pages() const {
+    long long least = 1ll << 30;
+    for (const Group& g : cache->groups) least = std::min(least, (long long)g.pool.n);
+    return least;
+  }
+  long long free_pages() const {
+    long long least = 1ll << 30;
+    for (const Group& g : cache->groups) least = std::min(least, (long long)g.pool.num_free());
+    return least;
+  }
+  SchedRequest* find(long long rid) {
+    auto it = requests.find(rid);
+    return it == requests.end() ? nullptr : &it->second;
+  }
+  void leave_running(long long rid) { running.erase(std::find(running.begin(), running.end(), rid)); }
+  void retire(long long rid, SchedRequest* r, bool was_cancelled) {
+    leave_running(rid);
+    reserved_total -= r->reserved_pages;
+    r->reserved_pages = 0;
+    r->state = was_cancelled ? kCancelled : kFinished;
+    ++(was_cancelled ? cancelled : finished);
+  }
+};
+
+}  // namespace
+
+void* leone_sched_create(void* cache, long long max_running, long long max_waiting, long long max_batch_tokens,
+                         long long prefill_chunk, int policy, int prefill_first, long long vocab,
+                         long long max_positions) {
+  if (max_running <= 0 || max_batch_tokens <= 0 || prefill_chunk <= 0 || policy < 0 || policy > 1) return nullptr;
+  Planner* p = new Planner();
+  p->cache = static_cast<Manager*>(cache);
+  p->max_running = max_running;
+  p->max_waiting = max_waiting;
+  p->max_batch_tokens = max_batch_tokens;
+  p->prefill_chunk = prefill_chunk;
+  p->policy = policy;
+  p->prefill_first = prefill_first;
+  p->vocab = vocab;
+  p->max_positions = max_positions;
+  return p;
+}
+void leone_sched_destroy(void* h) { delete static_cast<Planner*>(h); }
+
+// A new request joins the queue.  Returns 0, or why it can never run (a Reject code; the
+// reference's AdmissionReject, crates/leone/src/scheduler.rs:101-110) with a message.
+int leone_sched_add(void* h, long long rid, const long long* prompt, long long n, long long max_new) {
+  Planner* p = static_cast<Planner*>(h);
+  SchedRequest* old = p->find(rid);
+  if (old != nullptr && (old->state == kWaiting || old->state == kRunning))
+    return fail((Code)kDuplicate, "request id is already in flight");
+  if (n <= 0) return fail((Code)kEmptyPrompt, "a request needs at least one prompt token");
+  if (max_new <= 0) return fail((Code)kOutputLimit, "max_new_tokens must be positive");
+  std::string bad;
+  int n_bad = 0;
+  for (long long i = 0; i < n && n_bad < 8; ++i)
+    if (prompt[i] < 0 || prompt[i] >= p->vocab) bad += (n_bad++ ? ", " : "") + std::to_string(prompt[i]);
+  if (n_bad)
+    return fail((Code)kTokenId, "token ids [" + bad + "] are outside the vocabulary of " + std::to_string(p->vocab));
+  const long long need_positions = n + max_new - 1;
+  if (need_positions > p->max_positions)
+    return fail((Code)kPromptLimit, "prompt (" + std::to_string(n) + ") + max_new_tokens (" + std::to_string(max_new) +
+                                        ") - 1 exceeds the model's " + std::to_string(p->max_positions) + " positions");
+  if (p->has_groups() && p->pages_for(need_positions) > p->pool_pages())
+    return fail((Code)kKvCapacity, "the request needs " + std::to_string(p->pages_for(need_positions)) +
+                                       " pages; the pool has " + std::to_string(p->pool_pages()) + " even when empty");
+  if ((long long)p->waiting.size() >= p->max_waiting)
+    return fail((Code)kQueueLimit, std::to_string(p->max_waiting) + " requests are already waiting");
+  SchedRequest r;
+  r.n_tokens = n;
+  r.max_new = max_new;
+  r.arrival = p->arrivals++;
+  p->requests[rid] = r;
+  p->waiting.push_back(rid);
+  return kOk;
+}
+
+// Queued: leaves at once (returns 1).  Running: marked, leaves at the next step boundary
+// (returns 2; crates/leone/src/scheduler.rs:540-554).  Otherwise 0.
+int leone_sched_cancel(void* h, long long rid) {
+  Planner* p = static_cast<Planner*>(h);
+  SchedRequest* r = p->find(rid);
+  if (r == nullptr || r->state == kFinished || r->state == kCancelled) return 0;
+  if (r->state == kWaiting) {
+    p->waiting.erase(std::find(p->waiting.begin(), p->waiting.end(), rid));
+    r->state = kCancelled;
+    ++p->cancelled;
+    return 1;
+  }
+  r->cancel = true;
+  return 2;
+}
+
+// The running requests that were cancelled leave; the caller closes them.  Returns how many.
+int leone_sched_drop_cancelled(void* h, long long* out, int cap) {
+  Planner* p = static_cast<Planner*>(h);
+  int n = 0;
+  const std::vector<long long> now = p->running;
+  for (long long rid : now) {
+    SchedRequest* r = p->find(rid);
+    if (r->cancel && n < cap) {
+      p->retire(rid, r, true);
+      out[n++] = rid;
+    }
+  }
+  return n;
+}
+
+// Moves requests from the queue to running, in arrival order, while they fit.  The caller
+// opens them (each takes a state slot, which this call counts ahead).  Returns how many.
+int leone_sched_admit(void* h, long long* out, int cap) {
+  Planner* p = static_cast<Planner*>(h);
+  int n = 0;
+  long long slots_free = p->cache != nullptr ? p->cache->slots.num_free() : (1ll << 30);
+  while (!p->waiting.empty() && (long long)p->running.size() < p->max_running && n < cap) {
+    const long long rid = p->waiting.front();
+    SchedRequest* r = p->find(rid);
+    if (slots_free == 0) break;
+    if (p->policy == 0) {
+      const long long need = p->has_groups() ? p->pages_for(r->n_tokens + (r->max_new - r->generated) - 1) : 0;
+      const long long total = p->has_groups() ? p->pool_pages() : (1ll << 30);
+      if (p->reserved_total + need > total) break;
+      r->reserved_pages = need;
+      p->reserved_total += need;
+    } else {
+      const long long first = std::min(r->n_tokens, p->prefill_chunk);
+      if (!p->running.empty() && p->has_groups() && p->pages_for(first) > p->free_pages()) break;
+    }
+    p->waiting.pop_front();
+    r->state = kRunning;
+    r->computed = 0;
+    p->running.push_back(rid);
+    ++p->admitted;
+    --slots_free;
+    out[n++] = rid;
+  }
+  return n;
+}
+
+// The next step's entries: request, index of its first token, count.  Returns how many.
+int leone_sched_plan(void* h, long long* rids, long long* starts, long long* counts, int cap) {
+  Planner* p = static_cast<Planner*>(h);
+  long long budget = p->max_batch_tokens;
+  int n = 0;
+  bool hold_decodes = false;
+  if (p->prefill_first)
+    for (long long rid : p->running) hold_decodes = hold_decodes || !p->find(rid)->decoding();
+  if (!hold_decodes)
+    for (long long rid : p->running) {              // decode rows first
+      const SchedRequest* r = p->find(rid);
+      if (r->decoding() && budget > 0 && n < cap) {
+        rids[n] = rid, starts[n] = r->computed, counts[n] = 1;
+        ++n, --budget;
+      }
+    }
+  for (long long rid : p->running) {                // then prompt portions, oldest first
+    if (budget <= 0 || n >= cap) break;
+    const SchedRequest* r = p->find(rid);
+    const long long left = r->n_tokens - r->computed;
+    if (left >= 1 && !(left == 1 && r->generated > 0)) {
+      const long long count = std::min(std::min(left, p->prefill_chunk), budget);
+      rids[n] = rid, starts[n] = r->computed, counts[n] = count;
+      ++n, budget -= count;
+    }
+  }
+  return n;
+}
+
+// `count` more of the request's tokens are in the cache.
+int leone_sched_computed(void* h, long long rid, long long count) {
+  Planner* p = static_cast<Planner*>(h);
+  SchedRequest* r = p->find(rid);
+  if (r == nullptr || r->state != kRunning) return fail(kRuleBroken, "request " + std::to_string(rid) + " is not running");
+  if (count < 0 || r->computed + count > r->n_tokens)
+    return fail(kRuleBroken, "request " + std::to_string(rid) + ": more tokens computed than it has");
+  r->computed += count;
+  return kOk;
+}
+
+// The request emitted a token.  Returns why it ends now (a Finish code; it has then left the
+// running list and the caller closes it) or 0.  Finished when eos or no tokens remain
+// (crates/leone/src/scheduler.rs:1341-1343).
+int leone_sched_emitted(void* h, long long rid, int is_eos) {
+  Planner* p = static_cast<Planner*>(h);
+  SchedRequest* r = p->find(rid);
+  if (r == nullptr || r->state != kRunning) return -1;
+  ++r->generated;
+  ++r->n_tokens;
+  int reason = kNotFinished;
+  if (is_eos) reason = kEos;
+  else if (r->generated >= r->max_new) reason = kLength;
+  else if (r->n_tokens > p->max_positions) reason = kMaxPositions;
+  if (reason != kNotFinished) p->retire(rid, r, false);
+  return reason;
+}
+
+// The youngest running request other than `keep` (-1: none kept) goes back to the front of the
+// queue, to be recomputed from its first token; the caller closes it.  Returns 1 and the
+// victim, or 0 if nobody can be preempted.
+int leone_sched_preempt_youngest(void* h, long long keep, long long* victim) {
+  Planner* p = static_cast<Planner*>(h);
+  long long best = -1, best_arrival = -1;
+  for (long long rid : p->running) {
+    if (rid == keep) continue;
+    const SchedRequest* r = p->find(rid);
+    if (r->arrival > best_arrival) best = rid, best_arrival = r->arrival;
+  }
+  if (best < 0) return 0;
+  SchedRequest* r = p->find(best);
+  p->leave_running(best);
+  r->state = kWaiting;
+  r->computed = 0;
+  ++r->preemptions;
+  ++p->preemptions;
+  p->waiting.push_front(best);
+  *victim = best;
+  return 1;
+}
+
+// The running request that arrived first, or -1.
+long long leone_sched_oldest_running(void* h) {
+  Planner* p = static_cast<Planner*>(h);
+  long long best = -1, best_arrival = 1ll << 62;
+  for (long long rid : p->running) {
+    const SchedRequest* r = p->find(rid);
+    if (r->arrival < best_arrival) best = rid, best_arrival = r->arrival;
+  }
+  return best;
+}
+
+// How many decode steps these requests can take together without the host: at most `quantum`,
+// what each may still emit, and what the model's positions leave.
+long long leone_sched_decode_quantum(void* h, int n, const long long* rids, long long quantum) {
+  Planner* p = static_cast<Planner*>(h);
+  long long q = quantum;
+  for (int i = 0; i < n; ++i) {
+    const SchedRequest* r = p->find(rids[i]);
+    if (r == nullptr) continue;
+    q = std::min(q, r->max_new - r->generated);
+    q = std::min(q, p->max_positions - r->n_tokens + 1);
+  }
+  return std::max(1ll, q);
+}
+
+// what: 0 tokens, 1 computed, 2 generated, 3 state, 4 reserved pages, 5 preemptions, 6 arrival,
+// 7 cancel requested.  -1 for an unknown request.
+long long leone_sched_get(void* h, long long rid, int what) {
+  const SchedRequest* r = static_cast<Planner*>(h)->find(rid);
+  if (r == nullptr) return -1;
+  switch (what) {
+    case 0: return r->n_tokens;
+    case 1: return r->computed;
+    case 2: return r->generated;
+    case 3: return r->state;
+    case 4: return r->reserved_pages;
+    case 5: return r->preemptions;
+    case 6: return r->arrival;
+    case 7: return r->cancel ? 1 : 0;
+  }
+  return -1;
+}
+
+// what: 0 waiting, 1 running, 2 admitted, 3 finished, 4 cancelled, 5 preemptions, 6 pages set aside.
+long long leone_sched_count(void* h, int what) {
+  const Planner* p = static_cast<Planner*>(h);
+  switch (what) {
+    case 0: return (long long)p->waiting.size();
+    case 1: return (long long)p->running.size();
+    case 2: return p->admitted;
+    case 3: return p->finished;
+    case 4: return p->cancelled;
+    case 5: return p->preemptions;
+    case 6: return p->reserved_total;
+  }
+  return -1;
+}
+
+// The queue (which 0) or the running list (which 1), in order.  Returns how many.
+int leone_sched_list(void* h, int which, long long* out, int cap) {
+  const Planner* p = static_cast<Planner*>(h);
+  int n = 0;
+  if (which == 0) {
+    for (long long rid : p->waiting)
+      if (n < cap) out[n++] = rid;
+  } else {
+    for (long long rid : p->running)
+      if (n < cap) out[n++] = rid;
+  }
+  return n;
 }
 
 }  // extern "C"

@@ -1,15 +1,19 @@
 """The scheduler: admits requests, cuts prompts into portions, decodes, finishes and frees.
 
-Each call of :meth:`Scheduler.step` builds one batch for the engine's step
-function: one token for every request that is decoding, then portions of
-waiting prompts in arrival order until the token budget is used
-(``max_batch_tokens`` for the whole step, ``prefill_chunk_tokens`` per
-request).  With ``prefill_first`` decode rows are held back while any running
-request still has prompt left, so requests that start together also decode
-together (larger decode batches; the choice for offline generation).  The reference dispatches per request with a token budget of
-``min(remaining_prefill, prefill_chunk_tokens)`` or a decode quantum
-(crates/leone/src/scheduler.rs:341-378) and runs prompt portions and decode
-rows in separate passes; here they share one batch.
+The decisions are C++ (``csrc/host_runtime.cpp``, ``leone_sched_*``): who is admitted, what
+the next step holds, when a request ends, whom to preempt.  This module is their front: it
+keeps the token ids, opens and closes requests in the engine as the planner decides, runs the
+step function and the sampler, and mirrors each request's progress in a :class:`Request`.
+
+Each call of :meth:`Scheduler.step` builds one batch for the engine's step function: one token
+for every request that is decoding, then portions of waiting prompts in arrival order until
+the token budget is used (``max_batch_tokens`` for the whole step, ``prefill_chunk_tokens``
+per request).  With ``prefill_first`` decode rows are held back while any running request
+still has prompt left, so requests that start together also decode together (larger decode
+batches; the choice for offline generation).  The reference dispatches per request with a
+token budget of ``min(remaining_prefill, prefill_chunk_tokens)`` or a decode quantum
+(crates/leone/src/scheduler.rs:341-378) and runs prompt portions and decode rows in separate
+passes; here they share one batch.
 
 What happens when pages run out is a policy:
 
@@ -28,13 +32,17 @@ one sampled from the prompt, so N new tokens need the cache for P + N - 1 positi
 """
 from __future__ import annotations
 
-import itertools
-from collections import deque
+import ctypes
+from ctypes import c_int, c_longlong, c_void_p
 from dataclasses import dataclass, field
-from typing import Callable, Deque, Dict, Hashable, List, Optional, Sequence
+from typing import Callable, Dict, Hashable, List, Optional, Sequence
 
-from ..cache.pages import OutOfPages
+from ..cache.pages import OutOfPages, host_library
 from ..sampling.sampler import SamplingParams
+
+_REJECTS = {1: "duplicate", 2: "empty_prompt", 3: "output_limit", 4: "token_id", 5: "prompt_limit",
+            6: "kv_capacity", 7: "queue_limit"}
+_FINISH = {1: "eos", 2: "length", 3: "max_positions"}
 
 
 class AdmissionError(ValueError):
@@ -66,13 +74,13 @@ class SchedulerConfig:
 
 @dataclass
 class Request:
+    """A request as the caller sees it; the planner's counts are mirrored here after every call."""
     rid: Hashable
     prompt: List[int]
     max_new_tokens: int
     sampling: SamplingParams = field(default_factory=SamplingParams)
     eos_token_id: Optional[int] = None
     arrival: int = 0
-    # progress
     tokens: List[int] = field(default_factory=list)      # prompt + generated, what the cache must hold
     computed: int = 0                                    # tokens already in the cache
     generated: List[int] = field(default_factory=list)
@@ -81,6 +89,7 @@ class Request:
     reserved_pages: int = 0
     preemptions: int = 0
     cancel_requested: bool = False
+    key: int = 0                                         # the planner's name for this request
 
     @property
     def remaining_new(self) -> int:
@@ -102,144 +111,143 @@ class Scheduler:
 
     def __init__(self, engine, config: Optional[SchedulerConfig] = None):
         self.engine = engine
-        self.config = config or SchedulerConfig()
-        self.waiting: Deque[Request] = deque()
-        self.running: List[Request] = []
+        self.config = cfg = config or SchedulerConfig()
+        self._lib = lib = host_library()
+        lib.leone_sched_create.restype = c_void_p
+        for name in ("leone_sched_oldest_running", "leone_sched_decode_quantum", "leone_sched_get",
+                     "leone_sched_count"):
+            getattr(lib, name).restype = c_longlong
+        cache_handle = getattr(engine.cache, "_h", None)
+        self._h = c_void_p(lib.leone_sched_create(
+            cache_handle, c_longlong(cfg.max_running), c_longlong(cfg.max_waiting),
+            c_longlong(cfg.max_batch_tokens), c_longlong(cfg.prefill_chunk_tokens),
+            0 if cfg.policy == "reserve" else 1, int(cfg.prefill_first), c_longlong(engine.spec.vocab_size),
+            c_longlong(engine.spec.max_positions)))
+        if not self._h:
+            raise ValueError("scheduler limits must be positive")
         self.requests: Dict[Hashable, Request] = {}
-        self._arrivals = itertools.count()
-        self._reserved_total = 0
-        self.stats = dict(steps=0, prefill_tokens=0, decode_tokens=0, preemptions=0, admitted=0,
-                          finished=0, cancelled=0, max_batch_tokens_seen=0)
+        self._by_key: Dict[int, Request] = {}
+        self._next_key = 1
+        self._cap = cfg.max_running + 8
+        self._buf = [(c_longlong * self._cap)() for _ in range(3)]
+        self._steps = self._prefill_tokens = self._decode_tokens = self._max_batch_tokens_seen = 0
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._lib.leone_sched_destroy(self._h)
+            self._h = None
+
+    # -- views -------------------------------------------------------------------------
+    def _count(self, what: int) -> int:
+        return int(self._lib.leone_sched_count(self._h, what))
+
+    def _listed(self, which: int) -> List[Request]:
+        n = max(self._count(which), 1)
+        out = (c_longlong * n)()
+        n = self._lib.leone_sched_list(self._h, which, out, n)
+        return [self._by_key[k] for k in out[:n]]
+
+    @property
+    def waiting(self) -> List[Request]:
+        return self._listed(0)
+
+    @property
+    def running(self) -> List[Request]:
+        return self._listed(1)
+
+    @property
+    def stats(self) -> dict:
+        return dict(steps=self._steps, prefill_tokens=self._prefill_tokens, decode_tokens=self._decode_tokens,
+                    preemptions=self._count(5), admitted=self._count(2), finished=self._count(3),
+                    cancelled=self._count(4), max_batch_tokens_seen=self._max_batch_tokens_seen)
+
+    def has_work(self) -> bool:
+        return self._count(0) + self._count(1) > 0
 
     # -- admission --------------------------------------------------------------------
-    def _pages_for(self, tokens: int) -> int:
-        return max(self.engine.cache.pages_needed_for(tokens))
-
     def add_request(self, rid: Hashable, prompt: Sequence[int], max_new_tokens: int,
                     sampling: Optional[SamplingParams] = None, eos_token_id: Optional[int] = None) -> Request:
-        spec = self.engine.spec
         prompt = [int(t) for t in prompt]
-        if rid in self.requests and self.requests[rid].state in ("waiting", "running"):
+        old = self.requests.get(rid)
+        if old is not None and old.state in ("waiting", "running"):
             raise AdmissionError("duplicate", f"request id {rid!r} is already in flight")
-        if len(prompt) == 0:
-            raise AdmissionError("empty_prompt", "a request needs at least one prompt token")
-        if max_new_tokens <= 0:
-            raise AdmissionError("output_limit", "max_new_tokens must be positive")
-        bad = [t for t in prompt if not 0 <= t < spec.vocab_size]
-        if bad:
-            raise AdmissionError("token_id", f"token ids {bad[:8]} are outside the vocabulary "
-                                             f"of {spec.vocab_size}")
-        need_positions = len(prompt) + max_new_tokens - 1
-        if need_positions > spec.max_positions:
-            raise AdmissionError("prompt_limit", f"prompt ({len(prompt)}) + max_new_tokens "
-                                 f"({max_new_tokens}) - 1 exceeds the model's {spec.max_positions} positions")
-        num_pages = min(g.pool.num_pages for g in self.engine.cache.groups) if self.engine.cache.groups else 0
-        if self.engine.cache.groups and self._pages_for(need_positions) > num_pages:
-            raise AdmissionError("kv_capacity", f"the request needs {self._pages_for(need_positions)} pages; "
-                                 f"the pool has {num_pages} even when empty")
-        if len(self.waiting) >= self.config.max_waiting:
-            raise AdmissionError("queue_limit", f"{self.config.max_waiting} requests are already waiting")
+        key = self._next_key
+        ids = (c_longlong * max(len(prompt), 1))(*prompt)
+        code = self._lib.leone_sched_add(self._h, c_longlong(key), ids, c_longlong(len(prompt)),
+                                         c_longlong(int(max_new_tokens)))
+        if code != 0:
+            raise AdmissionError(_REJECTS[code], self._lib.leone_host_last_error().decode())
+        self._next_key += 1
         req = Request(rid, prompt, max_new_tokens, sampling or SamplingParams(), eos_token_id,
-                      arrival=next(self._arrivals), tokens=list(prompt))
+                      arrival=int(self._lib.leone_sched_get(self._h, c_longlong(key), 6)),
+                      tokens=list(prompt), key=key)
         self.requests[rid] = req
-        self.waiting.append(req)
+        self._by_key[key] = req
         return req
 
     def cancel(self, rid: Hashable) -> None:
         """Queued: removed at once.  Running: stops at the next step boundary
         (crates/leone/src/scheduler.rs:540-554)."""
         req = self.requests.get(rid)
-        if req is None or req.state in ("finished", "cancelled"):
+        if req is None:
             return
-        if req.state == "waiting":
-            self.waiting.remove(req)
+        what = self._lib.leone_sched_cancel(self._h, c_longlong(req.key))
+        if what == 1:
             req.state, req.finish_reason = "cancelled", "cancelled"
-            self.stats["cancelled"] += 1
-        else:
+        elif what == 2:
             req.cancel_requested = True
 
-    def has_work(self) -> bool:
-        return bool(self.waiting or self.running)
-
     # -- one step's decisions -----------------------------------------------------------
-    def _free_pages(self) -> int:
-        return min(self.engine.cache.free_pages()) if self.engine.cache.groups else 1 << 30
+    def _keys(self, n: int) -> List[int]:
+        return list(self._buf[0][:n])
+
+    def _drop_cancelled(self) -> None:
+        n = self._lib.leone_sched_drop_cancelled(self._h, self._buf[0], self._cap)
+        for key in self._keys(n):
+            req = self._by_key[key]
+            self.engine.close(req.rid)
+            req.state, req.finish_reason, req.reserved_pages = "cancelled", "cancelled", 0
 
     def _try_admit(self) -> None:
         """Move requests from the queue to running, in arrival order, while they fit."""
-        cfg = self.config
-        while self.waiting and len(self.running) < cfg.max_running:
-            req = self.waiting[0]
-            if self.engine.cache.slots.num_free == 0:
-                break
-            if cfg.policy == "reserve":
-                need = self._pages_for(len(req.tokens) + req.remaining_new - 1)
-                total = min(g.pool.num_pages for g in self.engine.cache.groups) if self.engine.cache.groups else 1 << 30
-                if self._reserved_total + need > total:
-                    break
-                req.reserved_pages = need
-                self._reserved_total += need
-            else:
-                first = min(len(req.tokens), cfg.prefill_chunk_tokens)
-                if self.running and self._pages_for(first) > self._free_pages():
-                    break
-            self.waiting.popleft()
+        n = self._lib.leone_sched_admit(self._h, self._buf[0], self._cap)
+        for key in self._keys(n):
+            req = self._by_key[key]
             self.engine.open(req.rid)
-            req.state = "running"
-            req.computed = 0
-            self.running.append(req)
-            self.stats["admitted"] += 1
+            req.state, req.computed = "running", 0
+            req.reserved_pages = int(self._lib.leone_sched_get(self._h, c_longlong(key), 4))
 
     def plan(self, admit: bool = True):
         """Entries of the next step as ``(request, first token index, count)`` triples."""
         self._drop_cancelled()
         if admit:
             self._try_admit()
-        budget = self.config.max_batch_tokens
-        plan = []
-        decoding = lambda r: bool(r.generated) and r.computed == len(r.tokens) - 1   # noqa: E731
-        hold_decodes = self.config.prefill_first and any(not decoding(r) for r in self.running)
-        for req in self.running:                       # decode rows first
-            if hold_decodes:
-                break
-            if req.computed == len(req.tokens) - 1 and req.generated and budget > 0:
-                plan.append((req, req.computed, 1))
-                budget -= 1
-        for req in self.running:                       # then prompt portions, oldest first
-            if budget <= 0:
-                break
-            left = len(req.tokens) - req.computed
-            if left >= 1 and not (left == 1 and req.generated):
-                count = min(left, self.config.prefill_chunk_tokens, budget)
-                plan.append((req, req.computed, count))
-                budget -= count
-        return plan
+        rids, starts, counts = self._buf
+        n = self._lib.leone_sched_plan(self._h, rids, starts, counts, self._cap)
+        return [(self._by_key[rids[i]], int(starts[i]), int(counts[i])) for i in range(n)]
 
-    def _drop_cancelled(self) -> None:
-        for req in [r for r in self.running if r.cancel_requested]:
-            self._retire(req, "cancelled")
-
-    def _retire(self, req: Request, reason: str) -> None:
+    def _emitted(self, req: Request, tok: int) -> Optional[str]:
+        """Book a sampled token; returns why the request ends now, if it does (it is closed then)."""
+        req.generated.append(tok)
+        req.tokens.append(tok)
+        is_eos = req.eos_token_id is not None and tok == req.eos_token_id
+        code = self._lib.leone_sched_emitted(self._h, c_longlong(req.key), int(is_eos))
+        if code <= 0:
+            return None
         self.engine.close(req.rid)
-        self.running.remove(req)
-        self._reserved_total -= req.reserved_pages
-        req.reserved_pages = 0
-        req.state = "cancelled" if reason == "cancelled" else "finished"
-        req.finish_reason = reason
-        self.stats["cancelled" if reason == "cancelled" else "finished"] += 1
+        req.state, req.finish_reason, req.reserved_pages = "finished", _FINISH[code], 0
+        return req.finish_reason
 
-    def _preempt_youngest(self, keep: Optional[Request] = None) -> bool:
-        victims = [r for r in self.running if r is not keep]
-        if not victims:
+    def _preempt_youngest(self) -> bool:
+        """The youngest running request other than the oldest goes back to the queue."""
+        victim = c_longlong(-1)
+        keep = self._lib.leone_sched_oldest_running(self._h)
+        if not self._lib.leone_sched_preempt_youngest(self._h, c_longlong(keep), ctypes.byref(victim)):
             return False
-        victim = max(victims, key=lambda r: r.arrival)
-        self.engine.close(victim.rid)
-        self.running.remove(victim)
-        victim.state = "waiting"
-        victim.computed = 0
-        victim.preemptions += 1
-        self.stats["preemptions"] += 1
-        self.waiting.appendleft(victim)
+        req = self._by_key[victim.value]
+        self.engine.close(req.rid)
+        req.state, req.computed = "waiting", 0
+        req.preemptions += 1
         return True
 
     # -- one step ---------------------------------------------------------------------------
@@ -249,58 +257,41 @@ class Scheduler:
         while True:
             plan = self.plan(admit)
             if not plan:
-                if self.waiting and not self.running:
+                if self._count(0) and not self._count(1):
                     raise RuntimeError("the head of the queue cannot be admitted into an empty engine")
                 return []
-            if self._decode_only(plan) and self.config.use_graphs and hasattr(self.engine, "decode_steps"):
-                try:
-                    return self._decode_quantum([req for req, _, _ in plan])
-                except OutOfPages:
-                    if self.config.policy != "optimistic":
-                        raise
-                    oldest = min(self.running, key=lambda r: r.arrival)
-                    if not self._preempt_youngest(keep=oldest):
-                        raise
-                    admit = False
-                    continue
-            entries = []
-            for req, start, count in plan:
-                last = start + count == len(req.tokens)
-                entries.append((req.rid, req.tokens[start:start + count], [count - 1] if last else []))
             try:
+                if self._decode_only(plan) and self.config.use_graphs and hasattr(self.engine, "decode_steps"):
+                    return self._decode_quantum([req for req, _, _ in plan])
+                entries = []
+                for req, start, count in plan:
+                    last = start + count == len(req.tokens)
+                    entries.append((req.rid, req.tokens[start:start + count], [count - 1] if last else []))
                 logits = self.engine.step(entries)
                 break
             except OutOfPages:
-                if self.config.policy != "optimistic":
-                    raise
-                oldest = min(self.running, key=lambda r: r.arrival)
-                if not self._preempt_youngest(keep=oldest):
+                if self.config.policy != "optimistic" or not self._preempt_youngest():
                     raise
                 admit = False          # the freed pages go to the requests that stay
         outputs: List[StepOutput] = []
         sampled_reqs = []
         for req, start, count in plan:
-            req.computed = start + count
             if count == 1 and req.generated and start == len(req.tokens) - 1:
-                self.stats["decode_tokens"] += 1
+                self._decode_tokens += 1
             else:
-                self.stats["prefill_tokens"] += count
+                self._prefill_tokens += count
+            self._lib.leone_sched_computed(self._h, c_longlong(req.key), c_longlong(count))
+            req.computed = start + count
             if req.computed == len(req.tokens):
                 sampled_reqs.append(req)
-        self.stats["steps"] += 1
-        self.stats["max_batch_tokens_seen"] = max(self.stats["max_batch_tokens_seen"],
-                                                  sum(c for _, _, c in plan))
+        self._steps += 1
+        self._max_batch_tokens_seen = max(self._max_batch_tokens_seen, sum(c for _, _, c in plan))
         if sampled_reqs:
             ids = self.engine.sample(logits, [r.sampling for r in sampled_reqs],
                                      [len(r.tokens) - 1 for r in sampled_reqs])
             for req, tok in zip(sampled_reqs, ids):
-                tok = int(tok)
-                req.generated.append(tok)
-                req.tokens.append(tok)
-                reason = self._finish_reason(req, tok)
-                if reason:
-                    self._retire(req, reason)
-                outputs.append(StepOutput(req.rid, tok, reason is not None, reason))
+                reason = self._emitted(req, int(tok))
+                outputs.append(StepOutput(req.rid, int(tok), reason is not None, reason))
         return outputs
 
     @staticmethod
@@ -308,22 +299,12 @@ class Scheduler:
         return all(count == 1 and req.generated and start == len(req.tokens) - 1
                    for req, start, count in plan)
 
-    def _finish_reason(self, req: Request, tok: int) -> Optional[str]:
-        if req.eos_token_id is not None and tok == req.eos_token_id:
-            return "eos"
-        if len(req.generated) >= req.max_new_tokens:
-            return "length"
-        if len(req.tokens) > self.engine.spec.max_positions:
-            return "max_positions"
-        return None
-
     def _decode_quantum(self, reqs: List[Request]) -> List[StepOutput]:
         """Several decode steps of the same requests without the host in between.  A request
         that finishes inside the quantum drops the tokens sampled after its end (the reference
         bounds the same overshoot by its quantum, crates/leone/src/scheduler.rs:1334-1338)."""
-        q = min([self.config.decode_quantum] + [r.remaining_new for r in reqs] +
-                [self.engine.spec.max_positions - len(r.tokens) + 1 for r in reqs])
-        q = max(1, q)
+        keys = (c_longlong * len(reqs))(*[r.key for r in reqs])
+        q = int(self._lib.leone_sched_decode_quantum(self._h, len(reqs), keys, c_longlong(self.config.decode_quantum)))
         steps = self.engine.decode_steps([r.rid for r in reqs], [r.tokens[-1] for r in reqs],
                                          [r.sampling for r in reqs], q)
         outputs: List[StepOutput] = []
@@ -332,18 +313,15 @@ class Scheduler:
             for req, tok in zip(reqs, row):
                 if req.rid in done:
                     continue
-                tok = int(tok)
-                req.generated.append(tok)
-                req.tokens.append(tok)
+                self._lib.leone_sched_computed(self._h, c_longlong(req.key), c_longlong(1))
                 req.computed += 1
-                self.stats["decode_tokens"] += 1
-                reason = self._finish_reason(req, tok)
+                self._decode_tokens += 1
+                reason = self._emitted(req, int(tok))
                 if reason:
                     done.add(req.rid)
-                    self._retire(req, reason)
-                outputs.append(StepOutput(req.rid, tok, reason is not None, reason))
-        self.stats["steps"] += q
-        self.stats["max_batch_tokens_seen"] = max(self.stats["max_batch_tokens_seen"], len(reqs))
+                outputs.append(StepOutput(req.rid, int(tok), reason is not None, reason))
+        self._steps += q
+        self._max_batch_tokens_seen = max(self._max_batch_tokens_seen, len(reqs))
         return outputs
 
     def run_to_completion(self, on_token: Optional[Callable[[StepOutput], None]] = None) -> None:

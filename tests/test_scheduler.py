@@ -19,9 +19,10 @@ class FakeEngine:
     """The engine's interface without a model: the 'next token' is a function of the request's
     tokens so far, so any scheduling must produce the same stream as running alone."""
 
-    def __init__(self, pages=8, page_tokens=4, slots=4):
+    def __init__(self, pages=8, page_tokens=4, slots=4, cache_module=None):
         self.spec = FakeSpec()
-        self.cache = CacheManager([GroupSpec("full", 1, 8)], page_tokens, pages, slots)
+        make, group = (cache_module.CacheManager, cache_module.GroupSpec) if cache_module else (CacheManager, GroupSpec)
+        self.cache = make([group("full", 1, 8)], page_tokens, pages, slots)
         self.seen = {}
         self.batches = []
 
@@ -221,3 +222,61 @@ def test_generation_with_the_tiny_model_on_emulated_kernels(tmp_path):
                 assert got == want, (which, policy, first)
             eng.cache.check_invariants()
             assert eng.cache.free_pages()[0] == pages
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_the_native_planner_and_the_plain_scheduler_agree_step_by_step(seed):
+    """The same arrivals, cancellations and limits go to the scheduler (decisions in C++, over the
+    C++ cache manager) and to the Python model under tests/plain (over its own cache model):
+    every step's batch, every emitted token, every request's end and the counters are equal."""
+    from tests.plain import cache_model, scheduler_model
+    rng = random.Random(500 + seed)
+    policy = ["reserve", "optimistic"][seed % 2]
+    pages, page_tokens, slots = rng.choice([5, 7, 12]), rng.choice([2, 4]), rng.choice([2, 3, 5])
+    limits = dict(max_running=rng.choice([2, 3, 8]), max_waiting=rng.choice([3, 50]),
+                  max_batch_tokens=rng.choice([4, 8, 32]), prefill_chunk_tokens=rng.choice([2, 5, 32]),
+                  policy=policy, prefill_first=bool(seed % 3 == 0))
+    ea = FakeEngine(pages, page_tokens, slots)
+    eb = FakeEngine(pages, page_tokens, slots, cache_module=cache_model)
+    a = Scheduler(ea, SchedulerConfig(**limits))
+    b = scheduler_model.Scheduler(eb, scheduler_model.SchedulerConfig(**limits))
+    arrivals = 0
+    for tick in range(300):
+        for _ in range(rng.choice([0, 0, 1, 2])):
+            rid = arrivals if rng.random() < 0.9 else rng.randrange(arrivals + 1)
+            arrivals += 1
+            prompt = [rng.randrange(0, 103) for _ in range(rng.choice([0, 1, 3, 9, 20, 70]))]
+            new = rng.choice([0, 1, 2, 5, 9])
+            eos = rng.choice([None, None, 7, 50])
+            errs = []
+            for s_, err in ((a, AdmissionError), (b, scheduler_model.AdmissionError)):
+                try:
+                    s_.add_request(rid, prompt, new, None, eos)
+                    errs.append(None)
+                except err as exc:
+                    errs.append(exc.reason)
+            assert errs[0] == errs[1], (rid, prompt, new, errs)
+        if rng.random() < 0.1 and arrivals:
+            rid = rng.randrange(arrivals)
+            a.cancel(rid)
+            b.cancel(rid)
+        outs = []
+        for s_ in (a, b):
+            try:
+                outs.append([(o.rid, o.token, o.finished, o.finish_reason) for o in s_.step()])
+            except (OutOfPages, cache_model.OutOfPages):
+                outs.append("out of pages")
+            except RuntimeError as exc:
+                outs.append(str(exc))
+        assert outs[0] == outs[1], tick
+        assert ea.batches == eb.batches
+        assert [r.rid for r in a.running] == [r.rid for r in b.running]
+        assert [r.rid for r in a.waiting] == [r.rid for r in b.waiting]
+        assert a.stats == b.stats
+        assert ea.cache.free_pages() == eb.cache.free_pages()
+        if isinstance(outs[0], str):
+            break
+    for rid, rb in b.requests.items():
+        ra = a.requests[rid]
+        assert (ra.state, ra.finish_reason, ra.generated, ra.tokens, ra.computed, ra.preemptions, ra.reserved_pages) == \
+               (rb.state, rb.finish_reason, rb.generated, rb.tokens, rb.computed, rb.preemptions, rb.reserved_pages), rid
