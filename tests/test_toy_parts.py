@@ -1,6 +1,7 @@
 """Parts defined outside the framework are registered, built and stepped without touching it:
-a mixer with per-request state, an unfused position encoding, a windowed attention layer with
-partial rotary, three different mixers in three layers."""
+a mixer with per-request state, a feed-forward that routes tokens to experts, an unfused position
+encoding, a windowed attention layer with partial rotary; three different mixers and two different
+feed-forwards in three layers."""
 import pytest
 import torch
 

@@ -1,14 +1,15 @@
 """Toy parts defined by the tests, outside the framework: a mixer with a state of its own, a
-position encoding without a rotary table, and an architecture that mixes them with attention
-layer by layer.  Nothing here is a model of anyone's; it shows that parts are pluggable."""
+feed-forward that routes each token to two of several small experts, a position encoding
+without a rotary table, and an architecture that mixes them with attention and the dense
+feed-forward layer by layer.  Nothing here is a model of anyone's; it shows that parts are pluggable."""
 from dataclasses import dataclass
 
 import torch
 
 from leone_b200.config.base import ConfigReader, ModelConfig
-from leone_b200.parts.base import FixedState, Mixer, PositionEncoding, WeightSpec
+from leone_b200.parts.base import FeedForward, FixedState, Mixer, PositionEncoding, WeightSpec
 from leone_b200.parts.spec import LayerSpec, ModelSpec, PartSpec
-from leone_b200.registry import ARCHITECTURES, MIXERS, POSITION_ENCODINGS
+from leone_b200.registry import ARCHITECTURES, FEED_FORWARDS, MIXERS, POSITION_ENCODINGS
 
 
 class DecayMixer(Mixer):
@@ -43,6 +44,42 @@ class DecayMixer(Mixer):
             hidden[bounds[s]:bounds[s + 1]] += torch.stack(rows) @ self.w.float().t()
 
 
+class RoutedFeedForward(FeedForward):
+    """Each token goes to the ``top_k`` experts with the largest router logits (fp32), weighted by
+    the softmax over those logits; an expert is ``W_out relu(W_in x)``.  hidden += the mixture."""
+
+    def __init__(self, params, rt):
+        super().__init__(params, rt)
+        self.hidden = int(params["hidden_size"])
+        self.inter = int(params["expert_size"])
+        self.experts = int(params["num_experts"])
+        self.top_k = int(params["top_k"])
+        self.w = None
+
+    def weight_specs(self):
+        specs = [WeightSpec("router.weight", (self.experts, self.hidden))]
+        for e in range(self.experts):
+            specs += [WeightSpec(f"experts.{e}.in.weight", (self.inter, self.hidden)),
+                      WeightSpec(f"experts.{e}.out.weight", (self.hidden, self.inter))]
+        return specs
+
+    def load(self, tensors):
+        self.w = tensors
+
+    def forward(self, ctx, x, hidden):
+        xf = x.float()
+        logits = xf @ self.w["router.weight"].float().t()
+        top, chosen = logits.topk(self.top_k, dim=-1)
+        share = torch.softmax(top, dim=-1)
+        for e in range(self.experts):
+            rows, which = (chosen == e).nonzero(as_tuple=True)
+            if rows.numel() == 0:
+                continue
+            inner = torch.relu(xf[rows] @ self.w[f"experts.{e}.in.weight"].float().t())
+            out = inner @ self.w[f"experts.{e}.out.weight"].float().t()
+            hidden.index_add_(0, rows, (out * share[rows, which][:, None]).to(hidden.dtype))
+
+
 class AdditivePositions(PositionEncoding):
     """q and k get ``amplitude * sin(position * (dim index + 1) * rate)`` added: an encoding the
     attention kernel cannot fuse, applied through ``apply``."""
@@ -70,6 +107,8 @@ class ToyConfig(ModelConfig):
     max_position_embeddings: int = 0
     window: int = 0
     decay: float = 0.5
+    num_experts: int = 0
+    expert_size: int = 0
 
     @classmethod
     def from_dict(cls, raw):
@@ -77,15 +116,19 @@ class ToyConfig(ModelConfig):
         return cls("ToyStateLM", r.positive_int("hidden_size"), r.positive_int("vocab_size"),
                    r.positive_int("num_heads"), r.positive_int("head_dim"),
                    r.positive_int("intermediate_size"), r.positive_int("max_position_embeddings"),
-                   r.positive_int("window"), r.positive_float("decay"))
+                   r.positive_int("window"), r.positive_float("decay"), r.positive_int("num_experts"),
+                   r.positive_int("expert_size"))
 
 
 def build_toy_spec(cfg: ToyConfig) -> ModelSpec:
     norm = {"size": cfg.hidden_size, "eps": 1e-5}
     ffn = PartSpec("swiglu", {"hidden_size": cfg.hidden_size, "intermediate_size": cfg.intermediate_size})
 
+    routed = PartSpec("toy_routed", {"hidden_size": cfg.hidden_size, "expert_size": cfg.expert_size,
+                                     "num_experts": cfg.num_experts, "top_k": 2})
+
     def layer(i, mixer):
-        return LayerSpec(f"blocks.{i}", "pre_norm", mixer, ffn,
+        return LayerSpec(f"blocks.{i}", "pre_norm", mixer, routed if i == 1 else ffn,
                          PartSpec("rms_norm", {**norm, "name": "norm1.weight"}),
                          PartSpec("rms_norm", {**norm, "name": "norm2.weight"}))
 
@@ -106,18 +149,21 @@ def build_toy_spec(cfg: ToyConfig) -> ModelSpec:
 
 def register():
     MIXERS.register("toy_decay", DecayMixer)
+    FEED_FORWARDS.register("toy_routed", RoutedFeedForward)
     POSITION_ENCODINGS.register("toy_additive", AdditivePositions)
     ARCHITECTURES.add("ToyStateLM", ToyConfig, build_toy_spec)
 
 
 def unregister():
     MIXERS.unregister("toy_decay")
+    FEED_FORWARDS.unregister("toy_routed")
     POSITION_ENCODINGS.unregister("toy_additive")
     ARCHITECTURES.unregister("ToyStateLM")
 
 
 TOY = dict(architectures=["ToyStateLM"], hidden_size=48, vocab_size=97, num_heads=3, head_dim=32,
-           intermediate_size=80, max_position_embeddings=128, window=9, decay=0.7)
+           intermediate_size=80, max_position_embeddings=128, window=9, decay=0.7, num_experts=5,
+           expert_size=24)
 
 
 def plain_logits(cfg: ToyConfig, w, tokens):
@@ -131,6 +177,17 @@ def plain_logits(cfg: ToyConfig, w, tokens):
     def ffn(x, p):
         return pm.linear(pm.swiglu(pm.linear(x, w[p + "gate_proj.weight"]), pm.linear(x, w[p + "up_proj.weight"])),
                          w[p + "down_proj.weight"])
+
+    def routed(x, p):
+        logits = x @ w[p + "router.weight"].t()
+        out = torch.zeros_like(x)
+        for t in range(t_len):
+            top, chosen = logits[t].topk(2)
+            share = torch.softmax(top, dim=-1)
+            for s, e in zip(share, chosen.tolist()):
+                inner = torch.relu(w[f"{p}experts.{e}.in.weight"] @ x[t])
+                out[t] += s * (w[f"{p}experts.{e}.out.weight"] @ inner)
+        return out
 
     # layer 0: decay mixer
     x = pm.rms_norm(h, w["blocks.0.norm1.weight"], 1e-5)
@@ -157,5 +214,6 @@ def plain_logits(cfg: ToyConfig, w, tokens):
             k = pm.rope_half_split(k, pos, 100.0, rotary_dim=cfg.head_dim // 2)
         a = pm.attention(q, k, v, pos, window=window).reshape(t_len, -1)
         h = h + pm.linear(a, w[p + "o_proj.weight"])
-        h = h + ffn(pm.rms_norm(h, w[p + "norm2.weight"], 1e-5), p)
+        x = pm.rms_norm(h, w[p + "norm2.weight"], 1e-5)
+        h = h + (routed(x, p) if i == 1 else ffn(x, p))
     return pm.linear(pm.rms_norm(h, w["final_norm.weight"], 1e-5), w["head.weight"])
