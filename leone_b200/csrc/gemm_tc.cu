@@ -741,6 +741,11 @@ extern "C" int leone_gemm_tc_tiles(int m, int n) {
   return ((n + kTileW - 1) / kTileW) * ((m + bn - 1) / bn);
 }
 
+// Tiles of the token-major form (128 tokens x 256 weight rows), which takes any number of tokens.
+extern "C" int leone_gemm_tc_tiles_token_major(int m, int n) {
+  return ((n + 255) / 256) * ((m + kTileW - 1) / kTileW);
+}
+
 // Parts of the sums of squares a product of m tokens with n outputs leaves for the norm after
 // it: one per 32 weight rows up to 256 tokens, one per tile of 256 weight rows above.
 extern "C" int leone_gemm_tc_norm_parts(int m, int n) { return m <= 256 ? (n + 31) / 32 : (n + 255) / 256; }
@@ -782,10 +787,13 @@ extern "C" int leone_gemm_tc_cluster_capacity(int m, int splits) {
 // distributed shared memory (needs full_tiles == 0, 2 <= splits <= 8, at most 256 tokens, and
 // tiles * splits blocks resident at once: see leone_gemm_tc_cluster_capacity); workspace and
 // counters are not used.
+// token_major != 0: the token-major form (128 tokens x 256 weight rows per tile, never split)
+// also for 256 tokens or fewer, where it reads the token operand less often than the swapped
+// form does; the norm arguments must then be null.
 extern "C" int leone_gemm_tc(const void* x, const void* w, void* out, const float* residual, int m,
                              int n, int k, int ldx, int ldw, int ldc, int epilogue, int splits,
                              int full_tiles, float* workspace, int* counters, int* status,
-                             int sm_count, int cluster, void* norm_out_x, const float* norm_out_w,
+                             int sm_count, int cluster, int token_major, void* norm_out_x, const float* norm_out_w,
                              float* norm_out_ss, int ld_norm_out, const float* norm_in_ss,
                              int norm_in_parts, float norm_eps, cudaStream_t stream) {
   if (m <= 0 || n <= 0) return 0;
@@ -794,7 +802,9 @@ extern "C" int leone_gemm_tc(const void* x, const void* w, void* out, const floa
   if (epilogue == 2 && residual == nullptr) return kRefusedSize;
   if (epilogue == 3 && (n % 32) != 0) return kRefusedSize;
   const int k_blocks = (k + kTileK - 1) / kTileK;
-  if (m > 256) splits = 1;
+  const bool swap = m <= 256 && !token_major;
+  if (!swap) splits = 1;
+  if (!swap && m <= 256 && (norm_out_x != nullptr || norm_in_ss != nullptr)) return kRefusedSize;
   if (splits > k_blocks) splits = k_blocks;
   // every split must own at least one k-block
   while (splits > 1 && (splits - 1) * ((k_blocks + splits - 1) / splits) >= k_blocks) --splits;
@@ -804,11 +814,10 @@ extern "C" int leone_gemm_tc(const void* x, const void* w, void* out, const floa
   if (norm_in_ss != nullptr && norm_in_parts < 1) return kRefusedSize;
   if (cluster && (full_tiles != 0 || splits > 8 || m > 256)) return kRefusedSize;
   if (splits > 1 && !cluster && (workspace == nullptr || counters == nullptr)) return kRefusedSize;
-  const int tiles = leone_gemm_tc_tiles(m, n);
+  const int tiles = swap ? leone_gemm_tc_tiles(m, n) : leone_gemm_tc_tiles_token_major(m, n);
   if (splits == 1) full_tiles = tiles;
   if (full_tiles < 0 || full_tiles > tiles) return kRefusedSize;
   const int bn = leone_gemm_tc_tile(m);
-  const bool swap = m <= 256;
   CUtensorMap mw, mx;
   int r = make_tensor_map_2d(&mw, w, (uint64_t)n, (uint64_t)k, (uint64_t)ldw, swap ? kTileW : 256);
   if (r != 0) return r;

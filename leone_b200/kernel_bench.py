@@ -55,7 +55,8 @@ def _time(fn, reps: int, warmup: int, flush=None, per_graph: int = 1) -> float:
     return times[len(times) // 2]
 
 
-def bench_gemm(ops, m, n, k, splits, epilogue, reps, warmup, flush, trace=False, cluster=False, norm="none"):
+def bench_gemm(ops, m, n, k, splits, epilogue, reps, warmup, flush, trace=False, cluster=False, norm="none",
+               token_major=None):
     fast = ops.fast
     x = torch.randn((m, k), device=DEV).to(torch.bfloat16)
     # several copies of the weight so successive launches do not hit L2
@@ -68,7 +69,11 @@ def bench_gemm(ops, m, n, k, splits, epilogue, reps, warmup, flush, trace=False,
         out.zero_()
     state = {"i": 0}
     full_tiles = 0
-    if splits is None:
+    if token_major is None:
+        token_major = splits is None and norm == "none" and fast.token_major(m, n)
+    if token_major:
+        splits, cluster = 1, False
+    elif splits is None:
         splits, full_tiles, cluster = fast.choose_splits(m, n, k)
 
     # an RMSNorm folded into this product: "out" = it is the product before the norm, "in" = after
@@ -84,14 +89,14 @@ def bench_gemm(ops, m, n, k, splits, epilogue, reps, warmup, flush, trace=False,
         w = ws[state["i"] % copies]
         state["i"] += 1
         fast._gemm(x, w, out, epilogue, res, n, splits=splits, full_tiles=full_tiles, cluster=cluster,
-                   norm_in=norm_in, norm_out=norm_out)
+                   norm_in=norm_in, norm_out=norm_out, token_major=token_major)
 
     ms = _time(run, reps, warmup, flush, per_graph=copies)
     if trace:
         _print_trace(ops, run, copies)
     bytes_ = n * k * 2 + m * k * 2 + out.numel() * out.element_size()
     flops = 2.0 * m * n * k
-    return dict(kernel="gemm_tc", m=m, n=n, k=k, norm=norm, splits=splits, full_tiles=full_tiles, cluster=bool(cluster), epilogue=epilogue, us=ms * 1e3,
+    return dict(kernel="gemm_tc", m=m, n=n, k=k, norm=norm, splits=splits, full_tiles=full_tiles, cluster=bool(cluster), token_major=bool(token_major), epilogue=epilogue, us=ms * 1e3,
                 gbs=bytes_ / ms / 1e6, tflops=flops / ms / 1e9)
 
 
@@ -215,6 +220,8 @@ def main(argv=None) -> int:
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--flush", action="store_true", help="write a 256 MB buffer between timed launches")
+    ap.add_argument("--token-major", choices=["auto", "0", "1"], default="auto",
+                    help="gemm, layer-shapes: force the token-major (1) or the swapped (0) form up to 256 tokens")
     ap.add_argument("--trace", action="store_true", help="gemm: print the kernel's phase time stamps")
     ap.add_argument("--prep", choices=["none", "kernel", "fused"], default="none",
                     help="decode-attention: where q/k norm, rotary and cache write are done")
@@ -230,12 +237,14 @@ def main(argv=None) -> int:
     rows = []
     if args.what == "gemm":
         rows.append(bench_gemm(ops, args.m, args.n, args.k, args.splits, args.epilogue, args.reps, args.warmup, flush,
-                               args.trace, args.cluster, args.norm))
+                               args.trace, args.cluster, args.norm,
+                               None if args.token_major == "auto" else args.token_major == "1"))
     elif args.what == "layer-shapes":
         h, inter, qkv = 4096, 12288, (args.heads + 2 * args.kv_heads) * args.head_dim
         for name, n, k, epi in (("qkv", qkv, h, 0), ("o_proj", h, args.heads * args.head_dim, 2),
                                 ("gate_up", 2 * inter, h, 3), ("down", h, inter, 2), ("lm_head", 151936, h, 1)):
-            r = bench_gemm(ops, args.m, n, k, None, epi, args.reps, args.warmup, flush)
+            r = bench_gemm(ops, args.m, n, k, None, epi, args.reps, args.warmup, flush,
+                           token_major=None if args.token_major == "auto" else args.token_major == "1")
             r["name"] = name
             rows.append(r)
     elif args.what == "decode-attention":

@@ -36,6 +36,13 @@ class FastKernels:
         # LEONE_NO_FUSED_NORM=1 keeps every RMSNorm a kernel of its own
         self.fuse_norm = os.environ.get("LEONE_NO_FUSED_NORM", "0") != "1"
         self.fuse_norm_tokens = 32
+        # LEONE_NO_TOKEN_MAJOR=1 keeps every product of up to 256 tokens in the swapped form
+        # LEONE_NO_DIVIDED_STEPS=1 sends a mixed step's decode rows through the prompt attention kernel too
+        self.divide_mixed_steps = os.environ.get("LEONE_NO_DIVIDED_STEPS", "0") != "1"
+        self.mixed_decode_rows_from = 1
+        self.use_token_major = os.environ.get("LEONE_NO_TOKEN_MAJOR", "0") != "1"
+        self.token_major_from = 64         # tokens above which the token-major form is considered
+        self.token_major_fill = 0.6        # of the SMs that its tiles must fill
         self.force_decode_splits = int(os.environ.get("LEONE_DECODE_SPLITS", "0"))    # tuning aid
         # LEONE_NO_FUSED_DECODE=1 keeps q/k norm, rotation and cache write in their own kernel
         self.fuse_decode = os.environ.get("LEONE_NO_FUSED_DECODE", "0") != "1"
@@ -122,8 +129,25 @@ class FastKernels:
         return (k % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
                 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
+    def token_major(self, m: int, n: int) -> bool:
+        """Which form of the product runs: tokens on the MMA's 128-row side and 256 weight rows
+        per tile (True), or weights on that side and the tokens as the tile's width (False).
+        Always above 256 tokens.  From 65 to 256 tokens too when the token-major tiles fill
+        at least ``token_major_fill`` of the SMs and at most two rounds of them (the gate/up
+        product of a wide feed-forward): the swapped form re-reads the whole token operand for
+        every 128 weight rows, twice the bytes of the weights at 256 tokens (gate/up of the 8B
+        shape: 65 µs against 49 at 128 tokens, 100 against 68 at 256).  With fewer tiles the
+        swapped form's split along K keeps more SMs busy; with many more (an output head, whose
+        time is the fp32 logits it writes) the swapped form measured a few percent faster."""
+        if m > 256:
+            return True
+        if m <= self.token_major_from or not self.use_token_major:
+            return False
+        tiles = int(self.lib.leone_gemm_tc_tiles_token_major(m, n))
+        return self.token_major_fill * self.sm_count <= tiles <= 2 * self.sm_count
+
     def _gemm(self, x, w, out, epilogue, residual, n_rows, splits=None, full_tiles=0, cluster=False,
-              norm_in=None, norm_out=None) -> bool:
+              norm_in=None, norm_out=None, token_major=None) -> bool:
         """``splits=None`` lets :meth:`choose_splits` decide; otherwise tiles from
         ``full_tiles`` on are split ``splits`` ways, summed through a workspace or, with
         ``cluster``, inside a thread-block cluster.
@@ -133,7 +157,11 @@ class FastKernels:
         for the RMSNorm that follows it; ``norm_in=(ss, parts, eps)``: ``x`` is such an ``xn``
         and every output row is scaled by the norm's ``rsqrt(mean + eps)``."""
         m, k = x.shape
-        if splits is None:
+        if token_major is None:
+            token_major = splits is None and norm_in is None and norm_out is None and self.token_major(m, n_rows)
+        if token_major:
+            splits, full_tiles, cluster = 1, 0, False
+        elif splits is None:
             splits, full_tiles, cluster = self.choose_splits(m, n_rows, k)
         ws = ct = None
         if splits > 1 and not cluster:
@@ -148,10 +176,10 @@ class FastKernels:
         code = self.lib.leone_gemm_tc(_ptr(x), _ptr(w), _ptr(out), _ptr(residual), m, n_rows, k,
                                       x.stride(0), w.stride(0), out.stride(0), epilogue, splits,
                                       full_tiles, _ptr(ws), _ptr(ct), _ptr(self.status), self.sm_count,
-                                      1 if cluster else 0, *no, *ni, self._stream())
+                                      1 if cluster else 0, 1 if token_major else 0, *no, *ni, self._stream())
         if code != 0:
             raise RuntimeError(f"gemm_tc refused or failed with code {code} for m={m} n={n_rows} k={k} "
-                               f"splits={splits} cluster={cluster}")
+                               f"splits={splits} cluster={cluster} token_major={token_major}")
         return True
 
     def fuses_norm(self, m: int) -> bool:
@@ -229,48 +257,85 @@ class FastKernels:
         blocks = n_seqs * n_kv * (-(-g // 16)) * splits
         return self.use_clusters and (splits == 1 or (splits <= 8 and blocks <= 2 * self.sm_count))
 
+    def leading_decode_rows(self, ctx) -> int:
+        """In a mixed step, how many sequences at the front of the batch bring a single token
+        (the scheduler puts decode rows first).  Their attention runs on the decode kernel
+        (which streams a sequence's keys once for all its heads) and the rest on the prompt
+        kernel, which would spend a 128-row tile on each of them.  0: do not divide the step."""
+        q_lens = getattr(ctx, "q_lens", None)
+        if ctx.decode_only or getattr(ctx, "fixed_shapes", False) or q_lens is None or not self.divide_mixed_steps:
+            return 0
+        n = 0
+        while n < len(q_lens) and q_lens[n] == 1:
+            n += 1
+        return n if self.mixed_decode_rows_from <= n < len(q_lens) else 0
+
     def attention(self, ctx, qkv, out, n_q, n_kv, d, scale, window, cache, fuse=None) -> bool:
         if not self.attention_supported(qkv.dtype, n_q, n_kv, d, qkv.stride(0)):
             return False
-        g = n_q // n_kv
-        from ctypes import c_float
-        kp, vp, bt = cache.k_pool, cache.v_pool, cache.block_table
-        common = (_ptr(qkv), qkv.stride(0), _ptr(out), out.stride(0), _ptr(kp), _ptr(vp), _ptr(bt),
-                  bt.shape[1], _ptr(ctx.q_start), _ptr(ctx.ctx_len), ctx.n_seqs)
+        bt = cache.block_table
+        args = (qkv, out, n_q, n_kv, d, scale, window, cache)
         if ctx.decode_only:
-            splits = self.decode_splits(ctx.n_seqs, n_kv, g, ctx.max_ctx_len)
-            if self.decode_in_clusters(ctx.n_seqs, n_kv, g, ctx.max_ctx_len):
-                # the splits of a (sequence, KV head) merge inside a cluster; optionally the
-                # kernel norms and rotates q and the new k and writes the cache itself
-                fz = (0, None, None, c_float(0.0), None, 0, 0)
-                if fuse is not None:
-                    rope = fuse["rope"]
-                    fz = (1, _ptr(fuse["q_w"]), _ptr(fuse["k_w"]), c_float(fuse["eps"]), _ptr(rope),
-                          rope.shape[0] if rope is not None else 0, 1 if fuse["write_cache"] else 0)
-                code = self.lib.leone_attention_decode_cluster(
-                    *common, n_q, n_kv, d, c_float(scale), int(window or 0), cache.page_tokens,
-                    kp.shape[0], splits, *fz, _ptr(ctx.status), self._stream())
-            else:
-                if fuse is not None:
-                    raise RuntimeError("fused decode attention asked for where decode_fusable() is false")
-                scratch = None
-                if splits > 1:
-                    need = self.lib.leone_attention_decode_scratch(ctx.n_seqs, n_q, d, splits)
-                    scratch = self._attn_scratch(need)
-                code = self.lib.leone_attention_decode(
-                    *common, n_q, n_kv, d, c_float(scale), int(window or 0), cache.page_tokens,
-                    kp.shape[0], splits, _ptr(scratch), _ptr(ctx.status), self._stream())
+            self._attention_decode(*args, ctx.q_start, ctx.ctx_len, bt, ctx.n_seqs, ctx.max_ctx_len, ctx.status, fuse)
+            return True
+        if fuse is not None:
+            raise RuntimeError("fused q/k preparation is a decode-step feature")
+        n_dec = self.leading_decode_rows(ctx)
+        if n_dec:
+            self._attention_decode(*args, ctx.q_start[:n_dec + 1], ctx.ctx_len[:n_dec], bt[:n_dec], n_dec,
+                                   int(ctx.ctx_lens[:n_dec].max()), ctx.status, None)
+        self._attention_prompt(*args, ctx.q_start[n_dec:], ctx.ctx_len[n_dec:], bt[n_dec:], ctx.n_seqs - n_dec,
+                               int(ctx.q_lens[n_dec:].max()) if n_dec else ctx.max_q_len, ctx.status)
+        return True
+
+    def _attention_decode(self, qkv, out, n_q, n_kv, d, scale, window, cache, q_start, ctx_len, bt, n_seqs,
+                          max_ctx, status, fuse) -> None:
+        """Sequences with one query token each (row ``q_start[s]``)."""
+        from ctypes import c_float
+        g = n_q // n_kv
+        kp, vp = cache.k_pool, cache.v_pool
+        common = (_ptr(qkv), qkv.stride(0), _ptr(out), out.stride(0), _ptr(kp), _ptr(vp), _ptr(bt),
+                  bt.stride(0), _ptr(q_start), _ptr(ctx_len), n_seqs)
+        splits = self.decode_splits(n_seqs, n_kv, g, max_ctx)
+        if self.decode_in_clusters(n_seqs, n_kv, g, max_ctx):
+            # the splits of a (sequence, KV head) merge inside a cluster; optionally the
+            # kernel norms and rotates q and the new k and writes the cache itself
+            fz = (0, None, None, c_float(0.0), None, 0, 0)
+            if fuse is not None:
+                rope = fuse["rope"]
+                fz = (1, _ptr(fuse["q_w"]), _ptr(fuse["k_w"]), c_float(fuse["eps"]), _ptr(rope),
+                      rope.shape[0] if rope is not None else 0, 1 if fuse["write_cache"] else 0)
+            code = self.lib.leone_attention_decode_cluster(
+                *common, n_q, n_kv, d, c_float(scale), int(window or 0), cache.page_tokens,
+                kp.shape[0], splits, *fz, _ptr(status), self._stream())
         else:
             if fuse is not None:
-                raise RuntimeError("fused q/k preparation is a decode-step feature")
-            # head sizes 64 and 128 run on tcgen05; the others on the mma.sync kernel
-            tc = self.use_tc_attention and d in (64, 128) and g <= 128 and out.stride(0) % 8 == 0
-            entry = self.lib.leone_attention_prefill_tc if tc else self.lib.leone_attention_prefill
-            code = entry(*common, ctx.max_q_len, n_q, n_kv, d, c_float(scale), int(window or 0),
-                         cache.page_tokens, kp.shape[0], _ptr(ctx.status), self._stream())
+                raise RuntimeError("fused decode attention asked for where decode_fusable() is false")
+            scratch = None
+            if splits > 1:
+                need = self.lib.leone_attention_decode_scratch(n_seqs, n_q, d, splits)
+                scratch = self._attn_scratch(need)
+            code = self.lib.leone_attention_decode(
+                *common, n_q, n_kv, d, c_float(scale), int(window or 0), cache.page_tokens,
+                kp.shape[0], splits, _ptr(scratch), _ptr(status), self._stream())
         if code != 0:
-            raise RuntimeError(f"tiled attention refused or failed with code {code}")
-        return True
+            raise RuntimeError(f"decode attention refused or failed with code {code}")
+
+    def _attention_prompt(self, qkv, out, n_q, n_kv, d, scale, window, cache, q_start, ctx_len, bt, n_seqs,
+                          max_q_len, status) -> None:
+        """Sequences with any number of query tokens (rows ``q_start[s] .. q_start[s + 1]``)."""
+        from ctypes import c_float
+        g = n_q // n_kv
+        kp, vp = cache.k_pool, cache.v_pool
+        # head sizes 64 and 128 run on tcgen05; the others on the mma.sync kernel
+        tc = self.use_tc_attention and d in (64, 128) and g <= 128 and out.stride(0) % 8 == 0
+        entry = self.lib.leone_attention_prefill_tc if tc else self.lib.leone_attention_prefill
+        code = entry(_ptr(qkv), qkv.stride(0), _ptr(out), out.stride(0), _ptr(kp), _ptr(vp), _ptr(bt),
+                     bt.stride(0), _ptr(q_start), _ptr(ctx_len), n_seqs, max_q_len, n_q, n_kv, d,
+                     c_float(scale), int(window or 0), cache.page_tokens, kp.shape[0], _ptr(status),
+                     self._stream())
+        if code != 0:
+            raise RuntimeError(f"prompt attention refused or failed with code {code}")
 
     def _attn_scratch(self, floats: int):
         if self._attn_ws is None or self._attn_ws.numel() < floats:

@@ -2,6 +2,7 @@
 import math
 import types
 
+import numpy as np
 import pytest
 import torch
 
@@ -173,6 +174,50 @@ def test_gemm_tc_swiglu(ops16, m, inter, k):
     g = x.double() @ gate.double().t()
     u = x.double() @ up.double().t()
     _close(out, g / (1 + torch.exp(-g)) * u, 2 ** -7, 1e-4, "tc swiglu")
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 264, 64), (65, 520, 200), (100, 1000, 4096), (129, 256, 1024),
+                                   (200, 24576 // 8, 512), (256, 300, 72)])
+def test_gemm_tc_token_major_below_the_prompt_sizes(ops16, m, n, k):
+    """The token-major form (128 tokens x 256 weight rows per tile) forced for 256 tokens or
+    fewer: every epilogue against float64, and the refusal of a folded norm."""
+    fast = ops16.fast
+    x = _randn((m, k), 51, torch.bfloat16)
+    w = _randn((n, k), 52, torch.bfloat16, scale=0.05)
+    want = x.double() @ w.double().t()
+    atol32 = 2e-6 * math.sqrt(k) * 4
+    out = torch.empty((m, n), device=DEV, dtype=torch.bfloat16)
+    fast._gemm(x, w, out, 0, None, n, token_major=True)
+    _close(out, want, 2 ** -8, atol32, f"token-major bf16 out m{m} n{n} k{k}")
+    out32 = torch.empty((m, n), device=DEV)
+    fast._gemm(x, w, out32, 1, None, n, token_major=True)
+    _close(out32, want, 1e-5, atol32, "token-major fp32 out")
+    res = _randn((m, n), 53)
+    hidden = res.clone()
+    fast._gemm(x, w, hidden, 2, hidden, n, token_major=True)
+    _close(hidden, want + res.double(), 1e-5, atol32, "token-major residual in place")
+    inter = (n // 32) * 16
+    gate, up = w[:inter].contiguous(), w[inter:2 * inter].contiguous()
+    gu = ops16.prepare_gate_up(gate, up)
+    act = torch.empty((m, inter), device=DEV, dtype=torch.bfloat16)
+    fast._gemm(x, gu.weight, act, 3, None, 2 * inter, token_major=True)
+    g = x.double() @ gate.double().t()
+    u = x.double() @ up.double().t()
+    _close(act, g / (1 + torch.exp(-g)) * u, 2 ** -7, 1e-4, "token-major swiglu")
+    xn = torch.empty((m, n), device=DEV, dtype=torch.bfloat16)
+    ss = torch.empty((fast.norm_parts(m, n), m), device=DEV)
+    with pytest.raises(RuntimeError, match="refused"):
+        fast._gemm(x, w, hidden, 2, hidden, n, token_major=True, norm_out=(xn, torch.ones(n, device=DEV), ss))
+
+
+def test_the_dispatcher_picks_the_token_major_form_only_where_its_tiles_fill_the_device(ops16):
+    fast = ops16.fast
+    sms = fast.sm_count
+    assert fast.token_major(257, 64) and fast.token_major(2048, 4096)
+    assert not fast.token_major(64, 256 * sms)                       # decode-sized: always swapped
+    assert fast.token_major(128, 256 * sms) and fast.token_major(200, 128 * sms)
+    assert not fast.token_major(128, 256 * (sms // 2))               # too few tiles: swapped, split along K
+    assert not fast.token_major(128, 256 * 3 * sms)                  # many tiles (an output head): swapped
 
 
 @pytest.mark.parametrize("m,n,k,splits,full", [(8, 128 * 7, 1024, 3, 4), (40, 128 * 5 + 17, 2048, 4, 2),
@@ -508,7 +553,7 @@ def test_sample_temperature_matches_host(ops32, vocab):
 
 
 # -- tiled bf16 attention: prompt portions / mixed batches, and split-KV decode ------------------
-def _tiled_case(ops16, n_q, n_kv, d, pt, window, seq_lens, starts, seed):
+def _tiled_case(ops16, n_q, n_kv, d, pt, window, seq_lens, starts, seed, leading_decode_rows=None):
     positions, seqs, q_start = [], [], [0]
     for s, (l, st) in enumerate(zip(seq_lens, starts)):
         positions += list(range(st, l))
@@ -545,6 +590,11 @@ def _tiled_case(ops16, n_q, n_kv, d, pt, window, seq_lens, starts, seed):
     ctx.max_q_len = max(l - st for l, st in zip(seq_lens, starts))
     ctx.max_ctx_len = max(seq_lens)
     ctx.decode_only = ctx.max_q_len == 1
+    ctx.fixed_shapes = False
+    ctx.q_lens = np.array([l - st for l, st in zip(seq_lens, starts)])
+    ctx.ctx_lens = np.array(seq_lens)
+    if leading_decode_rows is not None:
+        assert ops16.fast.leading_decode_rows(ctx) == leading_decode_rows
     scale = 1 / math.sqrt(d)
     assert ops16.fast.attention(ctx, qkv, out, n_q, n_kv, d, scale, window, cache)
     assert ctx.status[0].item() == 0
@@ -562,6 +612,21 @@ def test_attention_prefill_tiled(ops16, n_q, n_kv, d, pt, window):
     # whole prompts, a continued portion, a 1-token row and a 2-token portion in one batch
     _tiled_case(ops16, n_q, n_kv, d, pt, window, seq_lens=[150, 3, 131, 70, 64], starts=[0, 0, 100, 69, 62],
                 seed=3)
+
+
+@pytest.mark.parametrize("n_q,n_kv,d,pt,window", [(8, 2, 128, 16, None), (6, 3, 32, 8, None), (10, 2, 64, 16, 90),
+                                                  (32, 8, 128, 16, None)])
+def test_attention_mixed_step_divided_between_the_decode_and_the_prompt_kernel(ops16, n_q, n_kv, d, pt, window):
+    """A mixed step whose first sequences bring one token each: those rows run on the decode
+    kernel and the rest on the prompt kernel, each over its own slice of the step's tables; and
+    the same batch through the prompt kernel alone."""
+    kw = dict(seq_lens=[300, 65, 1000, 150, 131, 40], starts=[299, 64, 999, 0, 100, 39], seed=9)
+    _tiled_case(ops16, n_q, n_kv, d, pt, window, leading_decode_rows=3, **kw)
+    ops16.fast.divide_mixed_steps = False
+    try:
+        _tiled_case(ops16, n_q, n_kv, d, pt, window, leading_decode_rows=0, **kw)
+    finally:
+        ops16.fast.divide_mixed_steps = True
 
 
 @pytest.mark.parametrize("n_q,n_kv,d,pt,window", [(10, 2, 64, 16, None), (28, 4, 128, 8, 200), (3, 1, 128, 32, None),

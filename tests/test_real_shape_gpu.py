@@ -44,12 +44,15 @@ def test_real_layer_sizes_under_cuts(setup, dtype, rtol, atol_scale, fusions):
     fall back to."""
     from leone_b200.engine.engine import Engine
     config, spec, tensors = setup
-    reqs = {"a": replay.random_tokens(151936, 300, 1), "b": replay.random_tokens(151936, 45, 2)}
+    # 300 tokens: the prompt-sized kernels; 45: the decode-sized ones; 150: between them, where the
+    # wide gate/up product takes the token-major form and the others the swapped one
+    reqs = {"a": replay.random_tokens(151936, 300, 1), "b": replay.random_tokens(151936, 45, 2),
+            "c": replay.random_tokens(151936, 150, 3)}
     want = {r: _plain_logits(tensors, t, dtype == "bfloat16").cpu() for r, t in reqs.items()}
 
     class Plain:
         def logits(self, tokens):
-            return want["a" if len(tokens) == 300 else "b"]
+            return want[{300: "a", 45: "b", 150: "c"}[len(tokens)]]
 
     traces = {"whole": replay.trace_whole(reqs), "tail": replay.trace_decode_tail(reqs, tail=8),
               "mixed": replay.trace_mixed(reqs, seed=1)}
@@ -62,7 +65,7 @@ def test_real_layer_sizes_under_cuts(setup, dtype, rtol, atol_scale, fusions):
                         max_requests=4, max_batch_tokens=320)
         if not fusions:
             fast = engine.ops.fast
-            fast.use_clusters = fast.fuse_norm = fast.fuse_decode = fast.use_tc_attention = False
+            fast.use_clusters = fast.fuse_norm = fast.fuse_decode = fast.use_tc_attention = fast.use_token_major = False
         out = replay.run_trace_engine(engine, steps)
         replay.compare(steps, out, Plain(), reqs, rtol, atol_scale, f"8B layer sizes {dtype} {name} fusions={fusions}")
         del engine

@@ -45,8 +45,11 @@ class DecayMixer(Mixer):
 
 
 class RoutedFeedForward(FeedForward):
-    """Each token goes to the ``top_k`` experts with the largest router logits (fp32), weighted by
-    the softmax over those logits; an expert is ``W_out relu(W_in x)``.  hidden += the mixture."""
+    """Each token goes to the ``top_k`` experts with the largest router logits (fp32).  An
+    expert's share is its logit's lead over the best expert left out, normalised, so that an
+    expert enters the chosen set with share zero and the output is continuous in the input
+    (rounding cannot flip a near-tie into a different result).  An expert is
+    ``W_out relu(W_in x)``; hidden += the mixture."""
 
     def __init__(self, params, rt):
         super().__init__(params, rt)
@@ -69,8 +72,10 @@ class RoutedFeedForward(FeedForward):
     def forward(self, ctx, x, hidden):
         xf = x.float()
         logits = xf @ self.w["router.weight"].float().t()
-        top, chosen = logits.topk(self.top_k, dim=-1)
-        share = torch.softmax(top, dim=-1)
+        top, chosen = logits.topk(self.top_k + 1, dim=-1)
+        lead = top[:, :self.top_k] - top[:, self.top_k:]
+        share = lead / (lead.sum(dim=-1, keepdim=True) + 1e-6)
+        chosen = chosen[:, :self.top_k]
         for e in range(self.experts):
             rows, which = (chosen == e).nonzero(as_tuple=True)
             if rows.numel() == 0:
@@ -182,9 +187,10 @@ def plain_logits(cfg: ToyConfig, w, tokens):
         logits = x @ w[p + "router.weight"].t()
         out = torch.zeros_like(x)
         for t in range(t_len):
-            top, chosen = logits[t].topk(2)
-            share = torch.softmax(top, dim=-1)
-            for s, e in zip(share, chosen.tolist()):
+            top, chosen = logits[t].topk(3)
+            lead = top[:2] - top[2]
+            share = lead / (lead.sum() + 1e-6)
+            for s, e in zip(share, chosen[:2].tolist()):
                 inner = torch.relu(w[f"{p}experts.{e}.in.weight"] @ x[t])
                 out[t] += s * (w[f"{p}experts.{e}.out.weight"] @ inner)
         return out
