@@ -18,7 +18,7 @@ if ROOT not in sys.path:
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=256, help="decode steps timed (the baseline workload decodes 256)")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="leone_b200", choices=["leone_b200", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")

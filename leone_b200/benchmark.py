@@ -156,7 +156,7 @@ def time_decode(engine, batch: int, context: int, steps: int, warmup: int, seed:
                 launches=graph.launches_per_step * steps)
 
 
-def time_prefill(engine, tokens: int, reps: int = 3, seed: int = 99):
+def time_prefill(engine, tokens: int, reps: int = 5, seed: int = 99):
     vocab = engine.spec.vocab_size
     times = []
     for rep in range(reps + 1):

@@ -230,7 +230,7 @@ def build_parser() -> argparse.ArgumentParser:
     r.add_argument("--store-dtype", choices=["float32", "bfloat16"], default="bfloat16")
     sub.add_parser("replay", help="same options as bin/trace_run", add_help=False)
     b = sub.add_parser("bench", help="decode/prefill throughput of a Qwen3-8B-shaped model")
-    b.add_argument("--steps", type=int, default=64)
+    b.add_argument("--steps", type=int, default=256)
     b.add_argument("--warmup", type=int, default=3)
     b.add_argument("--layers", type=int, default=None)
     b.add_argument("--batch", type=int, default=8)
