@@ -155,13 +155,84 @@ __device__ __forceinline__ void fetch_residual(const GemmParams& p, float (&r)[N
   }
 }
 
+// Token-major form, splits summed inside a cluster: 32 finished sums of token row m for the weight
+// rows n .. n+31 (n a multiple of 32) go out through the product's epilogue.  No folded norm.
+__device__ __forceinline__ void finish_token_major32(const GemmParams& p, float (&v)[32], int m, int n) {
+  if (m >= p.M || n >= p.N) return;
+  const bool vec_ok = (p.ldc & 7) == 0;
+  if (p.epilogue == 3) {                                 // 16 gate columns, then their 16 up columns
+    __nv_bfloat16* orow = (__nv_bfloat16*)p.out + (size_t)m * p.ldc;
+    const int col = n >> 1;
+    uint32_t packed[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float a = v[2 * j] / (1.f + expf(-v[2 * j])) * v[16 + 2 * j];
+      const float b = v[2 * j + 1] / (1.f + expf(-v[2 * j + 1])) * v[16 + 2 * j + 1];
+      __nv_bfloat162 v2 = __floats2bfloat162_rn(a, b);
+      packed[j] = *reinterpret_cast<uint32_t*>(&v2);
+    }
+    if (vec_ok) {
+      uint4* dst = reinterpret_cast<uint4*>(orow + col);
+      dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) *reinterpret_cast<uint32_t*>(orow + col + 2 * j) = packed[j];
+    }
+    return;
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int nn = n + 16 * h;
+    if (nn >= p.N) break;
+    float* vv = v + 16 * h;
+    const size_t o = (size_t)m * p.ldc + nn;
+    const bool full = nn + 16 <= p.N && vec_ok;
+    if (p.epilogue == 0) {
+      __nv_bfloat16* dst = (__nv_bfloat16*)p.out + o;
+      if (full) {
+        uint32_t packed[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          __nv_bfloat162 v2 = __floats2bfloat162_rn(vv[2 * j], vv[2 * j + 1]);
+          packed[j] = *reinterpret_cast<uint32_t*>(&v2);
+        }
+        reinterpret_cast<uint4*>(dst)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        reinterpret_cast<uint4*>(dst)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+      } else {
+        for (int j = 0; j < 16 && nn + j < p.N; ++j) dst[j] = __float2bfloat16_rn(vv[j]);
+      }
+    } else {
+      float* dst = (float*)p.out + o;
+      if (full) {
+        if (p.epilogue == 2) {
+          const float4* res = reinterpret_cast<const float4*>(p.residual + o);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float4 r = res[j];
+            vv[4 * j] += r.x; vv[4 * j + 1] += r.y; vv[4 * j + 2] += r.z; vv[4 * j + 3] += r.w;
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          reinterpret_cast<float4*>(dst)[j] = make_float4(vv[4 * j], vv[4 * j + 1], vv[4 * j + 2], vv[4 * j + 3]);
+      } else {
+        for (int j = 0; j < 16 && nn + j < p.N; ++j) {
+          if (p.epilogue == 2) vv[j] += p.residual[o + j];
+          dst[j] = vv[j];
+        }
+      }
+    }
+  }
+}
+
 // kSwap: weights on the MMA's M side (tile 128), tokens on its N side (tile BN).
 // !kSwap: tokens on the M side (tile 128), weights on the N side (tile BN); no split-K.
-// kCluster (swapped only): the `splits` blocks of a tile form a thread-block cluster, one unit
-// per block; every block leaves its fp32 partial tile in its own shared memory, then the tile's
-// rows are dealt to the blocks, each of which adds its rows' partials in rank order through
-// distributed shared memory and runs the epilogue on them.  No workspace, no counters, no
-// round trip through global memory.
+// kCluster: the `splits` blocks of a tile form a thread-block cluster, one unit per block; every
+// block leaves its fp32 partial tile in its own shared memory, then the tile's rows are dealt to
+// the blocks, each of which adds its rows' partials in rank order through distributed shared
+// memory and runs the epilogue on them.  No workspace, no counters, no round trip through global
+// memory.  In the token-major form (rows = tokens) without a folded norm.
 template <int BN, bool kSwap, bool kCluster>
 __global__ void __launch_bounds__(kGemmThreads, GemmCfg<BN>::kBlocksPerSm)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
@@ -343,6 +414,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       if (ep_tid == 0) stamp(p, 5);                        // accumulator of the (latest) unit complete
       const int row_local = quarter * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
+      if constexpr (kCluster) {
+        // this block's partial tile goes to its own shared memory, [accumulator column][row];
+        // the stages are free: the accumulator is complete, so every MMA has read its operands
+        static_assert(kStages * Cfg::kStageBytes >= BN * kTileW * 4, "partial tile must fit in the stages");
+        float* part = reinterpret_cast<float*>(aligned);
+        for (int c = 0; c < BN; c += 16) {
+          float v[16];
+          tmem_ld16(taddr + c, v);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) part[(c + j) * kTileW + row_local] = v[j];
+        }
+        break;                                           // one unit per block in this mode
+      }
       if (!kSwap) {
         // this thread owns token row m and walks the tile's weight rows 16 at a time
         const int m = m_tile * kTileW + row_local;
@@ -506,19 +590,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
       const int n = n_tile * kTileW + row_local;
       const int m0 = m_tile * BN;
-      if constexpr (kCluster) {
-        // this block's partial tile goes to its own shared memory, [token column][weight row];
-        // the stages are free: the accumulator is complete, so every MMA has read its operands
-        static_assert(kStages * Cfg::kStageBytes >= BN * kTileW * 4, "partial tile must fit in the stages");
-        float* part = reinterpret_cast<float*>(aligned);
-        for (int c = 0; c < BN; c += 16) {
-          float v[16];
-          tmem_ld16(taddr + c, v);
-#pragma unroll
-          for (int j = 0; j < 16; ++j) part[(c + j) * kTileW + row_local] = v[j];
-        }
-        break;                                           // one unit per block in this mode
-      }
       bool do_epilogue = true;
       const int split_tile = tile - p.full_tiles;        // index among the split tiles
       if (nsplit > 1) {
@@ -597,6 +668,46 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // In a chunk, lane = row and each epilogue warp owns a quarter of the token columns.
     __syncwarp();
     cluster_sync_all();                                  // all partial tiles are in place
+    if constexpr (!kSwap) {
+      // token-major: the rows are tokens; in a chunk lane = token row, and each epilogue warp
+      // owns a quarter of the tile's weight rows, 32 at a time (a gate/up group for SwiGLU)
+      if (warp >= 2 && blockIdx.x < total) {
+        const Unit un = unit_of(blockIdx.x, p);
+        const int m_tile = un.tile % m_tiles, n_tile = un.tile / m_tiles;
+        constexpr int kColsPerWarp = BN / 4;
+        static_assert(kColsPerWarp % 32 == 0, "a warp's share of the weight rows is whole gate/up groups");
+        const int rank = (int)cluster_ctarank();
+        for (int ch = rank; ch < kTileW / 32; ch += un.nsplit) {
+          const int row_local = ch * 32 + lane;
+          const int m = m_tile * kTileW + row_local;
+          const uint32_t mine = tiles_base + row_local * 4;
+          for (int c = (warp & 3) * kColsPerWarp; c < (warp & 3) * kColsPerWarp + kColsPerWarp; c += 32) {
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = 0.f;
+            for (int s0 = 0; s0 < un.nsplit; s0 += 2) {  // two ranks' loads in flight together
+              float t[2][32];
+#pragma unroll
+              for (int u = 0; u < 2; ++u) {
+                if (s0 + u < un.nsplit) {
+                  const uint32_t src = cluster_map(mine, s0 + u) + c * kTileW * 4;
+#pragma unroll
+                  for (int j = 0; j < 32; ++j) t[u][j] = cluster_ld_f32(src + j * kTileW * 4);
+                }
+              }
+#pragma unroll
+              for (int u = 0; u < 2; ++u) {              // rank order
+                if (s0 + u < un.nsplit) {
+#pragma unroll
+                  for (int j = 0; j < 32; ++j) v[j] += t[u][j];
+                }
+              }
+            }
+            finish_token_major32(p, v, m, n_tile * BN + c);
+          }
+        }
+      }
+    } else
     if (warp >= 2 && blockIdx.x < total) {
       const Unit un = unit_of(blockIdx.x, p);
       const int m_tile = un.tile % m_tiles, n_tile = un.tile / m_tiles;
@@ -685,10 +796,10 @@ int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& 
 
 // How many clusters of `splits` blocks of the swapped kernel for token tile BN can be resident
 // at once (0: this cluster size cannot be launched).
-template <int BN>
+template <int BN, bool kSwap = true>
 int cluster_capacity(int splits) {
   using Cfg = GemmCfg<BN>;
-  cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, true, true>,
+  cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, kSwap, true>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
   if (e != cudaSuccess) { cudaGetLastError(); return 0; }
   cudaLaunchConfig_t cfg = {};
@@ -703,7 +814,7 @@ int cluster_capacity(int splits) {
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
   int clusters = 0;
-  e = cudaOccupancyMaxActiveClusters(&clusters, gemm_tc_kernel<BN, true, true>, &cfg);
+  e = cudaOccupancyMaxActiveClusters(&clusters, gemm_tc_kernel<BN, kSwap, true>, &cfg);
   if (e != cudaSuccess) { cudaGetLastError(); return 0; }
   return clusters;
 }
@@ -771,6 +882,12 @@ extern "C" int leone_gemm_tc_cluster_capacity(int m, int splits) {
   }
 }
 
+// The same for the token-major form (any number of tokens).
+extern "C" int leone_gemm_tc_cluster_capacity_token_major(int splits) {
+  if (splits < 2 || splits > 8) return 0;
+  return cluster_capacity<256, false>(splits);
+}
+
 // x: [m, k] bf16 (row stride ldx), w: [n, k] bf16 (row stride ldw), out: [m, n] (row stride ldc).
 // epilogue 0: bf16 out; 1: fp32 out; 2: fp32 out = acc + residual (same layout as out);
 // 3: w holds interleaved gate/up rows, out is bf16 [m, n/2] = silu(gate) * up.
@@ -787,9 +904,10 @@ extern "C" int leone_gemm_tc_cluster_capacity(int m, int splits) {
 // distributed shared memory (needs full_tiles == 0, 2 <= splits <= 8, at most 256 tokens, and
 // tiles * splits blocks resident at once: see leone_gemm_tc_cluster_capacity); workspace and
 // counters are not used.
-// token_major != 0: the token-major form (128 tokens x 256 weight rows per tile, never split)
-// also for 256 tokens or fewer, where it reads the token operand less often than the swapped
-// form does; the norm arguments must then be null.
+// token_major != 0: the token-major form (128 tokens x 256 weight rows per tile) also for 256
+// tokens or fewer, where it reads the token operand less often than the swapped form does; the
+// norm arguments must then be null.  The token-major form is split along K only with cluster
+// != 0 (same conditions as above, for any number of tokens; no norm arguments).
 extern "C" int leone_gemm_tc(const void* x, const void* w, void* out, const float* residual, int m,
                              int n, int k, int ldx, int ldw, int ldc, int epilogue, int splits,
                              int full_tiles, float* workspace, int* counters, int* status,
@@ -803,8 +921,8 @@ extern "C" int leone_gemm_tc(const void* x, const void* w, void* out, const floa
   if (epilogue == 3 && (n % 32) != 0) return kRefusedSize;
   const int k_blocks = (k + kTileK - 1) / kTileK;
   const bool swap = m <= 256 && !token_major;
-  if (!swap) splits = 1;
-  if (!swap && m <= 256 && (norm_out_x != nullptr || norm_in_ss != nullptr)) return kRefusedSize;
+  if (!swap && !cluster) splits = 1;
+  if (!swap && (m <= 256 || cluster) && (norm_out_x != nullptr || norm_in_ss != nullptr)) return kRefusedSize;
   if (splits > k_blocks) splits = k_blocks;
   // every split must own at least one k-block
   while (splits > 1 && (splits - 1) * ((k_blocks + splits - 1) / splits) >= k_blocks) --splits;
@@ -812,7 +930,7 @@ extern "C" int leone_gemm_tc(const void* x, const void* w, void* out, const floa
   if (norm_out_x != nullptr && ((epilogue != 1 && epilogue != 2) || norm_out_w == nullptr || norm_out_ss == nullptr))
     return kRefusedSize;
   if (norm_in_ss != nullptr && norm_in_parts < 1) return kRefusedSize;
-  if (cluster && (full_tiles != 0 || splits > 8 || m > 256)) return kRefusedSize;
+  if (cluster && (full_tiles != 0 || splits > 8)) return kRefusedSize;
   if (splits > 1 && !cluster && (workspace == nullptr || counters == nullptr)) return kRefusedSize;
   const int tiles = swap ? leone_gemm_tc_tiles(m, n) : leone_gemm_tc_tiles_token_major(m, n);
   if (splits == 1) full_tiles = tiles;
@@ -827,6 +945,7 @@ extern "C" int leone_gemm_tc(const void* x, const void* w, void* out, const floa
                g_gemm_trace, (__nv_bfloat16*)norm_out_x, norm_out_w, norm_out_ss, ld_norm_out, norm_in_ss,
                norm_in_parts, norm_eps};
   if (g_gemm_trace != nullptr) g_gemm_trace += g_gemm_trace_stride;
+  if (!swap && cluster) return launch_gemm<256, false, true>(mw, mx, p, sm_count, stream);
   if (!swap) return launch_gemm<256, false>(mw, mx, p, sm_count, stream);
   if (cluster) {
     switch (bn) {

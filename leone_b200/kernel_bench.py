@@ -69,10 +69,11 @@ def bench_gemm(ops, m, n, k, splits, epilogue, reps, warmup, flush, trace=False,
         out.zero_()
     state = {"i": 0}
     full_tiles = 0
-    if token_major is None:
-        token_major = splits is None and norm == "none" and fast.token_major(m, n)
-    if token_major:
-        splits, cluster = 1, False
+    if token_major is None and splits is None and norm == "none":
+        token_major, splits, full_tiles, cluster = fast.plan_product(m, n, k)
+    elif token_major:
+        splits = splits or 1
+        cluster = splits > 1
     elif splits is None:
         splits, full_tiles, cluster = fast.choose_splits(m, n, k)
 

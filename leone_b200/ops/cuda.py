@@ -172,7 +172,8 @@ class CudaOps:
         ``d.xn = bf16(out * d.weight)`` and the sums of ``out^2`` in ``d.ss``) or as the one
         after it (``linear(d.xn, ..., norm_in=d)`` scales its rows by the norm's factor)."""
         wt = w.weight
-        return (self.fast is not None and self.fast.fuses_norm(n_tokens) and wt.dtype == torch.bfloat16
+        return (self.fast is not None and self.fast.fuses_norm(n_tokens, wt.shape[0], wt.shape[1])
+                and wt.dtype == torch.bfloat16
                 and wt.shape[0] % 8 == 0 and wt.shape[1] % 8 == 0 and wt.stride(0) % 8 == 0
                 and wt.data_ptr() % 16 == 0)
 

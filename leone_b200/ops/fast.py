@@ -42,6 +42,7 @@ class FastKernels:
         self.mixed_decode_rows_from = 1
         self.use_token_major = os.environ.get("LEONE_NO_TOKEN_MAJOR", "0") != "1"
         self.token_major_from = 64         # tokens above which the token-major form is considered
+        self.token_major_split_from = 128  # .. and its split along K (up to 128 tokens the swapped form's split measured the same or better)
         self.token_major_fill = 0.6        # of the SMs that its tiles must fill
         self.force_decode_splits = int(os.environ.get("LEONE_DECODE_SPLITS", "0"))    # tuning aid
         # LEONE_NO_FUSED_DECODE=1 keeps q/k norm, rotation and cache write in their own kernel
@@ -146,6 +147,40 @@ class FastKernels:
         tiles = int(self.lib.leone_gemm_tc_tiles_token_major(m, n))
         return self.token_major_fill * self.sm_count <= tiles <= 2 * self.sm_count
 
+    def token_major_split(self, m: int, n: int, k: int) -> int:
+        """Splits along K of the token-major form, summed inside thread-block clusters (1: none).
+        A product whose token-major tiles fill at most half of the SMs (the narrow products of a
+        layer between 65 and about 600 tokens) is split so that tiles x splits blocks fill them;
+        a split keeps at least 8 k-blocks.  Such a product takes no folded norm."""
+        if not (self.use_clusters and self.use_token_major) or m <= self.token_major_split_from:
+            return 1
+        tiles = int(self.lib.leone_gemm_tc_tiles_token_major(m, n))
+        if tiles * 2 > self.sm_count:
+            return 1
+        k_blocks = -(-k // 64)
+        # all clusters must be resident at once: a cluster needs its blocks' SMs free in one GPC
+        # at the same moment, and a grid that needs a second round of clusters was measured at
+        # twice the time (the occupancy query's count of resident clusters is what holds)
+        for s in range(min(8, self.sm_count // tiles, self.max_cluster), 1, -1):
+            if k_blocks // s >= 8 and tiles <= self._token_major_capacity(s):
+                return s
+        return 1
+
+    def _token_major_capacity(self, splits: int) -> int:
+        key = ("token-major", splits)
+        if key not in self._cluster_capacity:
+            self._cluster_capacity[key] = int(self.lib.leone_gemm_tc_cluster_capacity_token_major(splits))
+        return self._cluster_capacity[key]
+
+    def plan_product(self, m: int, n: int, k: int):
+        """``(token_major, splits, full_tiles, cluster)`` for a product without a folded norm."""
+        s = self.token_major_split(m, n, k)
+        if s > 1:
+            return True, s, 0, True
+        if self.token_major(m, n):
+            return True, 1, 0, False
+        return (False, *self.choose_splits(m, n, k))
+
     def _gemm(self, x, w, out, epilogue, residual, n_rows, splits=None, full_tiles=0, cluster=False,
               norm_in=None, norm_out=None, token_major=None) -> bool:
         """``splits=None`` lets :meth:`choose_splits` decide; otherwise tiles from
@@ -157,10 +192,11 @@ class FastKernels:
         for the RMSNorm that follows it; ``norm_in=(ss, parts, eps)``: ``x`` is such an ``xn``
         and every output row is scaled by the norm's ``rsqrt(mean + eps)``."""
         m, k = x.shape
-        if token_major is None:
-            token_major = splits is None and norm_in is None and norm_out is None and self.token_major(m, n_rows)
-        if token_major:
-            splits, full_tiles, cluster = 1, 0, False
+        if token_major is None and splits is None and norm_in is None and norm_out is None:
+            token_major, splits, full_tiles, cluster = self.plan_product(m, n_rows, k)
+        token_major = bool(token_major) or m > 256
+        if token_major and not cluster:
+            splits, full_tiles = 1, 0
         elif splits is None:
             splits, full_tiles, cluster = self.choose_splits(m, n_rows, k)
         ws = ct = None
@@ -182,12 +218,15 @@ class FastKernels:
                                f"splits={splits} cluster={cluster} token_major={token_major}")
         return True
 
-    def fuses_norm(self, m: int) -> bool:
+    def fuses_norm(self, m: int, n: int = 0, k: int = 0) -> bool:
         """Whether the products of ``m`` tokens carry an RMSNorm between them: decode-sized steps
         (up to 32 tokens; from there to 256 the extra work in the two epilogues was measured to
         cost more than the norm kernel it replaces) and prompt-sized ones (over 256 tokens,
-        where a thread owns a token row and the sums are its own)."""
-        return self.use_tensor_cores and self.fuse_norm and (0 < m <= self.fuse_norm_tokens or m > 256)
+        where a thread owns a token row and the sums are its own).  With ``n`` and ``k``: whether
+        this ``[n x k]`` product does; one that is split in the token-major form does not."""
+        if not (self.use_tensor_cores and self.fuse_norm and (0 < m <= self.fuse_norm_tokens or m > 256)):
+            return False
+        return not (n and k and self.token_major_split(m, n, k) > 1)
 
     def norm_parts(self, m: int, n: int) -> int:
         return int(self.lib.leone_gemm_tc_norm_parts(m, n))

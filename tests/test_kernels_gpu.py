@@ -210,6 +210,58 @@ def test_gemm_tc_token_major_below_the_prompt_sizes(ops16, m, n, k):
         fast._gemm(x, w, hidden, 2, hidden, n, token_major=True, norm_out=(xn, torch.ones(n, device=DEV), ss))
 
 
+@pytest.mark.parametrize("m,n,k,splits", [(100, 520, 2048, 3), (300, 264, 1024, 2), (129, 256, 4096, 8),
+                                          (512, 1000, 640, 5), (65, 4096, 512, 4), (1, 300, 1032, 2),
+                                          (600, 768, 12288, 7)])
+def test_gemm_tc_token_major_cluster_split(ops16, m, n, k, splits):
+    """The token-major form with the splits of a tile as a thread-block cluster: every epilogue
+    against float64, the same bits on every run, and the refusal of a folded norm."""
+    fast = ops16.fast
+    assert fast._token_major_capacity(splits) > 0
+    x = _randn((m, k), 61, torch.bfloat16)
+    w = _randn((n, k), 62, torch.bfloat16, scale=0.05)
+    want = x.double() @ w.double().t()
+    atol32 = 2e-6 * math.sqrt(k) * 4
+    kw = dict(splits=splits, cluster=True, token_major=True)
+    out = torch.full((m, n), 9.0, device=DEV, dtype=torch.bfloat16)
+    fast._gemm(x, w, out, 0, None, n, **kw)
+    _close(out, want, 2 ** -8, atol32, f"token-major cluster bf16 out m{m} n{n} k{k} s{splits}")
+    out32 = torch.full((m, n), 9.0, device=DEV)
+    fast._gemm(x, w, out32, 1, None, n, **kw)
+    _close(out32, want, 1e-5, atol32, "token-major cluster fp32 out")
+    res = _randn((m, n), 63)
+    hidden = res.clone()
+    fast._gemm(x, w, hidden, 2, hidden, n, **kw)
+    _close(hidden, want + res.double(), 1e-5, atol32, "token-major cluster residual in place")
+    again = res.clone()
+    fast._gemm(x, w, again, 2, again, n, **kw)
+    assert torch.equal(hidden, again)
+    inter = (n // 32) * 16
+    gate, up = w[:inter].contiguous(), w[inter:2 * inter].contiguous()
+    gu = ops16.prepare_gate_up(gate, up)
+    act = torch.full((m, inter), 9.0, device=DEV, dtype=torch.bfloat16)
+    fast._gemm(x, gu.weight, act, 3, None, 2 * inter, **kw)
+    g = x.double() @ gate.double().t()
+    u = x.double() @ up.double().t()
+    _close(act, g / (1 + torch.exp(-g)) * u, 2 ** -7, 1e-4, "token-major cluster swiglu")
+    xn = torch.empty((m, n), device=DEV, dtype=torch.bfloat16)
+    ss = torch.empty((fast.norm_parts(m, n), m), device=DEV)
+    with pytest.raises(RuntimeError, match="refused"):
+        fast._gemm(x, w, hidden, 2, hidden, n, norm_out=(xn, torch.ones(n, device=DEV), ss), **kw)
+    torch.cuda.synchronize()
+
+
+def test_the_dispatcher_splits_narrow_products_in_the_token_major_form(ops16):
+    fast = ops16.fast
+    sms = fast.sm_count
+    assert fast.plan_product(8, 4096, 4096)[0] is False                     # decode-sized: swapped
+    tm, s, full, cluster = fast.plan_product(300, 4096, 4096)                # 3 x 16 tiles
+    assert tm and cluster and full == 0 and 2 <= s <= 8 and 48 * s <= sms
+    assert fast.plan_product(2048, 4096, 4096) == (True, 1, 0, False)        # fills the SMs unsplit
+    assert not fast.fuses_norm(300, 4096, 4096) and fast.fuses_norm(2048, 4096, 4096)
+    assert fast.plan_product(300, 4096, 256)[:2] == (True, 1)                # too few k-blocks to split
+
+
 def test_the_dispatcher_picks_the_token_major_form_only_where_its_tiles_fill_the_device(ops16):
     fast = ops16.fast
     sms = fast.sm_count
@@ -307,7 +359,7 @@ def test_gemm_tc_norm_between_products(ops16, m, n, k, splits, cluster):
     want = (xn.double() @ w2.double().t()) * rs
     exact = (h64 * g.double() * rs) @ w2.double().t()
     out = torch.empty((m, n2), device=DEV, dtype=torch.bfloat16)
-    for s2, cl in ((1, False), (2, True), (3, False)):
+    for s2, cl in ((1, False), (2, m <= 256), (3, False)):      # a prompt-sized product with a norm is never split
         fast._gemm(xn, w2, out, 0, None, n2, splits=s2, cluster=cl, norm_in=(ss, parts, eps))
         _close(out, want, 2 ** -8, 1e-3, f"the product after the norm, splits {s2}")
         _close(out, exact, 2 ** -5, 5e-2, "against the exact norm")
