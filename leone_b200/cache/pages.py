@@ -346,6 +346,26 @@ class CacheManager:
         """The step that wrote tokens up to ``new_len`` succeeded."""
         _check(self._lib.leone_cache_commit(self._h, c_longlong(self._id(rid)), c_longlong(new_len)))
 
+    def reserve_steps(self, rids: Sequence[Hashable], steps: int):
+        """Pages for ``steps`` more tokens of every request, all or nothing, in one call.
+        Returns ``(lengths, versions, slots, table_lens)``: each request's committed length,
+        table version and slot, and ``table_lens[g][i]``, the length of its block table in
+        group ``g`` after the reservation."""
+        n = len(rids)
+        lengths = np.empty(max(n, 1), dtype=np.int64)
+        versions = np.empty(max(n, 1), dtype=np.int64)
+        slots = np.empty(max(n, 1), dtype=np.int32)
+        table_lens = np.empty((len(self.groups), max(n, 1)), dtype=np.int32)
+        ll, ci = ctypes.POINTER(c_longlong), ctypes.POINTER(c_int)
+        _check(self._lib.leone_cache_reserve_steps(
+            self._h, n, _ll(self._id(r) for r in rids), c_longlong(int(steps)), lengths.ctypes.data_as(ll),
+            versions.ctypes.data_as(ll), slots.ctypes.data_as(ci), table_lens.ctypes.data_as(ci)))
+        return lengths[:n], versions[:n], slots[:n], table_lens[:, :n]
+
+    def commit_many(self, rids: Sequence[Hashable], new_lens: Sequence[int]) -> None:
+        _check(self._lib.leone_cache_commit_many(self._h, len(rids), _ll(self._id(r) for r in rids),
+                                                 _ll(int(v) for v in new_lens)))
+
     def rollback(self, rid: Hashable) -> None:
         """The step failed: return pages beyond the committed length."""
         _check(self._lib.leone_cache_truncate(self._h, c_longlong(self._id(rid)), c_longlong(-1)))

@@ -275,6 +275,40 @@ int leone_cache_commit(void* h, long long rid, long long new_len) {
   return kOk;
 }
 
+// Several requests at once, for the decode loop (one call a step instead of one a request).
+// reserve_steps: pages for `steps` more tokens of every request, all or nothing; then, for each
+// request, its committed length, its table version, its slot, and per group the length of its
+// block table after the reservation (table_lens[g * n + i]).
+int leone_cache_reserve_steps(void* h, int n, const long long* rids, long long steps, long long* lengths,
+                              long long* versions, int* slots, int* table_lens) {
+  Manager* m = static_cast<Manager*>(h);
+  if (steps < 0) return fail(kBadArgument, "a negative number of steps");
+  std::vector<long long> want(n);
+  for (int i = 0; i < n; ++i) {
+    Request* rc = m->find(rids[i]);
+    if (!rc) return unknown(rids[i]);
+    lengths[i] = rc->committed;
+    want[i] = rc->committed + steps;
+  }
+  const int r = leone_cache_reserve(h, n, rids, want.data());
+  if (r != kOk) return r;
+  for (int i = 0; i < n; ++i) {
+    const Request* rc = m->find(rids[i]);
+    versions[i] = rc->version;
+    slots[i] = rc->slot;
+    for (size_t g = 0; g < m->groups.size(); ++g)
+      table_lens[g * n + i] = (int)m->groups[g].tables[rids[i]].size();
+  }
+  return kOk;
+}
+int leone_cache_commit_many(void* h, int n, const long long* rids, const long long* new_lens) {
+  for (int i = 0; i < n; ++i) {
+    const int r = leone_cache_commit(h, rids[i], new_lens[i]);
+    if (r != kOk) return r;
+  }
+  return kOk;
+}
+
 // Drop everything past `length` tokens (crates/leone/src/kv.rs:929-950); length < 0: roll
 // back to the committed length (the step failed).
 int leone_cache_truncate(void* h, long long rid, long long length) {
@@ -678,6 +712,17 @@ int leone_sched_emitted(void* h, long long rid, int is_eos) {
   else if (r->n_tokens > p->max_positions) reason = kMaxPositions;
   if (reason != kNotFinished) p->retire(rid, r, false);
   return reason;
+}
+
+// One decode step's tokens for n running requests: each has one more token in the cache and has
+// emitted one (is_eos[i]: it was the request's stop token).  reasons[i] as leone_sched_emitted.
+int leone_sched_decoded(void* h, int n, const long long* rids, const int* is_eos, int* reasons) {
+  for (int i = 0; i < n; ++i) {
+    const int r = leone_sched_computed(h, rids[i], 1);
+    if (r != kOk) return r;
+    reasons[i] = leone_sched_emitted(h, rids[i], is_eos[i]);
+  }
+  return kOk;
 }
 
 // The youngest running request other than `keep` (-1: none kept) goes back to the front of the

@@ -50,6 +50,7 @@ class DecodeGraph:
         self.graph = None
         self._filled_rids = None           # what fill() last wrote into the host copy
         self._filled_pages = [[0] * batch for _ in engine.cache.groups]
+        self._filled_sampling = None
         self.launches_per_step = 0
         self.stream = torch.cuda.Stream(device=dev)
 
@@ -82,10 +83,13 @@ class DecodeGraph:
         e.ops.decode_advance(self.ctx.token_ids, self.ctx.positions, self.ctx.ctx_len,
                              self.sample_dev[2 * b:3 * b], self.sampled, self.history, self.counter)
 
-    def fill(self, rids: Sequence[Hashable], last_tokens: Sequence[int], lengths: Sequence[int], params):
+    def fill(self, rids: Sequence[Hashable], last_tokens: Sequence[int], lengths: Sequence[int], params,
+             versions=None, slots=None, table_lens=None):
         """Host → device: this quantum's starting state.  The pinned host copy keeps what the
         last call wrote, so for the same requests in the same rows only what changed is
-        rewritten: tokens, lengths, and the block-table entries of pages taken since."""
+        rewritten: tokens, lengths, and the block-table entries of pages taken since.
+        ``versions``, ``slots`` and ``table_lens`` (``[group][request]``) are what
+        ``CacheManager.reserve_steps`` returned; without them the cache is asked."""
         e = self.engine
         b = self.batch
         host = self.meta_host.numpy()
@@ -98,18 +102,21 @@ class DecodeGraph:
         put("token_ids", np.asarray(last_tokens, dtype=np.int32))
         put("positions", lengths)
         put("ctx_len", lengths + 1)
-        key = tuple((r, e.cache.table_version(r)) for r in rids)
+        if versions is None:
+            versions = [e.cache.table_version(r) for r in rids]
+        key = (tuple(rids), tuple(int(v) for v in versions))
         same = key == self._filled_rids
         if not same:
             put("seq_of_token", np.arange(b, dtype=np.int32))
             put("q_start", np.arange(b + 1, dtype=np.int32))
-            put("slot_ids", np.asarray([e.cache.slot(r) for r in rids], dtype=np.int32))
+            put("slot_ids", np.asarray(slots if slots is not None else [e.cache.slot(r) for r in rids],
+                                       dtype=np.int32))
             put("logit_rows", np.arange(b, dtype=np.int32))
         for gi, (g, w, (o, shape)) in enumerate(zip(e.cache.groups, self.widths, self.bt_offsets)):
             view = host[o:o + shape[0] * shape[1]].reshape(shape)
             windowed = g.spec.kind == "window"
             for i, r in enumerate(rids):
-                n = g.tables.length(r)
+                n = int(table_lens[gi][i]) if table_lens is not None else g.tables.length(r)
                 if n > w:
                     raise ValueError(f"block table needs {n} columns, only {w} given")
                 done = 0 if (not same or windowed) else self._filled_pages[gi][i]
@@ -120,8 +127,11 @@ class DecodeGraph:
                 self._filled_pages[gi][i] = n
         self._filled_rids = key
         sh = self.sample_host.numpy()
-        self.sample_host[:b].view(torch.float32).numpy()[:b] = np.array([p.temperature for p in params], dtype=np.float32)
-        sh[b:2 * b] = np.array([p.seed & 0xFFFF_FFFF_FFFF_FFFF for p in params], dtype=np.uint64).view(np.int64)
+        sampling = [(p.temperature, p.seed) for p in params]
+        if not same or sampling != self._filled_sampling:
+            self.sample_host[:b].view(torch.float32).numpy()[:b] = np.array([t for t, _ in sampling], dtype=np.float32)
+            sh[b:2 * b] = np.array([s_ & 0xFFFF_FFFF_FFFF_FFFF for _, s_ in sampling], dtype=np.uint64).view(np.int64)
+            self._filled_sampling = sampling
         sh[2 * b:3 * b] = lengths      # position of the token being fed
         self.meta.copy_(self.meta_host, non_blocking=True)
         self.sample_dev.copy_(self.sample_host, non_blocking=True)

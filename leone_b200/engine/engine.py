@@ -293,12 +293,11 @@ class Engine:
         (:class:`OutOfPages` leaves everything as it was); lengths advance by ``steps``.
         """
         rids = list(rids)
-        lengths = [self.cache.length(r) for r in rids]
         if steps <= 0 or not rids:
             return []
-        if max(lengths) + steps > self.spec.max_positions:
-            raise ValueError("decode_steps would run past the model's positions")
         if not (use_graph and self.device.type == "cuda") or steps > 64:
+            if max(self.cache.length(r) for r in rids) + steps > self.spec.max_positions:
+                raise ValueError("decode_steps would run past the model's positions")
             out = []
             toks = list(last_tokens)
             for _ in range(steps):
@@ -306,24 +305,27 @@ class Engine:
                 toks = self.sample(logits, params, [self.cache.length(r) - 1 for r in rids])
                 out.append(toks)
             return out
-        self.cache.reserve({r: l + steps for r, l in zip(rids, lengths)})
+        # one call: pages for all the steps, and what the graph's buffers need to know
+        lengths, versions, slots, table_lens = self.cache.reserve_steps(rids, steps)
         try:
+            if int(lengths.max()) + steps > self.spec.max_positions:
+                raise ValueError("decode_steps would run past the model's positions")
             graph = self._decode_graphs.get(len(rids))
+            state = dict(versions=versions, slots=slots, table_lens=table_lens)
             if graph is None:
                 from .decode_graph import DecodeGraph
                 graph = DecodeGraph(self, len(rids))
                 # capture needs valid tables: fill first, then warm up and capture on them
-                graph.fill(rids, last_tokens, lengths, params)
+                graph.fill(rids, last_tokens, lengths, params, **state)
                 graph.capture()
                 self._decode_graphs[len(rids)] = graph
-            graph.fill(rids, last_tokens, lengths, params)
+            graph.fill(rids, last_tokens, lengths, params, **state)
             tokens = graph.run(steps)       # also reads and checks the status word
         except Exception:
             for r in rids:
                 self.cache.rollback(r)
             raise
-        for r, l in zip(rids, lengths):
-            self.cache.commit(r, l + steps)
+        self.cache.commit_many(rids, lengths + steps)
         self.steps_run += steps
         return tokens.tolist()
 

@@ -308,18 +308,33 @@ class Scheduler:
         steps = self.engine.decode_steps([r.rid for r in reqs], [r.tokens[-1] for r in reqs],
                                          [r.sampling for r in reqs], q)
         outputs: List[StepOutput] = []
-        done = set()
+        live = list(range(len(reqs)))                   # rows whose request has not ended
         for row in steps:
-            for req, tok in zip(reqs, row):
-                if req.rid in done:
-                    continue
-                self._lib.leone_sched_computed(self._h, c_longlong(req.key), c_longlong(1))
+            n = len(live)
+            toks = [int(row[i]) for i in live]
+            is_eos = (c_int * n)(*[int(reqs[i].eos_token_id is not None and t == reqs[i].eos_token_id)
+                                   for i, t in zip(live, toks)])
+            reasons = (c_int * n)()
+            code = self._lib.leone_sched_decoded(self._h, n, (c_longlong * n)(*[reqs[i].key for i in live]),
+                                                 is_eos, reasons)       # the step's bookkeeping in one call
+            if code != 0:
+                raise RuntimeError(self._lib.leone_host_last_error().decode())
+            still = []
+            for i, tok, code in zip(live, toks, reasons):
+                req = reqs[i]
                 req.computed += 1
-                self._decode_tokens += 1
-                reason = self._emitted(req, int(tok))
-                if reason:
-                    done.add(req.rid)
-                outputs.append(StepOutput(req.rid, int(tok), reason is not None, reason))
+                req.generated.append(tok)
+                req.tokens.append(tok)
+                reason = None
+                if code > 0:
+                    self.engine.close(req.rid)
+                    req.state, req.finish_reason, req.reserved_pages = "finished", _FINISH[code], 0
+                    reason = req.finish_reason
+                else:
+                    still.append(i)
+                outputs.append(StepOutput(req.rid, tok, reason is not None, reason))
+            self._decode_tokens += n
+            live = still
         self._steps += q
         self._max_batch_tokens_seen = max(self._max_batch_tokens_seen, len(reqs))
         return outputs

@@ -227,6 +227,24 @@ def test_the_native_manager_and_the_plain_model_agree_call_by_call(seed):
                         n = n - (1 if rng.random() < 0.1 and n > live[r] + 1 else 0)    # fewer than reserved
                         if _same_error(lambda: a.commit(r, n), lambda: b.commit(r, n)) is None:
                             live[r] = n
+        elif action < 0.75 and live:
+            # the decode loop's calls: several requests, the same number of steps, one call each way
+            picked = rng.sample(sorted(live), rng.randint(1, len(live)))
+            steps = rng.randint(1, 6)
+            got = []
+            kind = _same_error(lambda: got.append(a.reserve_steps(picked, steps)),
+                               lambda: b.reserve({r: live[r] + steps for r in picked}))
+            if kind is None:
+                lengths, versions, slots, table_lens = got[0]
+                assert lengths.tolist() == [live[r] for r in picked]
+                assert versions.tolist() == [b.table_version(r) for r in picked]
+                assert slots.tolist() == [b.slot(r) for r in picked]
+                for gi, gb in enumerate(b.groups):
+                    assert table_lens[gi].tolist() == [len(gb.tables[r]) for r in picked]
+                a.commit_many(picked, [live[r] + steps for r in picked])
+                for r in picked:
+                    b.commit(r, live[r] + steps)
+                    live[r] += steps
         elif action < 0.8 and live:
             rid = rng.choice(sorted(live))
             to = rng.randint(0, live[rid] + 2)

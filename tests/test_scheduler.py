@@ -53,6 +53,27 @@ class FakeEngine:
         return [next_token(r) for r in rows]
 
 
+class FakeGraphEngine(FakeEngine):
+    """The same with the engine's ``decode_steps``: several decode steps without the scheduler
+    in between, pages for all of them taken first."""
+
+    def decode_steps(self, rids, last_tokens, params, steps):
+        wants = {r: self.cache.length(r) + steps for r in rids}
+        self.cache.reserve(wants)
+        rows = []
+        toks = list(last_tokens)
+        for _ in range(steps):
+            for r, t in zip(rids, toks):
+                self.seen[r] = self.seen[r] + [t]
+            toks = [next_token(self.seen[r]) for r in rids]
+            rows.append(toks)
+        for r in rids:
+            self.cache.commit(r, wants[r])
+        self.batches.append([(r, steps) for r in rids])
+        self.cache.check_invariants()
+        return rows
+
+
 def next_token(prefix):
     return (sum(prefix) * 31 + len(prefix) * 7) % 100
 
@@ -236,8 +257,10 @@ def test_the_native_planner_and_the_plain_scheduler_agree_step_by_step(seed):
     limits = dict(max_running=rng.choice([2, 3, 8]), max_waiting=rng.choice([3, 50]),
                   max_batch_tokens=rng.choice([4, 8, 32]), prefill_chunk_tokens=rng.choice([2, 5, 32]),
                   policy=policy, prefill_first=bool(seed % 3 == 0))
-    ea = FakeEngine(pages, page_tokens, slots)
-    eb = FakeEngine(pages, page_tokens, slots, cache_module=cache_model)
+    make = FakeGraphEngine if seed % 4 >= 2 else FakeEngine       # with and without decode quanta
+    limits["decode_quantum"] = rng.choice([1, 2, 4])
+    ea = make(pages, page_tokens, slots)
+    eb = make(pages, page_tokens, slots, cache_module=cache_model)
     a = Scheduler(ea, SchedulerConfig(**limits))
     b = scheduler_model.Scheduler(eb, scheduler_model.SchedulerConfig(**limits))
     arrivals = 0
