@@ -136,6 +136,7 @@ def time_decode(engine, batch: int, context: int, steps: int, warmup: int, seed:
     last = firsts
     for _ in range(max(warmup, 1)):
         last = engine.decode_steps(rids, last, params, 1)[-1]
+    engine.drop_lookahead()
     graph = engine._decode_graphs[batch]
     lengths = [engine.cache.length(r) for r in rids]
     engine.cache.reserve({r: l + steps for r, l in zip(rids, lengths)})
@@ -328,7 +329,10 @@ def run(gpus: int, steps: int, warmup: int, impl: str, layers: Optional[int] = N
                               max_batch_tokens=engine.max_batch_tokens, max_running=batch)
     graph = engine._decode_graphs[batch]
     e2e = {"value": stats.decode_tokens_per_second, "unit": "tokens/s",
-           "h2d_bytes_per_step": int(graph.size * 4 + graph.sample_host.numel() * 8),
+           # a step launched ahead gets the host's positions and lengths (2 x 4 bytes a request) and
+           # new block-table entries; the first step of a run gets the whole metadata buffer
+           "h2d_bytes_per_step": int(8 * batch + 4) if engine.lookahead else
+           int(graph.size * 4 + graph.sample_host.numel() * 8),
            "d2h_bytes_per_step": int(batch * 4 + 16),
            "prefill_tokens_per_s": stats.prefill_tokens_per_second}
 

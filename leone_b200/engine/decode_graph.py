@@ -51,6 +51,8 @@ class DecodeGraph:
         self._filled_rids = None           # what fill() last wrote into the host copy
         self._filled_pages = [[0] * batch for _ in engine.cache.groups]
         self._filled_sampling = None
+        self._events = [torch.cuda.Event(), torch.cuda.Event()]
+        self._advance_host = [torch.zeros((2, batch), dtype=torch.int32, pin_memory=True) for _ in range(2)]
         self.launches_per_step = 0
         self.stream = torch.cuda.Stream(device=dev)
 
@@ -161,6 +163,50 @@ class DecodeGraph:
             self.launches_per_step = self.engine.ops.launches - before
         cur.wait_stream(self.stream)
         self.counter.zero_()
+
+    def advance_from_host(self, rids: Sequence[Hashable], lengths, table_lens, slot: int) -> None:
+        """Inputs of a step that is launched before the step before it has been read: the host's
+        own record of every request's position and length (the cache manager's; the device has
+        advanced its copy to the same values) and the block-table entries of pages taken since
+        the last :meth:`fill`.  The token ids are where the device put them.  The pinned staging
+        rows alternate with ``slot``, so a row is rewritten only after the step that read it
+        has been waited for."""
+        e = self.engine
+        b = self.batch
+        stage = self._advance_host[slot & 1]
+        stage[0].numpy()[:] = lengths                    # position of the token being fed
+        stage[1].numpy()[:] = lengths + 1                # the sequence's length after the step
+        self._view("positions").copy_(stage[0], non_blocking=True)
+        self._view("ctx_len").copy_(stage[1], non_blocking=True)
+        host = self.meta_host.numpy()
+        for gi, (g, w, (o, shape)) in enumerate(zip(e.cache.groups, self.widths, self.bt_offsets)):
+            for i, r in enumerate(rids):
+                n, done = int(table_lens[gi][i]), self._filled_pages[gi][i]
+                if n > w:
+                    raise ValueError(f"block table needs {n} columns, only {w} given")
+                if n > done:
+                    # entries past `done` are read by no copy in flight: only this step needs them
+                    at = o + i * shape[1]
+                    host[at + done:at + n] = g.tables.tail(r, done)
+                    self.meta[at + done:at + n].copy_(self.meta_host[at + done:at + n], non_blocking=True)
+                    self._filled_pages[gi][i] = n
+
+    def launch(self, slot: int) -> torch.cuda.Event:
+        """Enqueue one step, whose sampled ids go to row ``slot`` of the history, and their
+        read-back; returns the event that says the ids are on the host."""
+        self.graph.replay()
+        self.history_host[slot].copy_(self.history[slot], non_blocking=True)
+        self.status_host.copy_(self.engine.status, non_blocking=True)
+        event = self._events[slot & 1]
+        event.record()
+        return event
+
+    def collect(self, slot: int, event: torch.cuda.Event) -> List[int]:
+        """Wait for a launched step and return its sampled ids."""
+        event.synchronize()
+        if int(self.status_host[0]) != 0:
+            self.engine.check_status()
+        return self.history_host[slot].tolist()
 
     def run(self, steps: int) -> np.ndarray:
         """Replay ``steps`` steps and read the sampled ids back: int32 [steps, batch]."""

@@ -14,6 +14,7 @@ advance only after the step succeeded, and a failure gives the pages back.
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, Hashable, List, Optional, Sequence
 
 import numpy as np
@@ -132,6 +133,9 @@ class Engine:
         self.steps_run = 0
         self._sampler = None
         self._decode_graphs = {}
+        # a decode step launched before the step before it was read (see decode_steps)
+        self._ahead = None
+        self.lookahead = os.environ.get("LEONE_NO_LOOKAHEAD", "0") != "1"
 
     # -- construction helpers -----------------------------------------------------------
     @classmethod
@@ -155,12 +159,14 @@ class Engine:
 
     # -- request lifetime ---------------------------------------------------------------
     def open(self, rid: Hashable) -> int:
+        self.drop_lookahead()
         slot = self.cache.open(rid)
         for state in self._run_state.values():
             state[slot].zero_()
         return slot
 
     def close(self, rid: Hashable) -> None:
+        self.drop_lookahead()
         self.cache.close(rid)
 
     def length(self, rid: Hashable) -> int:
@@ -227,6 +233,7 @@ class Engine:
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         if not entries:
             return None
+        self.drop_lookahead()
         seen = set()
         total = 0
         for e in entries:
@@ -286,15 +293,23 @@ class Engine:
 
     # -- decode quanta ------------------------------------------------------------------
     def decode_steps(self, rids: Sequence[Hashable], last_tokens: Sequence[int], params,
-                     steps: int, use_graph: bool = True):
+                     steps: int, use_graph: bool = True, expect_more: bool = True):
         """Decode ``steps`` tokens for every request in ``rids``: feed ``last_tokens`` at each
         request's current length, sample, feed the sample, and so on.  Returns the sampled ids
         as ``[steps][len(rids)]`` host ints.  Pages for all ``steps`` positions are taken first
         (:class:`OutOfPages` leaves everything as it was); lengths advance by ``steps``.
+        ``expect_more``: the caller expects to ask for the step after this one with the same
+        requests, so a single step may launch it before this one's ids are read
+        (:meth:`_decode_one_ahead`); say False when a request ends with this step, or the
+        step launched ahead is wasted GPU time before whatever comes next.
         """
         rids = list(rids)
         if steps <= 0 or not rids:
             return []
+        if (steps == 1 and use_graph and self.lookahead and self.device.type == "cuda"
+                and all(g.spec.kind == "full" for g in self.cache.groups)):
+            return [self._decode_one_ahead(rids, [int(t) for t in last_tokens], list(params), expect_more)]
+        self.drop_lookahead()
         if not (use_graph and self.device.type == "cuda") or steps > 64:
             if max(self.cache.length(r) for r in rids) + steps > self.spec.max_positions:
                 raise ValueError("decode_steps would run past the model's positions")
@@ -310,15 +325,8 @@ class Engine:
         try:
             if int(lengths.max()) + steps > self.spec.max_positions:
                 raise ValueError("decode_steps would run past the model's positions")
-            graph = self._decode_graphs.get(len(rids))
             state = dict(versions=versions, slots=slots, table_lens=table_lens)
-            if graph is None:
-                from .decode_graph import DecodeGraph
-                graph = DecodeGraph(self, len(rids))
-                # capture needs valid tables: fill first, then warm up and capture on them
-                graph.fill(rids, last_tokens, lengths, params, **state)
-                graph.capture()
-                self._decode_graphs[len(rids)] = graph
+            graph = self._decode_graph(rids, last_tokens, lengths, params, state)
             graph.fill(rids, last_tokens, lengths, params, **state)
             tokens = graph.run(steps)       # also reads and checks the status word
         except Exception:
@@ -328,6 +336,76 @@ class Engine:
         self.cache.commit_many(rids, lengths + steps)
         self.steps_run += steps
         return tokens.tolist()
+
+    def _decode_graph(self, rids, last_tokens, lengths, params, state):
+        graph = self._decode_graphs.get(len(rids))
+        if graph is None:
+            from .decode_graph import DecodeGraph
+            graph = DecodeGraph(self, len(rids))
+            # capture needs valid tables: fill first, then warm up and capture on them
+            graph.fill(rids, last_tokens, lengths, params, **state)
+            graph.capture()
+            self._decode_graphs[len(rids)] = graph
+        return graph
+
+    def _decode_one_ahead(self, rids: List[Hashable], last_tokens: List[int], params,
+                          expect_more: bool = True) -> List[int]:
+        """One decode step of ``rids``, with the step after it launched before this one's ids
+        are read: the sampled ids are fed back on the device, so the next step needs nothing
+        from the host but the pages it may write (reserved here, given back if the next call
+        is not the expected one).  The next call finds its step already running if it names
+        the same requests and feeds the ids this call returns; anything else the engine is
+        asked to do in between (another step, opening or closing a request) drops it."""
+        a, self._ahead = self._ahead, None
+        if a is not None and a["rids"] == rids and a["feeds"] == last_tokens and a["params"] == params:
+            graph, lengths, slot, event = a["graph"], a["lengths"], a["slot"], a["event"]
+        else:
+            self._ahead = a
+            self.drop_lookahead()
+            lengths, versions, slots, table_lens = self.cache.reserve_steps(rids, 1)
+            try:
+                if int(lengths.max()) + 1 > self.spec.max_positions:
+                    raise ValueError("decode_steps would run past the model's positions")
+                state = dict(versions=versions, slots=slots, table_lens=table_lens)
+                graph = self._decode_graph(rids, last_tokens, lengths, params, state)
+                graph.fill(rids, last_tokens, lengths, params, **state)
+                slot, event = 0, graph.launch(0)
+            except Exception:
+                for r in rids:
+                    self.cache.rollback(r)
+                raise
+        try:
+            ahead = None
+            if (expect_more and slot + 1 < graph.max_quantum
+                    and int(lengths.max()) + 2 <= self.spec.max_positions):
+                try:
+                    table_lens = self.cache.reserve_steps(rids, 2)[3]      # this step's token and the next one's
+                except OutOfPages:
+                    pass                                                   # the next call decides what gives way
+                else:
+                    graph.advance_from_host(rids, lengths + 1, table_lens, slot + 1)
+                    ahead = dict(rids=rids, params=params, graph=graph, lengths=lengths + 1, slot=slot + 1,
+                                 event=graph.launch(slot + 1))
+            tokens = graph.collect(slot, event)
+        except Exception:
+            for r in rids:
+                self.cache.rollback(r)
+            raise
+        self.cache.commit_many(rids, lengths + 1)
+        if ahead is not None:
+            ahead["feeds"] = tokens
+            self._ahead = ahead
+        self.steps_run += 1
+        return tokens
+
+    def drop_lookahead(self) -> None:
+        """Forget a decode step that was launched ahead: what it reserved goes back.  Its kernels
+        may still be running; whatever is launched next is ordered behind them on the stream."""
+        a, self._ahead = self._ahead, None
+        if a is not None:
+            for r in a["rids"]:
+                if self.cache.is_open(r):
+                    self.cache.rollback(r)
 
     def check_status(self) -> None:
         word = self.status.tolist()

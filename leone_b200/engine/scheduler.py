@@ -305,8 +305,10 @@ class Scheduler:
         bounds the same overshoot by its quantum, crates/leone/src/scheduler.rs:1334-1338)."""
         keys = (c_longlong * len(reqs))(*[r.key for r in reqs])
         q = int(self._lib.leone_sched_decode_quantum(self._h, len(reqs), keys, c_longlong(self.config.decode_quantum)))
+        # no request reaches its limit in this quantum: the same batch decodes again
+        more = all(r.remaining_new > q for r in reqs)
         steps = self.engine.decode_steps([r.rid for r in reqs], [r.tokens[-1] for r in reqs],
-                                         [r.sampling for r in reqs], q)
+                                         [r.sampling for r in reqs], q, expect_more=more)
         outputs: List[StepOutput] = []
         live = list(range(len(reqs)))                   # rows whose request has not ended
         for row in steps:

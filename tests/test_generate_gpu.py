@@ -106,3 +106,47 @@ def test_a_captured_graph_survives_growth_of_the_scratch_buffers(folders):
     torch.cuda.synchronize()
     assert first == again
     assert len(eng.ops.fast._retired) > 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_launched_ahead_change_nothing(folders, dtype):
+    """A decode step launched before the step before it has been read: the same tokens as
+    without, with requests that end at different steps (by length and by a stop token, so
+    steps launched ahead are thrown away), few pages (new pages arrive while a step is in
+    flight), and another step of the engine between two decode steps."""
+    from leone_b200 import generate
+    from leone_b200.sampling.sampler import SamplingParams
+    prompts = [replay.random_tokens(331, n, 300 + n) for n in (5, 21, 34, 9)]
+    outs, ahead_seen = [], []
+    for lookahead in (False, True):
+        eng = _engine(folders["C"], "C", dtype, 30)
+        eng.lookahead = lookahead
+        free = generate(eng, prompts, 40, temperature=0.9, seed=11, eos_token_id=-1)
+        stop = free[1][17]                                # request 1 (and whoever else draws it) ends early
+        got = generate(eng, prompts, 40, temperature=0.9, seed=11, eos_token_id=stop)
+        assert got[1] == free[1][:free[1].index(stop) + 1]
+        outs.append((free, got))
+        assert eng.cache.free_pages() == [eng.num_pages] and eng._ahead is None
+        # the engine's own interface: three decode steps, a prompt step of another request
+        # in between, then more decode steps
+        rids = ["p", "q"]
+        firsts = []
+        for r, p in zip(rids, prompts[:2]):
+            logits = eng.step([(r, p, [len(p) - 1])])
+            firsts.append(eng.sample(logits, [SamplingParams()], [len(p) - 1])[0])
+        params = [SamplingParams(0.8, 5), SamplingParams(0.0, 0)]
+        seq, last = [], firsts
+        for i in range(9):
+            if i == 3:
+                eng.step([("other", prompts[2], [])])
+            last = eng.decode_steps(rids, last, params, 1)[0]
+            if i in (0, 4):
+                ahead_seen.append(eng._ahead is not None)
+            seq.append(last)
+        outs.append(seq)
+        for r in rids + ["other"]:
+            eng.close(r)
+        assert eng.cache.free_pages() == [eng.num_pages]
+        eng.cache.check_invariants()
+    assert outs[0] == outs[2] and outs[1] == outs[3]
+    assert ahead_seen == [False, False, True, True]

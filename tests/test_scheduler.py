@@ -57,7 +57,7 @@ class FakeGraphEngine(FakeEngine):
     """The same with the engine's ``decode_steps``: several decode steps without the scheduler
     in between, pages for all of them taken first."""
 
-    def decode_steps(self, rids, last_tokens, params, steps):
+    def decode_steps(self, rids, last_tokens, params, steps, **_):
         wants = {r: self.cache.length(r) + steps for r in rids}
         self.cache.reserve(wants)
         rows = []
