@@ -34,11 +34,16 @@ constexpr int kGemmThreads = 192;
 // Up to 64 tokens per tile a block keeps about 100 KB of stages, so two blocks (of this kernel
 // or of this one and the next) share an SM: while one drains its epilogue the other already
 // streams weights.  Larger token tiles take the whole SM.
+constexpr int pow2_at_least(int v) {
+  int p = 32;
+  while (p < v) p *= 2;
+  return p;
+}
 template <int BN> struct GemmCfg {
   static constexpr int kStageBytes = kTileW * kTileK * 2 + BN * kTileK * 2;
   static constexpr int kStages = BN <= 16 ? 5 : BN <= 32 ? 5 : BN <= 64 ? 4 : BN <= 128 ? 6 : 4;
   static constexpr int kBlocksPerSm = BN <= 64 ? 2 : 1;
-  static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+  static constexpr int kTmemCols = pow2_at_least(2 * BN);      // two accumulators, BN columns apart
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment*/ + 256 /*barriers*/;
 };
 
@@ -857,9 +862,45 @@ extern "C" int leone_gemm_tc_tiles_token_major(int m, int n) {
   return ((n + 255) / 256) * ((m + kTileW - 1) / kTileW);
 }
 
+static int device_sm_count() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+      sms = 148;
+  }
+  return sms;
+}
+
+// Weight rows per tile of the unsplit token-major form above 256 tokens: of 256 and 240 the
+// width whose tiles cost the fewer rounds over the SMs times the width (2,048 tokens x 4,096
+// outputs: 256 tiles of 256 are two rounds on 148 SMs, the second 73 % full; 288 tiles of 240
+// are two full rounds of narrower tiles: 72.6 -> 66.7 us).  gate_up_groups: the rows come in
+// gate/up groups of 32 (SwiGLU epilogue), which 240 would cut; 224 was measured no faster there.
+extern "C" int leone_gemm_tc_token_major_width(int m, int n, int gate_up_groups) {
+  if (m <= 256) return 256;
+  const int sms = device_sm_count();
+  const long long m_tiles = (m + kTileW - 1) / kTileW;
+  int best = 256;
+  long long best_cost = -1;
+  const int widths[2] = {256, 240};
+  for (int w : widths) {
+    if (gate_up_groups && (w % 32) != 0) continue;
+    const long long tiles = ((n + w - 1) / w) * m_tiles;
+    const long long cost = ((tiles + sms - 1) / sms) * w;
+    if (best_cost < 0 || cost < best_cost) best = w, best_cost = cost;
+  }
+  return best;
+}
+
 // Parts of the sums of squares a product of m tokens with n outputs leaves for the norm after
-// it: one per 32 weight rows up to 256 tokens, one per tile of 256 weight rows above.
-extern "C" int leone_gemm_tc_norm_parts(int m, int n) { return m <= 256 ? (n + 31) / 32 : (n + 255) / 256; }
+// it: one per 32 weight rows up to 256 tokens, one per tile of weight rows above.
+extern "C" int leone_gemm_tc_norm_parts(int m, int n) {
+  if (m <= 256) return (n + 31) / 32;
+  const int w = leone_gemm_tc_token_major_width(m, n, 0);
+  return (n + w - 1) / w;
+}
 
 // Workspace floats and counters needed when `split_tiles` tiles are split `splits` ways;
 // both 0 when splits == 1.
@@ -932,12 +973,15 @@ extern "C" int leone_gemm_tc(const void* x, const void* w, void* out, const floa
   if (norm_in_ss != nullptr && norm_in_parts < 1) return kRefusedSize;
   if (cluster && (full_tiles != 0 || splits > 8)) return kRefusedSize;
   if (splits > 1 && !cluster && (workspace == nullptr || counters == nullptr)) return kRefusedSize;
-  const int tiles = swap ? leone_gemm_tc_tiles(m, n) : leone_gemm_tc_tiles_token_major(m, n);
+  // the token-major tile's width: 256 when split or forced below the prompt sizes
+  const int tm_width = (swap || cluster || m <= 256) ? 256 : leone_gemm_tc_token_major_width(m, n, epilogue == 3);
+  const int tiles = swap ? leone_gemm_tc_tiles(m, n)
+                         : ((n + tm_width - 1) / tm_width) * ((m + kTileW - 1) / kTileW);
   if (splits == 1) full_tiles = tiles;
   if (full_tiles < 0 || full_tiles > tiles) return kRefusedSize;
   const int bn = leone_gemm_tc_tile(m);
   CUtensorMap mw, mx;
-  int r = make_tensor_map_2d(&mw, w, (uint64_t)n, (uint64_t)k, (uint64_t)ldw, swap ? kTileW : 256);
+  int r = make_tensor_map_2d(&mw, w, (uint64_t)n, (uint64_t)k, (uint64_t)ldw, swap ? kTileW : (uint32_t)tm_width);
   if (r != 0) return r;
   r = make_tensor_map_2d(&mx, x, (uint64_t)m, (uint64_t)k, (uint64_t)ldx, swap ? (uint32_t)bn : kTileW);
   if (r != 0) return r;
@@ -946,6 +990,7 @@ extern "C" int leone_gemm_tc(const void* x, const void* w, void* out, const floa
                norm_in_parts, norm_eps};
   if (g_gemm_trace != nullptr) g_gemm_trace += g_gemm_trace_stride;
   if (!swap && cluster) return launch_gemm<256, false, true>(mw, mx, p, sm_count, stream);
+  if (!swap && tm_width == 240) return launch_gemm<240, false>(mw, mx, p, sm_count, stream);
   if (!swap) return launch_gemm<256, false>(mw, mx, p, sm_count, stream);
   if (cluster) {
     switch (bn) {

@@ -262,6 +262,41 @@ def test_the_dispatcher_splits_narrow_products_in_the_token_major_form(ops16):
     assert fast.plan_product(300, 4096, 256)[:2] == (True, 1)                # too few k-blocks to split
 
 
+def test_gemm_tc_prompt_sized_tiles_of_240_weight_rows(ops16):
+    """Above 256 tokens the tile's width is 256 or 240, whichever costs fewer rounds: a size where
+    240 wins, with the folded norm on both sides (its parts follow the width) and a ragged edge."""
+    fast = ops16.fast
+    sms = fast.sm_count
+    m, k = 128 * 8, 256
+    n = 240 * (2 * sms // 8)                                # 2 rounds of 240-wide tiles; 256-wide ones need 3
+    assert fast.lib.leone_gemm_tc_token_major_width(m, n, 0) == 240
+    assert fast.lib.leone_gemm_tc_token_major_width(m, n, 1) == 256
+    assert fast.norm_parts(m, n) == n // 240
+    n -= 40                                                 # the last tile is ragged
+    x = _randn((m, k), 71, torch.bfloat16)
+    w = _randn((n, k), 72, torch.bfloat16, scale=0.05)
+    want = x.double() @ w.double().t()
+    res = _randn((m, n), 73)
+    g = 1 + 0.2 * _randn((n,), 74)
+    hidden = res.clone()
+    parts = fast.norm_parts(m, n)
+    xn = torch.empty((m, n), device=DEV, dtype=torch.bfloat16)
+    ss = torch.full((parts, m), -1.0, device=DEV)
+    fast._gemm(x, w, hidden, 2, hidden, n, norm_out=(xn, g, ss))
+    h64 = want + res.double()
+    _close(hidden, h64, 1e-5, 2e-6 * math.sqrt(k) * 4, "240-wide tiles, residual")
+    _close(ss.sum(0), (hidden.double() ** 2).sum(1), 1e-5, 1e-6, "240-wide tiles, sums of squares")
+    _close(xn, hidden.double() * g.double(), 2 ** -8, 1e-6, "240-wide tiles, bf16(out * weight)")
+    out = torch.empty((m, n), device=DEV, dtype=torch.bfloat16)
+    fast._gemm(x, w, out, 0, None, n)
+    _close(out, want, 2 ** -8, 2e-6 * math.sqrt(k) * 4, "240-wide tiles, bf16 out")
+    w2 = _randn((264, n), 75, torch.bfloat16, scale=0.05)
+    rs = torch.rsqrt((hidden.double() ** 2).mean(dim=1, keepdim=True) + 1e-5)
+    out2 = torch.empty((m, 264), device=DEV, dtype=torch.bfloat16)
+    fast._gemm(xn, w2, out2, 0, None, 264, norm_in=(ss, parts, 1e-5))
+    _close(out2, (xn.double() @ w2.double().t()) * rs, 2 ** -8, 1e-3, "the product after, parts of 240")
+
+
 def test_the_dispatcher_picks_the_token_major_form_only_where_its_tiles_fill_the_device(ops16):
     fast = ops16.fast
     sms = fast.sm_count
