@@ -64,7 +64,7 @@ def cmd_generate(args) -> int:
                           eos_token_id=args.eos, prefill_chunk=args.prefill_chunk,
                           max_batch_tokens=args.max_batch_tokens, return_stats=True,
                           use_graphs=not args.eager_decode and not args.debug_logits,
-                          decode_quantum=args.decode_quantum)
+                          decode_quantum=args.decode_quantum, truncations=tuple(args.truncations or ()))
     for toks in out:
         print(",".join(str(t) for t in toks))
     if args.debug_tokens:
@@ -207,6 +207,29 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("-n", "--tokens", type=int, required=True, help="tokens to generate per prompt")
     g.add_argument("--temp", type=float, default=None, help="scale logits by 1/t (default: greedy)")
     g.add_argument("--seed", type=int, default=0, help="seed the sampler. Default: 0")
+
+    class Stage(argparse.Action):
+        """Truncation stages apply in the order their flags are given
+        (crates/leone-cli/src/main.rs:1378-1430)."""
+
+        def __call__(self, parser, namespace, value, option_string=None):
+            stages = list(getattr(namespace, "truncations", None) or [])
+            stages.append((self.dest, value))
+            namespace.truncations = stages
+
+    for flag, dest, kind, text in (
+            ("--top-k", "top_k", int, "Keep the n highest-probability tokens"),
+            ("--top-p", "top_p", float, "Keep the shortest prefix whose mass reaches p"),
+            ("--min-p", "min_p", float, "Keep tokens above m times the highest"),
+            ("--top-a", "top_a", float, "Keep tokens above a times the highest squared"),
+            ("--tfs", "tfs", float, "Tail-free sampling on the second derivative"),
+            ("--typical", "typical", float, "Locally typical sampling to mass p"),
+            ("--epsilon", "epsilon", float, "Keep tokens with probability at least e"),
+            ("--eta", "eta", float, "Entropy-relaxed probability floor"),
+            ("--min-k", "min_k", float, "Keep the top k raw logits at the sharpest drop"),
+            ("--top-n-sigma", "top_n_sigma", float, "Keep raw logits within n deviations of the peak")):
+        g.add_argument(flag, dest=dest, type=kind, action=Stage, help=text)
+    g.set_defaults(truncations=None)
     g.add_argument("--eager-decode", action="store_true", help="disable decode graph replay")
     g.add_argument("--kv", choices=["q8", "f16", "f32", "bf16"], default=None,
                    help="KV cache storage; only the run dtype is available")

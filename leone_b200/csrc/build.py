@@ -28,7 +28,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 MODULES: Dict[str, List[str]] = {
     # every run needs these: both dtypes, every size
-    "core": ["elementwise.cu", "gemm_simt.cu", "attention_generic.cu"],
+    "core": ["elementwise.cu", "gemm_simt.cu", "attention_generic.cu", "sampling_pipeline.cu"],
     # the bfloat16 serving path: tensor-core products and tiled attention
     "bf16": ["gemm_tc.cu", "attention_tiled.cu", "attention_prefill_tc.cu"],
     # the entry point that allocates nothing (leone_static.h); it compiles attention_tiled.cu in

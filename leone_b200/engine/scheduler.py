@@ -296,8 +296,10 @@ class Scheduler:
 
     @staticmethod
     def _decode_only(plan) -> bool:
+        """Every entry is a decode row that the captured step can sample (greedy or temperature;
+        truncation stages run outside the graph)."""
         return all(count == 1 and req.generated and start == len(req.tokens) - 1
-                   for req, start, count in plan)
+                   and not getattr(req.sampling, "truncates", False) for req, start, count in plan)
 
     def _decode_quantum(self, reqs: List[Request]) -> List[StepOutput]:
         """Several decode steps of the same requests without the host in between.  A request

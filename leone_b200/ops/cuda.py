@@ -15,6 +15,7 @@ import os
 from ctypes import c_float, c_int, c_void_p
 from typing import Optional
 
+import numpy as np
 import torch
 
 from ..csrc.build import ensure_built
@@ -96,6 +97,7 @@ class CudaOps:
             from .fast import FastKernels
             self.fast = FastKernels(self.device)
         self.launches = 0
+        self._sample_scratch = None
         self.status = None
         # LEONE_NO_PDL=1 launches every kernel fully serialised after its predecessor
         self.set_pdl(os.environ.get("LEONE_NO_PDL", "0") != "1")
@@ -342,6 +344,37 @@ class CudaOps:
         self.launches += 1
         _check(self.core.leone_sample(_ptr(logits), rows, vocab, _ptr(temperature), _ptr(seeds),
                                       _ptr(positions), _ptr(out), self._stream()), "sample")
+
+    def sample_truncated(self, logits, temperatures, seeds, positions, stages, want_probs: bool = False):
+        """Rows that sample through truncation stages: ``stages`` is a list of (stage number,
+        value) applied in order to every row (``csrc/sampling_pipeline.cu``).  Returns the ids
+        as an int32 device tensor (and the fp64 distribution the draw was made from)."""
+        import ctypes
+        rows, vocab = logits.shape
+        _need(logits.dtype == torch.float32 and logits.is_contiguous(), "logits must be fp32")
+        _need(rows == len(temperatures) == len(seeds) == len(positions), "one temperature, seed and position a row")
+        _need(all(t > 0 for t in temperatures), "truncation stages need a temperature")
+        self.core.leone_sample_truncated_scratch.restype = ctypes.c_longlong
+        need = int(self.core.leone_sample_truncated_scratch(rows, vocab))
+        if self._sample_scratch is None or self._sample_scratch.numel() < need:
+            self._sample_scratch = torch.empty(need, dtype=torch.uint8, device=self.device)
+        dev = self.device
+        t = torch.tensor(temperatures, dtype=torch.float64, device=dev)
+        sd = torch.tensor(np.array([s_ & 0xFFFF_FFFF_FFFF_FFFF for s_ in seeds], dtype=np.uint64).view(np.int64),
+                          device=dev)
+        pos = torch.tensor(positions, dtype=torch.int64, device=dev)
+        out = torch.empty(rows, dtype=torch.int32, device=dev)
+        probs = torch.empty((rows, vocab), dtype=torch.float64, device=dev) if want_probs else None
+        n = len(stages)
+        types = (ctypes.c_int * max(n, 1))(*[int(a) for a, _ in stages])
+        values = (ctypes.c_double * max(n, 1))(*[float(b) for _, b in stages])
+        self.launches += 1
+        _check(self.core.leone_sample_truncated(_ptr(logits), rows, vocab, _ptr(t), _ptr(sd), _ptr(pos), n,
+                                                types, values, _ptr(self._sample_scratch), _ptr(out),
+                                                _ptr(probs), self._stream()), "sample_truncated")
+        if bool((out < 0).any()):
+            raise ValueError("every logit of a row is non-finite, so no token can be sampled")
+        return (out, probs) if want_probs else out
 
     def decode_advance(self, token_ids, positions, ctx_len, sample_pos, sampled, history, counter):
         n = token_ids.numel()

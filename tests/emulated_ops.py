@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import math
 
+import numpy as np
 import torch
 
 
@@ -118,3 +119,13 @@ class EmulatedOps:
         from tests.plain.model import sample
         for i in range(logits.shape[0]):
             out[i] = sample(logits[i].tolist(), float(temperature[i]), int(seeds[i]), int(positions[i]))
+
+    def sample_truncated(self, logits, temperatures, seeds, positions, stages, want_probs=False):
+        from leone_b200.sampling.sampler import TRUNCATION_STAGES
+        from tests.plain.model import select, truncated_probs, uniform
+        names = {v: k for k, v in TRUNCATION_STAGES.items()}
+        named = [(names[t], v) for t, v in stages]
+        rows = [truncated_probs(logits[i].tolist(), temperatures[i], named) for i in range(logits.shape[0])]
+        out = torch.tensor([select(p, uniform(seeds[i], positions[i])) for i, p in enumerate(rows)],
+                           dtype=torch.int32)
+        return (out, torch.tensor(np.stack(rows))) if want_probs else out

@@ -238,13 +238,140 @@ def select(probs, u):
     return last
 
 
-def sample(logits, temperature, seed, position):
+def _entropy(kept):
+    """Entropy of a normalised distribution in nats (crates/leone/src/sampler.rs:625-630)."""
+    return float(sum(-p * math.log(p) for p in kept if p > 0.0))
+
+
+def _threshold_keep(kept, floor):
+    """Leading entries with probability >= floor (crates/leone/src/sampler.rs:635-637)."""
+    n = 0
+    for p in kept:
+        if not p >= floor:
+            break
+        n += 1
+    return n
+
+
+def truncated_probs(logits, temperature, stages):
+    """The distribution a temperature and an ordered list of truncation stages produce from one
+    row of logits, float64, in id order (crates/leone/src/sampler.rs:451-469).
+
+    ``stages``: ``(name, value)`` pairs; names top_k, top_p, min_p, top_a, tfs, typical, epsilon,
+    eta, min_k, top_n_sigma (crates/leone/src/sampler.rs:184-234).  Finite logits are sorted
+    descending, ties by lower id (:512-516), weights exp(l/t - l_max/t) normalised (:517-530).
+    min_k and top_n_sigma read the raw logits and run first (:532-553); the others run in the
+    order given, each on the renormalised survivors of the one before, always keeping at least
+    the most probable token (:555-612)."""
+    l = [float(x) for x in logits]
+    order = sorted((i for i in range(len(l)) if math.isfinite(l[i])), key=lambda i: (-l[i], i))
+    if not order:
+        raise ValueError("every logit is non-finite")
+    top = l[order[0]] / temperature
+    kept = [math.exp(l[i] / temperature - top) for i in order]
+    total = sum(kept)
+    kept = [w / total for w in kept]
+
+    def renorm(v):
+        t = sum(v)
+        return [x / t for x in v]
+
+    changed = False
+    for name, value in stages:
+        if name == "top_n_sigma":            # crates/leone/src/sampler.rs:659-689
+            if len(order) >= 2:
+                n = len(order)
+                mean = sum(l[i] for i in order) / n
+                dev = math.sqrt(sum((l[i] - mean) ** 2 for i in order) / n)
+                keep = n
+                if math.isfinite(dev):
+                    cut = l[order[0]] - value * dev
+                    keep = max(1, _threshold_keep([l[i] for i in order], cut))
+                order, kept = order[:max(keep, 1)], kept[:max(keep, 1)]
+            changed = True
+        elif name == "min_k":                # crates/leone/src/sampler.rs:733-762
+            n = len(order)
+            keep = n
+            if n >= 2:
+                rng = l[order[0]] - l[order[-1]] + 1e-8
+                if math.isfinite(rng) and rng > 0.0:
+                    cliff, best = 1, -math.inf
+                    for rank in range(1, n):
+                        weighted = ((l[order[rank - 1]] - l[order[rank]]) / rng) / rank
+                        if weighted > best:
+                            best, cliff = weighted, rank
+                    fb = math.floor(value / rng)
+                    fallback = min(int(fb), n) if math.isfinite(fb) and fb >= 0 else n
+                    keep = min(max(cliff, fallback, 1), n)
+            order, kept = order[:max(keep, 1)], kept[:max(keep, 1)]
+            changed = True
+    if changed:
+        kept = renorm(kept)
+
+    for name, value in stages:
+        keep = None
+        if name == "top_k":
+            keep = min(int(value), len(kept))
+        elif name == "top_p":                # shortest prefix whose mass reaches p (:640-649)
+            covered, keep = 0.0, len(kept)
+            for count, p in enumerate(kept):
+                covered += p
+                if covered >= value:
+                    keep = count + 1
+                    break
+        elif name == "min_p":
+            keep = _threshold_keep(kept, value * kept[0])
+        elif name == "top_a":
+            keep = _threshold_keep(kept, value * kept[0] * kept[0])
+        elif name == "epsilon":
+            keep = _threshold_keep(kept, value)
+        elif name == "eta":                  # floor = min(eta, sqrt(eta) * exp(-H)) (:601-607)
+            keep = _threshold_keep(kept, min(value, math.sqrt(value) * math.exp(-_entropy(kept))))
+        elif name == "tfs":                  # crates/leone/src/sampler.rs:697-723
+            keep = len(kept)
+            if len(kept) >= 3:
+                second = [abs(kept[s] - 2.0 * kept[s + 1] + kept[s + 2]) for s in range(len(kept) - 2)]
+                tot = sum(second)
+                if tot > 0.0 and math.isfinite(tot):
+                    covered, keep = 0.0, 1
+                    for v in second:
+                        covered += v / tot
+                        if covered <= value:
+                            keep += 1
+                        else:
+                            break
+        elif name == "typical":              # crates/leone/src/sampler.rs:766-790
+            h = _entropy(kept)
+            scored = sorted(range(len(kept)),
+                            key=lambda s_: (abs(-math.log(kept[s_]) - h) if kept[s_] > 0.0 else math.inf, s_))
+            covered, chosen = 0.0, []
+            for s_ in scored:
+                chosen.append(s_)
+                covered += kept[s_]
+                if covered >= value:
+                    break
+            chosen.sort()
+            order, kept = [order[s_] for s_ in chosen], renorm([kept[s_] for s_ in chosen])
+            continue
+        else:
+            continue                          # the raw-logit stages ran first
+        keep = max(keep, 1)
+        order, kept = order[:keep], renorm(kept[:keep])
+    probs = np.zeros(len(l), dtype=np.float64)
+    for i, p in zip(order, kept):
+        probs[i] = p
+    return probs
+
+
+def sample(logits, temperature, seed, position, truncations=()):
+    if truncations and temperature:
+        return select(truncated_probs(logits, temperature, truncations), uniform(seed, position))
     if temperature is None or temperature == 0.0:
         return argmax(logits)
     return select(temperature_probs(logits, temperature), uniform(seed, position))
 
 
-def generate(model: PlainModel, prompt, max_new_tokens, temperature=0.0, seed=0, eos=None):
+def generate(model: PlainModel, prompt, max_new_tokens, temperature=0.0, seed=0, eos=None, truncations=()):
     """Greedy/temperature generation by re-running the whole sequence each token.  The draw
     for a token uses the position of the token whose logits are sampled
     (crates/leone/src/runtime.rs:4945, 6080)."""
@@ -252,7 +379,7 @@ def generate(model: PlainModel, prompt, max_new_tokens, temperature=0.0, seed=0,
     out = []
     for _ in range(max_new_tokens):
         logits = model.logits(tokens)[-1].tolist()
-        tok = sample(logits, temperature, seed, len(tokens) - 1)
+        tok = sample(logits, temperature, seed, len(tokens) - 1, truncations)
         out.append(tok)
         tokens.append(tok)
         if eos is not None and tok == eos:

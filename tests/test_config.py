@@ -100,3 +100,15 @@ def test_run_order_and_borrowed_caches_are_checked():
     replace(spec, layers=borrowed).validate()
     with pytest.raises(ValueError, match="before"):
         replace(spec, layers=borrowed, run_order=(2, 0, 1)).validate()
+
+
+def test_cli_truncation_flags_keep_their_order():
+    """Stages apply in the order their flags are given (crates/leone-cli/src/main.rs:1378-1430)."""
+    from leone_b200.cli import build_parser
+    from leone_b200.sampling.sampler import SamplingParams
+    args = build_parser().parse_args(["generate", "-m", "x", "-t", "1,2", "-n", "4", "--temp", "0.8", "--min-p", "0.1",
+                                      "--top-k", "40", "--typical", "0.9", "--top-k", "5"])
+    assert args.truncations == [("min_p", 0.1), ("top_k", 40), ("typical", 0.9), ("top_k", 5)]
+    params = SamplingParams(args.temp, args.seed, tuple(args.truncations))
+    assert params.truncates and not SamplingParams(0.0, 0, tuple(args.truncations)).truncates
+    assert build_parser().parse_args(["generate", "-m", "x", "-t", "1", "-n", "1"]).truncations is None

@@ -150,3 +150,20 @@ def test_steps_launched_ahead_change_nothing(folders, dtype):
         eng.cache.check_invariants()
     assert outs[0] == outs[2] and outs[1] == outs[3]
     assert ahead_seen == [False, False, True, True]
+
+
+def test_generation_with_truncation_stages(folders):
+    """Temperature with top-k, top-p and min-p, and a pipeline with typical, through the entry
+    point against the plain implementation; other requests of the batch sample without."""
+    from leone_b200 import generate
+    plain = PlainModel(folders["B"])
+    prompts = [replay.random_tokens(384, n, 400 + n) for n in (3, 11, 20)]
+    for stages in ((("top_k", 12), ("top_p", 0.9), ("min_p", 0.02)), (("top_n_sigma", 1.5), ("typical", 0.8))):
+        want = [plain_generate(plain, p, 7, temperature=1.1, seed=21 + i, truncations=stages)
+                for i, p in enumerate(prompts)]
+        got = generate(folders["B"], prompts, 7, temperature=1.1, seed=21, dtype="float32", page_tokens=8,
+                       eos_token_id=-1, truncations=stages)
+        assert got == want
+        unrestricted = generate(folders["B"], prompts, 7, temperature=1.1, seed=21, dtype="float32",
+                                page_tokens=8, eos_token_id=-1)
+        assert unrestricted != got

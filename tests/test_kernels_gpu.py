@@ -801,3 +801,80 @@ def test_attention_decode_cluster_refuses_what_it_cannot_do(ops16):
                                     splits, fuse, z, z, c_float(1e-6), z, 0, 0, z, z)
     assert lib.leone_attention_decode_cluster(*args(128, 9, 0)) != 0        # more splits than a cluster holds
     assert lib.leone_attention_decode_cluster(*args(96, 2, 1)) != 0         # fused preparation needs d 64 or 128
+
+
+# -- the sampler's truncation stages (fp64 pipeline) ---------------------------------------------
+PIPELINES = [
+    [("top_k", 40)], [("top_p", 0.9)], [("min_p", 0.05)], [("top_a", 0.2)], [("tfs", 0.95)], [("typical", 0.7)],
+    [("epsilon", 3e-4)], [("eta", 2e-3)], [("min_k", 3.0)], [("top_n_sigma", 1.0)],
+    [("top_k", 50), ("top_p", 0.9), ("min_p", 0.05)],
+    [("top_n_sigma", 2.0), ("typical", 0.8), ("tfs", 0.9), ("top_k", 7)],
+    [("min_k", 1.0), ("eta", 0.01), ("typical", 0.9), ("typical", 0.5), ("epsilon", 1e-3), ("top_a", 0.1)],
+    [("top_p", 1.0), ("top_k", 1)], [("epsilon", 1.0), ("tfs", 1e-9)],
+]
+
+
+@pytest.mark.parametrize("vocab", [7, 331, 5000])
+@pytest.mark.parametrize("stages", PIPELINES, ids=lambda s: "+".join(n for n, _ in s))
+def test_sample_truncated_matches_the_plain_sampler(ops32, vocab, stages):
+    """Every stage and several pipelines: the distribution against the plain float64 sampler
+    entry by entry, and the drawn ids; rows with ties, excluded entries and different
+    temperatures."""
+    from leone_b200.sampling.sampler import TRUNCATION_STAGES
+    from tests.plain.model import select, truncated_probs, uniform
+    rows = 4
+    logits = _randn((rows, vocab), 70 + vocab, scale=3.0)
+    logits[0, 3] = float("-inf")
+    logits[1, 1] = float("nan")
+    logits[2] = torch.round(logits[2] * 2) / 2                 # many equal logits: ties go to the lower id
+    logits[3, :vocab // 2] = float("-inf")
+    temps = [0.7, 1.0, 1.3, 0.25]
+    seeds = [1, 2, 12345678901, 4]
+    positions = [0, 17, 300, 2047]
+    numbered = [(TRUNCATION_STAGES[n], v) for n, v in stages]
+    out, probs = ops32.sample_truncated(logits, temps, seeds, positions, numbered, want_probs=True)
+    host = logits.cpu().numpy()
+    for r in range(rows):
+        want = truncated_probs(host[r], temps[r], stages)
+        got = probs[r].cpu().numpy()
+        assert (got > 0).tolist() == (want > 0).tolist(), f"row {r}: the surviving sets differ"
+        assert np.abs(got - want).max() < 1e-13, f"row {r}: {np.abs(got - want).max()}"
+        assert int(out[r]) == select(want, uniform(seeds[r], positions[r]))
+
+
+def test_sample_truncated_full_vocabulary(ops32):
+    """A row of 151,936 logits (the sort's global passes, the scans over long rows)."""
+    from leone_b200.sampling.sampler import TRUNCATION_STAGES
+    from tests.plain.model import select, truncated_probs, uniform
+    vocab = 151936
+    logits = _randn((2, vocab), 99, scale=2.5)
+    logits[0, 5] = float("-inf")
+    for stages in ([("top_p", 0.95), ("min_p", 0.01)], [("typical", 0.9), ("top_k", 100)], [("tfs", 0.97)]):
+        numbered = [(TRUNCATION_STAGES[n], v) for n, v in stages]
+        out, probs = ops32.sample_truncated(logits, [0.8, 1.1], [7, 8], [11, 12], numbered, want_probs=True)
+        host = logits.cpu().numpy()
+        for r in range(2):
+            want = truncated_probs(host[r], [0.8, 1.1][r], stages)
+            got = probs[r].cpu().numpy()
+            assert (got > 0).tolist() == (want > 0).tolist()
+            assert np.abs(got - want).max() < 1e-13
+            assert int(out[r]) == select(want, uniform([7, 8][r], [11, 12][r]))
+
+
+def test_sampler_routes_rows_with_stages_through_the_pipeline(ops32):
+    from leone_b200.sampling.sampler import Sampler, SamplingParams
+    from tests.plain.model import sample as plain_sample
+    vocab = 500
+    logits = _randn((5, vocab), 123, scale=3.0)
+    params = [SamplingParams(), SamplingParams(0.9, 3), SamplingParams(0.9, 3, (("top_k", 5),)),
+              SamplingParams(0.0, 1, (("top_k", 5),)), SamplingParams(1.2, 9, (("min_p", 0.1), ("top_p", 0.8)))]
+    positions = [4, 5, 6, 7, 8]
+    got = Sampler(ops32, DEV).sample(logits, params, positions).tolist()
+    host = logits.cpu().numpy()
+    want = [plain_sample(host[i].tolist(), p.temperature, p.seed, positions[i], p.truncations)
+            for i, p in enumerate(params)]
+    assert got == want
+    with pytest.raises(ValueError, match="valid range"):
+        SamplingParams(1.0, 0, (("top_p", 1.5),))
+    with pytest.raises(ValueError, match="unknown"):
+        SamplingParams(1.0, 0, (("top_q", 0.5),))

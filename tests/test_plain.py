@@ -74,3 +74,44 @@ def test_whole_model_prefix_property(tmp_path):
     b = m.logits([5, 9, 200, 1, 1])
     assert torch.allclose(a[:3], b[:3]) and not torch.allclose(a[3], b[3])
     assert a.shape == (5, 384)
+
+
+def test_truncation_stages_of_the_plain_sampler():
+    """Each stage on a small row, against what its definition gives by hand
+    (crates/leone/src/sampler.rs:184-234)."""
+    import math
+    import numpy as np
+    from tests.plain.model import truncated_probs
+    logits = [2.0, 1.0, 0.0, -1.0, float("-inf"), 1.0]
+    base = truncated_probs(logits, 1.0, [])
+    w = np.array([math.exp(x - 2.0) if math.isfinite(x) else 0.0 for x in logits])
+    assert np.allclose(base, w / w.sum(), atol=1e-15) and base[4] == 0.0
+    # top-k 2: the highest, and of the two tied at 1.0 the lower id
+    p = truncated_probs(logits, 1.0, [("top_k", 2)])
+    assert (p > 0).tolist() == [True, True, False, False, False, False] and abs(p.sum() - 1) < 1e-15
+    # top-p: the shortest prefix whose mass reaches p
+    order = [0, 1, 5, 2, 3]
+    cum = np.cumsum([base[i] for i in order])
+    for mass in (0.3, 0.6, 0.8, 0.99):
+        p = truncated_probs(logits, 1.0, [("top_p", mass)])
+        assert int((p > 0).sum()) == int(np.searchsorted(cum, mass) + 1)
+    # min-p: at least a fraction of the highest
+    p = truncated_probs(logits, 1.0, [("min_p", 0.3)])
+    assert (p > 0).tolist() == [bool(b >= 0.3 * base[0]) for b in base]
+    # stages see the renormalised survivors of the stage before
+    two = truncated_probs(logits, 1.0, [("top_k", 3), ("epsilon", 0.25)])
+    three = truncated_probs(logits, 1.0, [("top_k", 3)])
+    assert (two > 0).tolist() == [bool(b >= 0.25) for b in three]
+    # typical can drop the most probable token when it is atypically certain
+    peaked = [6.0] + [0.0] * 600           # 0.4 on one token, 0.001 on each of 600: entropy 4.5 nats
+    p = truncated_probs(peaked, 1.0, [("typical", 0.2)])
+    assert p[0] == 0.0 and 195 < (p > 0).sum() < 210 and abs(p.sum() - 1) < 1e-12
+    # the raw-logit stages do not depend on the temperature
+    rng = np.random.default_rng(3)
+    row = (rng.normal(size=200) * 2).tolist()
+    for stage in (("top_n_sigma", 1.5), ("min_k", 3.0)):
+        a = truncated_probs(row, 0.5, [stage]) > 0
+        b = truncated_probs(row, 2.0, [stage]) > 0
+        assert a.tolist() == b.tolist() and 1 <= a.sum() < 200
+    # no stage empties the set
+    assert (truncated_probs(row, 1.0, [("epsilon", 1.0), ("top_a", 1.0), ("tfs", 1e-9)]) > 0).sum() == 1
