@@ -51,6 +51,9 @@ def cmd_generate(args) -> int:
             return 2
     from .engine.engine import Engine
     from .engine.generate import generate
+    from .sampling.sampler import Penalties
+    penalties = Penalties(args.repeat_penalty, args.presence_penalty, args.frequency_penalty, args.penalty_window,
+                          args.dry_multiplier, args.dry_base, args.dry_allowed_length, args.dry_window)
     prompts = [parse_token_ids(t) for t in args.prompt_tokens]
     longest = max(len(p) for p in prompts) + args.tokens
     pages = args.num_pages or (-(-longest // args.page_tokens) + 1) * len(prompts)
@@ -64,7 +67,8 @@ def cmd_generate(args) -> int:
                           eos_token_id=args.eos, prefill_chunk=args.prefill_chunk,
                           max_batch_tokens=args.max_batch_tokens, return_stats=True,
                           use_graphs=not args.eager_decode and not args.debug_logits,
-                          decode_quantum=args.decode_quantum, truncations=tuple(args.truncations or ()))
+                          decode_quantum=args.decode_quantum, truncations=tuple(args.truncations or ()),
+                          penalties=penalties if penalties.active else None)
     for toks in out:
         print(",".join(str(t) for t in toks))
     if args.debug_tokens:
@@ -230,6 +234,15 @@ def build_parser() -> argparse.ArgumentParser:
             ("--top-n-sigma", "top_n_sigma", float, "Keep raw logits within n deviations of the peak")):
         g.add_argument(flag, dest=dest, type=kind, action=Stage, help=text)
     g.set_defaults(truncations=None)
+    # crates/leone-cli/src/main.rs:850-857
+    g.add_argument("--repeat-penalty", type=float, default=1.0, help="Apply sign-aware scaling to seen logits. 1.0 is off")
+    g.add_argument("--presence-penalty", type=float, default=0.0, help="Subtract once from any seen token")
+    g.add_argument("--frequency-penalty", type=float, default=0.0, help="Subtract once per earlier occurrence")
+    g.add_argument("--penalty-window", type=int, default=64, help="Tokens considered. Zero disables. Default: 64")
+    g.add_argument("--dry-multiplier", type=float, default=0.0, help="Enable the repeated-suffix penalty. 0.0 is off")
+    g.add_argument("--dry-base", type=float, default=1.75, help="Growth per token of match. Default: 1.75")
+    g.add_argument("--dry-allowed-length", type=int, default=2, help="Free match length. Default: 2")
+    g.add_argument("--dry-window", type=int, default=64, help="Tokens of history searched. Default: 64")
     g.add_argument("--eager-decode", action="store_true", help="disable decode graph replay")
     g.add_argument("--kv", choices=["q8", "f16", "f32", "bf16"], default=None,
                    help="KV cache storage; only the run dtype is available")

@@ -488,6 +488,35 @@ select_kernel(int vocab, int P, uint8_t* scratch, const long long* __restrict__ 
   }
 }
 
+// Penalties from the decode history, before the sampler (crates/leone/src/penalty.rs:163-206).
+// The host has walked the history (it owns it) and lists, per (row, token), how often the token
+// occurs in the row's window and the largest repeated-suffix (DRY) penalty that reaches it; the
+// arithmetic on the logits is done here, in fp64 as there: a seen token's logit is divided by
+// the repetition factor if positive, multiplied if not, then loses the presence penalty once
+// and the frequency penalty per occurrence, and is rounded to fp32; the DRY penalty is then
+// subtracted from that.
+__global__ void penalize_kernel(float* __restrict__ logits, int vocab, int n, const int* __restrict__ rows,
+                                const int* __restrict__ tokens, const int* __restrict__ counts,
+                                const double* __restrict__ dry, const double* __restrict__ repetition,
+                                const double* __restrict__ presence, const double* __restrict__ frequency) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= n) return;
+  const int row = rows[e], token = tokens[e];
+  if (token < 0 || token >= vocab) return;
+  float* at = logits + (size_t)row * vocab + token;
+  float logit = *at;
+  const double rep = repetition[row], pres = presence[row], freq = frequency[row];
+  if (counts[e] > 0 && (rep != 1.0 || pres != 0.0 || freq != 0.0)) {
+    double value = (double)logit;
+    value = value > 0.0 ? value / rep : value * rep;
+    value -= pres;
+    value -= freq * (double)counts[e];
+    logit = (float)value;
+  }
+  if (dry[e] > 0.0) logit = (float)((double)logit - dry[e]);
+  *at = logit;
+}
+
 }  // namespace samp
 }  // namespace leone
 
@@ -542,5 +571,18 @@ extern "C" int leone_sample_truncated(const float* logits, int rows, int vocab, 
     done = cut + 1;
   }
   select_kernel<<<rows, kThreads, 0, stream>>>(vocab, P, sc, seeds, positions, out, probs);
+  return (int)cudaGetLastError();
+}
+
+// logits: fp32 [.., vocab], changed in place at the n listed (row, token) entries (each at most
+// once); counts: occurrences in the row's window (0: only the DRY penalty applies); dry: the DRY
+// penalty (0: none); repetition, presence, frequency: fp64 per row.
+extern "C" int leone_penalize(float* logits, int vocab, int n, const int* rows, const int* tokens,
+                              const int* counts, const double* dry, const double* repetition,
+                              const double* presence, const double* frequency, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (vocab <= 0) return kRefusedSize;
+  penalize_kernel<<<(n + 255) / 256, 256, 0, stream>>>(logits, vocab, n, rows, tokens, counts, dry, repetition,
+                                                      presence, frequency);
   return (int)cudaGetLastError();
 }

@@ -45,7 +45,7 @@ def generate(model: Union[str, Engine], prompts: Sequence[Sequence[int]], max_ne
              num_pages: Optional[int] = None, prefill_chunk: int = 2048,
              max_batch_tokens: int = 2048, max_running: int = 64, policy: str = "reserve",
              device: str = "cuda:0", return_stats: bool = False, decode_quantum: int = 1,
-             use_graphs: bool = True, prefill_first: bool = True, truncations=()):
+             use_graphs: bool = True, prefill_first: bool = True, truncations=(), penalties=None):
     """Generate ``max_new_tokens`` tokens for each prompt (a list of token ids).
 
     ``model`` is a model folder (config.json + model.safetensors) or an :class:`Engine`.
@@ -57,7 +57,9 @@ def generate(model: Union[str, Engine], prompts: Sequence[Sequence[int]], max_ne
     ``truncations``: ``(stage, value)`` pairs applied in order after the temperature (top_k,
     top_p, min_p, top_a, tfs, typical, epsilon, eta, min_k, top_n_sigma: the reference's
     ``--top-k`` .. ``--top-n-sigma``, crates/leone-cli/src/main.rs:836-845); such requests decode
-    step by step outside the captured graph.
+    step by step outside the captured graph.  ``penalties``: a
+    :class:`leone_b200.sampling.sampler.Penalties` applied to the logits from each request's own
+    history before sampling (greedy included).
     """
     prompts = [list(map(int, p)) for p in prompts]
     if isinstance(model, Engine):
@@ -78,7 +80,7 @@ def generate(model: Union[str, Engine], prompts: Sequence[Sequence[int]], max_ne
                                               decode_quantum=decode_quantum, use_graphs=use_graphs,
                                               prefill_first=prefill_first))
     for i, p in enumerate(prompts):
-        sched.add_request(i, p, max_new_tokens, SamplingParams(temperature, seed + i, tuple(truncations)), eos_token_id)
+        sched.add_request(i, p, max_new_tokens, SamplingParams(temperature, seed + i, tuple(truncations), penalties), eos_token_id)
     stats = GenerationStats(prompt_tokens=sum(len(p) for p in prompts))
     t0 = time.perf_counter()
     first_done = None

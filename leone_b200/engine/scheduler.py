@@ -287,8 +287,11 @@ class Scheduler:
         self._steps += 1
         self._max_batch_tokens_seen = max(self._max_batch_tokens_seen, sum(c for _, _, c in plan))
         if sampled_reqs:
+            kw = {}
+            if any(getattr(r.sampling, "penalizes", False) for r in sampled_reqs):
+                kw["histories"] = [r.tokens for r in sampled_reqs]      # the whole history, prompt included
             ids = self.engine.sample(logits, [r.sampling for r in sampled_reqs],
-                                     [len(r.tokens) - 1 for r in sampled_reqs])
+                                     [len(r.tokens) - 1 for r in sampled_reqs], **kw)
             for req, tok in zip(sampled_reqs, ids):
                 reason = self._emitted(req, int(tok))
                 outputs.append(StepOutput(req.rid, int(tok), reason is not None, reason))
@@ -297,9 +300,9 @@ class Scheduler:
     @staticmethod
     def _decode_only(plan) -> bool:
         """Every entry is a decode row that the captured step can sample (greedy or temperature;
-        truncation stages run outside the graph)."""
+        truncation stages and penalties run outside the graph)."""
         return all(count == 1 and req.generated and start == len(req.tokens) - 1
-                   and not getattr(req.sampling, "truncates", False) for req, start, count in plan)
+                   and not getattr(req.sampling, "outside_graph", False) for req, start, count in plan)
 
     def _decode_quantum(self, reqs: List[Request]) -> List[StepOutput]:
         """Several decode steps of the same requests without the host in between.  A request

@@ -345,6 +345,24 @@ class CudaOps:
         _check(self.core.leone_sample(_ptr(logits), rows, vocab, _ptr(temperature), _ptr(seeds),
                                       _ptr(positions), _ptr(out), self._stream()), "sample")
 
+    def penalize(self, logits, entries, penalties):
+        """Penalties from the decode history, in place: ``entries`` lists (row, token, occurrences
+        in the row's window, DRY penalty), each (row, token) once; ``penalties[row]`` holds the
+        row's repetition, presence and frequency factors (``csrc/sampling_pipeline.cu``)."""
+        rows, vocab = logits.shape
+        _need(logits.dtype == torch.float32 and logits.is_contiguous(), "logits must be fp32")
+        _need(len(penalties) == rows and all(0 <= e[0] < rows for e in entries), "penalize: rows")
+        dev = self.device
+        ints = torch.tensor([[e[0] for e in entries], [e[1] for e in entries], [e[2] for e in entries]],
+                            dtype=torch.int32, device=dev)
+        dry = torch.tensor([e[3] for e in entries], dtype=torch.float64, device=dev)
+        per_row = torch.tensor([[p.repetition for p in penalties], [p.presence for p in penalties],
+                                [p.frequency for p in penalties]], dtype=torch.float64, device=dev)
+        self.launches += 1
+        _check(self.core.leone_penalize(_ptr(logits), vocab, len(entries), _ptr(ints[0]), _ptr(ints[1]),
+                                        _ptr(ints[2]), _ptr(dry), _ptr(per_row[0]), _ptr(per_row[1]),
+                                        _ptr(per_row[2]), self._stream()), "penalize")
+
     def sample_truncated(self, logits, temperatures, seeds, positions, stages, want_probs: bool = False):
         """Rows that sample through truncation stages: ``stages`` is a list of (stage number,
         value) applied in order to every row (``csrc/sampling_pipeline.cu``).  Returns the ids

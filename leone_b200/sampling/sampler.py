@@ -16,14 +16,18 @@ The reference's truncation stages (crates/leone/src/sampler.rs:184-234: top-k, t
 top-a, tail-free, typical, epsilon, eta, min-k, top-n-sigma, applied in the order given, each
 on the renormalised survivors of the one before) run on the device too, in float64
 (``csrc/sampling_pipeline.cu``: a sort of the row, block-wide sums and scans, an id-order
-draw); rows that ask for them take that path, the others the single kernel.  Its penalties,
-Mirostat and grammar constraint (crates/leone/src/penalty.rs, crates/leone/src/sampler.rs:97-164)
-are not built.
+draw); rows that ask for them take that path, the others the single kernel.
+
+Its penalties (crates/leone/src/penalty.rs: repetition, presence and frequency over a window of
+the history, and the repeated-suffix penalty DRY) change the logits before any sampling, greedy
+included: the host walks the history it owns and lists which tokens are touched and how
+(:class:`Penalties`), a kernel does the arithmetic on the logits in float64.  Mirostat and the
+grammar constraint (crates/leone/src/sampler.rs:97-164) are not built.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Optional, Sequence, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -37,12 +41,93 @@ MAX_TRUNCATIONS = 16
 
 
 @dataclass(frozen=True)
+class Penalties:
+    """What is applied to a logit row before the sampler sees it
+    (crates/leone/src/penalty.rs:116-126; defaults :130-138, 81-89)."""
+    repetition: float = 1.0          # divides positive logits of seen tokens, multiplies the others; 1.0 is off
+    presence: float = 0.0            # subtracted once from any seen token
+    frequency: float = 0.0           # subtracted once per earlier occurrence
+    window: Optional[int] = 64       # tokens of history the three look at; 0 disables, None is all
+    dry_multiplier: float = 0.0      # the repeated-suffix penalty; 0.0 is off
+    dry_base: float = 1.75
+    dry_allowed_length: int = 2
+    dry_window: int = 64
+    dry_breakers: Tuple[int, ...] = ()
+
+    def __post_init__(self):
+        fin = np.isfinite
+        # crates/leone/src/penalty.rs:147-158, 92-107
+        if not (fin(self.repetition) and self.repetition > 0.0):
+            raise ValueError("the repetition penalty must be finite and greater than zero")
+        if not fin(self.presence):
+            raise ValueError("the presence penalty must be finite")
+        if not fin(self.frequency):
+            raise ValueError("the frequency penalty must be finite")
+        if self.window is not None and self.window < 0:
+            raise ValueError("the penalty window cannot be negative")
+        if not (fin(self.dry_multiplier) and self.dry_multiplier >= 0.0):
+            raise ValueError("the DRY multiplier is outside its valid range")
+        if not (fin(self.dry_base) and self.dry_base > 0.0):
+            raise ValueError("the DRY base is outside its valid range")
+        if self.dry_allowed_length < 1:
+            raise ValueError("the DRY allowed length is outside its valid range")
+        if self.dry_window < 0:
+            raise ValueError("the DRY window cannot be negative")
+
+    @property
+    def counting(self) -> bool:
+        return self.window != 0 and (self.repetition != 1.0 or self.presence != 0.0 or self.frequency != 0.0)
+
+    @property
+    def dry(self) -> bool:
+        return self.dry_multiplier > 0.0 and self.dry_window > 0
+
+    @property
+    def active(self) -> bool:
+        """Whether any penalty would change a logit (crates/leone/src/penalty.rs:141-145)."""
+        return self.counting or self.dry
+
+    def touched(self, context: Sequence[int]) -> Dict[int, Tuple[int, float]]:
+        """token -> (occurrences in the counting window, DRY penalty) for the history ``context``
+        (the whole of it, prompt included): which logits change; the arithmetic is the kernel's.
+        DRY (crates/leone/src/penalty.rs:208-257): for every earlier place in its window that
+        holds the last token, the length of the match that ends there against the history's end
+        (not across a breaker); from ``dry_allowed_length`` on, the token that followed that place
+        is charged ``multiplier * base ** (length - allowed)``, the largest charge if several."""
+        out: Dict[int, List] = {}
+        if self.counting:
+            recent = context if self.window is None else context[max(0, len(context) - self.window):]
+            for t in recent:
+                out.setdefault(int(t), [0, 0.0])[0] += 1
+        if self.dry:
+            recent = list(context[max(0, len(context) - self.dry_window):])
+            last = len(recent) - 1
+            for start in range(last):
+                if recent[start] != recent[last]:
+                    continue
+                length = 1
+                while (length <= start and length <= last and recent[start - length] == recent[last - length]
+                       and recent[last - length] not in self.dry_breakers):
+                    length += 1
+                if length < self.dry_allowed_length:
+                    continue
+                nxt = int(recent[start + 1])
+                if nxt in self.dry_breakers:
+                    continue
+                charge = self.dry_multiplier * self.dry_base ** (length - self.dry_allowed_length)
+                entry = out.setdefault(nxt, [0, 0.0])
+                entry[1] = max(entry[1], charge)
+        return {t: (c, d) for t, (c, d) in out.items()}
+
+
+@dataclass(frozen=True)
 class SamplingParams:
     temperature: float = 0.0     # 0 = greedy
     seed: int = 0
     # (stage name, value) pairs in the order they apply; greedy takes no notice of them
     # (crates/leone/src/sampler.rs:489-499 returns before any stage)
     truncations: Tuple[Tuple[str, float], ...] = ()
+    penalties: Optional[Penalties] = None
 
     def __post_init__(self):
         t = float(self.temperature)
@@ -71,6 +156,16 @@ class SamplingParams:
     def truncates(self) -> bool:
         return bool(self.truncations) and self.temperature > 0
 
+    @property
+    def penalizes(self) -> bool:
+        return self.penalties is not None and self.penalties.active
+
+    @property
+    def outside_graph(self) -> bool:
+        """Whether a request samples with more than the captured decode step holds (greedy and
+        temperature): truncation stages, or penalties, which need the history."""
+        return self.truncates or self.penalizes
+
 
 class Sampler:
     def __init__(self, ops, device, max_rows: int = 256):
@@ -88,11 +183,22 @@ class Sampler:
         self._out = torch.empty(rows, dtype=torch.int32, device=self.device)
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams],
-               positions: Sequence[int]) -> torch.Tensor:
-        """One token id per logits row, as an int32 device tensor."""
+               positions: Sequence[int], histories: Optional[Sequence[Sequence[int]]] = None) -> torch.Tensor:
+        """One token id per logits row, as an int32 device tensor.  ``histories``: every row's
+        whole token history (prompt included), needed by rows whose parameters hold penalties;
+        their logits are changed in place."""
         rows = logits.shape[0]
         if rows != len(params) or rows != len(positions):
             raise ValueError("sample: one SamplingParams and one position per logits row")
+        if any(p.penalizes for p in params):
+            if histories is None or len(histories) != rows:
+                raise ValueError("sample: penalties need every row's token history")
+            entries = [(i, t, c, d) for i, p in enumerate(params) if p.penalizes
+                       for t, (c, d) in p.penalties.touched(histories[i]).items()]
+            if entries:
+                neutral = Penalties()
+                self.ops.penalize(logits, entries, [(p.penalties or neutral) if p.penalizes else neutral
+                                                    for p in params])
         if rows > self._cap:
             self._grow(max(rows, 2 * self._cap))
         host = self._host.numpy()

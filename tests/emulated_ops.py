@@ -120,6 +120,19 @@ class EmulatedOps:
         for i in range(logits.shape[0]):
             out[i] = sample(logits[i].tolist(), float(temperature[i]), int(seeds[i]), int(positions[i]))
 
+    def penalize(self, logits, entries, penalties):
+        for row, token, count, dry in entries:
+            p = penalties[row]
+            value = logits[row, token].item()
+            if count > 0 and (p.repetition != 1.0 or p.presence != 0.0 or p.frequency != 0.0):
+                v = float(value)
+                v = v / p.repetition if v > 0.0 else v * p.repetition
+                v = v - p.presence - p.frequency * count
+                value = float(np.float32(v))
+            if dry > 0.0:
+                value = float(np.float32(float(value) - dry))
+            logits[row, token] = value
+
     def sample_truncated(self, logits, temperatures, seeds, positions, stages, want_probs=False):
         from leone_b200.sampling.sampler import TRUNCATION_STAGES
         from tests.plain.model import select, truncated_probs, uniform

@@ -363,6 +363,55 @@ def truncated_probs(logits, temperature, stages):
     return probs
 
 
+def apply_penalties(logits, context, repetition=1.0, presence=0.0, frequency=0.0, window=64,
+                    dry_multiplier=0.0, dry_base=1.75, dry_allowed_length=2, dry_window=64, dry_breakers=()):
+    """The logit row after the penalties, the slow and obvious way: every token of the vocabulary
+    is looked up in the history (crates/leone/src/penalty.rs:163-206).  A token seen in the last
+    ``window`` tokens (None: all, 0: none): positive logits are divided by ``repetition``, the
+    others multiplied; ``presence`` is subtracted once and ``frequency`` once per occurrence; the
+    result is rounded to float32.  DRY (:208-257): every earlier place in the last ``dry_window``
+    tokens that holds the last token starts a match backwards against the end of the history
+    (stopped by a breaker); from ``dry_allowed_length`` on, the token after that place is charged
+    ``multiplier * base ** (length - allowed)``, the largest charge counts, subtracted in float64
+    from the float32 logit."""
+    out = np.array(logits, dtype=np.float32)
+    context = [int(t) for t in context]
+    recent = [] if window == 0 else (context if window is None else context[max(0, len(context) - window):])
+    if repetition != 1.0 or presence != 0.0 or frequency != 0.0:
+        for token in range(len(out)):
+            count = sum(1 for t in recent if t == token)
+            if count == 0:
+                continue
+            value = float(out[token])
+            value = value / repetition if value > 0.0 else value * repetition
+            value -= presence
+            value -= frequency * count
+            out[token] = np.float32(value)
+    if dry_multiplier > 0.0 and dry_window > 0:
+        recent = context[max(0, len(context) - dry_window):]
+        if len(recent) >= 2:
+            last = len(recent) - 1
+            best = {}
+            for start in range(last):
+                if recent[start] != recent[last]:
+                    continue
+                length = 1
+                while (length <= start and recent[start - length] == recent[last - length]
+                       and recent[last - length] not in dry_breakers):
+                    length += 1
+                nxt = recent[start + 1]
+                if length < dry_allowed_length or nxt in dry_breakers or nxt >= len(out):
+                    continue
+                charge = dry_multiplier
+                for _ in range(length - dry_allowed_length):
+                    charge *= dry_base
+                best[nxt] = max(best.get(nxt, 0.0), charge)
+            for token, charge in best.items():
+                if charge > 0.0:
+                    out[token] = np.float32(float(out[token]) - charge)
+    return out
+
+
 def sample(logits, temperature, seed, position, truncations=()):
     if truncations and temperature:
         return select(truncated_probs(logits, temperature, truncations), uniform(seed, position))
@@ -371,7 +420,8 @@ def sample(logits, temperature, seed, position, truncations=()):
     return select(temperature_probs(logits, temperature), uniform(seed, position))
 
 
-def generate(model: PlainModel, prompt, max_new_tokens, temperature=0.0, seed=0, eos=None, truncations=()):
+def generate(model: PlainModel, prompt, max_new_tokens, temperature=0.0, seed=0, eos=None, truncations=(),
+             penalties=None):
     """Greedy/temperature generation by re-running the whole sequence each token.  The draw
     for a token uses the position of the token whose logits are sampled
     (crates/leone/src/runtime.rs:4945, 6080)."""
@@ -379,6 +429,8 @@ def generate(model: PlainModel, prompt, max_new_tokens, temperature=0.0, seed=0,
     out = []
     for _ in range(max_new_tokens):
         logits = model.logits(tokens)[-1].tolist()
+        if penalties:
+            logits = apply_penalties(np.array(logits, dtype=np.float32), tokens, **penalties).tolist()
         tok = sample(logits, temperature, seed, len(tokens) - 1, truncations)
         out.append(tok)
         tokens.append(tok)

@@ -167,3 +167,24 @@ def test_generation_with_truncation_stages(folders):
         unrestricted = generate(folders["B"], prompts, 7, temperature=1.1, seed=21, dtype="float32",
                                 page_tokens=8, eos_token_id=-1)
         assert unrestricted != got
+
+
+def test_generation_with_penalties(folders):
+    """Greedy and temperature generation with repetition, frequency and repeated-suffix penalties
+    over each request's own history, against the plain implementation; a prompt that repeats
+    itself, so that the penalties bite from the first token."""
+    from leone_b200 import generate
+    from leone_b200.sampling.sampler import Penalties
+    plain = PlainModel(folders["A"])
+    base = replay.random_tokens(256, 6, 77)
+    prompts = [base + base + base[:3], replay.random_tokens(256, 9, 78)]
+    kw = dict(repetition=1.4, frequency=0.3, window=32, dry_multiplier=1.5, dry_allowed_length=2)
+    for temperature in (0.0, 0.9):
+        want = [plain_generate(plain, p, 10, temperature=temperature, seed=5 + i, penalties=kw)
+                for i, p in enumerate(prompts)]
+        got = generate(folders["A"], prompts, 10, temperature=temperature, seed=5, dtype="float32", page_tokens=4,
+                       eos_token_id=-1, penalties=Penalties(**kw))
+        assert got == want
+        free = generate(folders["A"], prompts, 10, temperature=temperature, seed=5, dtype="float32", page_tokens=4,
+                        eos_token_id=-1)
+        assert free != got

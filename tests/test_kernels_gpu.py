@@ -878,3 +878,32 @@ def test_sampler_routes_rows_with_stages_through_the_pipeline(ops32):
         SamplingParams(1.0, 0, (("top_p", 1.5),))
     with pytest.raises(ValueError, match="unknown"):
         SamplingParams(1.0, 0, (("top_q", 0.5),))
+
+
+def test_penalize_matches_the_plain_penalties(ops32):
+    """The penalty kernel on rows with different settings and histories (ids past the vocabulary,
+    repeated suffixes, a row without penalties) against the plain implementation, bit for bit."""
+    from leone_b200.sampling.sampler import Penalties, Sampler, SamplingParams
+    from tests.plain.model import apply_penalties, sample as plain_sample
+    vocab = 300
+    rng = np.random.default_rng(11)
+    settings = [dict(repetition=1.3, presence=0.2, frequency=0.05, window=20),
+                dict(repetition=0.7, window=None, dry_multiplier=0.9, dry_allowed_length=1, dry_breakers=(7,)),
+                dict(), dict(frequency=-0.3, window=64, dry_multiplier=0.5, dry_base=2.0, dry_window=16)]
+    histories = []
+    for i in range(len(settings)):
+        h = rng.integers(0, 40, 50).tolist()
+        h = h + h[10:18] + [vocab + 5] + h[10:14]              # a repeated stretch, an id past the vocabulary
+        histories.append(h)
+    logits = _randn((len(settings), vocab), 200, scale=3.0)
+    host = logits.cpu().numpy().copy()
+    params = [SamplingParams(0.0 if i % 2 else 0.8, i, (), Penalties(**kw)) for i, kw in enumerate(settings)]
+    got = Sampler(ops32, DEV).sample(logits, params, [len(h) - 1 for h in histories], histories).tolist()
+    for i, kw in enumerate(settings):
+        want = apply_penalties(host[i], histories[i], **kw)
+        assert logits[i].cpu().numpy().tolist() == want.tolist(), f"row {i}"
+        if kw:
+            assert want.tolist() != host[i].tolist()
+        assert got[i] == plain_sample(want.tolist(), params[i].temperature, params[i].seed, len(histories[i]) - 1)
+    with pytest.raises(ValueError, match="history"):
+        Sampler(ops32, DEV).sample(logits, params, [0] * len(settings))

@@ -115,3 +115,45 @@ def test_truncation_stages_of_the_plain_sampler():
         assert a.tolist() == b.tolist() and 1 <= a.sum() < 200
     # no stage empties the set
     assert (truncated_probs(row, 1.0, [("epsilon", 1.0), ("top_a", 1.0), ("tfs", 1e-9)]) > 0).sum() == 1
+
+
+def test_penalties_of_the_plain_sampler_and_the_products_history_walk():
+    """The plain penalties on a hand-made case, and the product's list of touched tokens
+    (computed from the history on the host) against it on random histories."""
+    import numpy as np
+    from leone_b200.sampling.sampler import Penalties
+    from tests.plain.model import apply_penalties
+    logits = np.array([2.0, -1.0, 0.5, 3.0, -2.0, 1.0], dtype=np.float32)
+    out = apply_penalties(logits, [0, 1, 1, 5], repetition=2.0, presence=0.25, frequency=0.5)
+    assert out.tolist() == [2.0 / 2 - 0.25 - 0.5, -1.0 * 2 - 0.25 - 1.0, 0.5, 3.0, -2.0, 1.0 / 2 - 0.25 - 0.5]
+    assert apply_penalties(logits, [0, 1, 1, 5], repetition=2.0, window=0).tolist() == logits.tolist()
+    assert apply_penalties(logits, [0, 1, 1, 5], repetition=2.0, window=1).tolist() == [2.0, -1.0, 0.5, 3.0, -2.0, 0.5]
+    # DRY: "1 2 3 4 | 2 3 9 | 1 2 3": 4 would extend a match of three, 9 a match of two
+    out = apply_penalties(logits * 0, [1, 2, 3, 4, 2, 3, 5, 1, 2, 3], dry_multiplier=0.8)
+    assert np.allclose(out, [0, 0, 0, 0, -0.8 * 1.75, -0.8]) and out[1] == 0
+    out = apply_penalties(logits * 0, [1, 2, 3, 4, 2, 3, 5, 1, 2, 3], dry_multiplier=0.8, dry_breakers=(2,))
+    assert out.tolist() == [0.0] * 6               # the match cannot cross the breaker, one token is allowed free
+    rng = np.random.default_rng(5)
+    for trial in range(40):
+        vocab = 12
+        context = rng.integers(0, vocab + 3, int(rng.integers(0, 60))).tolist()     # some ids past the vocabulary
+        kw = dict(repetition=float(rng.choice([1.0, 1.3, 0.8])), presence=float(rng.choice([0.0, 0.4, -0.2])),
+                  frequency=float(rng.choice([0.0, 0.1])), window=rng.choice([None, 0, 5, 64]),
+                  dry_multiplier=float(rng.choice([0.0, 0.7])), dry_base=1.5, dry_allowed_length=int(rng.integers(1, 4)),
+                  dry_window=int(rng.choice([0, 8, 64])), dry_breakers=tuple(rng.integers(0, vocab, 2).tolist()))
+        kw["window"] = None if kw["window"] is None else int(kw["window"])
+        row = rng.normal(size=vocab).astype(np.float32)
+        want = apply_penalties(row, context, **kw)
+        p = Penalties(**kw)
+        got = row.copy()
+        for token, (count, dry) in (p.touched(context).items() if p.active else ()):
+            if token >= vocab:
+                continue
+            v = float(got[token])
+            if count > 0 and p.counting:
+                v = v / p.repetition if v > 0 else v * p.repetition
+                v = float(np.float32(v - p.presence - p.frequency * count))
+            if dry > 0:
+                v = float(np.float32(v - dry))
+            got[token] = v
+        assert got.tolist() == want.tolist(), (trial, kw)
