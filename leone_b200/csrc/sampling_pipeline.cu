@@ -444,6 +444,27 @@ typical_select_kernel(int vocab, int P, uint8_t* scratch, double mass) {
   if (threadIdx.x == 0) *r.n = m;
 }
 
+// Mirostat v2's filter (crates/leone/src/sampler.rs:383-420): of the distribution the stages
+// left (the target), the tokens whose surprise -ln p is at most the row's current maximum are
+// kept and renormalised (the most probable one if none is); the target's probabilities stay in
+// aux_f so that the draw can report the chosen token's.
+__global__ void __launch_bounds__(kThreads)
+surprise_filter_kernel(int vocab, int P, uint8_t* scratch, const double* __restrict__ maximum_surprise) {
+  __shared__ Shared sh;
+  const Row r = row_of(scratch, blockIdx.x, P, vocab);
+  const int n = *r.n;
+  __syncthreads();
+  if (n <= 0) return;
+  const double mu = maximum_surprise[blockIdx.x];
+  int first_out = n;
+  for (int i = threadIdx.x; i < n; i += kThreads) r.aux_f[i] = r.kept[i];
+  for (int i = threadIdx.x; i < n; i += kThreads)
+    if (!(-log(r.kept[i]) <= mu)) { first_out = i; break; }
+  const int keep = max(1, block_min(first_out, sh));
+  renormalize(r.kept, keep, sh);
+  if (threadIdx.x == 0) *r.n = keep;
+}
+
 __device__ __forceinline__ unsigned long long splitmix64(unsigned long long v) {
   unsigned long long z = v + 0x9e3779b97f4a7c15ull;
   z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
@@ -455,7 +476,8 @@ __device__ __forceinline__ unsigned long long splitmix64(unsigned long long v) {
 // the last id with any probability.
 __global__ void __launch_bounds__(kThreads)
 select_kernel(int vocab, int P, uint8_t* scratch, const long long* __restrict__ seeds,
-              const long long* __restrict__ positions, int* __restrict__ out, double* __restrict__ probs) {
+              const long long* __restrict__ positions, int* __restrict__ out, double* __restrict__ probs,
+              double* __restrict__ chosen_prob) {
   __shared__ Shared sh;
   const int row = blockIdx.x;
   const Row r = row_of(scratch, row, P, vocab);
@@ -480,12 +502,11 @@ select_kernel(int vocab, int P, uint8_t* scratch, const long long* __restrict__ 
   for (int i = threadIdx.x; i < vocab; i += kThreads)
     if (dense[i] > 0.0) last = i;
   last = -block_min(-last, sh);
-  if (threadIdx.x == 0) {
-    int token = at;
-    // the hit must be an id with probability: a zero entry cannot make the sum pass u
-    if (at == INT_MAX) token = last;
-    out[row] = token;
-  }
+  const int token = at == INT_MAX ? last : at;     // a zero entry cannot make the sum pass u
+  if (threadIdx.x == 0) out[row] = token;
+  if (chosen_prob != nullptr)                      // the token's probability before the surprise filter
+    for (int i = threadIdx.x; i < n; i += kThreads)
+      if (r.order[i] == token) chosen_prob[row] = r.aux_f[i];
 }
 
 // Penalties from the decode history, before the sampler (crates/leone/src/penalty.rs:163-206).
@@ -537,10 +558,13 @@ extern "C" long long leone_sample_truncated_scratch(int rows, int vocab) {
 // logits: fp32 [rows, vocab]; temperature: fp64 [rows] (> 0); seeds, positions: int64 [rows];
 // the stage list (types and values, in the order they apply) is the same for all rows; out: int32
 // [rows] sampled ids; probs: fp64 [rows, vocab] or null, the distribution the draw was made from.
+// maximum_surprise: fp64 [rows] or null: Mirostat v2's filter after the stages; chosen_prob (fp64
+// [rows], with it) gets the drawn token's probability before that filter.
 extern "C" int leone_sample_truncated(const float* logits, int rows, int vocab, const double* temperature,
                                       const long long* seeds, const long long* positions, int n_stages,
                                       const int* types, const double* values, void* scratch, int* out,
-                                      double* probs, cudaStream_t stream) {
+                                      double* probs, const double* maximum_surprise, double* chosen_prob,
+                                      cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (vocab <= 0 || n_stages < 0 || n_stages > kMaxStages) return kRefusedSize;
   Stages st;
@@ -570,7 +594,12 @@ extern "C" int leone_sample_truncated(const float* logits, int rows, int vocab, 
     typical_select_kernel<<<rows, kThreads, 0, stream>>>(vocab, P, sc, st.value[cut]);
     done = cut + 1;
   }
-  select_kernel<<<rows, kThreads, 0, stream>>>(vocab, P, sc, seeds, positions, out, probs);
+  if (maximum_surprise != nullptr) {
+    if (chosen_prob == nullptr) return kRefusedSize;
+    surprise_filter_kernel<<<rows, kThreads, 0, stream>>>(vocab, P, sc, maximum_surprise);
+  }
+  select_kernel<<<rows, kThreads, 0, stream>>>(vocab, P, sc, seeds, positions, out, probs,
+                                               maximum_surprise != nullptr ? chosen_prob : nullptr);
   return (int)cudaGetLastError();
 }
 

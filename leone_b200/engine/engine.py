@@ -284,13 +284,13 @@ class Engine:
         self.steps_run += 1
         return logits
 
-    def sample(self, logits: torch.Tensor, params, positions, histories=None) -> List[int]:
+    def sample(self, logits: torch.Tensor, params, positions, histories=None, states=None) -> List[int]:
         """One token per logits row (greedy, temperature, truncation stages; penalties if the
-        rows' token histories are given); returns host ints."""
+        rows' token histories are given, Mirostat if their sampler states are); returns host ints."""
         if self._sampler is None:
             from ..sampling.sampler import Sampler
             self._sampler = Sampler(self.ops, self.device)
-        return self._sampler.sample(logits, params, positions, histories).tolist()
+        return self._sampler.sample(logits, params, positions, histories, states).tolist()
 
     # -- decode quanta ------------------------------------------------------------------
     def decode_steps(self, rids: Sequence[Hashable], last_tokens: Sequence[int], params,

@@ -45,7 +45,7 @@ def generate(model: Union[str, Engine], prompts: Sequence[Sequence[int]], max_ne
              num_pages: Optional[int] = None, prefill_chunk: int = 2048,
              max_batch_tokens: int = 2048, max_running: int = 64, policy: str = "reserve",
              device: str = "cuda:0", return_stats: bool = False, decode_quantum: int = 1,
-             use_graphs: bool = True, prefill_first: bool = True, truncations=(), penalties=None):
+             use_graphs: bool = True, prefill_first: bool = True, truncations=(), penalties=None, mirostat=None):
     """Generate ``max_new_tokens`` tokens for each prompt (a list of token ids).
 
     ``model`` is a model folder (config.json + model.safetensors) or an :class:`Engine`.
@@ -59,7 +59,8 @@ def generate(model: Union[str, Engine], prompts: Sequence[Sequence[int]], max_ne
     ``--top-k`` .. ``--top-n-sigma``, crates/leone-cli/src/main.rs:836-845); such requests decode
     step by step outside the captured graph.  ``penalties``: a
     :class:`leone_b200.sampling.sampler.Penalties` applied to the logits from each request's own
-    history before sampling (greedy included).
+    history before sampling (greedy included).  ``mirostat``: ``(target surprise, learning rate)``
+    for Mirostat v2, which keeps a maximum surprise per request.
     """
     prompts = [list(map(int, p)) for p in prompts]
     if isinstance(model, Engine):
@@ -80,7 +81,8 @@ def generate(model: Union[str, Engine], prompts: Sequence[Sequence[int]], max_ne
                                               decode_quantum=decode_quantum, use_graphs=use_graphs,
                                               prefill_first=prefill_first))
     for i, p in enumerate(prompts):
-        sched.add_request(i, p, max_new_tokens, SamplingParams(temperature, seed + i, tuple(truncations), penalties), eos_token_id)
+        sched.add_request(i, p, max_new_tokens, SamplingParams(temperature, seed + i, tuple(truncations), penalties, mirostat),
+                          eos_token_id)
     stats = GenerationStats(prompt_tokens=sum(len(p) for p in prompts))
     t0 = time.perf_counter()
     first_done = None

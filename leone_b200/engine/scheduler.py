@@ -38,7 +38,7 @@ from dataclasses import dataclass, field
 from typing import Callable, Dict, Hashable, List, Optional, Sequence
 
 from ..cache.pages import OutOfPages, host_library
-from ..sampling.sampler import SamplingParams
+from ..sampling.sampler import SamplerState, SamplingParams
 
 _REJECTS = {1: "duplicate", 2: "empty_prompt", 3: "output_limit", 4: "token_id", 5: "prompt_limit",
             6: "kv_capacity", 7: "queue_limit"}
@@ -90,6 +90,7 @@ class Request:
     preemptions: int = 0
     cancel_requested: bool = False
     key: int = 0                                         # the planner's name for this request
+    sampler_state: Optional[SamplerState] = None         # what the sampler remembers between tokens
 
     @property
     def remaining_new(self) -> int:
@@ -181,6 +182,8 @@ class Scheduler:
         req = Request(rid, prompt, max_new_tokens, sampling or SamplingParams(), eos_token_id,
                       arrival=int(self._lib.leone_sched_get(self._h, c_longlong(key), 6)),
                       tokens=list(prompt), key=key)
+        if getattr(req.sampling, "mirostat", None):
+            req.sampler_state = SamplerState(req.sampling)
         self.requests[rid] = req
         self._by_key[key] = req
         return req
@@ -290,6 +293,8 @@ class Scheduler:
             kw = {}
             if any(getattr(r.sampling, "penalizes", False) for r in sampled_reqs):
                 kw["histories"] = [r.tokens for r in sampled_reqs]      # the whole history, prompt included
+            if any(r.sampler_state is not None for r in sampled_reqs):
+                kw["states"] = [r.sampler_state for r in sampled_reqs]
             ids = self.engine.sample(logits, [r.sampling for r in sampled_reqs],
                                      [len(r.tokens) - 1 for r in sampled_reqs], **kw)
             for req, tok in zip(sampled_reqs, ids):

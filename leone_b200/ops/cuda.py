@@ -363,10 +363,13 @@ class CudaOps:
                                         _ptr(ints[2]), _ptr(dry), _ptr(per_row[0]), _ptr(per_row[1]),
                                         _ptr(per_row[2]), self._stream()), "penalize")
 
-    def sample_truncated(self, logits, temperatures, seeds, positions, stages, want_probs: bool = False):
+    def sample_truncated(self, logits, temperatures, seeds, positions, stages, want_probs: bool = False,
+                         maximum_surprise=None):
         """Rows that sample through truncation stages: ``stages`` is a list of (stage number,
         value) applied in order to every row (``csrc/sampling_pipeline.cu``).  Returns the ids
-        as an int32 device tensor (and the fp64 distribution the draw was made from)."""
+        as an int32 device tensor (and the fp64 distribution the draw was made from).
+        ``maximum_surprise`` (one per row): Mirostat's filter after the stages; the drawn tokens'
+        probabilities before that filter are returned too (fp64 device tensor)."""
         import ctypes
         rows, vocab = logits.shape
         _need(logits.dtype == torch.float32 and logits.is_contiguous(), "logits must be fp32")
@@ -383,16 +386,23 @@ class CudaOps:
         pos = torch.tensor(positions, dtype=torch.int64, device=dev)
         out = torch.empty(rows, dtype=torch.int32, device=dev)
         probs = torch.empty((rows, vocab), dtype=torch.float64, device=dev) if want_probs else None
+        mu = chosen = None
+        if maximum_surprise is not None:
+            _need(len(maximum_surprise) == rows, "one maximum surprise a row")
+            mu = torch.tensor([float(m) for m in maximum_surprise], dtype=torch.float64, device=dev)
+            chosen = torch.zeros(rows, dtype=torch.float64, device=dev)
         n = len(stages)
         types = (ctypes.c_int * max(n, 1))(*[int(a) for a, _ in stages])
         values = (ctypes.c_double * max(n, 1))(*[float(b) for _, b in stages])
         self.launches += 1
         _check(self.core.leone_sample_truncated(_ptr(logits), rows, vocab, _ptr(t), _ptr(sd), _ptr(pos), n,
                                                 types, values, _ptr(self._sample_scratch), _ptr(out),
-                                                _ptr(probs), self._stream()), "sample_truncated")
+                                                _ptr(probs), _ptr(mu), _ptr(chosen), self._stream()),
+               "sample_truncated")
         if bool((out < 0).any()):
             raise ValueError("every logit of a row is non-finite, so no token can be sampled")
-        return (out, probs) if want_probs else out
+        result = (out,) + ((probs,) if want_probs else ()) + ((chosen,) if mu is not None else ())
+        return result if len(result) > 1 else out
 
     def decode_advance(self, token_ids, positions, ctx_len, sample_pos, sampled, history, counter):
         n = token_ids.numel()

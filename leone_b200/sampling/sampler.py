@@ -21,13 +21,21 @@ draw); rows that ask for them take that path, the others the single kernel.
 Its penalties (crates/leone/src/penalty.rs: repetition, presence and frequency over a window of
 the history, and the repeated-suffix penalty DRY) change the logits before any sampling, greedy
 included: the host walks the history it owns and lists which tokens are touched and how
-(:class:`Penalties`), a kernel does the arithmetic on the logits in float64.  Mirostat and the
-grammar constraint (crates/leone/src/sampler.rs:97-164) are not built.
+(:class:`Penalties`), a kernel does the arithmetic on the logits in float64.
+
+Mirostat v2 (crates/leone/src/sampler.rs:97-164, 383-420) keeps one number per request, the
+maximum surprise: after the stages, tokens more surprising than that are dropped, the draw is
+made from the rest, and the number moves by ``learning_rate * (observed - target)`` with the
+drawn token's surprise under the distribution before the drop (:class:`SamplerState`).  The
+grammar constraint is not built.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
+
+import math
+import sys
 
 import numpy as np
 import torch
@@ -120,6 +128,21 @@ class Penalties:
         return {t: (c, d) for t, (c, d) in out.items()}
 
 
+class SamplerState:
+    """What a request's sampler remembers between its tokens: Mirostat's maximum surprise, which
+    starts at twice the target (crates/leone/src/sampler.rs:138-144)."""
+
+    def __init__(self, params: "SamplingParams"):
+        self.maximum_surprise = 2.0 * params.mirostat[0] if params.mirostat else None
+
+    def observe(self, params: "SamplingParams", probability: float) -> None:
+        """The drawn token had this probability before the surprise filter
+        (crates/leone/src/sampler.rs:392-396)."""
+        target, rate = params.mirostat
+        self.maximum_surprise -= rate * (-math.log(probability) - target)
+        self.maximum_surprise = max(self.maximum_surprise, sys.float_info.epsilon)
+
+
 @dataclass(frozen=True)
 class SamplingParams:
     temperature: float = 0.0     # 0 = greedy
@@ -128,8 +151,17 @@ class SamplingParams:
     # (crates/leone/src/sampler.rs:489-499 returns before any stage)
     truncations: Tuple[Tuple[str, float], ...] = ()
     penalties: Optional[Penalties] = None
+    mirostat: Optional[Tuple[float, float]] = None      # (target surprise in nats, learning rate)
 
     def __post_init__(self):
+        if self.mirostat is not None:
+            target, rate = (float(v) for v in self.mirostat)
+            object.__setattr__(self, "mirostat", (target, rate))
+            # crates/leone/src/sampler.rs:111-123
+            if not (np.isfinite(target) and target > 0.0):
+                raise ValueError("the Mirostat target must be finite and greater than zero")
+            if not (np.isfinite(rate) and 0.0 < rate <= 1.0):
+                raise ValueError("the Mirostat learning rate must be finite and in (0, 1]")
         t = float(self.temperature)
         if not (t >= 0.0) or t == float("inf"):
             # crates/leone/src/sampler.rs:330-336: a temperature must be finite and > 0
@@ -163,8 +195,9 @@ class SamplingParams:
     @property
     def outside_graph(self) -> bool:
         """Whether a request samples with more than the captured decode step holds (greedy and
-        temperature): truncation stages, or penalties, which need the history."""
-        return self.truncates or self.penalizes
+        temperature): truncation stages, penalties (which need the history), Mirostat (which
+        keeps a number per request)."""
+        return self.truncates or self.penalizes or self.mirostat is not None
 
 
 class Sampler:
@@ -183,10 +216,12 @@ class Sampler:
         self._out = torch.empty(rows, dtype=torch.int32, device=self.device)
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams],
-               positions: Sequence[int], histories: Optional[Sequence[Sequence[int]]] = None) -> torch.Tensor:
+               positions: Sequence[int], histories: Optional[Sequence[Sequence[int]]] = None,
+               states: Optional[Sequence[Optional[SamplerState]]] = None) -> torch.Tensor:
         """One token id per logits row, as an int32 device tensor.  ``histories``: every row's
         whole token history (prompt included), needed by rows whose parameters hold penalties;
-        their logits are changed in place."""
+        their logits are changed in place.  ``states``: every row's :class:`SamplerState`,
+        needed (and updated) by rows with Mirostat."""
         rows = logits.shape[0]
         if rows != len(params) or rows != len(positions):
             raise ValueError("sample: one SamplingParams and one position per logits row")
@@ -215,15 +250,28 @@ class Sampler:
         out = self._out[:rows]
         self.ops.sample(logits, t, seeds, pos, out)
         # rows with truncation stages: grouped by their stage list, through the fp64 pipeline
+        if any(p.mirostat for p in params) and (states is None or len(states) != rows or any(
+                p.mirostat and states[i] is None for i, p in enumerate(params))):
+            raise ValueError("sample: Mirostat needs every such row's SamplerState")
         groups = {}
         for i, p in enumerate(params):
-            if p.truncates:
-                groups.setdefault(p.truncations, []).append(i)
-        for stages, members in groups.items():
+            if p.temperature > 0 and (p.truncations or p.mirostat):
+                groups.setdefault((p.truncations, p.mirostat is not None), []).append(i)
+        for (stages, surprise), members in groups.items():
             index = torch.tensor(members, dtype=torch.int64, device=logits.device)
-            picked = self.ops.sample_truncated(
+            got = self.ops.sample_truncated(
                 logits.index_select(0, index), [float(params[i].temperature) for i in members],
                 [params[i].seed for i in members], [int(positions[i]) for i in members],
-                [(TRUNCATION_STAGES[n], v) for n, v in stages])
+                [(TRUNCATION_STAGES[n], v) for n, v in stages],
+                maximum_surprise=[states[i].maximum_surprise for i in members] if surprise else None)
+            if surprise:
+                picked, chosen = got
+                for i, p_ in zip(members, chosen.tolist()):
+                    states[i].observe(params[i], p_)
+            else:
+                picked = got
             out.index_copy_(0, index, picked)
+        for i, p in enumerate(params):
+            if p.mirostat and not p.temperature > 0:
+                states[i].observe(p, 1.0)       # greedy: the one token has probability one
         return out

@@ -133,12 +133,18 @@ class EmulatedOps:
                 value = float(np.float32(float(value) - dry))
             logits[row, token] = value
 
-    def sample_truncated(self, logits, temperatures, seeds, positions, stages, want_probs=False):
+    def sample_truncated(self, logits, temperatures, seeds, positions, stages, want_probs=False,
+                         maximum_surprise=None):
         from leone_b200.sampling.sampler import TRUNCATION_STAGES
-        from tests.plain.model import select, truncated_probs, uniform
+        from tests.plain.model import mirostat_select, select, truncated_probs, uniform
+        import math
         names = {v: k for k, v in TRUNCATION_STAGES.items()}
         named = [(names[t], v) for t, v in stages]
         rows = [truncated_probs(logits[i].tolist(), temperatures[i], named) for i in range(logits.shape[0])]
+        if maximum_surprise is not None:
+            drawn = [mirostat_select(p, maximum_surprise[i], uniform(seeds[i], positions[i])) for i, p in enumerate(rows)]
+            return (torch.tensor([t for t, _ in drawn], dtype=torch.int32),
+                    torch.tensor([math.exp(-s_) for _, s_ in drawn], dtype=torch.float64))
         out = torch.tensor([select(p, uniform(seeds[i], positions[i])) for i, p in enumerate(rows)],
                            dtype=torch.int32)
         return (out, torch.tensor(np.stack(rows))) if want_probs else out

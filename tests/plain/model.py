@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import json
 import math
+import sys
 import os
 import struct
 
@@ -412,6 +413,19 @@ def apply_penalties(logits, context, repetition=1.0, presence=0.0, frequency=0.0
     return out
 
 
+def mirostat_select(target, maximum_surprise, u):
+    """Mirostat v2's draw (crates/leone/src/sampler.rs:383-420): of the target distribution the
+    tokens whose surprise -ln p is at most the maximum are kept (the most probable one if none
+    is) and renormalised, the token is drawn in id order, and its surprise under the target is
+    returned with it."""
+    kept = np.array([p if p > 0.0 and -math.log(p) <= maximum_surprise else 0.0 for p in target])
+    if kept.sum() == 0.0:
+        best = max(range(len(target)), key=lambda i: (target[i], -i))
+        kept[best] = target[best]
+    token = select(kept / kept.sum(), u)
+    return token, -math.log(target[token])
+
+
 def sample(logits, temperature, seed, position, truncations=()):
     if truncations and temperature:
         return select(truncated_probs(logits, temperature, truncations), uniform(seed, position))
@@ -421,16 +435,27 @@ def sample(logits, temperature, seed, position, truncations=()):
 
 
 def generate(model: PlainModel, prompt, max_new_tokens, temperature=0.0, seed=0, eos=None, truncations=(),
-             penalties=None):
+             penalties=None, mirostat=None):
     """Greedy/temperature generation by re-running the whole sequence each token.  The draw
     for a token uses the position of the token whose logits are sampled
     (crates/leone/src/runtime.rs:4945, 6080)."""
     tokens = list(prompt)
     out = []
+    maximum_surprise = 2.0 * mirostat[0] if mirostat else None      # crates/leone/src/sampler.rs:138-144
     for _ in range(max_new_tokens):
         logits = model.logits(tokens)[-1].tolist()
         if penalties:
             logits = apply_penalties(np.array(logits, dtype=np.float32), tokens, **penalties).tolist()
+        if mirostat and temperature:
+            target = truncated_probs(logits, temperature, truncations)
+            tok, observed = mirostat_select(target, maximum_surprise, uniform(seed, len(tokens) - 1))
+            maximum_surprise -= mirostat[1] * (observed - mirostat[0])
+            maximum_surprise = max(maximum_surprise, sys.float_info.epsilon)
+            out.append(tok)
+            tokens.append(tok)
+            if eos is not None and tok == eos:
+                break
+            continue
         tok = sample(logits, temperature, seed, len(tokens) - 1, truncations)
         out.append(tok)
         tokens.append(tok)

@@ -188,3 +188,21 @@ def test_generation_with_penalties(folders):
         free = generate(folders["A"], prompts, 10, temperature=temperature, seed=5, dtype="float32", page_tokens=4,
                         eos_token_id=-1)
         assert free != got
+
+
+def test_generation_with_mirostat(folders):
+    """Mirostat v2 with and without truncation stages and penalties through the entry point:
+    every request's maximum surprise follows its own tokens."""
+    from leone_b200 import generate
+    from leone_b200.sampling.sampler import Penalties
+    plain = PlainModel(folders["B"])
+    prompts = [replay.random_tokens(384, n, 500 + n) for n in (4, 13)]
+    pen = dict(frequency=0.2, window=8)
+    for case in (dict(mirostat=(3.0, 0.4)), dict(mirostat=(1.0, 1.0), truncations=(("top_p", 0.95),), penalties=pen)):
+        want = [plain_generate(plain, p, 9, temperature=1.0, seed=40 + i, **case) for i, p in enumerate(prompts)]
+        product = dict(case)
+        if "penalties" in product:
+            product["penalties"] = Penalties(**pen)
+        got = generate(folders["B"], prompts, 9, temperature=1.0, seed=40, dtype="float32", page_tokens=8,
+                       eos_token_id=-1, **product)
+        assert got == want

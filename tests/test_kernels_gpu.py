@@ -907,3 +907,28 @@ def test_penalize_matches_the_plain_penalties(ops32):
         assert got[i] == plain_sample(want.tolist(), params[i].temperature, params[i].seed, len(histories[i]) - 1)
     with pytest.raises(ValueError, match="history"):
         Sampler(ops32, DEV).sample(logits, params, [0] * len(settings))
+
+
+@pytest.mark.parametrize("vocab", [50, 5000])
+def test_mirostat_filter_matches_the_plain_sampler(ops32, vocab):
+    """Mirostat v2's surprise filter after the stages: the drawn ids and the drawn tokens'
+    probabilities before the filter, with maxima that keep everything, a part, and nothing
+    (the most probable token is then the only one left)."""
+    import math
+    from leone_b200.sampling.sampler import TRUNCATION_STAGES
+    from tests.plain.model import mirostat_select, truncated_probs, uniform
+    rows = 4
+    logits = _randn((rows, vocab), 300 + vocab, scale=2.0)
+    temps = [1.0, 0.8, 1.2, 1.0]
+    seeds, positions = [3, 4, 5, 6], [9, 10, 11, 12]
+    maxima = [50.0, 3.0, 1.0, 1e-9]
+    for stages in ([], [("top_k", 30), ("min_p", 0.01)]):
+        numbered = [(TRUNCATION_STAGES[n], v) for n, v in stages]
+        out, chosen = ops32.sample_truncated(logits, temps, seeds, positions, numbered, maximum_surprise=maxima)
+        host = logits.cpu().numpy()
+        for r in range(rows):
+            target = truncated_probs(host[r], temps[r], stages)
+            token, observed = mirostat_select(target, maxima[r], uniform(seeds[r], positions[r]))
+            assert int(out[r]) == token
+            assert abs(-math.log(float(chosen[r])) - observed) < 1e-12
+    assert int(out[3]) == int(torch.argmax(logits[3]))

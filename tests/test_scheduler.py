@@ -303,3 +303,42 @@ def test_the_native_planner_and_the_plain_scheduler_agree_step_by_step(seed):
         ra = a.requests[rid]
         assert (ra.state, ra.finish_reason, ra.generated, ra.tokens, ra.computed, ra.preemptions, ra.reserved_pages) == \
                (rb.state, rb.finish_reason, rb.generated, rb.tokens, rb.computed, rb.preemptions, rb.reserved_pages), rid
+
+
+def test_sampler_options_through_the_scheduler_on_emulated_kernels(tmp_path):
+    """Truncation stages, penalties and Mirostat through generate() and the scheduler (CPU
+    stand-in kernels), with few pages under the optimistic policy, so that a preempted request
+    is recomputed and its Mirostat state and history carry on: against the plain implementation
+    run on each request alone."""
+    from leone_b200.engine.engine import Engine
+    from leone_b200.engine.generate import generate
+    from leone_b200.sampling.sampler import Penalties
+    from tests import replay
+    from tests.emulated_ops import EmulatedOps
+    from tests.plain.model import PlainModel, generate as plain_generate
+    from tests.tiny import PAGE_TOKENS, make_folder
+    folder = make_folder(tmp_path, "B")
+    plain = PlainModel(folder)
+    prompts = [replay.random_tokens(plain.cfg["vocab_size"], n, 90 + n) for n in (2, 9, 16)]
+    stages = (("top_k", 20), ("typical", 0.9), ("min_p", 0.02))
+    pen = dict(repetition=1.2, presence=0.1, window=16, dry_multiplier=0.6)
+    cases = [dict(truncations=stages), dict(penalties=pen), dict(mirostat=(2.5, 0.3)),
+             dict(truncations=stages, penalties=pen, mirostat=(1.5, 0.5))]
+    for case in cases:
+        want = [plain_generate(plain, p, 7, 0.9, 30 + i, **case) for i, p in enumerate(prompts)]
+        product = dict(case)
+        if "penalties" in product:
+            product["penalties"] = Penalties(**pen)
+        for policy, pages in (("reserve", 12), ("optimistic", 7)):
+            eng = Engine.from_folder(folder, dtype="float32", device="cpu", ops=EmulatedOps(),
+                                     page_tokens=PAGE_TOKENS["B"], num_pages=pages, max_requests=3,
+                                     max_batch_tokens=16)
+            got = generate(eng, prompts, 7, temperature=0.9, seed=30, prefill_chunk=6, max_batch_tokens=16,
+                           policy=policy, eos_token_id=-1, prefill_first=False, **product)
+            assert got == want, (sorted(case), policy)
+            assert eng.cache.free_pages()[0] == pages
+    # greedy takes no notice of truncation stages; penalties still apply to it
+    want = [plain_generate(plain, p, 5, 0.0, 0, penalties=pen) for p in prompts]
+    eng = Engine.from_folder(folder, dtype="float32", device="cpu", ops=EmulatedOps(), page_tokens=PAGE_TOKENS["B"],
+                             num_pages=12, max_requests=3, max_batch_tokens=16)
+    assert generate(eng, prompts, 5, eos_token_id=-1, truncations=stages, penalties=Penalties(**pen)) == want
