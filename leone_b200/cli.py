@@ -89,14 +89,14 @@ def _wrap_sampling_for_debug(engine, rows) -> None:
     import torch
     inner = engine.sample
 
-    def sample(logits, params, positions):
+    def sample(logits, params, positions, **kw):
         top = torch.topk(logits.float(), k=min(5, logits.shape[1]), dim=1)
         for r in range(logits.shape[0]):
             rows.append({"position": int(positions[r]), "top": [
                 {"token": int(i), "logit": float(v),
                  "bits": f"{struct.unpack('<I', struct.pack('<f', float(v)))[0]:08x}"}
                 for v, i in zip(top.values[r].tolist(), top.indices[r].tolist())]})
-        return inner(logits, params, positions)
+        return inner(logits, params, positions, **kw)
 
     engine.sample = sample
 
