@@ -203,9 +203,31 @@ def bench_prefill_attention(ops, tokens, n_q, n_kv, d, page_tokens, reps, warmup
     return dict(kernel="attention_prefill", tokens=tokens, us=ms * 1e3, tflops=flops / ms / 1e9)
 
 
+def bench_sampling(ops, rows, vocab, stages, reps, warmup):
+    """The sampler's truncation pipeline (sort, stages, draw) on ``rows`` rows of ``vocab`` logits;
+    wall time with a synchronize on both sides (the call makes dozens of small launches)."""
+    import time
+    from .sampling.sampler import TRUNCATION_STAGES
+    logits = torch.randn((rows, vocab), device=DEV) * 3
+    numbered = [(TRUNCATION_STAGES[n], v) for n, v in stages]
+    args = (logits, [0.8] * rows, list(range(rows)), list(range(rows)), numbered)
+    for _ in range(warmup):
+        ops.sample_truncated(*args)
+    torch.cuda.synchronize()
+    t = time.perf_counter()
+    for _ in range(reps):
+        ops.sample_truncated(*args)
+    torch.cuda.synchronize()
+    return dict(kernel="sample_truncated", rows=rows, vocab=vocab, stages=[f"{n}={v}" for n, v in stages],
+                us=(time.perf_counter() - t) / reps * 1e6)
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m leone_b200.kernel_bench")
-    ap.add_argument("what", choices=["gemm", "decode-attention", "prefill-attention", "layer-shapes"])
+    ap.add_argument("what", choices=["gemm", "decode-attention", "prefill-attention", "layer-shapes", "sampling"])
+    ap.add_argument("--stages", default="top_k=40,top_p=0.95",
+                    help="sampling: truncation stages in order, e.g. top_k=40,typical=0.9")
+    ap.add_argument("--vocab", type=int, default=151936)
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -248,6 +270,9 @@ def main(argv=None) -> int:
                            token_major=None if args.token_major == "auto" else args.token_major == "1")
             r["name"] = name
             rows.append(r)
+    elif args.what == "sampling":
+        stages = [(n, float(v)) for n, v in (item.split("=") for item in args.stages.split(",") if item)]
+        rows.append(bench_sampling(ops, args.batch, args.vocab, stages, args.reps, args.warmup))
     elif args.what == "decode-attention":
         rows.append(bench_decode_attention(ops, args.batch, args.context, args.heads, args.kv_heads,
                                            args.head_dim, args.page_tokens, args.reps, args.warmup, flush, args.prep))
