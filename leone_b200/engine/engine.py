@@ -338,6 +338,32 @@ class Engine:
         self.steps_run += steps
         return tokens.tolist()
 
+    def decode_logits(self, rids: Sequence[Hashable], last_tokens: Sequence[int]) -> torch.Tensor:
+        """One decode step of ``rids`` from the captured graph, for a caller that samples itself:
+        returns the fp32 logits ``[len(rids), vocab]`` (the graph's own buffer, valid until the
+        next decode step); lengths advance by one.  The graph's built-in greedy draw is ignored."""
+        from ..sampling.sampler import SamplingParams
+        rids = list(rids)
+        self.drop_lookahead()
+        if self.device.type != "cuda":
+            return self.step([(r, [int(t)], [0]) for r, t in zip(rids, last_tokens)])
+        params = [SamplingParams() for _ in rids]
+        lengths, versions, slots, table_lens = self.cache.reserve_steps(rids, 1)
+        try:
+            if int(lengths.max()) + 1 > self.spec.max_positions:
+                raise ValueError("decode_logits would run past the model's positions")
+            state = dict(versions=versions, slots=slots, table_lens=table_lens)
+            graph = self._decode_graph(rids, last_tokens, lengths, params, state)
+            graph.fill(rids, last_tokens, lengths, params, **state)
+            graph.run(1)                    # reads and checks the status word
+        except Exception:
+            for r in rids:
+                self.cache.rollback(r)
+            raise
+        self.cache.commit_many(rids, lengths + 1)
+        self.steps_run += 1
+        return graph.logits
+
     def _decode_graph(self, rids, last_tokens, lengths, params, state):
         graph = self._decode_graphs.get(len(rids))
         if graph is None:

@@ -266,6 +266,12 @@ class Scheduler:
             try:
                 if self._decode_only(plan) and self.config.use_graphs and hasattr(self.engine, "decode_steps"):
                     return self._decode_quantum([req for req, _, _ in plan])
+                if (self._decode_rows(plan) and self.config.use_graphs and hasattr(self.engine, "decode_logits")):
+                    # requests whose sampler the captured step does not hold: the step still runs
+                    # from the graph, and its logits are sampled below like any other step's
+                    logits = self.engine.decode_logits([req.rid for req, _, _ in plan],
+                                                       [req.tokens[-1] for req, _, _ in plan])
+                    break
                 entries = []
                 for req, start, count in plan:
                     last = start + count == len(req.tokens)
@@ -303,11 +309,16 @@ class Scheduler:
         return outputs
 
     @staticmethod
-    def _decode_only(plan) -> bool:
-        """Every entry is a decode row that the captured step can sample (greedy or temperature;
-        truncation stages and penalties run outside the graph)."""
-        return all(count == 1 and req.generated and start == len(req.tokens) - 1
-                   and not getattr(req.sampling, "outside_graph", False) for req, start, count in plan)
+    def _decode_rows(plan) -> bool:
+        """Every entry feeds the one token its request sampled last."""
+        return all(count == 1 and req.generated and start == len(req.tokens) - 1 for req, start, count in plan)
+
+    @classmethod
+    def _decode_only(cls, plan) -> bool:
+        """Every entry is a decode row that the captured step can also sample (greedy or
+        temperature; truncation stages, penalties and Mirostat run outside the graph)."""
+        return cls._decode_rows(plan) and not any(getattr(req.sampling, "outside_graph", False)
+                                                  for req, _, _ in plan)
 
     def _decode_quantum(self, reqs: List[Request]) -> List[StepOutput]:
         """Several decode steps of the same requests without the host in between.  A request
