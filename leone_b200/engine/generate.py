@@ -56,8 +56,8 @@ def generate(model: Union[str, Engine], prompts: Sequence[Sequence[int]], max_ne
     generated ids per prompt (and a :class:`GenerationStats` if ``return_stats``).
     ``truncations``: ``(stage, value)`` pairs applied in order after the temperature (top_k,
     top_p, min_p, top_a, tfs, typical, epsilon, eta, min_k, top_n_sigma: the reference's
-    ``--top-k`` .. ``--top-n-sigma``, crates/leone-cli/src/main.rs:836-845); such requests decode
-    step by step outside the captured graph.  ``penalties``: a
+    ``--top-k`` .. ``--top-n-sigma``, crates/leone-cli/src/main.rs:836-845); such requests' decode
+    steps run from the captured graph one at a time and are sampled outside it.  ``penalties``: a
     :class:`leone_b200.sampling.sampler.Penalties` applied to the logits from each request's own
     history before sampling (greedy included).  ``mirostat``: ``(target surprise, learning rate)``
     for Mirostat v2, which keeps a maximum surprise per request.
