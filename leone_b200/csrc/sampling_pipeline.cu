@@ -97,13 +97,13 @@ __global__ void count_finite_kernel(int vocab, int P, uint8_t* scratch) {
 
 // All passes with stride below the tile for the levels k_first..k_last, in shared memory.
 __global__ void __launch_bounds__(kThreads)
-bitonic_tile_kernel(int which, int vocab, int P, uint8_t* scratch, int k_first, int k_last) {
+bitonic_tile_kernel(int which, int vocab, int P, int n_sort, uint8_t* scratch, int k_first, int k_last) {
   __shared__ double sk[kTile];
   __shared__ int si[kTile];
   const Row r = row_of(scratch, blockIdx.y, P, vocab);
   double* keys = which ? r.skeys : r.keys;
   int* idx = which ? r.sidx : r.order;
-  const int tile = P < kTile ? P : kTile;
+  const int tile = n_sort < kTile ? n_sort : kTile;
   const int base = blockIdx.x * tile;
   for (int t = threadIdx.x; t < tile; t += blockDim.x) {
     sk[t] = keys[base + t];
@@ -135,12 +135,12 @@ bitonic_tile_kernel(int which, int vocab, int P, uint8_t* scratch, int k_first, 
 }
 
 // One pass with a stride of at least a tile.
-__global__ void bitonic_global_kernel(int which, int vocab, int P, uint8_t* scratch, int k, int j) {
+__global__ void bitonic_global_kernel(int which, int vocab, int P, int n_sort, uint8_t* scratch, int k, int j) {
   const Row r = row_of(scratch, blockIdx.y, P, vocab);
   double* keys = which ? r.skeys : r.keys;
   int* idx = which ? r.sidx : r.order;
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
-  if (t >= (P >> 1)) return;
+  if (t >= (n_sort >> 1)) return;
   const int i = 2 * j * (t / j) + (t % j), l = i + j;
   const bool up = (i & k) == 0;
   const double ka = keys[i], kb = keys[l];
@@ -152,15 +152,50 @@ __global__ void bitonic_global_kernel(int which, int vocab, int P, uint8_t* scra
   }
 }
 
-static int sort_rows(int which, int vocab, int P, int rows, uint8_t* scratch, cudaStream_t stream) {
-  const int tile = P < kTile ? P : kTile;
-  bitonic_tile_kernel<<<dim3(P / tile, rows), kThreads, 0, stream>>>(which, vocab, P, scratch, 2, tile);
-  for (int k = 2 * tile; k <= P; k <<= 1) {
+// Sorts the first n_sort (a power of two) pairs of every row's first or second pair of arrays.
+// tiles_only: stop when every tile of 2,048 is sorted in itself.
+static int sort_rows(int which, int vocab, int P, int n_sort, int rows, uint8_t* scratch, cudaStream_t stream,
+                     bool tiles_only = false) {
+  const int tile = n_sort < kTile ? n_sort : kTile;
+  bitonic_tile_kernel<<<dim3(n_sort / tile, rows), kThreads, 0, stream>>>(which, vocab, P, n_sort, scratch, 2, tile);
+  for (int k = 2 * tile; k <= n_sort && !tiles_only; k <<= 1) {
     for (int j = k >> 1; j >= tile; j >>= 1)
-      bitonic_global_kernel<<<dim3((P / 2 + 255) / 256, rows), 256, 0, stream>>>(which, vocab, P, scratch, k, j);
-    bitonic_tile_kernel<<<dim3(P / tile, rows), kThreads, 0, stream>>>(which, vocab, P, scratch, k, k);
+      bitonic_global_kernel<<<dim3((n_sort / 2 + 255) / 256, rows), 256, 0, stream>>>(which, vocab, P, n_sort,
+                                                                                       scratch, k, j);
+    bitonic_tile_kernel<<<dim3(n_sort / tile, rows), kThreads, 0, stream>>>(which, vocab, P, n_sort, scratch, k, k);
   }
   return (int)cudaGetLastError();
+}
+
+// After the tiles are sorted in themselves, every tile alternately descending and ascending
+// (the network's direction at level kTile): the `take` best pairs of every tile, which hold the
+// row's `take` best, go to the front of the second pair of arrays (padded to n_out with pairs
+// that sort last).
+__global__ void gather_tile_heads_kernel(int vocab, int P, uint8_t* scratch, int take, int n_out) {
+  const Row r = row_of(scratch, blockIdx.y, P, vocab);
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_out) return;
+  const int tiles = P / kTile;
+  const int t = i / take, e = i - t * take;
+  if (t < tiles) {
+    // tile t is sorted descending ("up") if bit kTile of its base is clear, else ascending
+    const int base = t * kTile;
+    const int at = (base & kTile) == 0 ? base + e : base + kTile - 1 - e;
+    r.skeys[i] = r.keys[at];
+    r.sidx[i] = r.order[at];
+  } else {
+    r.skeys[i] = -INFINITY;
+    r.sidx[i] = vocab + P + i;
+  }
+}
+
+__global__ void take_heads_kernel(int vocab, int P, uint8_t* scratch, int count) {
+  const Row r = row_of(scratch, blockIdx.y, P, vocab);
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= P) return;
+  // the sorted heads become the row; what follows them is marked as excluded
+  r.keys[i] = i < count ? r.skeys[i] : -INFINITY;
+  r.order[i] = i < count ? r.sidx[i] : vocab + i;
 }
 
 // ---- block-wide fp64 helpers (one block of kThreads per row) ----------------------------------
@@ -577,8 +612,26 @@ extern "C" int leone_sample_truncated(const float* logits, int rows, int vocab, 
   const int P = pow2_at_least(vocab);
   uint8_t* sc = static_cast<uint8_t*>(scratch);
   sort_init_logits_kernel<<<dim3((P + 255) / 256, rows), 256, 0, stream>>>(logits, vocab, P, sc);
-  int e = sort_rows(0, vocab, P, rows, sc, stream);
-  if (e != 0) return e;
+  // A pipeline that starts with a small top-k and has no raw-logit stage needs only the row's k
+  // best pairs, which are among the k best of every tile: the tiles are sorted in themselves,
+  // their heads gathered and sorted, and the rest of the row is never ordered.
+  bool raw = false;
+  for (int s = 0; s < n_stages; ++s) raw = raw || st.type[s] == kMinK || st.type[s] == kTopNSigma;
+  const int tiles = P / kTile;
+  int e;
+  if (!raw && n_stages > 0 && st.type[0] == kTopK && P > kTile && st.value[0] * tiles <= 4 * kTile) {
+    const int take = (int)st.value[0];
+    const int n_out = pow2_at_least(take * tiles);
+    e = sort_rows(0, vocab, P, P, rows, sc, stream, true);
+    if (e != 0) return e;
+    gather_tile_heads_kernel<<<dim3((n_out + 255) / 256, rows), 256, 0, stream>>>(vocab, P, sc, take, n_out);
+    e = sort_rows(1, vocab, P, n_out, rows, sc, stream);
+    if (e != 0) return e;
+    take_heads_kernel<<<dim3((P + 255) / 256, rows), 256, 0, stream>>>(vocab, P, sc, take);
+  } else {
+    e = sort_rows(0, vocab, P, P, rows, sc, stream);
+    if (e != 0) return e;
+  }
   count_finite_kernel<<<dim3((P + 255) / 256, rows), 256, 0, stream>>>(vocab, P, sc);
   int done = 0;
   bool begun = false;
@@ -589,7 +642,7 @@ extern "C" int leone_sample_truncated(const float* logits, int rows, int vocab, 
     begun = true;
     if (cut >= n_stages) break;
     typical_scores_kernel<<<rows, kThreads, 0, stream>>>(vocab, P, sc);
-    e = sort_rows(1, vocab, P, rows, sc, stream);
+    e = sort_rows(1, vocab, P, P, rows, sc, stream);
     if (e != 0) return e;
     typical_select_kernel<<<rows, kThreads, 0, stream>>>(vocab, P, sc, st.value[cut]);
     done = cut + 1;

@@ -932,3 +932,31 @@ def test_mirostat_filter_matches_the_plain_sampler(ops32, vocab):
             assert int(out[r]) == token
             assert abs(-math.log(float(chosen[r])) - observed) < 1e-12
     assert int(out[3]) == int(torch.argmax(logits[3]))
+
+
+@pytest.mark.parametrize("vocab", [5000, 151936])
+def test_sample_truncated_small_top_k_first(ops32, vocab):
+    """A pipeline that starts with a small top-k orders only the heads of the row's tiles: equal
+    logits across tiles (ties go to the lower id), a row with fewer finite logits than k, the
+    largest k the short way takes and the first it does not."""
+    from leone_b200.sampling.sampler import TRUNCATION_STAGES
+    from tests.plain.model import select, truncated_probs, uniform
+    rows = 4
+    logits = _randn((rows, vocab), 400 + vocab, scale=2.0)
+    logits[1] = torch.round(logits[1])                         # thousands of equal logits
+    logits[2, 7:] = float("-inf")                              # seven finite logits
+    logits[3, ::3] = float("nan")
+    temps, seeds, positions = [0.9, 1.0, 1.1, 0.7], [5, 6, 7, 8], [1, 2, 3, 4]
+    tiles = (1 << (vocab - 1).bit_length()) // 2048
+    edge = 8192 // tiles
+    for stages in ([("top_k", 40), ("top_p", 0.9)], [("top_k", 1)], [("top_k", edge), ("min_p", 0.001)],
+                   [("top_k", edge + 1), ("tfs", 0.99)], [("top_k", 12), ("typical", 0.8), ("top_k", 3)]):
+        numbered = [(TRUNCATION_STAGES[n], v) for n, v in stages]
+        out, probs = ops32.sample_truncated(logits, temps, seeds, positions, numbered, want_probs=True)
+        host = logits.cpu().numpy()
+        for r in range(rows):
+            want = truncated_probs(host[r], temps[r], stages)
+            got = probs[r].cpu().numpy()
+            assert (got > 0).tolist() == (want > 0).tolist(), (stages, r)
+            assert np.abs(got - want).max() < 1e-13
+            assert int(out[r]) == select(want, uniform(seeds[r], positions[r]))
