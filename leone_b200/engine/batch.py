@@ -22,7 +22,6 @@ from typing import Dict, Hashable, List, Optional, Sequence
 import numpy as np
 import torch
 
-from ..parts.base import PagedCacheView, StateView
 
 
 @dataclass

@@ -17,7 +17,7 @@ from __future__ import annotations
 
 import gc
 import weakref
-from typing import Dict, Hashable, List, Sequence
+from typing import Hashable, List, Sequence
 
 import numpy as np
 import torch

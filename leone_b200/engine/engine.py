@@ -25,7 +25,6 @@ from ..parts.base import FixedState, PagedCacheView, PagedKV, Runtime, StateView
 from ..parts.spec import ModelSpec
 from ..registry import config_from_folder, spec_from_config
 from ..weights.loader import load_checkpoint
-from ..weights.random_init import random_tensors
 from .batch import StepContext, StepEntry, pack_metadata
 from .model import Model
 

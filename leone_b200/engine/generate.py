@@ -8,8 +8,8 @@ meanings are used here; prompts are token ids because no tokenizer is built.
 from __future__ import annotations
 
 import time
-from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence, Union
+from dataclasses import dataclass
+from typing import Optional, Sequence, Union
 
 from ..sampling.sampler import SamplingParams
 from .engine import Engine

@@ -7,8 +7,6 @@ matrices are stacked row-wise at load time so one product feeds both
 """
 from __future__ import annotations
 
-import torch
-
 from ..registry import FEED_FORWARDS
 from .base import DeferredNorm, FeedForward, WeightSpec
 

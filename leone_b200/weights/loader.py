@@ -12,7 +12,7 @@ become bfloat16 (float32 in a 32-bit run).  Integer tables become int32.
 """
 from __future__ import annotations
 
-from typing import Dict, List, Sequence
+from typing import Dict, Sequence
 
 import torch
 
