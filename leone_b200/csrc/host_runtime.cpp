@@ -725,6 +725,16 @@ int leone_sched_decoded(void* h, int n, const long long* rids, const int* is_eos
   return kOk;
 }
 
+// A finished or cancelled request is forgotten (its id may be used again).  Returns 1 if it was
+// known and is gone now, 0 otherwise (unknown, or still waiting or running).
+int leone_sched_forget(void* h, long long rid) {
+  Planner* p = static_cast<Planner*>(h);
+  SchedRequest* r = p->find(rid);
+  if (r == nullptr || r->state == kWaiting || r->state == kRunning) return 0;
+  p->requests.erase(rid);
+  return 1;
+}
+
 // The youngest running request other than `keep` (-1: none kept) goes back to the front of the
 // queue, to be recomputed from its first token; the caller closes it.  Returns 1 and the
 // victim, or 0 if nobody can be preempted.

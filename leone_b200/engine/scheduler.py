@@ -162,6 +162,17 @@ class Scheduler:
                     preemptions=self._count(5), admitted=self._count(2), finished=self._count(3),
                     cancelled=self._count(4), max_batch_tokens_seen=self._max_batch_tokens_seen)
 
+    def forget(self, rid: Hashable) -> Optional[Request]:
+        """Drop a finished or cancelled request from the scheduler's records (a long-lived
+        scheduler would otherwise keep every request it ever saw).  Returns it, or None if it is
+        unknown or still in flight."""
+        req = self.requests.get(rid)
+        if req is None or not self._lib.leone_sched_forget(self._h, c_longlong(req.key)):
+            return None
+        del self.requests[rid]
+        del self._by_key[req.key]
+        return req
+
     def has_work(self) -> bool:
         return self._count(0) + self._count(1) > 0
 

@@ -342,3 +342,19 @@ def test_sampler_options_through_the_scheduler_on_emulated_kernels(tmp_path):
     eng = Engine.from_folder(folder, dtype="float32", device="cpu", ops=EmulatedOps(), page_tokens=PAGE_TOKENS["B"],
                              num_pages=12, max_requests=3, max_batch_tokens=16)
     assert generate(eng, prompts, 5, eos_token_id=-1, truncations=stages, penalties=Penalties(**pen)) == want
+
+
+def test_a_finished_request_can_be_forgotten():
+    eng = FakeEngine(pages=16)
+    s = Scheduler(eng, SchedulerConfig())
+    s.add_request("a", [1, 2, 3], 2)
+    s.add_request("b", [4], 50)
+    assert s.forget("a") is None                    # still in flight
+    while s.requests["a"].state != "finished":
+        s.step()
+    done = s.forget("a")
+    assert done.generated == alone([1, 2, 3], 2) and "a" not in s.requests and s.forget("a") is None
+    s.add_request("a", [9], 1)                      # the name is free again
+    s.cancel("b")
+    _run(s)
+    assert s.forget("b").state == "cancelled" and s.requests["a"].generated == alone([9], 1)
