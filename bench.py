@@ -23,15 +23,17 @@ def main() -> int:
     ap.add_argument("--impl", default="leone_b200", choices=["leone_b200", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--context", type=int, default=2048)
+    ap.add_argument("--context", type=int, default=None, help="decode context (default: the shape's)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
+    ap.add_argument("--shape", default="qwen3-8b", choices=["qwen3-8b", "qwen3-1.7b", "qwen3-32b"],
+                    help="layer sizes (default: the headline Qwen3-8B shape)")
     args = ap.parse_args()
     if args.impl != "reference" and args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     from leone_b200.benchmark import run
     return run(args.gpus, args.steps, max(args.warmup, 3), args.impl, layers=args.layers,
-               batch=args.batch, context=args.context, points=not args.no_points)
+               batch=args.batch, context=args.context, points=not args.no_points, shape=args.shape)
 
 
 if __name__ == "__main__":

@@ -27,12 +27,12 @@ import torch
 QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=36, hidden_size=4096,
                 num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288,
                 vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6,
-                max_position_embeddings=4096, tie_word_embeddings=False)
+                max_position_embeddings=40960, tie_word_embeddings=False)   # positions as the checkpoints' config.json has them
 
 QWEN3_1_7B = dict(QWEN3_8B, num_hidden_layers=28, hidden_size=2048, num_attention_heads=16,
                   intermediate_size=6144, tie_word_embeddings=True)
 QWEN3_32B = dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64,
-                 intermediate_size=25600, max_position_embeddings=16384)
+                 intermediate_size=25600)
 # name -> (config, decode context, batch sizes measured beside the headline batch)
 SHAPES = {"qwen3-8b": (QWEN3_8B, 2048, (1, 64)), "qwen3-1.7b": (QWEN3_1_7B, 2048, (1, 64)),
           "qwen3-32b": (QWEN3_32B, 8192, (1, 32))}
@@ -125,8 +125,11 @@ def prefill_all(engine, rids, prompts, chunk: int) -> List[int]:
     return firsts
 
 
-def time_decode(engine, batch: int, context: int, steps: int, warmup: int, seed: int = 0):
-    """Device-timed decode: ``steps`` graph replays with tokens fed back on the device."""
+def time_decode(engine, batch: int, context: int, steps: int, warmup: int, seed: int = 0, reps: int = 5):
+    """Device-timed decode through ``Engine.decode_steps``: ``reps`` runs of exactly ``steps``
+    decode steps each (captured steps replayed in quanta of up to 64 with the sampled ids fed
+    back on the device, and read back once per quantum), CUDA events around each run; the
+    median run is reported."""
     from .sampling.sampler import SamplingParams
     vocab = engine.spec.vocab_size
     rids = [f"bench{batch}_{i}" for i in range(batch)]
@@ -134,29 +137,32 @@ def time_decode(engine, batch: int, context: int, steps: int, warmup: int, seed:
     firsts = prefill_all(engine, rids, prompts, engine.max_batch_tokens)
     params = [SamplingParams() for _ in rids]
     last = firsts
-    for _ in range(max(warmup, 1)):
-        last = engine.decode_steps(rids, last, params, 1)[-1]
-    engine.drop_lookahead()
+    last = engine.decode_steps(rids, last, params, max(warmup, 1))[-1]
+    times = []
+    mid = []
+    for _ in range(reps):
+        # every run starts from the same context length: the tokens of the run before are dropped
+        engine.drop_lookahead()
+        for r in rids:
+            engine.cache.truncate(r, context + max(warmup, 1))
+        mid.append(engine.cache.length(rids[0]) + steps / 2.0)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        done, feed = 0, last
+        while done < steps:
+            q = min(64, steps - done)
+            feed = engine.decode_steps(rids, feed, params, q)[-1]
+            done += q
+        stop.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(stop))
+    ms = statistics.median(times)
     graph = engine._decode_graphs[batch]
-    lengths = [engine.cache.length(r) for r in rids]
-    engine.cache.reserve({r: l + steps for r, l in zip(rids, lengths)})
-    graph.fill(rids, last, lengths, params)
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    start.record()
-    for _ in range(steps):
-        graph.graph.replay()
-    stop.record()
-    torch.cuda.synchronize()
-    ms = start.elapsed_time(stop)
-    engine.check_status()
-    for r, l in zip(rids, lengths):
-        engine.cache.commit(r, l + steps)
-    mid_ctx = lengths[0] + steps / 2.0
     for r in rids:
         engine.close(r)
-    return dict(ms_per_step=ms / steps, tokens_per_s=batch * steps / (ms / 1e3), mid_context=mid_ctx,
-                launches=graph.launches_per_step * steps)
+    return dict(ms_per_step=ms / steps, tokens_per_s=batch * steps / (ms / 1e3), mid_context=mid[0],
+                launches=graph.launches_per_step * steps, runs_ms=[round(t, 3) for t in times])
 
 
 def time_prefill(engine, tokens: int, reps: int = 5, seed: int = 99):
@@ -286,7 +292,7 @@ def run(gpus: int, steps: int, warmup: int, impl: str, layers: Optional[int] = N
     peaks = measured_peaks()
     page_tokens = 16
     big = max(other_batches + (batch,)) if points else batch
-    pool_tokens = big * (context + steps + warmup + 64)
+    pool_tokens = big * (context + steps + warmup + 128)
     t_build = time.time()
     engine = Engine.from_config(config, seed=0, dtype="bfloat16", page_tokens=page_tokens,
                                 max_tokens=pool_tokens, max_requests=max(big, batch),
@@ -351,7 +357,8 @@ def run(gpus: int, steps: int, warmup: int, impl: str, layers: Optional[int] = N
                    "max_context": cfg["max_position_embeddings"], "page_tokens": page_tokens,
                    "prefill_tokens": prefill_tokens, "parallelism": "1 gpu",
                    "cache_between_steps": "each step reads all weights (GBs), far beyond the 126 MB L2",
-                   "decode": "CUDA graph per step, sampled ids fed back on device"},
+                   "decode": "Engine.decode_steps: captured step replayed, sampled ids fed back on device, "
+                             "read back per quantum of 64; median of 5 runs of `steps` steps"},
         "clocks": clocks, "e2e": e2e, "gpu_launches": main["launches"], "prefill": prefill,
         "roofline": roofline, "points": extra, "impl": "leone_b200", "build_seconds": round(build_s, 1),
     }

@@ -141,14 +141,22 @@ class StateSlots(_FreeList):
 @dataclass
 class GroupSpec:
     """What a group of layers needs from the cache."""
-    kind: str                   # "full" or "window"
+    kind: str                   # "full" or "window": when pages go back to the pool
     num_kv_heads: int
-    head_dim: int
+    head_dim: int               # elements of a cached key row
     window: Optional[int] = None
     layers: List[int] = field(default_factory=list)
+    value_head_dim: Optional[int] = None    # elements of a cached value row (None: head_dim; 0: no values)
+    dtype: object = None        # storage dtype of the pages (None: the engine's run dtype)
+    tag: str = ""               # groups with different tags are never merged
 
     def key(self):
-        return (self.kind, self.num_kv_heads, self.head_dim, self.window)
+        return (self.kind, self.num_kv_heads, self.head_dim, self.window, self.value_head_dim, self.dtype, self.tag)
+
+    def page_elements(self, page_tokens: int):
+        """Elements of one page of one layer: (key pool, value pool)."""
+        vd = self.head_dim if self.value_head_dim is None else self.value_head_dim
+        return (self.num_kv_heads * page_tokens * self.head_dim, self.num_kv_heads * page_tokens * vd)
 
 
 @dataclass(frozen=True)

@@ -57,9 +57,14 @@ def cmd_generate(args) -> int:
     prompts = [parse_token_ids(t) for t in args.prompt_tokens]
     longest = max(len(p) for p in prompts) + args.tokens
     pages = args.num_pages or (-(-longest // args.page_tokens) + 1) * len(prompts)
-    engine = Engine.from_folder(args.model, dtype=args.dtype, page_tokens=args.page_tokens,
-                                num_pages=pages, max_requests=max(len(prompts), 1),
-                                max_batch_tokens=args.max_batch_tokens)
+    kw = dict(dtype=args.dtype, page_tokens=args.page_tokens, num_pages=pages, max_requests=max(len(prompts), 1),
+              max_batch_tokens=args.max_batch_tokens)
+    if args.random_weights:
+        from .engine.generate import load_config
+        engine = Engine.from_config(load_config(args.model),
+                                    args.seed if args.weights_seed is None else args.weights_seed, **kw)
+    else:
+        engine = Engine.from_folder(args.model, **kw)
     debug_rows = []
     if args.debug_logits:
         _wrap_sampling_for_debug(engine, debug_rows)
@@ -204,7 +209,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="leone", description="leone_b200 command line")
     sub = ap.add_subparsers(dest="command")
     g = sub.add_parser("generate", help="generate -m <dir> -t <token ids> -n <tokens> [options]")
-    g.add_argument("-m", "--model", required=True, help="model folder (config.json + model.safetensors)")
+    g.add_argument("-m", "--model", required=True,
+                   help="model folder (config.json + model.safetensors; with --random-weights config.json alone)")
     g.add_argument("-p", "--prompt", help="prompt text (refused: no tokenizer is built)")
     g.add_argument("-t", "--prompt-tokens", action="append",
                    help='prompt token ids: "1,2,3" or @file (u32le or .json); repeat for a batch')
@@ -243,6 +249,10 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--dry-base", type=float, default=1.75, help="Growth per token of match. Default: 1.75")
     g.add_argument("--dry-allowed-length", type=int, default=2, help="Free match length. Default: 2")
     g.add_argument("--dry-window", type=int, default=64, help="Tokens of history searched. Default: 64")
+    g.add_argument("--random-weights", action="store_true",
+                   help="read no tensor file: -m names a folder with config.json (or that file) and the "
+                        "weights are drawn from --weights-seed")
+    g.add_argument("--weights-seed", type=int, default=None, help="seed of --random-weights. Default: --seed")
     g.add_argument("--eager-decode", action="store_true", help="disable decode graph replay")
     g.add_argument("--kv", choices=["q8", "f16", "f32", "bf16"], default=None,
                    help="KV cache storage; only the run dtype is available")

@@ -134,6 +134,25 @@ class ModelConfig:
             json.dump(self.to_json_dict(), fh, indent=1)
 
 
+def read_stop_ids(raw: Mapping[str, Any], vocab_size: int) -> tuple:
+    """``eos_token_id`` as a tuple of ids: the key may hold one id or a list of them (every one
+    of which ends a request).  The reference stops on its tokenizer's single end id
+    (crates/leone/src/runtime.rs:5383); checkpoints of this architecture may list several."""
+    value = raw.get("eos_token_id")
+    if value is None:
+        return ()
+    ids = value if isinstance(value, list) else [value]
+    out = []
+    for i in ids:
+        if isinstance(i, bool) or not isinstance(i, int):
+            raise WrongType(f"config.json: 'eos_token_id' must be an integer or a list of integers, got {value!r}")
+        if not 0 <= i < vocab_size:
+            raise InvalidValue(f"config.json: eos_token_id {i} is outside the vocabulary ({vocab_size})")
+        if i not in out:
+            out.append(i)
+    return tuple(out)
+
+
 def read_config_json(folder: str) -> dict:
     path = os.path.join(folder, "config.json")
     if not os.path.isfile(path):
@@ -145,6 +164,16 @@ def read_config_json(folder: str) -> dict:
             raise ConfigError(f"{path}: not valid JSON ({err})") from None
     if not isinstance(raw, dict):
         raise WrongType(f"{path}: must hold a JSON object")
+    # generation_config.json beside it may name the stop ids when config.json does not
+    gen_path = os.path.join(folder, "generation_config.json")
+    if raw.get("eos_token_id") is None and os.path.isfile(gen_path):
+        try:
+            with open(gen_path) as fh:
+                gen = json.load(fh)
+        except json.JSONDecodeError as err:
+            raise ConfigError(f"{gen_path}: not valid JSON ({err})") from None
+        if isinstance(gen, dict) and gen.get("eos_token_id") is not None:
+            raw["eos_token_id"] = gen["eos_token_id"]
     return raw
 
 

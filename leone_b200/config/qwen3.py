@@ -11,9 +11,9 @@ reference requires ``head_dim == hidden_size / num_attention_heads``
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Mapping, Optional
+from typing import Any, Mapping, Optional, Tuple
 
-from .base import ConfigReader, InvalidValue, ModelConfig, UnsupportedField
+from .base import ConfigReader, InvalidValue, ModelConfig, UnsupportedField, read_stop_ids
 
 
 @dataclass(frozen=True)
@@ -30,9 +30,17 @@ class Qwen3Config(ModelConfig):
     max_position_embeddings: int = 0
     tie_word_embeddings: bool = False
     hidden_act: str = "silu"
-    eos_token_id: Optional[int] = None
+    eos_token_id: Optional[int] = None         # the first stop id
+    eos_token_ids: Tuple[int, ...] = ()        # all of them (config.json may list several)
 
     ARCHITECTURE = "Qwen3ForCausalLM"
+
+    def to_json_dict(self) -> dict:
+        out = super().to_json_dict()
+        ids = out.pop("eos_token_ids", ())
+        if len(ids) > 1:
+            out["eos_token_id"] = list(ids)
+        return out
 
     @classmethod
     def from_dict(cls, raw: Mapping[str, Any]) -> "Qwen3Config":
@@ -64,14 +72,9 @@ class Qwen3Config(ModelConfig):
         act = r.string("hidden_act", "silu")
         if act != "silu":
             raise UnsupportedField(f"config.json: hidden_act '{act}' is not supported (silu only)")
-        eos = raw.get("eos_token_id")
-        if isinstance(eos, list):
-            eos = eos[0] if eos else None
-        if eos is not None and (isinstance(eos, bool) or not isinstance(eos, int)):
-            eos = None
         vocab = r.positive_int("vocab_size")
-        if eos is not None and not 0 <= eos < vocab:
-            raise InvalidValue(f"config.json: eos_token_id {eos} is outside the vocabulary ({vocab})")
+        stop_ids = read_stop_ids(raw, vocab)
+        eos = stop_ids[0] if stop_ids else None
         return cls(
             architecture=cls.ARCHITECTURE,
             num_hidden_layers=r.positive_int("num_hidden_layers"),
@@ -87,4 +90,5 @@ class Qwen3Config(ModelConfig):
             tie_word_embeddings=r.boolean("tie_word_embeddings", False),
             hidden_act=act,
             eos_token_id=eos,
+            eos_token_ids=stop_ids,
         )

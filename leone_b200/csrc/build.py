@@ -28,16 +28,17 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 MODULES: Dict[str, List[str]] = {
     # every run needs these: both dtypes, every size
-    "core": ["elementwise.cu", "gemm_simt.cu", "attention_generic.cu", "sampling_pipeline.cu"],
+    "core": ["elementwise.cu", "gemm_simt.cu", "attention_generic.cu", "sampling_pipeline.cu", "random_weights.cu"],
     # the bfloat16 serving path: tensor-core products and tiled attention
     "bf16": ["gemm_tc.cu", "attention_tiled.cu", "attention_prefill_tc.cu"],
     # the entry point that allocates nothing (leone_static.h); it compiles attention_tiled.cu in
     "static": ["attention_decode_static.cu"],
-    # the host side of the runtime (pages, block tables, step metadata): plain C++, no device code
-    "host": ["host_runtime.cpp"],
+    # the host side of the runtime (pages, block tables, step metadata, the scheduler's decisions,
+    # seeded random weights for CPU tensors): plain C++, no device code
+    "host": ["host_runtime.cpp", "random_weights_host.cpp"],
 }
 HOST_ONLY = {"host"}
-HEADERS = ["common.cuh", "tc_common.cuh", "leone_static.h", "attention_tiled.cu"]
+HEADERS = ["common.cuh", "tc_common.cuh", "leone_static.h", "attention_tiled.cu", "random_draw.h"]
 
 # -fno-gnu-unique: statics inside inline functions and templates (the once-per-kernel set-up
 # flags, the launch mode switch) must belong to one library image each; with GNU unique
@@ -45,6 +46,10 @@ HEADERS = ["common.cuh", "tc_common.cuh", "leone_static.h", "attention_tiled.cu"
 # loaded with local scope.
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fno-gnu-unique", "--expt-relaxed-constexpr"]
+
+
+# -ffp-contract=off: the seeded random weights must round as the device's do (random_draw.h)
+HOST_FLAGS = ["-fPIC", "-ffp-contract=off", "-pthread"]
 
 
 class BuildError(RuntimeError):
@@ -78,7 +83,7 @@ def build_dir() -> str:
 
 def _digest(module: str) -> str:
     h = hashlib.sha256()
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(HOST_FLAGS if module in HOST_ONLY else NVCC_FLAGS).encode())
     for name in MODULES[module] + HEADERS:
         path = os.path.join(HERE, name)
         if os.path.isfile(path):
@@ -193,8 +198,9 @@ def _build_host(module, lib, stamp, digest, fresh, out_dir, verbose) -> str:
             t0 = time.time()
             tmp_lib = lib + f".tmp{os.getpid()}"
             srcs = [os.path.join(HERE, s) for s in MODULES[module]]
-            flags = ["-O2", "-std=c++17", "-shared", "-Xcompiler", "-fPIC"] if os.path.basename(cxx).startswith("nvcc") \
-                else ["-O2", "-std=c++17", "-shared", "-fPIC", "-fno-gnu-unique"]
+            flags = ["-O2", "-std=c++17", "-shared", "-Xcompiler", ",".join(HOST_FLAGS)] \
+                if os.path.basename(cxx).startswith("nvcc") \
+                else ["-O2", "-std=c++17", "-shared", "-fno-gnu-unique", *HOST_FLAGS]
             _run_with_heartbeat([cxx, *flags, "-I", HERE, *srcs, "-o", tmp_lib], MODULES[module][0])
             os.replace(tmp_lib, lib)
             with open(stamp, "w") as fh:

@@ -10,10 +10,12 @@ namespace leone {
 // Embedding gather: out[t,:] = table[id_t,:]  (crates/leone/src/cpu.rs:1243-1265;
 // CUDA counterpart crates/leone-cuda/cuda/ie_cuda.cu:3569).  Output is the fp32
 // residual stream.  An id outside [0, vocab) sets the status word and zeroes the row.
+// `scale` multiplies every element (1 for the reference's models, which have no embedding
+// multiplier; a product with 1 is exact).
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                                 float* __restrict__ out, int hidden, int vocab, int* status) {
+                                 float* __restrict__ out, int hidden, int vocab, float scale, int* status) {
   pdl_trigger();
   pdl_wait();
   const int row = blockIdx.x;
@@ -25,7 +27,23 @@ __global__ void embedding_kernel(const T* __restrict__ table, const int* __restr
     return;
   }
   const T* src = table + (size_t)id * hidden;
-  for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = to_float<T>(src[c]);
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = to_float<T>(src[c]) * scale;
+}
+
+// ---------------------------------------------------------------------------
+// Logit post-processing for an output head that has one: l <- l * scale, then (cap > 0)
+// l <- cap * tanh(l / cap).  The reference's models have neither (no logit scale, soft-cap or
+// bias: crates/leone/src/runtime.rs:7442-7452); the head part skips this kernel for them.
+// ---------------------------------------------------------------------------
+__global__ void logit_post_kernel(float* __restrict__ logits, long long n, float scale, float cap) {
+  pdl_trigger();
+  pdl_wait();
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    float v = logits[i] * scale;
+    if (cap > 0.f) v = cap * tanhf(v / cap);
+    logits[i] = v;
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -503,17 +521,24 @@ extern "C" int leone_decode_advance(int* token_ids, int* positions, int* ctx_len
 // Turns programmatic dependent launch on or off for the kernels of this library.
 extern "C" void leone_core_set_pdl(int enabled) { pdl_flag() = enabled ? 1 : 0; }
 
+extern "C" int leone_logit_post(float* logits, long long n, float scale, float cap, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const long long want = (n + 255) / 256;
+  return launch_kernel(logit_post_kernel, dim3((unsigned)(want < 148 * 8 ? want : 148 * 8)), dim3(256), 0, stream,
+                       logits, n, scale, cap);
+}
+
 extern "C" int leone_embedding(int dtype, const void* table, const int* ids, float* out, int n,
-                               int hidden, int vocab, int* status, cudaStream_t stream) {
+                               int hidden, int vocab, float scale, int* status, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (hidden <= 0 || vocab <= 0) return kRefusedSize;
   const int threads = hidden >= 1024 ? 256 : 128;
   if (dtype == 0)
     return launch_kernel(embedding_kernel<float>, dim3(n), dim3(threads), 0, stream, (const float*)table,
-                         ids, out, hidden, vocab, status);
+                         ids, out, hidden, vocab, scale, status);
   if (dtype == 1)
     return launch_kernel(embedding_kernel<__nv_bfloat16>, dim3(n), dim3(threads), 0, stream,
-                         (const __nv_bfloat16*)table, ids, out, hidden, vocab, status);
+                         (const __nv_bfloat16*)table, ids, out, hidden, vocab, scale, status);
   return kRefusedDtype;
 }
 

@@ -4,10 +4,15 @@ For a fixed set of B decoding requests the whole step — embedding, every layer
 output head, sampling, and the kernel that turns the sampled ids into the next step's inputs —
 is captured once and replayed.  Everything that changes between steps (token ids, positions,
 lengths, block tables, sampling positions) lives in device buffers that the captured kernels
-read, so one graph serves any context length.  The reference captures its single-request
-decode chain the same way and keeps the position in a device word
-(crates/leone/src/runtime.rs:7107-7291, crates/leone/src/backend.rs:1586-1595); it re-captures
-when the context bucket changes (crates/leone/src/runtime.rs:5005-5009), which is not needed here.
+read, so one captured step serves every context length up to the one it was captured for.
+The reference captures its single-request decode chain the same way and keeps the position in a
+device word (crates/leone/src/runtime.rs:7107-7291, crates/leone/src/backend.rs:1586-1595); it
+re-captures when the context bucket changes (next power of two, at least 512:
+crates/leone/src/backend.rs:1616, crates/leone/src/runtime.rs:5005-5009).  Here too a step is
+captured per *context bucket* (same rule, capped by the model's positions): what is fixed at
+capture is how the kernels are launched (how many ways the attention splits a sequence's keys),
+and that is chosen for the bucket, not for the model's limit.  All buckets of a batch size share
+one set of buffers.
 
 A *quantum* of up to ``max_quantum`` steps runs without the host: pages for the whole quantum
 are reserved and written into the block tables first, and the sampled ids of all its steps are
@@ -47,14 +52,34 @@ class DecodeGraph:
         self.status_host = torch.zeros(4, dtype=torch.int32, pin_memory=True)
         self.logits = torch.empty((batch, engine.spec.vocab_size), dtype=torch.float32, device=dev)
         self.ctx = self._context()
-        self.graph = None
+        self.graphs = {}                   # context bucket -> captured step
+        self.graph = None                  # the selected bucket's
+        self.bucket = None
         self._filled_rids = None           # what fill() last wrote into the host copy
         self._filled_pages = [[0] * batch for _ in engine.cache.groups]
         self._filled_sampling = None
+        self._tables_at = min((o for o, _ in self.bt_offsets), default=None)   # where the block tables start
         self._events = [torch.cuda.Event(), torch.cuda.Event()]
         self._advance_host = [torch.zeros((2, batch), dtype=torch.int32, pin_memory=True) for _ in range(2)]
         self.launches_per_step = 0
         self.stream = torch.cuda.Stream(device=dev)
+
+    def bucket_for(self, longest: int) -> int:
+        """The context bucket of a step whose longest sequence holds ``longest`` tokens after it:
+        the next power of two, at least 512, at most the model's positions."""
+        limit = self.engine.spec.max_positions
+        bucket = 512
+        while bucket < longest:
+            bucket *= 2
+        return min(bucket, limit)
+
+    def select(self, bucket: int) -> bool:
+        """Make ``bucket``'s captured step the one that is replayed; False if there is none yet."""
+        graph = self.graphs.get(bucket)
+        if graph is None:
+            return False
+        self.graph, self.bucket = graph, bucket
+        return True
 
     def _view(self, name):
         o, s = self.offsets[name]
@@ -114,9 +139,12 @@ class DecodeGraph:
             put("slot_ids", np.asarray(slots if slots is not None else [e.cache.slot(r) for r in rids],
                                        dtype=np.int32))
             put("logit_rows", np.arange(b, dtype=np.int32))
+        appended = []                       # [lo, hi) ranges of the host copy that gained entries
         for gi, (g, w, (o, shape)) in enumerate(zip(e.cache.groups, self.widths, self.bt_offsets)):
             view = host[o:o + shape[0] * shape[1]].reshape(shape)
             windowed = g.spec.kind == "window"
+            if windowed:
+                same = False                # a window's table also loses entries at its front: rewrite
             for i, r in enumerate(rids):
                 n = int(table_lens[gi][i]) if table_lens is not None else g.tables.length(r)
                 if n > w:
@@ -126,6 +154,7 @@ class DecodeGraph:
                     view[i, :] = -1
                 if n > done:
                     view[i, done:n] = g.tables.tail(r, done)
+                    appended.append((o + i * shape[1] + done, o + i * shape[1] + n))
                 self._filled_pages[gi][i] = n
         self._filled_rids = key
         sh = self.sample_host.numpy()
@@ -135,21 +164,30 @@ class DecodeGraph:
             sh[b:2 * b] = np.array([s_ & 0xFFFF_FFFF_FFFF_FFFF for _, s_ in sampling], dtype=np.uint64).view(np.int64)
             self._filled_sampling = sampling
         sh[2 * b:3 * b] = lengths      # position of the token being fed
-        self.meta.copy_(self.meta_host, non_blocking=True)
+        if same and self._tables_at is not None:
+            # same requests in the same rows: the per-token and per-sequence vectors, and the
+            # block-table entries that were appended
+            self.meta[:self._tables_at].copy_(self.meta_host[:self._tables_at], non_blocking=True)
+            for lo, hi in appended:
+                self.meta[lo:hi].copy_(self.meta_host[lo:hi], non_blocking=True)
+        else:
+            self.meta.copy_(self.meta_host, non_blocking=True)
         self.sample_dev.copy_(self.sample_host, non_blocking=True)
         self.counter.zero_()
 
-    def capture(self):
+    def capture(self, bucket: int):
         """Run one step eagerly on the filled buffers (so every scratch buffer exists), then
-        capture one step.  The caller fills the buffers again afterwards: the eager step has
-        advanced them."""
+        capture one step for contexts of up to ``bucket`` tokens and select it.  The caller fills
+        the buffers again afterwards: the eager step has advanced them."""
+        self.ctx.max_ctx_len = bucket
         cur = torch.cuda.current_stream(self.engine.device)
         self.stream.wait_stream(cur)
         with torch.cuda.stream(self.stream):
             self._one_step()
             self.stream.synchronize()
             before = self.engine.ops.launches
-            self.graph = torch.cuda.CUDAGraph()
+            self.graph = self.graphs[bucket] = torch.cuda.CUDAGraph()
+            self.bucket = bucket
             # an object that the collector finalises in the middle of a capture (an older
             # graph, a freed pool) would invalidate the capture: keep the collector out
             was_enabled = gc.isenabled()

@@ -24,7 +24,8 @@ from ..cache.pages import CacheManager, GroupSpec, OutOfPages
 from ..parts.base import FixedState, PagedCacheView, PagedKV, Runtime, StateView
 from ..parts.spec import ModelSpec
 from ..registry import config_from_folder, spec_from_config
-from ..weights.loader import load_checkpoint
+from ..weights.loader import check_names_and_shapes, load_checkpoint, target_dtype
+from .budget import check_memory_budget, plan_memory
 from .batch import StepContext, StepEntry, pack_metadata
 from .model import Model
 
@@ -55,7 +56,10 @@ class Engine:
                  dtype="bfloat16", device="cuda:0", page_tokens: int = 16,
                  max_tokens: Optional[int] = None, num_pages: Optional[int] = None,
                  max_requests: int = 64, max_batch_tokens: int = 2048, ops=None,
-                 folder: Optional[str] = None, random_seed: Optional[int] = None):
+                 folder: Optional[str] = None, random_seed: Optional[int] = None, free_bytes=None):
+        """``free_bytes``: a callable that says how many bytes the device has free, for the
+        memory budget (default: the CUDA driver's figure plus what torch's allocator holds
+        unused; no check on a device without such a figure)."""
         self.dtype = parse_dtype(dtype)
         self.device = torch.device(device)
         self.spec = spec
@@ -66,26 +70,8 @@ class Engine:
         self.max_batch_tokens = max_batch_tokens
         self.model = Model(spec, self.rt)
         specs = self.model.weight_specs()
-        if tensors is None and folder is not None:
-            from ..weights.safetensors import Checkpoint
-            probe = Checkpoint(folder)
-            notes = self.model.load_notes(set(probe.names()))
-            probe.close()
-            tensors = load_checkpoint(folder, specs, self.dtype, self.device, notes)
-        elif tensors is None:
-            if random_seed is None:
-                raise ValueError("an engine needs a model folder, tensors or a random seed")
-            tensors = self._random_on_device(specs, random_seed)
-        else:
-            from ..weights.loader import check_names_and_shapes, target_dtype
-            check_names_and_shapes(specs, tensors, self.model.load_notes(set(tensors)))
-            by_name = {s.name: s for s in specs}
-            tensors = {n: t.to(target_dtype(by_name[n], t.dtype, self.dtype)).to(self.device).contiguous()
-                       for n, t in tensors.items()}
-        self.model.load(tensors)
-        del tensors
 
-        # -- cache ----------------------------------------------------------------------
+        # -- what the cache will hold (nothing is allocated yet) ------------------------------
         self.page_tokens = page_tokens
         if num_pages is None:
             if max_tokens is None:
@@ -98,12 +84,15 @@ class Engine:
         self._run_group: Dict[int, tuple] = {}      # run position -> (gid, index within group)
         self._run_state: Dict[int, torch.Tensor] = {}
         self._run_source: Dict[int, int] = {}       # run position -> position whose cache it reads
+        state_shapes: Dict[int, tuple] = {}
         for pos, (req, source) in enumerate(plan):
             if source is not None:
                 self._run_source[pos] = source
             elif isinstance(req, PagedKV):
-                gs = GroupSpec("window" if req.window else "full", req.num_kv_heads, req.head_dim,
-                               req.window)
+                # the part says what it caches (widths, dtype, when pages go back); equal requests share a group
+                r = req.resolved(self.dtype)
+                gs = GroupSpec(r.lifetime, r.num_kv_heads, r.head_dim, r.window, value_head_dim=r.value_head_dim,
+                               dtype=r.dtype, tag=r.tag)
                 for gid, existing in enumerate(group_specs):
                     if existing.key() == gs.key():
                         break
@@ -113,16 +102,59 @@ class Engine:
                 self._run_group[pos] = (gid, len(group_specs[gid].layers))
                 group_specs[gid].layers.append(pos)
             elif isinstance(req, FixedState):
-                self._run_state[pos] = torch.zeros((max_requests,) + tuple(req.shape),
-                                                   dtype=torch.float32, device=self.device)
+                state_shapes[pos] = (max_requests,) + tuple(int(d) for d in req.shape)
             elif req is not None:
                 raise TypeError(f"run position {pos}: unknown cache request {req!r}")
+
+        # -- the memory budget, before anything is uploaded -----------------------------------
+        stored = None
+        if tensors is None and folder is not None:
+            from ..weights.safetensors import Checkpoint
+            probe = Checkpoint(folder)
+            notes = self.model.load_notes(set(probe.names()))
+            stored = {n: e.dtype for n, e in probe.entries.items()}
+            probe.close()
+        elif tensors is not None:
+            stored = {n: t.dtype for n, t in tensors.items()}
+        self.memory_plan = plan_memory(self.model, specs, stored, self.dtype, group_specs, num_pages, page_tokens,
+                                       state_shapes, max_requests, max_batch_tokens)
+        if tensors is not None:
+            # tensors already on the device are not uploaded again
+            by_name = {s.name: s for s in specs}
+            resident = sum(t.numel() * t.element_size() for n, t in tensors.items()
+                           if n in by_name and t.device == self.device
+                           and t.dtype == target_dtype(by_name[n], t.dtype, self.dtype))
+            self.memory_plan["weights"] -= resident
+            self.memory_plan["required"] -= resident
+        check_memory_budget(self.memory_plan, self.device, free_bytes)
+
+        # -- weights ------------------------------------------------------------------------------
+        if tensors is None and folder is not None:
+            tensors = load_checkpoint(folder, specs, self.dtype, self.device, notes)
+        elif tensors is None:
+            if random_seed is None:
+                raise ValueError("an engine needs a model folder, tensors or a random seed")
+            tensors = self._random_on_device(specs, random_seed)
+        else:
+            check_names_and_shapes(specs, tensors, self.model.load_notes(set(tensors)))
+            by_name = {s.name: s for s in specs}
+            tensors = {n: t.to(target_dtype(by_name[n], t.dtype, self.dtype)).to(self.device).contiguous()
+                       for n, t in tensors.items()}
+        self.model.load(tensors)        # empties the dict as the parts take their tensors
+        del tensors
+
+        # -- cache ----------------------------------------------------------------------------------
+        for pos, shape in state_shapes.items():
+            self._run_state[pos] = torch.zeros(shape, dtype=torch.float32, device=self.device)
         self.cache = CacheManager(group_specs, page_tokens, num_pages, max_requests)
         self.pools = []
         for gs in group_specs:
-            shape = (len(gs.layers), num_pages, gs.num_kv_heads, page_tokens, gs.head_dim)
-            self.pools.append((torch.zeros(shape, dtype=self.dtype, device=self.device),
-                               torch.zeros(shape, dtype=self.dtype, device=self.device)))
+            k_el, v_el = gs.page_elements(page_tokens)
+            head = (len(gs.layers), num_pages, gs.num_kv_heads, page_tokens)
+            k_pool = torch.zeros(head + (gs.head_dim,), dtype=gs.dtype, device=self.device)
+            v_pool = torch.zeros(head + (v_el // (gs.num_kv_heads * page_tokens),), dtype=gs.dtype,
+                                 device=self.device) if v_el else None
+            self.pools.append((k_pool, v_pool))
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
         if hasattr(self.ops, "bind_status"):
             self.ops.bind_status(self.status)
@@ -132,6 +164,7 @@ class Engine:
         self.steps_run = 0
         self._sampler = None
         self._decode_graphs = {}
+        self.max_decode_graphs = 8          # batch sizes whose captured decode steps are kept
         # a decode step launched before the step before it was read (see decode_steps)
         self._ahead = None
         self.lookahead = os.environ.get("LEONE_NO_LOOKAHEAD", "0") != "1"
@@ -148,13 +181,12 @@ class Engine:
         return cls(spec_from_config(config), random_seed=seed, **kw)
 
     def _random_on_device(self, specs, seed):
+        """Every tensor drawn in place in its storage dtype: the values are a function of
+        (seed, name, index), the same on the device as in a folder written on the host."""
         from ..weights.loader import target_dtype
-        out = {}
-        for spec in specs:
-            from ..weights.random_init import draw
-            t = draw(spec, seed, self.device)
-            out[spec.name] = t.to(target_dtype(spec, torch.float32, self.dtype))
-        return out
+        from ..weights.random_init import draw
+        return {spec.name: draw(spec, seed, self.device, target_dtype(spec, torch.float32, self.dtype))
+                for spec in specs}
 
     # -- request lifetime ---------------------------------------------------------------
     def open(self, rid: Hashable) -> int:
@@ -217,7 +249,7 @@ class Engine:
             if src in self._run_group:
                 gid, k = self._run_group[src]
                 kp, vp = self.pools[gid]
-                ctx.layer_caches[pos] = PagedCacheView(kp[k], vp[k], ctx.block_tables[gid],
+                ctx.layer_caches[pos] = PagedCacheView(kp[k], None if vp is None else vp[k], ctx.block_tables[gid],
                                                        self.page_tokens, writes)
             elif src in self._run_state:
                 ctx.layer_caches[pos] = StateView(self._run_state[src], writes)
@@ -306,8 +338,11 @@ class Engine:
         rids = list(rids)
         if steps <= 0 or not rids:
             return []
+        # A step launched ahead and then dropped has run its kernels.  Pages it wrote are given
+        # back and rewritten, but fixed-size state would have been advanced by a token for good,
+        # and a window group would have released pages: such models decode without looking ahead.
         if (steps == 1 and use_graph and self.lookahead and self.device.type == "cuda"
-                and all(g.spec.kind == "full" for g in self.cache.groups)):
+                and not self._run_state and all(g.spec.kind == "full" for g in self.cache.groups)):
             return [self._decode_one_ahead(rids, [int(t) for t in last_tokens], list(params), expect_more)]
         self.drop_lookahead()
         if not (use_graph and self.device.type == "cuda") or steps > 64:
@@ -326,7 +361,7 @@ class Engine:
             if int(lengths.max()) + steps > self.spec.max_positions:
                 raise ValueError("decode_steps would run past the model's positions")
             state = dict(versions=versions, slots=slots, table_lens=table_lens)
-            graph = self._decode_graph(rids, last_tokens, lengths, params, state)
+            graph = self._decode_graph(rids, last_tokens, lengths, params, state, steps)
             graph.fill(rids, last_tokens, lengths, params, **state)
             tokens = graph.run(steps)       # also reads and checks the status word
         except Exception:
@@ -363,15 +398,23 @@ class Engine:
         self.steps_run += 1
         return graph.logits
 
-    def _decode_graph(self, rids, last_tokens, lengths, params, state):
-        graph = self._decode_graphs.get(len(rids))
+    def _decode_graph(self, rids, last_tokens, lengths, params, state, steps: int = 1):
+        """The captured decode step for this batch size and for the context bucket that holds
+        the longest sequence after ``steps`` more tokens, captured now if it is not yet.  One
+        set of buffers per batch size; the least recently used batch size is dropped beyond
+        ``max_decode_graphs`` of them."""
+        graph = self._decode_graphs.pop(len(rids), None)
         if graph is None:
             from .decode_graph import DecodeGraph
             graph = DecodeGraph(self, len(rids))
+        self._decode_graphs[len(rids)] = graph                 # most recently used last
+        while len(self._decode_graphs) > self.max_decode_graphs:
+            self._decode_graphs.pop(next(iter(self._decode_graphs)))
+        bucket = graph.bucket_for(int(max(lengths)) + steps)
+        if not graph.select(bucket):
             # capture needs valid tables: fill first, then warm up and capture on them
             graph.fill(rids, last_tokens, lengths, params, **state)
-            graph.capture()
-            self._decode_graphs[len(rids)] = graph
+            graph.capture(bucket)
         return graph
 
     def _decode_one_ahead(self, rids: List[Hashable], last_tokens: List[int], params,
@@ -402,8 +445,10 @@ class Engine:
                 raise
         try:
             ahead = None
+            # the step after this one must fit the captured step's context bucket (a new bucket
+            # is captured by the next call, with nothing in flight)
             if (expect_more and slot + 1 < graph.max_quantum
-                    and int(lengths.max()) + 2 <= self.spec.max_positions):
+                    and int(lengths.max()) + 2 <= min(self.spec.max_positions, graph.bucket)):
                 try:
                     table_lens = self.cache.reserve_steps(rids, 2)[3]      # this step's token and the next one's
                 except OutOfPages:

@@ -39,16 +39,38 @@ class GenerationStats:
         return n / self.decode_seconds if self.decode_seconds > 0 else 0.0
 
 
+def load_config(source):
+    """A typed configuration from a model folder, a ``config.json`` path, a dict or itself."""
+    import json
+    import os
+    from ..config.base import ModelConfig
+    from ..registry import config_from_dict, config_from_folder
+    if isinstance(source, ModelConfig):
+        return source
+    if isinstance(source, dict):
+        return config_from_dict(source)
+    if isinstance(source, str) and os.path.isfile(source):
+        with open(source) as fh:
+            return config_from_dict(json.load(fh))
+    return config_from_folder(source)
+
+
 def generate(model: Union[str, Engine], prompts: Sequence[Sequence[int]], max_new_tokens: int,
              temperature: float = 0.0, seed: int = 0, dtype: str = "bfloat16",
-             eos_token_id: Optional[int] = None, page_tokens: int = 16,
+             eos_token_id=None, page_tokens: int = 16,
              num_pages: Optional[int] = None, prefill_chunk: int = 2048,
              max_batch_tokens: int = 2048, max_running: int = 64, policy: str = "reserve",
              device: str = "cuda:0", return_stats: bool = False, decode_quantum: int = 1,
-             use_graphs: bool = True, prefill_first: bool = True, truncations=(), penalties=None, mirostat=None):
+             use_graphs: bool = True, prefill_first: bool = True, truncations=(), penalties=None, mirostat=None,
+             random_weights: bool = False, weights_seed: Optional[int] = None):
     """Generate ``max_new_tokens`` tokens for each prompt (a list of token ids).
 
     ``model`` is a model folder (config.json + model.safetensors) or an :class:`Engine`.
+    With ``random_weights`` no tensor file is read: ``model`` is a folder with a ``config.json``,
+    the path of such a file, its contents as a dict, or a typed configuration, and the weights
+    are drawn on the device from ``weights_seed`` (default: ``seed``) as
+    ``leone_b200.weights.random_init`` defines them, the same values as a folder written by
+    ``write_random_model`` for that configuration and seed holds.
     ``temperature`` 0 is greedy; otherwise each request ``i`` draws with seed ``seed + i`` so
     its stream does not depend on what it is batched with.  ``prefill_first`` (default) runs
     all prompts before decoding starts, so the requests decode as one batch; ``False`` mixes
@@ -70,11 +92,14 @@ def generate(model: Union[str, Engine], prompts: Sequence[Sequence[int]], max_ne
         if num_pages is None:
             per_request = -(-longest // page_tokens) + 1
             num_pages = per_request * min(len(prompts), max_running)
-        engine = Engine.from_folder(model, dtype=dtype, device=device, page_tokens=page_tokens,
-                                    num_pages=num_pages, max_requests=max_running,
-                                    max_batch_tokens=max_batch_tokens)
+        kw = dict(dtype=dtype, device=device, page_tokens=page_tokens, num_pages=num_pages,
+                  max_requests=max_running, max_batch_tokens=max_batch_tokens)
+        if random_weights:
+            engine = Engine.from_config(load_config(model), seed if weights_seed is None else weights_seed, **kw)
+        else:
+            engine = Engine.from_folder(model, **kw)
     if eos_token_id is None:
-        eos_token_id = engine.spec.eos_token_id
+        eos_token_id = engine.spec.stop_ids() or None
     sched = Scheduler(engine, SchedulerConfig(max_running=min(max_running, engine.max_requests),
                                               max_batch_tokens=min(max_batch_tokens, engine.max_batch_tokens),
                                               prefill_chunk_tokens=prefill_chunk, policy=policy,

@@ -1,10 +1,11 @@
 """A model built from a :class:`ModelSpec`: embedding, layers in run order, final norm, head.
 
-The forward pass runs only the tokens of the step: embedding gather
+The forward pass runs only the tokens of the step: the embedding part
 (crates/leone/src/runtime.rs:6686-6692), the layers in ``run_order``, then the
-final norm and the output head on the wanted rows only
+final norm and the head part on the wanted rows only
 (crates/leone/src/runtime.rs:7428-7452, 6542-6608).  A tied head reads the
-embedding table (crates/leone/src/model.rs:452-471).
+embedding table (crates/leone/src/model.rs:452-471).  Embedding and head are
+parts like the others, chosen by kind from the spec.
 """
 from __future__ import annotations
 
@@ -16,7 +17,8 @@ import torch
 from .. import parts as _parts  # noqa: F401  (registers built-in parts)
 from ..parts.base import FixedState, PagedKV, Runtime, WeightSpec
 from ..parts.spec import ModelSpec
-from ..registry import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, spec_from_config
+from ..registry import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS,
+                        spec_from_config)
 
 
 class _Prefixed:
@@ -31,7 +33,9 @@ class _Prefixed:
                 for s in self.part.weight_specs()]
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.part.load({s.name: tensors[f"{self.prefix}.{s.name}"] for s in self.part.weight_specs()})
+        """Hands the part its tensors and takes them out of ``tensors``: what the part keeps it
+        holds itself, what it fused into a copy is freed at once."""
+        self.part.load({s.name: tensors.pop(f"{self.prefix}.{s.name}") for s in self.part.weight_specs()})
 
 
 def _build_mixer(spec, rt, position_encodings):
@@ -62,35 +66,38 @@ class Model:
             self._holders += [_Prefixed(layer.prefix, p) for p in (mixer, ffn, n1, n2)]
         self.final_norm = NORMS.get(spec.final_norm.kind)(
             {**spec.final_norm.params, "name": spec.final_norm_name}, rt)
-        self.embedding = None
-        self.lm_head = None
+        es, hs = spec.embedding_spec(), spec.head_spec()
+        self.embedding = EMBEDDINGS.get(es.kind)(dict(es.params), rt)
+        self.head = HEADS.get(hs.kind)(dict(hs.params), rt)
 
     # -- weights ----------------------------------------------------------------------
     def weight_specs(self) -> List[WeightSpec]:
-        s = self.spec
-        specs = [WeightSpec(s.embedding_name, (s.vocab_size, s.hidden_size), role="embedding")]
+        specs = list(self.embedding.weight_specs())
         for holder in self._holders:
             specs += holder.full_specs()
         specs += self.final_norm.weight_specs()
-        if s.lm_head_name is not None:
-            specs.append(WeightSpec(s.lm_head_name, (s.vocab_size, s.hidden_size)))
+        specs += self.head.weight_specs()
         return specs
 
     def load_notes(self, names) -> List[str]:
-        """Extra findings for the weight error: a tied model whose file still has a head."""
-        if self.spec.lm_head_name is None and "lm_head.weight" in names:
-            return ["lm_head.weight is present although the configuration ties the head to "
-                    "the embedding table"]
-        return []
+        """Extra findings for the weight error that a part can name better than "unexpected
+        tensor" (a tied head whose file still has a head tensor)."""
+        notes: List[str] = []
+        for part in (self.embedding, self.head):
+            if hasattr(part, "load_notes"):
+                notes += part.load_notes(names)
+        return notes
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        """Gives every part its tensors; ``tensors`` is emptied on the way, so a source that a
+        part fused into a copy of its own (q/k/v stacked, gate/up interleaved) is freed as soon
+        as that part is loaded."""
         s = self.spec
-        self.embedding = tensors[s.embedding_name]
+        self.embedding.load({w.name: tensors.pop(w.name) for w in self.embedding.weight_specs()})
         for holder in self._holders:
             holder.load(tensors)
-        self.final_norm.load({s.final_norm_name: tensors[s.final_norm_name]})
-        head = self.embedding if s.lm_head_name is None else tensors[s.lm_head_name]
-        self.lm_head = self.rt.ops.prepare_matrix(head)
+        self.final_norm.load({s.final_norm_name: tensors.pop(s.final_norm_name)})
+        self.head.load({w.name: tensors.pop(w.name) for w in self.head.weight_specs()}, self.embedding)
 
     # -- cache needs ------------------------------------------------------------------
     def cache_plan(self):
@@ -121,14 +128,31 @@ class Model:
             for part in (block.mixer, block.feed_forward):
                 if hasattr(part, "weight_bytes"):
                     total += part.weight_bytes()
-        total += self.vocab_size * self.hidden_size * self.rt.dtype.itemsize
+        total += self.head.weight_bytes()
         return total
+
+    def scratch_bytes(self, max_tokens: int, max_logit_rows: int) -> int:
+        """An estimate of the scratch a step of ``max_tokens`` tokens asks the runtime for: the fp32
+        residual stream, the normed tokens (twice: a folded norm keeps its own copy), the largest
+        layer's buffers (layers share them by name), and fp32 logits for ``max_logit_rows`` rows."""
+        item = self.rt.dtype.itemsize
+        total = max_tokens * self.hidden_size * (4 + 3 * item)
+        per_layer = [sum(p.scratch_bytes(max_tokens) for p in (b.mixer, b.feed_forward, b.mixer_norm, b.ffn_norm))
+                     for b in self.blocks]
+        total += max(per_layer, default=0)
+        total += max_logit_rows * (self.vocab_size * 4 + self.hidden_size * item)
+        return total
+
+    def load_transient_bytes(self) -> int:
+        """The most any one part holds beyond its inputs while it loads."""
+        parts = [h.part for h in self._holders] + [self.embedding, self.head, self.final_norm]
+        return max((p.load_transient_bytes() for p in parts), default=0)
 
     # -- forward ----------------------------------------------------------------------
     def forward(self, ctx) -> Optional[torch.Tensor]:
         rt = self.rt
         hidden = rt.buffer("hidden", ctx.n_tokens, self.hidden_size, torch.float32)
-        rt.ops.embedding(self.embedding, ctx.token_ids, hidden, ctx.status)
+        self.embedding.forward(ctx, hidden)
         order = self.spec.run_order
         pre = None           # the entry norm of the next block, if the last product before it folded it in
         for pos, idx in enumerate(order):
@@ -150,7 +174,7 @@ class Model:
         x = self.final_norm.forward(ctx, hidden, rows=ctx.logit_rows, out_name="final_normed")
         out = ctx.logits_out if ctx.logits_out is not None else torch.empty(
             (m, self.vocab_size), dtype=torch.float32, device=self.rt.device)
-        self.rt.ops.linear(x, self.lm_head, out)
+        self.head.forward(ctx, x, out)
         return out
 
 

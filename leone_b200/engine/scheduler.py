@@ -79,7 +79,8 @@ class Request:
     prompt: List[int]
     max_new_tokens: int
     sampling: SamplingParams = field(default_factory=SamplingParams)
-    eos_token_id: Optional[int] = None
+    eos_token_id: Optional[int] = None                   # as given (an id, several, or None)
+    stop_ids: tuple = ()                                 # every id that ends the request
     arrival: int = 0
     tokens: List[int] = field(default_factory=list)      # prompt + generated, what the cache must hold
     computed: int = 0                                    # tokens already in the cache
@@ -178,8 +179,16 @@ class Scheduler:
 
     # -- admission --------------------------------------------------------------------
     def add_request(self, rid: Hashable, prompt: Sequence[int], max_new_tokens: int,
-                    sampling: Optional[SamplingParams] = None, eos_token_id: Optional[int] = None) -> Request:
+                    sampling: Optional[SamplingParams] = None, eos_token_id=None) -> Request:
+        """``eos_token_id``: one id or several (a list or tuple); sampling any of them ends the
+        request (the reference stops on its tokenizer's end id, crates/leone/src/runtime.rs:5383)."""
         prompt = [int(t) for t in prompt]
+        if eos_token_id is None:
+            stop_ids = ()
+        elif isinstance(eos_token_id, (list, tuple, set, frozenset)):
+            stop_ids = tuple(int(t) for t in eos_token_id)
+        else:
+            stop_ids = (int(eos_token_id),)
         old = self.requests.get(rid)
         if old is not None and old.state in ("waiting", "running"):
             raise AdmissionError("duplicate", f"request id {rid!r} is already in flight")
@@ -190,7 +199,7 @@ class Scheduler:
         if code != 0:
             raise AdmissionError(_REJECTS[code], self._lib.leone_host_last_error().decode())
         self._next_key += 1
-        req = Request(rid, prompt, max_new_tokens, sampling or SamplingParams(), eos_token_id,
+        req = Request(rid, prompt, max_new_tokens, sampling or SamplingParams(), eos_token_id, stop_ids,
                       arrival=int(self._lib.leone_sched_get(self._h, c_longlong(key), 6)),
                       tokens=list(prompt), key=key)
         if getattr(req.sampling, "mirostat", None):
@@ -244,7 +253,7 @@ class Scheduler:
         """Book a sampled token; returns why the request ends now, if it does (it is closed then)."""
         req.generated.append(tok)
         req.tokens.append(tok)
-        is_eos = req.eos_token_id is not None and tok == req.eos_token_id
+        is_eos = tok in req.stop_ids
         code = self._lib.leone_sched_emitted(self._h, c_longlong(req.key), int(is_eos))
         if code <= 0:
             return None
@@ -346,8 +355,7 @@ class Scheduler:
         for row in steps:
             n = len(live)
             toks = [int(row[i]) for i in live]
-            is_eos = (c_int * n)(*[int(reqs[i].eos_token_id is not None and t == reqs[i].eos_token_id)
-                                   for i, t in zip(live, toks)])
+            is_eos = (c_int * n)(*[int(t in reqs[i].stop_ids) for i, t in zip(live, toks)])
             reasons = (c_int * n)()
             code = self._lib.leone_sched_decoded(self._h, n, (c_longlong * n)(*[reqs[i].key for i in live]),
                                                  is_eos, reasons)       # the step's bookkeeping in one call

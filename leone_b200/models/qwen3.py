@@ -70,6 +70,9 @@ def build_spec(cfg: Qwen3Config) -> ModelSpec:
         lm_head_name=None if cfg.tie_word_embeddings else "lm_head.weight",
         position_encodings={"rope": rope},
         eos_token_id=cfg.eos_token_id,
+        eos_token_ids=cfg.eos_token_ids,
+        head=PartSpec("linear_head", {"name": None if cfg.tie_word_embeddings else "lm_head.weight",
+                                      "tied_name": "lm_head.weight"}),
     )
     spec.validate()
     return spec

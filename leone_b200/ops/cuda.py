@@ -136,15 +136,23 @@ class CudaOps:
         return m
 
     # -- kernels ------------------------------------------------------------------------
-    def embedding(self, table, ids, out, status):
+    def embedding(self, table, ids, out, status, scale: float = 1.0):
         n, hidden = out.shape
         _need(out.dtype == torch.float32 and out.is_contiguous(), "embedding output must be fp32")
         _need(ids.dtype == torch.int32 and ids.numel() == n, "embedding ids must be int32 [N]")
         _need(table.shape[1] == hidden and table.is_contiguous(), "embedding table shape")
         self.launches += 1
         _check(self.core.leone_embedding(_dt(table.dtype), _ptr(table), _ptr(ids), _ptr(out), n,
-                                         hidden, table.shape[0], _ptr(status), self._stream()),
+                                         hidden, table.shape[0], c_float(scale), _ptr(status), self._stream()),
                "embedding")
+
+    def logit_post(self, logits, scale: float = 1.0, soft_cap: Optional[float] = None):
+        """In place: ``logits * scale``, then ``cap * tanh(. / cap)`` if a soft cap is given."""
+        _need(logits.dtype == torch.float32 and logits.is_contiguous(), "logits must be contiguous fp32")
+        _need(soft_cap is None or soft_cap > 0, "a soft cap must be positive")
+        self.launches += 1
+        _check(self.core.leone_logit_post(_ptr(logits), ctypes.c_longlong(logits.numel()), c_float(scale),
+                                          c_float(soft_cap or 0.0), self._stream()), "logit_post")
 
     def rms_norm(self, x, weight, out, eps, rows=None):
         n_out, hidden = out.shape

@@ -1,9 +1,9 @@
 """Parts a layer is built from.  Importing this package registers the built-in kinds."""
-from . import attention, block, rms_norm, rotary, swiglu  # noqa: F401
-from .base import (Block, FeedForward, FixedState, Mixer, Norm, PagedCacheView, PagedKV, Part,
+from . import attention, block, embedding, head, rms_norm, rotary, swiglu  # noqa: F401
+from .base import (Block, Embedding, FeedForward, FixedState, Head, Mixer, Norm, PagedCacheView, PagedKV, Part,
                    PositionEncoding, Runtime, StateView, WeightSpec)
 from .spec import LayerSpec, ModelSpec, PartSpec
 
-__all__ = ["Block", "FeedForward", "FixedState", "Mixer", "Norm", "PagedCacheView", "PagedKV",
+__all__ = ["Block", "Embedding", "FeedForward", "FixedState", "Head", "Mixer", "Norm", "PagedCacheView", "PagedKV",
            "Part", "PositionEncoding", "Runtime", "StateView", "WeightSpec", "LayerSpec",
            "ModelSpec", "PartSpec"]

@@ -78,6 +78,12 @@ class Attention(Mixer):
     def weight_bytes(self):
         return (self.qkv_cols * self.hidden + self.hidden * self.n_q * self.d) * self.rt.dtype.itemsize
 
+    def scratch_bytes(self, max_tokens):
+        return max_tokens * (self.qkv_cols + self.n_q * self.d) * self.rt.dtype.itemsize
+
+    def load_transient_bytes(self):
+        return self.qkv_cols * self.hidden * self.rt.dtype.itemsize       # q, k, v beside their stacked copy
+
     def cache_request(self):
         return PagedKV(self.n_kv, self.d, self.window)
 

@@ -31,6 +31,14 @@ Interfaces, by kind:
 
 ``Block.forward(ctx, cache, hidden) -> None``
     The arrangement of norm, mixer and feed-forward around the residual stream.
+
+``Embedding.forward(ctx, hidden) -> None`` / ``Head.forward(ctx, x, out) -> None``
+    What stands before the first layer (token ids → fp32 residual stream) and after the final
+    norm (normed wanted rows → fp32 logits).  A multiplier, learned positions added to the
+    token rows, a logit scale or soft cap live in parts of these two kinds.
+
+A mixer whose ``__init__`` takes a ``position_encodings`` keyword is given the model's named
+position encodings (a dict) when it is built; one without it is built from ``(params, rt)``.
 """
 from __future__ import annotations
 
@@ -57,10 +65,35 @@ class WeightSpec:
 
 @dataclass
 class PagedKV:
-    """A mixer's request for paged keys and values."""
+    """A mixer's request for a paged cache: per token and KV head one key row of ``head_dim``
+    elements and one value row of ``value_head_dim`` elements.
+
+    ``value_head_dim``: ``None`` = as wide as the key; 0 = no value pool at all (a mixer that
+    caches one vector per token, a latent, and derives the rest).  ``dtype``: storage dtype of
+    the pages (``None`` = the run dtype).  ``lifetime``: when pages go back to the pool:
+    ``"full"`` (at the request's end) or ``"window"`` (as soon as every later query lies more
+    than ``window`` tokens past the page); ``None`` = ``"window"`` if a window is given.
+    ``tag``: requests with different tags never share a group (a pool and a block table).
+    Layers whose requests are equal share a group."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    value_head_dim: Optional[int] = None
+    dtype: Optional[torch.dtype] = None
+    lifetime: Optional[str] = None
+    tag: str = ""
+
+    def resolved(self, run_dtype: torch.dtype) -> "PagedKV":
+        lifetime = self.lifetime or ("window" if self.window else "full")
+        if lifetime not in ("full", "window"):
+            raise ValueError(f"a paged cache's lifetime is 'full' or 'window', not '{lifetime}'")
+        if lifetime == "window" and not self.window:
+            raise ValueError("a paged cache with lifetime 'window' needs a window")
+        vd = self.head_dim if self.value_head_dim is None else int(self.value_head_dim)
+        if self.num_kv_heads <= 0 or self.head_dim <= 0 or vd < 0:
+            raise ValueError(f"a paged cache needs positive sizes, got {self}")
+        return PagedKV(self.num_kv_heads, self.head_dim, self.window if lifetime == "window" else None,
+                       vd, self.dtype or run_dtype, lifetime, self.tag)
 
 
 @dataclass
@@ -73,7 +106,7 @@ class FixedState:
 class PagedCacheView:
     """What a mixer sees of a paged group for one layer in one step."""
     k_pool: torch.Tensor          # [pages, kv_heads, page_tokens, head_dim]
-    v_pool: torch.Tensor
+    v_pool: Optional[torch.Tensor]  # [pages, kv_heads, page_tokens, value_head_dim]; None if the request had no values
     block_table: torch.Tensor     # int32 [B, max_blocks]; -1 where no page
     page_tokens: int
     writes: bool = True           # False for a layer that borrows another layer's cache
@@ -109,10 +142,18 @@ class DeferredNorm:
     ready: bool = False
 
     def prepare(self, rt, parts: int) -> None:
+        """Buffers for a step of ``n`` tokens: ``xn [n, size]`` and the partial sums ``ss
+        [parts, n]``, a view of one flat allocation per tag that is large enough for any step
+        (``parts`` never exceeds the row width; a step never exceeds ``rt.max_tokens``), so its
+        address is the same for every step size and a captured graph keeps seeing it."""
         n, size = self.hidden.shape
         self.parts = parts
         self.xn = rt.buffer(f"deferred_norm_x_{self.tag}", n, size, rt.dtype)
-        self.ss = rt.buffer(f"deferred_norm_ss_{self.tag}_{n}", parts, n, torch.float32)
+        # up to 32 tokens a part is 32 weight rows (parts * n <= size); prompt-sized steps have a
+        # part per tile of at least 240 weight rows: reserve for the larger of the two at once
+        flat = rt.flat_buffer(f"deferred_norm_ss_{self.tag}", parts * n, torch.float32,
+                              reserve=max(size, (size // 240 + 2) * rt.max_tokens))
+        self.ss = flat[:parts * n].view(parts, n)
 
     def materialize(self) -> torch.Tensor:
         return self.norm.forward(self.ctx, self.hidden)
@@ -147,6 +188,26 @@ class Runtime:
         return buf[:rows]
 
 
+    def flat_buffer(self, name: str, numel: int, dtype: torch.dtype, reserve: int = 0) -> torch.Tensor:
+        """A scratch vector of at least ``numel`` elements under ``name`` (``reserve``: what to
+        allocate at once, so that later, larger asks need no new allocation).  It only ever
+        grows (by at least a factor of two), and an outgrown allocation is kept alive for
+        captured graphs that may still use it."""
+        key = f"flat/{name}/{dtype}"
+        buf = self._buffers.get(key)
+        if buf is None or buf.numel() < numel:
+            if buf is not None:
+                self._buffers[f"retired/{id(buf)}"] = buf
+            cap = max(numel, reserve, 2 * buf.numel() if buf is not None else 0)
+            buf = torch.empty(cap, dtype=dtype, device=self.device)
+            self._buffers[key] = buf
+        return buf
+
+    def allocated_bytes(self) -> int:
+        """Bytes of all scratch buffers alive (retired ones included)."""
+        return sum(b.numel() * b.element_size() for b in self._buffers.values())
+
+
 class Part:
     def __init__(self, params: dict, rt: Runtime):
         self.params = params
@@ -157,6 +218,16 @@ class Part:
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         pass
+
+    def scratch_bytes(self, max_tokens: int) -> int:
+        """Bytes of scratch buffers this part asks the runtime for in a step of ``max_tokens``
+        tokens (an estimate for the memory budget that is checked before anything is loaded)."""
+        return 0
+
+    def load_transient_bytes(self) -> int:
+        """Bytes ``load`` holds on top of the tensors it was given while it runs (a fused copy
+        next to its sources); for the same budget."""
+        return 0
 
 
 class Norm(Part):
@@ -198,6 +269,37 @@ class PositionEncoding(Part):
 
     def apply(self, ctx, q, k):
         raise NotImplementedError
+
+
+class Embedding(Part):
+    """Token ids → the fp32 residual stream.  Its tensors are named in full (no layer prefix).
+    ``params`` always hold ``vocab_size`` and ``hidden_size``."""
+
+    def forward(self, ctx, hidden) -> None:
+        """Fill ``hidden`` (fp32 ``[N, hidden_size]``) for the step's ``ctx.token_ids`` (at
+        ``ctx.positions``); an id outside the vocabulary sets ``ctx.status`` and zeroes the row."""
+        raise NotImplementedError
+
+    def table(self) -> Optional[torch.Tensor]:
+        """The ``[vocab, hidden]`` token table, for an output head that is tied to it."""
+        return None
+
+
+class Head(Part):
+    """Normed rows → fp32 logits.  Its tensors are named in full.  ``params`` always hold
+    ``vocab_size`` and ``hidden_size``."""
+
+    def load(self, tensors: Dict[str, torch.Tensor], embedding: Optional[Embedding] = None) -> None:
+        pass
+
+    def forward(self, ctx, x, out) -> None:
+        """``x``: the final norm's output for the wanted rows ``[M, hidden]`` in the run dtype;
+        ``out``: fp32 ``[M, vocab]`` to fill."""
+        raise NotImplementedError
+
+    def weight_bytes(self) -> int:
+        """Bytes of weights one step reads here."""
+        return 0
 
 
 class Block:

@@ -52,7 +52,26 @@ class ModelSpec:
     final_norm_name: str
     lm_head_name: Optional[str]               # None: tied to the embedding table
     position_encodings: Dict[str, PartSpec] = field(default_factory=dict)
-    eos_token_id: Optional[int] = None
+    eos_token_id: Optional[int] = None        # the first of ``eos_token_ids`` (kept for callers that want one)
+    eos_token_ids: Tuple[int, ...] = ()       # every id that ends a request
+    # What stands before the first layer and after the final norm.  ``None``: the built-in
+    # ``token_embedding`` of ``embedding_name`` and ``linear_head`` of ``lm_head_name``.  The
+    # engine adds ``vocab_size`` and ``hidden_size`` to the params of either.
+    embedding: Optional[PartSpec] = None
+    head: Optional[PartSpec] = None
+
+    def embedding_spec(self) -> PartSpec:
+        base = self.embedding or PartSpec("token_embedding", {"name": self.embedding_name})
+        return PartSpec(base.kind, {"vocab_size": self.vocab_size, "hidden_size": self.hidden_size, **base.params})
+
+    def head_spec(self) -> PartSpec:
+        base = self.head or PartSpec("linear_head", {"name": self.lm_head_name})
+        return PartSpec(base.kind, {"vocab_size": self.vocab_size, "hidden_size": self.hidden_size, **base.params})
+
+    def stop_ids(self) -> Tuple[int, ...]:
+        if self.eos_token_ids:
+            return tuple(self.eos_token_ids)
+        return () if self.eos_token_id is None else (self.eos_token_id,)
 
     def validate(self) -> None:
         n = len(self.layers)

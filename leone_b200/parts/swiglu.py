@@ -38,6 +38,13 @@ class SwiGLU(FeedForward):
     def weight_bytes(self):
         return (2 * self.inter * self.hidden + self.hidden * self.inter) * self.rt.dtype.itemsize
 
+    def scratch_bytes(self, max_tokens):
+        # the activation; a path without the fused epilogue also holds gate and up side by side
+        return max_tokens * 3 * self.inter * self.rt.dtype.itemsize
+
+    def load_transient_bytes(self):
+        return 2 * self.inter * self.hidden * self.rt.dtype.itemsize       # gate and up beside their interleaved copy
+
     def forward(self, ctx, x, hidden, then=None):
         n = hidden.shape[0]
         ops = self.rt.ops

@@ -5,7 +5,7 @@ that turns a configuration into a :class:`~leone_b200.parts.spec.ModelSpec`
 (the reference's counterpart is the architecture support table,
 crates/leone-gguf/src/support.rs:39-56, and ``ModelArchitecture::from_gguf``,
 crates/leone/src/model.rs:23-31).  Parts (mixer, feed-forward, norm, position
-encoding, block arrangement) are registered by kind name and looked up layer
+encoding, block arrangement, embedding, output head) are registered by kind name and looked up layer
 by layer from the spec, so code outside this package can add one without
 touching any file here.
 """
@@ -51,6 +51,8 @@ FEED_FORWARDS = Registry("feed-forward")
 NORMS = Registry("norm")
 POSITION_ENCODINGS = Registry("position encoding")
 BLOCKS = Registry("block arrangement")
+EMBEDDINGS = Registry("embedding")
+HEADS = Registry("output head")
 
 
 class ArchitectureEntry:

@@ -30,8 +30,13 @@ class EmulatedOps:
         return f"emulated status {word}"
 
     # -- kernels ------------------------------------------------------------------------
-    def embedding(self, table, ids, out, status):
-        out.copy_(table[ids.long()].float())
+    def embedding(self, table, ids, out, status, scale=1.0):
+        out.copy_(table[ids.long()].float() * scale)
+
+    def logit_post(self, logits, scale=1.0, soft_cap=None):
+        logits.mul_(scale)
+        if soft_cap:
+            logits.copy_(soft_cap * torch.tanh(logits / soft_cap))
 
     def rms_norm(self, x, weight, out, eps, rows=None):
         src = x if rows is None else x[rows.long()]

@@ -165,8 +165,47 @@ def forward_logits(cfg, w, tokens):
     return linear(h, head)
 
 
+def tensor_list(cfg):
+    """(name, shape, role) of every tensor of the architecture, by the checkpoint's names
+    (the reference's eleven tensors per layer, crates/leone/src/model.rs:513-560)."""
+    h, i, d = cfg["hidden_size"], cfg["intermediate_size"], cfg["head_dim"]
+    nq, nkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    out = [("model.embed_tokens.weight", (cfg["vocab_size"], h), "matrix")]
+    for layer in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{layer}"
+        out += [(f"{p}.self_attn.q_proj.weight", (nq * d, h), "matrix"),
+                (f"{p}.self_attn.k_proj.weight", (nkv * d, h), "matrix"),
+                (f"{p}.self_attn.v_proj.weight", (nkv * d, h), "matrix"),
+                (f"{p}.self_attn.o_proj.weight", (h, nq * d), "matrix"),
+                (f"{p}.self_attn.q_norm.weight", (d,), "norm"),
+                (f"{p}.self_attn.k_norm.weight", (d,), "norm"),
+                (f"{p}.mlp.gate_proj.weight", (i, h), "matrix"),
+                (f"{p}.mlp.up_proj.weight", (i, h), "matrix"),
+                (f"{p}.mlp.down_proj.weight", (h, i), "matrix"),
+                (f"{p}.input_layernorm.weight", (h,), "norm"),
+                (f"{p}.post_attention_layernorm.weight", (h,), "norm")]
+    out.append(("model.norm.weight", (h,), "norm"))
+    if not cfg.get("tie_word_embeddings", False):
+        out.append(("lm_head.weight", (cfg["vocab_size"], h), "matrix"))
+    return out
+
+
 class PlainModel:
     """A model folder read once; ``logits(tokens)`` runs the whole sequence."""
+
+    @classmethod
+    def from_seed(cls, cfg, seed, matrices_as_bf16=False):
+        """No file: the seeded random weights as tests/plain/random_draw.py restates them
+        (matrices N(0, 0.02), norm weights 1 + N(0, 0.1))."""
+        from tests.plain import random_draw
+        self = cls.__new__(cls)
+        self.cfg = dict(cfg)
+        self.w = {}
+        for name, shape, role in tensor_list(cfg):
+            t = torch.from_numpy(random_draw.draw(seed, name, shape, role, 0.1 if role == "norm" else 0.02)).double()
+            self.w[name] = round_bf16(t) if (matrices_as_bf16 and t.dim() == 2) else t
+        self._memo = {}
+        return self
 
     def __init__(self, folder, matrices_as_bf16=False):
         self.cfg, self.w = read_folder(folder)

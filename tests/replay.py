@@ -171,3 +171,27 @@ def compare(steps, outputs, plain, requests, rtol, atol_scale, what):
                 f"col {c}: got {got[r, c]:.6g}, want {want[r, c]:.6g}, err {err[r, c]:.3g} > {bound[r, c]:.3g}")
         worst = max(worst, float((err / scale).max()))
     return worst
+
+
+# -- tolerances ------------------------------------------------------------------------------------
+# fp32: only summation order differs from the float64 plain implementation.
+FP32_TOL = (2e-5, 2e-5)
+# bfloat16: weights are the same bf16 values on both sides; the engine rounds activations to
+# bf16 (8 significant bits, relative step 2^-8) at about six places per layer.  This blanket
+# bound only catches gross faults; `check_worst` holds each case to what a clean run showed.
+BF16_TOL = (3e-2, 3e-2)
+
+
+def tolerance(dtype):
+    """(rtol, atol_scale) for :func:`compare`."""
+    return FP32_TOL if dtype == "float32" else BF16_TOL
+
+
+def check_worst(key, worst):
+    """Hold a case to twice the worst error (relative to the largest logit) that a clean run of
+    it showed (``tests/recorded_worst.py``), so that a defect small enough to hide under the
+    blanket tolerance (a misplaced key among forty, a dropped split) still fails."""
+    from tests.recorded_worst import RECORDED
+    print(f"worst {key!r}: {worst:.4e}")
+    if key in RECORDED:
+        assert worst <= 2.0 * RECORDED[key], f"{key}: worst error {worst:.3e} is more than twice the recorded {RECORDED[key]:.3e}"

@@ -112,3 +112,25 @@ def test_cli_truncation_flags_keep_their_order():
     params = SamplingParams(args.temp, args.seed, tuple(args.truncations))
     assert params.truncates and not SamplingParams(0.0, 0, tuple(args.truncations)).truncates
     assert build_parser().parse_args(["generate", "-m", "x", "-t", "1", "-n", "1"]).truncations is None
+
+
+def test_stop_ids_may_be_a_list_and_come_from_generation_config(tmp_path):
+    import json
+    from leone_b200.config.base import InvalidValue, WrongType
+    from leone_b200.registry import config_from_dict, config_from_folder, spec_from_config
+    from tests.tiny import TINY_B
+    cfg = config_from_dict({**TINY_B, "eos_token_id": [7, 9, 7]})
+    assert cfg.eos_token_ids == (7, 9) and cfg.eos_token_id == 7
+    assert spec_from_config(cfg).stop_ids() == (7, 9)
+    assert config_from_dict(cfg.to_json_dict()).eos_token_ids == (7, 9)          # survives a round trip
+    assert config_from_dict({**TINY_B, "eos_token_id": 5}).eos_token_ids == (5,)
+    assert spec_from_config(config_from_dict(TINY_B)).stop_ids() == ()
+    with pytest.raises(InvalidValue):
+        config_from_dict({**TINY_B, "eos_token_id": [7, 100000]})
+    with pytest.raises(WrongType):
+        config_from_dict({**TINY_B, "eos_token_id": "7"})
+    folder = tmp_path / "m"
+    folder.mkdir()
+    (folder / "config.json").write_text(json.dumps(TINY_B))
+    (folder / "generation_config.json").write_text(json.dumps({"eos_token_id": [3, 4]}))
+    assert config_from_folder(str(folder)).eos_token_ids == (3, 4)

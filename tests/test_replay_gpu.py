@@ -11,11 +11,8 @@ from tests.tiny import PAGE_TOKENS, make_folder
 
 pytestmark = pytest.mark.gpu
 
-# fp32: only summation order differs from the float64 plain implementation.
-FP32_TOL = dict(rtol=2e-5, atol_scale=2e-5)
-# bfloat16: weights are the same bf16 values on both sides; the engine rounds activations to
-# bf16 (8 significant bits, relative step 2^-8) at about six places per layer.
-BF16_TOL = dict(rtol=3e-2, atol_scale=3e-2)
+FP32_TOL = dict(zip(("rtol", "atol_scale"), replay.FP32_TOL))
+BF16_TOL = dict(zip(("rtol", "atol_scale"), replay.BF16_TOL))
 LENGTHS = [40, 7, 75, 33, 1, 64, 50]
 
 
@@ -52,7 +49,8 @@ def test_replay_in_process(folders, plains, which, dtype, mode):
                                 max_tokens=pool, max_requests=8, max_batch_tokens=128)
     out = replay.run_trace_engine(engine, steps)
     tol = FP32_TOL if dtype == "float32" else BF16_TOL
-    replay.compare(steps, out, plain, reqs, what=f"{which}/{dtype}/{mode}", **tol)
+    worst = replay.compare(steps, out, plain, reqs, what=f"{which}/{dtype}/{mode}", **tol)
+    replay.check_worst(("tiny", which, dtype, mode), worst)
     if mode == "mixed":
         pool_pages = engine.cache.groups[0].pool
         total_blocks = sum(-(-len(t) // engine.page_tokens) for t in reqs.values())

@@ -194,6 +194,21 @@ def test_eos_and_length():
     assert got["b"] == free[:4] and s.requests["b"].finish_reason == "length"
 
 
+def test_any_of_several_stop_ids_ends_a_request():
+    """A checkpoint may list several end ids; a request stops at the first one it samples."""
+    eng = FakeEngine(pages=16)
+    s = Scheduler(eng)
+    free = alone([9, 9], 6)
+    distinct = [t for i, t in enumerate(free) if t not in free[:i]]
+    assert len(distinct) >= 3
+    unused = next(t for t in range(1000) if t not in free)
+    s.add_request("a", [9, 9], 6, eos_token_id=[unused, distinct[2]])
+    s.add_request("b", [9, 9], 6, eos_token_id=(distinct[1], distinct[2]))
+    got = _run(s)
+    assert got["a"] == free[:free.index(distinct[2]) + 1] and s.requests["a"].finish_reason == "eos"
+    assert got["b"] == free[:free.index(distinct[1]) + 1] and s.requests["b"].finish_reason == "eos"
+
+
 @pytest.mark.parametrize("seed", range(5))
 def test_interleaved_transcripts_equal_isolated_ones(seed):
     """A scripted arrival trace: whatever the interleaving, each request's tokens are the ones
