@@ -319,6 +319,20 @@ int leone_cache_truncate(void* h, long long rid, long long length) {
   if (length > rc->committed)
     return fail(kRuleBroken, "request " + std::to_string(rid) + ": cannot truncate to " + std::to_string(length) +
                                  " past its length");
+  // A window group has given back the pages that queries past the committed length cannot
+  // see.  A query at a shorter length sees further back: if those pages are gone the rewind
+  // cannot be served from the cache (the tokens would have to be computed again), so it is
+  // refused before anything changes.
+  for (Group& g : m->groups) {
+    if (g.kind != 1) continue;
+    const std::vector<int>& table = g.tables[rid];
+    const long long keep = std::min<long long>(g.blocks_for(length), (long long)table.size());
+    for (long long b = g.first_live_block(length); b < keep; ++b)
+      if (table[b] < 0)
+        return fail(kRuleBroken, "request " + std::to_string(rid) + ": cannot truncate to " + std::to_string(length) +
+                                     ": its window has released block " + std::to_string(b) +
+                                     ", which a query at that length reads");
+  }
   for (Group& g : m->groups) {
     std::vector<int>& table = g.tables[rid];
     const size_t keep = (size_t)g.blocks_for(length);
@@ -494,7 +508,8 @@ struct SchedRequest {
   long long generated = 0;
   long long max_new = 0;
   long long arrival = 0;
-  long long reserved_pages = 0;
+  long long reserved_pages = 0;  // the largest of `needs` (what a caller is shown)
+  std::vector<long long> needs;  // pages set aside per cache group under the reserve policy
   long long preemptions = 0;
   int state = kWaiting;
   bool cancel = false;
@@ -506,6 +521,8 @@ struct Planner {
   long long max_running, max_waiting, max_batch_tokens, prefill_chunk;
   int policy, prefill_first;
   long long vocab, max_positions;
+  long long decode_quantum = 1;  // most decode steps reserved in one call
+  std::vector<long long> reserved_by_group;
   std::deque<long long> waiting;
   std::vector<long long> running;
   std::unordered_map<long long, SchedRequest> requests;
@@ -513,20 +530,31 @@ struct Planner {
   long long admitted = 0, finished = 0, cancelled = 0, preemptions = 0;
 
   bool has_groups() const { return cache != nullptr && !cache->groups.empty(); }
-  long long pages_for(long long tokens) const {
+  // The most tokens one request brings to a step: a prompt portion, or a decode quantum.
+  long long step_tokens() const { return std::max(std::min(prefill_chunk, max_batch_tokens), decode_quantum); }
+  // The most pages one request holds at a time in group g when it comes to hold `total` tokens.
+  // A full group keeps every page.  A window group holds, during a step from length c to
+  // c + portion, the blocks from first_live_block(c) to blocks_for(c + portion); past the
+  // window that count depends on c only through c mod page_tokens.
+  long long group_need(const Group& g, long long total) const {
+    const long long all = g.blocks_for(total);
+    if (g.kind != 1) return all;
     long long most = 0;
-    for (const Group& g : cache->groups) most = std::max(most, g.blocks_for(tokens));
-    return most;
+    for (long long c = g.window; c < g.window + g.page_tokens; ++c)
+      most = std::max(most, g.blocks_for(c + step_tokens()) - g.first_live_block(c));
+    return std::min(all, most);
   }
-  long long pool_pages() const {
-    long long least = 1ll << 30;
-    for (const Group& g : cache->groups) least = std::min(least, (long long)g.pool.n);
-    return least;
-  }
-  long long free_pages() const {
-    long long least = 1ll << 30;
-    for (const Group& g : cache->groups) least = std::min(least, (long long)g.pool.num_free());
-    return least;
+  // Per group, the request's need; false if some group's pool is too small even when empty.
+  bool fits_empty_pool(long long total, std::string* why) const {
+    for (size_t i = 0; i < cache->groups.size(); ++i) {
+      const Group& g = cache->groups[i];
+      if (group_need(g, total) > g.pool.n) {
+        *why = "the request needs " + std::to_string(group_need(g, total)) + " pages; the pool has " +
+               std::to_string(g.pool.n) + " even when empty";
+        return false;
+      }
+    }
+    return true;
   }
   SchedRequest* find(long long rid) {
     auto it = requests.find(rid);
@@ -537,6 +565,8 @@ struct Planner {
     leave_running(rid);
     reserved_total -= r->reserved_pages;
     r->reserved_pages = 0;
+    for (size_t i = 0; i < r->needs.size() && i < reserved_by_group.size(); ++i) reserved_by_group[i] -= r->needs[i];
+    r->needs.clear();
     r->state = was_cancelled ? kCancelled : kFinished;
     ++(was_cancelled ? cancelled : finished);
   }
@@ -560,6 +590,10 @@ void* leone_sched_create(void* cache, long long max_running, long long max_waiti
   p->max_positions = max_positions;
   return p;
 }
+// The most decode steps the caller will reserve in one call (a window group's worst case counts it).
+void leone_sched_set_decode_quantum(void* h, long long quantum) {
+  static_cast<Planner*>(h)->decode_quantum = std::max(1ll, quantum);
+}
 void leone_sched_destroy(void* h) { delete static_cast<Planner*>(h); }
 
 // A new request joins the queue.  Returns 0, or why it can never run (a Reject code; the
@@ -581,9 +615,8 @@ int leone_sched_add(void* h, long long rid, const long long* prompt, long long n
   if (need_positions > p->max_positions)
     return fail((Code)kPromptLimit, "prompt (" + std::to_string(n) + ") + max_new_tokens (" + std::to_string(max_new) +
                                         ") - 1 exceeds the model's " + std::to_string(p->max_positions) + " positions");
-  if (p->has_groups() && p->pages_for(need_positions) > p->pool_pages())
-    return fail((Code)kKvCapacity, "the request needs " + std::to_string(p->pages_for(need_positions)) +
-                                       " pages; the pool has " + std::to_string(p->pool_pages()) + " even when empty");
+  std::string why;
+  if (p->has_groups() && !p->fits_empty_pool(need_positions, &why)) return fail((Code)kKvCapacity, why);
   if ((long long)p->waiting.size() >= p->max_waiting)
     return fail((Code)kQueueLimit, std::to_string(p->max_waiting) + " requests are already waiting");
   SchedRequest r;
@@ -637,14 +670,33 @@ int leone_sched_admit(void* h, long long* out, int cap) {
     SchedRequest* r = p->find(rid);
     if (slots_free == 0) break;
     if (p->policy == 0) {
-      const long long need = p->has_groups() ? p->pages_for(r->n_tokens + (r->max_new - r->generated) - 1) : 0;
-      const long long total = p->has_groups() ? p->pool_pages() : (1ll << 30);
-      if (p->reserved_total + need > total) break;
-      r->reserved_pages = need;
-      p->reserved_total += need;
+      // every group must be able to set aside what the request holds there at its largest
+      // (crates/leone/src/scheduler.rs:652-667 reserves prompt + output, rounded up to pages)
+      const long long total = r->n_tokens + (r->max_new - r->generated) - 1;
+      std::vector<long long> needs;
+      bool fits = true;
+      if (p->has_groups()) {
+        p->reserved_by_group.resize(p->cache->groups.size(), 0);
+        for (size_t i = 0; i < p->cache->groups.size(); ++i) {
+          needs.push_back(p->group_need(p->cache->groups[i], total));
+          fits = fits && p->reserved_by_group[i] + needs[i] <= p->cache->groups[i].pool.n;
+        }
+      }
+      if (!fits) break;
+      r->reserved_pages = 0;
+      for (size_t i = 0; i < needs.size(); ++i) {
+        p->reserved_by_group[i] += needs[i];
+        r->reserved_pages = std::max(r->reserved_pages, needs[i]);
+      }
+      r->needs = needs;
+      p->reserved_total += r->reserved_pages;
     } else {
+      // the first portion must fit every group's free pages (nothing is released before a commit)
       const long long first = std::min(r->n_tokens, p->prefill_chunk);
-      if (!p->running.empty() && p->has_groups() && p->pages_for(first) > p->free_pages()) break;
+      bool fits = true;
+      if (!p->running.empty() && p->has_groups())
+        for (const Group& g : p->cache->groups) fits = fits && g.blocks_for(first) <= g.pool.num_free();
+      if (!fits) break;
     }
     p->waiting.pop_front();
     r->state = kRunning;

@@ -127,6 +127,7 @@ class Scheduler:
             c_longlong(engine.spec.max_positions)))
         if not self._h:
             raise ValueError("scheduler limits must be positive")
+        lib.leone_sched_set_decode_quantum(self._h, c_longlong(max(1, cfg.decode_quantum)))
         self.requests: Dict[Hashable, Request] = {}
         self._by_key: Dict[int, Request] = {}
         self._next_key = 1

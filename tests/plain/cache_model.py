@@ -259,6 +259,13 @@ class CacheManager:
         if length > rc.committed_len:
             raise CacheError(f"request {rid!r}: cannot truncate to {length} past its length")
         for g in self.groups:
+            # a rewind into what a window group has already released cannot be served
+            if g.spec.kind == "window":
+                table = g.tables[rid]
+                for b in range(g.first_live_block(length), min(g.blocks_for(length), len(table))):
+                    if table[b] < 0:
+                        raise CacheError(f"request {rid!r}: cannot truncate to {length}: block {b} was released")
+        for g in self.groups:
             table = g.tables[rid]
             keep = g.blocks_for(length)
             extra = [p for p in table[keep:] if p >= 0]

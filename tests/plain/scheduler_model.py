@@ -91,12 +91,27 @@ class Scheduler:
         self.requests: Dict[Hashable, Request] = {}
         self._arrivals = itertools.count()
         self._reserved_total = 0
+        self._reserved_by_group: List[int] = []
         self.stats = dict(steps=0, prefill_tokens=0, decode_tokens=0, preemptions=0, admitted=0,
                           finished=0, cancelled=0, max_batch_tokens_seen=0)
 
     # -- admission --------------------------------------------------------------------
-    def _pages_for(self, tokens: int) -> int:
-        return max(self.engine.cache.pages_needed_for(tokens))
+    def _needs(self, total: int) -> List[int]:
+        """Per cache group, the most pages a request that comes to hold ``total`` tokens holds at
+        one time: all its blocks in a full group; in a window group what lies between the first
+        block a query can still see and the end of the step's tokens, at the worst alignment."""
+        cfg = self.config
+        portion = max(min(cfg.prefill_chunk_tokens, cfg.max_batch_tokens), cfg.decode_quantum)
+        needs = []
+        for g in self.engine.cache.groups:
+            every = g.blocks_for(total)
+            if g.spec.kind != "window":
+                needs.append(every)
+                continue
+            w = g.spec.window
+            most = max(g.blocks_for(c + portion) - g.first_live_block(c) for c in range(w, w + g.page_tokens))
+            needs.append(min(every, most))
+        return needs
 
     def add_request(self, rid: Hashable, prompt: Sequence[int], max_new_tokens: int,
                     sampling=None, eos_token_id: Optional[int] = None) -> Request:
@@ -116,10 +131,10 @@ class Scheduler:
         if need_positions > spec.max_positions:
             raise AdmissionError("prompt_limit", f"prompt ({len(prompt)}) + max_new_tokens "
                                  f"({max_new_tokens}) - 1 exceeds the model's {spec.max_positions} positions")
-        num_pages = min(g.pool.num_pages for g in self.engine.cache.groups) if self.engine.cache.groups else 0
-        if self.engine.cache.groups and self._pages_for(need_positions) > num_pages:
-            raise AdmissionError("kv_capacity", f"the request needs {self._pages_for(need_positions)} pages; "
-                                 f"the pool has {num_pages} even when empty")
+        for g, need in zip(self.engine.cache.groups, self._needs(need_positions)):
+            if need > g.pool.num_pages:
+                raise AdmissionError("kv_capacity", f"the request needs {need} pages; "
+                                     f"the pool has {g.pool.num_pages} even when empty")
         if len(self.waiting) >= self.config.max_waiting:
             raise AdmissionError("queue_limit", f"{self.config.max_waiting} requests are already waiting")
         req = Request(rid, prompt, max_new_tokens, sampling, eos_token_id,
@@ -156,15 +171,20 @@ class Scheduler:
             if self.engine.cache.slots.num_free == 0:
                 break
             if cfg.policy == "reserve":
-                need = self._pages_for(len(req.tokens) + req.remaining_new - 1)
-                total = min(g.pool.num_pages for g in self.engine.cache.groups) if self.engine.cache.groups else 1 << 30
-                if self._reserved_total + need > total:
+                needs = self._needs(len(req.tokens) + req.remaining_new - 1)
+                groups = self.engine.cache.groups
+                if len(self._reserved_by_group) != len(groups):
+                    self._reserved_by_group = [0] * len(groups)
+                if any(have + need > g.pool.num_pages
+                       for have, need, g in zip(self._reserved_by_group, needs, groups)):
                     break
-                req.reserved_pages = need
-                self._reserved_total += need
+                self._reserved_by_group = [have + need for have, need in zip(self._reserved_by_group, needs)]
+                req.needs = needs
+                req.reserved_pages = max(needs, default=0)
+                self._reserved_total += req.reserved_pages
             else:
                 first = min(len(req.tokens), cfg.prefill_chunk_tokens)
-                if self.running and self._pages_for(first) > self._free_pages():
+                if self.running and any(g.blocks_for(first) > g.pool.num_free for g in self.engine.cache.groups):
                     break
             self.waiting.popleft()
             self.engine.open(req.rid)
@@ -207,6 +227,9 @@ class Scheduler:
         self.running.remove(req)
         self._reserved_total -= req.reserved_pages
         req.reserved_pages = 0
+        for i, need in enumerate(getattr(req, "needs", [])):
+            self._reserved_by_group[i] -= need
+        req.needs = []
         req.state = "cancelled" if reason == "cancelled" else "finished"
         req.finish_reason = reason
         self.stats["cancelled" if reason == "cancelled" else "finished"] += 1

@@ -193,5 +193,9 @@ def check_worst(key, worst):
     blanket tolerance (a misplaced key among forty, a dropped split) still fails."""
     from tests.recorded_worst import RECORDED
     print(f"worst {key!r}: {worst:.4e}")
+    log = os.environ.get("LEONE_WORST_LOG")         # a clean run's figures, to put into recorded_worst.py
+    if log:
+        with open(log, "a") as fh:
+            fh.write(f"    {key!r}: {worst:.3e},\n")
     if key in RECORDED:
         assert worst <= 2.0 * RECORDED[key], f"{key}: worst error {worst:.3e} is more than twice the recorded {RECORDED[key]:.3e}"

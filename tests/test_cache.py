@@ -82,6 +82,22 @@ def test_truncate():
         m.truncate("a", 6)
 
 
+def test_a_rewind_into_what_a_window_has_released_is_refused():
+    """Pages that a window has passed are gone; a query at a shorter length would read them."""
+    m = _manager(pages=16, page_tokens=4, window=6)
+    m.open("a")
+    m.reserve({"a": 30}), m.commit("a", 30)                 # blocks before position 24 are released
+    free = m.free_pages()
+    table = list(m.groups[0].tables["a"])
+    with pytest.raises(CacheError, match="released"):
+        m.truncate("a", 20)                                 # needs keys from position 15: block 3 is gone
+    assert m.length("a") == 30 and m.free_pages() == free and m.groups[0].tables["a"] == table
+    m.truncate("a", 29)                                     # needs keys from 24: still there
+    assert m.length("a") == 29
+    m.rollback("a")                                         # a rollback never goes below the committed length
+    m.check_invariants()
+
+
 def test_table_version_changes_only_when_a_table_does_not_just_grow():
     m = _manager(pages=16, page_tokens=4)
     m.open("a")

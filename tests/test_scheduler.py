@@ -19,10 +19,12 @@ class FakeEngine:
     """The engine's interface without a model: the 'next token' is a function of the request's
     tokens so far, so any scheduling must produce the same stream as running alone."""
 
-    def __init__(self, pages=8, page_tokens=4, slots=4, cache_module=None):
+    def __init__(self, pages=8, page_tokens=4, slots=4, cache_module=None, windows=(None,)):
+        """``windows``: one cache group per entry; None is a full group, a number a window group."""
         self.spec = FakeSpec()
         make, group = (cache_module.CacheManager, cache_module.GroupSpec) if cache_module else (CacheManager, GroupSpec)
-        self.cache = make([group("full", 1, 8)], page_tokens, pages, slots)
+        self.cache = make([group("window", 1, 8, w) if w else group("full", 1, 8) for w in windows],
+                          page_tokens, pages, slots)
         self.seen = {}
         self.batches = []
 
@@ -274,8 +276,9 @@ def test_the_native_planner_and_the_plain_scheduler_agree_step_by_step(seed):
                   policy=policy, prefill_first=bool(seed % 3 == 0))
     make = FakeGraphEngine if seed % 4 >= 2 else FakeEngine       # with and without decode quanta
     limits["decode_quantum"] = rng.choice([1, 2, 4])
-    ea = make(pages, page_tokens, slots)
-    eb = make(pages, page_tokens, slots, cache_module=cache_model)
+    windows = [(None,), (None, 6), (5,)][seed % 3]               # one full group; full + window; a window alone
+    ea = make(pages, page_tokens, slots, windows=windows)
+    eb = make(pages, page_tokens, slots, cache_module=cache_model, windows=windows)
     a = Scheduler(ea, SchedulerConfig(**limits))
     b = scheduler_model.Scheduler(eb, scheduler_model.SchedulerConfig(**limits))
     arrivals = 0
@@ -318,6 +321,46 @@ def test_the_native_planner_and_the_plain_scheduler_agree_step_by_step(seed):
         ra = a.requests[rid]
         assert (ra.state, ra.finish_reason, ra.generated, ra.tokens, ra.computed, ra.preemptions, ra.reserved_pages) == \
                (rb.state, rb.finish_reason, rb.generated, rb.tokens, rb.computed, rb.preemptions, rb.reserved_pages), rid
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_admission_counts_each_group_and_a_reserved_request_never_runs_out(seed):
+    """Under the reserve policy every group sets aside what a request holds there at its largest:
+    all its blocks in a full group, a window's worth in a window group.  With a window group
+    alone, more requests run at once than their full lengths would allow, and no step of an
+    admitted request ever fails for pages."""
+    rng = random.Random(900 + seed)
+    page_tokens, window = rng.choice([2, 4]), rng.choice([3, 6, 9])
+    cfg = SchedulerConfig(max_running=6, max_batch_tokens=rng.choice([6, 16]), prefill_chunk_tokens=rng.choice([3, 5]),
+                          decode_quantum=rng.choice([1, 4]), policy="reserve")
+    portion = max(min(cfg.prefill_chunk_tokens, cfg.max_batch_tokens), cfg.decode_quantum)
+    worst = -(-(window + portion) // page_tokens) + 1
+    make = FakeGraphEngine if cfg.decode_quantum > 1 else FakeEngine
+    eng = make(pages=3 * worst, page_tokens=page_tokens, slots=6, windows=(window,))
+    s = Scheduler(eng, cfg)
+    specs = {i: ([rng.randrange(100) for _ in range(rng.randint(20, 40))], rng.randint(5, 20)) for i in range(6)}
+    for i, (prompt, n) in specs.items():
+        s.add_request(i, prompt, n)
+    most_running = 0
+    guard = 0
+    while s.has_work():
+        s.step()                                       # OutOfPages here would fail the test
+        most_running = max(most_running, len(s.running))
+        guard += 1
+        assert guard < 5000
+    # by full length each request would need at least 25 / page_tokens pages: fewer would fit
+    by_full_length = (3 * worst) // -(-25 // page_tokens)
+    assert most_running >= 3 and most_running >= by_full_length
+    for i, (prompt, n) in specs.items():
+        assert s.requests[i].generated == alone(prompt, n), i
+    assert eng.cache.free_pages() == [3 * worst]
+    # two groups: the full group is the one that limits
+    eng2 = FakeEngine(pages=12, page_tokens=4, slots=6, windows=(None, 4))
+    s2 = Scheduler(eng2, SchedulerConfig(max_running=6, policy="reserve"))
+    for i in range(3):
+        s2.add_request(i, [1] * 20, 4)                 # 23 positions: 6 pages of the full group each
+    s2.step()
+    assert len(s2.running) == 2 and len(s2.waiting) == 1
 
 
 def test_sampler_options_through_the_scheduler_on_emulated_kernels(tmp_path):
