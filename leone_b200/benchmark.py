@@ -338,7 +338,7 @@ def run(gpus: int, steps: int, warmup: int, impl: str, layers: Optional[int] = N
            # a step launched ahead gets the host's positions and lengths (2 x 4 bytes a request) and
            # new block-table entries; the first step of a run gets the whole metadata buffer
            "h2d_bytes_per_step": int(8 * batch + 4) if engine.lookahead else
-           int(graph.size * 4 + graph.sample_host.numel() * 8),
+           int(graph.size * 4 + batch * 64),
            "d2h_bytes_per_step": int(batch * 4 + 16),
            "prefill_tokens_per_s": stats.prefill_tokens_per_second}
 

@@ -370,11 +370,20 @@ __device__ __forceinline__ double warp_sum_f64(double v) {
 // weights with coalesced loads; the run that holds u * total is found by a scan over the 32
 // warp sums in id order, and that warp walks its run 32 ids at a time with a warp prefix sum,
 // so the chosen token is the first in id order whose cumulative weight exceeds the target.
+//
+// The sampling parameters of a row come either from three arrays indexed by row, or (records !=
+// null) from the per-request slot records: row r belongs to slot slot_ids[r], whose record holds
+// the position of the token being sampled (field kSlotPosition), the seed (kSlotSeed) and the
+// temperature (kSlotTemperature, fp32 bits).
+constexpr int kSlotFields = 8;
+constexpr int kSlotLength = 0, kSlotPosition = 1, kSlotSeed = 2, kSlotTemperature = 3, kSlotLastToken = 4;
+
 __global__ void __launch_bounds__(1024)
 sample_kernel(const float* __restrict__ logits, int vocab,
                               const float* __restrict__ temperature,
                               const long long* __restrict__ seeds,
-                              const long long* __restrict__ positions, int* __restrict__ out) {
+                              const long long* __restrict__ positions, int* __restrict__ out,
+                              const int* __restrict__ slot_ids, const long long* __restrict__ records) {
   __shared__ float s_val[32];
   __shared__ int s_idx[32];
   __shared__ double s_sum[32];
@@ -412,7 +421,8 @@ sample_kernel(const float* __restrict__ logits, int vocab,
   __syncthreads();
   const float top = s_val[0];
   const int top_i = s_idx[0];
-  const float temp = temperature ? temperature[row] : 0.f;
+  const long long* record = records ? records + (size_t)slot_ids[row] * kSlotFields : nullptr;
+  const float temp = record ? __int_as_float((int)record[kSlotTemperature]) : (temperature ? temperature[row] : 0.f);
   if (!(temp > 0.f) || top_i < 0) {
     if (tid == 0) out[row] = top_i;
     return;
@@ -432,8 +442,9 @@ sample_kernel(const float* __restrict__ logits, int vocab,
     double total = 0.0;
     for (int i = 0; i < 32; ++i) total += s_sum[i];
     const unsigned long long purpose = 0xbf58476d1ce4e5b9ull;
-    const unsigned long long mixed = splitmix64(
-        (unsigned long long)seeds[row] ^ splitmix64((unsigned long long)positions[row] ^ purpose));
+    const unsigned long long seed = (unsigned long long)(record ? record[kSlotSeed] : seeds[row]);
+    const unsigned long long position = (unsigned long long)(record ? record[kSlotPosition] : positions[row]);
+    const unsigned long long mixed = splitmix64(seed ^ splitmix64(position ^ purpose));
     const double u = (double)(mixed >> 11) * (1.0 / 9007199254740992.0);
     const double target = u * total;
     double c = 0.0;
@@ -487,9 +498,12 @@ sample_kernel(const float* __restrict__ logits, int vocab,
 // its decode position in a device word that a kernel increments for graph replay
 // (crates/leone-cuda/cuda/ie_cuda.cu:2940); this is the same idea for a whole batch.
 // ---------------------------------------------------------------------------
+// With slot records (records != null) the request's record is advanced instead of sample_pos:
+// its position and length by one, its last token set.
 __global__ void decode_advance_kernel(int* token_ids, int* positions, int* ctx_len,
                                       long long* sample_pos, const int* sampled, int* history,
-                                      int* step_counter, int n, int max_steps) {
+                                      int* step_counter, int n, int max_steps, const int* slot_ids,
+                                      long long* records) {
   pdl_trigger();
   pdl_wait();
   const int step = *step_counter;
@@ -499,7 +513,14 @@ __global__ void decode_advance_kernel(int* token_ids, int* positions, int* ctx_l
     token_ids[i] = tok;
     positions[i] += 1;
     ctx_len[i] += 1;
-    sample_pos[i] += 1;
+    if (records) {
+      long long* record = records + (size_t)slot_ids[i] * kSlotFields;
+      record[kSlotPosition] += 1;
+      record[kSlotLength] += 1;
+      record[kSlotLastToken] = tok;
+    } else {
+      sample_pos[i] += 1;
+    }
     if (step < max_steps) history[(size_t)step * n + i] = tok;
   }
   if (threadIdx.x == 0) *step_counter = step + 1;
@@ -511,11 +532,13 @@ using namespace leone;
 
 extern "C" int leone_decode_advance(int* token_ids, int* positions, int* ctx_len,
                                     long long* sample_pos, const int* sampled, int* history,
-                                    int* step_counter, int n, int max_steps, cudaStream_t stream) {
+                                    int* step_counter, int n, int max_steps, const int* slot_ids,
+                                    long long* records, cudaStream_t stream) {
   if (n <= 0) return 0;
+  if ((records != nullptr) == (sample_pos != nullptr)) return kRefusedSize;    // one of the two
   return launch_kernel(decode_advance_kernel, dim3(1), dim3(n < 1024 ? ((n + 31) / 32) * 32 : 1024), 0,
                        stream, token_ids, positions, ctx_len, sample_pos, sampled, history,
-                       step_counter, n, max_steps);
+                       step_counter, n, max_steps, slot_ids, records);
 }
 
 // Turns programmatic dependent launch on or off for the kernels of this library.
@@ -635,5 +658,14 @@ extern "C" int leone_sample(const float* logits, int rows, int vocab, const floa
   if (rows <= 0) return 0;
   if (vocab <= 0) return kRefusedSize;
   return launch_kernel(sample_kernel, dim3(rows), dim3(1024), 0, stream, logits, vocab, temperature,
-                       seeds, positions, out);
+                       seeds, positions, out, (const int*)nullptr, (const long long*)nullptr);
+}
+
+// The same with every row's parameters taken from its request's slot record.
+extern "C" int leone_sample_slots(const float* logits, int rows, int vocab, const int* slot_ids,
+                                  const long long* records, int* out, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (vocab <= 0 || slot_ids == nullptr || records == nullptr) return kRefusedSize;
+  return launch_kernel(sample_kernel, dim3(rows), dim3(1024), 0, stream, logits, vocab, (const float*)nullptr,
+                       (const long long*)nullptr, (const long long*)nullptr, out, slot_ids, records);
 }

@@ -43,8 +43,6 @@ class DecodeGraph:
         self.size = packed.size
         self.meta = torch.zeros(self.size, dtype=torch.int32, device=dev)
         self.meta_host = torch.zeros(self.size, dtype=torch.int32, pin_memory=True)
-        self.sample_host = torch.zeros(3 * batch, dtype=torch.int64, pin_memory=True)
-        self.sample_dev = torch.zeros(3 * batch, dtype=torch.int64, device=dev)
         self.sampled = torch.zeros(batch, dtype=torch.int32, device=dev)
         self.history = torch.zeros((max_quantum, batch), dtype=torch.int32, device=dev)
         self.history_host = torch.zeros((max_quantum, batch), dtype=torch.int32, pin_memory=True)
@@ -57,7 +55,6 @@ class DecodeGraph:
         self.bucket = None
         self._filled_rids = None           # what fill() last wrote into the host copy
         self._filled_pages = [[0] * batch for _ in engine.cache.groups]
-        self._filled_sampling = None
         self._tables_at = min((o for o, _ in self.bt_offsets), default=None)   # where the block tables start
         self._events = [torch.cuda.Event(), torch.cuda.Event()]
         self._advance_host = [torch.zeros((2, batch), dtype=torch.int32, pin_memory=True) for _ in range(2)]
@@ -105,10 +102,12 @@ class DecodeGraph:
         e = self.engine
         b = self.batch
         logits = e.model.forward(self.ctx)
-        temps = self.sample_dev[:b].view(torch.float32)[:b]
-        e.ops.sample(logits, temps, self.sample_dev[b:2 * b], self.sample_dev[2 * b:3 * b], self.sampled)
-        e.ops.decode_advance(self.ctx.token_ids, self.ctx.positions, self.ctx.ctx_len,
-                             self.sample_dev[2 * b:3 * b], self.sampled, self.history, self.counter)
+        # temperature, seed and position of every row come from its request's slot record, which
+        # the advance kernel moves on by a token, like the step's own positions and lengths
+        records = e.slot_records.on_device
+        e.ops.sample_slots(logits, self.ctx.slot_ids, records, self.sampled)
+        e.ops.decode_advance(self.ctx.token_ids, self.ctx.positions, self.ctx.ctx_len, None, self.sampled,
+                             self.history, self.counter, slot_ids=self.ctx.slot_ids, records=records)
 
     def fill(self, rids: Sequence[Hashable], last_tokens: Sequence[int], lengths: Sequence[int], params,
              versions=None, slots=None, table_lens=None):
@@ -157,13 +156,14 @@ class DecodeGraph:
                     appended.append((o + i * shape[1] + done, o + i * shape[1] + n))
                 self._filled_pages[gi][i] = n
         self._filled_rids = key
-        sh = self.sample_host.numpy()
-        sampling = [(p.temperature, p.seed) for p in params]
-        if not same or sampling != self._filled_sampling:
-            self.sample_host[:b].view(torch.float32).numpy()[:b] = np.array([t for t, _ in sampling], dtype=np.float32)
-            sh[b:2 * b] = np.array([s_ & 0xFFFF_FFFF_FFFF_FFFF for _, s_ in sampling], dtype=np.uint64).view(np.int64)
-            self._filled_sampling = sampling
-        sh[2 * b:3 * b] = lengths      # position of the token being fed
+        # the requests' slot records: sampling parameters, and where each stands (the position
+        # of the token being fed is the position that is sampled at)
+        records = e.slot_records
+        row_slots = slots if slots is not None else [e.cache.slot(r) for r in rids]
+        for slot, p, length, tok in zip(row_slots, params, lengths, last_tokens):
+            records.set_sampling(int(slot), p.seed, p.temperature)
+            records.set_progress(int(slot), int(length), int(length), int(tok))
+        records.sync()
         if same and self._tables_at is not None:
             # same requests in the same rows: the per-token and per-sequence vectors, and the
             # block-table entries that were appended
@@ -172,7 +172,6 @@ class DecodeGraph:
                 self.meta[lo:hi].copy_(self.meta_host[lo:hi], non_blocking=True)
         else:
             self.meta.copy_(self.meta_host, non_blocking=True)
-        self.sample_dev.copy_(self.sample_host, non_blocking=True)
         self.counter.zero_()
 
     def capture(self, bucket: int):

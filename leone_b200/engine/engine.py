@@ -21,6 +21,7 @@ import numpy as np
 import torch
 
 from ..cache.pages import CacheManager, GroupSpec, OutOfPages
+from ..cache.slots import SlotRecords
 from ..parts.base import FixedState, PagedCacheView, PagedKV, Runtime, StateView
 from ..parts.spec import ModelSpec
 from ..registry import config_from_folder, spec_from_config
@@ -155,6 +156,7 @@ class Engine:
             v_pool = torch.zeros(head + (v_el // (gs.num_kv_heads * page_tokens),), dtype=gs.dtype,
                                  device=self.device) if v_el else None
             self.pools.append((k_pool, v_pool))
+        self.slot_records = SlotRecords(max_requests, self.device)
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
         if hasattr(self.ops, "bind_status"):
             self.ops.bind_status(self.status)
@@ -190,15 +192,21 @@ class Engine:
 
     # -- request lifetime ---------------------------------------------------------------
     def open(self, rid: Hashable) -> int:
+        """A new request: block tables in every group and one state slot, whose record and
+        fixed-size state rows start at zero."""
         self.drop_lookahead()
         slot = self.cache.open(rid)
+        self.slot_records.open(slot)
         for state in self._run_state.values():
             state[slot].zero_()
         return slot
 
     def close(self, rid: Hashable) -> None:
+        """The request's pages and its slot (with its record) go back."""
         self.drop_lookahead()
+        slot = self.cache.slot(rid)
         self.cache.close(rid)
+        self.slot_records.close(slot)
 
     def length(self, rid: Hashable) -> int:
         return self.cache.length(rid)
@@ -299,12 +307,21 @@ class Engine:
             for rid in opened:
                 self.cache.close(rid)
             raise
+        saved = None
         try:
+            if self._run_state:
+                # fixed-size state is overwritten in place: keep the step's slots as they were,
+                # so that a failed step leaves them (like the pages) as it found them
+                rows = torch.tensor([self.cache.slot(e.rid) for e in entries], dtype=torch.long, device=self.device)
+                saved = (rows, {pos: st.index_select(0, rows) for pos, st in self._run_state.items()})
             ctx = self.build_context(entries)
             logits = self.model.forward(ctx)
             if check:
                 self.check_status()
         except Exception:
+            if saved is not None:
+                for pos, rows_before in saved[1].items():
+                    self._run_state[pos].index_copy_(0, saved[0], rows_before)
             for e in entries:
                 self.cache.rollback(e.rid)
             for rid in opened:

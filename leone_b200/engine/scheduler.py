@@ -91,6 +91,7 @@ class Request:
     preemptions: int = 0
     cancel_requested: bool = False
     key: int = 0                                         # the planner's name for this request
+    slot: Optional[int] = None                           # its state slot while it runs
     sampler_state: Optional[SamplerState] = None         # what the sampler remembers between tokens
 
     @property
@@ -220,6 +221,7 @@ class Scheduler:
             req.state, req.finish_reason = "cancelled", "cancelled"
         elif what == 2:
             req.cancel_requested = True
+            self._record(req, cancel=True)
 
     # -- one step's decisions -----------------------------------------------------------
     def _keys(self, n: int) -> List[int]:
@@ -230,14 +232,32 @@ class Scheduler:
         for key in self._keys(n):
             req = self._by_key[key]
             self.engine.close(req.rid)
-            req.state, req.finish_reason, req.reserved_pages = "cancelled", "cancelled", 0
+            req.state, req.finish_reason, req.reserved_pages, req.slot = "cancelled", "cancelled", 0, None
+
+    def _record(self, req: Request, **fields) -> None:
+        """Mirror the request's state into its slot record (``leone_b200.cache.slots``): the
+        record is what the captured decode step reads, and where the request's sampling state,
+        progress and cancellation flag live for as long as it holds its slot."""
+        records = getattr(self.engine, "slot_records", None)
+        if records is None or req.slot is None:
+            return
+        if "sampling" in fields:
+            records.set_sampling(req.slot, req.sampling.seed, req.sampling.temperature)
+        if "progress" in fields:
+            records.set_progress(req.slot, req.computed, max(len(req.tokens) - 1, 0),
+                                 req.tokens[-1] if req.tokens else None)
+        if "cancel" in fields:
+            records.request_cancel(req.slot)
+        if "sampler" in fields and req.sampler_state is not None and req.sampler_state.maximum_surprise is not None:
+            records.set_sampler_state(req.slot, req.sampler_state.maximum_surprise)
 
     def _try_admit(self) -> None:
         """Move requests from the queue to running, in arrival order, while they fit."""
         n = self._lib.leone_sched_admit(self._h, self._buf[0], self._cap)
         for key in self._keys(n):
             req = self._by_key[key]
-            self.engine.open(req.rid)
+            req.slot = self.engine.open(req.rid)
+            self._record(req, sampling=True, progress=True, sampler=True)
             req.state, req.computed = "running", 0
             req.reserved_pages = int(self._lib.leone_sched_get(self._h, c_longlong(key), 4))
 
@@ -257,9 +277,10 @@ class Scheduler:
         is_eos = tok in req.stop_ids
         code = self._lib.leone_sched_emitted(self._h, c_longlong(req.key), int(is_eos))
         if code <= 0:
+            self._record(req, progress=True, sampler=True)
             return None
         self.engine.close(req.rid)
-        req.state, req.finish_reason, req.reserved_pages = "finished", _FINISH[code], 0
+        req.state, req.finish_reason, req.reserved_pages, req.slot = "finished", _FINISH[code], 0, None
         return req.finish_reason
 
     def _preempt_youngest(self) -> bool:
@@ -270,7 +291,7 @@ class Scheduler:
             return False
         req = self._by_key[victim.value]
         self.engine.close(req.rid)
-        req.state, req.computed = "waiting", 0
+        req.state, req.computed, req.slot = "waiting", 0, None
         req.preemptions += 1
         return True
 
@@ -371,7 +392,7 @@ class Scheduler:
                 reason = None
                 if code > 0:
                     self.engine.close(req.rid)
-                    req.state, req.finish_reason, req.reserved_pages = "finished", _FINISH[code], 0
+                    req.state, req.finish_reason, req.reserved_pages, req.slot = "finished", _FINISH[code], 0, None
                     reason = req.finish_reason
                 else:
                     still.append(i)

@@ -252,9 +252,20 @@ def main(argv=None) -> int:
                     help="gemm: fold an RMSNorm after (out) or before (in) the product into it")
     ap.add_argument("--cluster", action="store_true",
                     help="gemm with --splits: sum the splits inside thread-block clusters")
+    ap.add_argument("--decode-splits", type=int, default=0,
+                    help="decode-attention: split every sequence's keys this many ways (0: the dispatcher's choice)")
+    ap.add_argument("--max-cluster", type=int, default=8, help="largest thread-block cluster the dispatchers may use")
+    ap.add_argument("--gemm-splits", default="",
+                    help='layer-shapes: forced splits by product, "6144x4096:4,4096x12288:c8" (c: inside a cluster)')
     args = ap.parse_args(argv)
     from .ops.cuda import CudaOps
     ops = CudaOps(DEV, torch.bfloat16)
+    ops.fast.force_decode_splits = args.decode_splits
+    ops.fast.max_cluster = args.max_cluster
+    for item in filter(None, args.gemm_splits.split(",")):
+        shape, _, how = item.partition(":")
+        n_, _, k_ = shape.partition("x")
+        ops.fast.split_override[(int(n_), int(k_))] = (int(how.lstrip("c")), how.startswith("c"))
     peaks = measured_peaks()
     flush = torch.zeros(64 << 20, device=DEV) if args.flush else None
     rows = []

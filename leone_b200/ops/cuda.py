@@ -353,6 +353,19 @@ class CudaOps:
         _check(self.core.leone_sample(_ptr(logits), rows, vocab, _ptr(temperature), _ptr(seeds),
                                       _ptr(positions), _ptr(out), self._stream()), "sample")
 
+    def sample_slots(self, logits, slot_ids, records, out):
+        """One token per row with the row's temperature, seed and position taken from the slot
+        record of its request (``records``: int64 ``[slots, 8]`` on the device, see
+        :mod:`leone_b200.cache.slots`)."""
+        rows, vocab = logits.shape
+        _need(logits.dtype == torch.float32 and logits.is_contiguous(), "logits must be fp32")
+        _need(slot_ids.dtype == torch.int32 and slot_ids.numel() >= rows and records.dtype == torch.int64
+              and records.is_contiguous() and records.shape[1] == 8 and out.dtype == torch.int32
+              and out.numel() >= rows, "sample_slots arguments")
+        self.launches += 1
+        _check(self.core.leone_sample_slots(_ptr(logits), rows, vocab, _ptr(slot_ids), _ptr(records), _ptr(out),
+                                            self._stream()), "sample_slots")
+
     def penalize(self, logits, entries, penalties):
         """Penalties from the decode history, in place: ``entries`` lists (row, token, occurrences
         in the row's window, DRY penalty), each (row, token) once; ``penalties[row]`` holds the
@@ -412,12 +425,21 @@ class CudaOps:
         result = (out,) + ((probs,) if want_probs else ()) + ((chosen,) if mu is not None else ())
         return result if len(result) > 1 else out
 
-    def decode_advance(self, token_ids, positions, ctx_len, sample_pos, sampled, history, counter):
+    def decode_advance(self, token_ids, positions, ctx_len, sample_pos, sampled, history, counter,
+                       slot_ids=None, records=None):
+        """Feeds the sampled ids back as the next step's inputs.  Either ``sample_pos`` (int64 per
+        row) is advanced, or, with ``slot_ids`` and ``records``, each request's slot record."""
         n = token_ids.numel()
-        _need(history.dtype == torch.int32 and history.shape[1] == n and counter.dtype == torch.int32
-              and sample_pos.dtype == torch.int64, "decode_advance arguments")
+        _need(history.dtype == torch.int32 and history.shape[1] == n and counter.dtype == torch.int32,
+              "decode_advance arguments")
+        if records is not None:
+            _need(sample_pos is None and slot_ids is not None and slot_ids.dtype == torch.int32
+                  and records.dtype == torch.int64 and records.shape[1] == 8, "decode_advance: slot records")
+        else:
+            _need(sample_pos is not None and sample_pos.dtype == torch.int64, "decode_advance: sample positions")
         self.launches += 1
         _check(self.core.leone_decode_advance(_ptr(token_ids), _ptr(positions), _ptr(ctx_len),
                                               _ptr(sample_pos), _ptr(sampled), _ptr(history),
-                                              _ptr(counter), n, history.shape[0], self._stream()),
+                                              _ptr(counter), n, history.shape[0], _ptr(slot_ids), _ptr(records),
+                                              self._stream()),
                "decode_advance")

@@ -44,17 +44,13 @@ class FastKernels:
         self.token_major_from = 64         # tokens above which the token-major form is considered
         self.token_major_split_from = 128  # .. and its split along K (up to 128 tokens the swapped form's split measured the same or better)
         self.token_major_fill = 0.6        # of the SMs that its tiles must fill
-        self.force_decode_splits = int(os.environ.get("LEONE_DECODE_SPLITS", "0"))    # tuning aid
+        self.force_decode_splits = 0       # > 0: every decode attention splits its keys this many ways (kernel_bench sets it)
         # LEONE_NO_FUSED_DECODE=1 keeps q/k norm, rotation and cache write in their own kernel
         self.fuse_decode = os.environ.get("LEONE_NO_FUSED_DECODE", "0") != "1"
-        self.max_cluster = int(os.environ.get("LEONE_MAX_CLUSTER", "8"))
-        # tuning aid: LEONE_GEMM_SPLITS="6144x4096:4,4096x12288:c8" forces the split of [n x k]
-        # products at decode sizes ("c": summed inside a cluster)
+        self.max_cluster = 8               # the portable cluster size
+        # (n, k) -> (splits, cluster): a forced split of an [n x k] product at decode sizes; empty
+        # in the product, filled by kernel_bench's sweeps
         self.split_override = {}
-        for item in filter(None, os.environ.get("LEONE_GEMM_SPLITS", "").split(",")):
-            shape, _, how = item.partition(":")
-            n_, _, k_ = shape.partition("x")
-            self.split_override[(int(n_), int(k_))] = (int(how.lstrip("c")), how.startswith("c"))
         self.status = None
         self._attn_ws = None
         self.use_tiled_attention = os.environ.get("LEONE_NO_TILED_ATTENTION", "0") != "1"

@@ -21,7 +21,9 @@ CASES = [
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference/research/prefix_attention"
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_attention_golden.py <the reference checkout's research/prefix_attention folder>")
+    ref = sys.argv[1]
     sys.path.insert(0, ref)
     import common_oracle as oracle
     out = []

@@ -7,9 +7,10 @@ from dataclasses import dataclass
 import torch
 
 from leone_b200.config.base import ConfigReader, ModelConfig
-from leone_b200.parts.base import FeedForward, FixedState, Mixer, PositionEncoding, WeightSpec
+from leone_b200.parts.base import (Embedding, FeedForward, FixedState, Mixer, PagedKV, PositionEncoding,
+                                   WeightSpec)
 from leone_b200.parts.spec import LayerSpec, ModelSpec, PartSpec
-from leone_b200.registry import ARCHITECTURES, FEED_FORWARDS, MIXERS, POSITION_ENCODINGS
+from leone_b200.registry import ARCHITECTURES, EMBEDDINGS, FEED_FORWARDS, MIXERS, POSITION_ENCODINGS
 
 
 class DecayMixer(Mixer):
@@ -32,6 +33,13 @@ class DecayMixer(Mixer):
         return FixedState((self.size,))
 
     def forward(self, ctx, cache, x, hidden):
+        if ctx.decode_only:
+            # one token per sequence, no host read: this is what a captured decode step replays
+            slots = ctx.slot_ids.long()
+            state = self.decay * cache.state[slots] + (1.0 - self.decay) * x.float()
+            cache.state.index_copy_(0, slots, state)
+            hidden += state @ self.w.float().t()
+            return
         slots = ctx.slot_ids.tolist()
         bounds = ctx.q_start.tolist()
         for s, slot in enumerate(slots):
@@ -77,12 +85,11 @@ class RoutedFeedForward(FeedForward):
         share = lead / (lead.sum(dim=-1, keepdim=True) + 1e-6)
         chosen = chosen[:, :self.top_k]
         for e in range(self.experts):
-            rows, which = (chosen == e).nonzero(as_tuple=True)
-            if rows.numel() == 0:
-                continue
-            inner = torch.relu(xf[rows] @ self.w[f"experts.{e}.in.weight"].float().t())
-            out = inner @ self.w[f"experts.{e}.out.weight"].float().t()
-            hidden.index_add_(0, rows, (out * share[rows, which][:, None]).to(hidden.dtype))
+            # every row through every expert, weighted by its share there (zero where not chosen):
+            # no host read, so a captured decode step can replay it
+            weight = (share * (chosen == e)).sum(dim=-1, keepdim=True)
+            inner = torch.relu(xf @ self.w[f"experts.{e}.in.weight"].float().t())
+            hidden += (inner @ self.w[f"experts.{e}.out.weight"].float().t()) * weight
 
 
 class AdditivePositions(PositionEncoding):
@@ -100,6 +107,68 @@ class AdditivePositions(PositionEncoding):
         enc = self.amplitude * torch.sin(ctx.positions.float()[:, None] * dims[None, :] * self.rate)
         q.copy_((q.float() + enc[:, None, :]).to(q.dtype))
         k.copy_((k.float() + enc[:, None, :]).to(k.dtype))
+
+
+class LatentMixer(Mixer):
+    """Caches one latent vector per token, ``c_t = W_down x_t``, and nothing else: its paged cache
+    has a key pool of its own width, no value pool, and is kept in float32 whatever the run
+    dtype.  ``hidden_t += W_up sum_j softmax_j(c_t . c_j / sqrt(L)) c_j`` over ``j <= t``."""
+
+    def __init__(self, params, rt):
+        super().__init__(params, rt)
+        self.size = int(params["hidden_size"])
+        self.latent = int(params["latent_size"])
+        self.w = None
+
+    def weight_specs(self):
+        return [WeightSpec("down.weight", (self.latent, self.size)), WeightSpec("up.weight", (self.size, self.latent))]
+
+    def load(self, tensors):
+        self.w = tensors
+
+    def cache_request(self):
+        return PagedKV(1, self.latent, value_head_dim=0, dtype=torch.float32, tag="latent")
+
+    def forward(self, ctx, cache, x, hidden):
+        assert cache.v_pool is None and cache.k_pool.dtype == torch.float32
+        page = cache.page_tokens
+        c = x.float() @ self.w["down.weight"].float().t()                      # [N, L]
+        seq = ctx.seq_of_token.long()
+        pos = ctx.positions.long()
+        table = cache.block_table.long()                                        # [B, W]
+        cache.k_pool.index_put_((table[seq, pos // page], torch.zeros_like(pos), pos % page), c)
+        keys = cache.k_pool[table.clamp(min=0)][:, :, 0].flatten(1, 2)          # [B, W * page, L]
+        mine = keys[seq]                                                        # [N, W * page, L]
+        scores = torch.einsum("nl,nkl->nk", c, mine) / self.latent ** 0.5
+        seen = torch.arange(mine.shape[1], device=c.device)[None, :] <= pos[:, None]
+        probs = torch.softmax(scores.masked_fill(~seen, float("-inf")), dim=-1)
+        mixed = torch.einsum("nk,nkl->nl", probs, torch.where(seen[:, :, None], mine, torch.zeros_like(mine)))
+        hidden += mixed @ self.w["up.weight"].float().t()
+
+
+class PositionalEmbedding(Embedding):
+    """``h_t = scale * E[id_t] + P[position_t]``: a multiplier and learned absolute positions,
+    which the built-in embedding does not have."""
+
+    def __init__(self, params, rt):
+        super().__init__(params, rt)
+        self.scale = float(params["scale"])
+        self.max_positions = int(params["max_positions"])
+        self.tokens = self.positions = None
+
+    def weight_specs(self):
+        return [WeightSpec("embed.weight", (self.params["vocab_size"], self.params["hidden_size"]), role="embedding"),
+                WeightSpec("positions.weight", (self.max_positions, self.params["hidden_size"]), role="embedding")]
+
+    def load(self, tensors):
+        self.tokens, self.positions = tensors["embed.weight"], tensors["positions.weight"]
+
+    def table(self):
+        return self.tokens
+
+    def forward(self, ctx, hidden):
+        hidden.copy_(self.scale * self.tokens[ctx.token_ids.long()].float()
+                     + self.positions[ctx.positions.long()].float())
 
 
 @dataclass(frozen=True)
@@ -152,7 +221,39 @@ def build_toy_spec(cfg: ToyConfig) -> ModelSpec:
                                                              "theta": 100.0, "max_positions": cfg.max_position_embeddings})})
 
 
+def build_latent_spec(cfg: ToyConfig) -> ModelSpec:
+    """A second toy: learned positions and a multiplier at the embedding, a latent-caching mixer,
+    the state mixer beside a routed feed-forward, and a tied head with a logit scale and a soft cap."""
+    norm = {"size": cfg.hidden_size, "eps": 1e-5}
+    ffn = PartSpec("swiglu", {"hidden_size": cfg.hidden_size, "intermediate_size": cfg.intermediate_size})
+    routed = PartSpec("toy_routed", {"hidden_size": cfg.hidden_size, "expert_size": cfg.expert_size,
+                                     "num_experts": cfg.num_experts, "top_k": 2})
+
+    def layer(i, mixer, feed_forward):
+        return LayerSpec(f"blocks.{i}", "pre_norm", mixer, feed_forward,
+                         PartSpec("rms_norm", {**norm, "name": "norm1.weight"}),
+                         PartSpec("rms_norm", {**norm, "name": "norm2.weight"}))
+
+    layers = (layer(0, PartSpec("toy_latent", {"hidden_size": cfg.hidden_size, "latent_size": 20}), ffn),
+              layer(1, PartSpec("toy_decay", {"hidden_size": cfg.hidden_size, "decay": cfg.decay}), routed))
+    return ModelSpec("ToyLatentLM", cfg.hidden_size, cfg.vocab_size, cfg.max_position_embeddings,
+                     "embed.weight", layers, (0, 1), PartSpec("rms_norm", norm), "final_norm.weight", None,
+                     embedding=PartSpec("toy_positional", {"scale": 1.5, "max_positions": cfg.max_position_embeddings}),
+                     head=PartSpec("linear_head", {"name": None, "logit_scale": 0.5, "soft_cap": 3.0}))
+
+
+@dataclass(frozen=True)
+class ToyLatentConfig(ToyConfig):
+    @classmethod
+    def from_dict(cls, raw):
+        base = ToyConfig.from_dict(raw)
+        return cls(**{**base.__dict__, "architecture": "ToyLatentLM"})
+
+
 def register():
+    MIXERS.register("toy_latent", LatentMixer)
+    EMBEDDINGS.register("toy_positional", PositionalEmbedding)
+    ARCHITECTURES.add("ToyLatentLM", ToyLatentConfig, build_latent_spec)
     MIXERS.register("toy_decay", DecayMixer)
     FEED_FORWARDS.register("toy_routed", RoutedFeedForward)
     POSITION_ENCODINGS.register("toy_additive", AdditivePositions)
@@ -160,6 +261,9 @@ def register():
 
 
 def unregister():
+    MIXERS.unregister("toy_latent")
+    EMBEDDINGS.unregister("toy_positional")
+    ARCHITECTURES.unregister("ToyLatentLM")
     MIXERS.unregister("toy_decay")
     FEED_FORWARDS.unregister("toy_routed")
     POSITION_ENCODINGS.unregister("toy_additive")
@@ -223,3 +327,42 @@ def plain_logits(cfg: ToyConfig, w, tokens):
         x = pm.rms_norm(h, w[p + "norm2.weight"], 1e-5)
         h = h + (routed(x, p) if i == 1 else ffn(x, p))
     return pm.linear(pm.rms_norm(h, w["final_norm.weight"], 1e-5), w["head.weight"])
+
+
+def plain_logits_latent(cfg: ToyConfig, w, tokens):
+    """The second toy on a whole sequence in float64, written without the framework."""
+    from tests.plain import model as pm
+    w = {k: v.double() for k, v in w.items()}
+    t_len = len(tokens)
+    h = 1.5 * w["embed.weight"][torch.tensor(tokens)] + w["positions.weight"][:t_len]
+    # layer 0: the latent mixer
+    x = pm.rms_norm(h, w["blocks.0.norm1.weight"], 1e-5)
+    c = x @ w["blocks.0.down.weight"].t()
+    mixed = []
+    for t in range(t_len):
+        probs = torch.softmax(c[:t + 1] @ c[t] / 20 ** 0.5, dim=0)
+        mixed.append(probs @ c[:t + 1])
+    h = h + torch.stack(mixed) @ w["blocks.0.up.weight"].t()
+    x = pm.rms_norm(h, w["blocks.0.norm2.weight"], 1e-5)
+    h = h + pm.linear(pm.swiglu(pm.linear(x, w["blocks.0.gate_proj.weight"]), pm.linear(x, w["blocks.0.up_proj.weight"])),
+                      w["blocks.0.down_proj.weight"])
+    # layer 1: the state mixer and the routed feed-forward
+    x = pm.rms_norm(h, w["blocks.1.norm1.weight"], 1e-5)
+    state = torch.zeros(cfg.hidden_size, dtype=torch.float64)
+    rows = []
+    for t in range(t_len):
+        state = cfg.decay * state + (1 - cfg.decay) * x[t]
+        rows.append(state)
+    h = h + torch.stack(rows) @ w["blocks.1.mix.weight"].t()
+    x = pm.rms_norm(h, w["blocks.1.norm2.weight"], 1e-5)
+    logits = x @ w["blocks.1.router.weight"].t()
+    out = torch.zeros_like(x)
+    for t in range(t_len):
+        top, chosen = logits[t].topk(3)
+        lead = top[:2] - top[2]
+        share = lead / (lead.sum() + 1e-6)
+        for sh, e in zip(share, chosen[:2].tolist()):
+            out[t] += sh * (w[f"blocks.1.experts.{e}.out.weight"] @ torch.relu(w[f"blocks.1.experts.{e}.in.weight"] @ x[t]))
+    h = h + out
+    raw = pm.linear(pm.rms_norm(h, w["final_norm.weight"], 1e-5), w["embed.weight"]) * 0.5
+    return 3.0 * torch.tanh(raw / 3.0)
