@@ -182,7 +182,13 @@ class DecodeGraph:
         cur = torch.cuda.current_stream(self.engine.device)
         self.stream.wait_stream(cur)
         with torch.cuda.stream(self.stream):
+            # The eager step really runs.  What it writes into pages and into the step's own
+            # buffers is written again by the first replayed step, but fixed-size state would
+            # be advanced by a token for good: keep it and put it back.
+            kept = {pos: state.clone() for pos, state in self.engine._run_state.items()}
             self._one_step()
+            for pos, state in kept.items():
+                self.engine._run_state[pos].copy_(state)
             self.stream.synchronize()
             before = self.engine.ops.launches
             self.graph = self.graphs[bucket] = torch.cuda.CUDAGraph()
