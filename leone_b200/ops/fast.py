@@ -364,7 +364,7 @@ class FastKernels:
         kp, vp = cache.k_pool, cache.v_pool
         # head sizes 64 and 128 run on tcgen05; the others on the mma.sync kernel
         tc = self.use_tc_attention and d in (64, 128) and g <= 128 and out.stride(0) % 8 == 0
-        entry = self.lib.leone_attention_prefill_tc if tc else self.lib.leone_attention_prefill
+        entry = self.lib.leone_attention_prefill_pingpong if tc else self.lib.leone_attention_prefill
         code = entry(_ptr(qkv), qkv.stride(0), _ptr(out), out.stride(0), _ptr(kp), _ptr(vp), _ptr(bt),
                      bt.stride(0), _ptr(q_start), _ptr(ctx_len), n_seqs, max_q_len, n_q, n_kv, d,
                      c_float(scale), int(window or 0), cache.page_tokens, kp.shape[0], _ptr(status),

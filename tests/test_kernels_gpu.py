@@ -724,12 +724,25 @@ def test_attention_prefill_tensor_memory_kernel_long(ops16, n_q, n_kv, d, pt, wi
     windows that end inside a tile; and the mma.sync kernel on the same batch."""
     assert ops16.fast.use_tc_attention
     kw = dict(seq_lens=[700, 517, 130], starts=[0, 300, 127], seed=8)
-    _tiled_case(ops16, n_q, n_kv, d, pt, window, **kw)
+    _tiled_case(ops16, n_q, n_kv, d, pt, window, **kw)        # tcgen05: two query tiles per block, P in tensor memory
     ops16.fast.use_tc_attention = False
     try:
-        _tiled_case(ops16, n_q, n_kv, d, pt, window, **kw)
+        _tiled_case(ops16, n_q, n_kv, d, pt, window, **kw)    # mma.sync
     finally:
         ops16.fast.use_tc_attention = True
+
+
+@pytest.mark.parametrize("n_q,n_kv,d,pt,window", [(32, 8, 128, 16, None), (6, 2, 64, 8, 70), (5, 1, 128, 16, None)])
+def test_attention_prefill_pingpong_short_and_uneven_portions(ops16, n_q, n_kv, d, pt, window):
+    """The kernel with two query tiles per block on portions that fill less than one query tile,
+    exactly one, one and a bit (the second tile nearly empty), and on a portion whose two query
+    tiles read different numbers of key tiles."""
+    assert ops16.fast.use_tc_attention
+    g = n_q // n_kv
+    tq = 128 // g
+    _tiled_case(ops16, n_q, n_kv, d, pt, window, seq_lens=[2, tq, tq + 1, 2 * tq, 3 * tq + 5, 128 + tq + 3],
+                starts=[0, 0, 0, 0, 0, 128 - tq + 1], seed=11)
+    _tiled_case(ops16, n_q, n_kv, d, pt, window, seq_lens=[1500], starts=[0], seed=12)
 
 
 @pytest.mark.parametrize("n_q,n_kv,d,pt,window", [(5, 1, 48, 16, None), (6, 3, 32, 8, None),
