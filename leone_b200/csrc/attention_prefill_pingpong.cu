@@ -318,23 +318,6 @@ attention_prefill_pingpong_kernel(const __nv_bfloat16* __restrict__ qkv, int row
     } else if (warp >= kLoadWarp0) {
       // ---------------- the warps that gather the tiles ----------------
       const int lt = tid - kLoadWarp0 * 32;              // 0..127
-      // both query tiles: row r of tile j = (token lo_j + r / g, head r % g)
-      for (int idx = lt; idx < 2 * kRows * kChunks; idx += kLoadThreads) {
-        const int j = idx / (kRows * kChunks), rem = idx - j * (kRows * kChunks);
-        const int r = rem / kChunks, ch = rem - r * kChunks;
-        const int tl = r / g, hh = r - tl * g;
-        const int token = tok0 + j * tq + tl;
-        const bool ok = tl < tq && token < q_len;
-        const __nv_bfloat16* src =
-            qkv + (size_t)(q0 + (ok ? token : 0)) * row_stride + (size_t)(kvh * g + hh) * D + ch * 8;
-        cp_async16(q_t + j * kTileBytes + swizzled(r, ch), src, ok);
-      }
-      cp_async_commit();
-      cp_async_wait<0>();
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_q);
-
       const bool values = lt >= kStreamThreads;
       const int st = lt & (kStreamThreads - 1);
       const __nv_bfloat16* pool = values ? pa.v_pool : pa.k_pool;
@@ -361,12 +344,26 @@ attention_prefill_pingpong_kernel(const __nv_bfloat16* __restrict__ qkv, int row
         else if (page >= 0) src = (((long long)page * pa.n_kv + kvh) * pa.page_tokens + (kj % pa.page_tokens)) * D;
         return src;
       };
+      // the first tile's page numbers are on their way while the query tiles are requested
+      int page_a = page_of(0, st), page_b = page_of(0, st + kStreamThreads);
+      // both query tiles: row r of tile j = (token lo_j + r / g, head r % g).  Their copies are
+      // not waited for here: they land with the first key and value tiles.
+      for (int idx = lt; idx < 2 * kRows * kChunks; idx += kLoadThreads) {
+        const int j = idx / (kRows * kChunks), rem = idx - j * (kRows * kChunks);
+        const int r = rem / kChunks, ch = rem - r * kChunks;
+        const int tl = r / g, hh = r - tl * g;
+        const int token = tok0 + j * tq + tl;
+        const bool ok = tl < tq && token < q_len;
+        const __nv_bfloat16* src =
+            qkv + (size_t)(q0 + (ok ? token : 0)) * row_stride + (size_t)(kvh * g + hh) * D + ch * 8;
+        cp_async16(q_t + j * kTileBytes + swizzled(r, ch), src, ok);
+      }
+      cp_async_commit();
       // a thread copies two neighbouring chunks (one 32-byte sector) of rows r0, r0 + step, ..
       constexpr int kPairs = kChunks / 2;
       constexpr int kStep = kStreamThreads / kPairs;     // 8 rows for D = 128, 16 for D = 64: the swizzle phase stays
       const int ch0 = (st % kPairs) * 2, r0 = st / kPairs;
       bool ok_all = true;
-      int page_a = page_of(0, st), page_b = page_of(0, st + kStreamThreads);
       // A tile is announced as soon as it has landed; only then does the thread turn to the next
       // tile, whose buffer it may have to wait for.
       for (int t = 0; t < n_tiles; ++t) {
@@ -392,6 +389,7 @@ attention_prefill_pingpong_kernel(const __nv_bfloat16* __restrict__ qkv, int row
         cp_async_wait<0>();
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
+        if (lane == 0 && t == 0) mbar_arrive(bar_q);     // this warp's share of the query tiles landed before
         if (lane == 0) mbar_arrive(bar_full + 8 * (t & 1));
       }
     } else {
