@@ -48,7 +48,7 @@ class DecodeGraph:
         self.history_host = torch.zeros((max_quantum, batch), dtype=torch.int32, pin_memory=True)
         self.counter = torch.zeros(1, dtype=torch.int32, device=dev)
         self.status_host = torch.zeros(4, dtype=torch.int32, pin_memory=True)
-        self.logits = torch.empty((batch, engine.spec.vocab_size), dtype=torch.float32, device=dev)
+        self.logits = engine.decode_logits_buffer()[:batch]      # one buffer for every batch size
         self.ctx = self._context()
         self.graphs = {}                   # context bucket -> captured step
         self.graph = None                  # the selected bucket's

@@ -166,7 +166,11 @@ class Engine:
         self.steps_run = 0
         self._sampler = None
         self._decode_graphs = {}
-        self.max_decode_graphs = 8          # batch sizes whose captured decode steps are kept
+        # batch sizes whose captured decode steps are kept (a scheduler whose requests finish one
+        # by one passes through every size, and a capture costs far more than a step); what a
+        # size holds is small, because the logits buffer is shared
+        self.max_decode_graphs = max(64, max_requests)
+        self._decode_logits = None
         # a decode step launched before the step before it was read (see decode_steps)
         self._ahead = None
         self.lookahead = os.environ.get("LEONE_NO_LOOKAHEAD", "0") != "1"
@@ -415,11 +419,19 @@ class Engine:
         self.steps_run += 1
         return graph.logits
 
+    def decode_logits_buffer(self) -> torch.Tensor:
+        """fp32 ``[max_requests, vocab]``: the logits of a captured decode step of any batch size
+        (its first ``batch`` rows), valid until the next decode step."""
+        if self._decode_logits is None:
+            self._decode_logits = torch.empty((self.max_requests, self.spec.vocab_size), dtype=torch.float32,
+                                              device=self.device)
+        return self._decode_logits
+
     def _decode_graph(self, rids, last_tokens, lengths, params, state, steps: int = 1):
         """The captured decode step for this batch size and for the context bucket that holds
         the longest sequence after ``steps`` more tokens, captured now if it is not yet.  One
-        set of buffers per batch size; the least recently used batch size is dropped beyond
-        ``max_decode_graphs`` of them."""
+        set of (small) buffers per batch size, one logits buffer for all; the least recently used
+        batch size is dropped beyond ``max_decode_graphs`` of them."""
         graph = self._decode_graphs.pop(len(rids), None)
         if graph is None:
             from .decode_graph import DecodeGraph
