@@ -47,6 +47,14 @@ template <int BN> struct GemmCfg {
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment*/ + 256 /*barriers*/;
 };
 
+// Decode-sized token tiles in cluster mode push their partial sums into the shared memory of the
+// block that finishes the rows (see the kernel): that block needs an inbox beside its stages, one
+// slot of [BN columns][32 rows] floats per (chunk it owns, rank): at most 8 slots.
+template <int BN, bool kSwap, bool kCluster> constexpr bool gemm_pushes() { return kCluster && kSwap && BN <= 16; }
+template <int BN, bool kSwap, bool kCluster> constexpr int gemm_smem_bytes() {
+  return GemmCfg<BN>::kSmemBytes + (gemm_pushes<BN, kSwap, kCluster>() ? 8 * BN * 32 * 4 : 0);
+}
+
 struct GemmParams {
   void* out;
   const float* residual;
@@ -252,6 +260,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   // barriers: full[kStages], empty[kStages], acc_full[2], acc_empty[2]
   const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * kStages;
   const uint32_t acc_full0 = empty0 + 8 * kStages, acc_empty0 = acc_full0 + 16;
+  constexpr bool kPush = gemm_pushes<BN, kSwap, kCluster>();
+  // the inbox of pushed partial sums: [slot][column][row of the chunk] floats, behind the barriers
+  float* inbox = reinterpret_cast<float*>(aligned + kStages * Cfg::kStageBytes + 256);
   __shared__ uint32_t tmem_holder;
   __shared__ int gave_up;
   __shared__ int last_flag;
@@ -290,6 +301,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   volatile int* giveup = &gave_up;
   pdl_trigger();
   if (threadIdx.x == 0) stamp(p, 0);                       // set-up done
+  // pushing blocks write into their cluster peers' shared memory before any full barrier: this
+  // arrival (waited for just before the first such write) says that this block is running
+  if constexpr (kPush) cluster_arrive_relaxed();
+  bool started_seen = false;                               // this thread has waited for that arrival
 
   if (warp == 0) {
     // ---------------- producer ----------------
@@ -419,7 +434,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       if (ep_tid == 0) stamp(p, 5);                        // accumulator of the (latest) unit complete
       const int row_local = quarter * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
-      if constexpr (kCluster) {
+      if constexpr (kPush) {
+        // this thread's row of the partial tile goes straight into the inbox of the block that
+        // finishes the row's chunk (chunk = this warp's quarter of the rows; owner = chunk %
+        // splits), slot (chunk / splits, this block's rank): one remote store per column, 32
+        // lanes side by side.  After the one cluster barrier below nothing remote is touched
+        // again, so no second barrier is needed and a finished block just leaves.
+        const uint32_t my_rank = cluster_ctarank();
+        const uint32_t owner = (uint32_t)quarter % (uint32_t)nsplit;
+        const uint32_t slot = smem_u32(inbox) + ((((quarter / nsplit) * nsplit + my_rank) * BN) * 32 + lane) * 4;
+        const uint32_t dst = cluster_map(slot, owner);
+        cluster_wait();                                  // every block of the cluster is running
+        started_seen = true;
+        for (int c = 0; c < BN; c += 16) {
+          float v[16];
+          tmem_ld16(taddr + c, v);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) cluster_st_f32(dst + (c + j) * 32 * 4, v[j]);
+        }
+        break;                                           // one unit per block in this mode
+      } else if constexpr (kCluster) {
         // this block's partial tile goes to its own shared memory, [accumulator column][row];
         // the stages are free: the accumulator is complete, so every MMA has read its operands
         static_assert(kStages * Cfg::kStageBytes >= BN * kTileW * 4, "partial tile must fit in the stages");
@@ -672,7 +706,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // block of rank ch % splits, so the sums and the epilogue are spread over the cluster.
     // In a chunk, lane = row and each epilogue warp owns a quarter of the token columns.
     __syncwarp();
+    if constexpr (kPush) {
+      if (!started_seen) cluster_wait();                 // pairs the arrival at the block's start
+    }
     cluster_sync_all();                                  // all partial tiles are in place
+    if constexpr (kPush) {
+      // The chunks this block owns lie in its own inbox, one slot per rank: sum them in rank
+      // order and finish.  Lane = row of the chunk; each epilogue warp owns a quarter of the
+      // token columns.
+      if (warp >= 2 && blockIdx.x < total) {
+        const Unit un = unit_of(blockIdx.x, p);
+        const int m_tile = un.tile % m_tiles, n_tile = un.tile / m_tiles;
+        const int m0 = m_tile * BN;
+        constexpr int NC = BN / 4;
+        const int rank = (int)cluster_ctarank();
+        for (int ch = rank; ch < kTileW / 32; ch += un.nsplit) {
+          const int n = n_tile * kTileW + ch * 32 + lane;
+          const float* mine = inbox + (size_t)((ch / un.nsplit) * un.nsplit) * BN * 32 + lane;
+          const int c = (warp & 3) * NC;
+          float v[NC], r[NC];
+          fetch_residual<NC>(p, r, n, m0, c);
+#pragma unroll
+          for (int j = 0; j < NC; ++j) v[j] = 0.f;
+          for (int s0 = 0; s0 < un.nsplit; ++s0) {       // rank order
+#pragma unroll
+            for (int j = 0; j < NC; ++j) v[j] += mine[((size_t)s0 * BN + c + j) * 32];
+          }
+          finish_swapped<NC>(p, v, r, n, m0, c, lane, rs_s);
+        }
+      }
+    } else
     if constexpr (!kSwap) {
       // token-major: the rows are tokens; in a chunk lane = token row, and each epilogue warp
       // owns a quarter of the tile's weight rows, 32 at a time (a gate/up group for SwiGLU)
@@ -754,7 +817,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
     }
     __syncwarp();
-    cluster_sync_all();                                  // the partial tiles may go away
+    if constexpr (!kPush) cluster_sync_all();            // the partial tiles may go away
   }
 
   // ---------------- teardown ----------------
@@ -781,7 +844,8 @@ int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& 
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, kSwap, kCluster>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         gemm_smem_bytes<BN, kSwap, kCluster>());
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
@@ -793,10 +857,10 @@ int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& 
   if constexpr (kCluster) {
     if (total > slots) return kRefusedSize;              // one unit per block, one round
     return launch_kernel_cluster(gemm_tc_kernel<BN, kSwap, true>, dim3((unsigned)total), dim3(kGemmThreads),
-                                 Cfg::kSmemBytes, stream, dim3(p.splits), mw, mx, p);
+                                 gemm_smem_bytes<BN, kSwap, true>(), stream, dim3(p.splits), mw, mx, p);
   }
-  return launch_kernel(gemm_tc_kernel<BN, kSwap, kCluster>, dim3(grid), dim3(kGemmThreads), Cfg::kSmemBytes,
-                       stream, mw, mx, p);
+  return launch_kernel(gemm_tc_kernel<BN, kSwap, kCluster>, dim3(grid), dim3(kGemmThreads),
+                       gemm_smem_bytes<BN, kSwap, kCluster>(), stream, mw, mx, p);
 }
 
 // How many clusters of `splits` blocks of the swapped kernel for token tile BN can be resident
@@ -805,12 +869,13 @@ template <int BN, bool kSwap = true>
 int cluster_capacity(int splits) {
   using Cfg = GemmCfg<BN>;
   cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, kSwap, true>,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       gemm_smem_bytes<BN, kSwap, true>());
   if (e != cudaSuccess) { cudaGetLastError(); return 0; }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(splits * 64);
   cfg.blockDim = dim3(kGemmThreads);
-  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.dynamicSmemBytes = gemm_smem_bytes<BN, kSwap, true>();
   cudaLaunchAttribute attr;
   attr.id = cudaLaunchAttributeClusterDimension;
   attr.val.clusterDim.x = splits;
