@@ -5,6 +5,8 @@
 
 Prints one JSON line.  ``--gpus N`` with N > 1 prints one line saying that this engine runs
 on one GPU and exits with 2.  ``--impl reference`` prints why the reference cannot run here.
+``--shape qwen3-32b | qwen3-1.7b``, ``--batch``, ``--context`` measure the other baseline
+configurations; ``--workload serving`` runs many requests through the scheduler.
 """
 import argparse
 import os
@@ -25,15 +27,21 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=None, help="decode context (default: the shape's)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
-    ap.add_argument("--shape", default="qwen3-8b", choices=["qwen3-8b", "qwen3-1.7b", "qwen3-32b"],
-                    help="layer sizes (default: the headline Qwen3-8B shape)")
+    ap.add_argument("--shape", default=None, choices=["qwen3-8b", "qwen3-1.7b", "qwen3-32b"],
+                    help="layer sizes (default: the headline Qwen3-8B shape; for --workload serving the 1.7B shape)")
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving"],
+                    help="serving: many requests with mixed prompt lengths through the scheduler (its own JSON line)")
+    ap.add_argument("--requests", type=int, default=64, help="serving: concurrent requests")
     args = ap.parse_args()
     if args.impl != "reference" and args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.workload == "serving" and args.impl != "reference":
+        from leone_b200.benchmark import serving
+        return serving(args.shape or "qwen3-1.7b", requests=args.requests, layers=args.layers)
     from leone_b200.benchmark import run
     return run(args.gpus, args.steps, max(args.warmup, 3), args.impl, layers=args.layers,
-               batch=args.batch, context=args.context, points=not args.no_points, shape=args.shape)
+               batch=args.batch, context=args.context, points=not args.no_points, shape=args.shape or "qwen3-8b")
 
 
 if __name__ == "__main__":

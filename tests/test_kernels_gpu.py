@@ -757,6 +757,15 @@ def test_attention_decode_tiled(ops16, n_q, n_kv, d, pt, window, seq_lens, clust
     _tiled_case(ops16, n_q, n_kv, d, pt, window, seq_lens=seq_lens, starts=[l - 1 for l in seq_lens], seed=4)
 
 
+@pytest.mark.parametrize("seq_lens", [[9000, 130], [33000], [17000, 16999, 5, 4097]])
+def test_attention_decode_long_contexts(ops16, seq_lens):
+    """Contexts of tens of thousands of tokens (more splits than a cluster holds, the merge
+    kernel, block tables thousands of entries wide), at the 8B head shape; a far key dominates
+    the first head of every sequence, so a lost split shows."""
+    _tiled_case(ops16, 32, 8, 128, 16, None, seq_lens=seq_lens, starts=[l - 1 for l in seq_lens], seed=21)
+    _tiled_case(ops16, 6, 2, 64, 16, 4500, seq_lens=seq_lens, starts=[l - 1 for l in seq_lens], seed=22)
+
+
 @pytest.mark.parametrize("n_q,n_kv,d,pt,window,qk_norm,rotary", [
     (8, 2, 128, 16, None, True, True), (6, 3, 64, 8, None, True, True), (5, 1, 64, 16, 40, False, True),
     (40, 2, 128, 16, None, True, False), (4, 4, 128, 4, 300, True, True)])
