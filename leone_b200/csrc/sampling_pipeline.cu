@@ -72,13 +72,16 @@ __device__ __forceinline__ bool precedes(double ka, int ia, double kb, int ib) {
 }
 
 // ---- sort ----------------------------------------------------------------------------------
-__global__ void sort_init_logits_kernel(const float* __restrict__ logits, int vocab, int P, uint8_t* scratch) {
+// row_map (or null): row r of this call works on row row_map[r] of `logits`.
+__global__ void sort_init_logits_kernel(const float* __restrict__ logits, const int* __restrict__ row_map,
+                                        int vocab, int P, uint8_t* scratch) {
   const int row = blockIdx.y;
   const Row r = row_of(scratch, row, P, vocab);
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i == 0) *r.n = 0;
   if (i >= P) return;
-  const float v = i < vocab ? logits[(size_t)row * vocab + i] : NAN;
+  const int src = row_map != nullptr ? row_map[row] : row;
+  const float v = i < vocab ? logits[(size_t)src * vocab + i] : NAN;
   const bool ok = i < vocab && isfinite(v);
   r.keys[i] = ok ? (double)v : -INFINITY;
   r.order[i] = ok ? i : vocab + i;            // the excluded ones sort last, in a fixed order
@@ -511,10 +514,11 @@ __device__ __forceinline__ unsigned long long splitmix64(unsigned long long v) {
 // the last id with any probability.
 __global__ void __launch_bounds__(kThreads)
 select_kernel(int vocab, int P, uint8_t* scratch, const long long* __restrict__ seeds,
-              const long long* __restrict__ positions, int* __restrict__ out, double* __restrict__ probs,
-              double* __restrict__ chosen_prob) {
+              const long long* __restrict__ positions, int* __restrict__ out, const int* __restrict__ row_map,
+              double* __restrict__ probs, double* __restrict__ chosen_prob) {
   __shared__ Shared sh;
   const int row = blockIdx.x;
+  const int dst = row_map != nullptr ? row_map[row] : row;      // where the row's id goes
   const Row r = row_of(scratch, row, P, vocab);
   const int n = *r.n;
   for (int i = threadIdx.x; i < vocab; i += kThreads) r.dense[i] = 0.0;
@@ -524,7 +528,7 @@ select_kernel(int vocab, int P, uint8_t* scratch, const long long* __restrict__ 
   if (probs != nullptr)
     for (int i = threadIdx.x; i < vocab; i += kThreads) probs[(size_t)row * vocab + i] = r.dense[i];
   if (n <= 0) {
-    if (threadIdx.x == 0) out[row] = -1;
+    if (threadIdx.x == 0) out[dst] = -1;
     return;
   }
   const unsigned long long purpose = 0xbf58476d1ce4e5b9ull;
@@ -538,7 +542,7 @@ select_kernel(int vocab, int P, uint8_t* scratch, const long long* __restrict__ 
     if (dense[i] > 0.0) last = i;
   last = -block_min(-last, sh);
   const int token = at == INT_MAX ? last : at;     // a zero entry cannot make the sum pass u
-  if (threadIdx.x == 0) out[row] = token;
+  if (threadIdx.x == 0) out[dst] = token;
   if (chosen_prob != nullptr)                      // the token's probability before the surprise filter
     for (int i = threadIdx.x; i < n; i += kThreads)
       if (r.order[i] == token) chosen_prob[row] = r.aux_f[i];
@@ -592,14 +596,16 @@ extern "C" long long leone_sample_truncated_scratch(int rows, int vocab) {
 
 // logits: fp32 [rows, vocab]; temperature: fp64 [rows] (> 0); seeds, positions: int64 [rows];
 // the stage list (types and values, in the order they apply) is the same for all rows; out: int32
-// [rows] sampled ids; probs: fp64 [rows, vocab] or null, the distribution the draw was made from.
+// sampled ids; probs: fp64 [rows, vocab] or null, the distribution the draw was made from.
+// row_map: int32 [rows] or null: row r of the call reads logits row row_map[r] and writes
+// out[row_map[r]] (a subset of a step's rows is sampled in place, without gathering it first).
 // maximum_surprise: fp64 [rows] or null: Mirostat v2's filter after the stages; chosen_prob (fp64
 // [rows], with it) gets the drawn token's probability before that filter.
 extern "C" int leone_sample_truncated(const float* logits, int rows, int vocab, const double* temperature,
                                       const long long* seeds, const long long* positions, int n_stages,
                                       const int* types, const double* values, void* scratch, int* out,
                                       double* probs, const double* maximum_surprise, double* chosen_prob,
-                                      cudaStream_t stream) {
+                                      const int* row_map, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (vocab <= 0 || n_stages < 0 || n_stages > kMaxStages) return kRefusedSize;
   Stages st;
@@ -611,7 +617,7 @@ extern "C" int leone_sample_truncated(const float* logits, int rows, int vocab, 
   }
   const int P = pow2_at_least(vocab);
   uint8_t* sc = static_cast<uint8_t*>(scratch);
-  sort_init_logits_kernel<<<dim3((P + 255) / 256, rows), 256, 0, stream>>>(logits, vocab, P, sc);
+  sort_init_logits_kernel<<<dim3((P + 255) / 256, rows), 256, 0, stream>>>(logits, row_map, vocab, P, sc);
   // A pipeline that starts with a small top-k and has no raw-logit stage needs only the row's k
   // best pairs, which are among the k best of every tile: the tiles are sorted in themselves,
   // their heads gathered and sorted, and the rest of the row is never ordered.
@@ -651,7 +657,7 @@ extern "C" int leone_sample_truncated(const float* logits, int rows, int vocab, 
     if (chosen_prob == nullptr) return kRefusedSize;
     surprise_filter_kernel<<<rows, kThreads, 0, stream>>>(vocab, P, sc, maximum_surprise);
   }
-  select_kernel<<<rows, kThreads, 0, stream>>>(vocab, P, sc, seeds, positions, out, probs,
+  select_kernel<<<rows, kThreads, 0, stream>>>(vocab, P, sc, seeds, positions, out, row_map, probs,
                                                maximum_surprise != nullptr ? chosen_prob : nullptr);
   return (int)cudaGetLastError();
 }

@@ -342,7 +342,10 @@ class Engine:
         if self._sampler is None:
             from ..sampling.sampler import Sampler
             self._sampler = Sampler(self.ops, self.device)
-        return self._sampler.sample(logits, params, positions, histories, states).tolist()
+        ids = self._sampler.sample(logits, params, positions, histories, states).tolist()
+        if any(t < 0 for t in ids):
+            raise ValueError("every logit of a row is non-finite, so no token can be sampled")
+        return ids
 
     # -- decode quanta ------------------------------------------------------------------
     def decode_steps(self, rids: Sequence[Hashable], last_tokens: Sequence[int], params,

@@ -385,19 +385,25 @@ class CudaOps:
                                         _ptr(per_row[2]), self._stream()), "penalize")
 
     def sample_truncated(self, logits, temperatures, seeds, positions, stages, want_probs: bool = False,
-                         maximum_surprise=None):
+                         maximum_surprise=None, rows=None, out=None):
         """Rows that sample through truncation stages: ``stages`` is a list of (stage number,
-        value) applied in order to every row (``csrc/sampling_pipeline.cu``).  Returns the ids
-        as an int32 device tensor (and the fp64 distribution the draw was made from).
-        ``maximum_surprise`` (one per row): Mirostat's filter after the stages; the drawn tokens'
-        probabilities before that filter are returned too (fp64 device tensor)."""
+        value) applied in order to every row (``csrc/sampling_pipeline.cu``).  ``rows``: which
+        rows of ``logits`` take part (default: all); their ids are written to ``out`` at the same
+        row numbers (``out``: int32 device tensor with a place per logits row; default: a new
+        one).  Returns ``out`` (and the fp64 distribution the draws were made from, one row per
+        participating row).  ``maximum_surprise`` (one per participating row): Mirostat's filter
+        after the stages; the drawn tokens' probabilities before that filter are returned too
+        (fp64 device tensor).  A row whose logits are all non-finite gets the id -1."""
         import ctypes
-        rows, vocab = logits.shape
+        n_rows, vocab = logits.shape
+        members = list(range(n_rows)) if rows is None else [int(r) for r in rows]
+        count = len(members)
         _need(logits.dtype == torch.float32 and logits.is_contiguous(), "logits must be fp32")
-        _need(rows == len(temperatures) == len(seeds) == len(positions), "one temperature, seed and position a row")
+        _need(count == len(temperatures) == len(seeds) == len(positions), "one temperature, seed and position a row")
+        _need(all(0 <= r < n_rows for r in members) and len(set(members)) == count, "rows must be distinct rows of the logits")
         _need(all(t > 0 for t in temperatures), "truncation stages need a temperature")
         self.core.leone_sample_truncated_scratch.restype = ctypes.c_longlong
-        need = int(self.core.leone_sample_truncated_scratch(rows, vocab))
+        need = int(self.core.leone_sample_truncated_scratch(count, vocab))
         if self._sample_scratch is None or self._sample_scratch.numel() < need:
             self._sample_scratch = torch.empty(need, dtype=torch.uint8, device=self.device)
         dev = self.device
@@ -405,23 +411,24 @@ class CudaOps:
         sd = torch.tensor(np.array([s_ & 0xFFFF_FFFF_FFFF_FFFF for s_ in seeds], dtype=np.uint64).view(np.int64),
                           device=dev)
         pos = torch.tensor(positions, dtype=torch.int64, device=dev)
-        out = torch.empty(rows, dtype=torch.int32, device=dev)
-        probs = torch.empty((rows, vocab), dtype=torch.float64, device=dev) if want_probs else None
+        row_map = None if rows is None else torch.tensor(members, dtype=torch.int32, device=dev)
+        if out is None:
+            out = torch.empty(n_rows, dtype=torch.int32, device=dev)
+        _need(out.dtype == torch.int32 and out.numel() >= n_rows and out.is_contiguous(), "out: int32, a place per logits row")
+        probs = torch.empty((count, vocab), dtype=torch.float64, device=dev) if want_probs else None
         mu = chosen = None
         if maximum_surprise is not None:
-            _need(len(maximum_surprise) == rows, "one maximum surprise a row")
+            _need(len(maximum_surprise) == count, "one maximum surprise a row")
             mu = torch.tensor([float(m) for m in maximum_surprise], dtype=torch.float64, device=dev)
-            chosen = torch.zeros(rows, dtype=torch.float64, device=dev)
+            chosen = torch.zeros(count, dtype=torch.float64, device=dev)
         n = len(stages)
         types = (ctypes.c_int * max(n, 1))(*[int(a) for a, _ in stages])
         values = (ctypes.c_double * max(n, 1))(*[float(b) for _, b in stages])
         self.launches += 1
-        _check(self.core.leone_sample_truncated(_ptr(logits), rows, vocab, _ptr(t), _ptr(sd), _ptr(pos), n,
+        _check(self.core.leone_sample_truncated(_ptr(logits), count, vocab, _ptr(t), _ptr(sd), _ptr(pos), n,
                                                 types, values, _ptr(self._sample_scratch), _ptr(out),
-                                                _ptr(probs), _ptr(mu), _ptr(chosen), self._stream()),
+                                                _ptr(probs), _ptr(mu), _ptr(chosen), _ptr(row_map), self._stream()),
                "sample_truncated")
-        if bool((out < 0).any()):
-            raise ValueError("every logit of a row is non-finite, so no token can be sampled")
         result = (out,) + ((probs,) if want_probs else ()) + ((chosen,) if mu is not None else ())
         return result if len(result) > 1 else out
 

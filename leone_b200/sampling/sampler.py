@@ -258,19 +258,17 @@ class Sampler:
             if p.temperature > 0 and (p.truncations or p.mirostat):
                 groups.setdefault((p.truncations, p.mirostat is not None), []).append(i)
         for (stages, surprise), members in groups.items():
-            index = torch.tensor(members, dtype=torch.int64, device=logits.device)
+            # the group's rows are sampled where they lie: the kernels read those rows of the
+            # logits and write their ids over what the plain kernel left there
             got = self.ops.sample_truncated(
-                logits.index_select(0, index), [float(params[i].temperature) for i in members],
+                logits, [float(params[i].temperature) for i in members],
                 [params[i].seed for i in members], [int(positions[i]) for i in members],
                 [(TRUNCATION_STAGES[n], v) for n, v in stages],
-                maximum_surprise=[states[i].maximum_surprise for i in members] if surprise else None)
+                maximum_surprise=[states[i].maximum_surprise for i in members] if surprise else None,
+                rows=members, out=out)
             if surprise:
-                picked, chosen = got
-                for i, p_ in zip(members, chosen.tolist()):
+                for i, p_ in zip(members, got[1].tolist()):
                     states[i].observe(params[i], p_)
-            else:
-                picked = got
-            out.index_copy_(0, index, picked)
         for i, p in enumerate(params):
             if p.mirostat and not p.temperature > 0:
                 states[i].observe(p, 1.0)       # greedy: the one token has probability one

@@ -139,17 +139,21 @@ class EmulatedOps:
             logits[row, token] = value
 
     def sample_truncated(self, logits, temperatures, seeds, positions, stages, want_probs=False,
-                         maximum_surprise=None):
+                         maximum_surprise=None, rows=None, out=None):
         from leone_b200.sampling.sampler import TRUNCATION_STAGES
         from tests.plain.model import mirostat_select, select, truncated_probs, uniform
         import math
         names = {v: k for k, v in TRUNCATION_STAGES.items()}
         named = [(names[t], v) for t, v in stages]
-        rows = [truncated_probs(logits[i].tolist(), temperatures[i], named) for i in range(logits.shape[0])]
+        members = list(range(logits.shape[0])) if rows is None else list(rows)
+        if out is None:
+            out = torch.zeros(logits.shape[0], dtype=torch.int32)
+        dists = [truncated_probs(logits[r].tolist(), temperatures[i], named) for i, r in enumerate(members)]
         if maximum_surprise is not None:
-            drawn = [mirostat_select(p, maximum_surprise[i], uniform(seeds[i], positions[i])) for i, p in enumerate(rows)]
-            return (torch.tensor([t for t, _ in drawn], dtype=torch.int32),
-                    torch.tensor([math.exp(-s_) for _, s_ in drawn], dtype=torch.float64))
-        out = torch.tensor([select(p, uniform(seeds[i], positions[i])) for i, p in enumerate(rows)],
-                           dtype=torch.int32)
-        return (out, torch.tensor(np.stack(rows))) if want_probs else out
+            drawn = [mirostat_select(p, maximum_surprise[i], uniform(seeds[i], positions[i])) for i, p in enumerate(dists)]
+            for r, (t, _) in zip(members, drawn):
+                out[r] = t
+            return out, torch.tensor([math.exp(-s_) for _, s_ in drawn], dtype=torch.float64)
+        for i, (r, p) in enumerate(zip(members, dists)):
+            out[r] = select(p, uniform(seeds[i], positions[i]))
+        return (out, torch.tensor(np.stack(dists))) if want_probs else out

@@ -864,6 +864,29 @@ def test_sample_truncated_matches_the_plain_sampler(ops32, vocab, stages):
         assert int(out[r]) == select(want, uniform(seeds[r], positions[r]))
 
 
+def test_sample_truncated_on_some_rows_in_place(ops32):
+    """A subset of a step's rows goes through the stages where it lies: the ids land at the rows'
+    own places, the other places keep what they held, and a row of non-finite logits gets -1."""
+    from leone_b200.sampling.sampler import TRUNCATION_STAGES
+    from tests.plain.model import select, truncated_probs, uniform
+    rows, vocab = 5, 777
+    logits = _randn((rows, vocab), 5150, scale=3.0)
+    logits[3] = float("nan")
+    stages = [("top_k", 50), ("top_p", 0.9)]
+    numbered = [(TRUNCATION_STAGES[n], v) for n, v in stages]
+    out = torch.full((rows,), 1234, dtype=torch.int32, device=DEV)
+    members, temps, seeds, positions = [4, 1, 3], [0.9, 1.2, 0.8], [5, 6, 7], [40, 41, 42]
+    got, probs = ops32.sample_truncated(logits, temps, seeds, positions, numbered, want_probs=True, rows=members, out=out)
+    assert got.data_ptr() == out.data_ptr() and probs.shape == (3, vocab)
+    host = logits.cpu().numpy()
+    want = out.tolist()
+    assert want[0] == 1234 and want[2] == 1234 and want[3] == -1
+    for i, r in enumerate(members[:2]):
+        dist = truncated_probs(host[r], temps[i], stages)
+        assert want[r] == select(dist, uniform(seeds[i], positions[i]))
+        assert np.abs(probs[i].cpu().numpy() - dist).max() < 1e-13
+
+
 def test_sample_truncated_full_vocabulary(ops32):
     """A row of 151,936 logits (the sort's global passes, the scans over long rows)."""
     from leone_b200.sampling.sampler import TRUNCATION_STAGES
