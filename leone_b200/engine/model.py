@@ -58,12 +58,25 @@ class Model:
         self.blocks = []
         self._holders: List[_Prefixed] = []
         for layer in spec.layers:
-            mixer = _build_mixer(layer.mixer, rt, self.position_encodings)
-            ffn = FEED_FORWARDS.get(layer.feed_forward.kind)(dict(layer.feed_forward.params), rt)
-            n1 = NORMS.get(layer.mixer_norm.kind)(dict(layer.mixer_norm.params), rt)
-            n2 = NORMS.get(layer.ffn_norm.kind)(dict(layer.ffn_norm.params), rt)
-            self.blocks.append(BLOCKS.get(layer.block)(mixer, ffn, n1, n2))
-            self._holders += [_Prefixed(layer.prefix, p) for p in (mixer, ffn, n1, n2)]
+            def build(registry, part_spec):
+                if part_spec is None:
+                    return None
+                if registry == "mixer":
+                    return _build_mixer(part_spec, rt, self.position_encodings)
+                table = {"feed_forward": FEED_FORWARDS, "norm": NORMS}.get(registry)
+                if table is None:
+                    raise ValueError(f"layer {layer.prefix}: no registry '{registry}' for an extra part")
+                return table.get(part_spec.kind)(dict(part_spec.params), rt)
+
+            mixer = build("mixer", layer.mixer)
+            ffn = build("feed_forward", layer.feed_forward)
+            n1, n2 = build("norm", layer.mixer_norm), build("norm", layer.ffn_norm)
+            extra = {name: build(registry, ps) for name, (registry, ps) in layer.extra.items()}
+            block = BLOCKS.get(layer.block)(mixer, ffn, n1, n2, **extra)
+            block.extra_parts = extra
+            self.blocks.append(block)
+            self._holders += [_Prefixed(layer.prefix, p) for p in (mixer, ffn, n1, n2, *extra.values())
+                              if p is not None]
         self.final_norm = NORMS.get(spec.final_norm.kind)(
             {**spec.final_norm.params, "name": spec.final_norm_name}, rt)
         es, hs = spec.embedding_spec(), spec.head_spec()
@@ -125,8 +138,8 @@ class Model:
         total = 0
         for idx in self.spec.run_order:
             block = self.blocks[idx]
-            for part in (block.mixer, block.feed_forward):
-                if hasattr(part, "weight_bytes"):
+            for part in (block.mixer, block.feed_forward, *getattr(block, "extra_parts", {}).values()):
+                if part is not None and hasattr(part, "weight_bytes"):
                     total += part.weight_bytes()
         total += self.head.weight_bytes()
         return total
@@ -137,7 +150,9 @@ class Model:
         layer's buffers (layers share them by name), and fp32 logits for ``max_logit_rows`` rows."""
         item = self.rt.dtype.itemsize
         total = max_tokens * self.hidden_size * (4 + 3 * item)
-        per_layer = [sum(p.scratch_bytes(max_tokens) for p in (b.mixer, b.feed_forward, b.mixer_norm, b.ffn_norm))
+        per_layer = [sum(p.scratch_bytes(max_tokens)
+                         for p in (b.mixer, b.feed_forward, b.mixer_norm, b.ffn_norm,
+                                   *getattr(b, "extra_parts", {}).values()) if p is not None)
                      for b in self.blocks]
         total += max(per_layer, default=0)
         total += max_logit_rows * (self.vocab_size * 4 + self.hidden_size * item)

@@ -303,11 +303,17 @@ class Head(Part):
 
 
 class Block:
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, ffn_norm: Norm):
+    """``feed_forward`` and either norm are ``None`` where the layer's spec has none; further
+    named parts of the layer (``LayerSpec.extra``) arrive as keyword arguments."""
+
+    def __init__(self, mixer: Mixer, feed_forward: Optional[FeedForward], mixer_norm: Optional[Norm],
+                 ffn_norm: Optional[Norm], **extra):
         self.mixer = mixer
         self.feed_forward = feed_forward
         self.mixer_norm = mixer_norm
         self.ffn_norm = ffn_norm
+        for name, part in extra.items():
+            setattr(self, name, part)
 
     def forward(self, ctx, cache, hidden):
         raise NotImplementedError

@@ -11,6 +11,11 @@ class PreNormBlock(Block):
 
     chains_norms = True       # forward takes pre= and after= (see below)
 
+    def __init__(self, mixer, feed_forward, mixer_norm, ffn_norm, **extra):
+        if feed_forward is None or mixer_norm is None or ffn_norm is None or extra:
+            raise ValueError("the pre_norm arrangement is norm, mixer, norm, feed-forward: it takes exactly those parts")
+        super().__init__(mixer, feed_forward, mixer_norm, ffn_norm)
+
     def entry_norm(self, ctx, hidden):
         """The norm before the mixer as a DeferredNorm for the block before this one to fill,
         or None if it has to run as a kernel."""

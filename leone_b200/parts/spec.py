@@ -25,7 +25,11 @@ class PartSpec:
 class LayerSpec:
     """One layer: a block arrangement of a mixer, a feed-forward and their norms.
 
-    ``prefix`` is the layer's tensor-name prefix in the checkpoint.
+    ``prefix`` is the layer's tensor-name prefix in the checkpoint.  The feed-forward and either
+    norm may be ``None`` for an arrangement that has none (the block then gets ``None`` in its
+    place); ``extra`` holds further named parts of the arrangement, each as ``(registry, spec)``
+    with ``registry`` one of ``"mixer"``, ``"feed_forward"``, ``"norm"`` (a second norm after the
+    mixer, a parallel branch), given to the block as keyword arguments.
     ``cache_of`` names another layer whose cache this layer's mixer reads
     instead of owning one (it then writes nothing).  A layer named twice in the
     run order shares its weights between the runs; each run owns its own cache.
@@ -33,10 +37,11 @@ class LayerSpec:
     prefix: str
     block: str
     mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    ffn_norm: PartSpec
+    feed_forward: Optional[PartSpec] = None
+    mixer_norm: Optional[PartSpec] = None
+    ffn_norm: Optional[PartSpec] = None
     cache_of: Optional[int] = None
+    extra: Dict[str, Tuple[str, PartSpec]] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)

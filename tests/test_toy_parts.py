@@ -133,7 +133,7 @@ def _check_latent(cfg, spec, tensors, device, ops, dtype, tol):
         k_pool, v_pool = eng.pools[0]
         assert (group.spec.kind, group.spec.tag) == ("full", "latent") and v_pool is None
         assert k_pool.dtype == torch.float32 and tuple(k_pool.shape) == (1, eng.num_pages, 1, 8, 20)
-        assert eng.memory_plan["cache"] == k_pool.numel() * 4 and eng.memory_plan["state"] == 3 * 48 * 4
+        assert eng.memory_plan["cache"] == k_pool.numel() * 4 and eng.memory_plan["state"] == 2 * 3 * 48 * 4
         out = replay.run_trace_engine(eng, steps)
         replay.compare(steps, out, Plain(), reqs, what=f"latent toy {name} {dtype}", **tol)
         assert eng.cache.free_pages() == [eng.num_pages]

@@ -7,10 +7,10 @@ from dataclasses import dataclass
 import torch
 
 from leone_b200.config.base import ConfigReader, ModelConfig
-from leone_b200.parts.base import (Embedding, FeedForward, FixedState, Mixer, PagedKV, PositionEncoding,
+from leone_b200.parts.base import (Block, Embedding, FeedForward, FixedState, Mixer, PagedKV, PositionEncoding,
                                    WeightSpec)
 from leone_b200.parts.spec import LayerSpec, ModelSpec, PartSpec
-from leone_b200.registry import ARCHITECTURES, EMBEDDINGS, FEED_FORWARDS, MIXERS, POSITION_ENCODINGS
+from leone_b200.registry import ARCHITECTURES, BLOCKS, EMBEDDINGS, FEED_FORWARDS, MIXERS, POSITION_ENCODINGS
 
 
 class DecayMixer(Mixer):
@@ -146,6 +146,22 @@ class LatentMixer(Mixer):
         hidden += mixed @ self.w["up.weight"].float().t()
 
 
+class ParallelPostNormBlock(Block):
+    """``h <- post_norm(h + mixer(norm(h)) + branch(norm(h)))``: one norm feeds the mixer and a
+    feed-forward branch beside it, a second norm comes after the sum, and the usual feed-forward
+    and its norm are not there at all."""
+
+    def __init__(self, mixer, feed_forward, mixer_norm, ffn_norm, branch=None, post_norm=None):
+        assert feed_forward is None and ffn_norm is None and branch is not None and post_norm is not None
+        super().__init__(mixer, None, mixer_norm, None, branch=branch, post_norm=post_norm)
+
+    def forward(self, ctx, cache, hidden):
+        x = self.mixer_norm.forward(ctx, hidden)
+        self.mixer.forward(ctx, cache, x, hidden)
+        self.branch.forward(ctx, x, hidden)
+        hidden.copy_(self.post_norm.forward(ctx, hidden).float())
+
+
 class PositionalEmbedding(Embedding):
     """``h_t = scale * E[id_t] + P[position_t]``: a multiplier and learned absolute positions,
     which the built-in embedding does not have."""
@@ -223,7 +239,9 @@ def build_toy_spec(cfg: ToyConfig) -> ModelSpec:
 
 def build_latent_spec(cfg: ToyConfig) -> ModelSpec:
     """A second toy: learned positions and a multiplier at the embedding, a latent-caching mixer,
-    the state mixer beside a routed feed-forward, and a tied head with a logit scale and a soft cap."""
+    the state mixer beside a routed feed-forward, a layer of another arrangement (no feed-forward
+    of the usual place, a parallel branch, a post-norm), and a tied head with a logit scale and a
+    soft cap."""
     norm = {"size": cfg.hidden_size, "eps": 1e-5}
     ffn = PartSpec("swiglu", {"hidden_size": cfg.hidden_size, "intermediate_size": cfg.intermediate_size})
     routed = PartSpec("toy_routed", {"hidden_size": cfg.hidden_size, "expert_size": cfg.expert_size,
@@ -234,10 +252,15 @@ def build_latent_spec(cfg: ToyConfig) -> ModelSpec:
                          PartSpec("rms_norm", {**norm, "name": "norm1.weight"}),
                          PartSpec("rms_norm", {**norm, "name": "norm2.weight"}))
 
+    parallel = LayerSpec("blocks.2", "toy_parallel", PartSpec("toy_decay", {"hidden_size": cfg.hidden_size, "decay": 0.4}),
+                         None, PartSpec("rms_norm", {**norm, "name": "norm1.weight"}), None,
+                         extra={"branch": ("feed_forward", ffn),
+                                "post_norm": ("norm", PartSpec("rms_norm", {**norm, "name": "post.weight"}))})
     layers = (layer(0, PartSpec("toy_latent", {"hidden_size": cfg.hidden_size, "latent_size": 20}), ffn),
-              layer(1, PartSpec("toy_decay", {"hidden_size": cfg.hidden_size, "decay": cfg.decay}), routed))
+              layer(1, PartSpec("toy_decay", {"hidden_size": cfg.hidden_size, "decay": cfg.decay}), routed),
+              parallel)
     return ModelSpec("ToyLatentLM", cfg.hidden_size, cfg.vocab_size, cfg.max_position_embeddings,
-                     "embed.weight", layers, (0, 1), PartSpec("rms_norm", norm), "final_norm.weight", None,
+                     "embed.weight", layers, (0, 1, 2), PartSpec("rms_norm", norm), "final_norm.weight", None,
                      embedding=PartSpec("toy_positional", {"scale": 1.5, "max_positions": cfg.max_position_embeddings}),
                      head=PartSpec("linear_head", {"name": None, "logit_scale": 0.5, "soft_cap": 3.0}))
 
@@ -251,6 +274,7 @@ class ToyLatentConfig(ToyConfig):
 
 
 def register():
+    BLOCKS.register("toy_parallel", ParallelPostNormBlock)
     MIXERS.register("toy_latent", LatentMixer)
     EMBEDDINGS.register("toy_positional", PositionalEmbedding)
     ARCHITECTURES.add("ToyLatentLM", ToyLatentConfig, build_latent_spec)
@@ -261,6 +285,7 @@ def register():
 
 
 def unregister():
+    BLOCKS.unregister("toy_parallel")
     MIXERS.unregister("toy_latent")
     EMBEDDINGS.unregister("toy_positional")
     ARCHITECTURES.unregister("ToyLatentLM")
@@ -364,5 +389,15 @@ def plain_logits_latent(cfg: ToyConfig, w, tokens):
         for sh, e in zip(share, chosen[:2].tolist()):
             out[t] += sh * (w[f"blocks.1.experts.{e}.out.weight"] @ torch.relu(w[f"blocks.1.experts.{e}.in.weight"] @ x[t]))
     h = h + out
+    # layer 2: one norm for the state mixer and a feed-forward branch beside it, then a post-norm
+    x = pm.rms_norm(h, w["blocks.2.norm1.weight"], 1e-5)
+    state = torch.zeros(cfg.hidden_size, dtype=torch.float64)
+    rows = []
+    for t in range(t_len):
+        state = 0.4 * state + 0.6 * x[t]
+        rows.append(state)
+    branch = pm.linear(pm.swiglu(pm.linear(x, w["blocks.2.gate_proj.weight"]), pm.linear(x, w["blocks.2.up_proj.weight"])),
+                       w["blocks.2.down_proj.weight"])
+    h = pm.rms_norm(h + torch.stack(rows) @ w["blocks.2.mix.weight"].t() + branch, w["blocks.2.post.weight"], 1e-5)
     raw = pm.linear(pm.rms_norm(h, w["final_norm.weight"], 1e-5), w["embed.weight"]) * 0.5
     return 3.0 * torch.tanh(raw / 3.0)
