@@ -285,9 +285,10 @@ class Engine:
             seen.add(e.rid)
             if len(e.tokens) == 0:
                 raise ValueError(f"request {e.rid!r}: a step entry needs at least one token")
-            bad = [t for t in e.tokens if not 0 <= int(t) < self.spec.vocab_size]
-            if bad:
-                raise ValueError(f"request {e.rid!r}: token ids {bad[:8]} are outside the "
+            ids = np.asarray(e.tokens, dtype=np.int64)
+            if ids.size and (int(ids.min()) < 0 or int(ids.max()) >= self.spec.vocab_size):
+                bad = [int(t) for t in ids[(ids < 0) | (ids >= self.spec.vocab_size)][:8]]
+                raise ValueError(f"request {e.rid!r}: token ids {bad} are outside the "
                                  f"vocabulary of {self.spec.vocab_size}")
             total += len(e.tokens)
         if total > self.rt.max_tokens:
