@@ -681,6 +681,10 @@ __device__ __forceinline__ void norm_rope_row(const __nv_bfloat16* src, __nv_bfl
   }
 }
 
+// Floats of the inbox's output part of the cluster kernel: up to 8 * NT heads of D outputs, each
+// block's range rounded up to a multiple of 4.
+template <int D, int NT> struct DecodeInbox { static constexpr int kFloats = 8 * NT * D + 4 * 8; };
+
 template <int D, int NT, bool kFuse>
 __global__ void __launch_bounds__(kThreads)
 attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
@@ -692,12 +696,20 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int row_s
   constexpr int kChunks = D / 8;
   constexpr int kGroupElems = 16 * kRow;
   extern __shared__ __align__(16) uint8_t smem_raw[];
-  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [16][kRow]
-  __nv_bfloat16* new_s = q_s + kGroupElems;             // the new token's key and value: [2][kRow]
-  __nv_bfloat16* kv_s = new_s + 2 * kRow;               // [4 warps][stages][K,V][16][kRow]
+  __nv_bfloat16* kv_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [4 warps][stages][K,V][16][kRow]
+  __nv_bfloat16* new_s = kv_s + 4 * kDecodeStages * 2 * kGroupElems;  // the new token's key and value: [2][kRow]
+  __nv_bfloat16* q_s = new_s + 2 * kRow;                               // [16][kRow]
+  // The inbox for the other splits' partial results lies over q_s (dead once every warp holds
+  // its query fragments) and runs to the end of the allocation.
+  float* inbox_o = reinterpret_cast<float*>(q_s);                      // [splits][per]
+  float* inbox_ml = inbox_o + DecodeInbox<D, NT>::kFloats;            // [splits][8 * NT rows][2]
 
+  // What the step's earlier kernels write for this one is the qkv rows (and, unfused, the new
+  // token's cache row).  The step's metadata and the cache rows of earlier positions are older
+  // than the step, so the fused kernel reads them, and requests its first keys, before it
+  // waits for its predecessor.
   pdl_trigger();
-  pdl_wait();
+  if constexpr (!kFuse) pdl_wait();
   const int g = n_q / pa.n_kv;
   const int groups = (g + 15) / 16;
   const int kvh = blockIdx.x / groups, hg = blockIdx.x - kvh * groups;
@@ -750,6 +762,7 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int row_s
     // the keys first: nothing of them depends on the query
 #pragma unroll
     for (int s0 = 0; s0 < kDecodeStages - 1; ++s0) issue(warp + 4 * s0, s0);
+    if constexpr (kFuse) pdl_wait();
 
     // the query rows (and the new key and value) while those copies are in flight
     const __nv_bfloat16* tok = qkv + (size_t)row_token * row_stride;
@@ -796,6 +809,7 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int row_s
     }
     __syncthreads();
     dw.load_q(q_s, lane);
+    if (splits > 1) cluster_arrive_release();      // q_s may now receive the other blocks' partials
     const float sl2 = scale * kLog2e;
     int it = 0;
     for (int grp = warp; grp < n_groups; grp += 4, ++it) {
@@ -818,75 +832,90 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int row_s
       __syncwarp();      // the stage is refilled by the next iteration's request
     }
     cp_async_wait<0>();
+  } else {
+    if constexpr (kFuse) pdl_wait();
+    if (splits > 1) cluster_arrive_release();
   }
   __syncthreads();     // every warp is done with its stages: the space becomes the merge buffer
 
   // the four warps -> one (max, sum, output) per query row of the block
   float* mo = reinterpret_cast<float*>(kv_s);          // [4 warps][16 rows][D]
   float* mml = mo + 4 * 16 * D;                        // [4][16][2]
-  float* cl_o = mml + 4 * 16 * 2;                      // [16][D]: this block's partial for the cluster
-  float* cl_ml = cl_o + 16 * D;                        // [16][2]
   dw.stash(mo, mml, warp, lane);
   __syncthreads();
-  for (int idx = tid; idx < heads * D; idx += kThreads) {
+  // With splits, block `s` finishes outputs [s * per, s * per + per) of the heads * D of this
+  // (sequence, head group): every block stores its partial sums of that range, and its (max,
+  // sum) per row, into block s's inbox, one cluster barrier follows, and each block finishes
+  // its range from its own shared memory.
+  const int n_out = heads * D;
+  const int per = ((n_out + splits - 1) / splits + 3) / 4 * 4;
+  constexpr int kRows = 8 * NT;
+  const uint32_t in_o = smem_u32(inbox_o), in_ml = smem_u32(inbox_ml);
+  if (splits > 1) cluster_wait_acquire();             // every block of the cluster holds its queries
+  for (int idx = tid * 4; idx < n_out; idx += kThreads * 4) {
     const int r = idx / D, c = idx - r * D;
     float m = -INFINITY;
 #pragma unroll
     for (int w = 0; w < 4; ++w) m = fmaxf(m, mml[(w * 16 + r) * 2]);
-    float l = 0.f, o = 0.f;
+    float l = 0.f;
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
       const float mw = mml[(w * 16 + r) * 2];
       const float f = mw == -INFINITY ? 0.f : exp2f(mw - m);
+      const float4 ow = *reinterpret_cast<const float4*>(mo + (size_t)(w * 16 + r) * D + c);
       l += f * mml[(w * 16 + r) * 2 + 1];
-      o += f * mo[(size_t)(w * 16 + r) * D + c];
+      o.x += f * ow.x;
+      o.y += f * ow.y;
+      o.z += f * ow.z;
+      o.w += f * ow.w;
     }
     if (splits > 1) {
-      cl_o[r * D + c] = o;
+      const int owner = idx / per;
+      cluster_st_f32x4(cluster_map(in_o + (uint32_t)(split * per + idx - owner * per) * 4, owner), o.x, o.y, o.z, o.w);
       if (c == 0) {
-        cl_ml[r * 2] = m;
-        cl_ml[r * 2 + 1] = l;
+        for (int s2 = 0; s2 < splits; ++s2)
+          cluster_st_f32x2(cluster_map(in_ml + (uint32_t)(split * kRows + r) * 8, s2), m, l);
       }
     } else {
-      out[(size_t)row_token * out_stride + (size_t)(head0 + r) * D + c] =
-          __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(out + (size_t)row_token * out_stride +
+                                                              (size_t)(head0 + r) * D + c);
+      dst[0] = __floats2bfloat162_rn(o.x * inv, o.y * inv);
+      dst[1] = __floats2bfloat162_rn(o.z * inv, o.w * inv);
     }
   }
   if (splits == 1) return;            // grid-uniform: a launch has clusters or it has none
 
-  // Every thread of every block of the cluster comes here.  Block `split` merges outputs
-  // [split * per, split * per + per) of the heads * D of this (sequence, head group).
-  cluster_sync_all();
-  const int n_out = heads * D;
-  const int per = (n_out + splits - 1) / splits;
-  const uint32_t o_base = smem_u32(cl_o), ml_base = smem_u32(cl_ml);
-  for (int idx = split * per + tid; idx < min(n_out, split * per + per); idx += kThreads) {
+  // Every thread of every block of the cluster comes here.
+  cluster_arrive_release();
+  cluster_wait_acquire();
+  const int mine = min(n_out, split * per + per) - split * per;
+  for (int j = tid * 2; j < mine; j += kThreads * 2) {
+    const int idx = split * per + j;
     const int r = idx / D;
-    float ms[8], ls[8], os[8];
     float m = -INFINITY;
+#pragma unroll
+    for (int s2 = 0; s2 < 8; ++s2)
+      if (s2 < splits) m = fmaxf(m, inbox_ml[(s2 * kRows + r) * 2]);
+    float l = 0.f, o0 = 0.f, o1 = 0.f;
 #pragma unroll
     for (int s2 = 0; s2 < 8; ++s2) {
       if (s2 < splits) {
-        ms[s2] = cluster_ld_f32(cluster_map(ml_base + r * 8, s2));
-        ls[s2] = cluster_ld_f32(cluster_map(ml_base + r * 8 + 4, s2));
-        os[s2] = cluster_ld_f32(cluster_map(o_base + idx * 4, s2));
+        const float ms = inbox_ml[(s2 * kRows + r) * 2];
+        if (ms != -INFINITY) {
+          const float f = exp2f(ms - m);
+          const float2 os = *reinterpret_cast<const float2*>(inbox_o + s2 * per + j);
+          l += f * inbox_ml[(s2 * kRows + r) * 2 + 1];
+          o0 += f * os.x;
+          o1 += f * os.y;
+        }
       }
     }
-#pragma unroll
-    for (int s2 = 0; s2 < 8; ++s2)
-      if (s2 < splits) m = fmaxf(m, ms[s2]);
-    float l = 0.f, o = 0.f;
-#pragma unroll
-    for (int s2 = 0; s2 < 8; ++s2) {
-      if (s2 < splits && ms[s2] != -INFINITY) {
-        const float f = exp2f(ms[s2] - m);
-        l += f * ls[s2];
-        o += f * os[s2];
-      }
-    }
-    out[(size_t)row_token * out_stride + (size_t)head0 * D + idx] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    *reinterpret_cast<__nv_bfloat162*>(out + (size_t)row_token * out_stride + (size_t)head0 * D + idx) =
+        __floats2bfloat162_rn(o0 * inv, o1 * inv);
   }
-  cluster_sync_all();                 // the partials may go away
 }
 
 template <int D> constexpr int prefill_smem() {
@@ -916,10 +945,11 @@ int launch_prefill(const __nv_bfloat16* qkv, int row_stride, __nv_bfloat16* out,
                        row_stride, out, out_stride, pa, q_start, ctx_len, n_q, scale, window, status);
 }
 
-template <int D> constexpr int decode_cluster_smem() {
-  const int tiles = (16 + 4 * kDecodeStages * 2 * 16) * (D + 8) * 2 + 2 * (D + 8) * 2;
-  const int merge = 18 * (D + 8) * 2 + (4 * 16 * D + 4 * 16 * 2 + 16 * D + 16 * 2) * 4;
-  return tiles > merge ? tiles : merge;
+template <int D, int NT> constexpr int decode_cluster_smem() {
+  const int rings = (4 * kDecodeStages * 2 * 16 + 2) * (D + 8) * 2;
+  const int q_rows = 16 * (D + 8) * 2;
+  const int inbox = (DecodeInbox<D, NT>::kFloats + 8 * 8 * NT * 2) * 4;
+  return rings + (q_rows > inbox ? q_rows : inbox);
 }
 
 template <int D, int NT, bool kFuse>
@@ -930,18 +960,18 @@ int launch_decode_cluster_nt(const __nv_bfloat16* qkv, int row_stride, __nv_bflo
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_decode_cluster_kernel<D, NT, kFuse>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, decode_cluster_smem<D>());
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, decode_cluster_smem<D, NT>());
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   const int g = n_q / pa.n_kv;
   dim3 grid(pa.n_kv * ((g + 15) / 16), splits, n_seqs);
   if (splits == 1)
-    return launch_kernel(attention_decode_cluster_kernel<D, NT, kFuse>, grid, dim3(kThreads), decode_cluster_smem<D>(),
+    return launch_kernel(attention_decode_cluster_kernel<D, NT, kFuse>, grid, dim3(kThreads), decode_cluster_smem<D, NT>(),
                          stream, qkv, row_stride, out, out_stride, pa, q_start, ctx_len, n_q, scale, window,
                          splits, fz, status);
   return launch_kernel_cluster(attention_decode_cluster_kernel<D, NT, kFuse>, grid, dim3(kThreads),
-                               decode_cluster_smem<D>(), stream, dim3(1, splits, 1), qkv, row_stride, out,
+                               decode_cluster_smem<D, NT>(), stream, dim3(1, splits, 1), qkv, row_stride, out,
                                out_stride, pa, q_start, ctx_len, n_q, scale, window, splits, fz, status);
 }
 

@@ -126,6 +126,21 @@ __device__ __forceinline__ uint32_t cluster_map(uint32_t addr, uint32_t rank) {
 __device__ __forceinline__ void cluster_st_f32(uint32_t addr, float v) {
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
+__device__ __forceinline__ void cluster_st_f32x4(uint32_t addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+__device__ __forceinline__ void cluster_st_f32x2(uint32_t addr, float a, float b) {
+  asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(addr), "f"(a), "f"(b) : "memory");
+}
+// An arrival that publishes this thread's earlier reads and writes to the cluster, and the wait
+// that makes the other blocks' published writes visible.
+__device__ __forceinline__ void cluster_arrive_release() {
+  asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait_acquire() {
+  asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+}
 // The two halves of a cluster barrier on their own: an arrival that orders nothing (it only says
 // "this thread of this block is running"), and the wait that completes the phase.  Every thread
 // pairs each arrival with one wait before it arrives again.

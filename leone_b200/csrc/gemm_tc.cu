@@ -105,9 +105,11 @@ __device__ __forceinline__ Unit unit_of(int u, const GemmParams& p) {
 // Swapped orientation: the thread that owns weight row n finishes NC token columns
 // m0 + c .. m0 + c + NC - 1 whose sums are in v (r: the residual values, fetched by the caller
 // before anything is stored, because the residual may be the output itself).
+// gw_known: the following norm's weight of row n if the caller fetched it already (else null).
 template <int NC>
 __device__ __forceinline__ void finish_swapped(const GemmParams& p, float (&v)[NC], const float (&r)[NC],
-                                               int n, int m0, int c, int lane, const float* rs_s) {
+                                               int n, int m0, int c, int lane, const float* rs_s,
+                                               const float* gw_known = nullptr) {
   if (p.norm_in_ss != nullptr) {
 #pragma unroll
     for (int j = 0; j < NC; ++j) v[j] *= rs_s[c + j];
@@ -144,7 +146,7 @@ __device__ __forceinline__ void finish_swapped(const GemmParams& p, float (&v)[N
   if (p.norm_out_x != nullptr) {
     // the operand of the product after the following norm, and this warp's 32 rows' share of
     // the sums of squares (the lanes of a warp are 32 consecutive weight rows)
-    const float gw = n < p.N ? p.norm_out_w[n] : 0.f;
+    const float gw = gw_known != nullptr ? *gw_known : n < p.N ? p.norm_out_w[n] : 0.f;
 #pragma unroll
     for (int j = 0; j < NC; ++j) {
       const int m = m0 + c + j;
@@ -168,9 +170,32 @@ __device__ __forceinline__ void fetch_residual(const GemmParams& p, float (&r)[N
   }
 }
 
+// The residual values that finish_token_major32 would add to token row m, weight rows n .. n+31
+// (zeros where there are none), so that the caller can have them in flight early.
+__device__ __forceinline__ void fetch_residual32(const GemmParams& p, float (&r)[32], int m, int n) {
+#pragma unroll
+  for (int j = 0; j < 32; ++j) r[j] = 0.f;
+  if (p.epilogue != 2 || m >= p.M || n >= p.N) return;
+  const size_t o = (size_t)m * p.ldc + n;
+  if (n + 32 <= p.N && (p.ldc & 3) == 0) {
+    const float4* res = reinterpret_cast<const float4*>(p.residual + o);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float4 q = res[j];
+      r[4 * j] = q.x; r[4 * j + 1] = q.y; r[4 * j + 2] = q.z; r[4 * j + 3] = q.w;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (n + j < p.N) r[j] = p.residual[o + j];
+  }
+}
+
 // Token-major form, splits summed inside a cluster: 32 finished sums of token row m for the weight
 // rows n .. n+31 (n a multiple of 32) go out through the product's epilogue.  No folded norm.
-__device__ __forceinline__ void finish_token_major32(const GemmParams& p, float (&v)[32], int m, int n) {
+// residual_added: the caller has added the residual already (fetch_residual32).
+__device__ __forceinline__ void finish_token_major32(const GemmParams& p, float (&v)[32], int m, int n,
+                                                     bool residual_added = false) {
   if (m >= p.M || n >= p.N) return;
   const bool vec_ok = (p.ldc & 7) == 0;
   if (p.epilogue == 3) {                                 // 16 gate columns, then their 16 up columns
@@ -218,7 +243,7 @@ __device__ __forceinline__ void finish_token_major32(const GemmParams& p, float 
     } else {
       float* dst = (float*)p.out + o;
       if (full) {
-        if (p.epilogue == 2) {
+        if (p.epilogue == 2 && !residual_added) {
           const float4* res = reinterpret_cast<const float4*>(p.residual + o);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
@@ -231,7 +256,7 @@ __device__ __forceinline__ void finish_token_major32(const GemmParams& p, float 
           reinterpret_cast<float4*>(dst)[j] = make_float4(vv[4 * j], vv[4 * j + 1], vv[4 * j + 2], vv[4 * j + 3]);
       } else {
         for (int j = 0; j < 16 && nn + j < p.N; ++j) {
-          if (p.epilogue == 2) vv[j] += p.residual[o + j];
+          if (p.epilogue == 2 && !residual_added) vv[j] += p.residual[o + j];
           dst[j] = vv[j];
         }
       }
@@ -269,6 +294,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __shared__ float rs_s[kSwap ? BN : 1];          // per token: the scale of the norm before this product
   __shared__ float red_s[kSwap ? 4 * BN : 1];
 
+  // Push mode: the residual values and the following norm's weight of the rows this thread
+  // finishes (up to four chunks of 32 rows), fetched while the products run.
+  constexpr int kPreNC = kPush ? BN / 4 : 1;
+  float pre_r[4][kPreNC], pre_gw[4];
+
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) stamp(p, 7);                       // first instruction of the block
   // tiles along the tokens (m) and along the weight rows (n); the token tile index runs
@@ -289,6 +319,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       mbar_init(acc_full0 + 8 * b, 1);
       mbar_init(acc_empty0 + 8 * b, 4);
     }
+    mbar_init(acc_empty0 + 16, 1);     // token-major cluster mode: the partial sums have landed
     mbar_fence_init();
     tma_prefetch_desc(&map_w);
     tma_prefetch_desc(&map_x);
@@ -423,6 +454,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         named_barrier_sync(1, 128);
       }
     }
+    if constexpr (kPush) {
+      if (blockIdx.x < total) {
+        const Unit un = unit_of(blockIdx.x, p);
+        const int m_tile = un.tile % m_tiles, n_tile = un.tile / m_tiles;
+        const int rank = (int)cluster_ctarank();
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int ch = rank + k * un.nsplit;
+          if (ch < kTileW / 32) {
+            const int n = n_tile * kTileW + ch * 32 + lane;
+            fetch_residual<kPreNC>(p, pre_r[k], n, m_tile * BN, (warp & 3) * kPreNC);
+            pre_gw[k] = p.norm_out_x != nullptr && n < p.N ? p.norm_out_w[n] : 0.f;
+          }
+        }
+      }
+    }
     for (int t = blockIdx.x; t < total && !*giveup; t += gridDim.x, ++it) {
       const Unit un = unit_of(t, p);
       const int tile = un.tile, split = un.split, nsplit = un.nsplit;
@@ -452,6 +499,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < 16; ++j) cluster_st_f32(dst + (c + j) * 32 * 4, v[j]);
         }
+        break;                                           // one unit per block in this mode
+      } else if constexpr (kCluster && !kSwap) {
+        // Token-major tiles are 128 KB of partial sums: they go through the workspace (L2), which
+        // moves several times the bytes per second that distributed shared memory does;
+        // [unit][chunk of 32 rows][accumulator column][row of the chunk]: 32 rows side by side
+        // in every store, and a chunk of one unit is 32 KB in one piece.
+        float* ws = p.workspace + (size_t)t * (BN * kTileW) + (size_t)quarter * (BN * 32) + lane;
+        for (int c = 0; c < BN; c += 64) {               // two loads of 32 columns in flight
+          uint32_t r[64];
+          tmem_ld32_issue(taddr + c, r);
+          tmem_ld32_issue(taddr + c + 32, r + 32);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 64; ++j) ws[(c + j) * 32] = __uint_as_float(r[j]);
+        }
+        __threadfence();
         break;                                           // one unit per block in this mode
       } else if constexpr (kCluster) {
         // this block's partial tile goes to its own shared memory, [accumulator column][row];
@@ -720,59 +783,90 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int m0 = m_tile * BN;
         constexpr int NC = BN / 4;
         const int rank = (int)cluster_ctarank();
-        for (int ch = rank; ch < kTileW / 32; ch += un.nsplit) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int ch = rank + k * un.nsplit;
+          if (ch >= kTileW / 32) break;
           const int n = n_tile * kTileW + ch * 32 + lane;
           const float* mine = inbox + (size_t)((ch / un.nsplit) * un.nsplit) * BN * 32 + lane;
           const int c = (warp & 3) * NC;
-          float v[NC], r[NC];
-          fetch_residual<NC>(p, r, n, m0, c);
+          float v[NC];
 #pragma unroll
           for (int j = 0; j < NC; ++j) v[j] = 0.f;
           for (int s0 = 0; s0 < un.nsplit; ++s0) {       // rank order
 #pragma unroll
             for (int j = 0; j < NC; ++j) v[j] += mine[((size_t)s0 * BN + c + j) * 32];
           }
-          finish_swapped<NC>(p, v, r, n, m0, c, lane, rs_s);
+          finish_swapped<NC>(p, v, pre_r[k], n, m0, c, lane, rs_s, &pre_gw[k]);
         }
       }
     } else
     if constexpr (!kSwap) {
-      // token-major: the rows are tokens; in a chunk lane = token row, and each epilogue warp
-      // owns a quarter of the tile's weight rows, 32 at a time (a gate/up group for SwiGLU)
-      if (warp >= 2 && blockIdx.x < total) {
+      // token-major: the rows are tokens; chunk ch (32 token rows) is finished by the block of
+      // rank ch % splits.  The chunk's partial sums of up to four ranks at a time are copied
+      // from the workspace into the (now free) stages in pieces of 32 KB, one per rank, by the
+      // copy engine; then lane = token row, and each epilogue warp adds, in rank order, a
+      // quarter of the tile's weight rows, 32 at a time (a gate/up group for SwiGLU).
+      if (warp >= 2 && blockIdx.x < total && !*giveup) {
         const Unit un = unit_of(blockIdx.x, p);
         const int m_tile = un.tile % m_tiles, n_tile = un.tile / m_tiles;
         constexpr int kColsPerWarp = BN / 4;
+        constexpr int kGroups = kColsPerWarp / 32;
+        constexpr uint32_t kPiece = BN * 32 * 4;         // one rank's partial sums of a chunk
         static_assert(kColsPerWarp % 32 == 0, "a warp's share of the weight rows is whole gate/up groups");
+        static_assert(kStages * Cfg::kStageBytes >= 4 * (int)kPiece, "four pieces must fit in the stages");
         const int rank = (int)cluster_ctarank();
+        const float* ws_tile = p.workspace + (size_t)(blockIdx.x - rank) * (BN * kTileW);
+        const float* box = reinterpret_cast<const float*>(aligned);
+        const uint32_t landed = acc_empty0 + 16;
+        const int et = (warp - 2) * 32 + lane;
+        const uint32_t read0 = acc_empty0;               // (count 4, unused otherwise in this mode)
+        uint32_t landed_phase = 0, read_phase = 0;
+        bool first = true;
         for (int ch = rank; ch < kTileW / 32; ch += un.nsplit) {
-          const int row_local = ch * 32 + lane;
-          const int m = m_tile * kTileW + row_local;
-          const uint32_t mine = tiles_base + row_local * 4;
-          for (int c = (warp & 3) * kColsPerWarp; c < (warp & 3) * kColsPerWarp + kColsPerWarp; c += 32) {
-            float v[32];
+          const int m = m_tile * kTileW + ch * 32 + lane;
+          // the sums start from the residual values, which are in flight while the pieces land
+          float v[kGroups][32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = 0.f;
-            for (int s0 = 0; s0 < un.nsplit; s0 += 2) {  // two ranks' loads in flight together
-              float t[2][32];
-#pragma unroll
-              for (int u = 0; u < 2; ++u) {
-                if (s0 + u < un.nsplit) {
-                  const uint32_t src = cluster_map(mine, s0 + u) + c * kTileW * 4;
-#pragma unroll
-                  for (int j = 0; j < 32; ++j) t[u][j] = cluster_ld_f32(src + j * kTileW * 4);
-                }
+          for (int g = 0; g < kGroups; ++g)
+            fetch_residual32(p, v[g], m, n_tile * BN + (warp & 3) * kColsPerWarp + g * 32);
+          bool ok = true;
+          for (int sb = 0; sb < un.nsplit; sb += 4) {
+            const int nb = min(4, un.nsplit - sb);
+            if (et == 0) {
+              // the pieces before these have been read by all four warps (every wait is bounded:
+              // if this one runs out nothing is requested and the others' waits run out too)
+              bool go = true;
+              if (!first) {
+                go = mbar_wait(read0, read_phase, giveup);
+                read_phase ^= 1;
               }
-#pragma unroll
-              for (int u = 0; u < 2; ++u) {              // rank order
-                if (s0 + u < un.nsplit) {
-#pragma unroll
-                  for (int j = 0; j < 32; ++j) v[j] += t[u][j];
-                }
+              if (go) {
+                fence_proxy_async();
+                mbar_expect_tx(landed, (uint32_t)nb * kPiece);
+                for (int u = 0; u < nb; ++u)
+                  bulk_load(tiles_base + (uint32_t)u * kPiece,
+                            ws_tile + (size_t)(sb + u) * (BN * kTileW) + (size_t)ch * (BN * 32), kPiece, landed);
               }
             }
-            finish_token_major32(p, v, m, n_tile * BN + c);
+            first = false;
+            if (!mbar_wait(landed, landed_phase, giveup)) { ok = false; break; }
+            landed_phase ^= 1;
+#pragma unroll
+            for (int g = 0; g < kGroups; ++g) {
+              const float* src = box + (size_t)((warp & 3) * kColsPerWarp + g * 32) * 32 + lane;
+              for (int u = 0; u < nb; ++u) {             // rank order
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[g][j] += src[(size_t)u * (BN * 32) + j * 32];
+              }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(read0);           // this warp has read the pieces
           }
+          if (!ok) break;
+#pragma unroll
+          for (int g = 0; g < kGroups; ++g)
+            finish_token_major32(p, v[g], m, n_tile * BN + (warp & 3) * kColsPerWarp + g * 32, true);
         }
       }
     } else
@@ -817,7 +911,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
     }
     __syncwarp();
-    if constexpr (!kPush) cluster_sync_all();            // the partial tiles may go away
+    if constexpr (!kPush && kSwap) cluster_sync_all();   // the partial tiles may go away
   }
 
   // ---------------- teardown ----------------
@@ -1038,6 +1132,7 @@ extern "C" int leone_gemm_tc(const void* x, const void* w, void* out, const floa
   if (norm_in_ss != nullptr && norm_in_parts < 1) return kRefusedSize;
   if (cluster && (full_tiles != 0 || splits > 8)) return kRefusedSize;
   if (splits > 1 && !cluster && (workspace == nullptr || counters == nullptr)) return kRefusedSize;
+  if (splits > 1 && cluster && !swap && workspace == nullptr) return kRefusedSize;
   // the token-major tile's width: 256 when split or forced below the prompt sizes
   const int tm_width = (swap || cluster || m <= 256) ? 256 : leone_gemm_tc_token_major_width(m, n, epilogue == 3);
   const int tiles = swap ? leone_gemm_tc_tiles(m, n)

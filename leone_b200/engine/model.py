@@ -147,7 +147,8 @@ class Model:
     def scratch_bytes(self, max_tokens: int, max_logit_rows: int) -> int:
         """An estimate of the scratch a step of ``max_tokens`` tokens asks the runtime for: the fp32
         residual stream, the normed tokens (twice: a folded norm keeps its own copy), the largest
-        layer's buffers (layers share them by name), and fp32 logits for ``max_logit_rows`` rows."""
+        layer's buffers (layers share them by name), fp32 logits for ``max_logit_rows`` rows, and what
+        the ops keep for themselves."""
         item = self.rt.dtype.itemsize
         total = max_tokens * self.hidden_size * (4 + 3 * item)
         per_layer = [sum(p.scratch_bytes(max_tokens)
@@ -156,7 +157,8 @@ class Model:
                      for b in self.blocks]
         total += max(per_layer, default=0)
         total += max_logit_rows * (self.vocab_size * 4 + self.hidden_size * item)
-        return total
+        ops_scratch = getattr(self.rt.ops, "scratch_bytes", None)
+        return total + (ops_scratch() if ops_scratch is not None else 0)
 
     def load_transient_bytes(self) -> int:
         """The most any one part holds beyond its inputs while it loads."""

@@ -123,6 +123,10 @@ class CudaOps:
         return _STATUS_TEXT.get(word, "unknown status")
 
     # -- weights ------------------------------------------------------------------------
+    def scratch_bytes(self) -> int:
+        """Device memory the ops allocate for themselves beyond the runtime's named buffers."""
+        return self.fast.scratch_bytes() if self.fast is not None else 0
+
     def prepare_matrix(self, w: torch.Tensor) -> PreparedMatrix:
         _need(w.dim() == 2 and w.is_contiguous(), "a weight matrix must be contiguous [out, in]")
         return PreparedMatrix(w)

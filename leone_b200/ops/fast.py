@@ -68,6 +68,15 @@ class FastKernels:
         if tensor is not None:
             self._retired.append(tensor)
 
+    def token_major_workspace_floats(self) -> int:
+        """One 128 x 256 fp32 partial tile per block of a round."""
+        return self.sm_count * 128 * 256
+
+    def scratch_bytes(self) -> int:
+        """What these ops allocate for themselves at most: the split products' workspace and the
+        split decode attention's partial results."""
+        return 4 * (max(self.min_scratch_floats, self.token_major_workspace_floats()) + self.min_scratch_floats)
+
     def _scratch(self, floats: int, counters: int):
         if self._workspace is None or self._workspace.numel() < floats:
             self._retire(self._workspace)
@@ -201,6 +210,12 @@ class FastKernels:
             floats, counters = c_longlong(0), c_int(0)
             self.lib.leone_gemm_tc_scratch(m, max(tiles - full_tiles, 0), splits, byref(floats), byref(counters))
             ws, ct = self._scratch(floats.value, counters.value)
+        elif splits > 1 and token_major:
+            # the token-major form's partial tiles (128 tokens x 256 weight rows, fp32) cross
+            # between the blocks of a cluster through the workspace
+            # (one round of blocks at most, so the largest request is asked for at once and the
+            # buffer never grows with the step's size)
+            ws, _ = self._scratch(self.token_major_workspace_floats(), 0)
         from ctypes import c_float
         no = (None, None, None, 0) if norm_out is None else \
             (_ptr(norm_out[0]), _ptr(norm_out[1]), _ptr(norm_out[2]), norm_out[0].stride(0))
