@@ -255,6 +255,8 @@ def main(argv=None) -> int:
     ap.add_argument("--decode-splits", type=int, default=0,
                     help="decode-attention: split every sequence's keys this many ways (0: the dispatcher's choice)")
     ap.add_argument("--max-cluster", type=int, default=8, help="largest thread-block cluster the dispatchers may use")
+    ap.add_argument("--decode-cluster-rounds", type=int, default=1,
+                    help="decode-attention: rounds of blocks that a launch of clusters may take")
     ap.add_argument("--gemm-splits", default="",
                     help='layer-shapes: forced splits by product, "6144x4096:4,4096x12288:c8" (c: inside a cluster)')
     args = ap.parse_args(argv)
@@ -262,6 +264,7 @@ def main(argv=None) -> int:
     ops = CudaOps(DEV, torch.bfloat16)
     ops.fast.force_decode_splits = args.decode_splits
     ops.fast.max_cluster = args.max_cluster
+    ops.fast.decode_cluster_rounds = args.decode_cluster_rounds
     for item in filter(None, args.gemm_splits.split(",")):
         shape, _, how = item.partition(":")
         n_, _, k_ = shape.partition("x")

@@ -48,6 +48,7 @@ class FastKernels:
         # LEONE_NO_FUSED_DECODE=1 keeps q/k norm, rotation and cache write in their own kernel
         self.fuse_decode = os.environ.get("LEONE_NO_FUSED_DECODE", "0") != "1"
         self.max_cluster = 8               # the portable cluster size
+        self.decode_cluster_rounds = 1     # rounds of blocks a clustered decode attention may take (kernel_bench sets it)
         # (n, k) -> (splits, cluster): a forced split of an [n x k] product at decode sizes; empty
         # in the product, filled by kernel_bench's sweeps
         self.split_override = {}
@@ -272,16 +273,19 @@ class FastKernels:
         """Splits of the key range.  Two blocks fit an SM; the cost of a choice is its number of
         rounds over those slots times the share of the keys a block walks, plus a little per
         split for the merge, plus a fixed charge when the splits cannot merge inside clusters
-        (scratch and a merge kernel; measured at batch 64: one split 101 us, two to four 109-112).
-        A split keeps at least 128 keys."""
+        (scratch, a merge kernel and the q/k preparation in a kernel of its own: a fixed part,
+        measured at batch 64: one split 101 us, two to four 109-112; and a tenth of the walk,
+        measured at batches 160 to 224: one fused split 242 / 289 / 326 us, three to six splits
+        250 / 309 / 366).  A split keeps at least 128 keys."""
         if self.force_decode_splits:
             return self.force_decode_splits
         blocks = n_seqs * n_kv * (-(-g // 16))
         slots = 2 * self.sm_count
         best, best_cost = 1, None
         for s in range(1, min(32, max(1, max_ctx // 128)) + 1):
-            clustered = self.use_clusters and s <= 8 and blocks * s <= slots
-            cost = -(-(blocks * s) // slots) / s + 0.03 * s + (0.0 if s == 1 or clustered else 0.2)
+            clustered = self.use_clusters and s <= 8 and blocks * s <= slots * self.decode_cluster_rounds
+            walk = -(-(blocks * s) // slots) / s
+            cost = walk + 0.03 * s + (0.0 if s == 1 or clustered else 0.2 + 0.1 * walk)
             if best_cost is None or cost < best_cost - 1e-9:
                 best, best_cost = s, cost
         return best
@@ -305,7 +309,8 @@ class FastKernels:
         and a merge kernel."""
         splits = self.decode_splits(n_seqs, n_kv, g, max_ctx)
         blocks = n_seqs * n_kv * (-(-g // 16)) * splits
-        return self.use_clusters and (splits == 1 or (splits <= 8 and blocks <= 2 * self.sm_count))
+        return self.use_clusters and (splits == 1 or (splits <= 8 and
+                                                      blocks <= 2 * self.sm_count * self.decode_cluster_rounds))
 
     def leading_decode_rows(self, ctx) -> int:
         """In a mixed step, how many sequences at the front of the batch bring a single token
