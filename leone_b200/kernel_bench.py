@@ -255,6 +255,8 @@ def main(argv=None) -> int:
     ap.add_argument("--decode-splits", type=int, default=0,
                     help="decode-attention: split every sequence's keys this many ways (0: the dispatcher's choice)")
     ap.add_argument("--max-cluster", type=int, default=8, help="largest thread-block cluster the dispatchers may use")
+    ap.add_argument("--l2-ahead", type=int, default=None,
+                    help="gemm, layer-shapes: k-blocks of weights a decode-sized product asks the L2 for ahead of its stages")
     ap.add_argument("--decode-cluster-rounds", type=int, default=1,
                     help="decode-attention: rounds of blocks that a launch of clusters may take")
     ap.add_argument("--gemm-splits", default="",
@@ -265,6 +267,8 @@ def main(argv=None) -> int:
     ops.fast.force_decode_splits = args.decode_splits
     ops.fast.max_cluster = args.max_cluster
     ops.fast.decode_cluster_rounds = args.decode_cluster_rounds
+    if args.l2_ahead is not None:
+        ops.fast.lib.leone_gemm_tc_set_l2_ahead(args.l2_ahead)
     for item in filter(None, args.gemm_splits.split(",")):
         shape, _, how = item.partition(":")
         n_, _, k_ = shape.partition("x")
