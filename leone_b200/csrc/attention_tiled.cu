@@ -631,6 +631,7 @@ struct DecodeFuse {
   const float2* rope;       // [max_positions][D / 2] (cos, sin) or null
   int max_positions;
   int write_cache;          // 0 for a layer that only reads another layer's cache
+  int adjacent;             // rotation pairs are elements (2i, 2i + 1) instead of (i, i + D/2)
 };
 
 // One warp: RMSNorm (if w) and half-split rotary over the whole row (if rope_row) of D bf16
@@ -639,7 +640,7 @@ struct DecodeFuse {
 template <int D>
 __device__ __forceinline__ void norm_rope_row(const __nv_bfloat16* src, __nv_bfloat16* dst,
                                               __nv_bfloat16* dst2, const float* w, float eps,
-                                              const float2* rope_row, int lane) {
+                                              const float2* rope_row, int lane, bool adjacent) {
   constexpr int E = D / 32;
   static_assert(D % 64 == 0, "two elements per lane at least");
   float v[E], wv[E];
@@ -654,7 +655,8 @@ __device__ __forceinline__ void norm_rope_row(const __nv_bfloat16* src, __nv_bfl
 #pragma unroll
   for (int i = 0; i < E; ++i) {
     wv[i] = w != nullptr ? w[lane * E + i] : 1.f;
-    cs[i] = rope_row != nullptr ? rope_row[(lane & 15) * E + i] : make_float2(1.f, 0.f);
+    const int pair = adjacent ? (lane * E) / 2 + (i >> 1) : (lane & 15) * E + i;
+    cs[i] = rope_row != nullptr ? rope_row[pair] : make_float2(1.f, 0.f);
   }
   if (w != nullptr) {
     float ss = 0.f;
@@ -665,7 +667,14 @@ __device__ __forceinline__ void norm_rope_row(const __nv_bfloat16* src, __nv_bfl
 #pragma unroll
     for (int i = 0; i < E; ++i) v[i] = v[i] * wv[i] * inv;
   }
-  if (rope_row != nullptr) {
+  if (rope_row != nullptr && adjacent) {             // both elements of a pair are this lane's own
+#pragma unroll
+    for (int i = 0; i < E; i += 2) {
+      const float a = v[i], b = v[i + 1];
+      v[i] = a * cs[i].x - b * cs[i].y;
+      v[i + 1] = a * cs[i].y + b * cs[i].x;
+    }
+  } else if (rope_row != nullptr) {
     const bool upper = lane >= 16;
 #pragma unroll
     for (int i = 0; i < E; ++i) {
@@ -777,7 +786,8 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int row_s
       }
       for (int r = warp; r < 16 + (own_new ? 2 : 0); r += 4) {
         if (r < heads) {
-          norm_rope_row<D>(tok + (size_t)(head0 + r) * D, q_s + r * kRow, nullptr, fz.q_w, fz.eps, rope_row, lane);
+          norm_rope_row<D>(tok + (size_t)(head0 + r) * D, q_s + r * kRow, nullptr, fz.q_w, fz.eps, rope_row, lane,
+                           fz.adjacent != 0);
         } else if (r < 16) {
           for (int c = lane; c < kRow; c += 32) q_s[r * kRow + c] = __float2bfloat16_rn(0.f);
         } else {
@@ -796,7 +806,7 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int row_s
           }
           const __nv_bfloat16* src = tok + (size_t)(n_q + (is_k ? 0 : pa.n_kv) + kvh) * D;
           norm_rope_row<D>(src, new_s + (r - 16) * kRow, cache_row, is_k ? fz.k_w : nullptr, fz.eps,
-                           is_k ? rope_row : nullptr, lane);
+                           is_k ? rope_row : nullptr, lane, fz.adjacent != 0);
         }
       }
     } else {
@@ -1103,7 +1113,8 @@ extern "C" int leone_attention_decode(const void* qkv, int row_stride, void* out
 // merges through distributed shared memory: 1 <= splits <= 8, no scratch.  With `fuse` != 0 the
 // rows of qkv are raw projections: the kernel applies the per-head RMSNorm (weights q_norm_w /
 // k_norm_w, fp32 [d], or null for none) and the rotary table (`rope`: [max_positions][d/2]
-// (cos, sin) fp32 over the whole head, or null) to the queries and to the new key at position
+// (cos, sin) fp32 over the whole head, or null; pairs (i, i + d/2), or (2i, 2i + 1) with
+// `adjacent`) to the queries and to the new key at position
 // ctx_len-1, uses the new key and value in place of what the cache holds there and, if
 // `write_cache`, stores them into the pools.  fuse needs d of 64 or 128.
 extern "C" int leone_attention_decode_cluster(const void* qkv, int row_stride, void* out, int out_stride,
@@ -1113,7 +1124,7 @@ extern "C" int leone_attention_decode_cluster(const void* qkv, int row_stride, v
                                               int page_tokens, int num_pages, int splits, int fuse,
                                               const float* q_norm_w, const float* k_norm_w, float eps,
                                               const float* rope, int max_positions, int write_cache,
-                                              int* status, cudaStream_t stream) {
+                                              int adjacent, int* status, cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
   int r = check_common(d, n_q, n_kv, row_stride, out_stride, qkv, k_pool, v_pool, page_tokens, table_width);
   if (r != 0) return r;
@@ -1122,7 +1133,7 @@ extern "C" int leone_attention_decode_cluster(const void* qkv, int row_stride, v
   PagedArgs pa{(const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, block_table, table_width,
                page_tokens, num_pages, n_kv};
   DecodeFuse fz{fuse ? 1 : 0, q_norm_w, k_norm_w, eps, reinterpret_cast<const float2*>(rope), max_positions,
-                write_cache};
+                write_cache, adjacent};
   if (fuse) {
     if (d == 64)
       return launch_decode_cluster<64, true>((const __nv_bfloat16*)qkv, row_stride, (__nv_bfloat16*)out,

@@ -152,10 +152,12 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
 }
 
 // ---------------------------------------------------------------------------
-// Per-head q/k RMSNorm + half-split rotary + paged cache write, one warp per
+// Per-head q/k RMSNorm + rotary + paged cache write, one warp per
 // (token, head) of the fused qkv row [q heads | k heads | v heads]
 // (crates/leone-cuda/cuda/ie_cuda.cu:2426-2484 does the same three things in one
-// launch; formulas crates/leone/src/cpu.rs:802-820 and 1747-1779).
+// launch; formulas crates/leone/src/cpu.rs:802-820 and 1747-1779).  Pair i of a head is
+// elements (i, i + rotary_dim/2), or with `adjacent` elements (2i, 2i + 1)
+// (crates/leone/src/backend.rs:1216-1222, crates/leone/src/cpu.rs:1767-1770).
 //  q heads: normed, rotated, written back in place.
 //  k heads: normed, rotated, written back in place and into the key page.
 //  v heads: copied into the value page.
@@ -170,7 +172,7 @@ __global__ void qk_norm_rope_write_kernel(
     const TW* __restrict__ k_w, float eps, const float2* __restrict__ rope, int rotary_dim,
     int max_positions, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
     const int* __restrict__ block_table, int table_width, int n_seqs, T* __restrict__ k_pool,
-    T* __restrict__ v_pool, int num_pages, int page_tokens, int* status) {
+    T* __restrict__ v_pool, int num_pages, int page_tokens, int adjacent, int* status) {
   extern __shared__ float smem[];
   pdl_trigger();
   pdl_wait();
@@ -225,10 +227,12 @@ __global__ void qk_norm_rope_write_kernel(
   for (int c = lane; c < d; c += 32) {
     float v = buf[c];
     if (rotate && c < rotary_dim) {
-      const int pair = c < half ? c : c - half;
+      // pair i of the head: elements (i, i + half), or (2i, 2i + 1) with adjacent pairing
+      const int pair = adjacent ? c >> 1 : (c < half ? c : c - half);
+      const bool first = adjacent ? (c & 1) == 0 : c < half;
       const float2 cs = rope[(size_t)pos * half + pair];
-      const float a = buf[pair], b = buf[pair + half];
-      v = c < half ? a * cs.x - b * cs.y : a * cs.y + b * cs.x;
+      const float a = buf[adjacent ? 2 * pair : pair], b = buf[adjacent ? 2 * pair + 1 : pair + half];
+      v = first ? a * cs.x - b * cs.y : a * cs.y + b * cs.x;
     }
     const T o = from_float<T>(v);
     if (is_q || is_k) row[c] = o;
@@ -248,7 +252,7 @@ qk_norm_rope_write_vec_kernel(
     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
     const int* __restrict__ block_table, int table_width, int n_seqs,
     __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool, int num_pages,
-    int page_tokens, int* status) {
+    int page_tokens, int adjacent, int* status) {
   // One block per token, a warp per head at a time: the token's position, page, rotation row
   // and the norm weights are fetched once per warp and serve all its heads, and the next
   // head's row is requested before the current one is worked on.
@@ -281,11 +285,12 @@ qk_norm_rope_write_vec_kernel(
   }
   const bool upper = lane >= 16;                   // elements of the second half
   const int pair0 = (lane & 15) * E;               // pair index of this lane's first element
-  float2 cs[E];
+  float2 cs[E];                                    // with adjacent pairing: of elements 2j, 2j + 1 in cs[j]
   float wq[E], wk[E];
 #pragma unroll
   for (int i = 0; i < E; ++i) {
-    cs[i] = rotate ? rope[(size_t)pos * (d / 2) + pair0 + i] : make_float2(1.f, 0.f);
+    const int pair = adjacent ? (lane * E) / 2 + (i >> 1) : pair0 + i;
+    cs[i] = rotate ? rope[(size_t)pos * (d / 2) + pair] : make_float2(1.f, 0.f);
     wq[i] = q_w != nullptr ? to_float<TW>(q_w[lane * E + i]) : 1.f;
     wk[i] = k_w != nullptr ? to_float<TW>(k_w[lane * E + i]) : 1.f;
   }
@@ -318,10 +323,19 @@ qk_norm_rope_write_vec_kernel(
       for (int i = 0; i < E; ++i) v[i] = v[i] * (is_q ? wq[i] : wk[i]) * inv;
     }
     if (rotate && (is_q || is_k)) {
+      if (adjacent) {                              // both elements of a pair are this lane's own
 #pragma unroll
-      for (int i = 0; i < E; ++i) {
-        const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
-        v[i] = upper ? other * cs[i].y + v[i] * cs[i].x : v[i] * cs[i].x - other * cs[i].y;
+        for (int i = 0; i < E; i += 2) {
+          const float a = v[i], b = v[i + 1];
+          v[i] = a * cs[i].x - b * cs[i].y;
+          v[i + 1] = a * cs[i].y + b * cs[i].x;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < E; ++i) {
+          const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
+          v[i] = upper ? other * cs[i].y + v[i] * cs[i].x : v[i] * cs[i].x - other * cs[i].y;
+        }
       }
     }
     __nv_bfloat162 o2[E / 2];
@@ -607,7 +621,7 @@ extern "C" int leone_qk_norm_rope_write(
     int dtype, void* qkv, int n_tokens, int n_q, int n_kv, int d, const void* q_w, const void* k_w,
     int w_dtype, float eps, const float* rope, int rotary_dim, int max_positions,
     const int* positions, const int* seq_of_token, const int* block_table, int table_width,
-    int n_seqs, void* k_pool, void* v_pool, int num_pages, int page_tokens, int* status,
+    int n_seqs, void* k_pool, void* v_pool, int num_pages, int page_tokens, int adjacent, int* status,
     cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (d <= 0 || d > 1024 || n_q <= 0 || n_kv <= 0) return kRefusedSize;
@@ -626,7 +640,7 @@ extern "C" int leone_qk_norm_rope_write(
                        (__nv_bfloat16*)qkv, n_tokens, n_q, n_kv, (const TW*)q_w, (const TW*)k_w, eps, \
                        (const float2*)rope, max_positions, positions, seq_of_token, block_table,  \
                        table_width, n_seqs, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool,        \
-                       num_pages, page_tokens, status)
+                       num_pages, page_tokens, adjacent, status)
     if (w_dtype == 0) {
       if (d == 64) LAUNCH_VEC(2, float);
       if (d == 128) LAUNCH_VEC(4, float);
@@ -643,7 +657,7 @@ extern "C" int leone_qk_norm_rope_write(
                        (T*)qkv, n_tokens, n_q, n_kv, d, (const TW*)q_w, (const TW*)k_w, eps,          \
                        (const float2*)rope, rotary_dim, max_positions, positions, seq_of_token,      \
                        block_table, table_width, n_seqs, (T*)k_pool, (T*)v_pool, num_pages,          \
-                       page_tokens, status)
+                       page_tokens, adjacent, status)
   if (dtype == 0 && w_dtype == 0) LAUNCH(float, float);
   if (dtype == 1 && w_dtype == 0) LAUNCH(__nv_bfloat16, float);
   if (dtype == 0 && w_dtype == 1) LAUNCH(float, __nv_bfloat16);

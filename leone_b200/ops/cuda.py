@@ -289,7 +289,10 @@ class CudaOps:
         return buf[:rows]
 
     def qk_norm_rope_write(self, ctx, qkv, n_q, n_kv, d, q_norm_w, k_norm_w, eps, table,
-                           rotary_dim, cache):
+                           rotary_dim, cache, pairing="half_split"):
+        """``pairing``: which elements of a head form rotation pair ``i``: ``(i, i + rotary_dim/2)``
+        ("half_split") or ``(2i, 2i + 1)`` ("adjacent")."""
+        _need(pairing in ("half_split", "adjacent"), f"rotary pairing '{pairing}'")
         n = qkv.shape[0]
         _need(qkv.is_contiguous() and qkv.shape[1] == (n_q + 2 * n_kv) * d, "qkv layout")
         w_dtype = 0
@@ -317,14 +320,14 @@ class CudaOps:
             _dt(qkv.dtype), _ptr(qkv), n, n_q, n_kv, d, _ptr(q_norm_w), _ptr(k_norm_w), w_dtype,
             c_float(eps), _ptr(table), rotary_dim, max_pos, _ptr(ctx.positions),
             _ptr(ctx.seq_of_token), pool_args[0], pool_args[1], pool_args[2], pool_args[3],
-            pool_args[4], pool_args[5], pool_args[6], _ptr(ctx.status), self._stream()),
-            "qk_norm_rope_write")
+            pool_args[4], pool_args[5], pool_args[6], 1 if pairing == "adjacent" else 0, _ptr(ctx.status),
+            self._stream()), "qk_norm_rope_write")
 
     def can_fuse_decode(self, ctx, qkv, n_q, n_kv, d) -> bool:
         """True if the attention kernel can do the q/k norm, rotation and cache write itself
         for this step (then ``qk_norm_rope_write`` is not called and ``attention`` gets
         ``fuse``: q_w, k_w (fp32 [d] or None), eps, rope ([positions, d/2, 2] fp32 or None),
-        write_cache)."""
+        write_cache, and optionally pairing ("half_split" or "adjacent"))."""
         return self.fast is not None and self.fast.decode_fusable(ctx, qkv.dtype, n_q, n_kv, d, qkv.stride(0))
 
     def attention(self, ctx, qkv, out, n_q, n_kv, d, scale, window, cache, fuse=None):

@@ -355,11 +355,12 @@ class FastKernels:
         if self.decode_in_clusters(n_seqs, n_kv, g, max_ctx):
             # the splits of a (sequence, KV head) merge inside a cluster; optionally the
             # kernel norms and rotates q and the new k and writes the cache itself
-            fz = (0, None, None, c_float(0.0), None, 0, 0)
+            fz = (0, None, None, c_float(0.0), None, 0, 0, 0)
             if fuse is not None:
                 rope = fuse["rope"]
                 fz = (1, _ptr(fuse["q_w"]), _ptr(fuse["k_w"]), c_float(fuse["eps"]), _ptr(rope),
-                      rope.shape[0] if rope is not None else 0, 1 if fuse["write_cache"] else 0)
+                      rope.shape[0] if rope is not None else 0, 1 if fuse["write_cache"] else 0,
+                      1 if fuse.get("pairing", "half_split") == "adjacent" else 0)
             code = self.lib.leone_attention_decode_cluster(
                 *common, n_q, n_kv, d, c_float(scale), int(window or 0), cache.page_tokens,
                 kp.shape[0], splits, *fz, _ptr(status), self._stream())

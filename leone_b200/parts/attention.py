@@ -114,8 +114,8 @@ class Attention(Mixer):
             table = self.pos.rotary_table()
             if table is not None:
                 rotary_dim, pairing = table.shape[1] * 2, self.pos.pairing
-                if pairing != "half_split":
-                    raise ValueError(f"attention kernels rotate half-split pairs, not '{pairing}'")
+                if pairing not in ("half_split", "adjacent"):
+                    raise ValueError(f"attention kernels rotate half-split or adjacent pairs, not '{pairing}'")
         attn = rt.buffer("attn_out", n, self.n_q * self.d, rt.dtype)
         # A decode step whose new key goes to this layer's own cache: the attention kernel may norm
         # and rotate q and the new k and write the cache itself.  (A layer that reads another
@@ -125,7 +125,7 @@ class Attention(Mixer):
                 rt.ops.can_fuse_decode(ctx, qkv, self.n_q, self.n_kv, self.d):
             rt.ops.attention(ctx, qkv, attn, self.n_q, self.n_kv, self.d, self.scale, self.window, cache,
                              fuse=dict(q_w=self.q_norm_f32, k_w=self.k_norm_f32, eps=self.eps, rope=table,
-                                       write_cache=True))
+                                       write_cache=True, pairing=pairing or "half_split"))
             self._out_proj(attn, hidden, then)
             return
         # q/k norm, rotation and the cache write are one kernel; an encoding without a
@@ -139,9 +139,10 @@ class Attention(Mixer):
             rt.ops.qk_norm_rope_write(ctx, qkv, self.n_q, self.n_kv, self.d, None, None,
                                       self.eps, None, 0, cache if cache.writes else None)
         else:
+            extra = {} if pairing in (None, "half_split") else dict(pairing=pairing)
             rt.ops.qk_norm_rope_write(ctx, qkv, self.n_q, self.n_kv, self.d, self.q_norm_w,
                                       self.k_norm_w, self.eps, table, rotary_dim,
-                                      cache if cache.writes else None)
+                                      cache if cache.writes else None, **extra)
         rt.ops.attention(ctx, qkv, attn, self.n_q, self.n_kv, self.d, self.scale,
                          self.window, cache)
         self._out_proj(attn, hidden, then)

@@ -1,6 +1,8 @@
-"""Rotary position encoding with half-split pairing.
+"""Rotary position encoding, with half-split or adjacent pairing.
 
-Pair ``i`` of a head is elements ``(i, i + rotary_dim/2)``; its angle at
+Pair ``i`` of a head is elements ``(i, i + rotary_dim/2)`` (half-split) or
+``(2i, 2i + 1)`` (adjacent; crates/leone/src/backend.rs:1216-1222,
+crates/leone/src/cpu.rs:1767-1770); its angle at
 position ``p`` is ``p * theta^(-2i/rotary_dim)``, inverse frequency and angle
 in float64 (crates/leone/src/cpu.rs:1735-1745 and 1747-1779); the rotation is
 ``x'_i = x_i cos - x_j sin``, ``x'_j = x_i sin + x_j cos``.  The reference's
@@ -44,3 +46,10 @@ class RotaryHalfSplit(PositionEncoding):
             self._table = build_rotary_table(
                 self.max_positions, self.rotary_dim, self.theta).to(self.rt.device)
         return self._table
+
+
+@POSITION_ENCODINGS.register("rotary_adjacent")
+class RotaryAdjacent(RotaryHalfSplit):
+    """The same angles with pair ``i`` made of elements ``(2i, 2i + 1)``: the table is the same,
+    the kernels are told which elements belong together."""
+    pairing = "adjacent"

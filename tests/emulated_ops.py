@@ -59,7 +59,7 @@ class EmulatedOps:
         out.copy_((g / (1.0 + torch.exp(-g)) * u).to(out.dtype))
 
     def qk_norm_rope_write(self, ctx, qkv, n_q, n_kv, d, q_norm_w, k_norm_w, eps, table,
-                           rotary_dim, cache):
+                           rotary_dim, cache, pairing="half_split"):
         n = qkv.shape[0]
         x = qkv.float().view(n, n_q + 2 * n_kv, d)
         q, k, v = x[:, :n_q], x[:, n_q:n_q + n_kv], x[:, n_q + n_kv:]
@@ -76,8 +76,13 @@ class EmulatedOps:
             half = rotary_dim // 2
             cs = table[ctx.positions.long()]          # [n, half, 2]
             cos, sin = cs[..., 0][:, None, :], cs[..., 1][:, None, :]
-            a, b = t[..., :half], t[..., half:rotary_dim]
             out = t.clone()
+            if pairing == "adjacent":
+                a, b = t[..., 0:rotary_dim:2], t[..., 1:rotary_dim:2]
+                out[..., 0:rotary_dim:2] = a * cos - b * sin
+                out[..., 1:rotary_dim:2] = a * sin + b * cos
+                return out
+            a, b = t[..., :half], t[..., half:rotary_dim]
             out[..., :half] = a * cos - b * sin
             out[..., half:rotary_dim] = a * sin + b * cos
             return out

@@ -90,6 +90,22 @@ def rope_half_split(x, positions, theta, rotary_dim=None):
     return out
 
 
+def rope_adjacent(x, positions, theta, rotary_dim=None):
+    """Adjacent-pair rotary: pair i = (2i, 2i+1), the same angles as the half-split form
+    (crates/leone/src/backend.rs:1216-1222, crates/leone/src/cpu.rs:1767-1770).  ``x``: [T, heads, d]."""
+    d = x.shape[-1]
+    rd = d if rotary_dim is None else rotary_dim
+    out = x.clone()
+    for t, p in enumerate(positions):
+        for i in range(rd // 2):
+            ang = float(p) * float(theta) ** (-2.0 * i / rd)
+            c, s_ = math.cos(ang), math.sin(ang)
+            a, b = x[t, :, 2 * i], x[t, :, 2 * i + 1]
+            out[t, :, 2 * i] = a * c - b * s_
+            out[t, :, 2 * i + 1] = a * s_ + b * c
+    return out
+
+
 def attention(q, k, v, positions, scale=None, window=None):
     """Causal grouped-query attention, one query row at a time.
 
@@ -131,8 +147,11 @@ def attention_layer(x, w, prefix, cfg, positions, window=None):
     v = linear(x, w[prefix + "self_attn.v_proj.weight"]).reshape(t_len, n_kv, d)
     q = rms_norm(q, w[prefix + "self_attn.q_norm.weight"], cfg["rms_norm_eps"])
     k = rms_norm(k, w[prefix + "self_attn.k_norm.weight"], cfg["rms_norm_eps"])
-    q = rope_half_split(q, positions, cfg["rope_theta"])
-    k = rope_half_split(k, positions, cfg["rope_theta"])
+    # "rope_pairing" is no key of the architecture's config.json: tests of the adjacent-pair
+    # position encoding put it into the dictionary they hand to this implementation
+    rope = rope_adjacent if cfg.get("rope_pairing", "half_split") == "adjacent" else rope_half_split
+    q = rope(q, positions, cfg["rope_theta"])
+    k = rope(k, positions, cfg["rope_theta"])
     a = attention(q, k, v, positions, window=window)
     return linear(a.reshape(t_len, n_q * d), w[prefix + "self_attn.o_proj.weight"])
 

@@ -484,8 +484,8 @@ def _rope_table(max_pos, rd, theta):
     return build_rotary_table(max_pos, rd, theta).to(DEV)
 
 
-def _ref_norm_rope(x, w, eps, positions, theta, rd):
-    """x [n, heads, d] float64."""
+def _ref_norm_rope(x, w, eps, positions, theta, rd, adjacent=False):
+    """x [n, heads, d] float64.  Pair i: elements (i, i + rd/2), or (2i, 2i + 1) if adjacent."""
     if w is not None:
         x = x * w.double() / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
     half = rd // 2
@@ -493,6 +493,11 @@ def _ref_norm_rope(x, w, eps, positions, theta, rd):
     ang = torch.tensor(positions, dtype=torch.float64, device=x.device)[:, None] * inv[None]
     cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
     out = x.clone()
+    if adjacent:
+        a, b = x[..., 0:rd:2], x[..., 1:rd:2]
+        out[..., 0:rd:2] = a * cos - b * sin
+        out[..., 1:rd:2] = a * sin + b * cos
+        return out
     a, b = x[..., :half], x[..., half:rd]
     out[..., :half] = a * cos - b * sin
     out[..., half:rd] = a * sin + b * cos
@@ -503,7 +508,8 @@ def _ref_norm_rope(x, w, eps, positions, theta, rd):
 @pytest.mark.parametrize("n_q,n_kv,d,pt,theta,eps", [(5, 1, 48, 16, 5e4, 3e-6), (6, 3, 32, 8, 1e6, 1e-5),
                                                      (8, 2, 128, 16, 1e6, 1e-6), (3, 3, 80, 4, 1e4, 1e-6),
                                                      (4, 2, 64, 16, 1e4, 1e-6), (2, 1, 256, 8, 1e6, 1e-5)])
-def test_qk_norm_rope_write(ops32, dtype, n_q, n_kv, d, pt, theta, eps):
+@pytest.mark.parametrize("pairing", ["half_split", "adjacent"])
+def test_qk_norm_rope_write(ops32, dtype, n_q, n_kv, d, pt, theta, eps, pairing):
     seq_lens = [11, 3, 25]
     starts = [4, 0, 20]                      # tokens of this step: positions start..len-1
     positions, seqs = [], []
@@ -519,11 +525,11 @@ def test_qk_norm_rope_write(ops32, dtype, n_q, n_kv, d, pt, theta, eps):
     orig = qkv.clone()
     cache = types.SimpleNamespace(k_pool=k_pool, v_pool=v_pool, block_table=table, page_tokens=pt)
     ctx = _ctx(positions, seqs)
-    ops32.qk_norm_rope_write(ctx, qkv, n_q, n_kv, d, qw, kw, eps, rope, d, cache)
+    ops32.qk_norm_rope_write(ctx, qkv, n_q, n_kv, d, qw, kw, eps, rope, d, cache, pairing=pairing)
     assert ctx.status[0].item() == 0
     x = orig.double().view(n, n_q + 2 * n_kv, d)
-    q_ref = _ref_norm_rope(x[:, :n_q], qw, eps, positions, theta, d)
-    k_ref = _ref_norm_rope(x[:, n_q:n_q + n_kv], kw, eps, positions, theta, d)
+    q_ref = _ref_norm_rope(x[:, :n_q], qw, eps, positions, theta, d, pairing == "adjacent")
+    k_ref = _ref_norm_rope(x[:, n_q:n_q + n_kv], kw, eps, positions, theta, d, pairing == "adjacent")
     got = qkv.view(n, n_q + 2 * n_kv, d)
     rt, at = (5e-6, 5e-6) if dtype == torch.float32 else (2 ** -7, 1e-5)
     _close(got[:, :n_q], q_ref, rt * 4, at, "q")
@@ -769,8 +775,10 @@ def test_attention_decode_long_contexts(ops16, seq_lens):
 @pytest.mark.parametrize("n_q,n_kv,d,pt,window,qk_norm,rotary", [
     (8, 2, 128, 16, None, True, True), (6, 3, 64, 8, None, True, True), (5, 1, 64, 16, 40, False, True),
     (40, 2, 128, 16, None, True, False), (4, 4, 128, 4, 300, True, True)])
-@pytest.mark.parametrize("seq_lens", [[300, 1, 64, 65, 17], [2100], [1, 2]])
-def test_attention_decode_fused_norm_rope_write(ops16, n_q, n_kv, d, pt, window, qk_norm, rotary, seq_lens):
+@pytest.mark.parametrize("seq_lens,pairing", [([300, 1, 64, 65, 17], "half_split"), ([2100], "half_split"),
+                                              ([1, 2], "half_split"), ([300, 1, 64, 65, 17], "adjacent"),
+                                              ([2100], "adjacent")])
+def test_attention_decode_fused_norm_rope_write(ops16, n_q, n_kv, d, pt, window, qk_norm, rotary, seq_lens, pairing):
     """The decode kernel doing q/k norm, rotation and cache write itself against the two-kernel
     path on the same raw projections: the same cache bit for bit, the same outputs."""
     dtype = torch.bfloat16
@@ -790,7 +798,8 @@ def test_attention_decode_fused_norm_rope_write(ops16, n_q, n_kv, d, pt, window,
     # two kernels
     qkv_a, k_a, v_a = raw.clone(), k_pool.clone(), v_pool.clone()
     cache_a = types.SimpleNamespace(k_pool=k_a, v_pool=v_a, block_table=table, page_tokens=pt)
-    ops16.qk_norm_rope_write(ctx, qkv_a, n_q, n_kv, d, qw, kw, 1e-6, rope, d if rotary else 0, cache_a)
+    ops16.qk_norm_rope_write(ctx, qkv_a, n_q, n_kv, d, qw, kw, 1e-6, rope, d if rotary else 0, cache_a,
+                             pairing=pairing)
     out_a = torch.empty((n, n_q * d), device=DEV, dtype=dtype)
     ops16.attention(ctx, qkv_a, out_a, n_q, n_kv, d, scale, window, cache_a)
     # one kernel
@@ -799,7 +808,7 @@ def test_attention_decode_fused_norm_rope_write(ops16, n_q, n_kv, d, pt, window,
     out_b = torch.full_like(out_a, 7.0)
     assert ops16.can_fuse_decode(ctx, qkv_b, n_q, n_kv, d)
     ops16.attention(ctx, qkv_b, out_b, n_q, n_kv, d, scale, window, cache_b,
-                    fuse=dict(q_w=qw, k_w=kw, eps=1e-6, rope=rope, write_cache=True))
+                    fuse=dict(q_w=qw, k_w=kw, eps=1e-6, rope=rope, write_cache=True, pairing=pairing))
     torch.cuda.synchronize()
     assert ctx.status[0].item() == 0
     assert torch.equal(k_a, k_b) and torch.equal(v_a, v_b), "the cache differs"
@@ -809,7 +818,7 @@ def test_attention_decode_fused_norm_rope_write(ops16, n_q, n_kv, d, pt, window,
     cache_c = types.SimpleNamespace(k_pool=k_c, v_pool=v_c, block_table=table, page_tokens=pt)
     out_c = torch.empty_like(out_a)
     ops16.attention(ctx, raw.clone(), out_c, n_q, n_kv, d, scale, window, cache_c,
-                    fuse=dict(q_w=qw, k_w=kw, eps=1e-6, rope=rope, write_cache=False))
+                    fuse=dict(q_w=qw, k_w=kw, eps=1e-6, rope=rope, write_cache=False, pairing=pairing))
     torch.cuda.synchronize()
     assert torch.equal(k_c, k_pool) and torch.equal(v_c, v_pool)
     assert torch.equal(out_c, out_a)
@@ -820,7 +829,7 @@ def test_attention_decode_cluster_refuses_what_it_cannot_do(ops16):
     lib = ops16.fast.lib
     z = c_void_p(0)
     args = lambda d, splits, fuse: (z, 1024, z, 1024, z, z, z, 4, z, z, 2, 8, 2, d, c_float(1.0), 0, 16, 8,
-                                    splits, fuse, z, z, c_float(1e-6), z, 0, 0, z, z)
+                                    splits, fuse, z, z, c_float(1e-6), z, 0, 0, 0, z, z)
     assert lib.leone_attention_decode_cluster(*args(128, 9, 0)) != 0        # more splits than a cluster holds
     assert lib.leone_attention_decode_cluster(*args(96, 2, 1)) != 0         # fused preparation needs d 64 or 128
 

@@ -211,3 +211,60 @@ def test_no_step_is_launched_ahead_when_a_mixer_keeps_state(toy):
     assert results[0][0] == results[1][0]
     assert all(torch.equal(a, b) for a, b in zip(results[0][1], results[1][1]))
     assert torch.equal(results[0][2], results[1][2])
+
+
+# -- the adjacent-pair rotary encoding in a whole model ------------------------------------------
+def _adjacent_case(which):
+    """A tiny configuration's own spec with its position encoding swapped for the adjacent-pair
+    one, its random tensors, and the plain implementation told the same."""
+    import dataclasses
+    from leone_b200.parts.spec import PartSpec
+    from tests import tiny
+    from tests.plain import model as plain
+    cfg = tiny.tiny_config(which)
+    spec = spec_from_config(cfg)
+    rope = spec.position_encodings["rope"]
+    spec = dataclasses.replace(spec, position_encodings={"rope": PartSpec("rotary_adjacent", dict(rope.params))})
+    tensors = random_tensors(Model(spec, Runtime("cpu", torch.float32, None, 0)).weight_specs(), 29)
+    for name in tensors:
+        if tensors[name].dim() == 2:
+            tensors[name] = tensors[name] * 3
+    plain_cfg = dict(tiny.CONFIGS[which], rope_pairing="adjacent")
+    return spec, tensors, plain_cfg, plain
+
+
+def _adjacent_check(which, device, ops, dtype, tol):
+    spec, tensors, plain_cfg, plain = _adjacent_case(which)
+    vocab = plain_cfg["vocab_size"]
+    reqs = {"a": replay.random_tokens(vocab, 70, 1), "b": replay.random_tokens(vocab, 41, 2)}
+    w = tensors if dtype == "float32" else {k: (v.to(torch.bfloat16).float() if v.dim() == 2 else v)
+                                           for k, v in tensors.items()}
+    want = {r: plain.forward_logits(plain_cfg, {k: v.double() for k, v in w.items()}, t) for r, t in reqs.items()}
+    half = {r: plain.forward_logits(dict(plain_cfg, rope_pairing="half_split"),
+                                    {k: v.double() for k, v in w.items()}, t) for r, t in reqs.items()}
+    assert float((want["a"] - half["a"]).abs().max()) > 0.05 * float(want["a"].abs().max()), \
+        "the two pairings must give different logits for the test to mean anything"
+
+    class Plain:
+        def logits(self, tokens):
+            return want[[r for r, t in reqs.items() if t == list(tokens)][0]]
+
+    for name, steps in (("tail", replay.trace_decode_tail(reqs, tail=24)), ("portions", replay.trace_portions(reqs)),
+                        ("mixed", replay.trace_mixed(reqs, seed=4, max_live=2))):
+        eng = Engine(spec, dict(tensors), dtype=dtype, device=device, ops=ops() if ops else None,
+                     page_tokens=8, max_tokens=replay.max_live_tokens(steps), max_requests=2, max_batch_tokens=96)
+        out = replay.run_trace_engine(eng, steps)
+        replay.compare(steps, out, Plain(), reqs, what=f"adjacent rotary {which} {name} {dtype}", **tol)
+
+
+def test_adjacent_pair_rotary_on_stand_in_kernels():
+    from tests.emulated_ops import EmulatedOps
+    _adjacent_check("C", "cpu", EmulatedOps, "float32", dict(rtol=1e-5, atol_scale=1e-5))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("which", ["C", "D"])            # head size 48: the any-size kernels; 64: the fused ones
+@pytest.mark.parametrize("dtype,tol", [("float32", dict(rtol=2e-5, atol_scale=2e-5)),
+                                       ("bfloat16", dict(rtol=3e-2, atol_scale=3e-2))])
+def test_adjacent_pair_rotary_on_the_gpu(which, dtype, tol):
+    _adjacent_check(which, "cuda:0", None, dtype, tol)
