@@ -272,20 +272,25 @@ class FastKernels:
     def decode_splits(self, n_seqs: int, n_kv: int, g: int, max_ctx: int) -> int:
         """Splits of the key range.  Two blocks fit an SM; the cost of a choice is its number of
         rounds over those slots times the share of the keys a block walks, plus a little per
-        split for the merge, plus a fixed charge when the splits cannot merge inside clusters
+        split for the merge (since the partial results are pushed into the finishing block the
+        merge costs next to nothing: batch 1 at 2,048 keys 9.7 / 9.1 / 8.6 us for six / seven /
+        eight splits, at 16,384 keys 50 / 39 us for six / eight), plus a fixed charge when the
+        splits cannot merge inside clusters
         (scratch, a merge kernel and the q/k preparation in a kernel of its own: a fixed part,
-        measured at batch 64: one split 101 us, two to four 109-112; and a tenth of the walk,
-        measured at batches 160 to 224: one fused split 242 / 289 / 326 us, three to six splits
-        250 / 309 / 366).  A split keeps at least 128 keys."""
+        measured at batch 64: one split 101 us, two to four 109-112, and at batch 20: one fused
+        split 50.0 us, seven splits 52.1; and a fifth of the walk, measured at batches 160 to 224:
+        one fused split 242 / 289 / 326 us, three to six splits 250 / 309 / 366; at batch 48
+        three splits are still the better choice, 91 us against 97).  A split keeps at least 128
+        keys."""
         if self.force_decode_splits:
             return self.force_decode_splits
         blocks = n_seqs * n_kv * (-(-g // 16))
         slots = 2 * self.sm_count
         best, best_cost = 1, None
         for s in range(1, min(32, max(1, max_ctx // 128)) + 1):
-            clustered = self.use_clusters and s <= 8 and blocks * s <= slots * self.decode_cluster_rounds
+            clustered = self.use_clusters and s <= 8 and blocks * s <= self._decode_cluster_slots()
             walk = -(-(blocks * s) // slots) / s
-            cost = walk + 0.03 * s + (0.0 if s == 1 or clustered else 0.2 + 0.1 * walk)
+            cost = walk + 0.01 * s + (0.0 if s == 1 or clustered else 0.3 + 0.2 * walk)
             if best_cost is None or cost < best_cost - 1e-9:
                 best, best_cost = s, cost
         return best
@@ -309,8 +314,15 @@ class FastKernels:
         and a merge kernel."""
         splits = self.decode_splits(n_seqs, n_kv, g, max_ctx)
         blocks = n_seqs * n_kv * (-(-g // 16)) * splits
-        return self.use_clusters and (splits == 1 or (splits <= 8 and
-                                                      blocks <= 2 * self.sm_count * self.decode_cluster_rounds))
+        return self.use_clusters and (splits == 1 or (splits <= 8 and blocks <= self._decode_cluster_slots()))
+
+    def _decode_cluster_slots(self) -> int:
+        """Blocks of the decode attention that clusters may count on at once: nine tenths of the
+        two per SM (a cluster needs its blocks' slots in one GPC, and the GPCs are not all the same
+        size: 96 clusters of three, 288 of 296 slots, measured 42.7 us at batch 12 where 96
+        clusters of two take 33.9 us; 64 clusters of four, 256 slots, are the best choice at
+        batch 8)."""
+        return 2 * self.sm_count * 9 // 10 * self.decode_cluster_rounds
 
     def leading_decode_rows(self, ctx) -> int:
         """In a mixed step, how many sequences at the front of the batch bring a single token
