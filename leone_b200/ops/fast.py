@@ -280,17 +280,23 @@ class FastKernels:
         measured at batch 64: one split 101 us, two to four 109-112, and at batch 20: one fused
         split 50.0 us, seven splits 52.1; and a fifth of the walk, measured at batches 160 to 224:
         one fused split 242 / 289 / 326 us, three to six splits 250 / 309 / 366; at batch 48
-        three splits are still the better choice, 91 us against 97).  A split keeps at least 128
+        three splits are still the better choice, 91 us against 97).  The fixed parts were
+        measured at 2,048 keys and are so many microseconds whatever the context, so in units of
+        a walk they shrink as the context grows: at batch 1 sixteen to thirty-two unclustered
+        splits beat eight clustered ones from 16,384 keys on (33 against 40 us; at 32,768 keys 46
+        against 75), at 8,192 keys they do not (24.5 against 22.4).  A split keeps at least 128
         keys."""
         if self.force_decode_splits:
             return self.force_decode_splits
         blocks = n_seqs * n_kv * (-(-g // 16))
         slots = 2 * self.sm_count
         best, best_cost = 1, None
+        fixed = 2048.0 / max(max_ctx, 128)        # the charges that do not grow with the keys, in walks
         for s in range(1, min(32, max(1, max_ctx // 128)) + 1):
             clustered = self.use_clusters and s <= 8 and blocks * s <= self._decode_cluster_slots()
             walk = -(-(blocks * s) // slots) / s
-            cost = walk + 0.01 * s + (0.0 if s == 1 or clustered else 0.3 + 0.2 * walk)
+            cost = walk + fixed * (0.01 * s + (0.0 if s == 1 or clustered else 0.3)) + \
+                (0.0 if s == 1 or clustered else 0.2 * walk)
             if best_cost is None or cost < best_cost - 1e-9:
                 best, best_cost = s, cost
         return best

@@ -97,6 +97,7 @@ def test_a_captured_graph_survives_growth_of_the_scratch_buffers(folders):
     eng = _engine(folders["C"], "C", "bfloat16", 200)
     eng.ops.fast.min_scratch_floats = 1            # every growth reallocates
     eng.ops.fast.use_clusters = False              # the paths that keep partial results in scratch
+    eng.ops.fast.force_decode_splits = 3           # ... whatever the dispatcher would choose here
     small = [replay.random_tokens(331, n, 90 + n) for n in (150, 140)]
     large = [replay.random_tokens(331, 150, 200 + i) for i in range(4)]
     first = generate(eng, small, 6, eos_token_id=-1)
