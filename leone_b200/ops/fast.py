@@ -284,8 +284,10 @@ class FastKernels:
         measured at 2,048 keys and are so many microseconds whatever the context, so in units of
         a walk they shrink as the context grows: at batch 1 sixteen to thirty-two unclustered
         splits beat eight clustered ones from 16,384 keys on (33 against 40 us; at 32,768 keys 46
-        against 75), at 8,192 keys they do not (24.5 against 22.4).  A split keeps at least 128
-        keys."""
+        against 75), at 8,192 keys they do not (24.5 against 22.4); the share of the walk shrinks
+        too, with the root of that factor (a short block's own start and end are what it stands
+        for: batch 16 at 32,768 keys, nine unclustered splits 351 us against 378 for two
+        clustered ones).  A split keeps at least 128 keys."""
         if self.force_decode_splits:
             return self.force_decode_splits
         blocks = n_seqs * n_kv * (-(-g // 16))
@@ -296,7 +298,7 @@ class FastKernels:
             clustered = self.use_clusters and s <= 8 and blocks * s <= self._decode_cluster_slots()
             walk = -(-(blocks * s) // slots) / s
             cost = walk + fixed * (0.01 * s + (0.0 if s == 1 or clustered else 0.3)) + \
-                (0.0 if s == 1 or clustered else 0.2 * walk)
+                (0.0 if s == 1 or clustered else 0.2 * fixed ** 0.5 * walk)
             if best_cost is None or cost < best_cost - 1e-9:
                 best, best_cost = s, cost
         return best
