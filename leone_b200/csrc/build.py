@@ -30,7 +30,7 @@ MODULES: Dict[str, List[str]] = {
     # every run needs these: both dtypes, every size
     "core": ["elementwise.cu", "gemm_simt.cu", "attention_generic.cu", "sampling_pipeline.cu", "random_weights.cu"],
     # the bfloat16 serving path: tensor-core products and tiled attention
-    "bf16": ["gemm_tc.cu", "attention_tiled.cu", "attention_prefill_pingpong.cu"],
+    "bf16": ["gemm_tc.cu", "gemm_pair.cu", "attention_tiled.cu", "attention_prefill_pingpong.cu"],
     # the entry point that allocates nothing (leone_static.h); it compiles attention_tiled.cu in
     "static": ["attention_decode_static.cu"],
     # the host side of the runtime (pages, block tables, step metadata, the scheduler's decisions,
@@ -38,7 +38,7 @@ MODULES: Dict[str, List[str]] = {
     "host": ["host_runtime.cpp", "random_weights_host.cpp"],
 }
 HOST_ONLY = {"host"}
-HEADERS = ["common.cuh", "tc_common.cuh", "leone_static.h", "attention_tiled.cu", "random_draw.h"]
+HEADERS = ["common.cuh", "tc_common.cuh", "gemm_parts.cuh", "leone_static.h", "attention_tiled.cu", "random_draw.h"]
 
 # -fno-gnu-unique: statics inside inline functions and templates (the once-per-kernel set-up
 # flags, the launch mode switch) must belong to one library image each; with GNU unique

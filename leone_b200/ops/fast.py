@@ -48,6 +48,9 @@ class FastKernels:
         # LEONE_NO_FUSED_DECODE=1 keeps q/k norm, rotation and cache write in their own kernel
         self.fuse_decode = os.environ.get("LEONE_NO_FUSED_DECODE", "0") != "1"
         self.max_cluster = 8               # the portable cluster size
+        # LEONE_NO_PAIRS=1 keeps prompt-sized products on single SMs (cta_group::1)
+        self.use_pairs = os.environ.get("LEONE_NO_PAIRS", "0") != "1"
+        self.pair_tile_cost = 0.9          # a pair's half tile against a single block's tile (measured 0.86 to 0.89)
         self.decode_cluster_rounds = 1     # rounds of blocks a clustered decode attention may take (kernel_bench sets it)
         # (n, k) -> (splits, cluster): a forced split of an [n x k] product at decode sizes; empty
         # in the product, filled by kernel_bench's sweeps
@@ -153,6 +156,14 @@ class FastKernels:
         tiles = int(self.lib.leone_gemm_tc_tiles_token_major(m, n))
         return self.token_major_fill * self.sm_count <= tiles <= 2 * self.sm_count
 
+    def in_pairs(self, m: int) -> bool:
+        """Whether an unsplit product of ``m`` tokens runs on pairs of SMs.  A pair's tile is 256
+        tokens and measured 0.87 of the time of two single tiles of 128; with the last tile half
+        empty (320, 384, 640 tokens) the single-block kernel's fewer tiles win."""
+        if not self.use_pairs or m <= 256:
+            return False
+        return 2 * -(-m // 256) * self.pair_tile_cost <= -(-m // 128)
+
     def token_major_split(self, m: int, n: int, k: int) -> int:
         """Splits along K of the token-major form, summed inside thread-block clusters (1: none).
         A product whose token-major tiles fill at most half of the SMs (the narrow products of a
@@ -221,6 +232,16 @@ class FastKernels:
         no = (None, None, None, 0) if norm_out is None else \
             (_ptr(norm_out[0]), _ptr(norm_out[1]), _ptr(norm_out[2]), norm_out[0].stride(0))
         ni = (None, 0, c_float(0.0)) if norm_in is None else (_ptr(norm_in[0]), int(norm_in[1]), c_float(norm_in[2]))
+        if splits == 1 and not cluster and self.in_pairs(m):
+            # prompt-sized: pairs of SMs on tiles of 256 tokens (gemm_pair.cu), the same tile width
+            # as the single-block kernel would take (the norm's parts are sized for it)
+            width = int(self.lib.leone_gemm_tc_token_major_width(m, n_rows, 1 if epilogue == 3 else 0))
+            code = self.lib.leone_gemm_pair(_ptr(x), _ptr(w), _ptr(out), _ptr(residual), m, n_rows, k,
+                                            x.stride(0), w.stride(0), out.stride(0), epilogue, width,
+                                            _ptr(self.status), self.sm_count, *no, *ni, self._stream())
+            if code != 0:
+                raise RuntimeError(f"gemm_pair refused or failed with code {code} for m={m} n={n_rows} k={k}")
+            return True
         code = self.lib.leone_gemm_tc(_ptr(x), _ptr(w), _ptr(out), _ptr(residual), m, n_rows, k,
                                       x.stride(0), w.stride(0), out.stride(0), epilogue, splits,
                                       full_tiles, _ptr(ws), _ptr(ct), _ptr(self.status), self.sm_count,

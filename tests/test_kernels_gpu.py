@@ -297,6 +297,73 @@ def test_gemm_tc_prompt_sized_tiles_of_240_weight_rows(ops16):
     _close(out2, (xn.double() @ w2.double().t()) * rs, 2 ** -8, 1e-3, "the product after, parts of 240")
 
 
+@pytest.mark.parametrize("m,n,k", [(257, 264, 64), (300, 520, 512), (513, 1000, 200), (640, 4096, 1024),
+                                   (1000, 1024, 264), (2048, 240 * 5 - 24, 4096)])
+def test_gemm_pair_on_two_sms(ops16, m, n, k):
+    """Prompt-sized products on pairs of SMs (one MMA of 256 tokens over both blocks' shared
+    memory), forced for every size above 256 tokens: ragged last pairs (a second block with no
+    token at all), ragged weight tiles, K that is no multiple of the k-block; every epilogue and
+    the folded norm on both sides against float64, and the same bits on every run."""
+    fast = ops16.fast
+    assert fast.use_pairs
+    saved = fast.pair_tile_cost
+    fast.pair_tile_cost = 0.0
+    try:
+        assert fast.in_pairs(m)
+        x = _randn((m, k), 81, torch.bfloat16)
+        w = _randn((n, k), 82, torch.bfloat16, scale=0.05)
+        want = x.double() @ w.double().t()
+        atol32 = 2e-6 * math.sqrt(k) * 4
+        out = torch.full((m, n), 9.0, device=DEV, dtype=torch.bfloat16)
+        fast._gemm(x, w, out, 0, None, n)
+        _close(out, want, 2 ** -8, atol32, f"pair bf16 out m{m} n{n} k{k}")
+        out32 = torch.full((m, n), 9.0, device=DEV)
+        fast._gemm(x, w, out32, 1, None, n)
+        _close(out32, want, 1e-5, atol32, "pair fp32 out")
+        res = _randn((m, n), 83)
+        g = 1 + 0.2 * _randn((n,), 84)
+        hidden = res.clone()
+        parts = fast.norm_parts(m, n)
+        xn = torch.full((m, n), 7.0, device=DEV, dtype=torch.bfloat16)
+        ss = torch.full((parts, m), -1.0, device=DEV)
+        fast._gemm(x, w, hidden, 2, hidden, n, norm_out=(xn, g, ss))
+        _close(hidden, want + res.double(), 1e-5, atol32, "pair residual in place")
+        h64 = hidden.double()
+        _close(xn, h64 * g.double(), 2 ** -8, 1e-6, "pair bf16(out * weight)")
+        _close(ss.sum(0), (h64 * h64).sum(1), 1e-5, 1e-6, "pair sums of squares")
+        again, xn2, ss2 = res.clone(), torch.empty_like(xn), torch.empty_like(ss)
+        fast._gemm(x, w, again, 2, again, n, norm_out=(xn2, g, ss2))
+        assert torch.equal(hidden, again) and torch.equal(xn, xn2) and torch.equal(ss, ss2)
+        n2, inter = 328, 160
+        w2 = _randn((n2, n), 85, torch.bfloat16, scale=0.05)
+        rs = torch.rsqrt((h64 * h64).mean(dim=1, keepdim=True) + 1e-5)
+        out2 = torch.empty((m, n2), device=DEV, dtype=torch.bfloat16)
+        fast._gemm(xn, w2, out2, 0, None, n2, norm_in=(ss, parts, 1e-5))
+        _close(out2, (xn.double() @ w2.double().t()) * rs, 2 ** -8, 1e-3, "pair, the product after the norm")
+        gate, up = w2[:inter].contiguous(), w2[inter:2 * inter].contiguous()
+        gu = ops16.prepare_gate_up(gate, up)
+        act = torch.full((m, inter), 9.0, device=DEV, dtype=torch.bfloat16)
+        fast._gemm(xn, gu.weight, act, 3, None, 2 * inter, norm_in=(ss, parts, 1e-5))
+        gg = (xn.double() @ gate.double().t()) * rs
+        uu = (xn.double() @ up.double().t()) * rs
+        _close(act, gg / (1 + torch.exp(-gg)) * uu, 2 ** -7, 1e-3, "pair swiglu after the norm")
+        # the single-block kernel on the same inputs: the same sums in the same order
+        fast.use_pairs = False
+        single = torch.empty_like(out32)
+        fast._gemm(x, w, single, 1, None, n)
+        assert torch.equal(single, out32)
+        torch.cuda.synchronize()
+        assert int(fast.status.abs().sum()) == 0
+    finally:
+        fast.pair_tile_cost, fast.use_pairs = saved, True
+
+
+def test_the_dispatcher_takes_pairs_where_their_tiles_are_full(ops16):
+    fast = ops16.fast
+    assert not fast.in_pairs(256) and not fast.in_pairs(320) and not fast.in_pairs(640)
+    assert fast.in_pairs(512) and fast.in_pairs(1000) and fast.in_pairs(2048) and fast.in_pairs(8192 + 1)
+
+
 def test_the_dispatcher_picks_the_token_major_form_only_where_its_tiles_fill_the_device(ops16):
     fast = ops16.fast
     sms = fast.sm_count
