@@ -82,6 +82,11 @@ __device__ __forceinline__ Unit unit_of(int u, const GemmParams& p) {
   return Unit{p.full_tiles + r / p.splits, r % p.splits, p.splits};
 }
 
+// SwiGLU of a gate and an up value for a bf16 result: g / (1 + e^-g) * u with the fast exponential
+// and division (a few units in the last place of fp32, far below the rounding to bf16; e^-g = inf
+// gives g * 0).
+__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
+
 // Swapped orientation: the thread that owns weight row n finishes NC token columns
 // m0 + c .. m0 + c + NC - 1 whose sums are in v (r: the residual values, fetched by the caller
 // before anything is stored, because the residual may be the output itself).
@@ -95,16 +100,19 @@ __device__ __forceinline__ void finish_swapped(const GemmParams& p, float (&v)[N
     for (int j = 0; j < NC; ++j) v[j] *= rs_s[c + j];
   }
   if (p.epilogue == 3) {
-    // rows come in groups of 32: 16 gate rows then their 16 up rows
+    // rows come in groups of 32: 16 gate rows (lanes 0-15) then their 16 up rows (lanes 16-31).
+    // The halves of the warp swap one value per pair of token columns, so that the lower half
+    // finishes the even column and the upper half the odd one (half the arithmetic of letting
+    // the lower half finish both, and every store is 32 lanes wide).
     const int col = (n >> 5) * 16 + (lane & 15);
+    const bool low = lane < 16;
+    static_assert(NC % 2 == 0, "token columns are finished in pairs");
 #pragma unroll
-    for (int j = 0; j < NC; ++j) {
-      const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
-      const int m = m0 + c + j;
-      if (lane < 16 && n < p.N && m < p.M) {
-        const float g = v[j], u = other;
-        ((__nv_bfloat16*)p.out)[(size_t)m * p.ldc + col] = __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
-      }
+    for (int j = 0; j < NC; j += 2) {
+      const float x = __shfl_xor_sync(0xffffffffu, low ? v[j + 1] : v[j], 16);
+      const float g = low ? v[j] : x, u = low ? x : v[j + 1];
+      const int m = m0 + c + j + (low ? 0 : 1);
+      if (n < p.N && m < p.M) ((__nv_bfloat16*)p.out)[(size_t)m * p.ldc + col] = __float2bfloat16_rn(silu_mul(g, u));
     }
     return;
   }
@@ -184,8 +192,8 @@ __device__ __forceinline__ void finish_token_major32(const GemmParams& p, float 
     uint32_t packed[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const float a = v[2 * j] / (1.f + expf(-v[2 * j])) * v[16 + 2 * j];
-      const float b = v[2 * j + 1] / (1.f + expf(-v[2 * j + 1])) * v[16 + 2 * j + 1];
+      const float a = silu_mul(v[2 * j], v[16 + 2 * j]);
+      const float b = silu_mul(v[2 * j + 1], v[16 + 2 * j + 1]);
       __nv_bfloat162 v2 = __floats2bfloat162_rn(a, b);
       packed[j] = *reinterpret_cast<uint32_t*>(&v2);
     }
@@ -299,8 +307,8 @@ __device__ __forceinline__ void finish_token_major_row(const GemmParams& p, uint
         uint32_t packed[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const float a = g[2 * j] / (1.f + expf(-g[2 * j])) * u[2 * j];
-          const float b = g[2 * j + 1] / (1.f + expf(-g[2 * j + 1])) * u[2 * j + 1];
+          const float a = silu_mul(g[2 * j], u[2 * j]);
+          const float b = silu_mul(g[2 * j + 1], u[2 * j + 1]);
           __nv_bfloat162 v2 = __floats2bfloat162_rn(a, b);
           packed[j] = *reinterpret_cast<uint32_t*>(&v2);
         }
