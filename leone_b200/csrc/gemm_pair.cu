@@ -3,12 +3,17 @@
 // The token-major form of gemm_tc.cu (128 tokens on the MMA's M side, a tile of weight rows on
 // its N side) spends 48 KB of operands per k-block and SM.  Here two blocks on neighbouring SMs
 // (a cluster of two) work on one tile of 256 tokens x BN weight rows: each block loads its own
-// 128 token rows and HALF of the tile's weight rows (32 KB per k-block and SM, a third less, and
-// six stages instead of four in the same shared memory), the first block issues one MMA of
+// 128 token rows and HALF of the tile's weight rows (at BN = 256: 32 KB per k-block and SM, a
+// third less, and six stages instead of four in the same shared memory), the first block issues one MMA of
 // M = 256 per 16 elements of K that reads both blocks' shared memory, and each block's tensor
 // memory receives the accumulators of its own 128 token rows, which it finishes exactly as the
 // single-block kernel does (same epilogue code: bf16 / fp32 / fp32 + residual / SwiGLU, and the
 // RMSNorm folded into the products around it).
+//
+// BN is a launch argument, any multiple of 16 from 32 to 256 (of 32 with the SwiGLU epilogue): the
+// host picks the width whose tiles fill whole rounds of the pairs (leone_gemm_pair_width), which
+// for the narrow products of a layer at a few hundred tokens takes the place of a split along K;
+// narrower tiles have smaller stages, so the ring holds more of them (up to ten).
 //
 // Per block: warp 0 loads (TMA loads into its own shared memory, no multicast; both blocks' loads
 // count their bytes on the FIRST block's barrier, which is what the cta_group::2 form of the copy
@@ -23,14 +28,24 @@
 namespace leone {
 namespace tc {
 
-constexpr int kPairStages = 6;
+constexpr int kPairMaxStages = 10;
 constexpr int kPairThreads = 192;
+constexpr int kPairSmemLimit = 226 * 1024;             // dynamic shared memory of a block (the static part is beside it)
 
-template <int BN> struct PairCfg {
-  static constexpr int kHalf = BN / 2;                                  // weight rows a block loads
-  static constexpr int kStageBytes = kTileW * kTileK * 2 + 16384;       // tokens, then the weight half (up to 128 rows)
-  static constexpr int kSmemBytes = kPairStages * kStageBytes + 1024 /*alignment*/ + 256 /*barriers*/;
+// Shared memory of a pair's block for tiles of bn weight rows: stages of 128 token rows and bn / 2
+// weight rows (each operand tile starts on a 1024-byte boundary, as the 128-byte swizzle wants).
+struct PairShape {
+  int half, stage_bytes, stages, smem_bytes;
 };
+__host__ __device__ inline PairShape pair_shape(int bn) {
+  PairShape c;
+  c.half = bn / 2;
+  c.stage_bytes = kTileW * kTileK * 2 + ((c.half * kTileK * 2 + 1023) & ~1023);
+  c.stages = (kPairSmemLimit - 1024 /*alignment*/ - 256 /*barriers*/) / c.stage_bytes;
+  if (c.stages > kPairMaxStages) c.stages = kPairMaxStages;
+  c.smem_bytes = c.stages * c.stage_bytes + 1024 + 256;
+  return c;
+}
 
 __device__ __forceinline__ void umma2_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                            uint32_t accumulate) {
@@ -99,17 +114,16 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
 
 // The pair's work: tile t of the launch is token rows [256 * (t % m_pairs), + 256) x weight rows
 // [BN * (t / m_pairs), + BN); pair q takes tiles q, q + pairs, ...
-template <int BN>
 __global__ void __launch_bounds__(kPairThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                 const GemmParams p) {
-  using Cfg = PairCfg<BN>;
-  constexpr int kStages = kPairStages;
+                 const GemmParams p, const int BN) {
+  const PairShape cfg = pair_shape(BN);
+  const int kStages = cfg.stages;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles_base = (raw + 1023u) & ~1023u;
   uint8_t* aligned = smem_raw + (tiles_base - raw);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + kStages * Cfg::kStageBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + kStages * cfg.stage_bytes);
   // barriers: full[kStages] (used in the first block), empty[kStages], acc_full[2], acc_empty[2]
   const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * kStages;
   const uint32_t acc_full0 = empty0 + 8 * kStages, acc_empty0 = acc_full0 + 16;
@@ -168,11 +182,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
               stop = true;
               break;
             }
-            const uint32_t dst = tiles_base + stage * Cfg::kStageBytes;
+            const uint32_t dst = tiles_base + stage * cfg.stage_bytes;
             const uint32_t bar = cluster_map(full0 + 8 * stage, 0);   // the first block's barrier counts both blocks' bytes
             if (!had_weights) {
-              if (rank == 0) mbar_expect_tx(full0 + 8 * stage, 2 * (kTileW * kTileK * 2 + Cfg::kHalf * kTileK * 2));
-              tma_load_2d_pair(dst + kTileW * kTileK * 2, &map_w, bar, kb * kTileK, n_tile * BN + (int)rank * Cfg::kHalf);
+              if (rank == 0) mbar_expect_tx(full0 + 8 * stage, 2 * (kTileW * kTileK * 2 + cfg.half * kTileK * 2));
+              tma_load_2d_pair(dst + kTileW * kTileK * 2, &map_w, bar, kb * kTileK, n_tile * BN + (int)rank * cfg.half);
             }
             if (pass == 1) tma_load_2d_pair(dst, &map_x, bar, kb * kTileK, m_tile * kTileW);
             if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -189,7 +203,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   } else if (warp == 1) {
     // ---------------- MMA issuer (the first block) ----------------
     if (lane == 0) {
-      constexpr uint32_t idesc = instr_desc_bf16(2 * kTileW, BN);
+      const uint32_t idesc = instr_desc_bf16(2 * kTileW, BN);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
@@ -202,7 +216,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait_cluster(full0 + 8 * stage, phase, giveup)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t a_addr = tiles_base + stage * Cfg::kStageBytes;
+          const uint32_t a_addr = tiles_base + stage * cfg.stage_bytes;
           const uint32_t b_addr = a_addr + kTileW * kTileK * 2;
           const uint64_t a_desc = smem_desc_sw128(a_addr), b_desc = smem_desc_sw128(b_addr);
 #pragma unroll
@@ -228,7 +242,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       if (!ok) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256;
-      finish_token_major_row<BN>(p, taddr, m_tile * kTileW + quarter * 32 + lane, n_tile * BN, n_tile);
+      finish_token_major_row(p, taddr, m_tile * kTileW + quarter * 32 + lane, n_tile * BN, n_tile, BN);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
@@ -255,20 +269,19 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   }
 }
 
-template <int BN>
-int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, int sm_count, cudaStream_t stream) {
+int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, int bn, int sm_count,
+                cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         PairCfg<BN>::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemLimit);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  const int n_tiles = (p.N + BN - 1) / BN, m_pairs = ((p.M + kTileW - 1) / kTileW + 1) / 2;
+  const int n_tiles = (p.N + bn - 1) / bn, m_pairs = ((p.M + kTileW - 1) / kTileW + 1) / 2;
   const long long total = (long long)n_tiles * m_pairs;
   const int pairs = (int)(total < sm_count / 2 ? total : sm_count / 2);
-  return launch_kernel_cluster(gemm_pair_kernel<BN>, dim3(2u * (unsigned)pairs), dim3(kPairThreads),
-                               (size_t)PairCfg<BN>::kSmemBytes, stream, dim3(2), mw, mx, p);
+  return launch_kernel_cluster(gemm_pair_kernel, dim3(2u * (unsigned)pairs), dim3(kPairThreads),
+                               (size_t)pair_shape(bn).smem_bytes, stream, dim3(2), mw, mx, p, bn);
 }
 
 }  // namespace tc
@@ -279,18 +292,17 @@ using namespace leone::tc;
 
 // The token-major product of gemm_tc.cu for more than 256 tokens on pairs of SMs: the same
 // arguments and epilogues (0 bf16, 1 fp32, 2 fp32 += residual, 3 SwiGLU) and the same norm
-// arguments; `width`: weight rows per tile, 256 or 240 (what leone_gemm_tc_token_major_width
-// gives for this product, so that the sums of squares of a folded norm have the parts the
-// caller sized them for).
+// arguments; `width`: weight rows per tile, a multiple of 16 from 32 to 256 (of 32 with the SwiGLU
+// epilogue); the sums of squares of a folded norm have one part per tile of that width.
 extern "C" int leone_gemm_pair(const void* x, const void* w, void* out, const float* residual, int m, int n, int k,
                                int ldx, int ldw, int ldc, int epilogue, int width, int* status, int sm_count,
                                void* norm_out_x, const float* norm_out_w, float* norm_out_ss, int ld_norm_out,
                                const float* norm_in_ss, int norm_in_parts, float norm_eps, cudaStream_t stream) {
   if (m <= 0 || n <= 0) return 0;
   if (k <= 0 || (k % 8) != 0 || (ldx % 8) != 0 || (ldw % 8) != 0) return kRefusedAlignment;
-  if (epilogue < 0 || epilogue > 3 || sm_count < 2 || (width != 256 && width != 240)) return kRefusedSize;
+  if (epilogue < 0 || epilogue > 3 || sm_count < 2 || width < 32 || width > 256 || (width % 16) != 0) return kRefusedSize;
   if (epilogue == 2 && residual == nullptr) return kRefusedSize;
-  if (epilogue == 3 && ((n % 32) != 0 || width != 256)) return kRefusedSize;
+  if (epilogue == 3 && ((n % 32) != 0 || (width % 32) != 0)) return kRefusedSize;
   if (norm_out_x != nullptr && ((epilogue != 1 && epilogue != 2) || norm_out_w == nullptr || norm_out_ss == nullptr))
     return kRefusedSize;
   if (norm_in_ss != nullptr && norm_in_parts < 1) return kRefusedSize;
@@ -301,6 +313,5 @@ extern "C" int leone_gemm_pair(const void* x, const void* w, void* out, const fl
   if (r != 0) return r;
   GemmParams p{out, residual, m, n, k, ldc, epilogue, 1, 0, nullptr, nullptr, status, nullptr,
                (__nv_bfloat16*)norm_out_x, norm_out_w, norm_out_ss, ld_norm_out, norm_in_ss, norm_in_parts, norm_eps, 0};
-  if (width == 240) return launch_pair<240>(mw, mx, p, sm_count, stream);
-  return launch_pair<256>(mw, mx, p, sm_count, stream);
+  return launch_pair(mw, mx, p, width, sm_count, stream);
 }

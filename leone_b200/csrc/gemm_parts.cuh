@@ -252,13 +252,13 @@ __device__ __forceinline__ void finish_token_major32(const GemmParams& p, float 
   }
 }
 
-// Token-major form: the thread that owns token row m finishes the tile's BN weight rows from n0
-// on (tile n_tile), 16 at a time, from tensor memory at taddr: the norm's factor before, the
-// product's epilogue, and the operand and sum of squares of a norm after it.  Warp-wide (the
-// loads from tensor memory are), so every thread of the warp calls it, rows past M too.
-template <int BN>
+// Token-major form: the thread that owns token row m finishes the tile's bn weight rows from n0
+// on (tile n_tile; bn a multiple of 16, of 32 with the SwiGLU epilogue), 16 at a time, from tensor
+// memory at taddr: the norm's factor before, the product's epilogue, and the operand and sum of
+// squares of a norm after it.  Warp-wide (the loads from tensor memory are), so every thread of
+// the warp calls it, rows past M too.
 __device__ __forceinline__ void finish_token_major_row(const GemmParams& p, uint32_t taddr, int m, int n0,
-                                                       int n_tile) {
+                                                       int n_tile, const int bn) {
   const bool vec_ok = (p.ldc & 7) == 0;
   // the norm before this product: this row's factor from the parts the product before left
   float rs = 1.f;
@@ -294,7 +294,7 @@ __device__ __forceinline__ void finish_token_major_row(const GemmParams& p, uint
   };
   if (p.epilogue == 3) {
     __nv_bfloat16* orow = (__nv_bfloat16*)p.out + (size_t)m * p.ldc;
-    for (int c = 0; c < BN; c += 32) {             // 16 gate columns, then their 16 up columns
+    for (int c = 0; c < bn; c += 32) {             // 16 gate columns, then their 16 up columns
       float g[16], u[16];
       tmem_ld16(taddr + c, g);
       tmem_ld16(taddr + c + 16, u);
@@ -322,7 +322,7 @@ __device__ __forceinline__ void finish_token_major_row(const GemmParams& p, uint
         }
       }
     }
-  } else if (p.epilogue == 2 && vec_ok && n0 + BN <= p.N) {
+  } else if (p.epilogue == 2 && vec_ok && n0 + bn <= p.N) {
     // fp32 out = acc + residual for a whole row of the tile: the residual is fetched three
     // chunks ahead of its use, so its latency is paid once per row, not once per chunk
     // (the residual may be the output itself: a chunk is read before it is written, and
@@ -333,35 +333,43 @@ __device__ __forceinline__ void finish_token_major_row(const GemmParams& p, uint
     const size_t row_at = (size_t)(row_ok ? m : 0) * p.ldc + n0;
     const float4* res = reinterpret_cast<const float4*>(p.residual + row_at);
     float4* dst = reinterpret_cast<float4*>((float*)p.out + row_at);
+    const int chunks = bn / 16;
     float4 rb[kAhead][4];
 #pragma unroll
-    for (int a = 0; a < kAhead; ++a)
+    for (int a = 0; a < kAhead; ++a) {
+      if (a < chunks) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) rb[a][j] = res[a * 4 + j];
-#pragma unroll
-    for (int i = 0; i < BN / 16; ++i) {
-      float v[16];
-      tmem_ld16(taddr + i * 16, v);
-      float4 r[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) r[j] = rb[i % kAhead][j];
-      if (i + kAhead < BN / 16) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) rb[i % kAhead][j] = res[(i + kAhead) * 4 + j];
+        for (int j = 0; j < 4; ++j) rb[a][j] = res[a * 4 + j];
       }
+    }
+    for (int i0 = 0; i0 < chunks; i0 += kAhead) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        v[4 * j] += r[j].x; v[4 * j + 1] += r[j].y; v[4 * j + 2] += r[j].z; v[4 * j + 3] += r[j].w;
-      }
-      if (row_ok) {
+      for (int a = 0; a < kAhead; ++a) {        // chunk i0 + a uses and refills slot a
+        const int i = i0 + a;
+        if (i >= chunks) break;
+        float v[16];
+        tmem_ld16(taddr + i * 16, v);
+        float4 r[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          dst[i * 4 + j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        for (int j = 0; j < 4; ++j) r[j] = rb[a][j];
+        if (i + kAhead < chunks) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) rb[a][j] = res[(i + kAhead) * 4 + j];
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          v[4 * j] += r[j].x; v[4 * j + 1] += r[j].y; v[4 * j + 2] += r[j].z; v[4 * j + 3] += r[j].w;
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            dst[i * 4 + j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        }
+        norm_out16(v, n0 + i * 16);
       }
-      norm_out16(v, n0 + i * 16);
     }
   } else {
-    for (int c = 0; c < BN; c += 16) {
+    for (int c = 0; c < bn; c += 16) {
       float v[16];
       tmem_ld16(taddr + c, v);
       const int n = n0 + c;
@@ -411,6 +419,11 @@ __device__ __forceinline__ void finish_token_major_row(const GemmParams& p, uint
     }
   }
   if (p.norm_out_x != nullptr && m < p.M) p.norm_out_ss[(size_t)n_tile * p.M + m] = ssq;
+}
+template <int BN>
+__device__ __forceinline__ void finish_token_major_row(const GemmParams& p, uint32_t taddr, int m, int n0,
+                                                       int n_tile) {
+  finish_token_major_row(p, taddr, m, n0, n_tile, BN);
 }
 
 }  // namespace tc

@@ -69,7 +69,10 @@ def bench_gemm(ops, m, n, k, splits, epilogue, reps, warmup, flush, trace=False,
         out.zero_()
     state = {"i": 0}
     full_tiles = 0
-    if token_major is None and splits is None and norm == "none":
+    pairs = token_major is None and splits is None and fast.in_pairs(m, n, k)    # gemm_pair.cu: no form is forced
+    if pairs:
+        pass
+    elif token_major is None and splits is None and norm == "none":
         token_major, splits, full_tiles, cluster = fast.plan_product(m, n, k)
     elif token_major:
         splits = splits or 1
@@ -97,6 +100,10 @@ def bench_gemm(ops, m, n, k, splits, epilogue, reps, warmup, flush, trace=False,
         _print_trace(ops, run, copies)
     bytes_ = n * k * 2 + m * k * 2 + out.numel() * out.element_size()
     flops = 2.0 * m * n * k
+    if pairs:
+        return dict(kernel="gemm_pair", m=m, n=n, k=k, norm=norm, splits=1, full_tiles=0, cluster=False, token_major=True,
+                    width=fast.pair_width(m, n, epilogue == 3), epilogue=epilogue, us=ms * 1e3,
+                    gbs=bytes_ / ms / 1e6, tflops=flops / ms / 1e9)
     return dict(kernel="gemm_tc", m=m, n=n, k=k, norm=norm, splits=splits, full_tiles=full_tiles, cluster=bool(cluster), token_major=bool(token_major), epilogue=epilogue, us=ms * 1e3,
                 gbs=bytes_ / ms / 1e6, tflops=flops / ms / 1e9)
 
@@ -257,6 +264,10 @@ def main(argv=None) -> int:
     ap.add_argument("--max-cluster", type=int, default=8, help="largest thread-block cluster the dispatchers may use")
     ap.add_argument("--l2-ahead", type=int, default=None,
                     help="gemm, layer-shapes: k-blocks of weights a decode-sized product asks the L2 for ahead of its stages")
+    ap.add_argument("--pair-width", type=int, default=0,
+                    help="gemm: tile width of the products on pairs of SMs (0: the dispatcher's choice)")
+    ap.add_argument("--pairs-from", type=int, default=None,
+                    help="gemm: tokens from which products run on pairs of SMs")
     ap.add_argument("--decode-cluster-rounds", type=int, default=1,
                     help="decode-attention: rounds of blocks that a launch of clusters may take")
     ap.add_argument("--gemm-splits", default="",
@@ -267,6 +278,9 @@ def main(argv=None) -> int:
     ops.fast.force_decode_splits = args.decode_splits
     ops.fast.max_cluster = args.max_cluster
     ops.fast.decode_cluster_rounds = args.decode_cluster_rounds
+    ops.fast.pair_width_override = args.pair_width
+    if args.pairs_from is not None:
+        ops.fast.pairs_from = args.pairs_from
     if args.l2_ahead is not None:
         ops.fast.lib.leone_gemm_tc_set_l2_ahead(args.l2_ahead)
     for item in filter(None, args.gemm_splits.split(",")):

@@ -50,7 +50,10 @@ class FastKernels:
         self.max_cluster = 8               # the portable cluster size
         # LEONE_NO_PAIRS=1 keeps prompt-sized products on single SMs (cta_group::1)
         self.use_pairs = os.environ.get("LEONE_NO_PAIRS", "0") != "1"
-        self.pair_tile_cost = 0.9          # a pair's half tile against a single block's tile (measured 0.86 to 0.89)
+        self.pairs_from = 129              # tokens from which unsplit products run on pairs
+        self.pair_padding = 0.8            # a pair's half tile against a single block's tile, at most (see in_pairs)
+        self.pair_width_override = 0       # > 0: the tile width of every product on pairs (kernel_bench sets it)
+        self._pair_widths = {}
         self.decode_cluster_rounds = 1     # rounds of blocks a clustered decode attention may take (kernel_bench sets it)
         # (n, k) -> (splits, cluster): a forced split of an [n x k] product at decode sizes; empty
         # in the product, filled by kernel_bench's sweeps
@@ -156,13 +159,40 @@ class FastKernels:
         tiles = int(self.lib.leone_gemm_tc_tiles_token_major(m, n))
         return self.token_major_fill * self.sm_count <= tiles <= 2 * self.sm_count
 
-    def in_pairs(self, m: int) -> bool:
-        """Whether an unsplit product of ``m`` tokens runs on pairs of SMs.  A pair's tile is 256
-        tokens and measured 0.87 of the time of two single tiles of 128; with the last tile half
-        empty (320, 384, 640 tokens) the single-block kernel's fewer tiles win."""
-        if not self.use_pairs or m <= 256:
+    def in_pairs(self, m: int, n: int = 0, k: int = 0) -> bool:
+        """Whether an unsplit product of ``m`` tokens runs on pairs of SMs (tiles of 256 tokens,
+        the width chosen by :meth:`pair_width`): from 129 tokens on, except from 257 to 384
+        tokens, where the second of two tiles of 256 would be half empty and the single-block
+        kernel's three tiles of 128 measured faster (gate/up at 384 tokens 62.3 us against 67.2;
+        at 640 tokens three pairs already beat five single tiles, 95.9 against 105.6).  With
+        ``n`` and ``k``: whether this ``[n x k]`` product does; the narrow products of a layer,
+        which up to about 600 tokens are split along K, do not (with tiles narrow enough to fill
+        the pairs, all pairs read the same few token tiles at once, and that measured slower
+        than the split: o_proj at 256 tokens 25.3 us against 18.7, down 61.7 against 37.1)."""
+        if not self.use_pairs or m < self.pairs_from:
             return False
-        return 2 * -(-m // 256) * self.pair_tile_cost <= -(-m // 128)
+        if 2 * -(-m // 256) * self.pair_padding > -(-m // 128):
+            return False
+        return not (n and k and self.token_major_split(m, n, k) > 1)
+
+    def pair_width(self, m: int, n: int, swiglu: bool) -> int:
+        """Weight rows per tile of a product on pairs of SMs: the width whose tiles cost the
+        fewest rounds over the pairs.  A tile's k-block costs what the copy of its operands
+        into a block's shared memory takes (128 token rows beside width / 2 weight rows: the
+        k-loop runs at the rate of those copies, 32 KB in 0.36 us, at every width that was
+        measured); of two widths within 1 percent the wider one stays."""
+        if self.pair_width_override:
+            return self.pair_width_override
+        key = (-(-m // 256), n, bool(swiglu))
+        if key not in self._pair_widths:
+            pairs, best = self.sm_count // 2, None
+            for w in range(256, 31, -32 if swiglu else -16):
+                rounds = -(-(-(-n // w) * key[0]) // pairs)
+                cost = rounds * (0.18 + 0.0007 * w)
+                if best is None or cost < 0.99 * best[0]:
+                    best = (cost, w)
+            self._pair_widths[key] = best[1]
+        return self._pair_widths[key]
 
     def token_major_split(self, m: int, n: int, k: int) -> int:
         """Splits along K of the token-major form, summed inside thread-block clusters (1: none).
@@ -194,6 +224,8 @@ class FastKernels:
         s = self.token_major_split(m, n, k)
         if s > 1:
             return True, s, 0, True
+        if self.in_pairs(m):
+            return True, 1, 0, False                 # on pairs of SMs (_gemm takes them where nothing is forced)
         if self.token_major(m, n):
             return True, 1, 0, False
         return (False, *self.choose_splits(m, n, k))
@@ -209,7 +241,11 @@ class FastKernels:
         for the RMSNorm that follows it; ``norm_in=(ss, parts, eps)``: ``x`` is such an ``xn``
         and every output row is scaled by the norm's ``rsqrt(mean + eps)``."""
         m, k = x.shape
-        if token_major is None and splits is None and norm_in is None and norm_out is None:
+        # on pairs of SMs unless the caller forces another form
+        pairs = token_major is None and splits in (None, 1) and not cluster and self.in_pairs(m, n_rows, k)
+        if pairs:
+            token_major, splits, full_tiles, cluster = True, 1, 0, False
+        elif token_major is None and splits is None and norm_in is None and norm_out is None:
             token_major, splits, full_tiles, cluster = self.plan_product(m, n_rows, k)
         token_major = bool(token_major) or m > 256
         if token_major and not cluster:
@@ -229,13 +265,16 @@ class FastKernels:
             # buffer never grows with the step's size)
             ws, _ = self._scratch(self.token_major_workspace_floats(), 0)
         from ctypes import c_float
+        if norm_out is not None and norm_out[2].shape[0] != self.norm_parts(m, n_rows, pairs):
+            raise ValueError(f"the sums of squares have {norm_out[2].shape[0]} parts, this product leaves "
+                             f"{self.norm_parts(m, n_rows, pairs)}")
         no = (None, None, None, 0) if norm_out is None else \
             (_ptr(norm_out[0]), _ptr(norm_out[1]), _ptr(norm_out[2]), norm_out[0].stride(0))
         ni = (None, 0, c_float(0.0)) if norm_in is None else (_ptr(norm_in[0]), int(norm_in[1]), c_float(norm_in[2]))
-        if splits == 1 and not cluster and self.in_pairs(m):
-            # prompt-sized: pairs of SMs on tiles of 256 tokens (gemm_pair.cu), the same tile width
-            # as the single-block kernel would take (the norm's parts are sized for it)
-            width = int(self.lib.leone_gemm_tc_token_major_width(m, n_rows, 1 if epilogue == 3 else 0))
+        if pairs:
+            # pairs of SMs on tiles of 256 tokens (gemm_pair.cu); a folded norm's parts follow the
+            # tile width (norm_parts)
+            width = self.pair_width(m, n_rows, epilogue == 3)
             code = self.lib.leone_gemm_pair(_ptr(x), _ptr(w), _ptr(out), _ptr(residual), m, n_rows, k,
                                             x.stride(0), w.stride(0), out.stride(0), epilogue, width,
                                             _ptr(self.status), self.sm_count, *no, *ni, self._stream())
@@ -261,7 +300,13 @@ class FastKernels:
             return False
         return not (n and k and self.token_major_split(m, n, k) > 1)
 
-    def norm_parts(self, m: int, n: int) -> int:
+    def norm_parts(self, m: int, n: int, pairs=None) -> int:
+        """Parts of the sums of squares that a product of ``m`` tokens with ``n`` outputs leaves
+        for the norm after it: on pairs of SMs (``pairs=None``: where the dispatcher takes them
+        for an unsplit product) one per tile of weight rows, else what the single-block kernel
+        leaves."""
+        if self.in_pairs(m) if pairs is None else pairs:
+            return -(-n // self.pair_width(m, n, False))
         return int(self.lib.leone_gemm_tc_norm_parts(m, n))
 
     def linear(self, x, w, out, epilogue, residual, norm_in=None, norm_out=None) -> bool:

@@ -205,7 +205,7 @@ def test_gemm_tc_token_major_below_the_prompt_sizes(ops16, m, n, k):
     u = x.double() @ up.double().t()
     _close(act, g / (1 + torch.exp(-g)) * u, 2 ** -7, 1e-4, "token-major swiglu")
     xn = torch.empty((m, n), device=DEV, dtype=torch.bfloat16)
-    ss = torch.empty((fast.norm_parts(m, n), m), device=DEV)
+    ss = torch.empty((fast.norm_parts(m, n, pairs=False), m), device=DEV)
     with pytest.raises(RuntimeError, match="refused"):
         fast._gemm(x, w, hidden, 2, hidden, n, token_major=True, norm_out=(xn, torch.ones(n, device=DEV), ss))
 
@@ -245,7 +245,7 @@ def test_gemm_tc_token_major_cluster_split(ops16, m, n, k, splits):
     u = x.double() @ up.double().t()
     _close(act, g / (1 + torch.exp(-g)) * u, 2 ** -7, 1e-4, "token-major cluster swiglu")
     xn = torch.empty((m, n), device=DEV, dtype=torch.bfloat16)
-    ss = torch.empty((fast.norm_parts(m, n), m), device=DEV)
+    ss = torch.empty((fast.norm_parts(m, n, pairs=False), m), device=DEV)
     with pytest.raises(RuntimeError, match="refused"):
         fast._gemm(x, w, hidden, 2, hidden, n, norm_out=(xn, torch.ones(n, device=DEV), ss), **kw)
     torch.cuda.synchronize()
@@ -262,10 +262,12 @@ def test_the_dispatcher_splits_narrow_products_in_the_token_major_form(ops16):
     assert fast.plan_product(300, 4096, 256)[:2] == (True, 1)                # too few k-blocks to split
 
 
-def test_gemm_tc_prompt_sized_tiles_of_240_weight_rows(ops16):
-    """Above 256 tokens the tile's width is 256 or 240, whichever costs fewer rounds: a size where
-    240 wins, with the folded norm on both sides (its parts follow the width) and a ragged edge."""
+def test_gemm_tc_prompt_sized_tiles_of_240_weight_rows(ops16, monkeypatch):
+    """The single-block kernel above 256 tokens: the tile's width is 256 or 240, whichever costs
+    fewer rounds: a size where 240 wins, with the folded norm on both sides (its parts follow the
+    width) and a ragged edge."""
     fast = ops16.fast
+    monkeypatch.setattr(fast, "use_pairs", False)
     sms = fast.sm_count
     m, k = 128 * 8, 256
     n = 240 * (2 * sms // 8)                                # 2 rounds of 240-wide tiles; 256-wide ones need 3
@@ -297,19 +299,22 @@ def test_gemm_tc_prompt_sized_tiles_of_240_weight_rows(ops16):
     _close(out2, (xn.double() @ w2.double().t()) * rs, 2 ** -8, 1e-3, "the product after, parts of 240")
 
 
-@pytest.mark.parametrize("m,n,k", [(257, 264, 64), (300, 520, 512), (513, 1000, 200), (640, 4096, 1024),
-                                   (1000, 1024, 264), (2048, 240 * 5 - 24, 4096)])
-def test_gemm_pair_on_two_sms(ops16, m, n, k):
-    """Prompt-sized products on pairs of SMs (one MMA of 256 tokens over both blocks' shared
-    memory), forced for every size above 256 tokens: ragged last pairs (a second block with no
-    token at all), ragged weight tiles, K that is no multiple of the k-block; every epilogue and
-    the folded norm on both sides against float64, and the same bits on every run."""
+@pytest.mark.parametrize("m,n,k,width", [(129, 264, 64, 0), (200, 4096, 1024, 0), (257, 264, 64, 48), (300, 520, 512, 0),
+                                         (513, 1000, 200, 112), (768, 4096, 1024, 0), (1000, 1024, 264, 176),
+                                         (256, 1200, 4096, 32), (2048, 240 * 5 - 24, 4096, 0), (384, 777 * 16, 136, 208)])
+def test_gemm_pair_on_two_sms(ops16, m, n, k, width):
+    """Products on pairs of SMs (one MMA of 256 tokens over both blocks' shared memory), at the
+    dispatcher's tile width (0) and at forced ones from 32 to 256: ragged last pairs (a second
+    block with no token at all), ragged weight tiles, K that is no multiple of the k-block; every
+    epilogue and the folded norm on both sides against float64, the same bits on every run and
+    the same as the single-block kernel's."""
     fast = ops16.fast
     assert fast.use_pairs
-    saved = fast.pair_tile_cost
-    fast.pair_tile_cost = 0.0
     try:
-        assert fast.in_pairs(m)
+        fast.pair_width_override = width
+        fast.pair_padding = 0.0                               # pairs also where their last tile is half empty
+        fast.token_major_split_from = 1 << 30                 # ... and where the dispatcher would split along K
+        assert fast.in_pairs(m, n, k)
         x = _randn((m, k), 81, torch.bfloat16)
         w = _randn((n, k), 82, torch.bfloat16, scale=0.05)
         want = x.double() @ w.double().t()
@@ -324,6 +329,7 @@ def test_gemm_pair_on_two_sms(ops16, m, n, k):
         g = 1 + 0.2 * _randn((n,), 84)
         hidden = res.clone()
         parts = fast.norm_parts(m, n)
+        assert parts == -(-n // (width or fast.pair_width(m, n, False)))
         xn = torch.full((m, n), 7.0, device=DEV, dtype=torch.bfloat16)
         ss = torch.full((parts, m), -1.0, device=DEV)
         fast._gemm(x, w, hidden, 2, hidden, n, norm_out=(xn, g, ss))
@@ -334,6 +340,9 @@ def test_gemm_pair_on_two_sms(ops16, m, n, k):
         again, xn2, ss2 = res.clone(), torch.empty_like(xn), torch.empty_like(ss)
         fast._gemm(x, w, again, 2, again, n, norm_out=(xn2, g, ss2))
         assert torch.equal(hidden, again) and torch.equal(xn, xn2) and torch.equal(ss, ss2)
+        plain = res.clone()                                   # the residual epilogue without the norm
+        fast._gemm(x, w, plain, 2, plain, n)
+        assert torch.equal(plain, hidden)
         n2, inter = 328, 160
         w2 = _randn((n2, n), 85, torch.bfloat16, scale=0.05)
         rs = torch.rsqrt((h64 * h64).mean(dim=1, keepdim=True) + 1e-5)
@@ -343,6 +352,7 @@ def test_gemm_pair_on_two_sms(ops16, m, n, k):
         gate, up = w2[:inter].contiguous(), w2[inter:2 * inter].contiguous()
         gu = ops16.prepare_gate_up(gate, up)
         act = torch.full((m, inter), 9.0, device=DEV, dtype=torch.bfloat16)
+        fast.pair_width_override = max(32, width // 32 * 32) if width else 0      # whole groups of gate and up rows
         fast._gemm(xn, gu.weight, act, 3, None, 2 * inter, norm_in=(ss, parts, 1e-5))
         gg = (xn.double() @ gate.double().t()) * rs
         uu = (xn.double() @ up.double().t()) * rs
@@ -350,18 +360,48 @@ def test_gemm_pair_on_two_sms(ops16, m, n, k):
         # the single-block kernel on the same inputs: the same sums in the same order
         fast.use_pairs = False
         single = torch.empty_like(out32)
-        fast._gemm(x, w, single, 1, None, n)
+        fast._gemm(x, w, single, 1, None, n, token_major=True)
         assert torch.equal(single, out32)
         torch.cuda.synchronize()
         assert int(fast.status.abs().sum()) == 0
     finally:
-        fast.pair_tile_cost, fast.use_pairs = saved, True
+        fast.pair_width_override, fast.use_pairs, fast.pair_padding, fast.token_major_split_from = 0, True, 0.8, 128
 
 
-def test_the_dispatcher_takes_pairs_where_their_tiles_are_full(ops16):
+def test_gemm_pair_refusals(ops16):
     fast = ops16.fast
-    assert not fast.in_pairs(256) and not fast.in_pairs(320) and not fast.in_pairs(640)
-    assert fast.in_pairs(512) and fast.in_pairs(1000) and fast.in_pairs(2048) and fast.in_pairs(8192 + 1)
+    x = _randn((400, 64), 86, torch.bfloat16)
+    w = _randn((512, 64), 87, torch.bfloat16)
+    out = torch.empty((400, 512), device=DEV, dtype=torch.bfloat16)
+    try:
+        for width in (16, 40, 272):                           # not a multiple of 16 between 32 and 256
+            fast.pair_width_override = width
+            with pytest.raises(RuntimeError, match="refused"):
+                fast._gemm(x, w, out, 0, None, 512)
+        fast.pair_width_override = 48                         # SwiGLU needs whole groups of 32 rows
+        act = torch.empty((400, 256), device=DEV, dtype=torch.bfloat16)
+        with pytest.raises(RuntimeError, match="refused"):
+            fast._gemm(x, w, act, 3, None, 512)
+    finally:
+        fast.pair_width_override = 0
+
+
+def test_the_dispatcher_takes_pairs_for_unsplit_products_at_widths_that_fill_their_rounds(ops16):
+    fast = ops16.fast
+    assert fast.pair_padding == 0.8 and fast.token_major_split_from == 128
+    assert [m for m in (128, 129, 256, 257, 384, 385, 512, 513, 640, 641, 2048, 8193) if fast.in_pairs(m)] == \
+        [129, 256, 385, 512, 513, 640, 641, 2048, 8193]
+    if fast.sm_count == 148:
+        assert fast.pair_width(256, 24576, True) == 192         # 128 tiles: two rounds of narrower tiles
+        assert fast.pair_width(2048, 4096, False) == 240        # 144 tiles: two rounds
+        assert fast.pair_width(2048, 24576, True) == 256 and fast.pair_width(2048, 151936, False) == 256
+        # the narrow products of a layer stay split along K up to about 600 tokens
+        assert not fast.in_pairs(256, 4096, 4096) and not fast.in_pairs(512, 4096, 12288)
+        assert fast.in_pairs(256, 24576, 4096) and fast.in_pairs(200, 151936, 4096) and fast.in_pairs(1024, 4096, 4096)
+        assert fast.plan_product(300, 4096, 4096)[1] > 1 and fast.plan_product(2048, 4096, 4096) == (True, 1, 0, False)
+    for m, n, swiglu in ((300, 1000, False), (129, 24576, True), (5000, 151936, False)):
+        w = fast.pair_width(m, n, swiglu)
+        assert 32 <= w <= 256 and w % (32 if swiglu else 16) == 0
 
 
 def test_the_dispatcher_picks_the_token_major_form_only_where_its_tiles_fill_the_device(ops16):
@@ -445,7 +485,7 @@ def test_gemm_tc_norm_between_products(ops16, m, n, k, splits, cluster):
     g = 1 + 0.2 * _randn((n,), 44)
     eps = 1e-5
     hidden = res.clone()
-    parts = fast.norm_parts(m, n)
+    parts = fast.norm_parts(m, n, pairs=None if splits == 1 else False)    # a forced split: the single-block kernel
     xn = torch.full((m, n), 7.0, device=DEV, dtype=torch.bfloat16)
     ss = torch.full((parts, m), -1.0, device=DEV)
     fast._gemm(x, w1, hidden, 2, hidden, n, splits=splits, cluster=cluster, norm_out=(xn, g, ss))
