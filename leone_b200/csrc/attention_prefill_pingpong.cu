@@ -199,7 +199,7 @@ attention_prefill_pingpong_kernel(const __nv_bfloat16* __restrict__ qkv, int row
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     gave_up = 0;
-    mbar_init(bar_q, kLoadThreads / 32);
+    mbar_init(bar_q, 2 * kTileWarps);                   // every softmax warp brings its share of its query tile
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_k_full + 8 * b, kStreamThreads / 32);
       mbar_init(bar_v_full + 8 * b, kStreamThreads / 32);
@@ -321,21 +321,9 @@ attention_prefill_pingpong_kernel(const __nv_bfloat16* __restrict__ qkv, int row
         else if (page >= 0) src = (((long long)page * pa.n_kv + kvh) * pa.page_tokens + (kj % pa.page_tokens)) * D;
         return src;
       };
-      // the first tile's page numbers are on their way while the query tiles are requested
+      // the first tile's page numbers (the query tiles are gathered by the softmax warps, which have
+      // nothing else to do yet, so the first keys are requested at once)
       int page_a = page_of(0, st), page_b = page_of(0, st + kStreamThreads);
-      // both query tiles: row r of tile j = (token lo_j + r / g, head r % g).  Their copies are
-      // not waited for here: they land with the first key and value tiles.
-      for (int idx = lt; idx < 2 * kRows * kChunks; idx += kLoadThreads) {
-        const int j = idx / (kRows * kChunks), rem = idx - j * (kRows * kChunks);
-        const int r = rem / kChunks, ch = rem - r * kChunks;
-        const int tl = r / g, hh = r - tl * g;
-        const int token = tok0 + j * tq + tl;
-        const bool ok = tl < tq && token < q_len;
-        const __nv_bfloat16* src =
-            qkv + (size_t)(q0 + (ok ? token : 0)) * row_stride + (size_t)(kvh * g + hh) * D + ch * 8;
-        cp_async16(q_t + j * kTileBytes + swizzled(r, ch), src, ok);
-      }
-      cp_async_commit();
       // a thread copies two neighbouring chunks (one 32-byte sector) of rows r0, r0 + step, ..
       constexpr int kPairs = kChunks / 2;
       constexpr int kStep = kStreamThreads / kPairs;     // 8 rows for D = 128, 16 for D = 64: the swizzle phase stays
@@ -366,7 +354,6 @@ attention_prefill_pingpong_kernel(const __nv_bfloat16* __restrict__ qkv, int row
         cp_async_wait<0>();
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
-        if (lane == 0 && t == 0) mbar_arrive(bar_q);     // this warp's share of the query tiles landed before
         if (lane == 0) mbar_arrive(bar_full + 8 * (t & 1));
       }
     } else {
@@ -386,6 +373,25 @@ attention_prefill_pingpong_kernel(const __nv_bfloat16* __restrict__ qkv, int row
       const int bar_id = 4 + j;
       float m_run = -INFINITY, l_run = 0.f;
       bool ok_all = true;
+      {
+        // this query tile's rows: row r = (token lo + r / g, head r % g), in the swizzled operand
+        // layout; the tile's 256 threads take 8 of its 16-byte chunks each
+        const int jt = tid - j * kTileThreads;
+        for (int idx = jt; idx < kRows * kChunks; idx += kTileThreads) {
+          const int r = idx / kChunks, ch = idx - r * kChunks;
+          const int tl = r / g, hh = r - tl * g;
+          const int token = tok0 + j * tq + tl;
+          const bool ok = tl < tq && token < q_len;
+          const __nv_bfloat16* src =
+              qkv + (size_t)(q0 + (ok ? token : 0)) * row_stride + (size_t)(kvh * g + hh) * D + ch * 8;
+          cp_async16(q_t + j * kTileBytes + swizzled(r, ch), src, ok);
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_q);
+      }
       for (int t = 0; t < nj; ++t) {
         const int tile_start = tile0 + t * kKeys + half * 64;     // this thread's first key
         // S_j(t) is complete, and so is PV_j(t - 1): O_j is at rest until this tile's go-ahead
