@@ -33,7 +33,8 @@
 // special-function unit was measured slower: the softmax is bound by its instruction stream,
 // not by that unit.)
 //
-// Warps: 0-7 softmax of query tile 0, 8-15 of query tile 1 (a warp reaches the 32 lanes of
+// Warps: 0-7 softmax of query tile 0, 8-15 of query tile 1, which first gather their own query
+// tile into shared memory (a warp reaches the 32 lanes of
 // tensor memory given by its number modulo 4; warps w and w + 4 share rows and split the
 // columns), 16 issues the tensor-core work, 17-18 gather key tiles, 19-20 gather value tiles
 // from the pages with 16-byte asynchronous copies that write the 128-byte-swizzled operand
