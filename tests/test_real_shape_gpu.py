@@ -57,8 +57,9 @@ def setup(request):
     tensors = _plain_weights(cfg)
     # 300 tokens: the prompt-sized kernels; 45: the decode-sized ones; 150: between them, where the
     # wide gate/up product takes the token-major form and the others the swapped one
+    # 400 (its own test): products on pairs of SMs with the norms folded into them
     reqs = {"a": replay.random_tokens(VOCAB, 300, 1), "b": replay.random_tokens(VOCAB, 45, 2),
-            "c": replay.random_tokens(VOCAB, 150, 3)}
+            "c": replay.random_tokens(VOCAB, 150, 3), "d": replay.random_tokens(VOCAB, 400, 4)}
     want = {}
     for bf in (False, True):
         for r, t in reqs.items():
@@ -75,6 +76,7 @@ def test_real_layer_sizes_under_cuts(setup, dtype, fusions):
     fall back to."""
     from leone_b200.engine.engine import Engine
     shape, cfg, config, reqs, want = setup
+    reqs = {r: reqs[r] for r in "abc"}
     bf = dtype == "bfloat16"
 
     class Plain:
@@ -100,6 +102,33 @@ def test_real_layer_sizes_under_cuts(setup, dtype, fusions):
         tol = (3e-5, 3e-5) if dtype == "float32" else replay.tolerance(dtype)
         worst = replay.compare(steps, out, Plain(), reqs, *tol, what)
         replay.check_worst(("real", shape, dtype, name, fusions), worst)
+        del engine
+        torch.cuda.empty_cache()
+
+
+def test_real_layer_sizes_a_prompt_on_pairs_of_sms(setup):
+    """A prompt of 400 tokens in one step (every product of the layers on pairs of SMs, with the
+    norms folded into them), and in portions of 385 and 15; a short request after it."""
+    from leone_b200.engine.engine import Engine
+    shape, cfg, config, reqs, want = setup
+    reqs = {r: reqs[r] for r in "db"}
+
+    class Plain:
+        def logits(self, tokens):
+            return want[(True, {400: "d", 45: "b"}[len(tokens)])]
+
+    for name, steps in {"whole": replay.trace_whole(reqs),
+                        "portions": replay.trace_portions(reqs, sizes=(385, 15, 2, 43))}.items():
+        for st in steps:
+            for e in st["entries"]:
+                e["want"] = [w for w in e["want"] if w % 7 == 0 or w == len(e["tokens"]) - 1]
+        engine = Engine.from_config(config, SEED, dtype="bfloat16", page_tokens=16,
+                                    max_tokens=replay.max_live_tokens(steps), max_requests=4, max_batch_tokens=448)
+        assert engine.ops.fast.in_pairs(400) and engine.ops.fast.fuses_norm(400)
+        out = replay.run_trace_engine(engine, steps)
+        worst = replay.compare(steps, out, Plain(), reqs, *replay.tolerance("bfloat16"),
+                               f"{shape} layer sizes, 400 tokens on pairs, {name}")
+        replay.check_worst(("real-pairs", shape, name), worst)
         del engine
         torch.cuda.empty_cache()
 
