@@ -1,19 +1,19 @@
-// out[M,N] = x[M,K] * w[N,K]^T for prompt-sized M on pairs of SMs (tcgen05 with cta_group::2).
+// out[M,N] = x[M,K] * w[N,K]^T for more than 128 tokens on pairs of SMs (tcgen05 with cta_group::2).
 //
 // The token-major form of gemm_tc.cu (128 tokens on the MMA's M side, a tile of weight rows on
 // its N side) spends 48 KB of operands per k-block and SM.  Here two blocks on neighbouring SMs
 // (a cluster of two) work on one tile of 256 tokens x BN weight rows: each block loads its own
 // 128 token rows and HALF of the tile's weight rows (at BN = 256: 32 KB per k-block and SM, a
-// third less, and six stages instead of four in the same shared memory), the first block issues one MMA of
+// third less, and seven stages instead of four in the same shared memory), the first block issues one MMA of
 // M = 256 per 16 elements of K that reads both blocks' shared memory, and each block's tensor
 // memory receives the accumulators of its own 128 token rows, which it finishes exactly as the
 // single-block kernel does (same epilogue code: bf16 / fp32 / fp32 + residual / SwiGLU, and the
 // RMSNorm folded into the products around it).
 //
 // BN is a launch argument, any multiple of 16 from 32 to 256 (of 32 with the SwiGLU epilogue): the
-// host picks the width whose tiles fill whole rounds of the pairs (leone_gemm_pair_width), which
-// for the narrow products of a layer at a few hundred tokens takes the place of a split along K;
-// narrower tiles have smaller stages, so the ring holds more of them (up to ten).
+// caller picks the width whose tiles cost the fewest rounds over the pairs (the k-loop's time
+// follows the bytes a block copies per k-block, so a narrower tile is cheaper by less than its
+// width); narrower tiles have smaller stages, so the ring holds more of them (up to ten).
 //
 // Per block: warp 0 loads (TMA loads into its own shared memory, no multicast; both blocks' loads
 // count their bytes on the FIRST block's barrier, which is what the cta_group::2 form of the copy
