@@ -309,7 +309,8 @@ def test_gemm_pair_on_two_sms(ops16, m, n, k, width):
     epilogue and the folded norm on both sides against float64, the same bits on every run and
     the same as the single-block kernel's."""
     fast = ops16.fast
-    assert fast.use_pairs
+    if not fast.use_pairs:
+        pytest.skip("LEONE_NO_PAIRS is set")
     try:
         fast.pair_width_override = width
         fast.pair_padding = 0.0                               # pairs also where their last tile is half empty
@@ -370,6 +371,8 @@ def test_gemm_pair_on_two_sms(ops16, m, n, k, width):
 
 def test_gemm_pair_refusals(ops16):
     fast = ops16.fast
+    if not fast.use_pairs:
+        pytest.skip("LEONE_NO_PAIRS is set")
     x = _randn((400, 64), 86, torch.bfloat16)
     w = _randn((512, 64), 87, torch.bfloat16)
     out = torch.empty((400, 512), device=DEV, dtype=torch.bfloat16)
@@ -388,6 +391,8 @@ def test_gemm_pair_refusals(ops16):
 
 def test_the_dispatcher_takes_pairs_for_unsplit_products_at_widths_that_fill_their_rounds(ops16):
     fast = ops16.fast
+    if not fast.use_pairs:
+        pytest.skip("LEONE_NO_PAIRS is set")
     assert fast.pair_padding == 0.8 and fast.token_major_split_from == 128
     assert [m for m in (128, 129, 256, 257, 384, 385, 512, 513, 640, 641, 2048, 8193) if fast.in_pairs(m)] == \
         [129, 256, 385, 512, 513, 640, 641, 2048, 8193]
