@@ -101,8 +101,9 @@ def bench_gemm(ops, m, n, k, splits, epilogue, reps, warmup, flush, trace=False,
     bytes_ = n * k * 2 + m * k * 2 + out.numel() * out.element_size()
     flops = 2.0 * m * n * k
     if pairs:
-        return dict(kernel="gemm_pair", m=m, n=n, k=k, norm=norm, splits=1, full_tiles=0, cluster=False, token_major=True,
-                    width=fast.pair_width(m, n, epilogue == 3), epilogue=epilogue, us=ms * 1e3,
+        ps = fast.pair_split(m, n, k) if norm == "none" else 1
+        return dict(kernel="gemm_pair", m=m, n=n, k=k, norm=norm, splits=ps, full_tiles=0, cluster=ps > 1, token_major=True,
+                    width=256 if ps > 1 else fast.pair_width(m, n, epilogue == 3), epilogue=epilogue, us=ms * 1e3,
                     gbs=bytes_ / ms / 1e6, tflops=flops / ms / 1e9)
     return dict(kernel="gemm_tc", m=m, n=n, k=k, norm=norm, splits=splits, full_tiles=full_tiles, cluster=bool(cluster), token_major=bool(token_major), epilogue=epilogue, us=ms * 1e3,
                 gbs=bytes_ / ms / 1e6, tflops=flops / ms / 1e9)

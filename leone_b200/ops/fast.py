@@ -51,8 +51,11 @@ class FastKernels:
         # LEONE_NO_PAIRS=1 keeps prompt-sized products on single SMs (cta_group::1)
         self.use_pairs = os.environ.get("LEONE_NO_PAIRS", "0") != "1"
         self.pairs_from = 129              # tokens from which unsplit products run on pairs
+        # LEONE_NO_PAIR_SPLITS=1 leaves the narrow products' split along K to the single-block kernel
+        self.use_pair_splits = os.environ.get("LEONE_NO_PAIR_SPLITS", "0") != "1"
         self.pair_padding = 0.8            # a pair's half tile against a single block's tile, at most (see in_pairs)
         self.pair_width_override = 0       # > 0: the tile width of every product on pairs (kernel_bench sets it)
+        self.pair_split_override = 0       # > 0: pairs per tile of every product on pairs (tests set it)
         self._pair_widths = {}
         self.decode_cluster_rounds = 1     # rounds of blocks a clustered decode attention may take (kernel_bench sets it)
         # (n, k) -> (splits, cluster): a forced split of an [n x k] product at decode sizes; empty
@@ -64,6 +67,7 @@ class FastKernels:
         # LEONE_NO_TC_ATTENTION=1 keeps prompt attention on the mma.sync kernel
         self.use_tc_attention = os.environ.get("LEONE_NO_TC_ATTENTION", "0") != "1"
         self.lib.leone_attention_decode_scratch.restype = ctypes.c_longlong
+        self.lib.leone_gemm_pair_workspace_floats.restype = ctypes.c_longlong
 
     def _stream(self):
         return c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
@@ -169,11 +173,37 @@ class FastKernels:
         which up to about 600 tokens are split along K, do not (with tiles narrow enough to fill
         the pairs, all pairs read the same few token tiles at once, and that measured slower
         than the split: o_proj at 256 tokens 25.3 us against 18.7, down 61.7 against 37.1)."""
-        if not self.use_pairs or m < self.pairs_from:
+        if not self._pairs_fit(m):
             return False
-        if 2 * -(-m // 256) * self.pair_padding > -(-m // 128):
-            return False
-        return not (n and k and self.token_major_split(m, n, k) > 1)
+        return not (n and k and self.token_major_split(m, n, k) > 1 and self.pair_split(m, n, k) == 1)
+
+    def _pairs_fit(self, m: int) -> bool:
+        return self.use_pairs and m >= self.pairs_from and 2 * -(-m // 256) * self.pair_padding <= -(-m // 128)
+
+    def pair_split(self, m: int, n: int, k: int) -> int:
+        """Pairs of SMs per tile of a narrow product (one that the single-block kernel would split
+        along K): 4 or 2 pairs share the k-blocks of a tile of 256 tokens x 256 weight rows when
+        their clusters of 8 or 4 blocks are all resident at once and a pair keeps at least 8
+        k-blocks; 1: not split on pairs.  Only where the pairs can split as many ways as the single
+        blocks would: with the same number of splits the pairs' k-loop wins (down at 512 tokens
+        50.3 us against 56.6, qkv at 256 tokens 23.4 against 25.3), against four single-block
+        splits two pairs lose (o_proj at 256 tokens 25.1 us against 18.8, down 46.5 against 37.4)."""
+        if self.pair_split_override:
+            return self.pair_split_override
+        if not (self.use_pair_splits and self.use_clusters and self._pairs_fit(m)) or self.token_major_split(m, n, k) == 1:
+            return 1
+        tiles, k_blocks = -(-n // 256) * -(-m // 256), -(-k // 64)
+        single = self.token_major_split(m, n, k)
+        for s in (4, 2):
+            if tiles * s <= self.sm_count // 2 and k_blocks // s >= 8 and tiles <= self._pair_capacity(s):
+                return s if s >= single else 1
+        return 1
+
+    def _pair_capacity(self, splits: int) -> int:
+        key = ("pairs", splits)
+        if key not in self._cluster_capacity:
+            self._cluster_capacity[key] = int(self.lib.leone_gemm_pair_capacity(256, splits))
+        return self._cluster_capacity[key]
 
     def pair_width(self, m: int, n: int, swiglu: bool) -> int:
         """Weight rows per tile of a product on pairs of SMs: the width whose tiles cost the
@@ -274,9 +304,14 @@ class FastKernels:
         if pairs:
             # pairs of SMs on tiles of 256 tokens (gemm_pair.cu); a folded norm's parts follow the
             # tile width (norm_parts)
-            width = self.pair_width(m, n_rows, epilogue == 3)
+            ps = self.pair_split(m, n_rows, k) if norm_in is None and norm_out is None else 1
+            width, pws = self.pair_width(m, n_rows, epilogue == 3), None
+            if ps > 1:
+                width = 256
+                need = int(self.lib.leone_gemm_pair_workspace_floats(m, n_rows, width, ps))
+                pws, _ = self._scratch(max(self.token_major_workspace_floats(), need), 0)
             code = self.lib.leone_gemm_pair(_ptr(x), _ptr(w), _ptr(out), _ptr(residual), m, n_rows, k,
-                                            x.stride(0), w.stride(0), out.stride(0), epilogue, width,
+                                            x.stride(0), w.stride(0), out.stride(0), epilogue, width, ps, _ptr(pws),
                                             _ptr(self.status), self.sm_count, *no, *ni, self._stream())
             if code != 0:
                 raise RuntimeError(f"gemm_pair refused or failed with code {code} for m={m} n={n_rows} k={k}")

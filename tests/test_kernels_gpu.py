@@ -369,6 +369,53 @@ def test_gemm_pair_on_two_sms(ops16, m, n, k, width):
         fast.pair_width_override, fast.use_pairs, fast.pair_padding, fast.token_major_split_from = 0, True, 0.8, 128
 
 
+@pytest.mark.parametrize("m,n,k,splits", [(129, 264, 1024, 2), (200, 520, 2048, 4), (256, 2048, 4096, 4),
+                                          (300, 1000, 4096, 2), (512, 1000, 2048, 4), (600, 768, 640, 2)])
+def test_gemm_pair_split_along_k(ops16, m, n, k, splits):
+    """Two or four pairs of SMs share the k-blocks of a tile (clusters of four or eight blocks, the
+    partial sums through the workspace): every epilogue against float64, the same bits on every
+    run, and the refusals."""
+    fast = ops16.fast
+    if not fast.use_pairs:
+        pytest.skip("LEONE_NO_PAIRS is set")
+    assert fast._pair_capacity(splits) > 0
+    try:
+        fast.pair_padding, fast.pair_split_override = 0.0, splits
+        x = _randn((m, k), 91, torch.bfloat16)
+        w = _randn((n, k), 92, torch.bfloat16, scale=0.05)
+        want = x.double() @ w.double().t()
+        atol32 = 2e-6 * math.sqrt(k) * 4
+        out = torch.full((m, n), 9.0, device=DEV, dtype=torch.bfloat16)
+        fast._gemm(x, w, out, 0, None, n)
+        _close(out, want, 2 ** -8, atol32, f"pair split bf16 out m{m} n{n} k{k} s{splits}")
+        out32 = torch.full((m, n), 9.0, device=DEV)
+        fast._gemm(x, w, out32, 1, None, n)
+        _close(out32, want, 1e-5, atol32, "pair split fp32 out")
+        res = _randn((m, n), 93)
+        hidden = res.clone()
+        fast._gemm(x, w, hidden, 2, hidden, n)
+        _close(hidden, want + res.double(), 1e-5, atol32, "pair split residual in place")
+        again = res.clone()
+        fast._gemm(x, w, again, 2, again, n)
+        assert torch.equal(hidden, again)
+        inter = (n // 32) * 16
+        gate, up = w[:inter].contiguous(), w[inter:2 * inter].contiguous()
+        gu = ops16.prepare_gate_up(gate, up)
+        act = torch.full((m, inter), 9.0, device=DEV, dtype=torch.bfloat16)
+        fast._gemm(x, gu.weight, act, 3, None, 2 * inter)
+        g = x.double() @ gate.double().t()
+        u = x.double() @ up.double().t()
+        _close(act, g / (1 + torch.exp(-g)) * u, 2 ** -7, 1e-4, "pair split swiglu")
+        torch.cuda.synchronize()
+        assert int(fast.status.abs().sum()) == 0
+        # fewer than four k-blocks a pair, or a width that is not 128 or 256
+        short = _randn((m, 64 * 3 * splits), 94, torch.bfloat16)
+        with pytest.raises(RuntimeError, match="refused"):
+            fast._gemm(short, w[:, :short.shape[1]].contiguous(), out, 0, None, n)
+    finally:
+        fast.pair_padding, fast.pair_split_override = 0.8, 0
+
+
 def test_gemm_pair_refusals(ops16):
     fast = ops16.fast
     if not fast.use_pairs:
@@ -401,9 +448,13 @@ def test_the_dispatcher_takes_pairs_for_unsplit_products_at_widths_that_fill_the
         assert fast.pair_width(2048, 4096, False) == 240        # 144 tiles: two rounds
         assert fast.pair_width(2048, 24576, True) == 256 and fast.pair_width(2048, 151936, False) == 256
         # the narrow products of a layer stay split along K up to about 600 tokens
-        assert not fast.in_pairs(256, 4096, 4096) and not fast.in_pairs(512, 4096, 12288)
+        assert not fast.in_pairs(256, 4096, 4096) and not fast.in_pairs(256, 4096, 12288)
         assert fast.in_pairs(256, 24576, 4096) and fast.in_pairs(200, 151936, 4096) and fast.in_pairs(1024, 4096, 4096)
         assert fast.plan_product(300, 4096, 4096)[1] > 1 and fast.plan_product(2048, 4096, 4096) == (True, 1, 0, False)
+        # ... unless pairs can split as many ways: two pairs a tile, clusters of four blocks
+        assert fast.pair_split(256, 6144, 4096) == 2 and fast.in_pairs(256, 6144, 4096)
+        assert fast.pair_split(512, 4096, 12288) == 2 and fast.pair_split(256, 4096, 12288) == 1
+        assert fast.pair_split(2048, 4096, 4096) == 1 and fast.pair_split(300, 4096, 4096) == 1
     for m, n, swiglu in ((300, 1000, False), (129, 24576, True), (5000, 151936, False)):
         w = fast.pair_width(m, n, swiglu)
         assert 32 <= w <= 256 and w % (32 if swiglu else 16) == 0
