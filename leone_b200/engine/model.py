@@ -167,6 +167,17 @@ class Model:
 
     # -- forward ----------------------------------------------------------------------
     def forward(self, ctx) -> Optional[torch.Tensor]:
+        # every launch of the step goes to the stream that is current now (looked up once)
+        pin = getattr(self.rt.ops, "pin_stream", None)
+        if pin is None:
+            return self._forward(ctx)
+        pin(True)
+        try:
+            return self._forward(ctx)
+        finally:
+            pin(False)
+
+    def _forward(self, ctx) -> Optional[torch.Tensor]:
         rt = self.rt
         hidden = rt.buffer("hidden", ctx.n_tokens, self.hidden_size, torch.float32)
         self.embedding.forward(ctx, hidden)

@@ -93,6 +93,7 @@ class CudaOps:
         self.dtype = dtype
         self.core = ctypes.CDLL(ensure_built("core"))
         self.fast = None
+        self._pinned_stream = None
         if dtype == torch.bfloat16:
             from .fast import FastKernels
             self.fast = FastKernels(self.device)
@@ -117,7 +118,17 @@ class CudaOps:
 
     # -- helpers ------------------------------------------------------------------------
     def _stream(self):
+        if self._pinned_stream is not None:        # (a handle of 0, the default stream, is a valid pin)
+            return self._pinned_stream
         return c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def pin_stream(self, on: bool) -> None:
+        """Between ``pin_stream(True)`` and ``pin_stream(False)`` every launch goes to the stream
+        that was current at the first call: a step looks its stream up once, not once per launch."""
+        handle = c_void_p(torch.cuda.current_stream(self.device).cuda_stream) if on else None
+        self._pinned_stream = handle
+        if self.fast is not None:
+            self.fast.pin_stream(handle)
 
     def describe_status(self, word: int) -> str:
         return _STATUS_TEXT.get(word, "unknown status")

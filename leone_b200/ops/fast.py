@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_int, c_longlong, c_void_p, byref
+from ctypes import c_float, c_int, c_longlong, c_void_p, byref
 
 import torch
 
@@ -57,20 +57,36 @@ class FastKernels:
         self.pair_width_override = 0       # > 0: the tile width of every product on pairs (kernel_bench sets it)
         self.pair_split_override = 0       # > 0: pairs per tile of every product on pairs (tests set it)
         self._pair_widths = {}
+        self._plans = {}                   # _gemm's decisions per (sizes, arguments)
         self.decode_cluster_rounds = 1     # rounds of blocks a clustered decode attention may take (kernel_bench sets it)
         # (n, k) -> (splits, cluster): a forced split of an [n x k] product at decode sizes; empty
         # in the product, filled by kernel_bench's sweeps
         self.split_override = {}
         self.status = None
         self._attn_ws = None
+        self._pinned_stream = None
         self.use_tiled_attention = os.environ.get("LEONE_NO_TILED_ATTENTION", "0") != "1"
         # LEONE_NO_TC_ATTENTION=1 keeps prompt attention on the mma.sync kernel
         self.use_tc_attention = os.environ.get("LEONE_NO_TC_ATTENTION", "0") != "1"
         self.lib.leone_attention_decode_scratch.restype = ctypes.c_longlong
         self.lib.leone_gemm_pair_workspace_floats.restype = ctypes.c_longlong
 
+    def __setattr__(self, name, value):
+        # a switch changed (a test, the kernel bench): the remembered decisions may no longer hold
+        if not name.startswith("_") and "_plans" in self.__dict__:
+            self._plans.clear()
+            self._pair_widths.clear()
+        object.__setattr__(self, name, value)
+
     def _stream(self):
+        if self._pinned_stream is not None:        # (a handle of 0, the default stream, is a valid pin)
+            return self._pinned_stream
         return c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def pin_stream(self, handle) -> None:
+        """The stream every launch goes to until ``pin_stream(None)``: a step looks its stream up
+        once, not once per launch (the lookup costs microseconds, a step has hundreds of launches)."""
+        object.__setattr__(self, "_pinned_stream", handle)
 
     # -- split-K scratch ----------------------------------------------------------------
     def _retire(self, tensor) -> None:
@@ -271,47 +287,26 @@ class FastKernels:
         for the RMSNorm that follows it; ``norm_in=(ss, parts, eps)``: ``x`` is such an ``xn``
         and every output row is scaled by the norm's ``rsqrt(mean + eps)``."""
         m, k = x.shape
-        # on pairs of SMs unless the caller forces another form
-        pairs = token_major is None and splits in (None, 1) and not cluster and self.in_pairs(m, n_rows, k)
-        if pairs:
-            token_major, splits, full_tiles, cluster = True, 1, 0, False
-        elif token_major is None and splits is None and norm_in is None and norm_out is None:
-            token_major, splits, full_tiles, cluster = self.plan_product(m, n_rows, k)
-        token_major = bool(token_major) or m > 256
-        if token_major and not cluster:
-            splits, full_tiles = 1, 0
-        elif splits is None:
-            splits, full_tiles, cluster = self.choose_splits(m, n_rows, k)
+        key = (m, n_rows, k, epilogue, splits, full_tiles, cluster, token_major, norm_in is not None,
+               norm_out is not None)
+        plan = self._plans.get(key)
+        if plan is None:
+            plan = self._plans[key] = self._plan_gemm(*key)
+        pairs, token_major, splits, full_tiles, cluster, ws_floats, ws_counters, parts, width = plan
         ws = ct = None
-        if splits > 1 and not cluster:
-            tiles = int(self.lib.leone_gemm_tc_tiles(m, n_rows))
-            floats, counters = c_longlong(0), c_int(0)
-            self.lib.leone_gemm_tc_scratch(m, max(tiles - full_tiles, 0), splits, byref(floats), byref(counters))
-            ws, ct = self._scratch(floats.value, counters.value)
-        elif splits > 1 and token_major:
-            # the token-major form's partial tiles (128 tokens x 256 weight rows, fp32) cross
-            # between the blocks of a cluster through the workspace
-            # (one round of blocks at most, so the largest request is asked for at once and the
-            # buffer never grows with the step's size)
-            ws, _ = self._scratch(self.token_major_workspace_floats(), 0)
-        from ctypes import c_float
-        if norm_out is not None and norm_out[2].shape[0] != self.norm_parts(m, n_rows, pairs):
-            raise ValueError(f"the sums of squares have {norm_out[2].shape[0]} parts, this product leaves "
-                             f"{self.norm_parts(m, n_rows, pairs)}")
+        if ws_floats or ws_counters:
+            ws, ct = self._scratch(ws_floats, ws_counters)
+            if not ws_counters:
+                ct = None
+        if norm_out is not None and norm_out[2].shape[0] != parts:
+            raise ValueError(f"the sums of squares have {norm_out[2].shape[0]} parts, this product leaves {parts}")
         no = (None, None, None, 0) if norm_out is None else \
             (_ptr(norm_out[0]), _ptr(norm_out[1]), _ptr(norm_out[2]), norm_out[0].stride(0))
         ni = (None, 0, c_float(0.0)) if norm_in is None else (_ptr(norm_in[0]), int(norm_in[1]), c_float(norm_in[2]))
         if pairs:
-            # pairs of SMs on tiles of 256 tokens (gemm_pair.cu); a folded norm's parts follow the
-            # tile width (norm_parts)
-            ps = self.pair_split(m, n_rows, k) if norm_in is None and norm_out is None else 1
-            width, pws = self.pair_width(m, n_rows, epilogue == 3), None
-            if ps > 1:
-                width = 256
-                need = int(self.lib.leone_gemm_pair_workspace_floats(m, n_rows, width, ps))
-                pws, _ = self._scratch(max(self.token_major_workspace_floats(), need), 0)
+            # pairs of SMs on tiles of 256 tokens (gemm_pair.cu)
             code = self.lib.leone_gemm_pair(_ptr(x), _ptr(w), _ptr(out), _ptr(residual), m, n_rows, k,
-                                            x.stride(0), w.stride(0), out.stride(0), epilogue, width, ps, _ptr(pws),
+                                            x.stride(0), w.stride(0), out.stride(0), epilogue, width, splits, _ptr(ws),
                                             _ptr(self.status), self.sm_count, *no, *ni, self._stream())
             if code != 0:
                 raise RuntimeError(f"gemm_pair refused or failed with code {code} for m={m} n={n_rows} k={k}")
@@ -324,6 +319,44 @@ class FastKernels:
             raise RuntimeError(f"gemm_tc refused or failed with code {code} for m={m} n={n_rows} k={k} "
                                f"splits={splits} cluster={cluster} token_major={token_major}")
         return True
+
+    def _plan_gemm(self, m, n_rows, k, epilogue, splits, full_tiles, cluster, token_major, has_norm_in, has_norm_out):
+        """What :meth:`_gemm` does for one combination of sizes and arguments (kept per combination;
+        every change of a switch of this object forgets the plans): ``(pairs, token_major, splits,
+        full_tiles, cluster, workspace floats, counters, parts of a folded norm's sums, tile width
+        on pairs)``.  On pairs, ``splits`` is the number of pairs per tile."""
+        no_norm = not has_norm_in and not has_norm_out
+        # on pairs of SMs unless the caller forces another form
+        pairs = token_major is None and splits in (None, 1) and not cluster and self.in_pairs(m, n_rows, k)
+        if pairs:
+            ps = self.pair_split(m, n_rows, k) if no_norm else 1
+            width, floats = self.pair_width(m, n_rows, epilogue == 3), 0
+            if ps > 1:
+                width = 256
+                floats = max(self.token_major_workspace_floats(),
+                             int(self.lib.leone_gemm_pair_workspace_floats(m, n_rows, width, ps)))
+            return True, True, ps, 0, False, floats, 0, self.norm_parts(m, n_rows, True), width
+        if token_major is None and splits is None and no_norm:
+            token_major, splits, full_tiles, cluster = self.plan_product(m, n_rows, k)
+        token_major = bool(token_major) or m > 256
+        if token_major and not cluster:
+            splits, full_tiles = 1, 0
+        elif splits is None:
+            splits, full_tiles, cluster = self.choose_splits(m, n_rows, k)
+        floats = counters = 0
+        if splits > 1 and not cluster:
+            tiles = int(self.lib.leone_gemm_tc_tiles(m, n_rows))
+            f, c = c_longlong(0), c_int(0)
+            self.lib.leone_gemm_tc_scratch(m, max(tiles - full_tiles, 0), splits, byref(f), byref(c))
+            floats, counters = f.value, c.value
+        elif splits > 1 and token_major:
+            # the token-major form's partial tiles (128 tokens x 256 weight rows, fp32) cross
+            # between the blocks of a cluster through the workspace
+            # (one round of blocks at most, so the largest request is asked for at once and the
+            # buffer never grows with the step's size)
+            floats = self.token_major_workspace_floats()
+        return False, token_major, splits, full_tiles, bool(cluster), floats, counters, \
+            self.norm_parts(m, n_rows, False), 0
 
     def fuses_norm(self, m: int, n: int = 0, k: int = 0) -> bool:
         """Whether the products of ``m`` tokens carry an RMSNorm between them: decode-sized steps
