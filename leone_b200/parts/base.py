@@ -170,6 +170,7 @@ class Runtime:
         self.ops = ops
         self.max_tokens = max_tokens
         self._buffers: Dict[str, torch.Tensor] = {}
+        self._views: Dict[tuple, torch.Tensor] = {}
 
     def buffer(self, name: str, rows: int, cols: int, dtype: torch.dtype) -> torch.Tensor:
         """A scratch ``[rows, cols]`` view; one allocation per name, sized for ``max_tokens`` rows.
@@ -177,6 +178,10 @@ class Runtime:
         The contents are whatever the last user left.  Two buffers of different
         names never overlap; the same name is the same memory.
         """
+        vkey = (name, rows, cols, dtype)
+        view = self._views.get(vkey)                  # a step asks for the same views layer after layer
+        if view is not None:
+            return view
         cap_rows = max(rows, self.max_tokens)
         key = f"{name}/{cols}/{dtype}"
         buf = self._buffers.get(key)
@@ -185,7 +190,11 @@ class Runtime:
                 self._buffers[f"retired/{id(buf)}"] = buf    # a captured graph may still use it
             buf = torch.empty((cap_rows, cols), dtype=dtype, device=self.device)
             self._buffers[key] = buf
-        return buf[:rows]
+            self._views.clear()
+        if len(self._views) > 4096:
+            self._views.clear()
+        view = self._views[vkey] = buf[:rows]
+        return view
 
 
     def flat_buffer(self, name: str, numel: int, dtype: torch.dtype, reserve: int = 0) -> torch.Tensor:
