@@ -24,6 +24,12 @@ class FastKernels:
         self.device = torch.device(device)
         self.lib = ctypes.CDLL(ensure_built("bf16"))
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self._configure()
+        self.lib.leone_attention_decode_scratch.restype = ctypes.c_longlong
+        self.lib.leone_gemm_pair_workspace_floats.restype = ctypes.c_longlong
+
+    def _configure(self) -> None:
+        """The switches and rules of the dispatchers (everything but the device and the library)."""
         self._workspace = None
         self._retired = []
         self.min_scratch_floats = 1 << 20
@@ -68,8 +74,6 @@ class FastKernels:
         self.use_tiled_attention = os.environ.get("LEONE_NO_TILED_ATTENTION", "0") != "1"
         # LEONE_NO_TC_ATTENTION=1 keeps prompt attention on the mma.sync kernel
         self.use_tc_attention = os.environ.get("LEONE_NO_TC_ATTENTION", "0") != "1"
-        self.lib.leone_attention_decode_scratch.restype = ctypes.c_longlong
-        self.lib.leone_gemm_pair_workspace_floats.restype = ctypes.c_longlong
 
     def __setattr__(self, name, value):
         # a switch changed (a test, the kernel bench): the remembered decisions may no longer hold
@@ -267,11 +271,11 @@ class FastKernels:
 
     def plan_product(self, m: int, n: int, k: int):
         """``(token_major, splits, full_tiles, cluster)`` for a product without a folded norm."""
+        if self.in_pairs(m, n, k):
+            return True, 1, 0, False                 # on pairs of SMs (_gemm takes them where nothing is forced)
         s = self.token_major_split(m, n, k)
         if s > 1:
             return True, s, 0, True
-        if self.in_pairs(m):
-            return True, 1, 0, False                 # on pairs of SMs (_gemm takes them where nothing is forced)
         if self.token_major(m, n):
             return True, 1, 0, False
         return (False, *self.choose_splits(m, n, k))
