@@ -267,6 +267,8 @@ def main(argv=None) -> int:
                     help="gemm, layer-shapes: k-blocks of weights a decode-sized product asks the L2 for ahead of its stages")
     ap.add_argument("--pair-width", type=int, default=0,
                     help="gemm: tile width of the products on pairs of SMs (0: the dispatcher's choice)")
+    ap.add_argument("--pair-padding", type=float, default=None,
+                    help="gemm: what a pair's half tile may cost against a single block's tile (0: pairs at any size)")
     ap.add_argument("--pairs-from", type=int, default=None,
                     help="gemm: tokens from which products run on pairs of SMs")
     ap.add_argument("--decode-cluster-rounds", type=int, default=1,
@@ -282,6 +284,8 @@ def main(argv=None) -> int:
     ops.fast.pair_width_override = args.pair_width
     if args.pairs_from is not None:
         ops.fast.pairs_from = args.pairs_from
+    if args.pair_padding is not None:
+        ops.fast.pair_padding = args.pair_padding
     if args.l2_ahead is not None:
         ops.fast.lib.leone_gemm_tc_set_l2_ahead(args.l2_ahead)
     for item in filter(None, args.gemm_splits.split(",")):

@@ -193,9 +193,9 @@ class FastKernels:
         which up to about 600 tokens are split along K, do not (with tiles narrow enough to fill
         the pairs, all pairs read the same few token tiles at once, and that measured slower
         than the split: o_proj at 256 tokens 25.3 us against 18.7, down 61.7 against 37.1)."""
-        if not self._pairs_fit(m):
-            return False
-        return not (n and k and self.token_major_split(m, n, k) > 1 and self.pair_split(m, n, k) == 1)
+        if n and k and self.token_major_split(m, n, k) > 1:
+            return self.pair_split(m, n, k) > 1
+        return self._pairs_fit(m)
 
     def _pairs_fit(self, m: int) -> bool:
         return self.use_pairs and m >= self.pairs_from and 2 * -(-m // 256) * self.pair_padding <= -(-m // 128)
@@ -207,10 +207,13 @@ class FastKernels:
         k-blocks; 1: not split on pairs.  Only where the pairs can split as many ways as the single
         blocks would: with the same number of splits the pairs' k-loop wins (down at 512 tokens
         50.3 us against 56.6, qkv at 256 tokens 23.4 against 25.3), against four single-block
-        splits two pairs lose (o_proj at 256 tokens 25.1 us against 18.8, down 46.5 against 37.4)."""
+        splits two pairs lose (o_proj at 256 tokens 25.1 us against 18.8, down 46.5 against 37.4).
+        Also from 257 to 384 tokens, where unsplit products stay in single blocks (down at 320
+        tokens 48.6 us against 55.4)."""
         if self.pair_split_override:
             return self.pair_split_override
-        if not (self.use_pair_splits and self.use_clusters and self._pairs_fit(m)) or self.token_major_split(m, n, k) == 1:
+        if not (self.use_pair_splits and self.use_clusters and self.use_pairs and m >= self.pairs_from) or \
+                self.token_major_split(m, n, k) == 1:
             return 1
         tiles, k_blocks = -(-n // 256) * -(-m // 256), -(-k // 64)
         single = self.token_major_split(m, n, k)

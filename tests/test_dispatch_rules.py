@@ -67,7 +67,9 @@ def test_pair_splits_only_where_they_match_the_single_block_split(fast):
     assert fast.token_major_split(512, 4096, 12288) == 2 and fast.pair_split(512, 4096, 12288) == 2
     assert fast.token_major_split(256, 4096, 12288) == 4 and fast.pair_split(256, 4096, 12288) == 1
     assert fast.pair_split(2048, 4096, 4096) == 1              # not split at all
-    assert fast.pair_split(300, 4096, 4096) == 1               # 257 to 384 tokens: no pairs
+    # 257 to 384 tokens: unsplit products stay in single blocks, split ones take pairs
+    assert fast.pair_split(300, 4096, 4096) == 2 and fast.in_pairs(300, 4096, 4096) and not fast.in_pairs(300)
+    assert not fast.in_pairs(300, 24576, 4096) and fast.pair_split(300, 24576, 4096) == 1
     assert fast.plan_product(512, 4096, 12288) == (True, 1, 0, False) and fast.in_pairs(512, 4096, 12288)
     fast.use_pair_splits = False
     assert fast.pair_split(512, 4096, 12288) == 1 and not fast.in_pairs(512, 4096, 12288)
