@@ -291,7 +291,8 @@ def main(argv=None) -> int:
     for item in filter(None, args.gemm_splits.split(",")):
         shape, _, how = item.partition(":")
         n_, _, k_ = shape.partition("x")
-        ops.fast.split_override[(int(n_), int(k_))] = (int(how.lstrip("c")), how.startswith("c"))
+        ops.fast.split_override = {**ops.fast.split_override,      # (assigned, not changed in place: forgets the plans)
+                                   (int(n_), int(k_)): (int(how.lstrip("c")), how.startswith("c"))}
     peaks = measured_peaks()
     flush = torch.zeros(64 << 20, device=DEV) if args.flush else None
     rows = []
